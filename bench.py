@@ -1,0 +1,394 @@
+"""Headline benchmark: dispatch + combine latency of one MoE exchange, device-timed, max over ranks.
+
+Config (BASELINE.json): hidden 7168, 256 experts, top-8 distinct uniform expert ids, softmax weights,
+BF16 tokens ~ N(0,1), T tokens per rank (default 4096; ``--tokens`` or ``--sweep`` for 128..8192),
+``do_expand=True``, BF16 wire.  One "step" is one dispatch followed by one combine of the received
+rows (identity experts), i.e. the full exchange a MoE layer performs around its expert FFN.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+    python bench.py --impl reference ...     # the unmodified reference from baseline/_ref (dispatch only)
+
+Rank 0 prints one JSON line.  ``value`` is microseconds per step (lower is better), the maximum over
+ranks of a CUDA-event interval around exactly ``steps`` steps.  ``e2e`` is the same metric through the
+public API including, every step, the host->device copy of that step's inputs from pinned memory and
+a device->host read of a checksum of the combined output.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HIDDEN, EXPERTS, TOPK = 7168, 256, 8
+# reference dispatch-only latency on 8x H20D, ms (RESULTS_CONTROL_PROGRESS.md:31-40)
+PUBLISHED_MS = {16: 0.260, 32: 0.282, 64: 0.405, 128: 0.647, 256: 1.033, 512: 1.950, 1024: 3.681, 2048: 7.079,
+                4096: 13.558, 8192: 26.546}
+INPUT_SETS = 4  # rotated every step: 4 x T x 14 KiB of tokens (> L2 at T >= 2304); see "l2" in config
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--tokens", type=int, default=4096)
+    p.add_argument("--topk", type=int, default=TOPK)
+    p.add_argument("--sweep", action="store_true", help="also time T in {128,256,1024,4096,8192} (device-timed only)")
+    p.add_argument("--wire", default="bf16", choices=["bf16", "fp8_e4m3"])
+    p.add_argument("--channels", type=int, default=0)
+    p.add_argument("--engine", default="tma", choices=["tma", "vector"])
+    p.add_argument("--transport", default="peer", choices=["peer", "host_staged"])
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+def init_distributed(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    if world == 1 and "MASTER_ADDR" not in os.environ:
+        store = dist.FileStore(tempfile.mktemp(prefix="bench-store-"), 1)
+        dist.init_process_group("gloo", store=store, rank=0, world_size=1)
+    else:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    return rank, world, local_rank
+
+
+def make_routes(tokens, experts, topk, rank, seed=20261024):
+    """Distinct uniform expert ids, softmax weights (same generator recipe as the reference benchmark,
+    benchmarks/benchmark.py:35-41)."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed + rank * 104729 + tokens)
+    idx = torch.rand(tokens, experts, generator=g).topk(topk, dim=1).indices.to(torch.int64)
+    weights = torch.softmax(torch.randn(tokens, topk, generator=g), dim=1).to(torch.float32)
+    return idx.contiguous(), weights.contiguous()
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.device_index = device_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            self.path = tempfile.mktemp(prefix="clocks-", suffix=".csv")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.device_index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [v.strip() for v in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    clocks.append(float(f[1]))
+                    max_clock = float(f[2])
+                except ValueError:
+                    continue
+                for name, value in zip(names, f[5:9]):
+                    if value.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def max_over_ranks(value):
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([float(value)], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def default_channels(world, tokens):
+    # one CTA per channel; enough channels to keep NVLink and HBM busy at large T, few at small T
+    if tokens <= 256:
+        return 16
+    if tokens <= 1024:
+        return 32
+    return 64
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    from pcie_ep_b200 import HostStagedConfig, HostStagedEPBuffer
+
+    device = torch.device("cuda", local_rank)
+
+    def time_config(tokens, steps, warmup, want_e2e):
+        channels = args.channels or default_channels(world, tokens)
+        config = HostStagedConfig(channels=channels, stage=7 if args.wire != "bf16" else 6, wire_dtype=args.wire,
+                                  copy_engine=args.engine, transport=args.transport, timeout_ms=20000,
+                                  output_pool_size=2, tx_warps=4, rx_warps=8)
+        buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
+        g = torch.Generator().manual_seed(1234 + rank)
+        host_x = [torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16).pin_memory() for _ in range(INPUT_SETS)]
+        idx_cpu, w_cpu = make_routes(tokens, EXPERTS, args.topk, rank)
+        host_idx, host_w = idx_cpu.pin_memory(), w_cpu.pin_memory()
+        dev_x = [h.to(device) for h in host_x]
+        dev_idx, dev_w = host_idx.to(device), host_w.to(device)
+
+        def step(i):
+            recv_x, _, _, handle, _ = buffer.dispatch(dev_x[i % INPUT_SETS], dev_idx, dev_w, do_expand=True)
+            combined, _, _ = buffer.combine(recv_x, handle)
+            return combined, handle
+
+        for i in range(warmup):
+            out, handle = step(i)
+        torch.cuda.synchronize()
+        buffer.check_errors()
+        del out, handle
+        sampler = ClockSampler(local_rank)
+        dist.barrier()
+        torch.cuda.synchronize()
+        sampler.start()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            out, handle = step(i)
+            del out, handle
+        end.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        clocks = sampler.stop()
+        total_ms = start.elapsed_time(end)
+        # split: dispatch alone
+        dist.barrier()
+        torch.cuda.synchronize()
+        d0.record()
+        for i in range(steps):
+            res = buffer.dispatch(dev_x[i % INPUT_SETS], dev_idx, dev_w, do_expand=True)
+            del res
+        d1.record()
+        torch.cuda.synchronize()
+        dispatch_ms = d0.elapsed_time(d1)
+        buffer.check_errors()
+        result = {
+            "us_per_step": max_over_ranks(total_ms * 1000.0 / steps),
+            "dispatch_us": max_over_ranks(dispatch_ms * 1000.0 / steps),
+            "clocks": clocks,
+            "channels": channels,
+        }
+        if want_e2e:
+            checksum_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+            h2d = host_x[0].numel() * 2 + host_idx.numel() * 8 + host_w.numel() * 4
+            stage_x = torch.empty_like(dev_x[0])
+            stage_idx, stage_w = torch.empty_like(dev_idx), torch.empty_like(dev_w)
+
+            def e2e_step(i):
+                stage_x.copy_(host_x[i % INPUT_SETS], non_blocking=True)
+                stage_idx.copy_(host_idx, non_blocking=True)
+                stage_w.copy_(host_w, non_blocking=True)
+                recv_x, _, _, handle, _ = buffer.dispatch(stage_x, stage_idx, stage_w, do_expand=True)
+                combined, _, _ = buffer.combine(recv_x, handle)
+                checksum_host.copy_(combined[:, :8].float().sum().reshape(1), non_blocking=True)
+                torch.cuda.current_stream().synchronize()  # the step's result is read on the host
+                return float(checksum_host[0])
+
+            for i in range(min(3, warmup)):
+                e2e_step(i)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(steps):
+                e2e_step(i)
+            e1.record()
+            torch.cuda.synchronize()
+            result["e2e"] = {"value": max_over_ranks(e0.elapsed_time(e1) * 1000.0 / steps), "unit": "us/step",
+                             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4}
+            buffer.check_errors()
+        buffer.close()
+        return result
+
+    headline = time_config(args.tokens, args.steps, args.warmup, not args.no_e2e)
+    sweep = {}
+    if args.sweep:
+        for tokens in (128, 256, 1024, 4096, 8192):
+            if tokens == args.tokens:
+                sweep[str(tokens)] = {"us_per_step": headline["us_per_step"], "dispatch_us": headline["dispatch_us"]}
+                continue
+            r = time_config(tokens, args.steps, args.warmup, False)
+            sweep[str(tokens)] = {"us_per_step": r["us_per_step"], "dispatch_us": r["dispatch_us"], "channels": r["channels"]}
+    if rank == 0:
+        published = PUBLISHED_MS.get(args.tokens)
+        value = headline["us_per_step"]
+        line = {
+            "metric": "dispatch+combine us (device, max over ranks), H=7168, E=256, top-%d" % args.topk,
+            "value": round(value, 2),
+            "unit": "us/step",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": round(value / 1000.0, 5),
+            "higher_is_better": False,
+            "scaling": "weak",
+            "vs_baseline": round(value / (published * 1000.0), 5) if published else None,
+            "baseline_note": "published number is the reference's dispatch-only latency at 8 ranks on 8xH20D PCIe5; "
+                             "value here includes combine",
+            "dtype": "bf16" if args.wire == "bf16" else "bf16 in/out, fp8_e4m3 wire",
+            "data": "synthetic: x~N(0,1) bf16, distinct uniform top-k expert ids, softmax weights, random-init",
+            "config": {
+                "model": "DeepSeek-V3-shaped MoE exchange (hidden 7168, 256 experts, top-%d)" % args.topk,
+                "tokens_per_rank": args.tokens,
+                "global_batch": args.tokens * world,
+                "seq_len": 1,
+                "parallelism": f"ep{world}",
+                "do_expand": True,
+                "channels": headline["channels"],
+                "transport": args.transport,
+                "copy_engine": args.engine,
+                "l2": f"inputs rotate over {INPUT_SETS} token sets ({INPUT_SETS * args.tokens * HIDDEN * 2 >> 20} MiB) and each "
+                      "step writes staging + expanded rows well beyond the 126 MB L2",
+            },
+            "dispatch_us": round(headline["dispatch_us"], 2),
+            "combine_us": round(value - headline["dispatch_us"], 2),
+            "clocks": headline["clocks"],
+            "gpu_launches": 2 * args.steps,
+            "impl": "ours",
+        }
+        if "e2e" in headline:
+            line["e2e"] = {k: (round(v, 2) if isinstance(v, float) else v) for k, v in headline["e2e"].items()}
+        if sweep:
+            line["sweep"] = sweep
+        print(json.dumps(line), flush=True)
+
+
+def run_reference(args, rank, world, local_rank):
+    """The unmodified reference (copied to baseline/_ref) through its own public API: dispatch only."""
+    import torch
+    import torch.distributed as dist
+
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "pcie_ep" / "__init__.py").exists():
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is missing (reference not installed)"}))
+        return
+    os.environ["TORCH_CUDA_ARCH_LIST"] = "10.0"
+    os.environ.setdefault("TORCH_EXTENSIONS_DIR", str(ROOT / "baseline" / "_ref_build"))
+    sys.path.insert(0, str(ref_root))
+    try:
+        from pcie_ep import HostStagedConfig, HostStagedEPBuffer
+
+        device = torch.device("cuda", local_rank)
+        tokens = args.tokens
+        config = HostStagedConfig(timeout_ms=20000)
+        buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
+        g = torch.Generator().manual_seed(1234 + rank)
+        xs = [torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16).to(device) for _ in range(INPUT_SETS)]
+        idx_cpu, w_cpu = make_routes(tokens, EXPERTS, args.topk, rank)
+        idx, w = idx_cpu.to(device), w_cpu.to(device)
+        for i in range(args.warmup):
+            res = buffer.dispatch(xs[i % INPUT_SETS], idx, w, do_expand=True)
+            del res
+        torch.cuda.synchronize()
+        buffer.check_errors()
+        sampler = ClockSampler(local_rank)
+        dist.barrier()
+        torch.cuda.synchronize()
+        sampler.start()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(args.steps):
+            res = buffer.dispatch(xs[i % INPUT_SETS], idx, w, do_expand=True)
+            del res
+        end.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        clocks = sampler.stop()
+        buffer.check_errors()
+        value = max_over_ranks(start.elapsed_time(end) * 1000.0 / args.steps)
+        buffer.close()
+    except Exception as exc:  # noqa: BLE001 - reported as unavailable
+        reason = f"{type(exc).__name__}: {str(exc).splitlines()[0][:200] if str(exc) else ''}"
+        failures = [None] * world
+        try:
+            dist.all_gather_object(failures, reason)
+        except Exception:  # noqa: BLE001
+            pass
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": reason}))
+        return
+    if rank == 0:
+        published = PUBLISHED_MS.get(args.tokens)
+        print(json.dumps({
+            "impl": "reference",
+            "metric": "dispatch us (device, max over ranks), H=7168, E=256, top-%d; the reference has no combine" % args.topk,
+            "value": round(value, 2), "unit": "us/step", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(value / 1000.0, 5), "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": round(value / (published * 1000.0), 5) if published else None,
+            "dtype": "bf16", "data": "synthetic, same generator as the other arm",
+            "config": {"model": "DeepSeek-V3-shaped MoE dispatch", "tokens_per_rank": args.tokens,
+                       "global_batch": args.tokens * world, "seq_len": 1, "parallelism": f"ep{world}",
+                       "transport": "host_staged (reference default config)"},
+            "clocks": clocks, "gpu_launches": 8 * args.steps,
+        }), flush=True)
+
+
+def main():
+    args = parse_args()
+    rank, world, local_rank = init_distributed(args)
+    import torch.distributed as dist
+
+    try:
+        if args.impl == "reference":
+            run_reference(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

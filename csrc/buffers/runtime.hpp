@@ -1,0 +1,554 @@
+// Native runtime of one (virtual) EP rank: owns the device-resident rank constants, the result
+// pools, the routing-plan pool and the launch logic.  Counterpart of the reference's AdvancedRuntime
+// (csrc/buffers/advanced.hpp:43-550) for the peer-memory transport.
+//
+// Result pools (reference: csrc/buffers/advanced.hpp:296-336,402-418): `output_pool_size` eager sets
+// plus one graph set are allocated up front.  A set is busy while any of its tensors -- or a view of
+// one -- is still referenced from Python; when every set is busy, dispatch fails with "pool exhausted"
+// instead of waiting or allocating.  Routing plans come from a pool of the same size (+1 for graphs).
+#pragma once
+
+#include <cstdint>
+#include <memory>
+#include <mutex>
+#include <optional>
+#include <string>
+#include <vector>
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "../comm/peer_memory.hpp"
+#include "../kernels/launch.hpp"
+
+namespace bep {
+
+namespace py = pybind11;
+
+// True when nothing outside this runtime can still reach the tensor's memory.  Pool tensors are never
+// handed out themselves: Python only ever receives aliases (distinct tensor objects sharing the
+// storage), so "some result tensor or a view of it is alive" is exactly "the storage has another
+// owner".  This needs nothing of PyTorch's Python-object bookkeeping (the reference's check does:
+// csrc/buffers/advanced.hpp:402-418).
+inline bool tensor_unowned(const at::Tensor& t) {
+    if (!t.defined()) return true;
+    return t.use_count() == 1 && t.unsafeGetTensorImpl()->unsafe_storage().use_count() == 1;
+}
+
+struct TensorRefs {
+    std::int64_t tensor_use_count, storage_use_count;
+};
+inline TensorRefs tensor_refs(const at::Tensor& t) {
+    return {static_cast<std::int64_t>(t.use_count()),
+            static_cast<std::int64_t>(t.unsafeGetTensorImpl()->unsafe_storage().use_count())};
+}
+
+struct RuntimeOptions {
+    int channels = 32;
+    int payload_slots = 0;
+    int timeout_ms = 30000;
+    bool wire_fp8 = false;
+    bool use_tma = true;
+    int tx_warps = 4;
+    int rx_warps = 6;
+    int output_pool_size = 3;
+    bool enable_graph = false;
+    bool enable_combine = true;
+    std::uint64_t delay_meta_ns = 0, delay_tx_ns = 0, delay_rx_ns = 0, delay_scatter_ns = 0;
+
+    static RuntimeOptions parse(const py::dict& d) {
+        RuntimeOptions o;
+        auto get = [&d](const char* key, auto fallback) {
+            using T = decltype(fallback);
+            return d.contains(key) ? d[key].cast<T>() : fallback;
+        };
+        o.channels = get("channels", o.channels);
+        o.payload_slots = get("payload_slots", o.payload_slots);
+        o.timeout_ms = get("timeout_ms", o.timeout_ms);
+        o.wire_fp8 = get("wire_dtype", std::string("bf16")) == "fp8_e4m3";
+        o.use_tma = get("copy_engine", std::string("tma")) == "tma";
+        o.tx_warps = get("tx_warps", o.tx_warps);
+        o.rx_warps = get("rx_warps", o.rx_warps);
+        o.output_pool_size = get("output_pool_size", o.output_pool_size);
+        o.enable_graph = get("enable_graph", o.enable_graph);
+        o.enable_combine = get("enable_combine", o.enable_combine);
+        o.delay_meta_ns = get("metadata_delay_ns", std::uint64_t{0});
+        o.delay_tx_ns = get("tx_delay_ns", std::uint64_t{0});
+        o.delay_rx_ns = get("rx_delay_ns", std::uint64_t{0});
+        o.delay_scatter_ns = get("scatter_delay_ns", std::uint64_t{0});
+        if (o.channels < 1 || o.channels > kMaxChannels) throw std::invalid_argument("channels out of range");
+        if (o.tx_warps < 1 || o.rx_warps < 1 || 1 + o.tx_warps + o.rx_warps > kMaxWarps)
+            throw std::invalid_argument("1 + tx_warps + rx_warps must not exceed 16");
+        if (o.output_pool_size < 2 || o.output_pool_size > 8) throw std::invalid_argument("output_pool_size must be in [2,8]");
+        if (o.timeout_ms < 1) throw std::invalid_argument("timeout_ms must be positive");
+        return o;
+    }
+};
+
+// One routing plan: what the layout phase computed for one topk_idx, reusable while the routing
+// tensor is unchanged (reference: AdvancedLayout, csrc/buffers/advanced.hpp:331-336).
+struct Layout {
+    at::Tensor mask, slot, expert_ord, counts;
+    int num_tokens = -1;
+    int alignment = 0;
+    bool expand = false;
+    bool valid = false;  // filled by a completed (enqueued) dispatch
+};
+
+struct OutputSet {
+    at::Tensor recv_x, recv_idx, recv_w, source_meta, comb_map, recv_chan_counts;
+    at::Tensor unique_count, expanded_count, expert_counts, expert_offsets, expert_prefix, source_offsets;
+    at::Tensor source_expert_prefix, error, stats, timestamps, prefix_tx_ts;
+    at::Tensor combine_error, combine_stats;
+
+    std::vector<const at::Tensor*> all() const {
+        return {&recv_x, &recv_idx, &recv_w, &source_meta, &comb_map, &recv_chan_counts, &unique_count,
+                &expanded_count, &expert_counts, &expert_offsets, &expert_prefix, &source_offsets,
+                &source_expert_prefix, &error, &stats, &timestamps, &prefix_tx_ts, &combine_error, &combine_stats};
+    }
+    bool free() const {
+        for (const at::Tensor* t : all())
+            if (!tensor_unowned(*t)) return false;
+        return true;
+    }
+};
+
+struct PreparedDispatch {
+    DispatchArgs args;
+    py::dict result;
+};
+struct PreparedCombine {
+    CombineArgs args;
+    at::Tensor out;
+};
+
+class Runtime {
+   public:
+    Runtime(int rank, int num_ranks, int num_max_tokens, int hidden, int num_topk, int num_experts,
+            const py::dict& options, const std::vector<std::int64_t>& segment_pointers, int device)
+        : rank_(rank), device_(device), options_(RuntimeOptions::parse(options)) {
+        if (num_ranks < 1 || num_ranks > kMaxRanks) throw std::invalid_argument("num_ranks must be in [1,16]");
+        if (rank < 0 || rank >= num_ranks) throw std::invalid_argument("rank out of range");
+        if (num_topk < 1 || num_topk > kMaxTopk) throw std::invalid_argument("num_topk must be in [1,32]");
+        if (num_experts < num_ranks || num_experts > kMaxExperts || num_experts % num_ranks)
+            throw std::invalid_argument("num_experts must be a multiple of num_ranks, at most 4096");
+        if (hidden < 1 || num_max_tokens < 1) throw std::invalid_argument("hidden and num_max_tokens must be positive");
+        if (static_cast<int>(segment_pointers.size()) != num_ranks) throw std::invalid_argument("one segment pointer per rank");
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+        lay_ = make_segment_layout(num_ranks, options_.channels, num_experts, num_topk, hidden, num_max_tokens,
+                                   options_.payload_slots, options_.enable_combine);
+        const bool vec_ok = (hidden * 2) % 16 == 0;
+        use_tma_ = options_.use_tma && vec_ok;
+        threads_ = 32 * (1 + options_.tx_warps + options_.rx_warps);
+        smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, use_tma_);
+        int max_optin = 0;
+        cuda_check(cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device), "query shared memory");
+        if (use_tma_ && smem_ > static_cast<std::size_t>(max_optin)) {
+            // too many row buffers for this hidden size: fall back to the register path
+            use_tma_ = false;
+            smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, false);
+        }
+        if (smem_ > static_cast<std::size_t>(max_optin)) throw std::runtime_error("dispatch kernel needs more shared memory than the device offers");
+        cuda_check(configure_kernels(smem_), "configure kernels");
+
+        const auto i32 = at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device);
+        const auto i64 = at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device);
+        const auto u8 = at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device);
+        const int P = num_ranks, C = options_.channels, E = num_experts, K = num_topk;
+        epochs_ = at::zeros({4}, i64);
+        grid_bar_ = at::zeros({2}, i64);
+        done_ctas_ = at::zeros({2}, i64);
+        block_hist_ = at::zeros({static_cast<std::int64_t>(C) * (E + P)}, i32);
+        sticky_ = at::zeros({8}, i32);
+        chan_stats_ = at::zeros({2, C, 10}, i64);
+        rank_const_ = at::zeros({static_cast<std::int64_t>(sizeof(RankConst))}, u8);
+
+        rc_ = RankConst{};
+        rc_.lay = lay_;
+        for (int r = 0; r < P; ++r) rc_.seg[r] = reinterpret_cast<std::uint8_t*>(segment_pointers[r]);
+        rc_.rank = rank;
+        rc_.ring_mode = lay_.slots < lay_.slots_full ? 1 : 0;
+        rc_.wire_fp8 = options_.wire_fp8 ? 1 : 0;
+        rc_.use_tma = use_tma_ ? 1 : 0;
+        rc_.vec_ok = vec_ok ? 1 : 0;
+        rc_.tx_warps = options_.tx_warps;
+        rc_.rx_warps = options_.rx_warps;
+        rc_.unique_cap = P * num_max_tokens;
+        rc_.expanded_cap = P * num_max_tokens * std::min(K, lay_.num_local_experts) + lay_.num_local_experts * 255;
+        rc_.timeout_ns = static_cast<std::uint64_t>(options_.timeout_ms) * 1000000ull;
+        rc_.epochs = reinterpret_cast<std::uint64_t*>(epochs_.data_ptr<std::int64_t>());
+        rc_.grid_bar = reinterpret_cast<unsigned long long*>(grid_bar_.data_ptr<std::int64_t>());
+        rc_.done_ctas = reinterpret_cast<unsigned long long*>(done_ctas_.data_ptr<std::int64_t>());
+        rc_.block_hist = block_hist_.data_ptr<int>();
+        rc_.sticky = sticky_.data_ptr<int>();
+        rc_.chan_stats = chan_stats_.data_ptr<std::int64_t>();
+        rc_.delay_meta_ns = options_.delay_meta_ns;
+        rc_.delay_tx_ns = options_.delay_tx_ns;
+        rc_.delay_rx_ns = options_.delay_rx_ns;
+        rc_.delay_scatter_ns = options_.delay_scatter_ns;
+        rc_.test_skip_done_to = -1;
+        upload_constants();
+
+        const int sets = options_.output_pool_size + (options_.enable_graph ? 1 : 0);
+        for (int i = 0; i < sets; ++i) {
+            pools_.push_back(make_output_set());
+            plans_.push_back(make_layout());
+        }
+    }
+
+    // ---- geometry -----------------------------------------------------------------------------
+    int rank() const { return rank_; }
+    int channels() const { return options_.channels; }
+    int threads() const { return threads_; }
+    std::size_t shared_bytes() const { return smem_; }
+    bool uses_tma() const { return use_tma_; }
+    const SegmentLayout& layout() const { return lay_; }
+    int unique_capacity() const { return rc_.unique_cap; }
+    int expanded_capacity() const { return rc_.expanded_cap; }
+
+    // ---- dispatch -------------------------------------------------------------------------------
+    PreparedDispatch prepare_dispatch(const at::Tensor& x, const at::Tensor& topk_idx,
+                                      const std::optional<at::Tensor>& topk_weights, int alignment, bool expand,
+                                      bool zero_padding, const std::shared_ptr<Layout>& cached, bool graph_pool) {
+        check_open();
+        validate_inputs(x, topk_idx, topk_weights, alignment, expand, zero_padding);
+        const int T = static_cast<int>(x.size(0));
+        OutputSet& out = select_output(graph_pool);
+        std::shared_ptr<Layout> plan;
+        if (cached) {
+            if (!cached->valid || cached->num_tokens != T || cached->alignment != alignment || cached->expand != expand)
+                throw std::invalid_argument("cached layout does not match this dispatch");
+            plan = cached;
+        } else {
+            plan = select_plan(graph_pool);
+            plan->num_tokens = T;
+            plan->alignment = alignment;
+            plan->expand = expand;
+            plan->valid = true;
+        }
+        PreparedDispatch p;
+        DispatchArgs& a = p.args;
+        a = DispatchArgs{};
+        a.rc = reinterpret_cast<const RankConst*>(rank_const_.data_ptr<std::uint8_t>());
+        a.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
+        a.topk_idx = topk_idx.data_ptr<std::int64_t>();
+        a.topk_w = topk_weights.has_value() ? topk_weights->data_ptr<float>() : nullptr;
+        a.num_tokens = T;
+        a.do_expand = expand ? 1 : 0;
+        a.alignment = alignment;
+        a.zero_padding = zero_padding ? 1 : 0;
+        a.cached = cached ? 1 : 0;
+        a.plan_mask = reinterpret_cast<std::uint32_t*>(plan->mask.data_ptr<int>());
+        a.plan_slot = plan->slot.data_ptr<int>();
+        a.plan_expert_ord = plan->expert_ord.data_ptr<int>();
+        a.plan_counts = plan->counts.data_ptr<int>();
+        a.recv_x = reinterpret_cast<__nv_bfloat16*>(out.recv_x.data_ptr());
+        a.recv_idx = out.recv_idx.data_ptr<std::int64_t>();
+        a.recv_w = out.recv_w.data_ptr<float>();
+        a.source_meta = out.source_meta.data_ptr<std::int64_t>();
+        a.comb_map = out.comb_map.data_ptr<int>();
+        a.recv_chan_counts = out.recv_chan_counts.data_ptr<int>();
+        a.unique_count = out.unique_count.data_ptr<std::int64_t>();
+        a.expanded_count = out.expanded_count.data_ptr<std::int64_t>();
+        a.expert_counts = out.expert_counts.data_ptr<int>();
+        a.expert_offsets = out.expert_offsets.data_ptr<int>();
+        a.expert_prefix = out.expert_prefix.data_ptr<int>();
+        a.source_offsets = out.source_offsets.data_ptr<int>();
+        a.source_expert_prefix = out.source_expert_prefix.data_ptr<int>();
+        a.error = out.error.data_ptr<int>();
+        a.stats = out.stats.data_ptr<std::int64_t>();
+        a.timestamps = out.timestamps.data_ptr<std::int64_t>();
+        a.prefix_tx_ts = out.prefix_tx_ts.data_ptr<std::int64_t>();
+        p.result = make_result(out, plan, expand, T);
+        return p;
+    }
+
+    py::dict dispatch(const at::Tensor& x, const at::Tensor& topk_idx, const std::optional<at::Tensor>& topk_weights,
+                      int alignment, bool expand, bool zero_padding, const std::shared_ptr<Layout>& cached,
+                      bool graph_pool) {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
+        PreparedDispatch p = prepare_dispatch(x, topk_idx, topk_weights, alignment, expand, zero_padding, cached, graph_pool);
+        DispatchLaunch launch{};
+        launch.num_virtual = 1;
+        launch.r[0] = p.args;
+        cuda_check(launch_dispatch(launch, options_.channels, threads_, smem_, at::cuda::getCurrentCUDAStream(device_)),
+                   "dispatch launch");
+        return p.result;
+    }
+
+    // ---- combine --------------------------------------------------------------------------------
+    PreparedCombine prepare_combine(const at::Tensor& y, const py::dict& dispatch_result, bool weighted,
+                                    const std::optional<at::Tensor>& out_opt) {
+        check_open();
+        if (!options_.enable_combine) throw std::runtime_error("this buffer was built with enable_combine=False");
+        auto layout = dispatch_result["_layout"].cast<std::shared_ptr<Layout>>();
+        if (!layout || !layout->valid) throw std::invalid_argument("dispatch result carries no routing plan");
+        const bool expand = dispatch_result["_expand"].cast<bool>();
+        const int cap = expand ? rc_.expanded_cap : rc_.unique_cap;
+        if (!y.is_cuda() || y.get_device() != device_ || y.scalar_type() != at::kBFloat16 || !y.is_contiguous() ||
+            y.dim() != 2 || y.size(1) != lay_.hidden || y.size(0) < 1 || y.size(0) > cap)
+            throw std::invalid_argument("expert outputs must be contiguous CUDA BF16 [rows <= capacity, hidden]");
+        const int T = layout->num_tokens;
+        at::Tensor out = out_opt.has_value()
+                             ? *out_opt
+                             : at::empty({T, lay_.hidden}, at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device_));
+        if (!out.is_cuda() || out.scalar_type() != at::kBFloat16 || !out.is_contiguous() || out.dim() != 2 ||
+            out.size(0) != T || out.size(1) != lay_.hidden)
+            throw std::invalid_argument("combine output must be contiguous CUDA BF16 [T, hidden]");
+        PreparedCombine p;
+        p.out = out;
+        CombineArgs& a = p.args;
+        a = CombineArgs{};
+        a.rc = reinterpret_cast<const RankConst*>(rank_const_.data_ptr<std::uint8_t>());
+        a.y = reinterpret_cast<const __nv_bfloat16*>(y.data_ptr());
+        a.comb_map = dispatch_result["comb_map"].cast<at::Tensor>().data_ptr<int>();
+        a.recv_chan_counts = dispatch_result["recv_chan_counts"].cast<at::Tensor>().data_ptr<int>();
+        a.plan_mask = reinterpret_cast<const std::uint32_t*>(layout->mask.data_ptr<int>());
+        a.num_tokens = T;
+        a.weighted = weighted ? 1 : 0;
+        a.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+        a.error = dispatch_result["combine_error"].cast<at::Tensor>().data_ptr<int>();
+        a.stats = dispatch_result["combine_stats"].cast<at::Tensor>().data_ptr<std::int64_t>();
+        return p;
+    }
+
+    at::Tensor combine(const at::Tensor& y, const py::dict& dispatch_result, bool weighted,
+                       const std::optional<at::Tensor>& out_opt) {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
+        PreparedCombine p = prepare_combine(y, dispatch_result, weighted, out_opt);
+        CombineLaunch launch{};
+        launch.num_virtual = 1;
+        launch.r[0] = p.args;
+        cuda_check(launch_combine(launch, options_.channels, threads_, at::cuda::getCurrentCUDAStream(device_)),
+                   "combine launch");
+        return p.out;
+    }
+
+    // ---- diagnostics / test hooks (reference: csrc/buffers/advanced.hpp:158-227) -------------
+    py::dict pool_debug() const {
+        py::dict d;
+        py::list busy;
+        for (const auto& set : pools_) busy.append(!set.free());
+        d["output_busy"] = busy;
+        py::list plan_busy;
+        for (const auto& plan : plans_) plan_busy.append(plan.use_count() != 1);
+        d["plan_busy"] = plan_busy;
+        d["output_sets"] = static_cast<int>(pools_.size());
+        d["graph_set"] = options_.enable_graph;
+        return d;
+    }
+    void set_test_delays(std::uint64_t meta, std::uint64_t tx, std::uint64_t rx, std::uint64_t scatter) {
+        rc_.delay_meta_ns = meta;
+        rc_.delay_tx_ns = tx;
+        rc_.delay_rx_ns = rx;
+        rc_.delay_scatter_ns = scatter;
+        upload_constants();
+    }
+    void set_test_prefix_delay_ns(std::uint64_t ns) {
+        rc_.delay_prefix_ns = ns;
+        upload_constants();
+    }
+    void set_test_skip_counts_ack_source(int peer) {
+        rc_.test_skip_done_to = peer;
+        upload_constants();
+    }
+    void set_test_withhold_counts(bool on) {
+        rc_.test_withhold_counts = on ? 1 : 0;
+        upload_constants();
+    }
+    void set_timeout_ms(int ms) {
+        rc_.timeout_ns = static_cast<std::uint64_t>(ms) * 1000000ull;
+        upload_constants();
+    }
+    at::Tensor sticky_error() const { return sticky_; }
+    at::Tensor epochs() const { return epochs_; }
+
+    void close() {
+        pools_.clear();
+        plans_.clear();
+        closed_ = true;
+    }
+    bool closed() const { return closed_; }
+
+   private:
+    void check_open() const {
+        if (closed_) throw std::runtime_error("runtime is closed");
+    }
+
+    void upload_constants() {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
+        // stream-ordered after everything already queued on the current stream
+        cuda_check(cudaMemcpyAsync(rank_const_.data_ptr<std::uint8_t>(), &rc_, sizeof(RankConst), cudaMemcpyHostToDevice,
+                                   at::cuda::getCurrentCUDAStream(device_)),
+                   "upload rank constants");
+        cuda_check(cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_)), "upload rank constants");
+    }
+
+    void validate_inputs(const at::Tensor& x, const at::Tensor& idx, const std::optional<at::Tensor>& w, int alignment,
+                         bool expand, bool zero_padding) const {
+        auto on_device = [this](const at::Tensor& t) { return t.is_cuda() && t.get_device() == device_; };
+        if (!on_device(x) || x.scalar_type() != at::kBFloat16 || !x.is_contiguous() || x.dim() != 2 || x.size(1) != lay_.hidden)
+            throw std::invalid_argument("x must be contiguous CUDA BF16 [T, hidden] on the buffer's device");
+        if (x.size(0) > lay_.num_max_tokens) throw std::invalid_argument("token count exceeds num_max_tokens_per_rank");
+        if (!on_device(idx) || idx.scalar_type() != at::kLong || !idx.is_contiguous() || idx.dim() != 2 ||
+            idx.size(0) != x.size(0) || idx.size(1) != lay_.num_topk)
+            throw std::invalid_argument("topk_idx must be contiguous CUDA int64 [T, num_topk]");
+        if (w.has_value()) {
+            if (!on_device(*w) || w->scalar_type() != at::kFloat || !w->is_contiguous() || w->sizes() != idx.sizes())
+                throw std::invalid_argument("topk_weights must be contiguous CUDA float32 [T, num_topk]");
+        }
+        if (alignment < 1 || alignment > kMaxAlignment) throw std::invalid_argument("expert_alignment must be in [1,256]");
+        if (zero_padding && !expand) throw std::invalid_argument("do_zero_padding requires do_expand");
+    }
+
+    OutputSet make_output_set() const {
+        const auto bf16 = at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device_);
+        const auto i32 = at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device_);
+        const auto i64 = at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device_);
+        const auto f32 = at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device_);
+        const std::int64_t P = lay_.num_ranks, C = lay_.num_channels, K = lay_.num_topk, El = lay_.num_local_experts;
+        const std::int64_t ecap = rc_.expanded_cap, ucap = rc_.unique_cap;
+        const std::int64_t rows = std::max(ecap, ucap);
+        const std::int64_t scalars = std::max(ecap, ucap * K);
+        OutputSet s;
+        s.recv_x = at::empty({rows, lay_.hidden}, bf16);
+        s.recv_idx = at::empty({scalars}, i64);
+        s.recv_w = at::empty({scalars}, f32);
+        s.source_meta = at::empty({rows, 3}, i64);
+        s.comb_map = at::zeros({P * C * lay_.slots_full, 2 + 2 * K}, i32);
+        s.recv_chan_counts = at::zeros({P, C}, i32);
+        s.unique_count = at::zeros({1}, i64);
+        s.expanded_count = at::zeros({1}, i64);
+        s.expert_counts = at::zeros({El}, i32);
+        s.expert_offsets = at::zeros({El + 1}, i32);
+        s.expert_prefix = at::zeros({El}, i32);
+        s.source_offsets = at::zeros({P + 1}, i32);
+        s.source_expert_prefix = at::zeros({P, El}, i32);
+        s.error = at::zeros({8}, i32);
+        s.stats = at::zeros({8}, i64);
+        s.timestamps = at::zeros({2}, i64);
+        s.prefix_tx_ts = at::zeros({C + 1, 2}, i64);
+        s.combine_error = at::zeros({8}, i32);
+        s.combine_stats = at::zeros({8}, i64);
+        return s;
+    }
+
+    std::shared_ptr<Layout> make_layout() const {
+        const auto i32 = at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device_);
+        const std::int64_t P = lay_.num_ranks, C = lay_.num_channels, K = lay_.num_topk, E = lay_.num_experts;
+        const std::int64_t T = lay_.num_max_tokens;
+        auto plan = std::make_shared<Layout>();
+        plan->mask = at::zeros({T}, i32);
+        plan->slot = at::zeros({T, P}, i32);
+        plan->expert_ord = at::zeros({T, K}, i32);
+        plan->counts = at::zeros({P + E + C * P}, i32);
+        return plan;
+    }
+
+    OutputSet& select_output(bool graph_pool) {
+        if (graph_pool) {
+            if (!options_.enable_graph) throw std::runtime_error("graph pool requires enable_graph=True");
+            return pools_.back();
+        }
+        for (int i = 0; i < options_.output_pool_size; ++i) {
+            const int index = (next_pool_ + i) % options_.output_pool_size;
+            if (pools_[index].free()) {
+                next_pool_ = (index + 1) % options_.output_pool_size;
+                return pools_[index];
+            }
+        }
+        throw std::runtime_error("output pool exhausted: every preallocated result set is still referenced");
+    }
+
+    std::shared_ptr<Layout> select_plan(bool graph_pool) {
+        if (graph_pool) return plans_.back();
+        for (int i = 0; i < options_.output_pool_size; ++i) {
+            if (plans_[i].use_count() == 1) return plans_[i];
+        }
+        throw std::runtime_error("routing plan pool exhausted: every plan is still referenced by a handle or cached layout");
+    }
+
+    py::dict make_result(const OutputSet& s, const std::shared_ptr<Layout>& plan, bool expand, int num_tokens) const {
+        py::dict d;
+        const std::int64_t K = lay_.num_topk;
+        if (expand) {
+            d["recv_x"] = s.recv_x.narrow(0, 0, rc_.expanded_cap);
+            d["recv_topk_idx"] = s.recv_idx.narrow(0, 0, rc_.expanded_cap);
+            d["recv_topk_weights"] = s.recv_w.narrow(0, 0, rc_.expanded_cap);
+            d["source_meta"] = s.source_meta.narrow(0, 0, rc_.expanded_cap);
+        } else {
+            d["recv_x"] = s.recv_x.narrow(0, 0, rc_.unique_cap);
+            d["recv_topk_idx"] = s.recv_idx.narrow(0, 0, rc_.unique_cap * K).view({rc_.unique_cap, K});
+            d["recv_topk_weights"] = s.recv_w.narrow(0, 0, rc_.unique_cap * K).view({rc_.unique_cap, K});
+            d["source_meta"] = s.source_meta.narrow(0, 0, rc_.unique_cap);
+        }
+        d["comb_map"] = at::alias(s.comb_map);
+        d["recv_chan_counts"] = at::alias(s.recv_chan_counts);
+        d["unique_count"] = at::alias(s.unique_count);
+        d["expanded_count"] = at::alias(s.expanded_count);
+        d["expert_counts"] = at::alias(s.expert_counts);
+        d["expert_offsets"] = at::alias(s.expert_offsets);
+        d["expert_prefix"] = at::alias(s.expert_prefix);
+        d["source_offsets"] = at::alias(s.source_offsets);
+        d["source_expert_prefix"] = at::alias(s.source_expert_prefix);
+        d["error"] = at::alias(s.error);
+        d["stats"] = at::alias(s.stats);
+        d["transport_timestamps_ns"] = at::alias(s.timestamps);
+        d["prefix_tx_timestamps_ns"] = at::alias(s.prefix_tx_ts);
+        d["combine_error"] = at::alias(s.combine_error);
+        d["combine_stats"] = at::alias(s.combine_stats);
+        d["_layout"] = plan;
+        d["_expand"] = expand;
+        d["_num_tokens"] = num_tokens;
+        return d;
+    }
+
+    int rank_, device_;
+    RuntimeOptions options_;
+    SegmentLayout lay_{};
+    RankConst rc_{};
+    bool use_tma_ = false;
+    int threads_ = 0;
+    std::size_t smem_ = 0;
+    at::Tensor epochs_, grid_bar_, done_ctas_, block_hist_, sticky_, chan_stats_, rank_const_;
+    std::vector<OutputSet> pools_;
+    std::vector<std::shared_ptr<Layout>> plans_;
+    int next_pool_ = 0;
+    bool closed_ = false;
+};
+
+// Several virtual ranks of one process in one cooperative launch (tests, single-GPU development).
+inline void launch_dispatch_group(const std::vector<std::shared_ptr<Runtime>>& runtimes,
+                                  const std::vector<PreparedDispatch>& prepared, int device) {
+    if (runtimes.empty() || runtimes.size() != prepared.size() || runtimes.size() > kMaxVirtualRanks)
+        throw std::invalid_argument("between 1 and 8 virtual ranks per launch");
+    DispatchLaunch launch{};
+    launch.num_virtual = static_cast<int>(runtimes.size());
+    for (std::size_t i = 0; i < runtimes.size(); ++i) {
+        if (runtimes[i]->channels() != runtimes[0]->channels() || runtimes[i]->threads() != runtimes[0]->threads() ||
+            runtimes[i]->shared_bytes() != runtimes[0]->shared_bytes())
+            throw std::invalid_argument("virtual ranks must share one configuration");
+        launch.r[i] = prepared[i].args;
+    }
+    const int resident = dispatch_resident_ctas(runtimes[0]->threads(), runtimes[0]->shared_bytes());
+    if (runtimes[0]->channels() * launch.num_virtual > resident)
+        throw std::runtime_error("channels * virtual_ranks exceeds the number of co-resident CTAs on this GPU");
+    cuda_check(launch_dispatch(launch, runtimes[0]->channels(), runtimes[0]->threads(), runtimes[0]->shared_bytes(),
+                               at::cuda::getCurrentCUDAStream(device)),
+               "dispatch launch");
+}
+
+inline void launch_combine_group(const std::vector<std::shared_ptr<Runtime>>& runtimes,
+                                 const std::vector<PreparedCombine>& prepared, int device) {
+    if (runtimes.empty() || runtimes.size() != prepared.size() || runtimes.size() > kMaxVirtualRanks)
+        throw std::invalid_argument("between 1 and 8 virtual ranks per launch");
+    CombineLaunch launch{};
+    launch.num_virtual = static_cast<int>(runtimes.size());
+    for (std::size_t i = 0; i < runtimes.size(); ++i) launch.r[i] = prepared[i].args;
+    cuda_check(launch_combine(launch, runtimes[0]->channels(), runtimes[0]->threads(),
+                              at::cuda::getCurrentCUDAStream(device)),
+               "combine launch");
+}
+
+}  // namespace bep

@@ -1,0 +1,80 @@
+// The CUDA translation unit: every __global__ kernel of the library and its launch wrapper.
+#include "launch.hpp"
+
+#include <algorithm>
+#include <mutex>
+
+#include "combine.cuh"
+#include "dispatch.cuh"
+
+namespace bep {
+
+std::size_t dispatch_shared_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma) {
+    return dispatch_smem_bytes(lay, tx_warps, rx_warps, use_tma);
+}
+
+cudaError_t configure_kernels(std::size_t dispatch_smem) {
+    // One attribute per kernel per process: several buffers may be alive, so only ever raise it
+    // (reference: configure_shared_memory, csrc/buffers/advanced.hpp:339-365).
+    static std::mutex mutex;
+    static std::size_t current[64] = {0};
+    std::lock_guard<std::mutex> guard(mutex);
+    int device = 0;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) return status;
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    if (dispatch_smem > current[device]) {
+        status = cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(dispatch_smem));
+        if (status != cudaSuccess) return status;
+        current[device] = dispatch_smem;
+    }
+    return cudaSuccess;
+}
+
+int dispatch_resident_ctas(int threads, std::size_t smem) {
+    int per_sm = 0, device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dispatch_kernel, threads, smem) != cudaSuccess) return 0;
+    return per_sm * sms;
+}
+
+int combine_resident_ctas(int threads) {
+    int per_sm = 0, device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, combine_kernel, threads, 0) != cudaSuccess) return 0;
+    return per_sm * sms;
+}
+
+namespace {
+
+template <typename Kernel, typename Args>
+cudaError_t cooperative_launch(Kernel kernel, const Args& args, dim3 grid, int threads, std::size_t smem,
+                               cudaStream_t stream) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeCooperative;  // every CTA resident: the waits inside are safe
+    attribute[0].val.cooperative = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, args);
+}
+
+}  // namespace
+
+cudaError_t launch_dispatch(const DispatchLaunch& launch, int channels, int threads, std::size_t smem,
+                            cudaStream_t stream) {
+    return cooperative_launch(dispatch_kernel, launch, dim3(channels, launch.num_virtual, 1), threads, smem, stream);
+}
+
+cudaError_t launch_combine(const CombineLaunch& launch, int channels, int threads, cudaStream_t stream) {
+    return cooperative_launch(combine_kernel, launch, dim3(channels, launch.num_virtual, 1), threads, 0, stream);
+}
+
+}  // namespace bep

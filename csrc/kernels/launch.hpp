@@ -1,0 +1,28 @@
+// Host-callable entry points of the CUDA translation unit (csrc/kernels/launch.cu).  The runtime
+// (plain C++, built without nvcc) only sees these.
+#pragma once
+
+#include <cstddef>
+
+#include <cuda_runtime.h>
+
+#include "protocol.cuh"
+
+namespace bep {
+
+// Shared-memory bytes the dispatch kernel needs for this configuration.
+std::size_t dispatch_shared_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma);
+
+// Raise (never lower) the kernels' dynamic shared-memory limit; thread-safe, idempotent.
+cudaError_t configure_kernels(std::size_t dispatch_smem_bytes);
+
+// How many CTAs of `threads` threads and `smem` dynamic bytes fit on the current device at once.
+int dispatch_resident_ctas(int threads, std::size_t smem);
+int combine_resident_ctas(int threads);
+
+// Cooperative launches: grid = (channels, virtual ranks).
+cudaError_t launch_dispatch(const DispatchLaunch& launch, int channels, int threads, std::size_t smem,
+                            cudaStream_t stream);
+cudaError_t launch_combine(const CombineLaunch& launch, int channels, int threads, cudaStream_t stream);
+
+}  // namespace bep

@@ -1,0 +1,137 @@
+// Python bindings of the native runtime (counterpart of the reference's csrc/runtime.cu:8-29).
+#include <torch/extension.h>
+
+#include "buffers/runtime.hpp"
+
+namespace py = pybind11;
+using namespace bep;
+
+namespace {
+
+py::dict layout_to_dict(const SegmentLayout& l) {
+    py::dict d;
+    d["size_bytes"] = l.size_bytes;
+    d["done_off"] = l.done_off;
+    d["abort_off"] = l.abort_off;
+    d["counts_flag_off"] = l.counts_flag_off;
+    d["counts_off"] = l.counts_off;
+    d["ready_off"] = l.ready_off;
+    d["ack_off"] = l.ack_off;
+    d["stage_off"] = l.stage_off;
+    d["cdone_off"] = l.cdone_off;
+    d["cready_off"] = l.cready_off;
+    d["cstage_off"] = l.cstage_off;
+    d["slots"] = l.slots;
+    d["slots_full"] = l.slots_full;
+    d["counts_stride"] = l.counts_stride;
+    d["row_stride"] = l.row_stride;
+    d["meta_off"] = l.meta_off;
+    d["meta_off_fp8"] = l.meta_off_fp8;
+    d["meta_bytes"] = l.meta_bytes;
+    d["crow_stride"] = l.crow_stride;
+    return d;
+}
+
+std::vector<py::dict> dispatch_group(const std::vector<std::shared_ptr<Runtime>>& runtimes,
+                                     const std::vector<at::Tensor>& xs, const std::vector<at::Tensor>& idxs,
+                                     const std::vector<std::optional<at::Tensor>>& weights, int alignment, bool expand,
+                                     bool zero_padding, const std::vector<std::shared_ptr<Layout>>& cached,
+                                     bool graph_pool, int device) {
+    if (xs.size() != runtimes.size() || idxs.size() != runtimes.size() || weights.size() != runtimes.size() ||
+        cached.size() != runtimes.size())
+        throw std::invalid_argument("one input set per virtual rank");
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    std::vector<PreparedDispatch> prepared;
+    prepared.reserve(runtimes.size());
+    for (std::size_t i = 0; i < runtimes.size(); ++i)
+        prepared.push_back(runtimes[i]->prepare_dispatch(xs[i], idxs[i], weights[i], alignment, expand, zero_padding,
+                                                         cached[i], graph_pool));
+    launch_dispatch_group(runtimes, prepared, device);
+    std::vector<py::dict> results;
+    for (auto& p : prepared) results.push_back(p.result);
+    return results;
+}
+
+std::vector<at::Tensor> combine_group(const std::vector<std::shared_ptr<Runtime>>& runtimes,
+                                      const std::vector<at::Tensor>& ys, const std::vector<py::dict>& results,
+                                      bool weighted, int device) {
+    if (ys.size() != runtimes.size() || results.size() != runtimes.size())
+        throw std::invalid_argument("one input set per virtual rank");
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+    std::vector<PreparedCombine> prepared;
+    for (std::size_t i = 0; i < runtimes.size(); ++i)
+        prepared.push_back(runtimes[i]->prepare_combine(ys[i], results[i], weighted, std::nullopt));
+    launch_combine_group(runtimes, prepared, device);
+    std::vector<at::Tensor> outs;
+    for (auto& p : prepared) outs.push_back(p.out);
+    return outs;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.doc() = "Blackwell expert-parallel dispatch/combine runtime";
+
+    m.def("segment_layout", [](int P, int C, int E, int K, int H, int Tmax, int payload_slots, bool combine) {
+        return layout_to_dict(make_segment_layout(P, C, E, K, H, Tmax, payload_slots, combine));
+    });
+    m.def("allocate_device_segment", [](std::size_t bytes, int device) {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+        return reinterpret_cast<std::int64_t>(allocate_device_segment(bytes).ptr);
+    });
+    m.def("export_device_segment", [](std::int64_t ptr) { return py::bytes(export_device_segment(reinterpret_cast<void*>(ptr))); });
+    m.def("import_device_segment", [](const std::string& handle, int device) {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+        return reinterpret_cast<std::int64_t>(import_device_segment(handle));
+    });
+    m.def("release_imported_segment", [](std::int64_t ptr) { release_imported_segment(reinterpret_cast<void*>(ptr)); });
+    m.def("free_device_segment", [](std::int64_t ptr) { free_device_segment(reinterpret_cast<void*>(ptr)); });
+    m.def("get_device_numa_node", &device_numa_node);
+    m.def("create_host_segment", &create_host_segment);
+    m.def("first_touch_host_segment", &first_touch_host_segment);
+    m.def("tensor_refs", [](const at::Tensor& t) {
+        const TensorRefs r = tensor_refs(t);
+        return py::make_tuple(r.tensor_use_count, r.storage_use_count);
+    });
+
+    py::class_<HostSegment, std::shared_ptr<HostSegment>>(m, "HostSegment")
+        .def(py::init<const std::string&, std::size_t, int>())
+        .def("host_pointer", &HostSegment::host_pointer)
+        .def("device_pointer", &HostSegment::device_pointer)
+        .def("close", &HostSegment::close);
+
+    py::class_<Layout, std::shared_ptr<Layout>>(m, "_Layout")
+        .def_readonly("num_tokens", &Layout::num_tokens)
+        .def_readonly("alignment", &Layout::alignment)
+        .def_readonly("expand", &Layout::expand)
+        .def_readonly("valid", &Layout::valid)
+        .def_readonly("mask", &Layout::mask)
+        .def_readonly("slot", &Layout::slot)
+        .def_readonly("expert_ord", &Layout::expert_ord)
+        .def_readonly("counts", &Layout::counts);
+
+    py::class_<Runtime, std::shared_ptr<Runtime>>(m, "Runtime")
+        .def(py::init<int, int, int, int, int, int, const py::dict&, const std::vector<std::int64_t>&, int>())
+        .def("dispatch", &Runtime::dispatch, py::arg("x"), py::arg("topk_idx"), py::arg("topk_weights"),
+             py::arg("alignment"), py::arg("expand"), py::arg("zero_padding"), py::arg("cached"), py::arg("graph_pool"))
+        .def("combine", &Runtime::combine, py::arg("y"), py::arg("dispatch_result"), py::arg("weighted"), py::arg("out"))
+        .def("pool_debug", &Runtime::pool_debug)
+        .def("set_test_delays", &Runtime::set_test_delays)
+        .def("set_test_prefix_delay_ns", &Runtime::set_test_prefix_delay_ns)
+        .def("set_test_skip_counts_ack_source", &Runtime::set_test_skip_counts_ack_source)
+        .def("set_test_withhold_counts", &Runtime::set_test_withhold_counts)
+        .def("set_timeout_ms", &Runtime::set_timeout_ms)
+        .def("sticky_error", &Runtime::sticky_error)
+        .def("epochs", &Runtime::epochs)
+        .def("channels", &Runtime::channels)
+        .def("threads", &Runtime::threads)
+        .def("shared_bytes", &Runtime::shared_bytes)
+        .def("uses_tma", &Runtime::uses_tma)
+        .def("unique_capacity", &Runtime::unique_capacity)
+        .def("expanded_capacity", &Runtime::expanded_capacity)
+        .def("segment_layout", [](const Runtime& r) { return layout_to_dict(r.layout()); })
+        .def("close", &Runtime::close);
+
+    m.def("dispatch_group", &dispatch_group);
+    m.def("combine_group", &combine_group);
+}

@@ -1,0 +1,177 @@
+"""Configuration of the expert-parallel dispatch/combine transport.
+
+``HostStagedConfig`` keeps the field names of the reference's flag system
+(reference: ``pcie_ep/config.py:42-63``) so that existing call sites keep
+working, and adds the fields that select the Blackwell transport.  The
+class is frozen: one instance is agreed on collectively when a buffer is
+built and never changes afterwards.
+
+Transports
+    ``peer``         per-rank symmetric segments in HBM, mapped into every
+                     peer over NVLink (CUDA IPC); the default on GPUs.
+    ``host_staged``  the same protocol over ``/dev/shm`` files registered
+                     with ``cudaHostRegister`` (the reference's substrate),
+                     optionally with CPU relay threads (``numa_mode="relay"``).
+    ``cpu``          pure PyTorch over a gloo group; the oracle and the
+                     fallback on machines without a GPU.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, fields
+from typing import Optional, Tuple
+
+_TRANSPORTS = ("peer", "host_staged", "cpu", "auto")
+_WIRE_DTYPES = ("bf16", "fp8_e4m3")
+_COPY_ENGINES = ("tma", "vector")
+
+#: hard limits shared with the native protocol headers (csrc/kernels/protocol.cuh)
+MAX_RANKS = 16
+MAX_TOPK = 32
+MAX_EXPERTS = 4096
+MAX_CHANNELS = 128
+MAX_ALIGNMENT = 256
+
+
+@dataclass(frozen=True)
+class HostStagedConfig:
+    """Capacity, protocol and transport selection for one EP buffer.
+
+    Arguments that exist in the reference keep their meaning:
+
+    payload_slots: per (source, channel) receive-ring capacity in rows.  ``0``
+        (the default here) sizes the ring for ``num_max_tokens_per_rank`` so a
+        sender never waits for credit; a positive value bounds peer memory and
+        turns on the ACK/credit path (reference: bounded rings,
+        ``docs/pcie-ep/design.md:176-200``).
+    descriptor_slots: kept for source compatibility; rows and their READY
+        flags share one ring here, so it must equal ``payload_slots`` or 0/256.
+    channels: number of independently owned channels = CTAs per rank.
+    stage: capability gate 6 (BF16), 7 (FP8 wire), 8 (relay); the gates are
+        checked exactly like the reference's (``pcie_ep/config.py:65-102``).
+    timeout_ms: device-side bound of every protocol wait.
+    wire_dtype: ``"bf16"`` or ``"fp8_e4m3"`` (one FP32 scale per token).
+    enable_graph: allocate the extra fixed-address result pool for
+        ``capture_dispatch``.
+    output_pool_size: number of eager result pools (2..8).
+    numa_mode / relay_*: CPU relay of the host-staged transport.
+    *_delay_ns: test-only injected delays in the last worker of each role.
+
+    Added for the Blackwell build:
+
+    transport: see module docstring; ``"auto"`` picks ``peer`` on CUDA and
+        ``cpu`` otherwise.
+    copy_engine: ``"tma"`` moves rows with ``cp.async.bulk`` through shared
+        memory, ``"vector"`` uses 16-byte loads/stores (also the path taken
+        automatically when ``hidden * 2`` is not a multiple of 16).
+    tx_warps / rx_warps: warps per channel CTA in the send and the
+        receive/expand role.
+    virtual_ranks: number of EP ranks emulated inside this one process on one
+        GPU (one cooperative launch covers all of them).  Used by tests and by
+        single-GPU development; 1 in production.
+    enable_combine: allocate the combine staging area.
+    """
+
+    payload_slots: int = 0
+    descriptor_slots: int = 0
+    channels: int = 32
+    stage: int = 6
+    timeout_ms: int = 30_000
+    directory: Optional[str] = None
+    numa_mode: str = "direct"
+    warp_specialization: bool = True
+    pipeline_stages: int = 2
+    fuse_receive_expand: bool = True
+    source_fusion: bool = True
+    wire_dtype: str = "bf16"
+    replica_slots: int = 256
+    enable_graph: bool = False
+    relay_workers_per_numa: int = 1
+    relay_cpu_affinity: Tuple[int, ...] = ()
+    metadata_delay_ns: int = 0
+    tx_delay_ns: int = 0
+    rx_delay_ns: int = 0
+    scatter_delay_ns: int = 0
+    output_pool_size: int = 3
+    receive_expand_mode: str = "pipelined"
+    # --- Blackwell additions -------------------------------------------------
+    transport: str = "auto"
+    copy_engine: str = "tma"
+    tx_warps: int = 4
+    rx_warps: int = 6
+    virtual_ranks: int = 1
+    enable_combine: bool = True
+
+    def __post_init__(self) -> None:
+        for name in ("timeout_ms", "replica_slots"):
+            if not isinstance(getattr(self, name), int) or getattr(self, name) < 1:
+                raise ValueError(f"{name} must be a positive integer")
+        for name in ("payload_slots", "descriptor_slots"):
+            if not isinstance(getattr(self, name), int) or getattr(self, name) < 0:
+                raise ValueError(f"{name} must be a nonnegative integer")
+        if self.stage not in (6, 7, 8):
+            raise ValueError("stages 1-5 are retired; stage must be 6, 7 or 8")
+        if not isinstance(self.channels, int) or not 1 <= self.channels <= MAX_CHANNELS:
+            raise ValueError(f"channels must be an integer in [1, {MAX_CHANNELS}]")
+        if self.pipeline_stages not in (2, 3):
+            raise ValueError("pipeline_stages must be 2 or 3")
+        if self.receive_expand_mode not in ("scalar", "vectorized", "pipelined"):
+            raise ValueError("receive_expand_mode must be 'scalar', 'vectorized' or 'pipelined'")
+        if self.receive_expand_mode != "scalar":
+            if not self.fuse_receive_expand or not self.warp_specialization:
+                raise ValueError("Non-scalar receive expansion requires fuse_receive_expand and warp_specialization")
+        if self.wire_dtype not in _WIRE_DTYPES:
+            raise ValueError("wire_dtype must be 'bf16' or 'fp8_e4m3'")
+        if self.stage < 7 and self.wire_dtype != "bf16":
+            raise NotImplementedError("FP8 wire transport requires S7")
+        if self.numa_mode not in ("direct", "relay"):
+            raise ValueError("numa_mode must be 'direct' or 'relay'")
+        if self.numa_mode == "relay" and self.stage < 8:
+            raise NotImplementedError("NUMA relay is an S8 optimization")
+        if not isinstance(self.relay_workers_per_numa, int) or not 1 <= self.relay_workers_per_numa <= self.channels:
+            raise ValueError("relay_workers_per_numa must be an integer in [1, channels]")
+        if not isinstance(self.relay_cpu_affinity, tuple) or any(
+            not isinstance(cpu, int) or cpu < 0 for cpu in self.relay_cpu_affinity
+        ):
+            raise ValueError("relay_cpu_affinity must be a tuple of nonnegative CPU indices")
+        if len(set(self.relay_cpu_affinity)) != len(self.relay_cpu_affinity):
+            raise ValueError("relay_cpu_affinity must contain distinct CPU indices")
+        if self.stage < 8 and (self.relay_workers_per_numa != 1 or self.relay_cpu_affinity):
+            raise NotImplementedError("Relay worker configuration requires S8")
+        if not isinstance(self.output_pool_size, int) or not 2 <= self.output_pool_size <= 8:
+            raise ValueError("output_pool_size must be at least two and at most eight")
+        for name in ("metadata_delay_ns", "tx_delay_ns", "rx_delay_ns", "scatter_delay_ns"):
+            if not isinstance(getattr(self, name), int) or getattr(self, name) < 0:
+                raise ValueError(f"{name} must be a nonnegative integer")
+        if self.transport not in _TRANSPORTS:
+            raise ValueError(f"transport must be one of {_TRANSPORTS}")
+        if self.copy_engine not in _COPY_ENGINES:
+            raise ValueError(f"copy_engine must be one of {_COPY_ENGINES}")
+        if not isinstance(self.tx_warps, int) or not 1 <= self.tx_warps <= 8:
+            raise ValueError("tx_warps must be an integer in [1, 8]")
+        if not isinstance(self.rx_warps, int) or not 1 <= self.rx_warps <= 12:
+            raise ValueError("rx_warps must be an integer in [1, 12]")
+        if not isinstance(self.virtual_ranks, int) or not 1 <= self.virtual_ranks <= MAX_RANKS:
+            raise ValueError(f"virtual_ranks must be an integer in [1, {MAX_RANKS}]")
+        if self.numa_mode == "relay" and self.transport not in ("host_staged", "auto"):
+            raise ValueError("numa_mode='relay' needs transport='host_staged'")
+        if self.descriptor_slots not in (0, 256, self.payload_slots):
+            raise ValueError("descriptor_slots must be 0, 256 or equal to payload_slots")
+
+    def native_options(self) -> dict:
+        """Options that every rank must agree on before memory is mapped."""
+        options = {field.name: getattr(self, field.name) for field in fields(self)}
+        options["relay_cpu_affinity"] = list(self.relay_cpu_affinity)
+        options["payload_dtype"] = "fp8" if self.wire_dtype == "fp8_e4m3" else "bf16"
+        options.pop("directory")
+        return options
+
+    def resolved_transport(self, cuda_available: bool) -> str:
+        if self.transport != "auto":
+            return self.transport
+        if self.numa_mode == "relay":
+            return "host_staged"
+        return "peer" if cuda_available else "cpu"
+
+
+EPConfig = HostStagedConfig
