@@ -289,6 +289,8 @@ class Runtime {
         if (!y.is_cuda() || y.get_device() != device_ || y.scalar_type() != at::kBFloat16 || !y.is_contiguous() ||
             y.dim() != 2 || y.size(1) != lay_.hidden || y.size(0) < 1 || y.size(0) > cap)
             throw std::invalid_argument("expert outputs must be contiguous CUDA BF16 [rows <= capacity, hidden]");
+        if (rc_.vec_ok && reinterpret_cast<std::uintptr_t>(y.data_ptr()) % 16 != 0)
+            throw std::invalid_argument("expert outputs must start on a 16-byte boundary");
         const int T = layout->num_tokens;
         at::Tensor out = out_opt.has_value()
                              ? *out_opt
@@ -391,6 +393,8 @@ class Runtime {
         if (!on_device(x) || x.scalar_type() != at::kBFloat16 || !x.is_contiguous() || x.dim() != 2 || x.size(1) != lay_.hidden)
             throw std::invalid_argument("x must be contiguous CUDA BF16 [T, hidden] on the buffer's device");
         if (x.size(0) > lay_.num_max_tokens) throw std::invalid_argument("token count exceeds num_max_tokens_per_rank");
+        if (rc_.vec_ok && reinterpret_cast<std::uintptr_t>(x.data_ptr()) % 16 != 0)
+            throw std::invalid_argument("x must start on a 16-byte boundary");
         if (!on_device(idx) || idx.scalar_type() != at::kLong || !idx.is_contiguous() || idx.dim() != 2 ||
             idx.size(0) != x.size(0) || idx.size(1) != lay_.num_topk)
             throw std::invalid_argument("topk_idx must be contiguous CUDA int64 [T, num_topk]");
