@@ -13,6 +13,7 @@
 #include <mutex>
 #include <optional>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include <ATen/cuda/CUDAContext.h>
@@ -114,9 +115,99 @@ struct OutputSet {
     }
 };
 
+// What dispatch returns to Python: a dict-like lease on one result pool.  Tensors are created on
+// first access (as aliases of the pool's tensors, never the pool tensors themselves) and cached, so a
+// dispatch costs no per-field work on the CPU.  The pool is busy while this object, or any tensor it
+// handed out, or a view of one, is alive.
+class DispatchResult {
+   public:
+    DispatchResult(std::shared_ptr<OutputSet> set, std::shared_ptr<Layout> layout, bool expand, int num_tokens,
+                   int unique_cap, int expanded_cap, int topk)
+        : set_(std::move(set)), layout_(std::move(layout)), expand_(expand), num_tokens_(num_tokens),
+          unique_cap_(unique_cap), expanded_cap_(expanded_cap), topk_(topk) {}
+
+    static const std::vector<std::string>& tensor_keys() {
+        static const std::vector<std::string> keys = {
+            "recv_x", "recv_topk_idx", "recv_topk_weights", "source_meta", "comb_map", "recv_chan_counts",
+            "unique_count", "expanded_count", "expert_counts", "expert_offsets", "expert_prefix", "source_offsets",
+            "source_expert_prefix", "error", "stats", "transport_timestamps_ns", "prefix_tx_timestamps_ns",
+            "combine_error", "combine_stats"};
+        return keys;
+    }
+
+    bool contains(const std::string& key) const {
+        if (overrides_.contains(key.c_str())) return true;
+        if (key == "_layout" || key == "_expand" || key == "_num_tokens") return true;
+        for (const auto& k : tensor_keys())
+            if (k == key) return true;
+        return false;
+    }
+
+    py::object get(const std::string& key) {
+        if (overrides_.contains(key.c_str())) return overrides_[key.c_str()];
+        if (key == "_layout") return py::cast(layout_);
+        if (key == "_expand") return py::cast(expand_);
+        if (key == "_num_tokens") return py::cast(num_tokens_);
+        auto hit = cache_.find(key);
+        if (hit != cache_.end()) return py::cast(hit->second);
+        at::Tensor t = make(key);
+        cache_.emplace(key, t);
+        return py::cast(t);
+    }
+    void set(const std::string& key, py::object value) { overrides_[key.c_str()] = std::move(value); }
+    py::list keys() const {
+        py::list out;
+        for (const auto& k : tensor_keys()) out.append(k);
+        out.append("_layout");
+        out.append("_expand");
+        out.append("_num_tokens");
+        return out;
+    }
+
+    const OutputSet& set_ref() const { return *set_; }
+    const std::shared_ptr<Layout>& layout() const { return layout_; }
+    bool expand() const { return expand_; }
+    int num_tokens() const { return num_tokens_; }
+
+   private:
+    at::Tensor make(const std::string& key) const {
+        const OutputSet& s = *set_;
+        const std::int64_t K = topk_;
+        if (key == "recv_x") return s.recv_x.narrow(0, 0, expand_ ? expanded_cap_ : unique_cap_);
+        if (key == "source_meta") return s.source_meta.narrow(0, 0, expand_ ? expanded_cap_ : unique_cap_);
+        if (key == "recv_topk_idx")
+            return expand_ ? s.recv_idx.narrow(0, 0, expanded_cap_) : s.recv_idx.narrow(0, 0, unique_cap_ * K).view({unique_cap_, K});
+        if (key == "recv_topk_weights")
+            return expand_ ? s.recv_w.narrow(0, 0, expanded_cap_) : s.recv_w.narrow(0, 0, unique_cap_ * K).view({unique_cap_, K});
+        if (key == "comb_map") return at::alias(s.comb_map);
+        if (key == "recv_chan_counts") return at::alias(s.recv_chan_counts);
+        if (key == "unique_count") return at::alias(s.unique_count);
+        if (key == "expanded_count") return at::alias(s.expanded_count);
+        if (key == "expert_counts") return at::alias(s.expert_counts);
+        if (key == "expert_offsets") return at::alias(s.expert_offsets);
+        if (key == "expert_prefix") return at::alias(s.expert_prefix);
+        if (key == "source_offsets") return at::alias(s.source_offsets);
+        if (key == "source_expert_prefix") return at::alias(s.source_expert_prefix);
+        if (key == "error") return at::alias(s.error);
+        if (key == "stats") return at::alias(s.stats);
+        if (key == "transport_timestamps_ns") return at::alias(s.timestamps);
+        if (key == "prefix_tx_timestamps_ns") return at::alias(s.prefix_tx_ts);
+        if (key == "combine_error") return at::alias(s.combine_error);
+        if (key == "combine_stats") return at::alias(s.combine_stats);
+        throw py::key_error(key);
+    }
+
+    std::shared_ptr<OutputSet> set_;
+    std::shared_ptr<Layout> layout_;
+    bool expand_;
+    int num_tokens_, unique_cap_, expanded_cap_, topk_;
+    std::unordered_map<std::string, at::Tensor> cache_;
+    py::dict overrides_;
+};
+
 struct PreparedDispatch {
     DispatchArgs args;
-    py::dict result;
+    std::shared_ptr<DispatchResult> result;
 };
 struct PreparedCombine {
     CombineArgs args;
@@ -192,8 +283,13 @@ class Runtime {
 
         const int sets = options_.output_pool_size + (options_.enable_graph ? 1 : 0);
         for (int i = 0; i < sets; ++i) {
-            pools_.push_back(make_output_set());
+            pools_.push_back(std::make_shared<OutputSet>(make_output_set()));
             plans_.push_back(make_layout());
+        }
+        if (options_.enable_combine) {
+            const auto bf16 = at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device);
+            for (int i = 0; i < options_.output_pool_size; ++i)
+                combine_pool_.push_back(at::empty({num_max_tokens, hidden}, bf16));
         }
     }
 
@@ -214,7 +310,8 @@ class Runtime {
         check_open();
         validate_inputs(x, topk_idx, topk_weights, alignment, expand, zero_padding);
         const int T = static_cast<int>(x.size(0));
-        OutputSet& out = select_output(graph_pool);
+        std::shared_ptr<OutputSet> out_set = select_output(graph_pool);
+        OutputSet& out = *out_set;
         std::shared_ptr<Layout> plan;
         if (cached) {
             if (!cached->valid || cached->num_tokens != T || cached->alignment != alignment || cached->expand != expand)
@@ -260,31 +357,34 @@ class Runtime {
         a.stats = out.stats.data_ptr<std::int64_t>();
         a.timestamps = out.timestamps.data_ptr<std::int64_t>();
         a.prefix_tx_ts = out.prefix_tx_ts.data_ptr<std::int64_t>();
-        p.result = make_result(out, plan, expand, T);
+        p.result = std::make_shared<DispatchResult>(out_set, plan, expand, T, rc_.unique_cap, rc_.expanded_cap, lay_.num_topk);
         return p;
     }
 
-    py::dict dispatch(const at::Tensor& x, const at::Tensor& topk_idx, const std::optional<at::Tensor>& topk_weights,
-                      int alignment, bool expand, bool zero_padding, const std::shared_ptr<Layout>& cached,
-                      bool graph_pool) {
+    // `stream` = raw cudaStream_t to launch on; 0 means the current PyTorch stream of the device.
+    std::shared_ptr<DispatchResult> dispatch(const at::Tensor& x, const at::Tensor& topk_idx,
+                                             const std::optional<at::Tensor>& topk_weights, int alignment, bool expand,
+                                             bool zero_padding, const std::shared_ptr<Layout>& cached, bool graph_pool,
+                                             std::int64_t stream) {
         c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
         PreparedDispatch p = prepare_dispatch(x, topk_idx, topk_weights, alignment, expand, zero_padding, cached, graph_pool);
         DispatchLaunch launch{};
         launch.num_virtual = 1;
         launch.r[0] = p.args;
-        cuda_check(launch_dispatch(launch, options_.channels, threads_, smem_, at::cuda::getCurrentCUDAStream(device_)),
-                   "dispatch launch");
+        cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
+                                                 : at::cuda::getCurrentCUDAStream(device_).stream();
+        cuda_check(launch_dispatch(launch, options_.channels, threads_, smem_, launch_stream), "dispatch launch");
         return p.result;
     }
 
     // ---- combine --------------------------------------------------------------------------------
-    PreparedCombine prepare_combine(const at::Tensor& y, const py::dict& dispatch_result, bool weighted,
+    PreparedCombine prepare_combine(const at::Tensor& y, const DispatchResult& dispatch_result, bool weighted,
                                     const std::optional<at::Tensor>& out_opt) {
         check_open();
         if (!options_.enable_combine) throw std::runtime_error("this buffer was built with enable_combine=False");
-        auto layout = dispatch_result["_layout"].cast<std::shared_ptr<Layout>>();
+        const std::shared_ptr<Layout>& layout = dispatch_result.layout();
         if (!layout || !layout->valid) throw std::invalid_argument("dispatch result carries no routing plan");
-        const bool expand = dispatch_result["_expand"].cast<bool>();
+        const bool expand = dispatch_result.expand();
         const int cap = expand ? rc_.expanded_cap : rc_.unique_cap;
         if (!y.is_cuda() || y.get_device() != device_ || y.scalar_type() != at::kBFloat16 || !y.is_contiguous() ||
             y.dim() != 2 || y.size(1) != lay_.hidden || y.size(0) < 1 || y.size(0) > cap)
@@ -292,9 +392,9 @@ class Runtime {
         if (rc_.vec_ok && reinterpret_cast<std::uintptr_t>(y.data_ptr()) % 16 != 0)
             throw std::invalid_argument("expert outputs must start on a 16-byte boundary");
         const int T = layout->num_tokens;
-        at::Tensor out = out_opt.has_value()
-                             ? *out_opt
-                             : at::empty({T, lay_.hidden}, at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device_));
+        // No allocation on the hot path: without `out`, the result comes from a small ring of
+        // preallocated [Tmax, hidden] tensors with the same "busy while referenced" rule as dispatch.
+        at::Tensor out = out_opt.has_value() ? *out_opt : select_combine_output(T);
         if (!out.is_cuda() || out.scalar_type() != at::kBFloat16 || !out.is_contiguous() || out.dim() != 2 ||
             out.size(0) != T || out.size(1) != lay_.hidden)
             throw std::invalid_argument("combine output must be contiguous CUDA BF16 [T, hidden]");
@@ -304,26 +404,28 @@ class Runtime {
         a = CombineArgs{};
         a.rc = reinterpret_cast<const RankConst*>(rank_const_.data_ptr<std::uint8_t>());
         a.y = reinterpret_cast<const __nv_bfloat16*>(y.data_ptr());
-        a.comb_map = dispatch_result["comb_map"].cast<at::Tensor>().data_ptr<int>();
-        a.recv_chan_counts = dispatch_result["recv_chan_counts"].cast<at::Tensor>().data_ptr<int>();
+        const OutputSet& set = dispatch_result.set_ref();
+        a.comb_map = set.comb_map.data_ptr<int>();
+        a.recv_chan_counts = set.recv_chan_counts.data_ptr<int>();
         a.plan_mask = reinterpret_cast<const std::uint32_t*>(layout->mask.data_ptr<int>());
         a.num_tokens = T;
         a.weighted = weighted ? 1 : 0;
         a.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
-        a.error = dispatch_result["combine_error"].cast<at::Tensor>().data_ptr<int>();
-        a.stats = dispatch_result["combine_stats"].cast<at::Tensor>().data_ptr<std::int64_t>();
+        a.error = set.combine_error.data_ptr<int>();
+        a.stats = set.combine_stats.data_ptr<std::int64_t>();
         return p;
     }
 
-    at::Tensor combine(const at::Tensor& y, const py::dict& dispatch_result, bool weighted,
-                       const std::optional<at::Tensor>& out_opt) {
+    at::Tensor combine(const at::Tensor& y, const DispatchResult& dispatch_result, bool weighted,
+                       const std::optional<at::Tensor>& out_opt, std::int64_t stream) {
         c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
         PreparedCombine p = prepare_combine(y, dispatch_result, weighted, out_opt);
         CombineLaunch launch{};
         launch.num_virtual = 1;
         launch.r[0] = p.args;
-        cuda_check(launch_combine(launch, options_.channels, threads_, at::cuda::getCurrentCUDAStream(device_)),
-                   "combine launch");
+        cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
+                                                 : at::cuda::getCurrentCUDAStream(device_).stream();
+        cuda_check(launch_combine(launch, options_.channels, threads_, launch_stream), "combine launch");
         return p.out;
     }
 
@@ -331,7 +433,7 @@ class Runtime {
     py::dict pool_debug() const {
         py::dict d;
         py::list busy;
-        for (const auto& set : pools_) busy.append(!set.free());
+        for (const auto& set : pools_) busy.append(!(set.use_count() == 1 && set->free()));
         d["output_busy"] = busy;
         py::list plan_busy;
         for (const auto& plan : plans_) plan_busy.append(plan.use_count() != 1);
@@ -369,6 +471,7 @@ class Runtime {
     void close() {
         pools_.clear();
         plans_.clear();
+        combine_pool_.clear();
         closed_ = true;
     }
     bool closed() const { return closed_; }
@@ -450,19 +553,36 @@ class Runtime {
         return plan;
     }
 
-    OutputSet& select_output(bool graph_pool) {
+    std::shared_ptr<OutputSet> select_output(bool graph_pool) {
         if (graph_pool) {
             if (!options_.enable_graph) throw std::runtime_error("graph pool requires enable_graph=True");
             return pools_.back();
         }
         for (int i = 0; i < options_.output_pool_size; ++i) {
             const int index = (next_pool_ + i) % options_.output_pool_size;
-            if (pools_[index].free()) {
+            if (pools_[index].use_count() == 1 && pools_[index]->free()) {
                 next_pool_ = (index + 1) % options_.output_pool_size;
                 return pools_[index];
             }
         }
         throw std::runtime_error("output pool exhausted: every preallocated result set is still referenced");
+    }
+
+    at::Tensor select_combine_output(int num_tokens) {
+        if (combine_pool_.empty()) {
+            const auto bf16 = at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device_);
+            for (int i = 0; i < options_.output_pool_size; ++i)
+                combine_pool_.push_back(at::empty({lay_.num_max_tokens, lay_.hidden}, bf16));
+        }
+        const int n = static_cast<int>(combine_pool_.size());
+        for (int i = 0; i < n; ++i) {
+            const int index = (next_combine_ + i) % n;
+            if (tensor_unowned(combine_pool_[index])) {
+                next_combine_ = (index + 1) % n;
+                return combine_pool_[index].narrow(0, 0, num_tokens);
+            }
+        }
+        throw std::runtime_error("combine output pool exhausted: every preallocated output is still referenced");
     }
 
     std::shared_ptr<Layout> select_plan(bool graph_pool) {
@@ -473,41 +593,6 @@ class Runtime {
         throw std::runtime_error("routing plan pool exhausted: every plan is still referenced by a handle or cached layout");
     }
 
-    py::dict make_result(const OutputSet& s, const std::shared_ptr<Layout>& plan, bool expand, int num_tokens) const {
-        py::dict d;
-        const std::int64_t K = lay_.num_topk;
-        if (expand) {
-            d["recv_x"] = s.recv_x.narrow(0, 0, rc_.expanded_cap);
-            d["recv_topk_idx"] = s.recv_idx.narrow(0, 0, rc_.expanded_cap);
-            d["recv_topk_weights"] = s.recv_w.narrow(0, 0, rc_.expanded_cap);
-            d["source_meta"] = s.source_meta.narrow(0, 0, rc_.expanded_cap);
-        } else {
-            d["recv_x"] = s.recv_x.narrow(0, 0, rc_.unique_cap);
-            d["recv_topk_idx"] = s.recv_idx.narrow(0, 0, rc_.unique_cap * K).view({rc_.unique_cap, K});
-            d["recv_topk_weights"] = s.recv_w.narrow(0, 0, rc_.unique_cap * K).view({rc_.unique_cap, K});
-            d["source_meta"] = s.source_meta.narrow(0, 0, rc_.unique_cap);
-        }
-        d["comb_map"] = at::alias(s.comb_map);
-        d["recv_chan_counts"] = at::alias(s.recv_chan_counts);
-        d["unique_count"] = at::alias(s.unique_count);
-        d["expanded_count"] = at::alias(s.expanded_count);
-        d["expert_counts"] = at::alias(s.expert_counts);
-        d["expert_offsets"] = at::alias(s.expert_offsets);
-        d["expert_prefix"] = at::alias(s.expert_prefix);
-        d["source_offsets"] = at::alias(s.source_offsets);
-        d["source_expert_prefix"] = at::alias(s.source_expert_prefix);
-        d["error"] = at::alias(s.error);
-        d["stats"] = at::alias(s.stats);
-        d["transport_timestamps_ns"] = at::alias(s.timestamps);
-        d["prefix_tx_timestamps_ns"] = at::alias(s.prefix_tx_ts);
-        d["combine_error"] = at::alias(s.combine_error);
-        d["combine_stats"] = at::alias(s.combine_stats);
-        d["_layout"] = plan;
-        d["_expand"] = expand;
-        d["_num_tokens"] = num_tokens;
-        return d;
-    }
-
     int rank_, device_;
     RuntimeOptions options_;
     SegmentLayout lay_{};
@@ -516,9 +601,11 @@ class Runtime {
     int threads_ = 0;
     std::size_t smem_ = 0;
     at::Tensor epochs_, grid_bar_, done_ctas_, block_hist_, sticky_, chan_stats_, rank_const_;
-    std::vector<OutputSet> pools_;
+    std::vector<std::shared_ptr<OutputSet>> pools_;
     std::vector<std::shared_ptr<Layout>> plans_;
+    std::vector<at::Tensor> combine_pool_;
     int next_pool_ = 0;
+    int next_combine_ = 0;
     bool closed_ = false;
 };
 

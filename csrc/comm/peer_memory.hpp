@@ -10,10 +10,12 @@
 // to another process.
 #pragma once
 
+#include <cctype>
 #include <cerrno>
+#include <cstdio>
+#include <cstdlib>
 #include <cstdint>
 #include <cstring>
-#include <fstream>
 #include <stdexcept>
 #include <string>
 
@@ -26,6 +28,11 @@
 #include <cuda_runtime.h>
 
 namespace bep {
+
+inline bool debug_enabled() {
+    const char* v = std::getenv("PCIE_EP_B200_DEBUG");
+    return v != nullptr && v[0] == '1';
+}
 
 inline void cuda_check(cudaError_t status, const char* what) {
     if (status != cudaSuccess) {
@@ -71,12 +78,18 @@ inline void free_device_segment(void* ptr) { cuda_check(cudaFree(ptr), "cudaFree
 // ---- host segments (transport "host_staged") -------------------------------------------------
 
 inline int device_numa_node(int device) {
-    char bdf[32] = {0};
-    if (cudaDeviceGetPCIBusId(bdf, sizeof(bdf), device) != cudaSuccess) return -1;
-    for (char* p = bdf; *p; ++p) *p = static_cast<char>(std::tolower(*p));
-    std::ifstream file(std::string("/sys/bus/pci/devices/") + bdf + "/numa_node");
+    char bdf[64] = {0};
+    if (cudaDeviceGetPCIBusId(bdf, static_cast<int>(sizeof(bdf)) - 1, device) != cudaSuccess) return -1;
+    for (char* p = bdf; *p; ++p) *p = static_cast<char>(std::tolower(static_cast<unsigned char>(*p)));
+    if (debug_enabled()) std::fprintf(stderr, "[pcie_ep_b200] device %d is %s\n", device, bdf);
+    // C stdio on purpose: this header is compiled by a newer g++ than the libstdc++ some hosts load at
+    // run time, and iostream locale machinery is where such a mismatch crashes.
+    const std::string path = std::string("/sys/bus/pci/devices/") + bdf + "/numa_node";
+    std::FILE* file = std::fopen(path.c_str(), "r");
+    if (file == nullptr) return -1;
     int node = -1;
-    if (!(file >> node)) return -1;
+    if (std::fscanf(file, "%d", &node) != 1) node = -1;
+    std::fclose(file);
     return node;
 }
 
@@ -96,24 +109,41 @@ struct HostMapping {
     bool registered = false;
 };
 
-// Owner side: map, bind to the GPU's NUMA node when the kernel allows it, first-touch by zeroing.
-// Returns whether the NUMA bind succeeded (it is advisory; containers often refuse it).
+inline bool numa_placement_enabled() {
+    const char* v = std::getenv("PCIE_EP_B200_NUMA_PLACEMENT");
+    return v != nullptr && v[0] == '1';
+}
+
+// Owner side: map and first-touch by zeroing, so the pages land on the NUMA node of the touching
+// thread (the kernel's default local-allocation policy).  An explicit placement request
+// (mbind, MPOL_PREFERRED towards the GPU's node) is made only when PCIE_EP_B200_NUMA_PLACEMENT=1:
+// in sandboxed containers the mbind system call can be fatal to the process rather than refused,
+// and a library must not take its host down by default.  Returns whether a placement request was
+// made and accepted.
 inline bool first_touch_host_segment(const std::string& path, std::size_t bytes, int numa_node) {
     const int fd = ::open(path.c_str(), O_RDWR);
     if (fd < 0) throw std::runtime_error("open(" + path + "): " + std::strerror(errno));
+    struct stat info {};
+    if (::fstat(fd, &info) != 0 || static_cast<std::size_t>(info.st_size) < bytes) {
+        ::close(fd);
+        throw std::runtime_error("segment file " + path + " is smaller than the segment");
+    }
     void* host = ::mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
     ::close(fd);
     if (host == MAP_FAILED) throw std::runtime_error("mmap(" + path + "): " + std::strerror(errno));
-    bool bound = false;
+    bool placed = false;
 #ifdef SYS_mbind
-    if (numa_node >= 0 && numa_node < 64) {
-        unsigned long nodemask = 1ul << numa_node;
-        bound = ::syscall(SYS_mbind, host, bytes, 2 /* MPOL_BIND */, &nodemask, 65ul, 0u) == 0;
+    if (numa_placement_enabled() && numa_node >= 0 && numa_node < 64 &&
+        ::access(("/sys/devices/system/node/node" + std::to_string(numa_node)).c_str(), F_OK) == 0) {
+        unsigned long nodemask[2] = {1ul << numa_node, 0ul};
+        placed = ::syscall(SYS_mbind, host, static_cast<unsigned long>(bytes), 1 /* MPOL_PREFERRED */, nodemask,
+                           static_cast<unsigned long>(65), static_cast<unsigned long>(0)) == 0;
     }
 #endif
+    if (debug_enabled()) std::fprintf(stderr, "[pcie_ep_b200] first touch %s bytes=%zu node=%d placed=%d\n", path.c_str(), bytes, numa_node, placed ? 1 : 0);
     std::memset(host, 0, bytes);
     ::munmap(host, bytes);
-    return bound;
+    return placed;
 }
 
 inline HostMapping map_host_segment(const std::string& path, std::size_t bytes) {

@@ -37,11 +37,110 @@ __device__ __forceinline__ uint4 pack_chunk(const float (&acc)[8]) {
     return out;
 }
 
+// dst[q] = bf16( sum_i w_i * rows_i[q] ) over `n` rows, FP32 accumulation in row order.  Lane i < n
+// holds row i's pointer and weight.  One pass keeps ROWS x CH 16-byte loads in flight per lane (64
+// registers of payload) before the first is consumed; the caller picks the shape from n.
+// n <= ROWS: the sum of one chunk is formed in one go, nothing is carried between passes.
+template <int ROWS, int CH, bool COHERENT>
+__device__ __forceinline__ void reduce_rows_once(const std::uint8_t* row_of_lane, float weight_of_lane, int n,
+                                                 std::uint8_t* dst, int chunks) {
+    const unsigned lane = ptx::lane_id();
+    const std::uint8_t* src[ROWS];
+    float w[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        src[r] = shfl_ptr(const_cast<std::uint8_t*>(row_of_lane), r);
+        w[r] = __shfl_sync(0xffffffffu, weight_of_lane, r);
+    }
+    for (int q0 = 0; q0 < chunks; q0 += 32 * CH) {
+        uint4 v[ROWS][CH];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            if (r < n) {
+#pragma unroll
+                for (int u = 0; u < CH; ++u) {
+                    const int q = q0 + u * 32 + lane;
+                    if (q < chunks)
+                        v[r][u] = COHERENT ? ptx::ld_v4(src[r] + static_cast<std::size_t>(q) * 16)
+                                           : ptx::ld_nc_v4(src[r] + static_cast<std::size_t>(q) * 16);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < CH; ++u) {
+            const int q = q0 + u * 32 + lane;
+            if (q < chunks) {
+                float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r)
+                    if (r < n) accumulate_chunk(acc, v[r][u], w[r]);
+                ptx::st_v4(dst + static_cast<std::size_t>(q) * 16, pack_chunk(acc));
+            }
+        }
+    }
+}
+
+// any n: rows in groups of 8, partial sums carried in registers
+template <bool COHERENT>
+__device__ __forceinline__ void reduce_rows_many(const std::uint8_t* row_of_lane, float weight_of_lane, int n,
+                                                 std::uint8_t* dst, int chunks) {
+    const unsigned lane = ptx::lane_id();
+    for (int q0 = 0; q0 < chunks; q0 += 64) {
+        float acc[2][8];
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[u][e] = 0.0f;
+        for (int i0 = 0; i0 < n; i0 += 4) {
+            uint4 v[4][2];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                if (i0 + r < n) {
+                    const std::uint8_t* src = shfl_ptr(const_cast<std::uint8_t*>(row_of_lane), i0 + r);
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int q = q0 + u * 32 + lane;
+                        if (q < chunks)
+                            v[r][u] = COHERENT ? ptx::ld_v4(src + static_cast<std::size_t>(q) * 16)
+                                               : ptx::ld_nc_v4(src + static_cast<std::size_t>(q) * 16);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                if (i0 + r < n) {
+                    const float w = __shfl_sync(0xffffffffu, weight_of_lane, i0 + r);
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int q = q0 + u * 32 + lane;
+                        if (q < chunks) accumulate_chunk(acc[u], v[r][u], w);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int q = q0 + u * 32 + lane;
+            if (q < chunks) ptx::st_v4(dst + static_cast<std::size_t>(q) * 16, pack_chunk(acc[u]));
+        }
+    }
+}
+
+template <bool COHERENT>
+__device__ __forceinline__ void reduce_rows_any(const std::uint8_t* row_of_lane, float weight_of_lane, int n,
+                                                std::uint8_t* dst, int chunks) {
+    if (n <= 2) reduce_rows_once<2, 4, COHERENT>(row_of_lane, weight_of_lane, n, dst, chunks);
+    else if (n <= 8) reduce_rows_once<8, 1, COHERENT>(row_of_lane, weight_of_lane, n, dst, chunks);
+    else reduce_rows_many<COHERENT>(row_of_lane, weight_of_lane, n, dst, chunks);
+}
+
 }  // namespace detail
 
-__global__ void __launch_bounds__(kMaxWarps * 32, 1) combine_kernel(const __grid_constant__ CombineLaunch launch) {
+constexpr int kCombineWarps = 10;  // every warp first reduces+pushes expert-side rows, then adds rows for its own tokens
+
+__global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __grid_constant__ CombineLaunch launch) {
     using namespace detail;
-    const CombineArgs& a = launch.r[blockIdx.y];
+    const CombineArgs a = launch.r[blockIdx.y];
     const RankConst* __restrict__ rc = a.rc;
     const SegmentLayout& lay = rc->lay;
     const int P = lay.num_ranks, C = lay.num_channels, K = lay.num_topk, H = lay.hidden, Qf = lay.slots_full;
@@ -53,7 +152,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) combine_kernel(const __grid
     const int warp = threadIdx.x >> 5;
     const unsigned lane = ptx::lane_id();
     const unsigned full = 0xffffffffu;
-    const int tx_warps = rc->tx_warps, rx_warps = rc->rx_warps;
+    const int num_warps = blockDim.x >> 5;
     const bool vec_ok = rc->vec_ok != 0;
     const int map_stride = 2 + 2 * K;
     __shared__ int cta_flag;
@@ -78,16 +177,16 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) combine_kernel(const __grid
     if (cta_failed(health, &cta_flag)) return;
 
     unsigned long long st_rows = 0, st_remote = 0, st_tokens = 0;
-    if (warp >= 1 && warp <= tx_warps) {
-        // ===== expert side: reduce + push =====
-        const int w = warp - 1;
+    {
+        // ===== expert side: reduce + push (never waits) =====
+        const int w = warp;
         int item = 0;
         for (int s = 0; s < P && !warp_failed(health); ++s) {
             const int n_s = a.recv_chan_counts[s * C + c];
             std::uint8_t* dst_base = rc->seg[s] + lay.cstage_off + static_cast<std::size_t>(me) * Tmax * lay.crow_stride;
             std::uint64_t* flag_base = reinterpret_cast<std::uint64_t*>(rc->seg[s] + lay.cready_off) + static_cast<std::size_t>(me) * Tmax;
             for (int j = 0; j < n_s; ++j, ++item) {
-                if (item % tx_warps != w) continue;
+                if (item % num_warps != w) continue;
                 const int* map = a.comb_map + ((static_cast<std::size_t>(s) * C + c) * Qf + j) * map_stride;
                 const int token = map[0];
                 const int n = map[1];
@@ -99,34 +198,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) combine_kernel(const __grid
                 }
                 std::uint8_t* dst = dst_base + static_cast<std::size_t>(token) * lay.crow_stride;
                 if (vec_ok) {
-                    const int chunks = H / 8;
-                    for (int q0 = 0; q0 < chunks; q0 += 128) {
-                        float acc[4][8];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) acc[u][e] = 0.0f;
-                        for (int i = 0; i < n; ++i) {
-                            const std::uint8_t* src = shfl_ptr(const_cast<std::uint8_t*>(row_ptr), i);
-                            const float wi = __shfl_sync(full, wgt, i);
-                            uint4 v[4];
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                const int q = q0 + u * 32 + lane;
-                                if (q < chunks) v[u] = ptx::ld_nc_v4(src + static_cast<std::size_t>(q) * 16);
-                            }
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) {
-                                const int q = q0 + u * 32 + lane;
-                                if (q < chunks) accumulate_chunk(acc[u], v[u], wi);
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int q = q0 + u * 32 + lane;
-                            if (q < chunks) ptx::st_v4(dst + static_cast<std::size_t>(q) * 16, pack_chunk(acc[u]));
-                        }
-                    }
+                    reduce_rows_any<false>(row_ptr, wgt, n, dst, H / 8);
                 } else {
                     for (int k = lane; k < H; k += 32) {
                         float acc = 0.0f;
@@ -146,10 +218,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) combine_kernel(const __grid
                 }
             }
         }
-    } else if (warp > tx_warps) {
+    }
+    {
         // ===== source side: add the partial rows of every destination rank, in rank order =====
-        const int w = warp - 1 - tx_warps;
-        for (int t = t0 + w; t < t1; t += rx_warps) {
+        const int w = warp;
+        for (int t = t0 + w; t < t1; t += num_warps) {
             if (warp_failed(health)) break;
             const unsigned mask = a.plan_mask[t];
             if (lane < static_cast<unsigned>(P) && (mask >> lane & 1u)) {
@@ -165,33 +238,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) combine_kernel(const __grid
             const std::uint8_t* base = my_seg + lay.cstage_off + static_cast<std::size_t>(t) * lay.crow_stride;
             const std::size_t rank_stride = static_cast<std::size_t>(Tmax) * lay.crow_stride;
             if (vec_ok) {
-                const int chunks = H / 8;
-                for (int q0 = 0; q0 < chunks; q0 += 128) {
-                    float acc[4][8];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u)
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) acc[u][e] = 0.0f;
-                    for (unsigned m = mask; m; m &= m - 1) {
-                        const std::uint8_t* src = base + static_cast<std::size_t>(__ffs(m) - 1) * rank_stride;
-                        uint4 v[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int q = q0 + u * 32 + lane;
-                            if (q < chunks) v[u] = ptx::ld_v4(src + static_cast<std::size_t>(q) * 16);
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int q = q0 + u * 32 + lane;
-                            if (q < chunks) accumulate_chunk(acc[u], v[u], 1.0f);
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int q = q0 + u * 32 + lane;
-                        if (q < chunks) ptx::st_v4(out + static_cast<std::size_t>(q) * 16, pack_chunk(acc[u]));
-                    }
+                // lane i holds the row of the i-th rank (ascending) in the token's mask
+                const std::uint8_t* src_of_lane = nullptr;
+                {
+                    unsigned m = mask;
+                    for (unsigned i = 0; m; m &= m - 1, ++i)
+                        if (lane == i) src_of_lane = base + static_cast<std::size_t>(__ffs(m) - 1) * rank_stride;
                 }
+                reduce_rows_any<true>(src_of_lane, 1.0f, __popc(mask), out, H / 8);
             } else {
                 for (int k = lane; k < H; k += 32) {
                     float acc = 0.0f;

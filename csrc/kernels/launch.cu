@@ -73,8 +73,8 @@ cudaError_t launch_dispatch(const DispatchLaunch& launch, int channels, int thre
     return cooperative_launch(dispatch_kernel, launch, dim3(channels, launch.num_virtual, 1), threads, smem, stream);
 }
 
-cudaError_t launch_combine(const CombineLaunch& launch, int channels, int threads, cudaStream_t stream) {
-    return cooperative_launch(combine_kernel, launch, dim3(channels, launch.num_virtual, 1), threads, 0, stream);
+cudaError_t launch_combine(const CombineLaunch& launch, int channels, int /*threads*/, cudaStream_t stream) {
+    return cooperative_launch(combine_kernel, launch, dim3(channels, launch.num_virtual, 1), kCombineWarps * 32, 0, stream);
 }
 
 }  // namespace bep

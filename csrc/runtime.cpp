@@ -32,7 +32,7 @@ py::dict layout_to_dict(const SegmentLayout& l) {
     return d;
 }
 
-std::vector<py::dict> dispatch_group(const std::vector<std::shared_ptr<Runtime>>& runtimes,
+std::vector<std::shared_ptr<DispatchResult>> dispatch_group(const std::vector<std::shared_ptr<Runtime>>& runtimes,
                                      const std::vector<at::Tensor>& xs, const std::vector<at::Tensor>& idxs,
                                      const std::vector<std::optional<at::Tensor>>& weights, int alignment, bool expand,
                                      bool zero_padding, const std::vector<std::shared_ptr<Layout>>& cached,
@@ -47,20 +47,21 @@ std::vector<py::dict> dispatch_group(const std::vector<std::shared_ptr<Runtime>>
         prepared.push_back(runtimes[i]->prepare_dispatch(xs[i], idxs[i], weights[i], alignment, expand, zero_padding,
                                                          cached[i], graph_pool));
     launch_dispatch_group(runtimes, prepared, device);
-    std::vector<py::dict> results;
+    std::vector<std::shared_ptr<DispatchResult>> results;
     for (auto& p : prepared) results.push_back(p.result);
     return results;
 }
 
 std::vector<at::Tensor> combine_group(const std::vector<std::shared_ptr<Runtime>>& runtimes,
-                                      const std::vector<at::Tensor>& ys, const std::vector<py::dict>& results,
+                                      const std::vector<at::Tensor>& ys,
+                                      const std::vector<std::shared_ptr<DispatchResult>>& results,
                                       bool weighted, int device) {
     if (ys.size() != runtimes.size() || results.size() != runtimes.size())
         throw std::invalid_argument("one input set per virtual rank");
     c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
     std::vector<PreparedCombine> prepared;
     for (std::size_t i = 0; i < runtimes.size(); ++i)
-        prepared.push_back(runtimes[i]->prepare_combine(ys[i], results[i], weighted, std::nullopt));
+        prepared.push_back(runtimes[i]->prepare_combine(ys[i], *results[i], weighted, std::nullopt));
     launch_combine_group(runtimes, prepared, device);
     std::vector<at::Tensor> outs;
     for (auto& p : prepared) outs.push_back(p.out);
@@ -110,11 +111,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def_readonly("expert_ord", &Layout::expert_ord)
         .def_readonly("counts", &Layout::counts);
 
+    py::class_<DispatchResult, std::shared_ptr<DispatchResult>>(m, "DispatchResult")
+        .def("__getitem__", &DispatchResult::get)
+        .def("__setitem__", &DispatchResult::set)
+        .def("__contains__", &DispatchResult::contains)
+        .def("keys", &DispatchResult::keys)
+        .def("get", [](DispatchResult& r, const std::string& key, py::object fallback) {
+            return r.contains(key) ? r.get(key) : fallback;
+        }, py::arg("key"), py::arg("default") = py::none());
+
     py::class_<Runtime, std::shared_ptr<Runtime>>(m, "Runtime")
         .def(py::init<int, int, int, int, int, int, const py::dict&, const std::vector<std::int64_t>&, int>())
         .def("dispatch", &Runtime::dispatch, py::arg("x"), py::arg("topk_idx"), py::arg("topk_weights"),
-             py::arg("alignment"), py::arg("expand"), py::arg("zero_padding"), py::arg("cached"), py::arg("graph_pool"))
-        .def("combine", &Runtime::combine, py::arg("y"), py::arg("dispatch_result"), py::arg("weighted"), py::arg("out"))
+             py::arg("alignment"), py::arg("expand"), py::arg("zero_padding"), py::arg("cached"), py::arg("graph_pool"),
+             py::arg("stream") = 0)
+        .def("combine", &Runtime::combine, py::arg("y"), py::arg("dispatch_result"), py::arg("weighted"), py::arg("out"),
+             py::arg("stream") = 0)
         .def("pool_debug", &Runtime::pool_debug)
         .def("set_test_delays", &Runtime::set_test_delays)
         .def("set_test_prefix_delay_ns", &Runtime::set_test_prefix_delay_ns)

@@ -208,7 +208,12 @@ class HostStagedEPBuffer:
         if previous_event is None:
             self._comm_stream.wait_stream(compute)
         elif hasattr(previous_event, "current_stream_wait"):
-            previous_event.current_stream_wait()
+            # an EventOverlap (or look-alike): the *communication* stream is the one that must wait
+            if getattr(previous_event, "event", None) is not None:
+                self._comm_stream.wait_event(previous_event.event)
+            else:
+                with torch.cuda.stream(self._comm_stream):
+                    previous_event.current_stream_wait()
         else:
             self._comm_stream.wait_event(previous_event)
         self._wait_consumer_streams(compute, compute_already_waited=previous_event is None)
@@ -305,8 +310,9 @@ class HostStagedEPBuffer:
                 output_handle,
             )
             if not async_with_compute_stream and self.on_gpu:
+                # result tensors live in pools owned by the runtime, not by the caching allocator:
+                # nothing to record, but the reader stream must be known before the pool is reused
                 compute.wait_event(event)
-                _record_tensors(result, compute)
                 self._register_consumer_stream(compute)
             if defer_epilogue:
                 overlap.register_hook_after_wait(lambda: outputs)
@@ -324,16 +330,17 @@ class HostStagedEPBuffer:
             if cumulative is not None:
                 cumulative.add_(result["expert_counts"])
             return result, None
-        with torch.cuda.stream(self._comm_stream):
-            self._wait_for_inputs(compute, previous_event)
-            _record_tensors((x, topk_idx, topk_weights), self._comm_stream)
-            result = self.runtime.dispatch(x, topk_idx, topk_weights, alignment, do_expand, do_zero_padding,
-                                           cached_layout, False)
-            if cumulative is not None:
+        comm = self._comm_stream
+        self._wait_for_inputs(compute, previous_event)
+        _record_tensors((x, topk_idx, topk_weights), comm)
+        result = self.runtime.dispatch(x, topk_idx, topk_weights, alignment, do_expand, do_zero_padding,
+                                       cached_layout, False, comm.cuda_stream)
+        if cumulative is not None:
+            with torch.cuda.stream(comm):
                 cumulative.add_(result["expert_counts"])
-                cumulative.record_stream(self._comm_stream)
-            event = torch.cuda.Event()
-            event.record(self._comm_stream)
+                cumulative.record_stream(comm)
+        event = torch.cuda.Event()
+        event.record(comm)
         return result, event
 
     # ------------------------------------------------------------------ combine
@@ -380,17 +387,18 @@ class HostStagedEPBuffer:
             if torch.cuda.is_current_stream_capturing():
                 raise NotImplementedError("combine cannot be issued inside a stream capture")
             compute = self._current_stream()
-            with torch.cuda.stream(self._comm_stream):
-                self._wait_for_inputs(compute, previous_event)
-                _record_tensors((x, out), self._comm_stream)
-                combined = self.runtime.combine(x, handle._result, weighted, out)
-                event = torch.cuda.Event()
-                event.record(self._comm_stream)
+            comm = self._comm_stream
+            self._wait_for_inputs(compute, previous_event)
+            _record_tensors((x, out), comm)
+            # without `out` the result is a preallocated pool tensor (busy while referenced)
+            combined = self.runtime.combine(x, handle._result, weighted, out, comm.cuda_stream)
+            event = torch.cuda.Event()
+            event.record(comm)
             self._last_event = event
             overlap = EventOverlap(event, (self, x, handle, combined), self._register_consumer_stream)
             if not async_with_compute_stream:
                 compute.wait_event(event)
-                combined.record_stream(compute)
+                self._register_consumer_stream(compute)
             return combined, None, overlap
 
     # ------------------------------------------------------------------ cache / graph

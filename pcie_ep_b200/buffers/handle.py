@@ -82,31 +82,45 @@ class HostStagedEPHandle(_RouteGuard):
         self._route_signature = _tensor_signature(topk_idx)
         self._layout = result.get("_layout")
         self._result = result
-        self.unique_count = result["unique_count"]
-        self.expanded_count = result["expanded_count"]
-        self.expert_counts = result["expert_counts"]
-        self.expert_offsets = result["expert_offsets"]
-        self.source_meta = result["source_meta"]
-        self.source_offsets = result["source_offsets"]
-        self.source_expert_prefix = result.get("source_expert_prefix")
-        self.error = result["error"]
-        self.stats = result["stats"]
-        self.transport_timestamps_ns = result.get("transport_timestamps_ns")
-        self.receive_expand_overlap = result.get("receive_expand_overlap")
-        self.prefix_tx_timestamps_ns = result.get("prefix_tx_timestamps_ns")
-        self.profiling = result.get("profiling")
-        # DeepEP-compatible names
-        self.num_recv_tokens = self.unique_count
-        self.num_expanded_tokens = self.expanded_count
         self.num_recv_tokens_per_expert_list = None
-        self.num_unaligned_recv_tokens_per_expert = self.expert_counts
-        self.recv_src_metadata = self.source_meta
-        self.psum_num_recv_tokens_per_scaleup_rank = self.source_offsets[1:]
-        self.psum_num_recv_tokens_per_expert = result.get("expert_prefix")
-        self.dst_buffer_slot_idx = result.get("dst_buffer_slot_idx")
         self.completion = event
         self._completion_event = event.event
         self._owner = owner
+
+    # Result fields are looked up when first asked for (a dispatch touches none of them on the CPU).
+    # name on the handle -> key in the native result; DeepEP-compatible aliases included.
+    _FIELDS = {
+        "unique_count": "unique_count",
+        "num_recv_tokens": "unique_count",
+        "expanded_count": "expanded_count",
+        "num_expanded_tokens": "expanded_count",
+        "expert_counts": "expert_counts",
+        "num_unaligned_recv_tokens_per_expert": "expert_counts",
+        "expert_offsets": "expert_offsets",
+        "source_meta": "source_meta",
+        "recv_src_metadata": "source_meta",
+        "source_offsets": "source_offsets",
+        "source_expert_prefix": "source_expert_prefix",
+        "psum_num_recv_tokens_per_expert": "expert_prefix",
+        "error": "error",
+        "stats": "stats",
+        "transport_timestamps_ns": "transport_timestamps_ns",
+        "receive_expand_overlap": "receive_expand_overlap",
+        "prefix_tx_timestamps_ns": "prefix_tx_timestamps_ns",
+        "profiling": "profiling",
+        "dst_buffer_slot_idx": "dst_buffer_slot_idx",
+    }
+
+    def __getattr__(self, name: str) -> Any:
+        # only called for attributes not set in __init__
+        if name == "psum_num_recv_tokens_per_scaleup_rank":
+            value = self._result["source_offsets"][1:]
+        elif name in HostStagedEPHandle._FIELDS:
+            value = self._result.get(HostStagedEPHandle._FIELDS[name])
+        else:
+            raise AttributeError(name)
+        self.__dict__[name] = value
+        return value
 
     def check_errors(self) -> None:
         """Explicit diagnostic synchronisation; never called by dispatch itself."""

@@ -1,0 +1,40 @@
+"""One process per GPU through the public API: peer-memory transport over NVLink (CUDA IPC) and the
+host-staged fallback.  World size 1 always runs; larger worlds run when the box has the GPUs."""
+
+import pytest
+import torch
+
+from tests.test_cpu_transport import run_workers
+
+pytestmark = pytest.mark.gpu
+
+
+def _need(gpus):
+    if torch.cuda.device_count() < gpus:
+        pytest.skip(f"needs {gpus} GPUs")
+
+
+@pytest.mark.parametrize("transport", ["peer", "host_staged"])
+def test_single_rank_public_api(transport):
+    run_workers(1, "--transport", transport, "--suite", "correctness", "--hidden", "256")
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_transport_correctness(world):
+    _need(world)
+    run_workers(world, "--transport", "peer", "--suite", "correctness", "--hidden", "512")
+
+
+def test_peer_transport_bounded_ring_world2():
+    _need(2)
+    run_workers(2, "--transport", "peer", "--suite", "correctness", "--hidden", "256", "--payload-slots", "2")
+
+
+def test_host_staged_transport_world2():
+    _need(2)
+    run_workers(2, "--transport", "host_staged", "--suite", "correctness", "--hidden", "256")
+
+
+def test_oracle_config_on_gpus():
+    _need(2)
+    run_workers(2, "--transport", "peer", "--suite", "oracle_config")

@@ -1,0 +1,171 @@
+"""Multi-process test program: one EP rank per process, driven through the public ``EPBuffer`` API.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P tests/workers/ep_worker.py --transport cpu|peer|host_staged --suite NAME
+
+Every rank checks its own result against the oracle (inputs are exchanged with ``all_gather_object``
+over gloo), failures are gathered so that all ranks exit non-zero together -- the structure of the
+reference's torchrun tests (``tests/test_correctness.py:26-29,186-226``).
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+
+import torch
+import torch.distributed as dist
+
+from pcie_ep_b200 import HostStagedConfig, HostStagedEPBuffer
+from pcie_ep_b200.ops import reference
+from tests.helpers import make_inputs
+
+
+def gather(value, group=None):
+    values = [None] * dist.get_world_size(group)
+    dist.all_gather_object(values, value, group=group)
+    return values
+
+
+def agree(failure, label):
+    failures = [f for f in gather(failure) if f]
+    if failures:
+        raise AssertionError(f"{label}: " + "; ".join(failures))
+
+
+def to_device(inputs, device):
+    return tuple(None if t is None else t.to(device) for t in inputs)
+
+
+def run_case(buffer, args, rank, world, device, case, dims, wire="bf16"):
+    experts, topk, hidden, tmax = dims
+    tokens = case["tokens"]
+    if case.get("unequal"):
+        tokens = 0 if rank == 0 else max(1, tokens - rank * 3)
+    dtype = torch.float32 if args.transport == "cpu" and args.fp32 else torch.bfloat16
+    mine = make_inputs(rank, world, tokens, hidden, experts, topk, case["pattern"], seed=case.get("seed", 7), dtype=dtype,
+                       weights=case.get("weights", True))
+    everyone = gather(mine)
+    x, idx, w = to_device(mine, device)
+    failure = None
+    try:
+        recv_x, recv_idx, recv_w, handle, event = buffer.dispatch(
+            x, topk_idx=idx, topk_weights=w, do_expand=case["expand"], expert_alignment=case["alignment"],
+            do_cpu_sync=False, do_zero_padding=case["expand"])
+        event.current_stream_wait()
+        buffer.check_errors()
+        expected = reference.dispatch_reference(everyone, rank, experts, tmax, do_expand=case["expand"],
+                                                expert_alignment=case["alignment"], do_zero_padding=case["expand"],
+                                                wire_dtype=wire)
+        actual = dict(handle._result)
+        actual["recv_topk_weights"] = recv_w
+        problems = reference.compare_dispatch(actual, expected, do_expand=case["expand"], do_zero_padding=case["expand"],
+                                              have_weights=case.get("weights", True))
+        if (recv_w is None) != (not case.get("weights", True)):
+            problems.append("recv_topk_weights presence does not follow the input")
+        if case.get("combine", True) and not problems:
+            # identity experts: combine(recv_x) == x * sum of the token's weights (expanded) / number of ranks hit (unique)
+            combined, _, cevent = buffer.combine(recv_x, handle)
+            cevent.current_stream_wait()
+            buffer.check_errors()
+            xs, idxs, ws = mine
+            valid = idxs >= 0
+            if case["expand"]:
+                weights = ws if ws is not None else torch.ones(idxs.shape)
+                factor = (weights * valid).sum(dim=1, keepdim=True)
+            else:
+                owners = torch.where(valid, idxs // (experts // world), torch.full_like(idxs, world))
+                hit = torch.zeros(idxs.shape[0], world + 1, dtype=torch.bool)
+                if idxs.numel():
+                    hit.scatter_(1, owners, True)
+                factor = hit[:, :world].sum(dim=1, keepdim=True).float()
+            want = xs.float() * factor
+            got = combined.detach().cpu().float()
+            if got.shape != want.shape or not torch.allclose(got, want, rtol=3e-2, atol=3e-2):
+                worst = (got - want).abs().max().item() if got.shape == want.shape and got.numel() else -1
+                problems.append(f"combine mismatch (max abs err {worst})")
+        if problems:
+            failure = f"rank {rank} case {case}: {problems}"
+    except Exception as exc:  # noqa: BLE001 - reported collectively
+        failure = f"rank {rank} case {case}: {type(exc).__name__}: {exc}"
+    agree(failure, "case failed")
+
+
+def suite_correctness(args, rank, world, device):
+    experts, topk, hidden, tmax = 8 * world if args.small else 32 * world // max(1, world // 8), 4, args.hidden, 48
+    experts = max(experts, world * 2)
+    dims = (experts, topk, hidden, tmax)
+    config = HostStagedConfig(channels=args.channels, timeout_ms=args.timeout_ms, transport=args.transport,
+                              tx_warps=2, rx_warps=3, payload_slots=args.payload_slots,
+                              descriptor_slots=args.payload_slots)
+    with HostStagedEPBuffer(dist.group.WORLD, tmax, hidden, topk, experts, config) as buffer:
+        cases = [dict(pattern=p, tokens=17, expand=e, alignment=1)
+                 for p in ["random", "local", "multicast", "hotspot", "partial", "none"] for e in (False, True)]
+        cases += [dict(pattern="random", tokens=t, unequal=u, expand=True, alignment=a)
+                  for t, u, a in [(0, False, 1), (48, True, 1), (33, False, 16)]]
+        cases += [dict(pattern="random", tokens=3 + i % 5, expand=bool(i % 2), alignment=8, seed=100 + i) for i in range(4)]
+        cases.append(dict(pattern="multicast", tokens=5, expand=True, alignment=1, weights=False))
+        for case in cases:
+            run_case(buffer, args, rank, world, device, case, dims)
+    return len(cases)
+
+
+def suite_oracle_config(args, rank, world, device):
+    """BASELINE config 1: T=64, hidden=128, fp32, 8 experts, top-2, softmax weights, seed 0."""
+    experts, topk, hidden, tmax = 8, 2, 128, 64
+    config = HostStagedConfig(channels=2, transport=args.transport, timeout_ms=args.timeout_ms)
+    g = torch.Generator().manual_seed(0 + rank)
+    x = torch.randn(tmax, hidden, generator=g, dtype=torch.float32)
+    idx = torch.rand(tmax, experts, generator=g).topk(topk, dim=1).indices.to(torch.int64)
+    w = torch.softmax(torch.randn(tmax, topk, generator=g), dim=1)
+    if args.transport != "cpu":
+        x = x.to(torch.bfloat16)
+    everyone = gather((x, idx, w))
+    with HostStagedEPBuffer(dist.group.WORLD, tmax, hidden, topk, experts, config) as buffer:
+        for expand in (False, True):
+            xs, ids, ws = to_device((x, idx, w), device)
+            recv_x, recv_idx, recv_w, handle, event = buffer.dispatch(xs, ids, ws, do_expand=expand)
+            event.current_stream_wait()
+            buffer.check_errors()
+            expected = reference.dispatch_reference(everyone, rank, experts, tmax, do_expand=expand)
+            actual = dict(handle._result)
+            problems = reference.compare_dispatch(actual, expected, do_expand=expand, do_zero_padding=False)
+            agree(f"rank {rank}: {problems}" if problems else None, "oracle config")
+    return 2
+
+
+SUITES = {"correctness": suite_correctness, "oracle_config": suite_oracle_config}
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--transport", default="cpu")
+    parser.add_argument("--suite", default="correctness")
+    parser.add_argument("--hidden", type=int, default=256)
+    parser.add_argument("--channels", type=int, default=4)
+    parser.add_argument("--payload-slots", type=int, default=0)
+    parser.add_argument("--timeout-ms", type=int, default=5000)
+    parser.add_argument("--small", action="store_true")
+    parser.add_argument("--fp32", action="store_true")
+    args = parser.parse_args()
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    if args.transport == "cpu":
+        device = torch.device("cpu")
+    else:
+        device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+        torch.cuda.set_device(device)
+    count = SUITES[args.suite](args, rank, world, device)
+    dist.barrier()
+    if rank == 0:
+        print(f"OK suite={args.suite} transport={args.transport} world={world} cases={count}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
