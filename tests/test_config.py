@@ -1,0 +1,62 @@
+"""Flag system: validation rules and the capability gates (reference: tests/test_api.py:121-209)."""
+
+import pytest
+
+from pcie_ep_b200 import HostStagedConfig
+
+
+def test_defaults_are_valid_and_frozen():
+    config = HostStagedConfig()
+    assert config.stage == 6 and config.wire_dtype == "bf16" and config.output_pool_size == 3
+    with pytest.raises(Exception):
+        config.channels = 4  # frozen dataclass
+
+
+@pytest.mark.parametrize("kwargs,error", [
+    (dict(stage=5), ValueError),
+    (dict(channels=0), ValueError),
+    (dict(channels=129), ValueError),
+    (dict(pipeline_stages=4), ValueError),
+    (dict(receive_expand_mode="fast"), ValueError),
+    (dict(receive_expand_mode="pipelined", fuse_receive_expand=False), ValueError),
+    (dict(wire_dtype="fp4"), ValueError),
+    (dict(wire_dtype="fp8_e4m3"), NotImplementedError),           # needs stage 7
+    (dict(numa_mode="relay"), NotImplementedError),               # needs stage 8
+    (dict(numa_mode="sideways", stage=8), ValueError),
+    (dict(relay_workers_per_numa=2), NotImplementedError),
+    (dict(stage=8, relay_workers_per_numa=0), ValueError),
+    (dict(stage=8, relay_cpu_affinity=(1, 1)), ValueError),
+    (dict(stage=8, relay_cpu_affinity=[1]), ValueError),
+    (dict(output_pool_size=1), ValueError),
+    (dict(output_pool_size=9), ValueError),
+    (dict(timeout_ms=0), ValueError),
+    (dict(payload_slots=-1), ValueError),
+    (dict(tx_delay_ns=-1), ValueError),
+    (dict(transport="carrier_pigeon"), ValueError),
+    (dict(copy_engine="dma"), ValueError),
+    (dict(tx_warps=0), ValueError),
+    (dict(rx_warps=13), ValueError),
+    (dict(virtual_ranks=17), ValueError),
+    (dict(stage=8, numa_mode="relay", transport="peer"), ValueError),
+    (dict(payload_slots=4, descriptor_slots=5), ValueError),
+])
+def test_rejections(kwargs, error):
+    with pytest.raises(error):
+        HostStagedConfig(**kwargs)
+
+
+def test_accepted_combinations():
+    HostStagedConfig(stage=7, wire_dtype="fp8_e4m3")
+    HostStagedConfig(stage=8, numa_mode="relay", relay_workers_per_numa=2, channels=4, relay_cpu_affinity=(0, 2))
+    HostStagedConfig(payload_slots=3, descriptor_slots=3)
+    HostStagedConfig(payload_slots=1, descriptor_slots=256)
+
+
+def test_native_options_and_transport_resolution():
+    config = HostStagedConfig(stage=7, wire_dtype="fp8_e4m3", channels=8)
+    options = config.native_options()
+    assert options["payload_dtype"] == "fp8" and options["channels"] == 8 and "directory" not in options
+    assert config.resolved_transport(True) == "peer"
+    assert config.resolved_transport(False) == "cpu"
+    assert HostStagedConfig(stage=8, numa_mode="relay").resolved_transport(True) == "host_staged"
+    assert HostStagedConfig(transport="host_staged").resolved_transport(True) == "host_staged"
