@@ -150,10 +150,10 @@ def max_over_ranks(value):
 def default_channels(world, tokens):
     # one CTA per channel; enough channels to keep NVLink and HBM busy at large T, few at small T
     if tokens <= 256:
-        return 16
-    if tokens <= 1024:
         return 32
-    return 64
+    if tokens <= 1024:
+        return 64
+    return 128
 
 
 def run_ours(args, rank, world, local_rank):

@@ -44,12 +44,13 @@ struct DispatchShared {
 };
 
 // Dynamic shared memory: header | cnt_e[E] | bits_e[E] | total_e[E] | eoff[El+1] | ecount[El] |
-// spre[P*El] | (TMA only) one row buffer per send/receive warp.
+// spre[P*El] | msg[P*counts_stride] | (TMA only) one row buffer per send/receive warp.
 inline std::size_t dispatch_smem_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma) {
     std::size_t bytes = align_up(sizeof(DispatchShared), 16);
     bytes += static_cast<std::size_t>(lay.num_experts) * 12;
     bytes += static_cast<std::size_t>(lay.num_local_experts) * 8 + 4;
     bytes += static_cast<std::size_t>(lay.num_ranks) * lay.num_local_experts * 4;
+    bytes = align_up(bytes, 16) + static_cast<std::size_t>(lay.num_ranks) * lay.counts_stride * 4;
     bytes = align_up(bytes, 128);
     if (use_tma) bytes += static_cast<std::size_t>(tx_warps + rx_warps) * align_up(lay.meta_off + lay.meta_bytes, 128);
     return bytes;
@@ -341,10 +342,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     int* eoff = total_e + E;      // [El+1]
     int* ecount = eoff + El + 1;  // [El]
     int* spre = ecount + El;      // [P*El]
-    const std::size_t slots_at =
-        align_up(align_up(sizeof(DispatchShared), 16) + static_cast<std::size_t>(E) * 12 +
-                     static_cast<std::size_t>(El) * 8 + 4 + static_cast<std::size_t>(P) * El * 4,
-                 128);
+    const std::size_t msg_at = align_up(align_up(sizeof(DispatchShared), 16) + static_cast<std::size_t>(E) * 12 +
+                                            static_cast<std::size_t>(El) * 8 + 4 + static_cast<std::size_t>(P) * El * 4,
+                                        16);
+    int* msg_sm = reinterpret_cast<int*>(smem_raw + msg_at);  // [P][counts_stride]: every source's counts message
+    const std::size_t slots_at = align_up(msg_at + static_cast<std::size_t>(P) * lay.counts_stride * 4, 128);
     const int slot_bytes = static_cast<int>(align_up(lay.meta_off + lay.meta_bytes, 128));
     unsigned char* my_slot = smem_raw + slots_at + static_cast<std::size_t>(warp > 0 ? warp - 1 : 0) * slot_bytes;
 
@@ -442,57 +444,78 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             for (int i = threadIdx.x; i < C * P; i += blockDim.x)
                 a.plan_counts[P + E + i] = __ldcg(rc->block_hist + static_cast<std::size_t>(i / P) * (E + P) + E + i % P);
         }
-        if (warp == 0) {
-            // Stable ordinals, 32 tokens at a time: lane = token.  bits_*[bin] collects which lanes hit a
-            // bin; an ordinal is (tokens before this chunk) + (lower lanes in the bin).
-            for (int base_t = t0; base_t < t1; base_t += 32) {
-                const int t = base_t + lane;
-                const bool active = t < t1;
-                const unsigned mask = active ? a.plan_mask[t] : 0u;
-                const std::int64_t* row = a.topk_idx + static_cast<std::size_t>(active ? t : 0) * K;
-                for (int k = 0; k < K; ++k) {
-                    const std::int64_t e = active ? row[k] : -1;
-                    if (e >= 0 && e < E) atomicOr(&bits_e[e], 1u << lane);
-                }
-                for (unsigned m = mask; m; m &= m - 1) atomicOr(&sh->bits_r[__ffs(m) - 1], 1u << lane);
-                __syncwarp();
-                if (active) {
-                    for (int k = 0; k < K; ++k) {
-                        const std::int64_t e = row[k];
-                        a.plan_expert_ord[static_cast<std::size_t>(t) * K + k] =
-                            (e >= 0 && e < E) ? cnt_e[e] + __popc(bits_e[e] & lt_mask) : -1;
-                    }
-                    for (int d = 0; d < P; ++d)
-                        a.plan_slot[static_cast<std::size_t>(t) * P + d] =
-                            (mask >> d & 1u) ? sh->cnt_r[d] + __popc(sh->bits_r[d] & lt_mask) : -1;
-                }
-                __syncwarp();
-                for (int k = 0; k < K; ++k) {
-                    const std::int64_t e = active ? row[k] : -1;
-                    if (e >= 0 && e < E) {
-                        const unsigned b = bits_e[e];
-                        if (lane == 31u - __clz(b)) cnt_e[e] += __popc(b);
-                    }
-                }
-                for (unsigned m = mask; m; m &= m - 1) {
-                    const int d = __ffs(m) - 1;
-                    const unsigned b = sh->bits_r[d];
-                    if (lane == 31u - __clz(b)) sh->cnt_r[d] += __popc(b);
-                }
-                __syncwarp();
-                for (int k = 0; k < K; ++k) {
-                    const std::int64_t e = active ? row[k] : -1;
-                    if (e >= 0 && e < E) bits_e[e] = 0;
-                }
-                for (unsigned m = mask; m; m &= m - 1) sh->bits_r[__ffs(m) - 1] = 0;
-                __syncwarp();
-            }
-        }
     } else {
         for (int i = threadIdx.x; i < P + E; i += blockDim.x) {
             if (i < P) sh->total_r[i] = a.plan_counts[i];
             else total_e[i - P] = a.plan_counts[i];
         }
+        __syncthreads();
+    }
+    // Two things happen side by side before the roles split: warp 1 tells every destination what to
+    // expect (counts message; reference: publish_counts, layout.cuh:7-29 -- channel d, d+C, ... serves
+    // destination d), warp 0 numbers this channel's tokens.
+    if (warp == 1 && !rc->test_withhold_counts) {
+        for (int d = c; d < P; d += C) {
+            int* msg = reinterpret_cast<int*>(rc->seg[d] + lay.counts_off) + static_cast<std::size_t>(me) * lay.counts_stride;
+            for (int i = lane; i < P + El + C; i += 32) {
+                int v;
+                if (i < P) v = sh->total_r[i];
+                else if (i < P + El) v = total_e[d * El + (i - P)];
+                else if (a.cached) v = a.plan_counts[P + E + (i - P - El) * P + d];
+                else v = __ldcg(rc->block_hist + static_cast<std::size_t>(i - P - El) * (E + P) + E + d);
+                msg[i] = v;
+            }
+            __syncwarp();
+            if (lane == 0) ptx::st_release_sys(flag_ptr(rc->seg[d], lay.counts_flag_off, me), epoch);
+        }
+    }
+    if (!a.cached) {
+    if (warp == 0) {
+        // Stable ordinals, 32 tokens at a time: lane = token.  bits_*[bin] collects which lanes hit a
+        // bin; an ordinal is (tokens before this chunk) + (lower lanes in the bin).
+        for (int base_t = t0; base_t < t1; base_t += 32) {
+            const int t = base_t + lane;
+            const bool active = t < t1;
+            const unsigned mask = active ? a.plan_mask[t] : 0u;
+            const std::int64_t* row = a.topk_idx + static_cast<std::size_t>(active ? t : 0) * K;
+            for (int k = 0; k < K; ++k) {
+                const std::int64_t e = active ? row[k] : -1;
+                if (e >= 0 && e < E) atomicOr(&bits_e[e], 1u << lane);
+            }
+            for (unsigned m = mask; m; m &= m - 1) atomicOr(&sh->bits_r[__ffs(m) - 1], 1u << lane);
+            __syncwarp();
+            if (active) {
+                for (int k = 0; k < K; ++k) {
+                    const std::int64_t e = row[k];
+                    a.plan_expert_ord[static_cast<std::size_t>(t) * K + k] =
+                        (e >= 0 && e < E) ? cnt_e[e] + __popc(bits_e[e] & lt_mask) : -1;
+                }
+                for (int d = 0; d < P; ++d)
+                    a.plan_slot[static_cast<std::size_t>(t) * P + d] =
+                        (mask >> d & 1u) ? sh->cnt_r[d] + __popc(sh->bits_r[d] & lt_mask) : -1;
+            }
+            __syncwarp();
+            for (int k = 0; k < K; ++k) {
+                const std::int64_t e = active ? row[k] : -1;
+                if (e >= 0 && e < E) {
+                    const unsigned b = bits_e[e];
+                    if (lane == 31u - __clz(b)) cnt_e[e] += __popc(b);
+                }
+            }
+            for (unsigned m = mask; m; m &= m - 1) {
+                const int d = __ffs(m) - 1;
+                const unsigned b = sh->bits_r[d];
+                if (lane == 31u - __clz(b)) sh->cnt_r[d] += __popc(b);
+            }
+            __syncwarp();
+            for (int k = 0; k < K; ++k) {
+                const std::int64_t e = active ? row[k] : -1;
+                if (e >= 0 && e < E) bits_e[e] = 0;
+            }
+            for (unsigned m = mask; m; m &= m - 1) sh->bits_r[__ffs(m) - 1] = 0;
+            __syncwarp();
+        }
+    }
     }
     if (cta_failed(health, &sh->cta_flag)) return;
 
@@ -514,13 +537,19 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         test_delay(rc->delay_prefix_ns);
         const bool bad = warp_failed(health);
         if (!bad) {
-            const int* msg = reinterpret_cast<const int*>(my_seg + lay.counts_off);
             const int stride = lay.counts_stride;
+            {   // bring all P messages into shared memory with wide, independent loads
+                const uint4* g = reinterpret_cast<const uint4*>(my_seg + lay.counts_off);
+                uint4* d4 = reinterpret_cast<uint4*>(msg_sm);
+                for (int i = lane; i < P * stride / 4; i += 32) d4[i] = ptx::ld_v4(g + i);
+            }
+            __syncwarp();
+            const int* msg = msg_sm;
             for (int el = lane; el < El; el += 32) {
                 int run = 0;
                 for (int s = 0; s < P; ++s) {
                     spre[s * El + el] = run;
-                    run += ptx::ld_volatile(msg + s * stride + P + el);
+                    run += msg[s * stride + P + el];
                 }
                 ecount[el] = run;
             }
@@ -547,7 +576,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             }
             if (lane == 0) eoff[El] = carry;
             // unique layout: rows grouped by source rank
-            const int from = lane < static_cast<unsigned>(P) ? ptx::ld_volatile(msg + lane * stride + me) : 0;
+            const int from = lane < static_cast<unsigned>(P) ? msg[lane * stride + me] : 0;
             int incl = from;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -560,9 +589,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             if (lane < static_cast<unsigned>(P)) {
                 const int* chan = msg + lane * stride + P + El;
                 int before = 0;
-                for (int c2 = 0; c2 < c; ++c2) before += ptx::ld_volatile(chan + c2);
+                for (int c2 = 0; c2 < c; ++c2) before += chan[c2];
                 sh->chan_base[lane] = before;
-                sh->chan_expected[lane] = ptx::ld_volatile(chan + c);
+                sh->chan_expected[lane] = chan[c];
                 a.recv_chan_counts[lane * C + c] = sh->chan_expected[lane];
             }
             if (carry > rc->expanded_cap || unique_total > rc->unique_cap) {
@@ -606,23 +635,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     } else if (warp <= tx_warps) {
         // ===== send =====
         const int w = warp - 1;
-        // counts message to destination d (reference: publish_counts, layout.cuh:7-29): the first send
-        // warp of channel d, d+C, ... writes it and releases that peer's counts flag.
-        if (w == 0 && !rc->test_withhold_counts) {
-            for (int d = c; d < P; d += C) {
-                int* msg = reinterpret_cast<int*>(rc->seg[d] + lay.counts_off) + static_cast<std::size_t>(me) * lay.counts_stride;
-                for (int i = lane; i < P + El + C; i += 32) {
-                    int v;
-                    if (i < P) v = sh->total_r[i];
-                    else if (i < P + El) v = total_e[d * El + (i - P)];
-                    else if (a.cached) v = a.plan_counts[P + E + (i - P - El) * P + d];
-                    else v = __ldcg(rc->block_hist + static_cast<std::size_t>(i - P - El) * (E + P) + E + d);
-                    msg[i] = v;
-                }
-                __syncwarp();
-                if (lane == 0) ptx::st_release_sys(flag_ptr(rc->seg[d], lay.counts_flag_off, me), epoch);
-            }
-        }
         unsigned parity = 0;
         unsigned char* meta_sm = use_tma ? my_slot + lay.meta_off : sh->meta[warp];
         const unsigned self_bit = 1u << me;

@@ -105,6 +105,7 @@ class HostStagedEPBuffer:
         self._lock = threading.RLock()
         self._consumer_streams: Dict[tuple, Any] = {}
         self._graph_capture = None
+        self._comm_busy = False  # work was queued on the communication stream that the compute stream has not waited for
         self._owns_control_group = False
         self.runtime = None
         self.segments = None
@@ -204,6 +205,27 @@ class HostStagedEPBuffer:
     def _current_stream(self) -> Any:
         return torch.cuda.current_stream(self.device) if self.on_gpu else _NullStream()
 
+    def _launch_stream(self, compute: Any, previous_event: Any, async_with_compute_stream: bool) -> Any:
+        """Pick the stream a launch goes to and set up its dependencies (device-side waits only).
+
+        A synchronous call without a producer event is "communication stream waits for the compute
+        stream, compute stream waits for the result": that is ordinary in-order execution, so the kernel
+        is put on the compute stream itself and both cross-stream hand-offs (tens of microseconds of
+        device latency per call) disappear.  Everything else goes to the communication stream.
+        """
+        if async_with_compute_stream or previous_event is not None:
+            self._wait_for_inputs(compute, previous_event)
+            self._comm_busy = True
+            return self._comm_stream
+        if self._comm_busy:
+            compute.wait_stream(self._comm_stream)
+            self._comm_busy = False
+        skip = {self._stream_key(self._comm_stream), self._stream_key(compute)}
+        for key, stream in self._consumer_streams.items():
+            if key not in skip:
+                compute.wait_stream(stream)
+        return compute
+
     def _wait_for_inputs(self, compute: Any, previous_event: Any) -> None:
         if previous_event is None:
             self._comm_stream.wait_stream(compute)
@@ -295,7 +317,7 @@ class HostStagedEPBuffer:
             compute = self._current_stream()
             result, event = self._dispatch_on_comm_stream(
                 x, topk_idx, topk_weights, cumulative_local_expert_recv_stats, alignment, do_expand,
-                do_zero_padding, compute, previous_event, cached_layout,
+                do_zero_padding, compute, previous_event, cached_layout, async_with_compute_stream,
             )
             refs = (self, x, topk_idx, topk_weights, result, cumulative_local_expert_recv_stats)
             if handle is not None:
@@ -312,7 +334,9 @@ class HostStagedEPBuffer:
             if not async_with_compute_stream and self.on_gpu:
                 # result tensors live in pools owned by the runtime, not by the caching allocator:
                 # nothing to record, but the reader stream must be known before the pool is reused
-                compute.wait_event(event)
+                if previous_event is not None:
+                    compute.wait_event(event)
+                    self._comm_busy = False
                 self._register_consumer_stream(compute)
             if defer_epilogue:
                 overlap.register_hook_after_wait(lambda: outputs)
@@ -321,7 +345,7 @@ class HostStagedEPBuffer:
 
     def _dispatch_on_comm_stream(
         self, x, topk_idx, topk_weights, cumulative, alignment, do_expand, do_zero_padding, compute,
-        previous_event, cached_layout=None,
+        previous_event, cached_layout=None, async_with_compute_stream=True,
     ):
         """Order dependencies, launch, record completion; never waits on the CPU."""
         if not self.on_gpu:
@@ -330,9 +354,9 @@ class HostStagedEPBuffer:
             if cumulative is not None:
                 cumulative.add_(result["expert_counts"])
             return result, None
-        comm = self._comm_stream
-        self._wait_for_inputs(compute, previous_event)
-        _record_tensors((x, topk_idx, topk_weights), comm)
+        comm = self._launch_stream(compute, previous_event, async_with_compute_stream)
+        if comm is not compute:
+            _record_tensors((x, topk_idx, topk_weights), comm)
         result = self.runtime.dispatch(x, topk_idx, topk_weights, alignment, do_expand, do_zero_padding,
                                        cached_layout, False, comm.cuda_stream)
         if cumulative is not None:
@@ -387,9 +411,9 @@ class HostStagedEPBuffer:
             if torch.cuda.is_current_stream_capturing():
                 raise NotImplementedError("combine cannot be issued inside a stream capture")
             compute = self._current_stream()
-            comm = self._comm_stream
-            self._wait_for_inputs(compute, previous_event)
-            _record_tensors((x, out), comm)
+            comm = self._launch_stream(compute, previous_event, async_with_compute_stream)
+            if comm is not compute:
+                _record_tensors((x, out), comm)
             # without `out` the result is a preallocated pool tensor (busy while referenced)
             combined = self.runtime.combine(x, handle._result, weighted, out, comm.cuda_stream)
             event = torch.cuda.Event()
@@ -397,7 +421,9 @@ class HostStagedEPBuffer:
             self._last_event = event
             overlap = EventOverlap(event, (self, x, handle, combined), self._register_consumer_stream)
             if not async_with_compute_stream:
-                compute.wait_event(event)
+                if previous_event is not None:
+                    compute.wait_event(event)
+                    self._comm_busy = False
                 self._register_consumer_stream(compute)
             return combined, None, overlap
 

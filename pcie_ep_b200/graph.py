@@ -55,19 +55,20 @@ class GraphDispatch:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("GraphDispatch.replay cannot be nested in another capture")
             compute = torch.cuda.current_stream(owner.device)
-            with torch.cuda.stream(owner._comm_stream):
-                owner._wait_for_inputs(compute, previous_event)
+            stream = owner._launch_stream(compute, previous_event, async_with_compute_stream)
+            with torch.cuda.stream(stream):
                 self._graph.replay()
                 event = torch.cuda.Event()
-                event.record(owner._comm_stream)
+                event.record(stream)
             refs = (owner, self, self.x, self.topk_idx, self.topk_weights, self._result)
             overlap = EventOverlap(event, refs, owner._register_consumer_stream)
             handle = HostStagedEPHandle(owner, self.topk_idx, self._result, self.do_expand, self.expert_alignment, overlap)
             owner._last_event, owner._last_handle = event, handle
             self._last_event = event
             if not async_with_compute_stream:
-                compute.wait_event(event)
-                _record_tensors(self._result, compute)
+                if previous_event is not None:
+                    compute.wait_event(event)
+                    owner._comm_busy = False
                 owner._register_consumer_stream(compute)
             return (
                 self._result["recv_x"],
