@@ -101,12 +101,12 @@ struct OutputSet {
     at::Tensor recv_x, recv_idx, recv_w, source_meta, comb_map, recv_chan_counts;
     at::Tensor unique_count, expanded_count, expert_counts, expert_offsets, expert_prefix, source_offsets;
     at::Tensor source_expert_prefix, error, stats, timestamps, prefix_tx_ts;
-    at::Tensor combine_error, combine_stats;
+    at::Tensor combine_error, combine_stats, profile;
 
     std::vector<const at::Tensor*> all() const {
         return {&recv_x, &recv_idx, &recv_w, &source_meta, &comb_map, &recv_chan_counts, &unique_count,
                 &expanded_count, &expert_counts, &expert_offsets, &expert_prefix, &source_offsets,
-                &source_expert_prefix, &error, &stats, &timestamps, &prefix_tx_ts, &combine_error, &combine_stats};
+                &source_expert_prefix, &error, &stats, &timestamps, &prefix_tx_ts, &combine_error, &combine_stats, &profile};
     }
     bool free() const {
         for (const at::Tensor* t : all())
@@ -131,7 +131,7 @@ class DispatchResult {
             "recv_x", "recv_topk_idx", "recv_topk_weights", "source_meta", "comb_map", "recv_chan_counts",
             "unique_count", "expanded_count", "expert_counts", "expert_offsets", "expert_prefix", "source_offsets",
             "source_expert_prefix", "error", "stats", "transport_timestamps_ns", "prefix_tx_timestamps_ns",
-            "combine_error", "combine_stats"};
+            "combine_error", "combine_stats", "profiling"};
         return keys;
     }
 
@@ -194,6 +194,7 @@ class DispatchResult {
         if (key == "prefix_tx_timestamps_ns") return at::alias(s.prefix_tx_ts);
         if (key == "combine_error") return at::alias(s.combine_error);
         if (key == "combine_stats") return at::alias(s.combine_stats);
+        if (key == "profiling") return at::alias(s.profile);
         throw py::key_error(key);
     }
 
@@ -357,6 +358,7 @@ class Runtime {
         a.stats = out.stats.data_ptr<std::int64_t>();
         a.timestamps = out.timestamps.data_ptr<std::int64_t>();
         a.prefix_tx_ts = out.prefix_tx_ts.data_ptr<std::int64_t>();
+        a.profile = out.profile.data_ptr<std::int64_t>();
         p.result = std::make_shared<DispatchResult>(out_set, plan, expand, T, rc_.unique_cap, rc_.expanded_cap, lay_.num_topk);
         return p;
     }
@@ -538,6 +540,7 @@ class Runtime {
         s.prefix_tx_ts = at::zeros({C + 1, 2}, i64);
         s.combine_error = at::zeros({8}, i32);
         s.combine_stats = at::zeros({8}, i64);
+        s.profile = at::zeros({C, 16}, i64);
         return s;
     }
 

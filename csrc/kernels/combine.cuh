@@ -181,7 +181,10 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
         // ===== expert side: reduce + push (never waits) =====
         const int w = warp;
         int item = 0;
-        for (int s = 0; s < P && !warp_failed(health); ++s) {
+        // Destinations are visited in a rank-rotated order: at any moment every rank pushes to a
+        // different peer, instead of all ranks converging on source 0 first, then source 1, ...
+        for (int step = 0; step < P && !warp_failed(health); ++step) {
+            const int s = (me + 1 + step) % P;
             const int n_s = a.recv_chan_counts[s * C + c];
             std::uint8_t* dst_base = rc->seg[s] + lay.cstage_off + static_cast<std::size_t>(me) * Tmax * lay.crow_stride;
             std::uint64_t* flag_base = reinterpret_cast<std::uint64_t*>(rc->seg[s] + lay.cready_off) + static_cast<std::size_t>(me) * Tmax;

@@ -353,6 +353,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     Health health(rc, a.error);
     const std::uint64_t epoch = rc->epochs[0] + 1;
     std::uint8_t* my_seg = rc->seg[me];
+    std::int64_t* prof = a.profile + static_cast<std::size_t>(c) * 16;
+#define BEP_PROF(point) prof[point] = static_cast<std::int64_t>(ptx::globaltimer_ns())
 
     // ---- launch-wide preconditions ---------------------------------------------------------------
     if (ptx::ld_volatile(&rc->sticky[0]) != 0) {
@@ -375,6 +377,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         }
     }
     const unsigned long long t_start = ptx::globaltimer_ns();
+    if (threadIdx.x == 0) {
+        prof[kProfStart] = static_cast<std::int64_t>(t_start);
+        prof[kProfFirstRxRow] = 0;
+        prof[kProfFirstTxDone] = 0;
+    }
 
     // Reuse guard: nothing of this epoch may reach a peer before that peer has finished reading the
     // previous epoch out of its segment (reference: the counts_consumed == epoch-1 wait of
@@ -384,6 +391,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         while (ptx::ld_acquire_sys(done) + 1 < epoch) {
             if (health.give_up(kErrReuseGuardWait, lane, 0)) break;
         }
+    }
+    if (warp == 0) {
+        __syncwarp();
+        if (lane == 0) BEP_PROF(kProfGuardDone);
     }
 
     // ---- phase A: routing layout (skipped with a cached plan) ------------------------------------
@@ -420,7 +431,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         __syncthreads();
         int* hist = rc->block_hist + static_cast<std::size_t>(c) * (E + P);
         for (int i = threadIdx.x; i < E + P; i += blockDim.x) hist[i] = i < E ? cnt_e[i] : sh->cnt_r[i - E];
+        if (threadIdx.x == 0) BEP_PROF(kProfHistDone);
         grid_barrier(&rc->grid_bar[0], health);
+        if (threadIdx.x == 0) BEP_PROF(kProfBarrierDone);
         // exclusive prefix over earlier channels (stable order = channel order = token order)
         for (int i = threadIdx.x; i < E + P; i += blockDim.x) {
             int base = 0, total = 0;
@@ -438,6 +451,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             }
         }
         __syncthreads();
+        if (threadIdx.x == 0) BEP_PROF(kProfPrefixScan);
         if (c == 0) {  // keep the totals with the plan so a cached dispatch can skip all of the above
             for (int i = threadIdx.x; i < P + E; i += blockDim.x)
                 a.plan_counts[i] = i < P ? sh->total_r[i] : total_e[i - P];
@@ -468,6 +482,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             __syncwarp();
             if (lane == 0) ptx::st_release_sys(flag_ptr(rc->seg[d], lay.counts_flag_off, me), epoch);
         }
+        if (lane == 0) BEP_PROF(kProfCountsSent);
     }
     if (!a.cached) {
     if (warp == 0) {
@@ -516,8 +531,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             __syncwarp();
         }
     }
+        if (warp == 0 && lane == 0) BEP_PROF(kProfOrdinalsDone);
     }
     if (cta_failed(health, &sh->cta_flag)) return;
+    if (threadIdx.x == 0) BEP_PROF(kProfRolesSplit);
 
     // ---- role split ------------------------------------------------------------------------------
     unsigned long long st_source = 0, st_remote_rows = 0, st_deliveries = 0, st_early = 0, st_probes = 0,
@@ -534,6 +551,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             }
         }
         __syncwarp();
+        if (lane == 0) BEP_PROF(kProfCountsArrived);
         test_delay(rc->delay_prefix_ns);
         const bool bad = warp_failed(health);
         if (!bad) {
@@ -616,7 +634,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             }
             __threadfence_block();
             __syncwarp();
-            if (lane == 0) *reinterpret_cast<volatile int*>(&sh->prefix_ready) = 1;
+            if (lane == 0) {
+                *reinterpret_cast<volatile int*>(&sh->prefix_ready) = 1;
+                BEP_PROF(kProfPrefixReady);
+            }
             // zero padding between expert segments (reference: advanced_zero_padding,
             // advanced_layout.cuh:250-265): channel c takes local experts c, c+C, ...
             if (a.do_expand && a.zero_padding && !warp_failed(health)) {
@@ -722,9 +743,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                 if (mask & self_bit) ++st_local;
                 st_published += __popc(mask);
                 if (*reinterpret_cast<volatile int*>(&sh->prefix_ready) == 0) ++st_early;
+                if (w == 0 && st_published == static_cast<unsigned long long>(__popc(mask))) BEP_PROF(kProfFirstTxDone);
             }
         }
         if (lane == 0) atomicMax(&sh->last_tx_ns, ptx::globaltimer_ns());
+        if (w == 0 && lane == 0) BEP_PROF(kProfTxDone);
     } else {
         // ===== receive + expand =====
         const int w = warp - 1 - tx_warps;
@@ -902,9 +925,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                         if (lane == 0) ptx::bulk_commit();
                     }
                     if (lane == 0 && s != me) ++st_remote_rows;
+                    if (w == 0 && lane == 0 && prof[kProfFirstRxRow] == 0) BEP_PROF(kProfFirstRxRow);
                 }
                 if (stop) break;
             }
+            if (w == 0 && lane == 0) BEP_PROF(kProfRxDone);
         }
     }
 
@@ -924,6 +949,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     __syncthreads();
     if (threadIdx.x == 0) {
         const unsigned long long t_end = ptx::globaltimer_ns();
+        prof[kProfEnd] = static_cast<std::int64_t>(t_end);
         std::int64_t* cs = rc->chan_stats + static_cast<std::size_t>(c) * 10;
         for (int i = 0; i < 8; ++i) cs[i] = static_cast<std::int64_t>(sh->stat[i]);
         cs[8] = static_cast<std::int64_t>(t_start);

@@ -208,6 +208,26 @@ struct DispatchArgs {
     std::int64_t* stats;           // [8]
     std::int64_t* timestamps;      // [2] transport start / end (globaltimer ns)
     std::int64_t* prefix_tx_ts;    // [C+1][2]
+    std::int64_t* profile;         // [C][16] per-channel phase timestamps (globaltimer ns), see ProfilePoint
+};
+
+// Phase timestamps every channel CTA leaves behind (one store each; always on).
+enum ProfilePoint : int {
+    kProfStart = 0,
+    kProfGuardDone = 1,     // reuse guard satisfied (warp 0)
+    kProfHistDone = 2,      // per-channel histogram written
+    kProfBarrierDone = 3,   // grid barrier passed
+    kProfPrefixScan = 4,    // exclusive prefix over channels done
+    kProfCountsSent = 5,    // counts messages released (warp 1)
+    kProfOrdinalsDone = 6,  // stable ordinals written (warp 0)
+    kProfRolesSplit = 7,
+    kProfCountsArrived = 8, // all P counts flags seen (control warp)
+    kProfPrefixReady = 9,
+    kProfFirstTxDone = 10,  // first token of send warp 0 published
+    kProfTxDone = 11,       // send warp 0 finished its tokens
+    kProfFirstRxRow = 12,   // receive warp 0 got its first row
+    kProfRxDone = 13,       // receive warp 0 finished its rows
+    kProfEnd = 14,
 };
 
 struct DispatchLaunch {
