@@ -101,12 +101,12 @@ struct OutputSet {
     at::Tensor recv_x, recv_idx, recv_w, source_meta, comb_map, recv_chan_counts;
     at::Tensor unique_count, expanded_count, expert_counts, expert_offsets, expert_prefix, source_offsets;
     at::Tensor source_expert_prefix, error, stats, timestamps, prefix_tx_ts;
-    at::Tensor combine_error, combine_stats, profile;
+    at::Tensor combine_error, combine_stats, profile, combine_profile;
 
     std::vector<const at::Tensor*> all() const {
         return {&recv_x, &recv_idx, &recv_w, &source_meta, &comb_map, &recv_chan_counts, &unique_count,
                 &expanded_count, &expert_counts, &expert_offsets, &expert_prefix, &source_offsets,
-                &source_expert_prefix, &error, &stats, &timestamps, &prefix_tx_ts, &combine_error, &combine_stats, &profile};
+                &source_expert_prefix, &error, &stats, &timestamps, &prefix_tx_ts, &combine_error, &combine_stats, &profile, &combine_profile};
     }
     bool free() const {
         for (const at::Tensor* t : all())
@@ -131,7 +131,7 @@ class DispatchResult {
             "recv_x", "recv_topk_idx", "recv_topk_weights", "source_meta", "comb_map", "recv_chan_counts",
             "unique_count", "expanded_count", "expert_counts", "expert_offsets", "expert_prefix", "source_offsets",
             "source_expert_prefix", "error", "stats", "transport_timestamps_ns", "prefix_tx_timestamps_ns",
-            "combine_error", "combine_stats", "profiling"};
+            "combine_error", "combine_stats", "profiling", "combine_profiling"};
         return keys;
     }
 
@@ -195,6 +195,7 @@ class DispatchResult {
         if (key == "combine_error") return at::alias(s.combine_error);
         if (key == "combine_stats") return at::alias(s.combine_stats);
         if (key == "profiling") return at::alias(s.profile);
+        if (key == "combine_profiling") return at::alias(s.combine_profile);
         throw py::key_error(key);
     }
 
@@ -415,6 +416,7 @@ class Runtime {
         a.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
         a.error = set.combine_error.data_ptr<int>();
         a.stats = set.combine_stats.data_ptr<std::int64_t>();
+        a.profile = set.combine_profile.data_ptr<std::int64_t>();
         return p;
     }
 
@@ -427,7 +429,7 @@ class Runtime {
         launch.r[0] = p.args;
         cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
                                                  : at::cuda::getCurrentCUDAStream(device_).stream();
-        cuda_check(launch_combine(launch, options_.channels, threads_, launch_stream), "combine launch");
+        cuda_check(launch_combine(launch, options_.channels, static_cast<std::size_t>(lay_.crow_stride), launch_stream), "combine launch");
         return p.out;
     }
 
@@ -541,6 +543,7 @@ class Runtime {
         s.combine_error = at::zeros({8}, i32);
         s.combine_stats = at::zeros({8}, i64);
         s.profile = at::zeros({C, 16}, i64);
+        s.combine_profile = at::zeros({C, 8}, i64);
         return s;
     }
 
@@ -640,7 +643,7 @@ inline void launch_combine_group(const std::vector<std::shared_ptr<Runtime>>& ru
     CombineLaunch launch{};
     launch.num_virtual = static_cast<int>(runtimes.size());
     for (std::size_t i = 0; i < runtimes.size(); ++i) launch.r[i] = prepared[i].args;
-    cuda_check(launch_combine(launch, runtimes[0]->channels(), runtimes[0]->threads(),
+    cuda_check(launch_combine(launch, runtimes[0]->channels(), static_cast<std::size_t>(runtimes[0]->layout().crow_stride),
                               at::cuda::getCurrentCUDAStream(device)),
                "combine launch");
 }

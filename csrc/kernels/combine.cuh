@@ -37,110 +37,58 @@ __device__ __forceinline__ uint4 pack_chunk(const float (&acc)[8]) {
     return out;
 }
 
-// dst[q] = bf16( sum_i w_i * rows_i[q] ) over `n` rows, FP32 accumulation in row order.  Lane i < n
-// holds row i's pointer and weight.  One pass keeps ROWS x CH 16-byte loads in flight per lane (64
-// registers of payload) before the first is consumed; the caller picks the shape from n.
-// n <= ROWS: the sum of one chunk is formed in one go, nothing is carried between passes.
-template <int ROWS, int CH, bool COHERENT>
-__device__ __forceinline__ void reduce_rows_once(const std::uint8_t* row_of_lane, float weight_of_lane, int n,
-                                                 std::uint8_t* dst, int chunks) {
+// dst[q] = bf16( sum_i w_i * rows_i[q] ) over `n` rows, FP32 accumulation in row order.  Row i lives at
+// base + index(lane i) * stride, its weight in lane i.  `dst` is a generic pointer (shared or global).
+// Rows are taken two at a time, four 16-byte chunks per lane each: 8 loads in flight per lane.
+__device__ __forceinline__ void reduce_rows(const std::uint8_t* base, std::size_t stride, int index_of_lane,
+                                            float weight_of_lane, int n, std::uint8_t* dst, int chunks) {
     const unsigned lane = ptx::lane_id();
-    const std::uint8_t* src[ROWS];
-    float w[ROWS];
+    for (int q0 = 0; q0 < chunks; q0 += 128) {
+        float acc[4][8];
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        src[r] = shfl_ptr(const_cast<std::uint8_t*>(row_of_lane), r);
-        w[r] = __shfl_sync(0xffffffffu, weight_of_lane, r);
-    }
-    for (int q0 = 0; q0 < chunks; q0 += 32 * CH) {
-        uint4 v[ROWS][CH];
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-            if (r < n) {
-#pragma unroll
-                for (int u = 0; u < CH; ++u) {
-                    const int q = q0 + u * 32 + lane;
-                    if (q < chunks)
-                        v[r][u] = COHERENT ? ptx::ld_v4(src[r] + static_cast<std::size_t>(q) * 16)
-                                           : ptx::ld_nc_v4(src[r] + static_cast<std::size_t>(q) * 16);
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < CH; ++u) {
-            const int q = q0 + u * 32 + lane;
-            if (q < chunks) {
-                float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-                for (int r = 0; r < ROWS; ++r)
-                    if (r < n) accumulate_chunk(acc, v[r][u], w[r]);
-                ptx::st_v4(dst + static_cast<std::size_t>(q) * 16, pack_chunk(acc));
-            }
-        }
-    }
-}
-
-// any n: rows in groups of 8, partial sums carried in registers
-template <bool COHERENT>
-__device__ __forceinline__ void reduce_rows_many(const std::uint8_t* row_of_lane, float weight_of_lane, int n,
-                                                 std::uint8_t* dst, int chunks) {
-    const unsigned lane = ptx::lane_id();
-    for (int q0 = 0; q0 < chunks; q0 += 64) {
-        float acc[2][8];
-#pragma unroll
-        for (int u = 0; u < 2; ++u)
+        for (int u = 0; u < 4; ++u)
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[u][e] = 0.0f;
-        for (int i0 = 0; i0 < n; i0 += 4) {
-            uint4 v[4][2];
+        for (int i0 = 0; i0 < n; i0 += 2) {
+            const bool two = i0 + 1 < n;
+            const std::uint8_t* src0 = base + static_cast<std::size_t>(__shfl_sync(0xffffffffu, index_of_lane, i0)) * stride;
+            const std::uint8_t* src1 = base + static_cast<std::size_t>(__shfl_sync(0xffffffffu, index_of_lane, two ? i0 + 1 : i0)) * stride;
+            const float w0 = __shfl_sync(0xffffffffu, weight_of_lane, i0);
+            const float w1 = __shfl_sync(0xffffffffu, weight_of_lane, two ? i0 + 1 : i0);
+            uint4 v0[4], v1[4];
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                if (i0 + r < n) {
-                    const std::uint8_t* src = shfl_ptr(const_cast<std::uint8_t*>(row_of_lane), i0 + r);
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int q = q0 + u * 32 + lane;
-                        if (q < chunks)
-                            v[r][u] = COHERENT ? ptx::ld_v4(src + static_cast<std::size_t>(q) * 16)
-                                               : ptx::ld_nc_v4(src + static_cast<std::size_t>(q) * 16);
-                    }
+            for (int u = 0; u < 4; ++u) {
+                const int q = q0 + u * 32 + lane;
+                if (q < chunks) {
+                    v0[u] = ptx::ld_v4(src0 + static_cast<std::size_t>(q) * 16);
+                    if (two) v1[u] = ptx::ld_v4(src1 + static_cast<std::size_t>(q) * 16);
                 }
             }
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                if (i0 + r < n) {
-                    const float w = __shfl_sync(0xffffffffu, weight_of_lane, i0 + r);
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int q = q0 + u * 32 + lane;
-                        if (q < chunks) accumulate_chunk(acc[u], v[r][u], w);
-                    }
+            for (int u = 0; u < 4; ++u) {
+                const int q = q0 + u * 32 + lane;
+                if (q < chunks) {
+                    accumulate_chunk(acc[u], v0[u], w0);
+                    if (two) accumulate_chunk(acc[u], v1[u], w1);
                 }
             }
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < 4; ++u) {
             const int q = q0 + u * 32 + lane;
-            if (q < chunks) ptx::st_v4(dst + static_cast<std::size_t>(q) * 16, pack_chunk(acc[u]));
+            if (q < chunks) *reinterpret_cast<uint4*>(dst + static_cast<std::size_t>(q) * 16) = pack_chunk(acc[u]);
         }
     }
-}
-
-template <bool COHERENT>
-__device__ __forceinline__ void reduce_rows_any(const std::uint8_t* row_of_lane, float weight_of_lane, int n,
-                                                std::uint8_t* dst, int chunks) {
-    if (n <= 2) reduce_rows_once<2, 4, COHERENT>(row_of_lane, weight_of_lane, n, dst, chunks);
-    else if (n <= 8) reduce_rows_once<8, 1, COHERENT>(row_of_lane, weight_of_lane, n, dst, chunks);
-    else reduce_rows_many<COHERENT>(row_of_lane, weight_of_lane, n, dst, chunks);
 }
 
 }  // namespace detail
 
-constexpr int kCombineWarps = 10;  // every warp first reduces+pushes expert-side rows, then adds rows for its own tokens
+// Each warp owns one row buffer in shared memory (the partial row it is about to push).
+constexpr int kCombineWarps = 12;  // every warp first reduces+pushes expert-side rows, then adds rows for its own tokens
 
 __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __grid_constant__ CombineLaunch launch) {
     using namespace detail;
-    const CombineArgs a = launch.r[blockIdx.y];
+    const CombineArgs& a = launch.r[blockIdx.y];
     const RankConst* __restrict__ rc = a.rc;
     const SegmentLayout& lay = rc->lay;
     const int P = lay.num_ranks, C = lay.num_channels, K = lay.num_topk, H = lay.hidden, Qf = lay.slots_full;
@@ -157,6 +105,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
     const int map_stride = 2 + 2 * K;
     __shared__ int cta_flag;
     __shared__ unsigned long long stat[4];
+    extern __shared__ __align__(128) unsigned char row_buffers[];  // [warps][crow_stride] (vector-capable hidden only)
+    unsigned char* my_buffer = row_buffers + static_cast<std::size_t>(warp) * lay.crow_stride;
 
     Health health(rc, a.error);
     const std::uint64_t epoch = rc->epochs[1] + 1;
@@ -174,97 +124,156 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
             if (health.give_up(kErrReuseGuardWait, lane, 1)) break;
         }
     }
+    std::int64_t* prof = a.profile + static_cast<std::size_t>(c) * 8;
+    if (threadIdx.x == 0) prof[0] = static_cast<std::int64_t>(ptx::globaltimer_ns());
     if (cta_failed(health, &cta_flag)) return;
+    if (threadIdx.x == 0) {
+        prof[1] = static_cast<std::int64_t>(ptx::globaltimer_ns());
+        prof[2] = 0;
+    }
 
     unsigned long long st_rows = 0, st_remote = 0, st_tokens = 0;
     {
-        // ===== expert side: reduce + push (never waits) =====
+        // Every warp walks one work list: first its share of the expert-side rows (reduce the local
+        // expert outputs of one received token, push the partial row to the token's source; never waits),
+        // then its share of this rank's own tokens (wait for the partial rows, add them in rank order).
+        // Both kinds of work end in the same reduction code, instantiated once.
         const int w = warp;
-        int item = 0;
-        // Destinations are visited in a rank-rotated order: at any moment every rank pushes to a
-        // different peer, instead of all ranks converging on source 0 first, then source 1, ...
-        for (int step = 0; step < P && !warp_failed(health); ++step) {
-            const int s = (me + 1 + step) % P;
-            const int n_s = a.recv_chan_counts[s * C + c];
-            std::uint8_t* dst_base = rc->seg[s] + lay.cstage_off + static_cast<std::size_t>(me) * Tmax * lay.crow_stride;
-            std::uint64_t* flag_base = reinterpret_cast<std::uint64_t*>(rc->seg[s] + lay.cready_off) + static_cast<std::size_t>(me) * Tmax;
-            for (int j = 0; j < n_s; ++j, ++item) {
-                if (item % num_warps != w) continue;
-                const int* map = a.comb_map + ((static_cast<std::size_t>(s) * C + c) * Qf + j) * map_stride;
-                const int token = map[0];
-                const int n = map[1];
-                const std::uint8_t* row_ptr = nullptr;
-                float wgt = 0.0f;
-                if (static_cast<int>(lane) < n) {
-                    row_ptr = reinterpret_cast<const std::uint8_t*>(a.y + static_cast<std::size_t>(map[2 + 2 * lane]) * H);
-                    wgt = a.weighted ? __int_as_float(map[3 + 2 * lane]) : 1.0f;
+        const std::size_t rank_stride = static_cast<std::size_t>(Tmax) * lay.crow_stride;
+        // expert-side cursor.  Sources are visited in a rank-rotated order: at any moment every rank
+        // pushes to a different peer instead of all ranks converging on source 0, then source 1, ...
+        int step = 0, j = 0, item = 0;
+        int s = (me + 1) % P;
+        int n_s = a.recv_chan_counts[s * C + c];
+        int t = t0 + w;  // source-side cursor
+        // A pushed row travels as one bulk copy from this warp's shared-memory buffer.  Its flag is
+        // released one row late: after the next row's copy has been issued and the older bulk group has
+        // completed (cp.async.bulk.wait_group 1), so the round trip to the peer overlaps the next row.
+        std::uint64_t* pending_flag = nullptr;
+        while (true) {
+            const std::uint8_t* row_base = nullptr;  // row i of the reduction = row_base + row_index(lane i) * row_stride
+            std::size_t row_stride = 0;
+            int row_index = 0;
+            float wgt = 1.0f;
+            int n = 0;
+            std::uint8_t* dst = nullptr;
+            std::uint64_t* flag = nullptr;
+            bool coherent_side = false;
+            // ---- next expert-side item of this warp
+            bool have = false;
+            while (step < P && !have) {
+                while (j < n_s && item % num_warps != w) {
+                    ++j;
+                    ++item;
                 }
-                std::uint8_t* dst = dst_base + static_cast<std::size_t>(token) * lay.crow_stride;
-                if (vec_ok) {
-                    reduce_rows_any<false>(row_ptr, wgt, n, dst, H / 8);
+                if (j < n_s) {
+                    have = true;
                 } else {
-                    for (int k = lane; k < H; k += 32) {
-                        float acc = 0.0f;
-                        for (int i = 0; i < n; ++i) {
-                            const auto* src = reinterpret_cast<const __nv_bfloat16*>(shfl_ptr(const_cast<std::uint8_t*>(row_ptr), i));
-                            const float wi = __shfl_sync(full, wgt, i);
-                            acc = fmaf(wi, __bfloat162float(src[k]), acc);
-                        }
-                        reinterpret_cast<__nv_bfloat16*>(dst)[k] = __float2bfloat16_rn(acc);
+                    ++step;
+                    j = 0;
+                    if (step < P) {
+                        s = (me + 1 + step) % P;
+                        n_s = a.recv_chan_counts[s * C + c];
                     }
                 }
-                __syncwarp();
+            }
+            if (have) {
+                const int* map = a.comb_map + ((static_cast<std::size_t>(s) * C + c) * Qf + j) * map_stride;
+                const int token = map[0];
+                n = map[1];
+                row_base = reinterpret_cast<const std::uint8_t*>(a.y);
+                row_stride = static_cast<std::size_t>(H) * 2;
+                if (static_cast<int>(lane) < n) {
+                    row_index = map[2 + 2 * lane];
+                    wgt = a.weighted ? __int_as_float(map[3 + 2 * lane]) : 1.0f;
+                }
+                dst = rc->seg[s] + lay.cstage_off + static_cast<std::size_t>(me) * rank_stride +
+                      static_cast<std::size_t>(token) * lay.crow_stride;
+                flag = reinterpret_cast<std::uint64_t*>(rc->seg[s] + lay.cready_off) + static_cast<std::size_t>(me) * Tmax + token;
+                ++j;
+                ++item;
                 if (lane == 0) {
-                    ptx::st_release_sys(flag_base + token, epoch);
                     ++st_rows;
                     if (s != me) ++st_remote;
                 }
-            }
-        }
-    }
-    {
-        // ===== source side: add the partial rows of every destination rank, in rank order =====
-        const int w = warp;
-        for (int t = t0 + w; t < t1; t += num_warps) {
-            if (warp_failed(health)) break;
-            const unsigned mask = a.plan_mask[t];
-            if (lane < static_cast<unsigned>(P) && (mask >> lane & 1u)) {
-                const std::uint64_t* flag = reinterpret_cast<const std::uint64_t*>(my_seg + lay.cready_off) +
-                                            static_cast<std::size_t>(lane) * Tmax + t;
-                while (ptx::ld_acquire_sys(flag) != epoch) {
-                    if (health.give_up(kErrRowWait, lane, t)) break;
+            } else {
+                // ---- next own token of this warp.  Nothing of the expert side may stay unpublished while
+                // this warp waits for its peers (they wait for exactly those rows).
+                if (pending_flag != nullptr) {
+                    if (lane == 0) {
+                        ptx::bulk_wait_all();
+                        ptx::st_release_sys(pending_flag, epoch);
+                    }
+                    pending_flag = nullptr;
                 }
-            }
-            __syncwarp();
-            if (warp_failed(health)) break;
-            std::uint8_t* out = reinterpret_cast<std::uint8_t*>(a.out + static_cast<std::size_t>(t) * H);
-            const std::uint8_t* base = my_seg + lay.cstage_off + static_cast<std::size_t>(t) * lay.crow_stride;
-            const std::size_t rank_stride = static_cast<std::size_t>(Tmax) * lay.crow_stride;
-            if (vec_ok) {
-                // lane i holds the row of the i-th rank (ascending) in the token's mask
-                const std::uint8_t* src_of_lane = nullptr;
-                {
-                    unsigned m = mask;
-                    for (unsigned i = 0; m; m &= m - 1, ++i)
-                        if (lane == i) src_of_lane = base + static_cast<std::size_t>(__ffs(m) - 1) * rank_stride;
+                if (warp == 0 && lane == 0 && prof[2] == 0) prof[2] = static_cast<std::int64_t>(ptx::globaltimer_ns());
+                if (t >= t1) break;
+                const unsigned mask = a.plan_mask[t];
+                if (lane < static_cast<unsigned>(P) && (mask >> lane & 1u)) {
+                    const std::uint64_t* ready = reinterpret_cast<const std::uint64_t*>(my_seg + lay.cready_off) +
+                                                 static_cast<std::size_t>(lane) * Tmax + t;
+                    while (ptx::ld_acquire_sys(ready) != epoch) {
+                        if (health.give_up(kErrRowWait, lane, t)) break;
+                    }
                 }
-                reduce_rows_any<true>(src_of_lane, 1.0f, __popc(mask), out, H / 8);
+                __syncwarp();
+                coherent_side = true;
+                row_base = my_seg + lay.cstage_off + static_cast<std::size_t>(t) * lay.crow_stride;
+                row_stride = rank_stride;
+                unsigned m = mask;
+                for (unsigned i = 0; m; m &= m - 1, ++i)
+                    if (lane == i) row_index = __ffs(m) - 1;
+                n = __popc(mask);
+                dst = reinterpret_cast<std::uint8_t*>(a.out + static_cast<std::size_t>(t) * H);
+                t += num_warps;
+                if (lane == 0) ++st_tokens;
+            }
+            if (warp_failed(health)) break;
+            if (vec_ok && flag != nullptr) {
+                if (lane == 0) ptx::bulk_wait_read_all();  // the previous copy has left the buffer
+                __syncwarp();
+                reduce_rows(row_base, row_stride, row_index, wgt, n, my_buffer, H / 8);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::bulk_s2g(dst, my_buffer, static_cast<unsigned>(H) * 2);
+                    ptx::bulk_commit();
+                    if (pending_flag != nullptr) {
+                        asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
+                        ptx::st_release_sys(pending_flag, epoch);
+                    }
+                }
+                pending_flag = flag;
+                continue;
+            } else if (vec_ok) {
+                reduce_rows(row_base, row_stride, row_index, wgt, n, dst, H / 8);
             } else {
                 for (int k = lane; k < H; k += 32) {
                     float acc = 0.0f;
-                    for (unsigned m = mask; m; m &= m - 1) {
-                        const auto* src = reinterpret_cast<const volatile std::uint16_t*>(base + static_cast<std::size_t>(__ffs(m) - 1) * rank_stride);
+                    for (int i = 0; i < n; ++i) {
+                        const auto* src = reinterpret_cast<const volatile std::uint16_t*>(
+                            row_base + static_cast<std::size_t>(__shfl_sync(full, row_index, i)) * row_stride);
+                        const float wi = __shfl_sync(full, wgt, i);
                         const std::uint16_t bits = src[k];
-                        acc += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&bits));
+                        acc = fmaf(wi, __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&bits)), acc);
                     }
-                    reinterpret_cast<__nv_bfloat16*>(out)[k] = __float2bfloat16_rn(acc);
+                    reinterpret_cast<__nv_bfloat16*>(dst)[k] = __float2bfloat16_rn(acc);
                 }
             }
-            if (lane == 0) ++st_tokens;
+            (void)coherent_side;
+            if (flag != nullptr) {
+                __syncwarp();
+                if (lane == 0) ptx::st_release_sys(flag, epoch);
+            }
+        }
+        if (lane == 0) {
+            ptx::bulk_wait_all();
+            if (pending_flag != nullptr) ptx::st_release_sys(pending_flag, epoch);
         }
     }
 
     __syncwarp();
+    if (warp == 0 && lane == 0) prof[3] = static_cast<std::int64_t>(ptx::globaltimer_ns());
     if (lane == 0) {
         atomicAdd(&stat[0], st_rows);
         atomicAdd(&stat[1], st_remote);
@@ -272,6 +281,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
     }
     __syncthreads();
     if (threadIdx.x == 0) {
+        prof[4] = static_cast<std::int64_t>(ptx::globaltimer_ns());
         std::int64_t* cs = rc->chan_stats + static_cast<std::size_t>(C + c) * 10;  // second half: combine
         for (int i = 0; i < 3; ++i) cs[i] = static_cast<std::int64_t>(stat[i]);
         __threadfence();

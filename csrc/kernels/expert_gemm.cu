@@ -1,0 +1,412 @@
+// tcgen05 grouped expert GEMM: device code and launcher.  See expert_gemm.cuh for the design.
+#include "expert_gemm.cuh"
+
+#include <mutex>
+
+#include "expert_gemm.hpp"
+
+namespace bep {
+namespace gemm {
+
+namespace {
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ std::uint32_t smem_addr(const void* p) {
+    return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(std::uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(std::uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(std::uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(std::uint64_t* bar, unsigned parity) {
+    std::uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait; returns false (and latches *abort) when the limit is hit or somebody else aborted
+__device__ __forceinline__ bool mbar_wait(std::uint64_t* bar, unsigned parity, volatile int* abort) {
+    for (std::uint32_t i = 0; i < kWaitLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort) return false;
+    }
+    *abort = 1;
+    return false;
+}
+
+// 2-D tiled TMA load, no multicast: box lands in shared memory with the tensor map's swizzle
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, std::uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_addr(smem_dst)), "l"(reinterpret_cast<std::uint64_t>(map)), "r"(x), "r"(y), "r"(smem_addr(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(std::uint32_t* smem_result, unsigned columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(smem_result)), "r"(columns)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(std::uint32_t taddr, unsigned columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]; one thread issues for the CTA
+__device__ __forceinline__ void umma_f16(std::uint32_t tmem_d, std::uint64_t desc_a, std::uint64_t desc_b,
+                                         std::uint32_t idesc, std::uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// all MMAs issued so far by this thread arrive on `bar` when they have completed
+__device__ __forceinline__ void umma_commit(std::uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
+                 : "memory");
+}
+// 32 lanes x 32 columns of FP32 out of TMEM: thread i gets columns [c, c+32) of lane (base lane + i)
+__device__ __forceinline__ void tmem_ld_32x32(std::uint32_t taddr, std::uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) wide, stored
+// with the 128-byte swizzle TMA applied: 8-row groups are 1024 bytes apart (stride byte offset), the
+// leading byte offset is unused for swizzled K-major operands, descriptor version 1 (sm_100),
+// layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ std::uint64_t make_smem_desc(const void* tile) {
+    const std::uint64_t addr = smem_addr(tile);
+    std::uint64_t desc = 0;
+    desc |= (addr & 0x3FFFFull) >> 4;                 // bits  0..13 start address / 16
+    desc |= static_cast<std::uint64_t>(0) << 16;      // bits 16..29 leading byte offset / 16
+    desc |= static_cast<std::uint64_t>(1024 >> 4) << 32;  // bits 32..45 stride byte offset / 16
+    desc |= static_cast<std::uint64_t>(1) << 46;      // bits 46..47 descriptor version
+    desc |= static_cast<std::uint64_t>(2) << 61;      // bits 61..63 swizzle mode: 128B
+    return desc;
+}
+
+// Instruction descriptor, kind::f16: D = F32, A = B = BF16, both K-major, N and M encoded /8 and /16.
+__host__ __device__ constexpr std::uint32_t make_idesc_bf16(int m, int n) {
+    return (1u << 4)                                   // D format: F32
+           | (1u << 7)                                 // A format: BF16
+           | (1u << 10)                                // B format: BF16
+           | (static_cast<std::uint32_t>(n >> 3) << 17)
+           | (static_cast<std::uint32_t>(m >> 4) << 24);
+}
+
+struct TileCursor {
+    // walks tiles in (expert, n-tile, m-tile) order: consecutive tiles share the weight tile
+    int expert = 0;
+    int first_tile = 0;  // index of the expert's first tile
+    int m_tiles = 0;
+
+    __device__ __forceinline__ bool locate(int tile, const GroupedGemmParams& p, int n_tiles, int& m_tile, int& n_tile) {
+        while (expert < p.num_experts) {
+            m_tiles = (p.expert_counts[expert] + kBlockM - 1) / kBlockM;
+            const int tiles_here = m_tiles * n_tiles;
+            if (tile < first_tile + tiles_here) {
+                const int local = tile - first_tile;
+                n_tile = local / m_tiles;
+                m_tile = local % m_tiles;
+                return true;
+            }
+            first_tile += tiles_here;
+            ++expert;
+        }
+        return false;
+    }
+};
+
+}  // namespace
+
+template <bool kSwiGLU>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GroupedGemmParams p) {
+    using Plan = SmemPlan<kSwiGLU>;
+    constexpr int kStages = Plan::kStages;
+    constexpr int kAccCols = kSwiGLU ? 2 * kBlockN : kBlockN;  // TMEM columns of one accumulator set
+    constexpr int kTmemCols = 2 * kAccCols;                    // double buffered: 256 or 512 (powers of two)
+
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<std::uintptr_t>(smem_unaligned) + 1023) & ~std::uintptr_t(1023));
+    unsigned char* tiles = smem;
+    std::uint64_t* full_bar = reinterpret_cast<std::uint64_t*>(smem + kStages * Plan::kStageBytes);
+    std::uint64_t* empty_bar = full_bar + kStages;
+    std::uint64_t* tmem_full = empty_bar + kStages;
+    std::uint64_t* tmem_empty = tmem_full + 2;
+    std::uint32_t* tmem_ptr = reinterpret_cast<std::uint32_t*>(tmem_empty + 2);
+    volatile int* abort = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_tiles = p.n / kBlockN;
+    const int k_blocks = p.k / kBlockK;
+    const int w_rows_per_expert = kSwiGLU ? 2 * p.n : p.n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 4);
+        }
+        *abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_ptr, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const std::uint32_t tmem_base = *tmem_ptr;
+
+    if (warp == 0) {
+        // ===== TMA producer =====
+        if (lane == 0) {
+            TileCursor cursor;
+            int stage = 0;
+            unsigned phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok; tile += gridDim.x) {
+                int m_tile, n_tile;
+                if (!cursor.locate(tile, p, n_tiles, m_tile, n_tile)) break;
+                const int row0 = p.expert_offsets[cursor.expert] + m_tile * kBlockM;
+                const int wrow0 = cursor.expert * w_rows_per_expert + n_tile * kBlockN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    unsigned char* stage_base = tiles + stage * Plan::kStageBytes;
+                    mbar_expect_tx(&full_bar[stage], Plan::kStageBytes);
+                    tma_load_2d(stage_base, &map_a, kb * kBlockK, row0, &full_bar[stage]);
+                    tma_load_2d(stage_base + Plan::kTileA, &map_b, kb * kBlockK, wrow0, &full_bar[stage]);
+                    if (kSwiGLU)
+                        tma_load_2d(stage_base + Plan::kTileA + Plan::kTileB, &map_b, kb * kBlockK, wrow0 + p.n, &full_bar[stage]);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            constexpr std::uint32_t idesc = make_idesc_bf16(kBlockM, kBlockN);
+            TileCursor cursor;
+            int stage = 0;
+            unsigned phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; ok; tile += gridDim.x, ++it) {
+                int m_tile, n_tile;
+                if (!cursor.locate(tile, p, n_tiles, m_tile, n_tile)) break;
+                const int buf = it & 1;
+                const unsigned acc_phase = (it >> 1) & 1u;
+                if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1u, abort)) break;
+                tc_fence_after();
+                const std::uint32_t acc = tmem_base + buf * kAccCols;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    unsigned char* stage_base = tiles + stage * Plan::kStageBytes;
+                    const std::uint64_t desc_a = make_smem_desc(stage_base);
+                    const std::uint64_t desc_b0 = make_smem_desc(stage_base + Plan::kTileA);
+                    const std::uint64_t desc_b1 = make_smem_desc(stage_base + Plan::kTileA + Plan::kTileB);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                        // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in the address field
+                        const std::uint64_t step = static_cast<std::uint64_t>(k * kUmmaK * 2) >> 4;
+                        const std::uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+                        umma_f16(acc, desc_a + step, desc_b0 + step, idesc, accumulate);
+                        if (kSwiGLU) umma_f16(acc + kBlockN, desc_a + step, desc_b1 + step, idesc, accumulate);
+                    }
+                    umma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(&tmem_full[buf]);
+            }
+        }
+    } else {
+        // ===== epilogue: 4 warps, warp q owns TMEM lanes [32q, 32q+32) =====
+        const int q = warp & 3;
+        TileCursor cursor;
+        int it = 0;
+        for (int tile = blockIdx.x;; tile += gridDim.x, ++it) {
+            int m_tile, n_tile;
+            if (!cursor.locate(tile, p, n_tiles, m_tile, n_tile)) break;
+            const int buf = it & 1;
+            const unsigned acc_phase = (it >> 1) & 1u;
+            if (!mbar_wait(&tmem_full[buf], acc_phase, abort)) break;
+            tc_fence_after();
+            const int row = m_tile * kBlockM + q * 32 + lane;
+            const bool valid = row < p.expert_counts[cursor.expert];
+            const long long out_row = static_cast<long long>(p.expert_offsets[cursor.expert]) + row;
+            __nv_bfloat16* out = p.out + out_row * p.n + n_tile * kBlockN;
+            const std::uint32_t lane_base = tmem_base + (static_cast<std::uint32_t>(q * 32) << 16) + buf * kAccCols;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kBlockN; c0 += 32) {
+                std::uint32_t g[32];
+                tmem_ld_32x32(lane_base + c0, g);
+                float v[32];
+                if (kSwiGLU) {
+                    std::uint32_t u[32];
+                    tmem_ld_32x32(lane_base + kBlockN + c0, u);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float gate = __uint_as_float(g[i]);
+                        v[i] = gate / (1.0f + __expf(-gate)) * __uint_as_float(u[i]);
+                    }
+                } else {
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(g[i]);
+                }
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 packed;
+                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+                        *reinterpret_cast<uint4*>(out + c0 + i) = packed;
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        }
+    }
+
+    // ---- teardown: every role has left its loop (normally or through the abort latch)
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort) atomicExch(&p.status[0], 1);
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+
+namespace {
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(entry);
+    });
+    return fn;
+}
+
+// [rows, k] row-major bf16, box = 64 columns x box_rows rows, 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* base, std::uint64_t rows, std::uint64_t k, std::uint32_t box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {k, rows};
+    const cuuint64_t strides[1] = {k * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool kSwiGLU>
+cudaError_t launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GroupedGemmParams& p, int ctas, cudaStream_t stream) {
+    static bool configured[64] = {false};
+    int device = 0;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) return status;
+    constexpr int smem = SmemPlan<kSwiGLU>::kBytes;
+    if (device >= 0 && device < 64 && !configured[device]) {
+        status = cudaFuncSetAttribute(grouped_gemm_kernel<kSwiGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (status != cudaSuccess) return status;
+        configured[device] = true;
+    }
+    grouped_gemm_kernel<kSwiGLU><<<ctas, kThreads, smem, stream>>>(map_a, map_b, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+}  // namespace gemm
+
+const char* grouped_gemm_bf16(const void* a, const void* w, void* out, const int* expert_offsets, const int* expert_counts,
+                              int* status, int rows_capacity, int num_experts, int n, int k, bool swiglu,
+                              cudaStream_t stream) {
+    using namespace gemm;
+    if (n % kBlockN != 0 || k % kBlockK != 0 || n <= 0 || k <= 0) return "n must be a multiple of 128 and k a multiple of 64";
+    if (reinterpret_cast<std::uintptr_t>(a) % 16 || reinterpret_cast<std::uintptr_t>(w) % 16 ||
+        reinterpret_cast<std::uintptr_t>(out) % 16)
+        return "operands must be 16-byte aligned";
+    CUtensorMap map_a, map_b;
+    const std::uint64_t w_rows = static_cast<std::uint64_t>(num_experts) * (swiglu ? 2 : 1) * n;
+    if (!make_map(&map_a, a, static_cast<std::uint64_t>(rows_capacity), static_cast<std::uint64_t>(k), kBlockM) ||
+        !make_map(&map_b, w, w_rows, static_cast<std::uint64_t>(k), kBlockN))
+        return "cuTensorMapEncodeTiled failed";
+    GroupedGemmParams p{};
+    p.expert_offsets = expert_offsets;
+    p.expert_counts = expert_counts;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.status = status;
+    p.num_experts = num_experts;
+    p.n = n;
+    p.k = k;
+    p.rows_capacity = rows_capacity;
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+        return "cannot query the device";
+    const cudaError_t err = swiglu ? launch<true>(map_a, map_b, p, sms, stream) : launch<false>(map_a, map_b, p, sms, stream);
+    return err == cudaSuccess ? nullptr : cudaGetErrorString(err);
+}
+
+}  // namespace bep

@@ -1,0 +1,59 @@
+// Grouped expert GEMM for the expanded dispatch layout, on the 5th-generation tensor cores:
+// tcgen05.mma issued by one elected thread, operands staged in shared memory by TMA
+// (cp.async.bulk.tensor, no multicast), FP32 accumulators in tensor memory (TMEM), read back with
+// tcgen05.ld for a fused epilogue.  The reference has no expert GEMM at all (docs/pcie-ep/design.md:304
+// puts it out of scope); this is the "grouped SwiGLU expert FFN" that sits between dispatch and combine.
+//
+//   rows of expert e = A[expert_offsets[e] .. expert_offsets[e] + expert_counts[e])   (device-side ints)
+//   plain  : out[row, n]        = sum_k A[row, k] * W[e, n, k]
+//   SwiGLU : out[row, n]        = silu(sum_k A[row,k] * W[e, n, k]) * (sum_k A[row,k] * W[e, N + n, k])
+//
+// Work decomposition: persistent CTAs walk a tile list (expert, n-tile, m-tile) computed on the
+// device from the counts -- the host never reads a count.  Per CTA: warp 0 = TMA producer,
+// warp 1 = MMA issuer (and TMEM owner), warps 2..5 = epilogue.  Shared-memory stages are handed over
+// with mbarriers (TMA complete_tx -> MMA; tcgen05.commit -> producer), accumulators are double
+// buffered in TMEM (tcgen05.commit -> epilogue; epilogue arrive -> MMA).
+//
+// Every mbarrier wait is bounded: on expiry the thread latches an abort flag, all roles drain, TMEM
+// is released and the kernel returns with status[0] != 0.
+#pragma once
+
+#include <cstdint>
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace bep {
+namespace gemm {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 128;
+constexpr int kBlockK = 64;  // 64 bf16 = 128 bytes = one 128B-swizzle atom row
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;  // 6 warps
+constexpr std::uint32_t kWaitLimit = 20u * 1000u * 1000u;  // try_wait probes before giving up (seconds at most)
+
+struct GroupedGemmParams {
+    const int* expert_offsets;  // [E+1] first row of every expert in A / out
+    const int* expert_counts;   // [E]   valid rows
+    __nv_bfloat16* out;         // [rows, N]
+    int* status;                // [4]: 0 = ok, 1 = a wait expired
+    int num_experts;
+    int n;                      // output columns
+    int k;                      // reduction length
+    int rows_capacity;          // rows of A / out
+};
+
+// stages of (A tile + B tiles) that fit; SwiGLU stages carry two B tiles
+template <bool kSwiGLU>
+struct SmemPlan {
+    static constexpr int kTileA = kBlockM * kBlockK * 2;
+    static constexpr int kTileB = kBlockN * kBlockK * 2;
+    static constexpr int kStageBytes = kTileA + (kSwiGLU ? 2 : 1) * kTileB;
+    static constexpr int kStages = kSwiGLU ? 4 : 6;
+    static constexpr int kBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+}  // namespace gemm
+}  // namespace bep

@@ -73,8 +73,22 @@ cudaError_t launch_dispatch(const DispatchLaunch& launch, int channels, int thre
     return cooperative_launch(dispatch_kernel, launch, dim3(channels, launch.num_virtual, 1), threads, smem, stream);
 }
 
-cudaError_t launch_combine(const CombineLaunch& launch, int channels, int /*threads*/, cudaStream_t stream) {
-    return cooperative_launch(combine_kernel, launch, dim3(channels, launch.num_virtual, 1), kCombineWarps * 32, 0, stream);
+cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_t crow_stride, cudaStream_t stream) {
+    const std::size_t smem = static_cast<std::size_t>(kCombineWarps) * crow_stride;
+    static std::mutex mutex;
+    static std::size_t configured[64] = {0};
+    {
+        std::lock_guard<std::mutex> guard(mutex);
+        int device = 0;
+        cudaError_t status = cudaGetDevice(&device);
+        if (status != cudaSuccess) return status;
+        if (device >= 0 && device < 64 && smem > configured[device]) {
+            status = cudaFuncSetAttribute(combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (status != cudaSuccess) return status;
+            configured[device] = smem;
+        }
+    }
+    return cooperative_launch(combine_kernel, launch, dim3(channels, launch.num_virtual, 1), kCombineWarps * 32, smem, stream);
 }
 
 }  // namespace bep

@@ -23,6 +23,6 @@ int combine_resident_ctas(int threads);
 // Cooperative launches: grid = (channels, virtual ranks).
 cudaError_t launch_dispatch(const DispatchLaunch& launch, int channels, int threads, std::size_t smem,
                             cudaStream_t stream);
-cudaError_t launch_combine(const CombineLaunch& launch, int channels, int threads, cudaStream_t stream);
+cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_t crow_stride, cudaStream_t stream);
 
 }  // namespace bep

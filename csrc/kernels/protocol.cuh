@@ -247,6 +247,7 @@ struct CombineArgs {
     __nv_bfloat16* out;           // [T, H]
     int* error;                   // [8]
     std::int64_t* stats;          // [8]
+    std::int64_t* profile;        // [C][8]: start, guard done, warp 0 expert side done, warp 0 source side done, end
 };
 
 struct CombineLaunch {

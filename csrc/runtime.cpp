@@ -2,6 +2,7 @@
 #include <torch/extension.h>
 
 #include "buffers/runtime.hpp"
+#include "kernels/expert_gemm.hpp"
 
 namespace py = pybind11;
 using namespace bep;
@@ -143,6 +144,37 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("expanded_capacity", &Runtime::expanded_capacity)
         .def("segment_layout", [](const Runtime& r) { return layout_to_dict(r.layout()); })
         .def("close", &Runtime::close);
+
+    // out[rows of expert e] = a[rows of expert e] @ w[e].T (+ SwiGLU epilogue): tcgen05 grouped GEMM
+    m.def("grouped_gemm", [](const at::Tensor& a, const at::Tensor& w, at::Tensor& out, const at::Tensor& expert_offsets,
+                             const at::Tensor& expert_counts, at::Tensor& status, bool swiglu, std::int64_t stream) {
+        auto check = [](bool ok, const char* what) {
+            if (!ok) throw std::invalid_argument(what);
+        };
+        check(a.is_cuda() && w.is_cuda() && out.is_cuda() && expert_offsets.is_cuda() && expert_counts.is_cuda() && status.is_cuda(),
+              "all tensors must be CUDA tensors");
+        check(a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16,
+              "a, w and out must be bfloat16");
+        check(a.dim() == 2 && w.dim() == 3 && out.dim() == 2 && a.is_contiguous() && w.is_contiguous() && out.is_contiguous(),
+              "a [rows,k], w [experts,n(,x2),k], out [rows,n] must be contiguous");
+        const int experts = static_cast<int>(w.size(0));
+        const int k = static_cast<int>(a.size(1));
+        const int n = static_cast<int>(out.size(1));
+        check(w.size(2) == k && w.size(1) == (swiglu ? 2 : 1) * n && out.size(0) == a.size(0), "shape mismatch between a, w and out");
+        check(expert_offsets.scalar_type() == at::kInt && expert_counts.scalar_type() == at::kInt &&
+                  expert_offsets.numel() >= experts + 1 && expert_counts.numel() >= experts &&
+                  expert_offsets.is_contiguous() && expert_counts.is_contiguous(),
+              "expert_offsets [experts+1] and expert_counts [experts] must be contiguous int32");
+        check(status.scalar_type() == at::kInt && status.numel() >= 4, "status must be int32 [4]");
+        c10::cuda::CUDAGuard guard(a.device());
+        cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
+                                                 : at::cuda::getCurrentCUDAStream(a.get_device()).stream();
+        const char* error = grouped_gemm_bf16(a.data_ptr(), w.data_ptr(), out.data_ptr(), expert_offsets.data_ptr<int>(),
+                                              expert_counts.data_ptr<int>(), status.data_ptr<int>(),
+                                              static_cast<int>(a.size(0)), experts, n, k, swiglu, launch_stream);
+        if (error != nullptr) throw std::runtime_error(std::string("grouped_gemm: ") + error);
+    }, py::arg("a"), py::arg("w"), py::arg("out"), py::arg("expert_offsets"), py::arg("expert_counts"), py::arg("status"),
+       py::arg("swiglu"), py::arg("stream") = 0);
 
     m.def("dispatch_group", &dispatch_group);
     m.def("combine_group", &combine_group);

@@ -29,3 +29,7 @@ def test_cpu_transport_correctness(world):
 def test_cpu_transport_oracle_config_world2():
     """world_size=2, T=64, hidden=128, fp32, 8 experts, top-2."""
     run_workers(2, "--transport", "cpu", "--suite", "oracle_config", "--fp32")
+
+
+def test_cpu_moe_layer_world2():
+    run_workers(2, "--transport", "cpu", "--suite", "moe_layer", "--hidden", "64")

@@ -38,3 +38,13 @@ def test_host_staged_transport_world2():
 def test_oracle_config_on_gpus():
     _need(2)
     run_workers(2, "--transport", "peer", "--suite", "oracle_config")
+
+
+def test_moe_layer_single_gpu():
+    run_workers(1, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256")
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_moe_layer_multi_gpu(world):
+    _need(world)
+    run_workers(world, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256")

@@ -138,7 +138,34 @@ def suite_oracle_config(args, rank, world, device):
     return 2
 
 
-SUITES = {"correctness": suite_correctness, "oracle_config": suite_oracle_config}
+def suite_moe_layer(args, rank, world, device):
+    """Full MoE layer (router -> dispatch -> grouped SwiGLU FFN -> combine) against a dense FP32 evaluation."""
+    from pcie_ep_b200.models.moe_layer import MoELayer, dense_moe_reference
+
+    experts, topk, hidden, inter, tmax = 4 * world, 2, args.hidden, 128, 96
+    config = HostStagedConfig(channels=args.channels, transport=args.transport, timeout_ms=args.timeout_ms,
+                              tx_warps=2, rx_warps=3)
+    on_gpu = args.transport != "cpu"
+    with HostStagedEPBuffer(dist.group.WORLD, tmax, hidden, topk, experts, config) as buffer:
+        layer = MoELayer(buffer, inter, seed=5)
+        for step, tokens in enumerate([tmax, 7 + rank, tmax - rank]):
+            g = torch.Generator().manual_seed(100 * step + rank)
+            x = torch.randn(tokens, hidden, generator=g).to(layer.dtype)
+            xd = x.to(device)
+            idx, w = layer.route(xd)
+            y = layer(xd, idx, w)
+            layer.check_errors()
+            want = dense_moe_reference(x, idx.cpu(), w.cpu(), 5, hidden, inter,
+                                       weight_dtype=torch.bfloat16 if on_gpu else torch.float32)
+            got = y.detach().cpu().float()
+            tol = 3e-2 if on_gpu else 1e-4
+            ok = got.shape == want.shape and torch.allclose(got, want, rtol=tol, atol=tol * max(1.0, float(want.abs().max())))
+            worst = float((got - want).abs().max()) if got.shape == want.shape and got.numel() else 0.0
+            agree(None if ok else f"rank {rank} step {step}: max abs err {worst}", "moe layer")
+    return 3
+
+
+SUITES = {"correctness": suite_correctness, "oracle_config": suite_oracle_config, "moe_layer": suite_moe_layer}
 
 
 def main():
