@@ -386,8 +386,33 @@ def run_reference(args, rank, world, local_rank):
         }), flush=True)
 
 
+def reexec_reference_with_system_libstdcxx():
+    """The reference's extension uses std::ifstream.  In this image an extension built by
+    torch.utils.cpp_extension does not record libstdc++ as a dependency, its iostream symbols then bind
+    to copies inside other loaded libraries and the first ifstream use segfaults.  Preloading the
+    system libstdc++ fixes the binding without touching the reference, so the reference arm runs in a
+    child process started with LD_PRELOAD (every rank starts its own child; RANK/WORLD_SIZE/MASTER_* are
+    inherited)."""
+    import glob
+
+    if os.environ.get("BENCH_REFERENCE_CHILD") == "1":
+        return False
+    candidates = sorted(glob.glob("/usr/lib/x86_64-linux-gnu/libstdc++.so.6") + glob.glob("/usr/lib64/libstdc++.so.6"))
+    if not candidates:
+        return False
+    env = dict(os.environ)
+    env["BENCH_REFERENCE_CHILD"] = "1"
+    env["LD_PRELOAD"] = candidates[0] + (":" + env["LD_PRELOAD"] if env.get("LD_PRELOAD") else "")
+    proc = subprocess.run([sys.executable, os.path.abspath(__file__), *sys.argv[1:]], env=env)
+    if proc.returncode != 0 and int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": f"reference process exited with code {proc.returncode}"}), flush=True)
+    return True
+
+
 def main():
     args = parse_args()
+    if args.impl == "reference" and reexec_reference_with_system_libstdcxx():
+        return
     rank, world, local_rank = init_distributed(args)
     import torch.distributed as dist
 
