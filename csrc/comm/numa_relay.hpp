@@ -1,0 +1,269 @@
+// CPU relay of the host-staged transport (numa_mode = "relay").
+//
+// Direct host-staged mode lets a GPU store straight into the destination's host segment, wherever
+// that memory lives.  In relay mode a GPU only ever touches host memory placed next to itself: rank r
+// writes what it would send to rank d into an *outbox* O(r->d) of its own (same layout as a segment),
+// and CPU threads of rank r's process forward it into d's real segment S(d), then publish the same
+// flags there.  The GPU kernels are unchanged -- only the pointer table differs -- and the hand-off
+// between GPU and CPU uses the very flags of the protocol: the GPU's st.release.sys is the CPU's
+// acquire load, the CPU's release store is the destination GPU's ld.acquire.sys.
+//
+// This is the counterpart of the reference's NumaRelay (csrc/comm/numa_relay.hpp:59-366 there:
+// pinned worker threads that copy payload + metadata into NUMA-local replica rings and republish
+// descriptors), re-expressed for the push protocol: a worker follows one or more flows (r->d) and
+// per flow forwards, in this order, the abort flag, the counts message, staged rows channel by
+// channel as their READY flags appear, the done/cdone hand-backs and the combine rows.
+//
+// Failure codes (reported through diagnostics() and, where possible, as the rank's abort flag):
+//   101 a flow's READY sequence went backwards, 102 counts announce more rows than a ring holds,
+//   199 the relay was stopped while rows were still pending.
+#pragma once
+
+#include <atomic>
+#include <chrono>
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include <pthread.h>
+#include <sched.h>
+
+#include <pybind11/pybind11.h>
+
+#include "../kernels/protocol.cuh"
+
+namespace bep {
+
+namespace py = pybind11;
+
+class NumaRelay {
+   public:
+    // options: num_ranks, channels, num_experts, num_topk, hidden, num_max_tokens, payload_slots,
+    //          enable_combine, workers, cpu_affinity (list of allowed CPUs, may be empty)
+    // outboxes[d] / targets[d]: host addresses of O(rank->d) and S(d); entries for d == rank are ignored.
+    NumaRelay(const py::dict& options, const std::vector<std::int64_t>& outboxes, const std::vector<std::int64_t>& targets,
+              int rank)
+        : rank_(rank) {
+        const int P = options["num_ranks"].cast<int>();
+        lay_ = make_segment_layout(P, options["channels"].cast<int>(), options["num_experts"].cast<int>(),
+                                   options["num_topk"].cast<int>(), options["hidden"].cast<int>(),
+                                   options["num_max_tokens"].cast<int>(), options["payload_slots"].cast<int>(),
+                                   options["enable_combine"].cast<bool>());
+        if (lay_.slots != lay_.slots_full) throw std::invalid_argument("relay mode needs full-size rings (payload_slots = 0)");
+        if (static_cast<int>(outboxes.size()) != P || static_cast<int>(targets.size()) != P)
+            throw std::invalid_argument("one outbox and one target per rank");
+        workers_ = std::max(1, options.contains("workers") ? options["workers"].cast<int>() : 1);
+        if (options.contains("cpu_affinity"))
+            for (auto cpu : options["cpu_affinity"].cast<std::vector<int>>()) affinity_.push_back(cpu);
+        for (int d = 0; d < P; ++d) {
+            if (d == rank) continue;
+            auto flow = std::make_unique<Flow>();
+            flow->dest = d;
+            flow->outbox = reinterpret_cast<std::uint8_t*>(outboxes[d]);
+            flow->target = reinterpret_cast<std::uint8_t*>(targets[d]);
+            flow->forwarded.assign(lay_.num_channels, 0);
+            flow->expected.assign(lay_.num_channels, 0);
+            flow->combine_epoch.assign(lay_.has_combine ? lay_.num_max_tokens : 0, 0);
+            flows_.push_back(std::move(flow));
+        }
+    }
+
+    ~NumaRelay() { stop(); }
+
+    void start() {
+        if (running_) return;
+        stopping_.store(false);
+        running_ = true;
+        const int count = std::min<int>(workers_, std::max<std::size_t>(1, flows_.size()));
+        for (int w = 0; w < count; ++w) threads_.emplace_back([this, w, count] { run(w, count); });
+    }
+
+    void stop() {
+        if (!running_) return;
+        stopping_.store(true);
+        for (auto& t : threads_) t.join();
+        threads_.clear();
+        running_ = false;
+        for (auto& flow : flows_)
+            if (flow->rows_pending() && flow->failure == 0) flow->failure = 199;
+    }
+
+    void set_delay_ns(std::uint64_t ns) { delay_ns_.store(ns); }
+
+    py::dict diagnostics() const {
+        py::dict d;
+        py::list flows;
+        for (const auto& flow : flows_) {
+            py::dict f;
+            f["dest"] = flow->dest;
+            f["rows_copied"] = flow->rows_copied.load();
+            f["bytes_copied"] = flow->bytes_copied.load();
+            f["counts_epoch"] = flow->counts_epoch.load();
+            f["combine_rows_copied"] = flow->combine_rows.load();
+            f["failure"] = flow->failure.load();
+            f["worker_cpu"] = flow->worker_cpu.load();
+            flows.append(f);
+        }
+        d["flows"] = flows;
+        d["workers"] = static_cast<int>(threads_.size());
+        d["running"] = running_;
+        return d;
+    }
+
+   private:
+    struct Flow {
+        int dest = 0;
+        std::uint8_t* outbox = nullptr;
+        std::uint8_t* target = nullptr;
+        std::vector<int> forwarded, expected;      // per channel, for the current counts epoch
+        std::vector<std::uint64_t> combine_epoch;  // per token: last combine epoch forwarded
+        std::uint64_t last_done = 0, last_cdone = 0, last_abort = 0;
+        std::atomic<std::uint64_t> counts_epoch{0}, rows_copied{0}, bytes_copied{0}, combine_rows{0};
+        std::atomic<int> failure{0}, worker_cpu{-1};
+        bool rows_pending() const {
+            for (std::size_t c = 0; c < forwarded.size(); ++c)
+                if (forwarded[c] < expected[c]) return true;
+            return false;
+        }
+    };
+
+    static std::uint64_t load_acquire(const std::uint8_t* p) {
+        return __atomic_load_n(reinterpret_cast<const std::uint64_t*>(p), __ATOMIC_ACQUIRE);
+    }
+    static void store_release(std::uint8_t* p, std::uint64_t v) {
+        __atomic_store_n(reinterpret_cast<std::uint64_t*>(p), v, __ATOMIC_RELEASE);
+    }
+
+    void pin(int worker) {
+        if (affinity_.empty()) return;
+        cpu_set_t set;
+        CPU_ZERO(&set);
+        CPU_SET(affinity_[worker % affinity_.size()], &set);
+        pthread_setaffinity_np(pthread_self(), sizeof(set), &set);  // best effort
+    }
+
+    void run(int worker, int count) {
+        pin(worker);
+        const int cpu = sched_getcpu();
+        unsigned idle = 0;
+        while (!stopping_.load(std::memory_order_relaxed)) {
+            bool progressed = false;
+            for (std::size_t i = worker; i < flows_.size(); i += count) {
+                flows_[i]->worker_cpu.store(cpu);
+                progressed |= progress(*flows_[i]);
+            }
+            if (progressed) {
+                idle = 0;
+            } else if (++idle > 2000) {
+                std::this_thread::sleep_for(std::chrono::microseconds(20));
+            }
+        }
+    }
+
+    // One pass over one flow; true if anything moved.
+    bool progress(Flow& f) {
+        if (f.failure.load() != 0) return false;
+        bool moved = false;
+        const int me = rank_;
+        const std::size_t flag = static_cast<std::size_t>(me) * kFlagStride;
+        // 1. abort
+        const std::uint64_t abort_value = load_acquire(f.outbox + lay_.abort_off + flag);
+        if (abort_value != f.last_abort) {
+            store_release(f.target + lay_.abort_off + flag, abort_value);
+            f.last_abort = abort_value;
+            moved = true;
+        }
+        // 2. counts message of a new epoch
+        const std::uint64_t epoch = load_acquire(f.outbox + lay_.counts_flag_off + flag);
+        if (epoch > f.counts_epoch.load()) {
+            const std::size_t bytes = static_cast<std::size_t>(lay_.counts_stride) * 4;
+            const std::size_t at = lay_.counts_off + static_cast<std::size_t>(me) * bytes;
+            std::memcpy(f.target + at, f.outbox + at, bytes);
+            const int* message = reinterpret_cast<const int*>(f.outbox + at);
+            const int* chan = message + lay_.num_ranks + lay_.num_local_experts;
+            for (int c = 0; c < lay_.num_channels; ++c) {
+                if (chan[c] > lay_.slots) {
+                    f.failure.store(102);
+                    return true;
+                }
+                f.expected[c] = chan[c];
+                f.forwarded[c] = 0;
+            }
+            store_release(f.target + lay_.counts_flag_off + flag, epoch);
+            f.counts_epoch.store(epoch);
+            moved = true;
+        }
+        // 3. staged rows, in channel order, as far as their READY flags have appeared
+        const std::uint64_t current = f.counts_epoch.load();
+        if (current != 0) {
+            const std::uint64_t delay = delay_ns_.load(std::memory_order_relaxed);
+            for (int c = 0; c < lay_.num_channels; ++c) {
+                while (f.forwarded[c] < f.expected[c]) {
+                    const int j = f.forwarded[c];
+                    const std::size_t ring = (static_cast<std::size_t>(me) * lay_.num_channels + c) * lay_.slots + j;
+                    const std::uint64_t want = make_seq(current, static_cast<std::uint32_t>(j + 1));
+                    const std::uint64_t seen = load_acquire(f.outbox + lay_.ready_off + ring * 8);
+                    if (seen != want) {
+                        if ((seen >> 32) > current) f.failure.store(101);
+                        break;
+                    }
+                    if (delay) std::this_thread::sleep_for(std::chrono::nanoseconds(delay));
+                    const std::size_t row = lay_.stage_off + ring * lay_.row_stride;
+                    const std::size_t bytes = static_cast<std::size_t>(lay_.meta_off) + lay_.meta_bytes;
+                    std::memcpy(f.target + row, f.outbox + row, bytes);
+                    store_release(f.target + lay_.ready_off + ring * 8, want);
+                    ++f.forwarded[c];
+                    f.rows_copied.fetch_add(1, std::memory_order_relaxed);
+                    f.bytes_copied.fetch_add(bytes, std::memory_order_relaxed);
+                    moved = true;
+                }
+            }
+        }
+        // 4. hand-backs
+        const std::uint64_t done = load_acquire(f.outbox + lay_.done_off + flag);
+        if (done != f.last_done) {
+            store_release(f.target + lay_.done_off + flag, done);
+            f.last_done = done;
+            moved = true;
+        }
+        if (lay_.has_combine) {
+            const std::uint64_t cdone = load_acquire(f.outbox + lay_.cdone_off + flag);
+            if (cdone != f.last_cdone) {
+                store_release(f.target + lay_.cdone_off + flag, cdone);
+                f.last_cdone = cdone;
+                moved = true;
+            }
+            // 5. combine rows: one flag per (this rank, token)
+            const std::size_t flags = lay_.cready_off + static_cast<std::size_t>(me) * lay_.num_max_tokens * 8;
+            const std::size_t rows = lay_.cstage_off + static_cast<std::size_t>(me) * lay_.num_max_tokens * lay_.crow_stride;
+            for (int t = 0; t < lay_.num_max_tokens; ++t) {
+                const std::uint64_t e = load_acquire(f.outbox + flags + static_cast<std::size_t>(t) * 8);
+                if (e > f.combine_epoch[t]) {
+                    const std::size_t at = rows + static_cast<std::size_t>(t) * lay_.crow_stride;
+                    std::memcpy(f.target + at, f.outbox + at, static_cast<std::size_t>(lay_.hidden) * 2);
+                    store_release(f.target + flags + static_cast<std::size_t>(t) * 8, e);
+                    f.combine_epoch[t] = e;
+                    f.combine_rows.fetch_add(1, std::memory_order_relaxed);
+                    moved = true;
+                }
+            }
+        }
+        return moved;
+    }
+
+    int rank_;
+    SegmentLayout lay_{};
+    int workers_ = 1;
+    std::vector<int> affinity_;
+    std::vector<std::unique_ptr<Flow>> flows_;
+    std::vector<std::thread> threads_;
+    std::atomic<bool> stopping_{false};
+    std::atomic<std::uint64_t> delay_ns_{0};
+    bool running_ = false;
+};
+
+}  // namespace bep

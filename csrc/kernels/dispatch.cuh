@@ -752,6 +752,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         // ===== receive + expand =====
         const int w = warp - 1 - tx_warps;
         const bool delayed = (w == rx_warps - 1);
+        // The control warp owns the diagnosis of a missing counts message (it knows which source is
+        // late); this wait only has to end, so its own deadline is a quarter of the timeout later.
+        health.deadline += rc->timeout_ns / 4;
         while (*reinterpret_cast<volatile int*>(&sh->prefix_ready) == 0) {
             if (warp_give_up(health, kErrCountsWait, -1, 0)) break;
         }

@@ -2,6 +2,7 @@
 #include <torch/extension.h>
 
 #include "buffers/runtime.hpp"
+#include "comm/numa_relay.hpp"
 #include "kernels/expert_gemm.hpp"
 
 namespace py = pybind11;
@@ -101,6 +102,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("host_pointer", &HostSegment::host_pointer)
         .def("device_pointer", &HostSegment::device_pointer)
         .def("close", &HostSegment::close);
+
+    py::class_<NumaRelay, std::shared_ptr<NumaRelay>>(m, "NumaRelay")
+        .def(py::init<const py::dict&, const std::vector<std::int64_t>&, const std::vector<std::int64_t>&, int>())
+        .def("start", &NumaRelay::start)
+        .def("stop", &NumaRelay::stop, py::call_guard<py::gil_scoped_release>())
+        .def("diagnostics", &NumaRelay::diagnostics)
+        .def("set_delay_ns", &NumaRelay::set_delay_ns);
 
     py::class_<Layout, std::shared_ptr<Layout>>(m, "_Layout")
         .def_readonly("num_tokens", &Layout::num_tokens)

@@ -126,6 +126,7 @@ _module = _load()
 
 Runtime = _module.Runtime
 HostSegment = _module.HostSegment
+NumaRelay = _module.NumaRelay
 segment_layout = _module.segment_layout
 allocate_device_segment = _module.allocate_device_segment
 export_device_segment = _module.export_device_segment

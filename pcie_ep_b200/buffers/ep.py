@@ -148,7 +148,7 @@ class HostStagedEPBuffer:
         )
         self.segments = open_segments(
             _C, chosen, self.rank_idx, self.num_ranks, int(layout["size_bytes"]), self.device, self.control_group,
-            self.config.directory,
+            self.config.directory, relay=self.config.numa_mode == "relay",
         )
         self.directory = self.segments.directory
 
@@ -162,6 +162,21 @@ class HostStagedEPBuffer:
             return runtime
 
         self.runtime = control.run_agreed(make_runtime, self.control_group, "runtime construction", self.rank_idx)
+
+        if self.config.numa_mode == "relay":
+            def make_relay() -> Any:
+                relay_options = {
+                    "num_ranks": self.num_ranks, "channels": self.config.channels, "num_experts": num_experts,
+                    "num_topk": num_topk, "hidden": hidden, "num_max_tokens": num_max_tokens_per_rank,
+                    "payload_slots": self.config.payload_slots, "enable_combine": self.config.enable_combine,
+                    "workers": self.config.relay_workers_per_numa, "cpu_affinity": list(self.config.relay_cpu_affinity),
+                }
+                relay = _C.NumaRelay(relay_options, self.segments.outbox_host_pointers, self.segments.host_pointers,
+                                     self.rank_idx)
+                relay.start()
+                return relay
+
+            self.relay = control.run_agreed(make_relay, self.control_group, "relay start", self.rank_idx)
 
     # ------------------------------------------------------------------ streams
     def get_comm_stream(self) -> Any:

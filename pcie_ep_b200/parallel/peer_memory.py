@@ -41,6 +41,9 @@ class Segments:
         self._own_ptr = 0
         self._imported: List[int] = []
         self._host: List[Any] = []
+        self.host_pointers: List[int] = [0] * num_ranks      # host addresses of every rank's real segment
+        self.outbox_host_pointers: List[int] = [0] * num_ranks  # relay mode: host addresses of this rank's outboxes
+        self.relay = False
         self._closed = False
 
     def close(self, control_group: Any, extension: Any) -> None:
@@ -81,9 +84,18 @@ def open_segments(
     device: int,
     control_group: Any,
     directory: Optional[str] = None,
+    relay: bool = False,
 ) -> Segments:
-    """Collective: allocate, exchange and map the segments of every rank."""
+    """Collective: allocate, exchange and map the segments of every rank.
+
+    With ``relay`` (host-staged only) every rank additionally owns one *outbox* per peer, laid out like
+    a segment; its GPU writes there instead of into the peer's segment and CPU threads forward the
+    contents (``csrc/comm/numa_relay.hpp``).  The pointer table then holds the outboxes for the peers.
+    """
     segments = Segments(transport, rank, num_ranks, size_bytes, device)
+    segments.relay = relay
+    if relay and transport != "host_staged":
+        raise ValueError("relay needs the host_staged transport")
     if transport == "peer":
         def allocate() -> bytes:
             segments._own_ptr = extension.allocate_device_segment(size_bytes, device)
@@ -106,16 +118,26 @@ def open_segments(
         segments.directory, _ = control.create_shared_directory(rank, control_group, directory)
         paths = [os.path.join(segments.directory, f"source-{peer}") for peer in range(num_ranks)]
 
+        outbox_paths = [os.path.join(segments.directory, f"relay-{rank}-{peer}") for peer in range(num_ranks)]
+
         def create() -> None:
             if rank == 0:
                 for path in paths:
                     extension.create_host_segment(path, size_bytes)
+            if relay:
+                for peer, path in enumerate(outbox_paths):
+                    if peer != rank:
+                        extension.create_host_segment(path, size_bytes)
 
         control.run_agreed(create, control_group, "segment creation", rank)
 
         def first_touch() -> None:
             node = extension.get_device_numa_node(device)
             segments.numa_bound = extension.first_touch_host_segment(paths[rank], size_bytes, node)
+            if relay:
+                for peer, path in enumerate(outbox_paths):
+                    if peer != rank:
+                        extension.first_touch_host_segment(path, size_bytes, node)
 
         # every owner places and touches its pages before anybody registers them
         # (reference: pcie_ep/comm.py:145-182)
@@ -126,6 +148,15 @@ def open_segments(
                 seg = extension.HostSegment(path, size_bytes, device)
                 segments._host.append(seg)
                 segments.pointers[peer] = seg.device_pointer()
+                segments.host_pointers[peer] = seg.host_pointer()
+            if relay:
+                for peer, path in enumerate(outbox_paths):
+                    if peer == rank:
+                        continue
+                    box = extension.HostSegment(path, size_bytes, device)
+                    segments._host.append(box)
+                    segments.pointers[peer] = box.device_pointer()  # the GPU writes to its own outbox
+                    segments.outbox_host_pointers[peer] = box.host_pointer()
 
         control.run_agreed(register, control_group, "host registration", rank)
     else:

@@ -48,3 +48,9 @@ def test_moe_layer_single_gpu():
 def test_moe_layer_multi_gpu(world):
     _need(world)
     run_workers(world, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256")
+
+
+def test_host_staged_relay_world2():
+    """GPU -> own outbox -> CPU relay threads -> destination segment -> destination GPU."""
+    _need(2)
+    run_workers(2, "--transport", "host_staged", "--numa-mode", "relay", "--suite", "correctness", "--hidden", "256")

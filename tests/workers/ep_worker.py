@@ -99,9 +99,11 @@ def suite_correctness(args, rank, world, device):
     experts, topk, hidden, tmax = 8 * world if args.small else 32 * world // max(1, world // 8), 4, args.hidden, 48
     experts = max(experts, world * 2)
     dims = (experts, topk, hidden, tmax)
+    relay = args.numa_mode == "relay"
     config = HostStagedConfig(channels=args.channels, timeout_ms=args.timeout_ms, transport=args.transport,
                               tx_warps=2, rx_warps=3, payload_slots=args.payload_slots,
-                              descriptor_slots=args.payload_slots)
+                              descriptor_slots=args.payload_slots, stage=8 if relay else 6, numa_mode=args.numa_mode,
+                              relay_workers_per_numa=2 if relay else 1)
     with HostStagedEPBuffer(dist.group.WORLD, tmax, hidden, topk, experts, config) as buffer:
         cases = [dict(pattern=p, tokens=17, expand=e, alignment=1)
                  for p in ["random", "local", "multicast", "hotspot", "partial", "none"] for e in (False, True)]
@@ -111,6 +113,12 @@ def suite_correctness(args, rank, world, device):
         cases.append(dict(pattern="multicast", tokens=5, expand=True, alignment=1, weights=False))
         for case in cases:
             run_case(buffer, args, rank, world, device, case, dims)
+        if relay and world > 1:
+            flows = buffer.relay.diagnostics()["flows"]
+            failure = None
+            if len(flows) != world - 1 or any(f["failure"] for f in flows) or not any(f["rows_copied"] for f in flows):
+                failure = f"rank {rank}: relay diagnostics {flows}"
+            agree(failure, "relay")
     return len(cases)
 
 
@@ -176,6 +184,7 @@ def main():
     parser.add_argument("--channels", type=int, default=4)
     parser.add_argument("--payload-slots", type=int, default=0)
     parser.add_argument("--timeout-ms", type=int, default=5000)
+    parser.add_argument("--numa-mode", default="direct")
     parser.add_argument("--small", action="store_true")
     parser.add_argument("--fp32", action="store_true")
     args = parser.parse_args()
