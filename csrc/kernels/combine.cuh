@@ -142,9 +142,14 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
         const std::size_t rank_stride = static_cast<std::size_t>(Tmax) * lay.crow_stride;
         // expert-side cursor.  Sources are visited in a rank-rotated order: at any moment every rank
         // pushes to a different peer instead of all ranks converging on source 0, then source 1, ...
-        int step = 0, j = 0, item = 0;
-        int s = (me + 1) % P;
-        int n_s = a.recv_chan_counts[s * C + c];
+        // expert-side cursor: rows are taken round-robin over the sources (row jj of every source in
+        // turn, starting with rank me+1), so a rank sprays all its peers at once like dispatch does and
+        // no destination is the target of every rank at the same time.
+        int step = 0, jj = 0, item = 0, s = 0;
+        const int my_count = lane < static_cast<unsigned>(P) ? a.recv_chan_counts[lane * C + c] : 0;
+        int max_count = my_count;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) max_count = max(max_count, __shfl_xor_sync(full, max_count, o));
         int t = t0 + w;  // source-side cursor
         // A pushed row travels as one bulk copy from this warp's shared-memory buffer.  Its flag is
         // released one row late: after the next row's copy has been issued and the older bulk group has
@@ -161,20 +166,22 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
             bool coherent_side = false;
             // ---- next expert-side item of this warp
             bool have = false;
-            while (step < P && !have) {
-                while (j < n_s && item % num_warps != w) {
-                    ++j;
-                    ++item;
+            int j = 0;
+            while (jj < max_count && !have) {
+                if (step >= P) {
+                    step = 0;
+                    ++jj;
+                    continue;
                 }
-                if (j < n_s) {
-                    have = true;
-                } else {
-                    ++step;
-                    j = 0;
-                    if (step < P) {
-                        s = (me + 1 + step) % P;
-                        n_s = a.recv_chan_counts[s * C + c];
+                s = (me + 1 + step) % P;
+                const int n_s = __shfl_sync(full, my_count, s);
+                ++step;
+                if (jj < n_s) {
+                    if (item % num_warps == w) {
+                        have = true;
+                        j = jj;
                     }
+                    ++item;
                 }
             }
             if (have) {
@@ -190,8 +197,6 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                 dst = rc->seg[s] + lay.cstage_off + static_cast<std::size_t>(me) * rank_stride +
                       static_cast<std::size_t>(token) * lay.crow_stride;
                 flag = reinterpret_cast<std::uint64_t*>(rc->seg[s] + lay.cready_off) + static_cast<std::size_t>(me) * Tmax + token;
-                ++j;
-                ++item;
                 if (lane == 0) {
                     ++st_rows;
                     if (s != me) ++st_remote;
