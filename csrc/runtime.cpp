@@ -4,6 +4,7 @@
 #include "buffers/runtime.hpp"
 #include "comm/numa_relay.hpp"
 #include "kernels/expert_gemm.hpp"
+#include "kernels/litmus.hpp"
 
 namespace py = pybind11;
 using namespace bep;
@@ -183,6 +184,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         if (error != nullptr) throw std::runtime_error(std::string("grouped_gemm: ") + error);
     }, py::arg("a"), py::arg("w"), py::arg("out"), py::arg("expert_offsets"), py::arg("expert_counts"), py::arg("status"),
        py::arg("swiglu"), py::arg("stream") = 0);
+
+    m.def("litmus", [](std::int64_t mine, std::int64_t theirs, int role, int rounds, int words, at::Tensor& status,
+                       int timeout_ms, int device) {
+        if (!status.is_cuda() || status.scalar_type() != at::kLong || status.numel() < (role < 0 ? 8 : 4))
+            throw std::invalid_argument("status must be a CUDA int64 tensor with 4 (8 for both roles) elements");
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+        const char* error = litmus_pingpong(reinterpret_cast<void*>(mine), reinterpret_cast<void*>(theirs), role, rounds, words,
+                                            reinterpret_cast<long long*>(status.data_ptr<std::int64_t>()),
+                                            static_cast<unsigned long long>(timeout_ms) * 1000000ull,
+                                            at::cuda::getCurrentCUDAStream(device).stream());
+        if (error != nullptr) throw std::runtime_error(std::string("litmus: ") + error);
+    });
 
     m.def("dispatch_group", &dispatch_group);
     m.def("combine_group", &combine_group);

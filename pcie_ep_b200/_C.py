@@ -33,6 +33,7 @@ SOURCES: List[Path] = [
     _CSRC / "kernels" / "launch.cu",
     _CSRC / "kernels" / "expert_gemm.cu",
     _CSRC / "kernels" / "layout_static.cu",
+    _CSRC / "kernels" / "litmus.cu",
 ]
 
 CUDA_FLAGS = [

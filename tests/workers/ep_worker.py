@@ -173,7 +173,34 @@ def suite_moe_layer(args, rank, world, device):
     return 3
 
 
-SUITES = {"correctness": suite_correctness, "oracle_config": suite_oracle_config, "moe_layer": suite_moe_layer}
+def suite_litmus(args, rank, world, device):
+    """Two processes, two GPUs: READY/ACK ping-pong over NVLink-mapped HBM with bounded waits."""
+    from pcie_ep_b200 import _C
+
+    assert world == 2, "the litmus has exactly two sides"
+    size, rounds, words = 1 << 20, 20000, 1024
+    own = _C.allocate_device_segment(size, device.index)
+    handles = gather(_C.export_device_segment(own))
+    peer = _C.import_device_segment(handles[1 - rank], device.index)
+    status = torch.zeros(4, dtype=torch.int64, device=device)
+    dist.barrier()
+    _C.litmus(own, peer, rank, rounds, words, status, 5000, device.index)
+    torch.cuda.synchronize()
+    timed_out, mismatches, done, elapsed = status.cpu().tolist()
+    failure = None
+    if timed_out or mismatches or done != rounds:
+        failure = f"rank {rank}: timed_out={timed_out} mismatches={mismatches} rounds={done}/{rounds}"
+    agree(failure, "litmus")
+    if rank == 0:
+        print(f"litmus: {rounds} rounds, {elapsed / rounds / 1000:.2f} us per READY/ACK round trip with {words * 8} payload bytes", flush=True)
+    dist.barrier()
+    _C.release_imported_segment(peer)
+    dist.barrier()
+    _C.free_device_segment(own)
+    return 1
+
+
+SUITES = {"litmus": suite_litmus, "correctness": suite_correctness, "oracle_config": suite_oracle_config, "moe_layer": suite_moe_layer}
 
 
 def main():
