@@ -86,56 +86,89 @@ def make_routes(tokens, experts, topk, rank, seed=20261024):
 
 
 class ClockSampler:
-    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    """SM clock and throttle reasons sampled every few milliseconds by a thread while the GPU works.
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    Read-only NVML queries (no setting is changed).  Falls back to one nvidia-smi query per sample when
+    the NVML binding is missing."""
+
+    REASONS = {
+        "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40, "sw_power_cap": 0x4,
+        "hw_power_brake_slowdown": 0x80,
+    }
 
     def __init__(self, device_index):
+        import threading
+
         self.device_index = device_index
-        self.proc = None
-        self.path = None
+        self.samples, self.max_clock, self.reasons = [], None, set()
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+        self._handle = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = device_index
+            if visible:
+                entries = [v.strip() for v in visible.split(",") if v.strip()]
+                if device_index < len(entries) and entries[device_index].isdigit():
+                    physical = int(entries[device_index])
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_clock = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+        except Exception:  # noqa: BLE001 - NVML binding unavailable: nvidia-smi fallback
+            self._nvml = None
+
+    def _sample_nvml(self):
+        nv = self._nvml
+        self.samples.append(float(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)))
+        try:
+            mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+        except Exception:  # noqa: BLE001 - older binding name
+            mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+        for name, bit in self.REASONS.items():
+            if mask & bit:
+                self.reasons.add(name)
+
+    def _sample_smi(self):
+        query = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        out = subprocess.run(["nvidia-smi", f"--query-gpu={query}", "--format=csv,noheader,nounits", "-i",
+                              str(self.device_index)], capture_output=True, text=True, timeout=10).stdout
+        f = [v.strip() for v in out.strip().split(",")]
+        if len(f) >= 6:
+            self.samples.append(float(f[0]))
+            self.max_clock = float(f[1])
+            for name, value in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], f[2:6]):
+                if value.lower().startswith("active"):
+                    self.reasons.add(name)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                if self._nvml is not None:
+                    self._sample_nvml()
+                else:
+                    self._sample_smi()
+            except Exception:  # noqa: BLE001 - a failed sample is skipped
+                pass
+            self._stop.wait(0.001 if self._nvml is not None else 0.05)
 
     def start(self):
-        try:
-            self.path = tempfile.mktemp(prefix="clocks-", suffix=".csv")
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
-                 str(self.device_index)],
-                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
+        import threading
+
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        clocks, max_clock, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        try:
-            for line in open(self.path):
-                f = [v.strip() for v in line.split(",")]
-                if len(f) < 9:
-                    continue
-                try:
-                    clocks.append(float(f[1]))
-                    max_clock = float(f[2])
-                except ValueError:
-                    continue
-                for name, value in zip(names, f[5:9]):
-                    if value.lower().startswith("active"):
-                        reasons.add(name)
-            os.unlink(self.path)
-        except OSError:
-            pass
-        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
-                "samples": len(clocks), "reasons": sorted(reasons)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=15)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_clock,
+                "samples": len(self.samples), "reasons": sorted(self.reasons),
+                "how": "NVML, about 1 ms period, during the timed loop" if self._nvml is not None else "nvidia-smi per sample"}
 
 
 def max_over_ranks(value):
