@@ -201,7 +201,7 @@ def run_ours(args, rank, world, local_rank):
         channels = args.channels or default_channels(world, tokens)
         config = HostStagedConfig(channels=channels, stage=7 if args.wire != "bf16" else 6, wire_dtype=args.wire,
                                   copy_engine=args.engine, transport=args.transport, timeout_ms=20000,
-                                  output_pool_size=2, tx_warps=4, rx_warps=8)
+                                  output_pool_size=2, tx_warps=2, rx_warps=10)
         buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
         g = torch.Generator().manual_seed(1234 + rank)
         host_x = [torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16).pin_memory() for _ in range(INPUT_SETS)]
@@ -263,31 +263,55 @@ def run_ours(args, rank, world, local_rank):
         if want_e2e:
             checksum_host = torch.zeros(1, dtype=torch.float32).pin_memory()
             h2d = host_x[0].numel() * 2 + host_idx.numel() * 8 + host_w.numel() * 4
-            stage_x = torch.empty_like(dev_x[0])
-            stage_idx, stage_w = torch.empty_like(dev_idx), torch.empty_like(dev_w)
+            # A serving loop: two input buffers on the device, a copy stream that brings step i+1's inputs
+            # from pinned host memory while step i computes, and a blocking read of every step's result.
+            # Every step's host->device copy and device->host read are inside the timed region.
+            copy_stream = torch.cuda.Stream()
+            stages = [(torch.empty_like(dev_x[0]), torch.empty_like(dev_idx), torch.empty_like(dev_w)) for _ in range(2)]
+            copied = [torch.cuda.Event() for _ in range(2)]
+            consumed = [torch.cuda.Event() for _ in range(2)]
 
-            def e2e_step(i):
-                stage_x.copy_(host_x[i % INPUT_SETS], non_blocking=True)
-                stage_idx.copy_(host_idx, non_blocking=True)
-                stage_w.copy_(host_w, non_blocking=True)
-                recv_x, _, _, handle, _ = buffer.dispatch(stage_x, stage_idx, stage_w, do_expand=True)
-                combined, _, _ = buffer.combine(recv_x, handle)
-                checksum_host.copy_(combined[:, :8].float().sum().reshape(1), non_blocking=True)
-                torch.cuda.current_stream().synchronize()  # the step's result is read on the host
-                return float(checksum_host[0])
+            def upload(i):
+                slot = i % 2
+                with torch.cuda.stream(copy_stream):
+                    copy_stream.wait_event(consumed[slot])  # the kernels that read this buffer two steps ago are done
+                    stages[slot][0].copy_(host_x[i % INPUT_SETS], non_blocking=True)
+                    stages[slot][1].copy_(host_idx, non_blocking=True)
+                    stages[slot][2].copy_(host_w, non_blocking=True)
+                    copied[slot].record(copy_stream)
 
-            for i in range(min(3, warmup)):
-                e2e_step(i)
+            def e2e_loop(count):
+                compute = torch.cuda.current_stream()
+                for slot in range(2):
+                    consumed[slot].record(compute)
+                upload(0)
+                total = 0.0
+                for i in range(count):
+                    slot = i % 2
+                    if i + 1 < count:
+                        upload(i + 1)
+                    compute.wait_event(copied[slot])
+                    sx, si, sw = stages[slot]
+                    recv_x, _, _, handle, _ = buffer.dispatch(sx, si, sw, do_expand=True)
+                    combined, _, _ = buffer.combine(recv_x, handle)
+                    consumed[slot].record(compute)
+                    checksum_host.copy_(combined[:, :8].float().sum().reshape(1), non_blocking=True)
+                    compute.synchronize()  # the step's result is read on the host
+                    total += float(checksum_host[0])
+                    del recv_x, handle, combined
+                return total
+
+            e2e_loop(min(3, warmup))
             dist.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for i in range(steps):
-                e2e_step(i)
+            e2e_loop(steps)
             e1.record()
             torch.cuda.synchronize()
             result["e2e"] = {"value": max_over_ranks(e0.elapsed_time(e1) * 1000.0 / steps), "unit": "us/step",
-                             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4}
+                             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                             "how": "inputs double-buffered: a copy stream uploads step i+1 from pinned memory while step i runs; every step ends with a blocking 4-byte read of its checksum"}
             buffer.check_errors()
         buffer.close()
         return result

@@ -48,7 +48,7 @@ def bench_one(args, tokens: int, rank: int, world: int, device: torch.device):
     wire_fp8 = args.wire == "fp8_e4m3"
     config = HostStagedConfig(channels=args.channels or channels_for(tokens), stage=7 if wire_fp8 else 6,
                               wire_dtype=args.wire, enable_graph=args.mode.startswith("graph"), timeout_ms=20000,
-                              output_pool_size=2, tx_warps=4, rx_warps=8, copy_engine=args.engine)
+                              output_pool_size=2, tx_warps=2, rx_warps=10, copy_engine=args.engine)
     spec = FixtureSpec(args.profile, tokens, args.experts, args.topk, world, args.seed)
     idx_cpu, w_cpu = make_routes(spec, rank)
     volume = route_volume(idx_cpu, rank, world, args.experts)

@@ -113,7 +113,7 @@ def main() -> None:
             return expand(gathered_rows, args.hidden, args.topk, rank, local)
 
         config = HostStagedConfig(channels=32 if tokens <= 256 else 64 if tokens <= 1024 else 128, timeout_ms=20000,
-                                  output_pool_size=2, tx_warps=4, rx_warps=8, enable_combine=False)
+                                  output_pool_size=2, tx_warps=2, rx_warps=10, enable_combine=False)
         buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, args.hidden, args.topk, args.experts, config,
                                     control_group=control)
 

@@ -59,7 +59,7 @@ def main() -> None:
         except Exception:  # noqa: BLE001
             peak = 1403.0
     config = HostStagedConfig(channels=128 if args.tokens > 1024 else 64, timeout_ms=20000, output_pool_size=2,
-                              tx_warps=4, rx_warps=8)
+                              tx_warps=2, rx_warps=10)
     spec = FixtureSpec("uniform", args.tokens, args.experts, args.topk, world, DEFAULT_SEED)
     idx_cpu, w_cpu = make_routes(spec, rank)
     idx, w = idx_cpu.to(device), w_cpu.to(device)

@@ -42,7 +42,7 @@ def main() -> None:
     args = parser.parse_args()
     torch.cuda.set_device(0)
     dist.init_process_group("gloo", store=dist.FileStore(tempfile.mktemp(prefix="profile-store-"), 1), rank=0, world_size=1)
-    config = HostStagedConfig(channels=args.channels, timeout_ms=20000, output_pool_size=2, tx_warps=4, rx_warps=8,
+    config = HostStagedConfig(channels=args.channels, timeout_ms=20000, output_pool_size=2, tx_warps=2, rx_warps=10,
                               stage=7, wire_dtype=args.wire)
     idx, w = make_routes(FixtureSpec("uniform", args.tokens, args.experts, args.topk, 1, DEFAULT_SEED), 0)
     idx, w = idx.cuda(), w.cuda()

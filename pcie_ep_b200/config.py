@@ -97,8 +97,8 @@ class HostStagedConfig:
     # --- Blackwell additions -------------------------------------------------
     transport: str = "auto"
     copy_engine: str = "tma"
-    tx_warps: int = 4
-    rx_warps: int = 6
+    tx_warps: int = 2
+    rx_warps: int = 10
     virtual_ranks: int = 1
     enable_combine: bool = True
 
