@@ -75,6 +75,15 @@ __device__ __forceinline__ void umma_f16(std::uint32_t tmem_d, std::uint64_t des
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+__device__ __forceinline__ void umma_f8(std::uint32_t tmem_d, std::uint64_t desc_a, std::uint64_t desc_b,
+                                        std::uint32_t idesc, std::uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // all MMAs issued so far by this thread arrive on `bar` when they have completed
 __device__ __forceinline__ void umma_commit(std::uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
@@ -118,6 +127,11 @@ __host__ __device__ constexpr std::uint32_t make_idesc_bf16(int m, int n) {
            | (static_cast<std::uint32_t>(m >> 4) << 24);
 }
 
+// kind::f8f6f4 with E4M3 operands (format code 0 for both), FP32 accumulation
+__host__ __device__ constexpr std::uint32_t make_idesc_e4m3(int m, int n) {
+    return (1u << 4) | (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(m >> 4) << 24);
+}
+
 struct TileCursor {
     // walks tiles in (expert, n-tile, m-tile) order: consecutive tiles share the weight tile
     int expert = 0;
@@ -143,7 +157,7 @@ struct TileCursor {
 
 }  // namespace
 
-template <bool kSwiGLU>
+template <bool kSwiGLU, bool kFp8>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GroupedGemmParams p) {
@@ -164,6 +178,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    constexpr int kElemBytes = kFp8 ? 1 : 2;
+    constexpr int kBlockK = kBlockKBytes / kElemBytes;  // elements of K per stage
     const int n_tiles = p.n / kBlockN;
     const int k_blocks = p.k / kBlockK;
     const int w_rows_per_expert = kSwiGLU ? 2 * p.n : p.n;
@@ -222,7 +238,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ===== MMA issuer =====
         if (lane == 0) {
-            constexpr std::uint32_t idesc = make_idesc_bf16(kBlockM, kBlockN);
+            constexpr std::uint32_t idesc = kFp8 ? make_idesc_e4m3(kBlockM, kBlockN) : make_idesc_bf16(kBlockM, kBlockN);
             TileCursor cursor;
             int stage = 0;
             unsigned phase = 0;
@@ -247,12 +263,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const std::uint64_t desc_b0 = make_smem_desc(stage_base + Plan::kTileA);
                     const std::uint64_t desc_b1 = make_smem_desc(stage_base + Plan::kTileA + Plan::kTileB);
 #pragma unroll
-                    for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                        // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in the address field
-                        const std::uint64_t step = static_cast<std::uint64_t>(k * kUmmaK * 2) >> 4;
+                    for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
+                        // 32 bytes further along K inside the swizzle atom: +2 in the address field
+                        const std::uint64_t step = static_cast<std::uint64_t>(k * kUmmaKBytes) >> 4;
                         const std::uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
-                        umma_f16(acc, desc_a + step, desc_b0 + step, idesc, accumulate);
-                        if (kSwiGLU) umma_f16(acc + kBlockN, desc_a + step, desc_b1 + step, idesc, accumulate);
+                        if (kFp8) {
+                            umma_f8(acc, desc_a + step, desc_b0 + step, idesc, accumulate);
+                            if (kSwiGLU) umma_f8(acc + kBlockN, desc_a + step, desc_b1 + step, idesc, accumulate);
+                        } else {
+                            umma_f16(acc, desc_a + step, desc_b0 + step, idesc, accumulate);
+                            if (kSwiGLU) umma_f16(acc + kBlockN, desc_a + step, desc_b1 + step, idesc, accumulate);
+                        }
                     }
                     umma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
                     if (++stage == kStages) {
@@ -279,6 +300,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const bool valid = row < p.expert_counts[cursor.expert];
             const long long out_row = static_cast<long long>(p.expert_offsets[cursor.expert]) + row;
             __nv_bfloat16* out = p.out + out_row * p.n + n_tile * kBlockN;
+            // FP8: the per-row activation scale and the per-output-channel weight scale factor out of the K sum
+            const float a_scale = (kFp8 && valid) ? p.a_scales[out_row] : 1.0f;
+            const float* w_scale = kFp8 ? p.w_scales + static_cast<long long>(cursor.expert) * w_rows_per_expert + n_tile * kBlockN : nullptr;
             const std::uint32_t lane_base = tmem_base + (static_cast<std::uint32_t>(q * 32) << 16) + buf * kAccCols;
 #pragma unroll 1
             for (int c0 = 0; c0 < kBlockN; c0 += 32) {
@@ -291,13 +315,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const float gate = __uint_as_float(g[i]);
-                        v[i] = gate / (1.0f + __expf(-gate)) * __uint_as_float(u[i]);
+                        float gate = __uint_as_float(g[i]);
+                        float up = __uint_as_float(u[i]);
+                        if (kFp8) {
+                            gate *= a_scale * __ldg(w_scale + c0 + i);
+                            up *= a_scale * __ldg(w_scale + p.n + c0 + i);
+                        }
+                        v[i] = gate / (1.0f + __expf(-gate)) * up;
                     }
                 } else {
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(g[i]);
+                    for (int i = 0; i < 32; ++i) {
+                        v[i] = __uint_as_float(g[i]);
+                        if (kFp8) v[i] *= a_scale * __ldg(w_scale + c0 + i);
+                    }
                 }
                 if (valid) {
 #pragma unroll
@@ -347,20 +379,21 @@ EncodeTiled encode_tiled() {
     return fn;
 }
 
-// [rows, k] row-major bf16, box = 64 columns x box_rows rows, 128-byte swizzle
-bool make_map(CUtensorMap* map, const void* base, std::uint64_t rows, std::uint64_t k, std::uint32_t box_rows) {
+// [rows, k] row-major (bf16 or 1-byte fp8), box = 128 bytes of K x box_rows rows, 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* base, std::uint64_t rows, std::uint64_t k, std::uint32_t box_rows, bool fp8) {
     EncodeTiled encode = encode_tiled();
     if (encode == nullptr) return false;
+    const std::uint64_t elem_bytes = fp8 ? 1 : 2;
     const cuuint64_t dims[2] = {k, rows};
-    const cuuint64_t strides[1] = {k * 2};
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), box_rows};
+    const cuuint64_t strides[1] = {k * elem_bytes};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockKBytes / elem_bytes), box_rows};
     const cuuint32_t elem[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+    return encode(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool kSwiGLU>
+template <bool kSwiGLU, bool kFp8>
 cudaError_t launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GroupedGemmParams& p, int ctas, cudaStream_t stream) {
     static bool configured[64] = {false};
     int device = 0;
@@ -368,11 +401,11 @@ cudaError_t launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Gro
     if (status != cudaSuccess) return status;
     constexpr int smem = SmemPlan<kSwiGLU>::kBytes;
     if (device >= 0 && device < 64 && !configured[device]) {
-        status = cudaFuncSetAttribute(grouped_gemm_kernel<kSwiGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        status = cudaFuncSetAttribute(grouped_gemm_kernel<kSwiGLU, kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (status != cudaSuccess) return status;
         configured[device] = true;
     }
-    grouped_gemm_kernel<kSwiGLU><<<ctas, kThreads, smem, stream>>>(map_a, map_b, p);
+    grouped_gemm_kernel<kSwiGLU, kFp8><<<ctas, kThreads, smem, stream>>>(map_a, map_b, p);
     return cudaGetLastError();
 }
 
@@ -380,23 +413,28 @@ cudaError_t launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Gro
 
 }  // namespace gemm
 
-const char* grouped_gemm_bf16(const void* a, const void* w, void* out, const int* expert_offsets, const int* expert_counts,
-                              int* status, int rows_capacity, int num_experts, int n, int k, bool swiglu,
-                              cudaStream_t stream) {
+const char* grouped_gemm(const void* a, const void* w, void* out, const float* a_scales, const float* w_scales,
+                         const int* expert_offsets, const int* expert_counts, int* status, int rows_capacity,
+                         int num_experts, int n, int k, bool swiglu, bool fp8, cudaStream_t stream) {
     using namespace gemm;
-    if (n % kBlockN != 0 || k % kBlockK != 0 || n <= 0 || k <= 0) return "n must be a multiple of 128 and k a multiple of 64";
+    const int block_k = kBlockKBytes / (fp8 ? 1 : 2);
+    if (n % kBlockN != 0 || k % block_k != 0 || n <= 0 || k <= 0)
+        return "n must be a multiple of 128 and k a multiple of 64 (bf16) / 128 (fp8)";
     if (reinterpret_cast<std::uintptr_t>(a) % 16 || reinterpret_cast<std::uintptr_t>(w) % 16 ||
         reinterpret_cast<std::uintptr_t>(out) % 16)
         return "operands must be 16-byte aligned";
+    if (fp8 && (a_scales == nullptr || w_scales == nullptr)) return "fp8 operands need their scales";
     CUtensorMap map_a, map_b;
     const std::uint64_t w_rows = static_cast<std::uint64_t>(num_experts) * (swiglu ? 2 : 1) * n;
-    if (!make_map(&map_a, a, static_cast<std::uint64_t>(rows_capacity), static_cast<std::uint64_t>(k), kBlockM) ||
-        !make_map(&map_b, w, w_rows, static_cast<std::uint64_t>(k), kBlockN))
+    if (!make_map(&map_a, a, static_cast<std::uint64_t>(rows_capacity), static_cast<std::uint64_t>(k), kBlockM, fp8) ||
+        !make_map(&map_b, w, w_rows, static_cast<std::uint64_t>(k), kBlockN, fp8))
         return "cuTensorMapEncodeTiled failed";
     GroupedGemmParams p{};
     p.expert_offsets = expert_offsets;
     p.expert_counts = expert_counts;
     p.out = static_cast<__nv_bfloat16*>(out);
+    p.a_scales = a_scales;
+    p.w_scales = w_scales;
     p.status = status;
     p.num_experts = num_experts;
     p.n = n;
@@ -405,7 +443,9 @@ const char* grouped_gemm_bf16(const void* a, const void* w, void* out, const int
     int device = 0, sms = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
         return "cannot query the device";
-    const cudaError_t err = swiglu ? launch<true>(map_a, map_b, p, sms, stream) : launch<false>(map_a, map_b, p, sms, stream);
+    cudaError_t err;
+    if (fp8) err = swiglu ? launch<true, true>(map_a, map_b, p, sms, stream) : launch<false, true>(map_a, map_b, p, sms, stream);
+    else err = swiglu ? launch<true, false>(map_a, map_b, p, sms, stream) : launch<false, false>(map_a, map_b, p, sms, stream);
     return err == cudaSuccess ? nullptr : cudaGetErrorString(err);
 }
 

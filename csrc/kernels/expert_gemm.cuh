@@ -29,8 +29,8 @@ namespace gemm {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kBlockK = 64;  // 64 bf16 = 128 bytes = one 128B-swizzle atom row
-constexpr int kUmmaK = 16;
+constexpr int kBlockKBytes = 128;  // one 128B-swizzle atom row: 64 bf16 or 128 fp8 elements of K
+constexpr int kUmmaKBytes = 32;    // K extent of one tcgen05.mma: 16 bf16 or 32 fp8
 constexpr int kThreads = 192;  // 6 warps
 constexpr std::uint32_t kWaitLimit = 20u * 1000u * 1000u;  // try_wait probes before giving up (seconds at most)
 
@@ -38,18 +38,20 @@ struct GroupedGemmParams {
     const int* expert_offsets;  // [E+1] first row of every expert in A / out
     const int* expert_counts;   // [E]   valid rows
     __nv_bfloat16* out;         // [rows, N]
+    const float* a_scales;      // FP8 only: one scale per row of A
+    const float* w_scales;      // FP8 only: one scale per weight row [E, (2)N]
     int* status;                // [4]: 0 = ok, 1 = a wait expired
     int num_experts;
     int n;                      // output columns
-    int k;                      // reduction length
+    int k;                      // reduction length in elements
     int rows_capacity;          // rows of A / out
 };
 
 // stages of (A tile + B tiles) that fit; SwiGLU stages carry two B tiles
 template <bool kSwiGLU>
 struct SmemPlan {
-    static constexpr int kTileA = kBlockM * kBlockK * 2;
-    static constexpr int kTileB = kBlockN * kBlockK * 2;
+    static constexpr int kTileA = kBlockM * kBlockKBytes;
+    static constexpr int kTileB = kBlockN * kBlockKBytes;
     static constexpr int kStageBytes = kTileA + (kSwiGLU ? 2 : 1) * kTileB;
     static constexpr int kStages = kSwiGLU ? 4 : 6;
     static constexpr int kBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;

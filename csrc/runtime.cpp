@@ -154,16 +154,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("segment_layout", [](const Runtime& r) { return layout_to_dict(r.layout()); })
         .def("close", &Runtime::close);
 
-    // out[rows of expert e] = a[rows of expert e] @ w[e].T (+ SwiGLU epilogue): tcgen05 grouped GEMM
+    // out[rows of expert e] = a[rows of expert e] @ w[e].T (+ SwiGLU epilogue): tcgen05 grouped GEMM.
+    // a and w are both bfloat16, or both float8_e4m3fn with a_scales [rows] and w_scales [experts, (2)n].
     m.def("grouped_gemm", [](const at::Tensor& a, const at::Tensor& w, at::Tensor& out, const at::Tensor& expert_offsets,
-                             const at::Tensor& expert_counts, at::Tensor& status, bool swiglu, std::int64_t stream) {
+                             const at::Tensor& expert_counts, at::Tensor& status, bool swiglu,
+                             const std::optional<at::Tensor>& a_scales, const std::optional<at::Tensor>& w_scales,
+                             std::int64_t stream) {
         auto check = [](bool ok, const char* what) {
             if (!ok) throw std::invalid_argument(what);
         };
         check(a.is_cuda() && w.is_cuda() && out.is_cuda() && expert_offsets.is_cuda() && expert_counts.is_cuda() && status.is_cuda(),
               "all tensors must be CUDA tensors");
-        check(a.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16,
-              "a, w and out must be bfloat16");
+        const bool fp8 = a.scalar_type() == at::kFloat8_e4m3fn;
+        check((fp8 || a.scalar_type() == at::kBFloat16) && w.scalar_type() == a.scalar_type() && out.scalar_type() == at::kBFloat16,
+              "a and w must both be bfloat16 or both float8_e4m3fn; out must be bfloat16");
         check(a.dim() == 2 && w.dim() == 3 && out.dim() == 2 && a.is_contiguous() && w.is_contiguous() && out.is_contiguous(),
               "a [rows,k], w [experts,n(,x2),k], out [rows,n] must be contiguous");
         const int experts = static_cast<int>(w.size(0));
@@ -175,15 +179,28 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                   expert_offsets.is_contiguous() && expert_counts.is_contiguous(),
               "expert_offsets [experts+1] and expert_counts [experts] must be contiguous int32");
         check(status.scalar_type() == at::kInt && status.numel() >= 4, "status must be int32 [4]");
+        const float* a_scale_ptr = nullptr;
+        const float* w_scale_ptr = nullptr;
+        if (fp8) {
+            check(a_scales.has_value() && w_scales.has_value(), "fp8 operands need a_scales and w_scales");
+            check(a_scales->is_cuda() && a_scales->scalar_type() == at::kFloat && a_scales->is_contiguous() &&
+                      a_scales->numel() >= a.size(0),
+                  "a_scales must be contiguous CUDA float32 [rows]");
+            check(w_scales->is_cuda() && w_scales->scalar_type() == at::kFloat && w_scales->is_contiguous() &&
+                      w_scales->numel() == w.size(0) * w.size(1),
+                  "w_scales must be contiguous CUDA float32 [experts, n(,x2)]");
+            a_scale_ptr = a_scales->data_ptr<float>();
+            w_scale_ptr = w_scales->data_ptr<float>();
+        }
         c10::cuda::CUDAGuard guard(a.device());
         cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
                                                  : at::cuda::getCurrentCUDAStream(a.get_device()).stream();
-        const char* error = grouped_gemm_bf16(a.data_ptr(), w.data_ptr(), out.data_ptr(), expert_offsets.data_ptr<int>(),
-                                              expert_counts.data_ptr<int>(), status.data_ptr<int>(),
-                                              static_cast<int>(a.size(0)), experts, n, k, swiglu, launch_stream);
+        const char* error = grouped_gemm(a.data_ptr(), w.data_ptr(), out.data_ptr(), a_scale_ptr, w_scale_ptr,
+                                         expert_offsets.data_ptr<int>(), expert_counts.data_ptr<int>(), status.data_ptr<int>(),
+                                         static_cast<int>(a.size(0)), experts, n, k, swiglu, fp8, launch_stream);
         if (error != nullptr) throw std::runtime_error(std::string("grouped_gemm: ") + error);
     }, py::arg("a"), py::arg("w"), py::arg("out"), py::arg("expert_offsets"), py::arg("expert_counts"), py::arg("status"),
-       py::arg("swiglu"), py::arg("stream") = 0);
+       py::arg("swiglu"), py::arg("a_scales") = py::none(), py::arg("w_scales") = py::none(), py::arg("stream") = 0);
 
     m.def("litmus", [](std::int64_t mine, std::int64_t theirs, int role, int rounds, int words, at::Tensor& status,
                        int timeout_ms, int device) {

@@ -18,9 +18,23 @@ from typing import Optional
 import torch
 
 
+def quantize_weights_fp8(w: torch.Tensor):
+    """Per-output-channel E4M3 quantisation of expert weights ``[experts, n, k]``: returns ``(codes float8_e4m3fn,
+    scales float32 [experts, n])`` with ``w ~= codes * scales[..., None]`` (scale = amax / 448, 1 for zero rows)."""
+    amax = w.float().abs().amax(dim=2)
+    scales = torch.where(amax == 0, torch.ones_like(amax), amax / 448.0)
+    codes = (w.float() / scales.unsqueeze(2)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return codes.contiguous(), scales.contiguous()
+
+
 def grouped_gemm_reference(a: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor, expert_counts: torch.Tensor,
-                           swiglu: bool = False) -> torch.Tensor:
-    """FP32 reference; rows outside every expert's valid range are zero."""
+                           swiglu: bool = False, a_scales: Optional[torch.Tensor] = None,
+                           w_scales: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """FP32 reference; rows outside every expert's valid range are zero.  FP8 operands are dequantised with
+    their scales first (``a * a_scales[:, None]``, ``w * w_scales[..., None]``)."""
+    if a_scales is not None:
+        a = a.float() * a_scales.float().unsqueeze(1)
+        w = w.float() * w_scales.float().unsqueeze(2)
     experts = w.shape[0]
     n = w.shape[1] // (2 if swiglu else 1)
     out = torch.zeros(a.shape[0], n, dtype=torch.float32, device=a.device)
@@ -40,17 +54,21 @@ def grouped_gemm_reference(a: torch.Tensor, w: torch.Tensor, expert_offsets: tor
 
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor, expert_counts: torch.Tensor, *,
-                 swiglu: bool = False, out: Optional[torch.Tensor] = None,
-                 status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 swiglu: bool = False, out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+                 a_scales: Optional[torch.Tensor] = None, w_scales: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[rows of e] = a[rows of e] @ w[e].T`` (with ``swiglu``: ``silu(gate) * up``, gate rows first in ``w[e]``).
 
     ``a`` is ``[rows, k]`` BF16, ``w`` ``[experts, n, k]`` (``[experts, 2n, k]`` with ``swiglu``); ``n`` must be a
     multiple of 128 and ``k`` of 64 on the GPU path.  Rows that belong to no expert are left untouched.
     ``status`` (int32 ``[4]``) is set non-zero by the kernel if one of its bounded waits expired.
+    With ``float8_e4m3fn`` operands (``kind::f8f6f4`` MMA, ``k`` a multiple of 128) ``a_scales`` ``[rows]`` and
+    ``w_scales`` ``[experts, n]`` are applied in the epilogue: per-row and per-output-channel scales factor out
+    of the reduction, so this is exact with respect to the quantised operands.
     """
     n = w.shape[1] // (2 if swiglu else 1)
     if not a.is_cuda:
-        result = grouped_gemm_reference(a, w, expert_offsets, expert_counts, swiglu).to(a.dtype)
+        result = grouped_gemm_reference(a, w, expert_offsets, expert_counts, swiglu, a_scales, w_scales)
+        result = result.to(torch.bfloat16 if a_scales is not None else a.dtype)
         if out is not None:
             out.copy_(result)
             return out
@@ -61,7 +79,7 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor,
         out = torch.empty(a.shape[0], n, dtype=torch.bfloat16, device=a.device)
     if status is None:
         status = torch.zeros(4, dtype=torch.int32, device=a.device)
-    _C.grouped_gemm(a, w, out, expert_offsets, expert_counts, status, swiglu, 0)
+    _C.grouped_gemm(a, w, out, expert_offsets, expert_counts, status, swiglu, a_scales, w_scales, 0)
     return out
 
 

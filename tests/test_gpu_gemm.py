@@ -4,7 +4,8 @@ experts, sizes that are not multiples of the 128-row tile, aligned gaps), plain 
 import pytest
 import torch
 
-from pcie_ep_b200.ops.grouped_ffn import grouped_gemm, grouped_gemm_reference, grouped_swiglu_ffn
+from pcie_ep_b200.ops.grouped_ffn import grouped_gemm, grouped_gemm_reference, grouped_swiglu_ffn, quantize_weights_fp8
+from pcie_ep_b200.quantization import quantize_fp8_reference
 
 pytestmark = pytest.mark.gpu
 
@@ -53,3 +54,34 @@ def test_swiglu_ffn_two_stage(ext):
     h = grouped_gemm_reference(x.cpu(), w13.cpu(), offsets, cnts, True).to(torch.bfloat16)
     want = grouped_gemm_reference(h, w2.cpu(), offsets, cnts, False)
     assert torch.allclose(y.cpu().float(), want, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_grouped_gemm_fp8_matches_dequantised_reference(ext, swiglu):
+    """E4M3 operands on kind::f8f6f4 with per-row / per-channel scales in the epilogue: exact w.r.t. the
+    quantised operands up to FP32 accumulation order and the BF16 output rounding."""
+    torch.manual_seed(2)
+    k, n = 512, 256
+    counts = [70, 0, 200, 129, 3]
+    offsets, cnts = _layout(counts)
+    rows = int(offsets[-1]) + 11
+    a = torch.randn(rows, k) * 0.7
+    a[5] *= 40.0  # an outlier row gets its own scale
+    codes, a_scales = quantize_fp8_reference(a)
+    a8 = codes.view(torch.float8_e4m3fn)
+    w = torch.randn(len(counts), (2 if swiglu else 1) * n, k) * 0.05
+    w8, w_scales = quantize_weights_fp8(w)
+    out = torch.full((rows, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    grouped_gemm(a8.cuda(), w8.cuda(), offsets.cuda(), cnts.cuda(), swiglu=swiglu, out=out, status=status,
+                 a_scales=a_scales.cuda(), w_scales=w_scales.cuda())
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    want = grouped_gemm_reference(a8, w8, offsets, cnts, swiglu, a_scales, w_scales)
+    valid = torch.zeros(rows, dtype=torch.bool)
+    for e, c in enumerate(counts):
+        valid[int(offsets[e]):int(offsets[e]) + c] = True
+    got = out.cpu().float()
+    scale = float(want[valid].abs().max())
+    assert torch.allclose(got[valid], want[valid], rtol=2e-2, atol=1e-2 * scale), (got[valid] - want[valid]).abs().max()
+    assert (got[~valid] == 7.0).all()
