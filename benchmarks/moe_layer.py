@@ -43,6 +43,7 @@ def main() -> None:
     parser.add_argument("--topk", type=int, default=8)
     parser.add_argument("--iterations", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--fp8", action="store_true", help="FP8 wire kept at the receiver + kind::f8f6f4 gate/up GEMM")
     parser.add_argument("--peak-tflops", type=float, default=0.0, help="cuBLAS BF16 peak to report against (0: read MEASURED_PEAKS.json)")
     args = parser.parse_args()
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -59,7 +60,8 @@ def main() -> None:
         except Exception:  # noqa: BLE001
             peak = 1403.0
     config = HostStagedConfig(channels=128 if args.tokens > 1024 else 64, timeout_ms=20000, output_pool_size=2,
-                              tx_warps=2, rx_warps=10)
+                              tx_warps=2, rx_warps=10, stage=7 if args.fp8 else 6,
+                              wire_dtype="fp8_e4m3" if args.fp8 else "bf16", recv_dtype="fp8_e4m3" if args.fp8 else "bf16")
     spec = FixtureSpec("uniform", args.tokens, args.experts, args.topk, world, DEFAULT_SEED)
     idx_cpu, w_cpu = make_routes(spec, rank)
     idx, w = idx_cpu.to(device), w_cpu.to(device)
@@ -79,8 +81,13 @@ def main() -> None:
             recv_x, _, _, handle, _ = buffer.dispatch(x, idx, w, do_expand=True)
             e[1].record()
             hidden_rows, out_rows = layer._buffers(recv_x.shape[0])
-            grouped_gemm(recv_x, layer.w_gate_up, handle.expert_offsets, handle.expert_counts, swiglu=True,
-                         out=hidden_rows, status=layer.gemm_status)
+            if layer.fp8:
+                grouped_gemm(recv_x, layer.w_gate_up_fp8, handle.expert_offsets, handle.expert_counts, swiglu=True,
+                             out=hidden_rows, status=layer.gemm_status, a_scales=handle._result["recv_x_scales"],
+                             w_scales=layer.w_gate_up_scales)
+            else:
+                grouped_gemm(recv_x, layer.w_gate_up, handle.expert_offsets, handle.expert_counts, swiglu=True,
+                             out=hidden_rows, status=layer.gemm_status)
             grouped_gemm(hidden_rows, layer.w_down, handle.expert_offsets, handle.expert_counts, swiglu=False,
                          out=out_rows, status=layer.gemm_status)
             e[2].record()
@@ -102,7 +109,7 @@ def main() -> None:
         tflops = flops / (parts[1] * 1e-6) / 1e12
         print(json.dumps({
             "metric": "MoE layer step us (dispatch + grouped SwiGLU FFN + combine), device, max over ranks",
-            "value": round(step, 1), "n_gpus": world, "tokens_per_rank": args.tokens,
+            "value": round(step, 1), "n_gpus": world, "fp8_path": bool(args.fp8), "tokens_per_rank": args.tokens,
             "dispatch_us": round(parts[0], 1), "expert_ffn_us": round(parts[1], 1), "combine_us": round(parts[2], 1),
             "expanded_rows_max": rows, "expert_ffn_tflops": round(tflops, 1),
             "fraction_of_measured_bf16_peak": round(tflops / peak, 3), "peak_tflops_used": peak,

@@ -50,6 +50,7 @@ struct RuntimeOptions {
     int payload_slots = 0;
     int timeout_ms = 30000;
     bool wire_fp8 = false;
+    bool recv_fp8 = false;
     bool use_tma = true;
     int tx_warps = 4;
     int rx_warps = 6;
@@ -68,6 +69,8 @@ struct RuntimeOptions {
         o.payload_slots = get("payload_slots", o.payload_slots);
         o.timeout_ms = get("timeout_ms", o.timeout_ms);
         o.wire_fp8 = get("wire_dtype", std::string("bf16")) == "fp8_e4m3";
+        o.recv_fp8 = get("recv_dtype", std::string("bf16")) == "fp8_e4m3";
+        if (o.recv_fp8 && !o.wire_fp8) throw std::invalid_argument("recv_dtype fp8_e4m3 needs wire_dtype fp8_e4m3");
         o.use_tma = get("copy_engine", std::string("tma")) == "tma";
         o.tx_warps = get("tx_warps", o.tx_warps);
         o.rx_warps = get("rx_warps", o.rx_warps);
@@ -98,13 +101,13 @@ struct Layout {
 };
 
 struct OutputSet {
-    at::Tensor recv_x, recv_idx, recv_w, source_meta, comb_map, recv_chan_counts;
+    at::Tensor recv_x, recv_idx, recv_w, recv_scale, source_meta, comb_map, recv_chan_counts;
     at::Tensor unique_count, expanded_count, expert_counts, expert_offsets, expert_prefix, source_offsets;
     at::Tensor source_expert_prefix, error, stats, timestamps, prefix_tx_ts;
     at::Tensor combine_error, combine_stats, profile, combine_profile;
 
     std::vector<const at::Tensor*> all() const {
-        return {&recv_x, &recv_idx, &recv_w, &source_meta, &comb_map, &recv_chan_counts, &unique_count,
+        return {&recv_x, &recv_idx, &recv_w, &recv_scale, &source_meta, &comb_map, &recv_chan_counts, &unique_count,
                 &expanded_count, &expert_counts, &expert_offsets, &expert_prefix, &source_offsets,
                 &source_expert_prefix, &error, &stats, &timestamps, &prefix_tx_ts, &combine_error, &combine_stats, &profile, &combine_profile};
     }
@@ -122,16 +125,16 @@ struct OutputSet {
 class DispatchResult {
    public:
     DispatchResult(std::shared_ptr<OutputSet> set, std::shared_ptr<Layout> layout, bool expand, int num_tokens,
-                   int unique_cap, int expanded_cap, int topk)
+                   int unique_cap, int expanded_cap, int topk, bool recv_fp8 = false)
         : set_(std::move(set)), layout_(std::move(layout)), expand_(expand), num_tokens_(num_tokens),
-          unique_cap_(unique_cap), expanded_cap_(expanded_cap), topk_(topk) {}
+          unique_cap_(unique_cap), expanded_cap_(expanded_cap), topk_(topk), recv_fp8_(recv_fp8) {}
 
     static const std::vector<std::string>& tensor_keys() {
         static const std::vector<std::string> keys = {
             "recv_x", "recv_topk_idx", "recv_topk_weights", "source_meta", "comb_map", "recv_chan_counts",
             "unique_count", "expanded_count", "expert_counts", "expert_offsets", "expert_prefix", "source_offsets",
             "source_expert_prefix", "error", "stats", "transport_timestamps_ns", "prefix_tx_timestamps_ns",
-            "combine_error", "combine_stats", "profiling", "combine_profiling"};
+            "combine_error", "combine_stats", "profiling", "combine_profiling", "recv_x_scales"};
         return keys;
     }
 
@@ -173,7 +176,14 @@ class DispatchResult {
     at::Tensor make(const std::string& key) const {
         const OutputSet& s = *set_;
         const std::int64_t K = topk_;
-        if (key == "recv_x") return s.recv_x.narrow(0, 0, expand_ ? expanded_cap_ : unique_cap_);
+        if (key == "recv_x") {
+            const std::int64_t cap = expand_ ? expanded_cap_ : unique_cap_;
+            if (!recv_fp8_) return s.recv_x.narrow(0, 0, cap);
+            // E4M3 rows occupy the first half of the BF16-sized pool tensor, one byte per element
+            const std::int64_t hidden = s.recv_x.size(1);
+            return s.recv_x.view(at::kByte).reshape({-1}).narrow(0, 0, cap * hidden).view({cap, hidden}).view(at::kFloat8_e4m3fn);
+        }
+        if (key == "recv_x_scales") return recv_fp8_ ? s.recv_scale.narrow(0, 0, expand_ ? expanded_cap_ : unique_cap_) : at::alias(s.recv_scale);
         if (key == "source_meta") return s.source_meta.narrow(0, 0, expand_ ? expanded_cap_ : unique_cap_);
         if (key == "recv_topk_idx")
             return expand_ ? s.recv_idx.narrow(0, 0, expanded_cap_) : s.recv_idx.narrow(0, 0, unique_cap_ * K).view({unique_cap_, K});
@@ -203,6 +213,7 @@ class DispatchResult {
     std::shared_ptr<Layout> layout_;
     bool expand_;
     int num_tokens_, unique_cap_, expanded_cap_, topk_;
+    bool recv_fp8_ = false;
     std::unordered_map<std::string, at::Tensor> cache_;
     py::dict overrides_;
 };
@@ -232,7 +243,7 @@ class Runtime {
         lay_ = make_segment_layout(num_ranks, options_.channels, num_experts, num_topk, hidden, num_max_tokens,
                                    options_.payload_slots, options_.enable_combine);
         const bool vec_ok = (hidden * 2) % 16 == 0;
-        use_tma_ = options_.use_tma && vec_ok;
+        use_tma_ = options_.use_tma && vec_ok && !(options_.recv_fp8 && hidden % 16 != 0);
         threads_ = 32 * (1 + options_.tx_warps + options_.rx_warps);
         smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, use_tma_);
         int max_optin = 0;
@@ -263,6 +274,7 @@ class Runtime {
         rc_.rank = rank;
         rc_.ring_mode = lay_.slots < lay_.slots_full ? 1 : 0;
         rc_.wire_fp8 = options_.wire_fp8 ? 1 : 0;
+        rc_.recv_fp8 = options_.recv_fp8 ? 1 : 0;
         rc_.use_tma = use_tma_ ? 1 : 0;
         rc_.vec_ok = vec_ok ? 1 : 0;
         rc_.tx_warps = options_.tx_warps;
@@ -345,6 +357,7 @@ class Runtime {
         a.recv_x = reinterpret_cast<__nv_bfloat16*>(out.recv_x.data_ptr());
         a.recv_idx = out.recv_idx.data_ptr<std::int64_t>();
         a.recv_w = out.recv_w.data_ptr<float>();
+        a.recv_scale = out.recv_scale.data_ptr<float>();
         a.source_meta = out.source_meta.data_ptr<std::int64_t>();
         a.comb_map = out.comb_map.data_ptr<int>();
         a.recv_chan_counts = out.recv_chan_counts.data_ptr<int>();
@@ -360,7 +373,8 @@ class Runtime {
         a.timestamps = out.timestamps.data_ptr<std::int64_t>();
         a.prefix_tx_ts = out.prefix_tx_ts.data_ptr<std::int64_t>();
         a.profile = out.profile.data_ptr<std::int64_t>();
-        p.result = std::make_shared<DispatchResult>(out_set, plan, expand, T, rc_.unique_cap, rc_.expanded_cap, lay_.num_topk);
+        p.result = std::make_shared<DispatchResult>(out_set, plan, expand, T, rc_.unique_cap, rc_.expanded_cap, lay_.num_topk,
+                                                    options_.recv_fp8);
         return p;
     }
 
@@ -526,6 +540,7 @@ class Runtime {
         s.recv_x = at::empty({rows, lay_.hidden}, bf16);
         s.recv_idx = at::empty({scalars}, i64);
         s.recv_w = at::empty({scalars}, f32);
+        s.recv_scale = at::zeros({options_.recv_fp8 ? rows : 1}, f32);
         s.source_meta = at::empty({rows, 3}, i64);
         s.comb_map = at::zeros({P * C * lay_.slots_full, 2 + 2 * K}, i32);
         s.recv_chan_counts = at::zeros({P, C}, i32);

@@ -210,6 +210,36 @@ __device__ __forceinline__ void rx_row_scatter(const std::uint8_t* src, bool is_
     }
 }
 
+// raw copy of `bytes` (E4M3 codes) from one staged row to n_rows output rows; lane i holds row pointer i
+__device__ __forceinline__ void rx_row_copy_bytes(const std::uint8_t* src, std::uint8_t* dst_of_lane, int n_rows, int bytes) {
+    const unsigned lane = ptx::lane_id();
+    if (bytes % 16 == 0) {
+        const int chunks = bytes / 16;
+        for (int q0 = 0; q0 < chunks; q0 += 128) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int q = q0 + u * 32 + lane;
+                if (q < chunks) v[u] = ptx::ld_v4(src + static_cast<std::size_t>(q) * 16);
+            }
+            for (int i = 0; i < n_rows; ++i) {
+                std::uint8_t* dst = shfl_ptr(dst_of_lane, i);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int q = q0 + u * 32 + lane;
+                    if (q < chunks) ptx::st_v4(dst + static_cast<std::size_t>(q) * 16, v[u]);
+                }
+            }
+        }
+    } else {
+        for (int i = 0; i < n_rows; ++i) {
+            std::uint8_t* dst = shfl_ptr(dst_of_lane, i);
+            const volatile std::uint8_t* s = src;
+            for (int k = lane; k < bytes; k += 32) dst[k] = s[k];
+        }
+    }
+}
+
 __device__ __forceinline__ void zero_row(std::uint8_t* dst, int hidden, bool vec_ok) {
     const unsigned lane = ptx::lane_id();
     if (vec_ok) {
@@ -244,8 +274,9 @@ __device__ __forceinline__ bool warp_give_up(Health& health, int code, int conte
 // destination row of rank d.  Returns false if a copy never completed.
 __device__ __forceinline__ void tx_token_tma(const SegmentLayout& lay, unsigned char* slot, std::uint8_t* dst_of_lane,
                                              unsigned mask, int self, bool wire_fp8) {
+    // self < 0: no BF16 bypass, this rank's own copy is quantised like everybody else's
     const unsigned lane = ptx::lane_id();
-    const unsigned self_bit = 1u << self;
+    const unsigned self_bit = self >= 0 ? 1u << self : 0u;
     const unsigned remote = mask & ~self_bit;
     const unsigned bf16_bytes = static_cast<unsigned>(lay.meta_off + lay.meta_bytes);
     const int hidden = lay.hidden;
@@ -268,7 +299,7 @@ __device__ __forceinline__ void tx_token_tma(const SegmentLayout& lay, unsigned 
     ptx::fence_proxy_async_smem();
     __syncwarp();
     {
-        std::uint8_t* dst = shfl_ptr(dst_of_lane, self);
+        std::uint8_t* dst = shfl_ptr(dst_of_lane, self >= 0 ? self : 0);
         if ((mask & self_bit) && lane == 0) {
             ptx::bulk_s2g(dst, slot, bf16_bytes);
             ptx::bulk_commit();
@@ -331,6 +362,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     const unsigned full = 0xffffffffu;
     const int tx_warps = rc->tx_warps, rx_warps = rc->rx_warps;
     const bool vec_ok = rc->vec_ok != 0, use_tma = rc->use_tma != 0, wire_fp8 = rc->wire_fp8 != 0;
+    const bool recv_fp8 = rc->recv_fp8 != 0;  // rows stay E4M3 at the receiver (scales in recv_scale); implies wire_fp8
+    const int bypass_rank = recv_fp8 ? -1 : me;  // the rank whose own copy stays BF16 under an FP8 wire
+    const std::size_t out_row_bytes = static_cast<std::size_t>(H) * (recv_fp8 ? 1 : 2);
+    std::uint8_t* const recv_bytes = reinterpret_cast<std::uint8_t*>(a.recv_x);
     const bool ring = rc->ring_mode != 0;
     const int map_stride = 2 + 2 * K;
 
@@ -643,7 +678,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             if (a.do_expand && a.zero_padding && !warp_failed(health)) {
                 for (int el = c; el < El; el += C) {
                     for (int row = eoff[el] + ecount[el]; row < eoff[el + 1]; ++row) {
-                        zero_row(reinterpret_cast<std::uint8_t*>(a.recv_x + static_cast<std::size_t>(row) * H), H, vec_ok);
+                        if (recv_fp8) {
+                            for (int b = lane; b < H; b += 32) recv_bytes[static_cast<std::size_t>(row) * H + b] = 0;
+                            if (lane == 0) a.recv_scale[row] = 0.0f;
+                        } else {
+                            zero_row(recv_bytes + static_cast<std::size_t>(row) * out_row_bytes, H, vec_ok);
+                        }
                         if (lane == 0) {
                             a.recv_idx[row] = -1;
                             a.recv_w[row] = 0.0f;
@@ -715,14 +755,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             if (delayed) test_delay(rc->delay_tx_ns);
             if (!use_tma) {
                 float scale = 1.0f;
-                if (wire_fp8 && (mask & ~self_bit)) scale = tx_row_fp8(src, dst, mask, me, H, vec_ok);
+                if (wire_fp8 && (recv_fp8 || (mask & ~self_bit))) scale = tx_row_fp8(src, dst, mask, bypass_rank, H, vec_ok);
                 else tx_row_bf16(src, dst, mask, H, vec_ok);
                 if (lane == 0) reinterpret_cast<float*>(meta_sm)[1] = scale;
                 __syncwarp();
                 for (unsigned m = mask; m; m &= m - 1) {
                     const int d = __ffs(m) - 1;
                     std::uint8_t* row = shfl_ptr(dst, d);
-                    std::uint8_t* mdst = row + ((wire_fp8 && d != me) ? lay.meta_off_fp8 : lay.meta_off);
+                    std::uint8_t* mdst = row + ((wire_fp8 && d != bypass_rank) ? lay.meta_off_fp8 : lay.meta_off);
                     for (int q = lane; q < lay.meta_bytes / 16; q += 32)
                         ptx::st_v4(mdst + q * 16, *reinterpret_cast<const uint4*>(meta_sm + q * 16));
                 }
@@ -730,7 +770,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                 const bool arrived = mbar_wait_bounded(&sh->mbar[warp], parity, health);
                 parity ^= 1u;
                 if (!__all_sync(full, arrived)) break;
-                tx_token_tma(lay, my_slot, dst, mask, me, wire_fp8);
+                tx_token_tma(lay, my_slot, dst, mask, bypass_rank, wire_fp8);
             }
             __syncwarp();
             // publish: READY of this row at every destination (one lane per destination releases)
@@ -787,7 +827,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                     const int s = __ffs(hm) - 1;
                     const int j = __shfl_sync(full, next_j, s);
                     if (lane == static_cast<unsigned>(s)) next_j += rx_warps;
-                    const bool fp8row = wire_fp8 && s != me;
+                    const bool fp8row = wire_fp8 && s != bypass_rank;
                     const std::size_t ring_index = (static_cast<std::size_t>(s) * C + c) * Q + (j % Q);
                     const std::uint8_t* row_src = my_seg + lay.stage_off + ring_index * lay.row_stride;
                     const int moff = fp8row ? lay.meta_off_fp8 : lay.meta_off;
@@ -856,9 +896,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                         // compact: the i-th local slot's row goes to lane i
                         for (unsigned lm = lmask, i = 0; lm; lm &= lm - 1, ++i) {
                             const int r = __shfl_sync(full, row, __ffs(lm) - 1);
-                            if (lane == i) out_ptr = reinterpret_cast<std::uint8_t*>(a.recv_x + static_cast<std::size_t>(r) * H);
+                            if (lane == i) out_ptr = recv_bytes + static_cast<std::size_t>(r) * out_row_bytes;
                         }
                         if (local && !overflow) {
+                            if (recv_fp8) a.recv_scale[row] = scale;
                             a.recv_idx[row] = el;
                             a.recv_w[row] = wgt;
                             a.source_meta[static_cast<std::size_t>(row) * 3 + 0] = s;
@@ -871,8 +912,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                         n_rows = 1;
                         const int row = sh->source_offsets[s] + sh->chan_base[s] + j;
                         overflow = row >= rc->unique_cap;
-                        if (lane == 0) out_ptr = reinterpret_cast<std::uint8_t*>(a.recv_x + static_cast<std::size_t>(row) * H);
+                        if (lane == 0) out_ptr = recv_bytes + static_cast<std::size_t>(row) * out_row_bytes;
                         if (!overflow) {
+                            if (recv_fp8 && lane == 0) a.recv_scale[row] = scale;
                             if (lane < static_cast<unsigned>(K)) {
                                 a.recv_idx[static_cast<std::size_t>(row) * K + lane] = el;
                                 a.recv_w[static_cast<std::size_t>(row) * K + lane] = local ? wgt : 0.0f;
@@ -899,7 +941,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                     std::uint64_t* ack = reinterpret_cast<std::uint64_t*>(rc->seg[s] + lay.ack_off) +
                                          (static_cast<std::size_t>(me) * C + c) * Q + (j % Q);
                     if (!use_tma) {
-                        rx_row_scatter(row_src, fp8row, scale, out_ptr, n_rows, H, vec_ok);
+                        if (recv_fp8) rx_row_copy_bytes(row_src, out_ptr, n_rows, H);
+                        else rx_row_scatter(row_src, fp8row, scale, out_ptr, n_rows, H, vec_ok);
                         if (ring) {
                             __syncwarp();
                             if (lane == 0) ptx::st_release_sys(ack, make_seq(epoch, static_cast<std::uint32_t>(j + 1)));
@@ -907,7 +950,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                     } else {
                         // the row is in shared memory: its ring slot can be handed back already
                         if (ring && lane == 0) ptx::st_release_sys(ack, make_seq(epoch, static_cast<std::uint32_t>(j + 1)));
-                        if (fp8row) {
+                        if (fp8row && !recv_fp8) {
                             // widen in place, decreasing order: chunk q is read before anything lands on it
                             const int chunks = H / 8;
                             for (int q0 = (chunks - 1) / 32 * 32; q0 >= 0; q0 -= 32) {
@@ -923,7 +966,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                         }
                         for (int i = 0; i < n_rows; ++i) {
                             std::uint8_t* dst = shfl_ptr(out_ptr, i);
-                            if (lane == 0) ptx::bulk_s2g(dst, my_slot, static_cast<unsigned>(H) * 2);
+                            if (lane == 0) ptx::bulk_s2g(dst, my_slot, static_cast<unsigned>(out_row_bytes));
                         }
                         if (lane == 0) ptx::bulk_commit();
                     }

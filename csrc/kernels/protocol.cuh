@@ -155,6 +155,7 @@ struct RankConst {
     int rank;
     int ring_mode;     // slots < slots_full: credit/ack path active
     int wire_fp8;      // remote rows travel as E4M3 + FP32 scale
+    int recv_fp8;      // received rows stay E4M3 (row scale in recv_scale); every row is quantised, local ones too
     int use_tma;       // rows move with cp.async.bulk through shared memory
     int vec_ok;        // hidden*2 is a multiple of 16: 16-byte accesses are legal on rows
     int tx_warps, rx_warps;
@@ -194,6 +195,7 @@ struct DispatchArgs {
     __nv_bfloat16* recv_x;
     std::int64_t* recv_idx;
     float* recv_w;
+    float* recv_scale;             // [cap] row scales when rows stay E4M3 at the receiver
     std::int64_t* source_meta;     // [cap][3]
     int* comb_map;                 // [P*C*slots_full][2 + 2K]: inverse map for combine
     int* recv_chan_counts;         // [P][C]

@@ -70,6 +70,10 @@ class HostStagedConfig:
         GPU (one cooperative launch covers all of them).  Used by tests and by
         single-GPU development; 1 in production.
     enable_combine: allocate the combine staging area.
+    recv_dtype: ``"bf16"`` (rows are decoded at the receiver, local rows bypass the wire format) or
+        ``"fp8_e4m3"`` (needs the FP8 wire): every row -- local ones too -- stays E4M3 at the receiver,
+        ``recv_x`` is ``float8_e4m3fn`` and the result carries ``recv_x_scales``, ready for the FP8
+        grouped GEMM.
     """
 
     payload_slots: int = 0
@@ -101,6 +105,7 @@ class HostStagedConfig:
     rx_warps: int = 10
     virtual_ranks: int = 1
     enable_combine: bool = True
+    recv_dtype: str = "bf16"
 
     def __post_init__(self) -> None:
         for name in ("timeout_ms", "replica_slots"):
@@ -145,6 +150,10 @@ class HostStagedConfig:
                 raise ValueError(f"{name} must be a nonnegative integer")
         if self.transport not in _TRANSPORTS:
             raise ValueError(f"transport must be one of {_TRANSPORTS}")
+        if self.recv_dtype not in _WIRE_DTYPES:
+            raise ValueError("recv_dtype must be 'bf16' or 'fp8_e4m3'")
+        if self.recv_dtype == "fp8_e4m3" and self.wire_dtype != "fp8_e4m3":
+            raise ValueError("recv_dtype='fp8_e4m3' needs wire_dtype='fp8_e4m3'")
         if self.copy_engine not in _COPY_ENGINES:
             raise ValueError(f"copy_engine must be one of {_COPY_ENGINES}")
         if not isinstance(self.tx_warps, int) or not 1 <= self.tx_warps <= 8:

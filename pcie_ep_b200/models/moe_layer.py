@@ -17,7 +17,8 @@ from typing import Any, Optional, Tuple
 
 import torch
 
-from ..ops.grouped_ffn import grouped_gemm
+from ..ops.grouped_ffn import grouped_gemm, quantize_weights_fp8
+from ..quantization import dequantize_fp8_reference, quantize_fp8_reference
 
 
 class MoELayer:
@@ -55,6 +56,13 @@ class MoELayer:
         if with_router:
             g = torch.Generator().manual_seed(seed * 1_000_003 + 999_983)
             self.router = (torch.randn(self.num_experts, self.hidden, generator=g) * weight_std).to(self.dtype).to(self.device)
+        # FP8 path: the dispatch delivers E4M3 rows + row scales (recv_dtype="fp8_e4m3"); the gate/up GEMM then
+        # runs on kind::f8f6f4 with per-output-channel weight scales, the down projection stays BF16.
+        self.fp8 = bool(buffer.on_gpu and getattr(buffer.config, "recv_dtype", "bf16") == "fp8_e4m3")
+        self.w_gate_up_fp8 = self.w_gate_up_scales = None
+        if self.fp8:
+            codes, scales = quantize_weights_fp8(self.w_gate_up.float().cpu())
+            self.w_gate_up_fp8, self.w_gate_up_scales = codes.to(self.device), scales.to(self.device)
         self._hidden_rows: Optional[torch.Tensor] = None
         self._out_rows: Optional[torch.Tensor] = None
         self.gemm_status = torch.zeros(4, dtype=torch.int32, device=self.device) if buffer.on_gpu else None
@@ -89,7 +97,11 @@ class MoELayer:
         recv_x, _, _, handle, _ = self.buffer.dispatch(x, topk_idx, topk_weights, do_expand=True)
         hidden_rows, out_rows = self._buffers(recv_x.shape[0])
         offsets, counts = handle.expert_offsets, handle.expert_counts
-        grouped_gemm(recv_x, self.w_gate_up, offsets, counts, swiglu=True, out=hidden_rows, status=self.gemm_status)
+        if self.fp8:
+            grouped_gemm(recv_x, self.w_gate_up_fp8, offsets, counts, swiglu=True, out=hidden_rows, status=self.gemm_status,
+                         a_scales=handle._result["recv_x_scales"], w_scales=self.w_gate_up_scales)
+        else:
+            grouped_gemm(recv_x, self.w_gate_up, offsets, counts, swiglu=True, out=hidden_rows, status=self.gemm_status)
         grouped_gemm(hidden_rows, self.w_down, offsets, counts, swiglu=False, out=out_rows, status=self.gemm_status)
         combined, _, _ = self.buffer.combine(out_rows, handle)
         return combined
@@ -105,13 +117,19 @@ class MoELayer:
 
 def dense_moe_reference(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, seed: int,
                         hidden: int, intermediate: int, weight_std: float = 0.02,
-                        weight_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """Single-process FP32 evaluation of the same layer (weights rounded to ``weight_dtype`` like the layer's)."""
+                        weight_dtype: torch.dtype = torch.bfloat16, fp8: bool = False) -> torch.Tensor:
+    """Single-process FP32 evaluation of the same layer (weights rounded to ``weight_dtype`` like the layer's).
+    ``fp8``: tokens and gate/up weights go through the same E4M3 quantisation as the FP8 path."""
     out = torch.zeros(x.shape[0], hidden, dtype=torch.float32)
     xf = x.float()
+    if fp8:
+        xf = (lambda c, s: c.view(torch.float8_e4m3fn).float() * s.unsqueeze(1))(*quantize_fp8_reference(x))
     for e in torch.unique(topk_idx[topk_idx >= 0]).tolist():
         w13, w2 = MoELayer.expert_weights(seed, e, hidden, intermediate, weight_std)
         w13, w2 = w13.to(weight_dtype).float(), w2.to(weight_dtype).float()
+        if fp8:
+            codes, scales = quantize_weights_fp8(w13.unsqueeze(0))
+            w13 = (codes.float() * scales.unsqueeze(2))[0]
         tokens, slots = torch.nonzero(topk_idx == e, as_tuple=True)
         full = xf[tokens] @ w13.t()
         h = torch.nn.functional.silu(full[:, :intermediate]) * full[:, intermediate:]

@@ -29,7 +29,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..quantization import fp8_roundtrip_reference
+from ..quantization import fp8_roundtrip_reference, quantize_fp8_reference
 
 Inputs = Sequence[Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]]
 
@@ -87,11 +87,14 @@ def dispatch_reference(
     do_zero_padding: bool = False,
     wire_dtype: str = "bf16",
     out_dtype: Optional[torch.dtype] = None,
+    recv_dtype: str = "bf16",
 ) -> Dict[str, torch.Tensor]:
     """Result of ``dispatch`` on ``rank`` given every source's inputs.
 
     The returned dict uses the native result's field names.  Rows outside the
     valid ranges are zero (payload, weights), ``-1`` (indices, metadata).
+    ``recv_dtype="fp8_e4m3"``: every row (local ones too) is the E4M3 code of the source row, ``recv_x``
+    is uint8 and ``recv_x_scales`` holds the row scales.
     """
     num_ranks = len(inputs)
     local = num_experts // num_ranks
@@ -100,6 +103,10 @@ def dispatch_reference(
     device = inputs[0][0].device
     dtype = out_dtype or inputs[0][0].dtype
     have_weights = inputs[0][2] is not None
+    keep_fp8 = recv_dtype == "fp8_e4m3"
+    if keep_fp8:
+        dtype = torch.uint8
+    row_scales: List[torch.Tensor] = []
 
     src_rank: List[torch.Tensor] = []
     src_token: List[torch.Tensor] = []
@@ -125,7 +132,10 @@ def dispatch_reference(
         src_rank.append(torch.full_like(tokens, source))
         src_token.append(tokens)
         rows = x[tokens]
-        if wire_dtype == "fp8_e4m3" and source != rank and rows.numel():
+        if keep_fp8:
+            rows, scales = quantize_fp8_reference(rows) if rows.numel() else (rows.new_zeros(rows.shape, dtype=torch.uint8), rows.new_zeros(0, dtype=torch.float32))
+            row_scales.append(scales.float())
+        elif wire_dtype == "fp8_e4m3" and source != rank and rows.numel():
             rows = fp8_roundtrip_reference(rows)
         payload.append(rows.to(dtype))
         local_idx = torch.where(mine, idx - rank * local, torch.full_like(idx, -1))[tokens]
@@ -138,6 +148,7 @@ def dispatch_reference(
     u_payload = torch.cat(payload)
     u_routes = torch.cat(routes)
     u_weights = torch.cat(weights)
+    u_scales = torch.cat(row_scales) if keep_fp8 else None
     unique_count = int(u_rank.numel())
 
     source_offsets = torch.zeros(num_ranks + 1, dtype=torch.int32, device=device)
@@ -191,6 +202,9 @@ def dispatch_reference(
         meta[e_rows, 2] = b_slot
         valid_rows = torch.zeros(cap, dtype=torch.bool, device=device)
         valid_rows[e_rows] = True
+        x_scales = torch.zeros(cap, dtype=torch.float32, device=device)
+        if keep_fp8:
+            x_scales[e_rows] = u_scales[b_row]
     else:
         cap = unique_capacity(num_ranks, num_max_tokens_per_rank)
         recv_x = torch.zeros(cap, hidden, dtype=dtype, device=device)
@@ -204,7 +218,11 @@ def dispatch_reference(
         meta[:unique_count, 1] = u_token
         valid_rows = torch.zeros(cap, dtype=torch.bool, device=device)
         valid_rows[:unique_count] = True
+        x_scales = torch.zeros(cap, dtype=torch.float32, device=device)
+        if keep_fp8:
+            x_scales[:unique_count] = u_scales
     result.update(
+        recv_x_scales=x_scales if keep_fp8 else None,
         recv_x=recv_x,
         recv_topk_idx=recv_idx,
         recv_topk_weights=recv_w if have_weights else None,
@@ -238,7 +256,9 @@ def compare_dispatch(actual: Dict[str, torch.Tensor], expected: Dict[str, torch.
         rows = rows.clone()
         rows[: int(expected["expert_offsets"][-1])] = True
     sel = torch.nonzero(rows).flatten()
-    same("recv_x", actual["recv_x"].cpu()[sel].view(torch.int16), expected["recv_x"].cpu()[sel].view(torch.int16))
+    same("recv_x", actual["recv_x"].cpu()[sel].contiguous().view(torch.uint8), expected["recv_x"].cpu()[sel].contiguous().view(torch.uint8))
+    if expected.get("recv_x_scales") is not None:
+        same("recv_x_scales", actual["recv_x_scales"].cpu()[sel], expected["recv_x_scales"].cpu()[sel])
     same("recv_topk_idx", actual["recv_topk_idx"].cpu()[sel], expected["recv_topk_idx"].cpu()[sel])
     if have_weights and actual.get("recv_topk_weights") is not None:
         same("recv_topk_weights", actual["recv_topk_weights"].cpu()[sel], expected["recv_topk_weights_full"].cpu()[sel])

@@ -39,6 +39,8 @@ def test_defaults_are_valid_and_frozen():
     (dict(virtual_ranks=17), ValueError),
     (dict(stage=8, numa_mode="relay", transport="peer"), ValueError),
     (dict(payload_slots=4, descriptor_slots=5), ValueError),
+    (dict(recv_dtype="fp8_e4m3"), ValueError),                    # needs the FP8 wire
+    (dict(recv_dtype="int8"), ValueError),
 ])
 def test_rejections(kwargs, error):
     with pytest.raises(error):

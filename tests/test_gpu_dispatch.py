@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _run_case(group, world, experts, topk, hidden, tmax, tokens, pattern, expand, alignment, weights=True, seed=7,
-              wire="bf16", zero_padding=None):
+              wire="bf16", zero_padding=None, recv="bf16"):
     from pcie_ep_b200.parallel.virtual import VirtualEPGroup  # noqa: F401
 
     cpu_inputs = [make_inputs(r, world, tokens[r], hidden, experts, topk, pattern, seed=seed, weights=weights)
@@ -27,7 +27,7 @@ def _run_case(group, world, experts, topk, hidden, tmax, tokens, pattern, expand
     for rank in range(world):
         expected = reference.dispatch_reference(cpu_inputs, rank, experts, tmax, do_expand=expand,
                                                 expert_alignment=alignment, do_zero_padding=zero_padding,
-                                                wire_dtype=wire)
+                                                wire_dtype=wire, recv_dtype=recv)
         problems = reference.compare_dispatch(results[rank], expected, do_expand=expand,
                                               do_zero_padding=zero_padding, have_weights=weights)
         assert not problems, f"rank {rank} pattern={pattern} expand={expand}: {problems}"
@@ -91,6 +91,22 @@ def test_dispatch_fp8_wire(ext, engine):
     with VirtualEPGroup(world, tmax, hidden, topk, experts, config) as group:
         for expand in (False, True):
             _run_case(group, world, experts, topk, hidden, tmax, [32, 7, 19, 32], "random", expand, 1, wire="fp8_e4m3")
+
+
+@pytest.mark.parametrize("engine", ["vector", "tma"])
+def test_dispatch_fp8_rows_stay_fp8_at_the_receiver(ext, engine):
+    """recv_dtype=fp8_e4m3: every row (local too) arrives as E4M3 codes plus one scale per row."""
+    from pcie_ep_b200.parallel.virtual import VirtualEPGroup
+
+    world, experts, topk, hidden, tmax = 4, 32, 4, 512, 32
+    config = HostStagedConfig(channels=4, stage=7, wire_dtype="fp8_e4m3", recv_dtype="fp8_e4m3", copy_engine=engine,
+                              timeout_ms=2000, tx_warps=2, rx_warps=3)
+    with VirtualEPGroup(world, tmax, hidden, topk, experts, config) as group:
+        for expand, alignment in ((False, 1), (True, 1), (True, 8)):
+            results, _ = _run_case(group, world, experts, topk, hidden, tmax, [32, 7, 19, 32], "random", expand, alignment,
+                                   wire="fp8_e4m3", recv="fp8_e4m3")
+            assert results[0]["recv_x"].dtype == torch.float8_e4m3fn
+            del results
 
 
 def test_dispatch_headline_shape_small_t(ext):

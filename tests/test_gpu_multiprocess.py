@@ -54,3 +54,13 @@ def test_host_staged_relay_world2():
     """GPU -> own outbox -> CPU relay threads -> destination segment -> destination GPU."""
     _need(2)
     run_workers(2, "--transport", "host_staged", "--numa-mode", "relay", "--suite", "correctness", "--hidden", "256")
+
+
+def test_moe_layer_fp8_path_single_gpu():
+    """FP8 wire kept at the receiver + kind::f8f6f4 gate/up GEMM, against the same quantisation done in PyTorch."""
+    run_workers(1, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256", "--fp8-layer")
+
+
+def test_moe_layer_fp8_path_two_gpus():
+    _need(2)
+    run_workers(2, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256", "--fp8-layer")

@@ -151,8 +151,10 @@ def suite_moe_layer(args, rank, world, device):
     from pcie_ep_b200.models.moe_layer import MoELayer, dense_moe_reference
 
     experts, topk, hidden, inter, tmax = 4 * world, 2, args.hidden, 128, 96
+    fp8 = args.fp8_layer
     config = HostStagedConfig(channels=args.channels, transport=args.transport, timeout_ms=args.timeout_ms,
-                              tx_warps=2, rx_warps=3)
+                              tx_warps=2, rx_warps=3, stage=7 if fp8 else 6, wire_dtype="fp8_e4m3" if fp8 else "bf16",
+                              recv_dtype="fp8_e4m3" if fp8 else "bf16")
     on_gpu = args.transport != "cpu"
     with HostStagedEPBuffer(dist.group.WORLD, tmax, hidden, topk, experts, config) as buffer:
         layer = MoELayer(buffer, inter, seed=5)
@@ -164,7 +166,7 @@ def suite_moe_layer(args, rank, world, device):
             y = layer(xd, idx, w)
             layer.check_errors()
             want = dense_moe_reference(x, idx.cpu(), w.cpu(), 5, hidden, inter,
-                                       weight_dtype=torch.bfloat16 if on_gpu else torch.float32)
+                                       weight_dtype=torch.bfloat16 if on_gpu else torch.float32, fp8=fp8)
             got = y.detach().cpu().float()
             tol = 3e-2 if on_gpu else 1e-4
             ok = got.shape == want.shape and torch.allclose(got, want, rtol=tol, atol=tol * max(1.0, float(want.abs().max())))
@@ -212,6 +214,7 @@ def main():
     parser.add_argument("--payload-slots", type=int, default=0)
     parser.add_argument("--timeout-ms", type=int, default=5000)
     parser.add_argument("--numa-mode", default="direct")
+    parser.add_argument("--fp8-layer", action="store_true")
     parser.add_argument("--small", action="store_true")
     parser.add_argument("--fp32", action="store_true")
     args = parser.parse_args()
