@@ -157,14 +157,19 @@ struct TileCursor {
 
 }  // namespace
 
-template <bool kSwiGLU, bool kFp8>
+// kBoxesB: 128-row weight boxes per stage.  Two boxes land back to back in shared memory and feed ONE
+// tcgen05.mma of N = 256 (A is read from shared memory once per 256 output columns): for SwiGLU they are
+// the gate and the up rows of the same 128 output columns, for the plain GEMM 256 adjacent output columns.
+template <bool kSwiGLU, bool kFp8, int kBoxesB>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GroupedGemmParams p) {
-    using Plan = SmemPlan<kSwiGLU>;
+    static_assert(kBoxesB == 2 || !kSwiGLU, "SwiGLU stages carry the gate and the up box");
+    using Plan = SmemPlan<kBoxesB>;
     constexpr int kStages = Plan::kStages;
-    constexpr int kAccCols = kSwiGLU ? 2 * kBlockN : kBlockN;  // TMEM columns of one accumulator set
-    constexpr int kTmemCols = 2 * kAccCols;                    // double buffered: 256 or 512 (powers of two)
+    constexpr int kAccCols = kBoxesB * kBlockN;   // TMEM columns of one accumulator set = N of one MMA
+    constexpr int kTmemCols = 2 * kAccCols;       // double buffered: 256 or 512 (powers of two)
+    constexpr int kOutN = kSwiGLU ? kBlockN : kAccCols;  // output columns of one tile
 
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<std::uintptr_t>(smem_unaligned) + 1023) & ~std::uintptr_t(1023));
@@ -180,7 +185,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int lane = threadIdx.x & 31;
     constexpr int kElemBytes = kFp8 ? 1 : 2;
     constexpr int kBlockK = kBlockKBytes / kElemBytes;  // elements of K per stage
-    const int n_tiles = p.n / kBlockN;
+    const int n_tiles = p.n / kOutN;
     const int k_blocks = p.k / kBlockK;
     const int w_rows_per_expert = kSwiGLU ? 2 * p.n : p.n;
 
@@ -216,7 +221,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 int m_tile, n_tile;
                 if (!cursor.locate(tile, p, n_tiles, m_tile, n_tile)) break;
                 const int row0 = p.expert_offsets[cursor.expert] + m_tile * kBlockM;
-                const int wrow0 = cursor.expert * w_rows_per_expert + n_tile * kBlockN;
+                const int wrow0 = cursor.expert * w_rows_per_expert + n_tile * kOutN;
+                const int wrow1 = wrow0 + (kSwiGLU ? p.n : kBlockN);
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort)) {
                         ok = false;
@@ -226,8 +232,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     mbar_expect_tx(&full_bar[stage], Plan::kStageBytes);
                     tma_load_2d(stage_base, &map_a, kb * kBlockK, row0, &full_bar[stage]);
                     tma_load_2d(stage_base + Plan::kTileA, &map_b, kb * kBlockK, wrow0, &full_bar[stage]);
-                    if (kSwiGLU)
-                        tma_load_2d(stage_base + Plan::kTileA + Plan::kTileB, &map_b, kb * kBlockK, wrow0 + p.n, &full_bar[stage]);
+                    if (kBoxesB == 2)
+                        tma_load_2d(stage_base + Plan::kTileA + Plan::kTileB, &map_b, kb * kBlockK, wrow1, &full_bar[stage]);
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -238,7 +244,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ===== MMA issuer =====
         if (lane == 0) {
-            constexpr std::uint32_t idesc = kFp8 ? make_idesc_e4m3(kBlockM, kBlockN) : make_idesc_bf16(kBlockM, kBlockN);
+            constexpr std::uint32_t idesc = kFp8 ? make_idesc_e4m3(kBlockM, kAccCols) : make_idesc_bf16(kBlockM, kAccCols);
             TileCursor cursor;
             int stage = 0;
             unsigned phase = 0;
@@ -260,20 +266,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tc_fence_after();
                     unsigned char* stage_base = tiles + stage * Plan::kStageBytes;
                     const std::uint64_t desc_a = make_smem_desc(stage_base);
-                    const std::uint64_t desc_b0 = make_smem_desc(stage_base + Plan::kTileA);
-                    const std::uint64_t desc_b1 = make_smem_desc(stage_base + Plan::kTileA + Plan::kTileB);
+                    // the B boxes are contiguous: 8-row groups stay 1024 bytes apart across the box boundary
+                    const std::uint64_t desc_b = make_smem_desc(stage_base + Plan::kTileA);
 #pragma unroll
                     for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
                         // 32 bytes further along K inside the swizzle atom: +2 in the address field
                         const std::uint64_t step = static_cast<std::uint64_t>(k * kUmmaKBytes) >> 4;
                         const std::uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
-                        if (kFp8) {
-                            umma_f8(acc, desc_a + step, desc_b0 + step, idesc, accumulate);
-                            if (kSwiGLU) umma_f8(acc + kBlockN, desc_a + step, desc_b1 + step, idesc, accumulate);
-                        } else {
-                            umma_f16(acc, desc_a + step, desc_b0 + step, idesc, accumulate);
-                            if (kSwiGLU) umma_f16(acc + kBlockN, desc_a + step, desc_b1 + step, idesc, accumulate);
-                        }
+                        if (kFp8) umma_f8(acc, desc_a + step, desc_b + step, idesc, accumulate);
+                        else umma_f16(acc, desc_a + step, desc_b + step, idesc, accumulate);
                     }
                     umma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
                     if (++stage == kStages) {
@@ -299,13 +300,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int row = m_tile * kBlockM + q * 32 + lane;
             const bool valid = row < p.expert_counts[cursor.expert];
             const long long out_row = static_cast<long long>(p.expert_offsets[cursor.expert]) + row;
-            __nv_bfloat16* out = p.out + out_row * p.n + n_tile * kBlockN;
+            __nv_bfloat16* out = p.out + out_row * p.n + n_tile * kOutN;
             // FP8: the per-row activation scale and the per-output-channel weight scale factor out of the K sum
             const float a_scale = (kFp8 && valid) ? p.a_scales[out_row] : 1.0f;
-            const float* w_scale = kFp8 ? p.w_scales + static_cast<long long>(cursor.expert) * w_rows_per_expert + n_tile * kBlockN : nullptr;
+            const float* w_scale = kFp8 ? p.w_scales + static_cast<long long>(cursor.expert) * w_rows_per_expert + n_tile * kOutN : nullptr;
             const std::uint32_t lane_base = tmem_base + (static_cast<std::uint32_t>(q * 32) << 16) + buf * kAccCols;
 #pragma unroll 1
-            for (int c0 = 0; c0 < kBlockN; c0 += 32) {
+            for (int c0 = 0; c0 < kOutN; c0 += 32) {
                 std::uint32_t g[32];
                 tmem_ld_32x32(lane_base + c0, g);
                 float v[32];
@@ -393,19 +394,19 @@ bool make_map(CUtensorMap* map, const void* base, std::uint64_t rows, std::uint6
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool kSwiGLU, bool kFp8>
+template <bool kSwiGLU, bool kFp8, int kBoxesB>
 cudaError_t launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GroupedGemmParams& p, int ctas, cudaStream_t stream) {
     static bool configured[64] = {false};
     int device = 0;
     cudaError_t status = cudaGetDevice(&device);
     if (status != cudaSuccess) return status;
-    constexpr int smem = SmemPlan<kSwiGLU>::kBytes;
+    constexpr int smem = SmemPlan<kBoxesB>::kBytes;
     if (device >= 0 && device < 64 && !configured[device]) {
-        status = cudaFuncSetAttribute(grouped_gemm_kernel<kSwiGLU, kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        status = cudaFuncSetAttribute(grouped_gemm_kernel<kSwiGLU, kFp8, kBoxesB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (status != cudaSuccess) return status;
         configured[device] = true;
     }
-    grouped_gemm_kernel<kSwiGLU, kFp8><<<ctas, kThreads, smem, stream>>>(map_a, map_b, p);
+    grouped_gemm_kernel<kSwiGLU, kFp8, kBoxesB><<<ctas, kThreads, smem, stream>>>(map_a, map_b, p);
     return cudaGetLastError();
 }
 
@@ -444,8 +445,16 @@ const char* grouped_gemm(const void* a, const void* w, void* out, const float* a
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
         return "cannot query the device";
     cudaError_t err;
-    if (fp8) err = swiglu ? launch<true, true>(map_a, map_b, p, sms, stream) : launch<false, true>(map_a, map_b, p, sms, stream);
-    else err = swiglu ? launch<true, false>(map_a, map_b, p, sms, stream) : launch<false, false>(map_a, map_b, p, sms, stream);
+    const bool wide = n % (2 * kBlockN) == 0;  // plain GEMM: 256-column tiles whenever n allows
+    if (fp8) {
+        err = swiglu ? launch<true, true, 2>(map_a, map_b, p, sms, stream)
+              : wide ? launch<false, true, 2>(map_a, map_b, p, sms, stream)
+                     : launch<false, true, 1>(map_a, map_b, p, sms, stream);
+    } else {
+        err = swiglu ? launch<true, false, 2>(map_a, map_b, p, sms, stream)
+              : wide ? launch<false, false, 2>(map_a, map_b, p, sms, stream)
+                     : launch<false, false, 1>(map_a, map_b, p, sms, stream);
+    }
     return err == cudaSuccess ? nullptr : cudaGetErrorString(err);
 }
 

@@ -8,6 +8,10 @@
 //   plain  : out[row, n]        = sum_k A[row, k] * W[e, n, k]
 //   SwiGLU : out[row, n]        = silu(sum_k A[row,k] * W[e, n, k]) * (sum_k A[row,k] * W[e, N + n, k])
 //
+// One tcgen05.mma covers 128 rows x 256 columns (two 128-row weight boxes back to back in shared memory:
+// gate + up rows for SwiGLU, 256 adjacent output columns for the plain GEMM when n allows), so A is read
+// from shared memory once per 256 accumulator columns.
+//
 // Work decomposition: persistent CTAs walk a tile list (expert, n-tile, m-tile) computed on the
 // device from the counts -- the host never reads a count.  Per CTA: warp 0 = TMA producer,
 // warp 1 = MMA issuer (and TMEM owner), warps 2..5 = epilogue.  Shared-memory stages are handed over
@@ -47,13 +51,13 @@ struct GroupedGemmParams {
     int rows_capacity;          // rows of A / out
 };
 
-// stages of (A tile + B tiles) that fit; SwiGLU stages carry two B tiles
-template <bool kSwiGLU>
+// stages of (A tile + B boxes) that fit; a stage carries one or two 128-row weight boxes
+template <int kBoxesB>
 struct SmemPlan {
     static constexpr int kTileA = kBlockM * kBlockKBytes;
     static constexpr int kTileB = kBlockN * kBlockKBytes;
-    static constexpr int kStageBytes = kTileA + (kSwiGLU ? 2 : 1) * kTileB;
-    static constexpr int kStages = kSwiGLU ? 4 : 6;
+    static constexpr int kStageBytes = kTileA + kBoxesB * kTileB;
+    static constexpr int kStages = kBoxesB == 2 ? 4 : 6;
     static constexpr int kBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 

@@ -19,10 +19,11 @@ def _layout(counts, alignment=1):
 
 
 @pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("n", [384, 512])  # plain GEMM: 128-column tiles / 256-column tiles
 @pytest.mark.parametrize("counts,alignment", [([128], 1), ([5, 0, 300, 129, 1, 0, 77, 256], 1), ([40, 130, 0, 9], 16)])
-def test_grouped_gemm_matches_reference(ext, swiglu, counts, alignment):
+def test_grouped_gemm_matches_reference(ext, swiglu, n, counts, alignment):
     torch.manual_seed(0)
-    k, n = 256, 384
+    k = 256
     offsets, cnts = _layout(counts, alignment)
     rows = int(offsets[-1]) + 37  # spare capacity behind the last expert
     a = (torch.randn(rows, k) * 0.5).to(torch.bfloat16).cuda()
