@@ -21,6 +21,7 @@
 #include <torch/extension.h>
 
 #include "../comm/peer_memory.hpp"
+#include "../kernels/expert_gemm.hpp"
 #include "../kernels/launch.hpp"
 
 namespace bep {
@@ -57,6 +58,7 @@ struct RuntimeOptions {
     int output_pool_size = 3;
     bool enable_graph = false;
     bool enable_combine = true;
+    bool enable_fused = false;
     std::uint64_t delay_meta_ns = 0, delay_tx_ns = 0, delay_rx_ns = 0, delay_scatter_ns = 0;
 
     static RuntimeOptions parse(const py::dict& d) {
@@ -77,6 +79,7 @@ struct RuntimeOptions {
         o.output_pool_size = get("output_pool_size", o.output_pool_size);
         o.enable_graph = get("enable_graph", o.enable_graph);
         o.enable_combine = get("enable_combine", o.enable_combine);
+        o.enable_fused = get("fused_expert_combine", o.enable_fused);
         o.delay_meta_ns = get("metadata_delay_ns", std::uint64_t{0});
         o.delay_tx_ns = get("tx_delay_ns", std::uint64_t{0});
         o.delay_rx_ns = get("rx_delay_ns", std::uint64_t{0});
@@ -241,7 +244,7 @@ class Runtime {
         if (static_cast<int>(segment_pointers.size()) != num_ranks) throw std::invalid_argument("one segment pointer per rank");
         c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
         lay_ = make_segment_layout(num_ranks, options_.channels, num_experts, num_topk, hidden, num_max_tokens,
-                                   options_.payload_slots, options_.enable_combine);
+                                   options_.payload_slots, options_.enable_combine, options_.enable_fused);
         const bool vec_ok = (hidden * 2) % 16 == 0;
         use_tma_ = options_.use_tma && vec_ok && !(options_.recv_fp8 && hidden % 16 != 0);
         threads_ = 32 * (1 + options_.tx_warps + options_.rx_warps);
@@ -300,6 +303,9 @@ class Runtime {
             pools_.push_back(std::make_shared<OutputSet>(make_output_set()));
             plans_.push_back(make_layout());
         }
+        fused_counters_ = at::zeros({2}, i64);
+        fused_status_ = at::zeros({4}, i32);
+        fused_gemm_ctas_ = grouped_gemm_ctas();
         if (options_.enable_combine) {
             const auto bf16 = at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device);
             for (int i = 0; i < options_.output_pool_size; ++i)
@@ -446,6 +452,82 @@ class Runtime {
         cuda_check(launch_combine(launch, options_.channels, static_cast<std::size_t>(lay_.crow_stride), launch_stream), "combine launch");
         return p.out;
     }
+
+    // ---- fused down-projection + combine ------------------------------------------------------------
+    // Step 1 (expert side): out rows = hidden_rows x w_down[e]^T, multiplied by the routing weight and written by
+    // the GEMM epilogue into the token owners' landing slots.  Step 2 (owner side): sum the K slots per token.
+    // The two steps are separate calls so that several virtual ranks of one process can run all their GEMMs
+    // before any reduction (a reduction waits for every rank's GEMM).
+    void fused_scatter_gemm(const at::Tensor& hidden_rows, const at::Tensor& w_down, const DispatchResult& dispatch_result,
+                            std::int64_t stream) {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
+        check_open();
+        if (!options_.enable_fused) throw std::runtime_error("this buffer was built with fused_expert_combine=False");
+        if (!dispatch_result.expand()) throw std::invalid_argument("the fused expert combine needs an expanded dispatch (do_expand=True)");
+        if (lay_.hidden % 256 != 0) throw std::invalid_argument("the fused expert combine needs hidden to be a multiple of 256");
+        const int cap = rc_.expanded_cap;
+        if (!hidden_rows.is_cuda() || hidden_rows.get_device() != device_ || hidden_rows.scalar_type() != at::kBFloat16 ||
+            !hidden_rows.is_contiguous() || hidden_rows.dim() != 2 || hidden_rows.size(0) < 1 || hidden_rows.size(0) > cap)
+            throw std::invalid_argument("expert activations must be contiguous CUDA BF16 [rows <= capacity, intermediate]");
+        const std::int64_t inter = hidden_rows.size(1);
+        if (!w_down.is_cuda() || w_down.get_device() != device_ || w_down.scalar_type() != at::kBFloat16 || !w_down.is_contiguous() ||
+            w_down.dim() != 3 || w_down.size(0) != lay_.num_local_experts || w_down.size(1) != lay_.hidden || w_down.size(2) != inter)
+            throw std::invalid_argument("w_down must be contiguous CUDA BF16 [local experts, hidden, intermediate]");
+        if (fused_gemm_epoch_ != fused_reduce_epoch_) throw std::runtime_error("fused_scatter_gemm called twice without fused_reduce");
+        if (grouped_gemm_ctas() != fused_gemm_ctas_) throw std::runtime_error("device changed under the fused expert combine");
+        const OutputSet& set = dispatch_result.set_ref();
+        gemm::ScatterTarget target{};
+        for (int r = 0; r < lay_.num_ranks; ++r) target.seg[r] = rc_.seg[r];
+        target.source_meta = reinterpret_cast<const long long*>(set.source_meta.data_ptr<std::int64_t>());
+        target.row_weights = set.recv_w.data_ptr<float>();
+        target.stage_off = lay_.fstage_off;
+        target.sig_off = lay_.fsig_off;
+        target.done_off = lay_.fdone_off;
+        target.epoch = fused_gemm_epoch_ + 1;
+        target.cta_done = reinterpret_cast<unsigned long long*>(fused_counters_.data_ptr<std::int64_t>());
+        target.timeout_ns = rc_.timeout_ns;
+        target.row_stride = lay_.crow_stride;
+        target.num_topk = lay_.num_topk;
+        target.num_ranks = lay_.num_ranks;
+        target.rank = rank_;
+        target.flag_stride = kFlagStride;
+        cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
+                                                 : at::cuda::getCurrentCUDAStream(device_).stream();
+        const char* message = grouped_gemm_scatter(hidden_rows.data_ptr(), w_down.data_ptr(), set.expert_offsets.data_ptr<int>(),
+                                                   set.expert_counts.data_ptr<int>(), fused_status_.data_ptr<int>(),
+                                                   static_cast<int>(hidden_rows.size(0)), lay_.num_local_experts, lay_.hidden,
+                                                   static_cast<int>(inter), target, launch_stream);
+        if (message != nullptr) throw std::runtime_error(std::string("fused scatter GEMM: ") + message);
+        ++fused_gemm_epoch_;
+    }
+
+    at::Tensor fused_reduce(const DispatchResult& dispatch_result, const std::optional<at::Tensor>& out_opt, std::int64_t stream) {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
+        check_open();
+        if (fused_reduce_epoch_ + 1 != fused_gemm_epoch_) throw std::runtime_error("fused_reduce needs one preceding fused_scatter_gemm");
+        const std::shared_ptr<Layout>& layout = dispatch_result.layout();
+        if (!layout || !layout->valid) throw std::invalid_argument("dispatch result carries no routing plan");
+        const int T = layout->num_tokens;
+        at::Tensor out = out_opt.has_value() ? *out_opt : select_combine_output(T);
+        if (!out.is_cuda() || out.scalar_type() != at::kBFloat16 || !out.is_contiguous() || out.dim() != 2 ||
+            out.size(0) != T || out.size(1) != lay_.hidden)
+            throw std::invalid_argument("combine output must be contiguous CUDA BF16 [T, hidden]");
+        FusedReduceArgs a{};
+        a.rc = reinterpret_cast<const RankConst*>(rank_const_.data_ptr<std::uint8_t>());
+        a.expert_ord = layout->expert_ord.data_ptr<int>();
+        a.gemm_status = fused_status_.data_ptr<int>();
+        a.num_tokens = T;
+        a.epoch = fused_reduce_epoch_ + 1;
+        a.cta_done = reinterpret_cast<unsigned long long*>(fused_counters_.data_ptr<std::int64_t>()) + 1;
+        a.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+        a.error = dispatch_result.set_ref().combine_error.data_ptr<int>();
+        cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
+                                                 : at::cuda::getCurrentCUDAStream(device_).stream();
+        cuda_check(launch_fused_reduce(a, 2 * fused_gemm_ctas_, launch_stream), "fused reduce launch");
+        ++fused_reduce_epoch_;
+        return out;
+    }
+    at::Tensor fused_status() const { return fused_status_; }
 
     // ---- diagnostics / test hooks (reference: csrc/buffers/advanced.hpp:158-227) -------------
     py::dict pool_debug() const {
@@ -625,6 +707,9 @@ class Runtime {
     std::vector<std::shared_ptr<OutputSet>> pools_;
     std::vector<std::shared_ptr<Layout>> plans_;
     std::vector<at::Tensor> combine_pool_;
+    at::Tensor fused_counters_, fused_status_;
+    std::uint64_t fused_gemm_epoch_ = 0, fused_reduce_epoch_ = 0;
+    int fused_gemm_ctas_ = 0;
     int next_pool_ = 0;
     int next_combine_ = 0;
     bool closed_ = false;

@@ -4,6 +4,7 @@
 #include <mutex>
 
 #include "expert_gemm.hpp"
+#include "ptx.cuh"
 
 namespace bep {
 namespace gemm {
@@ -160,19 +161,31 @@ struct TileCursor {
 // kBoxesB: 128-row weight boxes per stage.  Two boxes land back to back in shared memory and feed ONE
 // tcgen05.mma of N = 256 (A is read from shared memory once per 256 output columns): for SwiGLU they are
 // the gate and the up rows of the same 128 output columns, for the plain GEMM 256 adjacent output columns.
-template <bool kSwiGLU, bool kFp8, int kBoxesB>
+template <bool kSwiGLU, bool kFp8, int kBoxesB, bool kScatter>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GroupedGemmParams p) {
     static_assert(kBoxesB == 2 || !kSwiGLU, "SwiGLU stages carry the gate and the up box");
+    static_assert(!kScatter || (kBoxesB == 2 && !kSwiGLU && !kFp8), "the scatter epilogue exists for the plain BF16 256-column tile");
     using Plan = SmemPlan<kBoxesB>;
     constexpr int kStages = Plan::kStages;
     constexpr int kAccCols = kBoxesB * kBlockN;   // TMEM columns of one accumulator set = N of one MMA
     constexpr int kTmemCols = 2 * kAccCols;       // double buffered: 256 or 512 (powers of two)
     constexpr int kOutN = kSwiGLU ? kBlockN : kAccCols;  // output columns of one tile
 
-    extern __shared__ unsigned char smem_unaligned[];
+    extern __shared__ __align__(1024) unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<std::uintptr_t>(smem_unaligned) + 1023) & ~std::uintptr_t(1023));
+    if (kScatter) {
+        // the scatter variant asks for less alignment slack than the worst case: refuse (uniformly) instead of overrunning
+        std::uint32_t dynamic_bytes;
+        asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dynamic_bytes));
+        const std::uint32_t needed = static_cast<std::uint32_t>(smem - smem_unaligned) + kStages * Plan::kStageBytes + 256 + kScatterStagingBytes;
+        if (needed > dynamic_bytes) {
+            if (threadIdx.x == 0) atomicExch(&p.status[0], 2);
+            return;
+        }
+    }
+    unsigned char* staging = smem + kStages * Plan::kStageBytes + 256;
     unsigned char* tiles = smem;
     std::uint64_t* full_bar = reinterpret_cast<std::uint64_t*>(smem + kStages * Plan::kStageBytes);
     std::uint64_t* empty_bar = full_bar + kStages;
@@ -288,6 +301,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ===== epilogue: 4 warps, warp q owns TMEM lanes [32q, 32q+32) =====
         const int q = warp & 3;
+        const ScatterTarget& sc = p.scatter;
+        if (kScatter) {
+            // every rank must have summed the previous call's rows before its landing area is overwritten
+            if (lane < sc.num_ranks) {
+                const auto* flag = reinterpret_cast<const std::uint64_t*>(sc.seg[sc.rank] + sc.done_off +
+                                                                          static_cast<std::size_t>(lane) * sc.flag_stride);
+                const std::uint64_t deadline = ptx::globaltimer_ns() + sc.timeout_ns;
+                unsigned polls = 0;
+                while (ptx::ld_acquire_sys(flag) + 1 < sc.epoch) {
+                    if ((++polls & 63u) == 0 && (*abort || ptx::globaltimer_ns() > deadline)) {
+                        if (!*abort) atomicCAS(&p.status[0], 0, 3);
+                        *abort = 1;
+                        break;
+                    }
+                    ptx::nanosleep(64);
+                }
+            }
+            __syncwarp();
+        }
+        unsigned char* my_stage = staging + (q * 32 + lane) * kScatterRowPitch;
         TileCursor cursor;
         int it = 0;
         for (int tile = blockIdx.x;; tile += gridDim.x, ++it) {
@@ -305,6 +338,49 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const float a_scale = (kFp8 && valid) ? p.a_scales[out_row] : 1.0f;
             const float* w_scale = kFp8 ? p.w_scales + static_cast<long long>(cursor.expert) * w_rows_per_expert + n_tile * kOutN : nullptr;
             const std::uint32_t lane_base = tmem_base + (static_cast<std::uint32_t>(q * 32) << 16) + buf * kAccCols;
+            if (kScatter) {
+                int owner = -1, token = 0, slot = -1;
+                float weight = 1.0f;
+                if (valid) {
+                    const long long* meta = sc.source_meta + out_row * 3;
+                    owner = static_cast<int>(meta[0]);
+                    token = static_cast<int>(meta[1]);
+                    slot = static_cast<int>(meta[2]);
+                    if (sc.row_weights != nullptr) weight = sc.row_weights[out_row];
+                }
+                const bool send = valid && owner >= 0 && owner < sc.num_ranks && slot >= 0 && slot < sc.num_topk && token >= 0;
+                unsigned char* dst = nullptr;
+                if (send)
+                    dst = sc.seg[owner] + sc.stage_off +
+                          (static_cast<std::size_t>(token) * sc.num_topk + slot) * static_cast<std::size_t>(sc.row_stride) +
+                          static_cast<std::size_t>(n_tile) * kOutN * 2;
+#pragma unroll 1
+                for (int half = 0; half < kOutN / kBlockN; ++half) {
+                    ptx::bulk_wait_read_all();  // this lane's previous copy has left its staging row
+#pragma unroll 1
+                    for (int c0 = 0; c0 < kBlockN; c0 += 32) {
+                        std::uint32_t g[32];
+                        tmem_ld_32x32(lane_base + half * kBlockN + c0, g);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 packed;
+                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                h[j] = __floats2bfloat162_rn(__uint_as_float(g[i + 2 * j]) * weight, __uint_as_float(g[i + 2 * j + 1]) * weight);
+                            *reinterpret_cast<uint4*>(my_stage + (c0 + i) * 2) = packed;
+                        }
+                    }
+                    ptx::fence_proxy_async_smem();  // the lane copies the row it wrote itself
+                    if (send) ptx::bulk_s2g(dst + half * kBlockN * 2, my_stage, kBlockN * 2);
+                    ptx::bulk_commit();
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < kOutN; c0 += 32) {
                 std::uint32_t g[32];
@@ -347,6 +423,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
         }
+        if (kScatter) {
+            ptx::bulk_wait_all();  // every row of this lane has been written to its owner
+            ptx::fence_sys();
+        }
     }
 
     // ---- teardown: every role has left its loop (normally or through the abort latch)
@@ -356,7 +436,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
-    if (threadIdx.x == 0 && *abort) atomicExch(&p.status[0], 1);
+    if (threadIdx.x == 0 && *abort) atomicCAS(&p.status[0], 0, 1);
+    if (kScatter && threadIdx.x == 0) {
+        const ScatterTarget& sc = p.scatter;
+        ptx::fence_sys();
+        const unsigned long long finished = atomicAdd(sc.cta_done, 1ull) + 1ull;
+        if (finished == sc.epoch * gridDim.x) {
+            // last CTA of this launch: all rows of all CTAs are written; tell every owner (unless something gave up)
+            ptx::fence_sys();
+            if (*reinterpret_cast<volatile int*>(p.status) == 0) {
+                for (int r = 0; r < sc.num_ranks; ++r)
+                    ptx::st_release_sys(reinterpret_cast<std::uint64_t*>(sc.seg[r] + sc.sig_off + static_cast<std::size_t>(sc.rank) * sc.flag_stride),
+                                        sc.epoch);
+            }
+        }
+    }
 }
 
 // ---- host side ----------------------------------------------------------------------------------
@@ -394,19 +488,21 @@ bool make_map(CUtensorMap* map, const void* base, std::uint64_t rows, std::uint6
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool kSwiGLU, bool kFp8, int kBoxesB>
+template <bool kSwiGLU, bool kFp8, int kBoxesB, bool kScatter = false>
 cudaError_t launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const GroupedGemmParams& p, int ctas, cudaStream_t stream) {
     static bool configured[64] = {false};
     int device = 0;
     cudaError_t status = cudaGetDevice(&device);
     if (status != cudaSuccess) return status;
-    constexpr int smem = SmemPlan<kBoxesB>::kBytes;
+    // the scatter variant adds its staging rows and keeps 512 bytes of alignment slack (checked in the kernel)
+    constexpr int smem = kScatter ? SmemPlan<kBoxesB>::kStages * SmemPlan<kBoxesB>::kStageBytes + 256 + kScatterStagingBytes + 512
+                                  : SmemPlan<kBoxesB>::kBytes;
     if (device >= 0 && device < 64 && !configured[device]) {
-        status = cudaFuncSetAttribute(grouped_gemm_kernel<kSwiGLU, kFp8, kBoxesB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        status = cudaFuncSetAttribute(grouped_gemm_kernel<kSwiGLU, kFp8, kBoxesB, kScatter>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (status != cudaSuccess) return status;
         configured[device] = true;
     }
-    grouped_gemm_kernel<kSwiGLU, kFp8, kBoxesB><<<ctas, kThreads, smem, stream>>>(map_a, map_b, p);
+    grouped_gemm_kernel<kSwiGLU, kFp8, kBoxesB, kScatter><<<ctas, kThreads, smem, stream>>>(map_a, map_b, p);
     return cudaGetLastError();
 }
 
@@ -414,9 +510,11 @@ cudaError_t launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const Gro
 
 }  // namespace gemm
 
-const char* grouped_gemm(const void* a, const void* w, void* out, const float* a_scales, const float* w_scales,
-                         const int* expert_offsets, const int* expert_counts, int* status, int rows_capacity,
-                         int num_experts, int n, int k, bool swiglu, bool fp8, cudaStream_t stream) {
+namespace {
+const char* run_grouped_gemm(const void* a, const void* w, void* out, const float* a_scales, const float* w_scales,
+                             const int* expert_offsets, const int* expert_counts, int* status, int rows_capacity,
+                             int num_experts, int n, int k, bool swiglu, bool fp8, const gemm::ScatterTarget* target,
+                             cudaStream_t stream) {
     using namespace gemm;
     const int block_k = kBlockKBytes / (fp8 ? 1 : 2);
     if (n % kBlockN != 0 || k % block_k != 0 || n <= 0 || k <= 0)
@@ -424,6 +522,14 @@ const char* grouped_gemm(const void* a, const void* w, void* out, const float* a
     if (reinterpret_cast<std::uintptr_t>(a) % 16 || reinterpret_cast<std::uintptr_t>(w) % 16 ||
         reinterpret_cast<std::uintptr_t>(out) % 16)
         return "operands must be 16-byte aligned";
+    if (target != nullptr) {
+        if (swiglu || fp8 || n % (2 * kBlockN) != 0) return "the scatter epilogue needs a plain BF16 GEMM with n a multiple of 256";
+        if (target->num_ranks < 1 || target->num_ranks > kScatterMaxRanks || target->rank < 0 || target->rank >= target->num_ranks)
+            return "scatter target: bad rank table";
+        if (target->row_stride % 16 != 0 || target->row_stride < 2 * n || target->stage_off % 16 != 0 || target->epoch == 0 ||
+            target->cta_done == nullptr || target->source_meta == nullptr)
+            return "scatter target: bad landing-area description";
+    }
     if (fp8 && (a_scales == nullptr || w_scales == nullptr)) return "fp8 operands need their scales";
     CUtensorMap map_a, map_b;
     const std::uint64_t w_rows = static_cast<std::uint64_t>(num_experts) * (swiglu ? 2 : 1) * n;
@@ -441,12 +547,15 @@ const char* grouped_gemm(const void* a, const void* w, void* out, const float* a
     p.n = n;
     p.k = k;
     p.rows_capacity = rows_capacity;
+    if (target != nullptr) p.scatter = *target;
     int device = 0, sms = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
         return "cannot query the device";
     cudaError_t err;
     const bool wide = n % (2 * kBlockN) == 0;  // plain GEMM: 256-column tiles whenever n allows
-    if (fp8) {
+    if (target != nullptr) {
+        err = launch<false, false, 2, true>(map_a, map_b, p, sms, stream);
+    } else if (fp8) {
         err = swiglu ? launch<true, true, 2>(map_a, map_b, p, sms, stream)
               : wide ? launch<false, true, 2>(map_a, map_b, p, sms, stream)
                      : launch<false, true, 1>(map_a, map_b, p, sms, stream);
@@ -456,6 +565,29 @@ const char* grouped_gemm(const void* a, const void* w, void* out, const float* a
                      : launch<false, false, 1>(map_a, map_b, p, sms, stream);
     }
     return err == cudaSuccess ? nullptr : cudaGetErrorString(err);
+}
+}  // namespace
+
+const char* grouped_gemm(const void* a, const void* w, void* out, const float* a_scales, const float* w_scales,
+                         const int* expert_offsets, const int* expert_counts, int* status, int rows_capacity,
+                         int num_experts, int n, int k, bool swiglu, bool fp8, cudaStream_t stream) {
+    return run_grouped_gemm(a, w, out, a_scales, w_scales, expert_offsets, expert_counts, status, rows_capacity, num_experts,
+                            n, k, swiglu, fp8, nullptr, stream);
+}
+
+const char* grouped_gemm_scatter(const void* a, const void* w, const int* expert_offsets, const int* expert_counts,
+                                 int* status, int rows_capacity, int num_experts, int n, int k,
+                                 const gemm::ScatterTarget& target, cudaStream_t stream) {
+    // `out` is never written by the scatter epilogue; the A pointer stands in to satisfy the alignment check
+    return run_grouped_gemm(a, w, const_cast<void*>(a), nullptr, nullptr, expert_offsets, expert_counts, status, rows_capacity,
+                            num_experts, n, k, false, false, &target, stream);
+}
+
+int grouped_gemm_ctas() {
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+        return 0;
+    return sms;
 }
 
 }  // namespace bep

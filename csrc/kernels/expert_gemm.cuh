@@ -38,17 +38,37 @@ constexpr int kUmmaKBytes = 32;    // K extent of one tcgen05.mma: 16 bf16 or 32
 constexpr int kThreads = 192;  // 6 warps
 constexpr std::uint32_t kWaitLimit = 20u * 1000u * 1000u;  // try_wait probes before giving up (seconds at most)
 
+// Fused down-projection + combine send: instead of writing `out`, the epilogue multiplies every valid row by
+// its routing weight and stores it into the slot (token, k) of the token owner's landing area -- local memory or
+// a peer's, through the segment table -- so the NVLink transfer of a tile overlaps the MMAs of the next ones.
+// When the last CTA of the launch has drained its stores it publishes `epoch` to every rank.
+constexpr int kScatterMaxRanks = 16;
+constexpr int kScatterRowPitch = kBlockN * 2 + 16;  // one 128-column BF16 row segment + 16 B: conflict-free column writes
+constexpr int kScatterStagingBytes = 4 * 32 * kScatterRowPitch;
+struct ScatterTarget {
+    unsigned char* seg[kScatterMaxRanks];  // segment of every rank as addressed from this one
+    const long long* source_meta;          // [rows][3]: owner rank, token, slot k (-1: padding row)
+    const float* row_weights;              // [rows] routing weight of the row; nullptr: 1
+    unsigned long long stage_off, sig_off, done_off;  // landing area, "rows are here" flags, "area consumed" flags
+    unsigned long long epoch;              // number of this fused call (1, 2, ...), the same on every rank
+    unsigned long long* cta_done;          // local monotonic count of finished CTAs over all launches
+    unsigned long long timeout_ns;
+    int row_stride;                        // bytes between landing slots
+    int num_topk, num_ranks, rank, flag_stride;
+};
+
 struct GroupedGemmParams {
     const int* expert_offsets;  // [E+1] first row of every expert in A / out
     const int* expert_counts;   // [E]   valid rows
     __nv_bfloat16* out;         // [rows, N]
     const float* a_scales;      // FP8 only: one scale per row of A
     const float* w_scales;      // FP8 only: one scale per weight row [E, (2)N]
-    int* status;                // [4]: 0 = ok, 1 = a wait expired
+    int* status;                // [4]: 0 = ok, 1 = a wait expired, 2 = shared memory misaligned, 3 = a peer never freed its area
     int num_experts;
     int n;                      // output columns
     int k;                      // reduction length in elements
     int rows_capacity;          // rows of A / out
+    ScatterTarget scatter;      // only read by the scatter variant
 };
 
 // stages of (A tile + B boxes) that fit; a stage carries one or two 128-row weight boxes

@@ -3,6 +3,8 @@
 
 #include <cuda_runtime.h>
 
+#include "expert_gemm.cuh"
+
 namespace bep {
 
 // out[rows of expert e, :] = A[rows of expert e, :] x W[e]^T, optionally with the SwiGLU epilogue
@@ -14,5 +16,14 @@ namespace bep {
 const char* grouped_gemm(const void* a, const void* w, void* out, const float* a_scales, const float* w_scales,
                          const int* expert_offsets, const int* expert_counts, int* status, int rows_capacity,
                          int num_experts, int n, int k, bool swiglu, bool fp8, cudaStream_t stream);
+
+// Plain BF16 GEMM (n a multiple of 256) whose epilogue, instead of writing an output matrix, multiplies each row
+// by its routing weight and stores it into the token owner's landing slot (see gemm::ScatterTarget); the launch's
+// last CTA publishes target.epoch to every rank.  Every launch on a device must use the same CTA count
+// (grouped_gemm_ctas()) and consecutive epochs, because completion is detected with a monotonic counter.
+const char* grouped_gemm_scatter(const void* a, const void* w, const int* expert_offsets, const int* expert_counts,
+                                 int* status, int rows_capacity, int num_experts, int n, int k,
+                                 const gemm::ScatterTarget& target, cudaStream_t stream);
+int grouped_gemm_ctas();
 
 }  // namespace bep

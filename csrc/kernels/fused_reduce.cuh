@@ -1,0 +1,114 @@
+// Owner-side half of the fused down-projection + combine.  The expert ranks' GEMM epilogues have written
+// one weighted BF16 row per (token, slot k) into this rank's landing area (csrc/kernels/expert_gemm.cu,
+// scatter variant) and published their epoch; this kernel waits -- bounded -- for every rank's epoch,
+// sums the K slots of every token in slot order (FP32, deterministic) and hands the area back.
+// The reference has no combine at all (pcie_ep/buffers/ep.py:461-462).
+#pragma once
+
+#include "protocol.cuh"
+
+namespace bep {
+
+constexpr int kFusedReduceThreads = 256;
+
+struct FusedReduceArgs {
+    const RankConst* rc;
+    const int* expert_ord;         // [Tmax][K] routing plan of this rank's own tokens: -1 = unused slot
+    const int* gemm_status;        // status word of this rank's own scatter GEMM of the same call
+    int num_tokens;
+    std::uint64_t epoch;           // number of this fused call (1, 2, ...), the same on every rank
+    unsigned long long* cta_done;  // monotonic count of finished CTAs over all launches
+    __nv_bfloat16* out;            // [T, H]
+    int* error;                    // [8]
+};
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ void fused_accumulate(float (&acc)[8], const uint4& v) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+    }
+}
+
+__global__ void __launch_bounds__(kFusedReduceThreads) fused_reduce_kernel(const FusedReduceArgs a) {
+    const RankConst* rc = a.rc;
+    const SegmentLayout& lay = rc->lay;
+    const int P = lay.num_ranks, K = lay.num_topk;
+    __shared__ int failed;
+    if (threadIdx.x == 0) failed = 0;
+    __syncthreads();
+    if (static_cast<int>(threadIdx.x) < P) {
+        const int peer = threadIdx.x;
+        Health health(rc, a.error);
+        const auto* flag = reinterpret_cast<const std::uint64_t*>(rc->seg[rc->rank] + lay.fsig_off +
+                                                                  static_cast<std::size_t>(peer) * kFlagStride);
+        while (ptx::ld_acquire_sys(flag) < a.epoch) {
+            if (health.give_up(kErrFusedSignalWait, peer, 0)) {
+                failed = 1;
+                break;
+            }
+        }
+    } else if (static_cast<int>(threadIdx.x) == P) {
+        const int status = ptx::ld_volatile(a.gemm_status);
+        if (status != 0) {
+            record_error(rc, a.error, kErrFusedGemm, rc->rank, status);
+            failed = 1;
+        }
+    }
+    __syncthreads();
+
+    if (!failed) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int warps = kFusedReduceThreads / 32;
+        const int chunks = lay.hidden * 2 / 16;
+        const std::uint8_t* area = rc->seg[rc->rank] + lay.fstage_off;
+        const std::size_t pitch = static_cast<std::size_t>(lay.crow_stride);
+        for (int t = blockIdx.x * warps + warp; t < a.num_tokens; t += gridDim.x * warps) {
+            const int ord = lane < K ? a.expert_ord[static_cast<std::size_t>(t) * K + lane] : -1;
+            const unsigned valid = __ballot_sync(0xffffffffu, ord >= 0);
+            const std::uint8_t* rows = area + static_cast<std::size_t>(t) * K * pitch;
+            uint4* out = reinterpret_cast<uint4*>(a.out + static_cast<std::size_t>(t) * lay.hidden);
+            for (int c = lane; c < chunks; c += 32) {
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int k0 = 0; k0 < K; k0 += 8) {
+                    uint4 v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int k = k0 + j;
+                        v[j] = (k < K && (valid >> k & 1u)) ? ptx::ld_v4(rows + k * pitch + static_cast<std::size_t>(c) * 16)
+                                                           : make_uint4(0u, 0u, 0u, 0u);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) fused_accumulate(acc, v[j]);
+                }
+                uint4 packed;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                out[c] = packed;
+            }
+        }
+    }
+
+    // hand the landing area back: the launch's last CTA tells every rank that this epoch has been consumed
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        ptx::fence_sys();
+        const unsigned long long finished = atomicAdd(a.cta_done, 1ull) + 1ull;
+        if (finished == a.epoch * gridDim.x) {
+            ptx::fence_sys();
+            for (int r = 0; r < P; ++r)
+                ptx::st_release_sys(reinterpret_cast<std::uint64_t*>(rc->seg[r] + lay.fdone_off +
+                                                                     static_cast<std::size_t>(rc->rank) * kFlagStride),
+                                    a.epoch);
+        }
+    }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace bep

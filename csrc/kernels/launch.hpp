@@ -6,6 +6,7 @@
 
 #include <cuda_runtime.h>
 
+#include "fused_reduce.cuh"
 #include "protocol.cuh"
 
 namespace bep {
@@ -24,5 +25,9 @@ int combine_resident_ctas(int threads);
 cudaError_t launch_dispatch(const DispatchLaunch& launch, int channels, int threads, std::size_t smem,
                             cudaStream_t stream);
 cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_t crow_stride, cudaStream_t stream);
+
+// Owner-side reduction of the fused down-projection + combine; `ctas` must be the same for every launch of one
+// runtime (completion is counted monotonically).
+cudaError_t launch_fused_reduce(const FusedReduceArgs& args, int ctas, cudaStream_t stream);
 
 }  // namespace bep

@@ -54,6 +54,8 @@ enum ErrorCode : int {
     kErrPeerAbort = 22,        // a peer published abort (context = peer)
     kErrCreditWait = 23,       // ring mode: slot never acknowledged (context = peer)
     kErrCopyEngine = 24,       // a bulk copy never completed
+    kErrFusedSignalWait = 25,  // fused down-projection + combine: a peer's GEMM never signalled (context = peer)
+    kErrFusedGemm = 26,        // fused down-projection + combine: this rank's GEMM gave up (detail = its status word)
 };
 
 enum StatField : int {
@@ -92,6 +94,11 @@ struct SegmentLayout {
     std::size_t cdone_off;        // u64 [P] stride kFlagStride
     std::size_t cready_off;       // u64 [P][Tmax]
     std::size_t cstage_off;       // bytes [P][Tmax][crow_stride]
+    // fused down-projection + combine: the GEMM epilogue of the expert's rank writes weighted output rows
+    // straight into the token owner's slots; the owner sums its K slots per token
+    std::size_t fsig_off;         // u64 [P] stride kFlagStride : written by rank r's GEMM, epoch whose rows are all here
+    std::size_t fdone_off;        // u64 [P] stride kFlagStride : written by rank d's reduction, last epoch it has consumed
+    std::size_t fstage_off;       // bytes [Tmax][K][crow_stride]
     // relay (host_staged + numa_mode relay): outbox rows are written here by the owner and
     // forwarded by CPU threads; unused otherwise
     std::size_t relay_off;
@@ -105,10 +112,11 @@ struct SegmentLayout {
     int meta_bytes;
     int crow_stride;     // bytes per combine row = align128(H*2)
     int has_combine;
+    int has_fused;
 };
 
 inline SegmentLayout make_segment_layout(int P, int C, int E, int K, int H, int Tmax, int payload_slots,
-                                         bool with_combine) {
+                                         bool with_combine, bool with_fused = false) {
     SegmentLayout l{};
     l.num_ranks = P;
     l.num_channels = C;
@@ -126,6 +134,7 @@ inline SegmentLayout make_segment_layout(int P, int C, int E, int K, int H, int 
     l.row_stride = static_cast<int>(align_up(l.meta_off + l.meta_bytes, 128));
     l.crow_stride = static_cast<int>(align_up(static_cast<std::size_t>(H) * 2, 128));
     l.has_combine = with_combine ? 1 : 0;
+    l.has_fused = with_fused ? 1 : 0;
     std::size_t off = 0;
     auto take = [&off](std::size_t bytes) {
         std::size_t at = off;
@@ -142,6 +151,9 @@ inline SegmentLayout make_segment_layout(int P, int C, int E, int K, int H, int 
     l.cready_off = take(with_combine ? static_cast<std::size_t>(P) * Tmax * 8 : 0);
     l.stage_off = take(static_cast<std::size_t>(P) * C * l.slots * l.row_stride);
     l.cstage_off = take(with_combine ? static_cast<std::size_t>(P) * Tmax * l.crow_stride : 0);
+    l.fsig_off = take(static_cast<std::size_t>(P) * kFlagStride);
+    l.fdone_off = take(static_cast<std::size_t>(P) * kFlagStride);
+    l.fstage_off = take(with_fused ? static_cast<std::size_t>(Tmax) * K * l.crow_stride : 0);
     l.relay_off = off;
     l.size_bytes = align_up(off, 4096);
     return l;

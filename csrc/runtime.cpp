@@ -32,6 +32,10 @@ py::dict layout_to_dict(const SegmentLayout& l) {
     d["meta_off_fp8"] = l.meta_off_fp8;
     d["meta_bytes"] = l.meta_bytes;
     d["crow_stride"] = l.crow_stride;
+    d["fsig_off"] = l.fsig_off;
+    d["fdone_off"] = l.fdone_off;
+    d["fstage_off"] = l.fstage_off;
+    d["relay_off"] = l.relay_off;
     return d;
 }
 
@@ -76,9 +80,10 @@ std::vector<at::Tensor> combine_group(const std::vector<std::shared_ptr<Runtime>
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "Blackwell expert-parallel dispatch/combine runtime";
 
-    m.def("segment_layout", [](int P, int C, int E, int K, int H, int Tmax, int payload_slots, bool combine) {
-        return layout_to_dict(make_segment_layout(P, C, E, K, H, Tmax, payload_slots, combine));
-    });
+    m.def("segment_layout", [](int P, int C, int E, int K, int H, int Tmax, int payload_slots, bool combine, bool fused) {
+        return layout_to_dict(make_segment_layout(P, C, E, K, H, Tmax, payload_slots, combine, fused));
+    }, py::arg("P"), py::arg("C"), py::arg("E"), py::arg("K"), py::arg("H"), py::arg("Tmax"), py::arg("payload_slots"),
+       py::arg("combine"), py::arg("fused") = false);
     m.def("allocate_device_segment", [](std::size_t bytes, int device) {
         c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
         return reinterpret_cast<std::int64_t>(allocate_device_segment(bytes).ptr);
@@ -137,6 +142,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              py::arg("stream") = 0)
         .def("combine", &Runtime::combine, py::arg("y"), py::arg("dispatch_result"), py::arg("weighted"), py::arg("out"),
              py::arg("stream") = 0)
+        .def("fused_scatter_gemm", &Runtime::fused_scatter_gemm, py::arg("hidden_rows"), py::arg("w_down"),
+             py::arg("dispatch_result"), py::arg("stream") = 0)
+        .def("fused_reduce", &Runtime::fused_reduce, py::arg("dispatch_result"), py::arg("out"), py::arg("stream") = 0)
+        .def("fused_status", &Runtime::fused_status)
         .def("pool_debug", &Runtime::pool_debug)
         .def("set_test_delays", &Runtime::set_test_delays)
         .def("set_test_prefix_delay_ns", &Runtime::set_test_prefix_delay_ns)

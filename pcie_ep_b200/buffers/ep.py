@@ -144,7 +144,7 @@ class HostStagedEPBuffer:
         self._extension = _C
         layout = _C.segment_layout(
             self.num_ranks, self.config.channels, num_experts, num_topk, hidden, num_max_tokens_per_rank,
-            self.config.payload_slots, self.config.enable_combine,
+            self.config.payload_slots, self.config.enable_combine, self.config.fused_expert_combine,
         )
         self.segments = open_segments(
             _C, chosen, self.rank_idx, self.num_ranks, int(layout["size_bytes"]), self.device, self.control_group,
@@ -441,6 +441,43 @@ class HostStagedEPBuffer:
                     self._comm_busy = False
                 self._register_consumer_stream(compute)
             return combined, None, overlap
+
+    def fused_expert_combine(self, hidden_rows: torch.Tensor, w_down: torch.Tensor, handle: HostStagedEPHandle,
+                             *, out: Optional[torch.Tensor] = None) -> Any:
+        """Down projection and combine in one pass: ``out[t] = sum_k w[t,k] * (hidden_rows[row(t,k)] @ w_down[e]^T)``.
+
+        ``hidden_rows`` ``[rows, intermediate]`` are the expert activations in the layout of the (expanded)
+        dispatch's ``recv_x``, ``w_down`` ``[local experts, hidden, intermediate]``.  The tcgen05 GEMM's epilogue
+        multiplies every output row by the weight that travelled with the dispatch and stores it directly into
+        the owner rank's landing slot ``(token, k)`` over NVLink while later tiles are still being multiplied; the
+        owner then adds its K slots per token in slot order (FP32, deterministic).  Needs
+        ``HostStagedConfig(fused_expert_combine=True)``.  Returns ``(combined_x [T, hidden], None, event)``.
+        """
+        with self._lock:
+            self._check_live()
+            if not self.on_gpu:
+                raise NotImplementedError("fused_expert_combine needs the GPU runtime")
+            if not self.config.fused_expert_combine:
+                raise RuntimeError("this buffer was built with fused_expert_combine=False")
+            if not isinstance(handle, HostStagedEPHandle):
+                raise TypeError("fused_expert_combine needs the handle returned by dispatch")
+            if handle.buffer_id != self.buffer_id or handle.generation != self._generation:
+                raise ValueError("The handle belongs to another buffer generation")
+            if not handle.do_expand:
+                raise ValueError("fused_expert_combine needs a dispatch with do_expand=True")
+            if torch.cuda.is_current_stream_capturing():
+                raise NotImplementedError("fused_expert_combine cannot be issued inside a stream capture")
+            compute = self._current_stream()
+            comm = self._launch_stream(compute, None, False)
+            if comm is not compute:
+                _record_tensors((hidden_rows, w_down, out), comm)
+            self.runtime.fused_scatter_gemm(hidden_rows, w_down, handle._result, comm.cuda_stream)
+            combined = self.runtime.fused_reduce(handle._result, out, comm.cuda_stream)
+            event = torch.cuda.Event()
+            event.record(comm)
+            self._last_event = event
+            self._register_consumer_stream(compute)
+            return combined, None, EventOverlap(event, (self, hidden_rows, w_down, handle, combined), self._register_consumer_stream)
 
     # ------------------------------------------------------------------ cache / graph
     def capture_dispatch(self, *args: Any, **kwargs: Any) -> Any:

@@ -74,6 +74,10 @@ class HostStagedConfig:
         ``"fp8_e4m3"`` (needs the FP8 wire): every row -- local ones too -- stays E4M3 at the receiver,
         ``recv_x`` is ``float8_e4m3fn`` and the result carries ``recv_x_scales``, ready for the FP8
         grouped GEMM.
+    fused_expert_combine: allocate the per-(token, slot) landing area of ``fused_expert_combine``: the
+        down-projection GEMM's epilogue then writes each weighted output row straight into the token
+        owner's memory and a short reduction sums the K slots (expanded dispatches only, ``hidden`` a
+        multiple of 256).
     """
 
     payload_slots: int = 0
@@ -106,6 +110,7 @@ class HostStagedConfig:
     virtual_ranks: int = 1
     enable_combine: bool = True
     recv_dtype: str = "bf16"
+    fused_expert_combine: bool = False
 
     def __post_init__(self) -> None:
         for name in ("timeout_ms", "replica_slots"):
@@ -164,6 +169,8 @@ class HostStagedConfig:
             raise ValueError(f"virtual_ranks must be an integer in [1, {MAX_RANKS}]")
         if self.numa_mode == "relay" and self.transport not in ("host_staged", "auto"):
             raise ValueError("numa_mode='relay' needs transport='host_staged'")
+        if self.fused_expert_combine and self.numa_mode == "relay":
+            raise ValueError("fused_expert_combine writes peer memory directly; it cannot be combined with numa_mode='relay'")
         if self.descriptor_slots not in (0, 256, self.payload_slots):
             raise ValueError("descriptor_slots must be 0, 256 or equal to payload_slots")
 

@@ -63,6 +63,7 @@ class MoELayer:
         if self.fp8:
             codes, scales = quantize_weights_fp8(self.w_gate_up.float().cpu())
             self.w_gate_up_fp8, self.w_gate_up_scales = codes.to(self.device), scales.to(self.device)
+        self.fused_combine = bool(buffer.on_gpu and getattr(buffer.config, "fused_expert_combine", False))
         self._hidden_rows: Optional[torch.Tensor] = None
         self._out_rows: Optional[torch.Tensor] = None
         self.gemm_status = torch.zeros(4, dtype=torch.int32, device=self.device) if buffer.on_gpu else None
@@ -86,7 +87,8 @@ class MoELayer:
     def _buffers(self, rows: int) -> Tuple[torch.Tensor, torch.Tensor]:
         if self._hidden_rows is None or self._hidden_rows.shape[0] != rows:
             self._hidden_rows = torch.empty(rows, self.intermediate, dtype=self.dtype, device=self.device)
-            self._out_rows = torch.empty(rows, self.hidden, dtype=self.dtype, device=self.device)
+            # the fused path never materialises the down projection's output
+            self._out_rows = None if self.fused_combine else torch.empty(rows, self.hidden, dtype=self.dtype, device=self.device)
         return self._hidden_rows, self._out_rows
 
     def forward(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None,
@@ -102,6 +104,10 @@ class MoELayer:
                          a_scales=handle._result["recv_x_scales"], w_scales=self.w_gate_up_scales)
         else:
             grouped_gemm(recv_x, self.w_gate_up, offsets, counts, swiglu=True, out=hidden_rows, status=self.gemm_status)
+        if self.fused_combine:
+            # down projection and combine in one pass: the GEMM epilogue writes weighted rows into the owners' memory
+            combined, _, _ = self.buffer.fused_expert_combine(hidden_rows, self.w_down, handle)
+            return combined
         grouped_gemm(hidden_rows, self.w_down, offsets, counts, swiglu=False, out=out_rows, status=self.gemm_status)
         combined, _, _ = self.buffer.combine(out_rows, handle)
         return combined

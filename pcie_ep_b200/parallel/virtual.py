@@ -39,7 +39,7 @@ class VirtualEPGroup:
         self.device = torch.cuda.current_device() if device is None else device
         layout = _C.segment_layout(
             num_ranks, self.config.channels, num_experts, num_topk, hidden, num_max_tokens_per_rank,
-            self.config.payload_slots, self.config.enable_combine,
+            self.config.payload_slots, self.config.enable_combine, self.config.fused_expert_combine,
         )
         self.segment_bytes = int(layout["size_bytes"])
         self.layout = layout
@@ -72,6 +72,16 @@ class VirtualEPGroup:
 
     def combine(self, ys: Sequence[torch.Tensor], results: Sequence[Dict[str, Any]], weighted: bool = True) -> List[torch.Tensor]:
         return self._C.combine_group(self.runtimes, list(ys), list(results), weighted, self.device)
+
+    def fused_expert_combine(self, hidden_rows: Sequence[torch.Tensor], w_down: Sequence[torch.Tensor],
+                             results: Sequence[Dict[str, Any]], ranks: Optional[Sequence[int]] = None) -> List[torch.Tensor]:
+        """Down projection + combine of every virtual rank: all scatter GEMMs first (launches of one stream run in
+        order, and a reduction waits for every rank's GEMM), then every rank's reduction.  ``ranks`` restricts the
+        GEMMs to some ranks (tests of the bounded wait: the others never signal)."""
+        active = range(self.num_ranks) if ranks is None else ranks
+        for r in active:
+            self.runtimes[r].fused_scatter_gemm(hidden_rows[r], w_down[r], results[r], 0)
+        return [self.runtimes[r].fused_reduce(results[r], None, 0) for r in active]
 
     def errors(self, results: Sequence[Dict[str, Any]]) -> List[List[int]]:
         torch.cuda.synchronize(self.device)
