@@ -37,6 +37,60 @@ def timed(fn, iterations: int, warmup: int, flush: torch.Tensor) -> float:
     return statistics.median(samples)
 
 
+def scatter_timings(args, w2, flush) -> dict:
+    """One emulated rank that owns every expert: T = experts * rows / topk tokens, top-8 over the local experts, so
+    the expanded layout has the benchmark's shape.  Times the two-step path (plain down GEMM, combine kernel) and
+    the fused one (scatter GEMM, K-slot reduction) on the same dispatch result."""
+    from pcie_ep_b200 import HostStagedConfig
+    from pcie_ep_b200.parallel.virtual import VirtualEPGroup
+
+    topk = 8
+    tokens = args.experts * args.rows_per_expert // topk
+    config = HostStagedConfig(channels=128, timeout_ms=20000, output_pool_size=2, fused_expert_combine=True)
+    out = {}
+    with VirtualEPGroup(1, tokens, args.hidden, topk, args.experts, config) as group:
+        gen = torch.Generator(device="cuda").manual_seed(1)
+        x = torch.randn(tokens, args.hidden, device="cuda", generator=gen).to(torch.bfloat16)
+        idx = torch.rand(tokens, args.experts, device="cuda", generator=gen).topk(topk, dim=1).indices.contiguous()
+        w = torch.softmax(torch.randn(tokens, topk, device="cuda", generator=gen), dim=1).contiguous()
+        results = group.dispatch([x], [idx], [w], do_expand=True)
+        rows = results[0]["recv_x"].shape[0]
+        hid = (torch.randn(rows, args.intermediate, device="cuda", generator=gen) * 0.5).to(torch.bfloat16)
+        y = torch.empty(rows, args.hidden, dtype=torch.bfloat16, device="cuda")
+        status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        runtime = group.runtimes[0]
+        offsets, counts = results[0]["expert_offsets"], results[0]["expert_counts"]
+        flops = 2.0 * tokens * topk * args.hidden * args.intermediate
+        t_plain = timed(lambda: grouped_gemm(hid, w2, offsets, counts, swiglu=False, out=y, status=status), args.iterations, args.warmup, flush)
+        t_combine = timed(lambda: group.combine([y], results, weighted=True), args.iterations, args.warmup, flush)
+
+        def fused_pair():
+            runtime.fused_scatter_gemm(hid, w2, results[0], 0)
+            runtime.fused_reduce(results[0], None, 0)
+
+        t_fused = timed(fused_pair, args.iterations, args.warmup, flush)
+        # the reduction alone: the scatter GEMM outside the timed region
+        samples = []
+        for _ in range(args.iterations):
+            runtime.fused_scatter_gemm(hid, w2, results[0], 0)
+            flush.zero_()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runtime.fused_reduce(results[0], None, 0)
+            stop.record()
+            stop.synchronize()
+            samples.append(start.elapsed_time(stop) * 1e3)
+        t_reduce = statistics.median(samples)
+        assert int(runtime.fused_status()[0]) == 0 and status.tolist()[0] == 0
+        out = {"scatter_case": {"tokens": tokens, "topk": topk, "rows": tokens * topk},
+               "down_plain_us": round(t_plain, 1), "combine_kernel_us": round(t_combine, 1),
+               "two_step_us": round(t_plain + t_combine, 1),
+               "down_scatter_plus_reduce_us": round(t_fused, 1), "reduce_only_us": round(t_reduce, 1),
+               "down_scatter_tflops": round(flops / max(t_fused - t_reduce, 1e-3) / 1e6, 1)}
+        del results
+    return out
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__)
     parser.add_argument("--experts", type=int, default=32)
@@ -48,6 +102,9 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--fp8", action="store_true")
     parser.add_argument("--no-library", action="store_true", help="skip the per-expert torch.mm comparison")
+    parser.add_argument("--scatter", action="store_true",
+                        help="also time the down projection with the scatter epilogue (fused combine send) and the owner-side "
+                             "reduction, on a one-rank buffer whose tokens all route to local experts")
     args = parser.parse_args()
 
     torch.cuda.set_device(0)
@@ -103,6 +160,8 @@ def main() -> None:
         l_down = timed(library_down, args.iterations, args.warmup, flush)
         report.update({"library_gate_up_us_without_swiglu": round(l_up, 1), "library_gate_up_tflops": round(f_up / l_up / 1e6, 1),
                        "library_down_us": round(l_down, 1), "library_down_tflops": round(f_down / l_down / 1e6, 1)})
+    if args.scatter:
+        report.update(scatter_timings(args, w2, flush))
     peaks = ROOT / "MEASURED_PEAKS.json"
     if peaks.exists():
         measured = json.loads(peaks.read_text())

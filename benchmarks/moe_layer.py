@@ -44,6 +44,8 @@ def main() -> None:
     parser.add_argument("--iterations", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--fp8", action="store_true", help="FP8 wire kept at the receiver + kind::f8f6f4 gate/up GEMM")
+    parser.add_argument("--fused", action="store_true",
+                        help="down projection fused with the combine send (GEMM epilogue stores into the owners' memory)")
     parser.add_argument("--peak-tflops", type=float, default=0.0, help="cuBLAS BF16 peak to report against (0: read MEASURED_PEAKS.json)")
     args = parser.parse_args()
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -61,7 +63,8 @@ def main() -> None:
             peak = 1403.0
     config = HostStagedConfig(channels=128 if args.tokens > 1024 else 64, timeout_ms=20000, output_pool_size=2,
                               tx_warps=2, rx_warps=10, stage=7 if args.fp8 else 6,
-                              wire_dtype="fp8_e4m3" if args.fp8 else "bf16", recv_dtype="fp8_e4m3" if args.fp8 else "bf16")
+                              wire_dtype="fp8_e4m3" if args.fp8 else "bf16", recv_dtype="fp8_e4m3" if args.fp8 else "bf16",
+                              fused_expert_combine=args.fused)
     spec = FixtureSpec("uniform", args.tokens, args.experts, args.topk, world, DEFAULT_SEED)
     idx_cpu, w_cpu = make_routes(spec, rank)
     idx, w = idx_cpu.to(device), w_cpu.to(device)
@@ -88,10 +91,14 @@ def main() -> None:
             else:
                 grouped_gemm(recv_x, layer.w_gate_up, handle.expert_offsets, handle.expert_counts, swiglu=True,
                              out=hidden_rows, status=layer.gemm_status)
-            grouped_gemm(hidden_rows, layer.w_down, handle.expert_offsets, handle.expert_counts, swiglu=False,
-                         out=out_rows, status=layer.gemm_status)
-            e[2].record()
-            y, _, _ = buffer.combine(out_rows, handle)
+            if args.fused:
+                e[2].record()  # stage 2 = gate/up GEMM only; stage 3 = down projection + combine in one pass
+                y, _, _ = buffer.fused_expert_combine(hidden_rows, layer.w_down, handle)
+            else:
+                grouped_gemm(hidden_rows, layer.w_down, handle.expert_offsets, handle.expert_counts, swiglu=False,
+                             out=out_rows, status=layer.gemm_status)
+                e[2].record()
+                y, _, _ = buffer.combine(out_rows, handle)
             e[3].record()
             e[3].synchronize()
             rows = int(handle.expanded_count.item())
@@ -105,12 +112,14 @@ def main() -> None:
         step = statistics.mean(max(r[i] for r in everyone_total) for i in range(args.iterations))
         parts = [statistics.mean(max(r[i][k] for r in everyone_stage) for i in range(args.iterations)) for k in range(3)]
         rows = max(r[0][3] for r in everyone_stage)
-        flops = 2.0 * rows * args.hidden * args.intermediate * 3
+        flops = 2.0 * rows * args.hidden * args.intermediate * (2 if args.fused else 3)
         tflops = flops / (parts[1] * 1e-6) / 1e12
         print(json.dumps({
             "metric": "MoE layer step us (dispatch + grouped SwiGLU FFN + combine), device, max over ranks",
-            "value": round(step, 1), "n_gpus": world, "fp8_path": bool(args.fp8), "tokens_per_rank": args.tokens,
-            "dispatch_us": round(parts[0], 1), "expert_ffn_us": round(parts[1], 1), "combine_us": round(parts[2], 1),
+            "value": round(step, 1), "n_gpus": world, "fp8_path": bool(args.fp8), "fused_down_combine": bool(args.fused),
+            "tokens_per_rank": args.tokens, "dispatch_us": round(parts[0], 1),
+            ("gate_up_gemm_us" if args.fused else "expert_ffn_us"): round(parts[1], 1),
+            ("down_projection_plus_combine_us" if args.fused else "combine_us"): round(parts[2], 1),
             "expanded_rows_max": rows, "expert_ffn_tflops": round(tflops, 1),
             "fraction_of_measured_bf16_peak": round(tflops / peak, 3), "peak_tflops_used": peak,
         }), flush=True)

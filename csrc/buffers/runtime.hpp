@@ -523,7 +523,7 @@ class Runtime {
         a.error = dispatch_result.set_ref().combine_error.data_ptr<int>();
         cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
                                                  : at::cuda::getCurrentCUDAStream(device_).stream();
-        cuda_check(launch_fused_reduce(a, 2 * fused_gemm_ctas_, launch_stream), "fused reduce launch");
+        cuda_check(launch_fused_reduce(a, 4 * fused_gemm_ctas_, launch_stream), "fused reduce launch");
         ++fused_reduce_epoch_;
         return out;
     }

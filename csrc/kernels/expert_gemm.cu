@@ -354,9 +354,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     dst = sc.seg[owner] + sc.stage_off +
                           (static_cast<std::size_t>(token) * sc.num_topk + slot) * static_cast<std::size_t>(sc.row_stride) +
                           static_cast<std::size_t>(n_tile) * kOutN * 2;
+                const unsigned long long dst_bits = reinterpret_cast<unsigned long long>(dst);
+                const unsigned char* warp_stage = staging + q * 32 * kScatterRowPitch;
+                const int sub = lane & 15;  // 16-byte piece of a 256-byte row segment
 #pragma unroll 1
                 for (int half = 0; half < kOutN / kBlockN; ++half) {
-                    ptx::bulk_wait_read_all();  // this lane's previous copy has left its staging row
+                    // (1) lane = row: accumulator columns -> weighted BF16 -> this lane's staging row
 #pragma unroll 1
                     for (int c0 = 0; c0 < kBlockN; c0 += 32) {
                         std::uint32_t g[32];
@@ -372,13 +375,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             *reinterpret_cast<uint4*>(my_stage + (c0 + i) * 2) = packed;
                         }
                     }
-                    ptx::fence_proxy_async_smem();  // the lane copies the row it wrote itself
-                    if (send) ptx::bulk_s2g(dst + half * kBlockN * 2, my_stage, kBlockN * 2);
-                    ptx::bulk_commit();
+                    if (half == kOutN / kBlockN - 1) {
+                        // the accumulator has been read completely: the MMA warp may start the tile after next
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                    } else {
+                        __syncwarp();
+                    }
+                    // (2) half a warp = one row: 16 lanes store 256 contiguous bytes into the owner's slot, so a
+                    //     peer receives full 128-byte write packets instead of 32 scattered 16-byte pieces
+#pragma unroll 4
+                    for (int r = 0; r < 32; r += 2) {
+                        const int row_lane = r + (lane >> 4);
+                        const unsigned long long to = __shfl_sync(0xffffffffu, dst_bits, row_lane);
+                        const uint4 v = *reinterpret_cast<const uint4*>(warp_stage + row_lane * kScatterRowPitch + sub * 16);
+                        if (to != 0ull) ptx::st_v4(reinterpret_cast<unsigned char*>(to) + half * kBlockN * 2 + sub * 16, v);
+                    }
+                    __syncwarp();  // the staging rows are rewritten by the next half / tile
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&tmem_empty[buf]);
                 continue;
             }
 #pragma unroll 1
@@ -423,10 +438,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
         }
-        if (kScatter) {
-            ptx::bulk_wait_all();  // every row of this lane has been written to its owner
-            ptx::fence_sys();
-        }
+        if (kScatter) ptx::fence_sys();  // this thread's rows before the CTA is counted as finished
     }
 
     // ---- teardown: every role has left its loop (normally or through the abort latch)

@@ -34,7 +34,7 @@ __device__ __forceinline__ void fused_accumulate(float (&acc)[8], const uint4& v
     }
 }
 
-__global__ void __launch_bounds__(kFusedReduceThreads) fused_reduce_kernel(const FusedReduceArgs a) {
+__global__ void __launch_bounds__(kFusedReduceThreads, 4) fused_reduce_kernel(const FusedReduceArgs a) {
     const RankConst* rc = a.rc;
     const SegmentLayout& lay = rc->lay;
     const int P = lay.num_ranks, K = lay.num_topk;
@@ -62,35 +62,47 @@ __global__ void __launch_bounds__(kFusedReduceThreads) fused_reduce_kernel(const
     __syncthreads();
 
     if (!failed) {
+        // Work unit = (token, group of 32 sixteen-byte chunks): one warp iteration with up to 8 row loads per lane
+        // in flight.  Units are dealt out in equal contiguous ranges so that every warp of the grid gets the same
+        // share (a token per warp would leave the grid unbalanced at a few thousand tokens).
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int warps = kFusedReduceThreads / 32;
         const int chunks = lay.hidden * 2 / 16;
+        const int groups = (chunks + 31) / 32;
+        const long long units = static_cast<long long>(a.num_tokens) * groups;
+        const long long total_warps = static_cast<long long>(gridDim.x) * warps;
+        const long long me = static_cast<long long>(blockIdx.x) * warps + warp;
+        const long long first = units * me / total_warps, last = units * (me + 1) / total_warps;
         const std::uint8_t* area = rc->seg[rc->rank] + lay.fstage_off;
         const std::size_t pitch = static_cast<std::size_t>(lay.crow_stride);
-        for (int t = blockIdx.x * warps + warp; t < a.num_tokens; t += gridDim.x * warps) {
-            const int ord = lane < K ? a.expert_ord[static_cast<std::size_t>(t) * K + lane] : -1;
-            const unsigned valid = __ballot_sync(0xffffffffu, ord >= 0);
-            const std::uint8_t* rows = area + static_cast<std::size_t>(t) * K * pitch;
-            uint4* out = reinterpret_cast<uint4*>(a.out + static_cast<std::size_t>(t) * lay.hidden);
-            for (int c = lane; c < chunks; c += 32) {
-                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                for (int k0 = 0; k0 < K; k0 += 8) {
-                    uint4 v[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int k = k0 + j;
-                        v[j] = (k < K && (valid >> k & 1u)) ? ptx::ld_v4(rows + k * pitch + static_cast<std::size_t>(c) * 16)
-                                                           : make_uint4(0u, 0u, 0u, 0u);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) fused_accumulate(acc, v[j]);
-                }
-                uint4 packed;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-                out[c] = packed;
+        int cached_token = -1;
+        unsigned valid = 0;
+        for (long long u = first; u < last; ++u) {
+            const int t = static_cast<int>(u / groups);
+            const int c = static_cast<int>(u % groups) * 32 + lane;
+            if (t != cached_token) {
+                const int ord = lane < K ? a.expert_ord[static_cast<std::size_t>(t) * K + lane] : -1;
+                valid = __ballot_sync(0xffffffffu, ord >= 0);
+                cached_token = t;
             }
+            if (c >= chunks) continue;
+            const std::uint8_t* rows = area + static_cast<std::size_t>(t) * K * pitch + static_cast<std::size_t>(c) * 16;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int k0 = 0; k0 < K; k0 += 8) {
+                uint4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int k = k0 + j;
+                    v[j] = (k < K && (valid >> k & 1u)) ? ptx::ld_v4(rows + k * pitch) : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) fused_accumulate(acc, v[j]);
+            }
+            uint4 packed;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+            reinterpret_cast<uint4*>(a.out + static_cast<std::size_t>(t) * lay.hidden)[c] = packed;
         }
     }
 

@@ -64,3 +64,20 @@ def test_moe_layer_fp8_path_single_gpu():
 def test_moe_layer_fp8_path_two_gpus():
     _need(2)
     run_workers(2, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256", "--fp8-layer")
+
+
+def test_moe_layer_fused_down_projection_and_combine_single_gpu():
+    """The GEMM epilogue writes into the (here: own) landing area; the owner-side reduction finishes the layer."""
+    run_workers(1, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256", "--fused-layer")
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_moe_layer_fused_down_projection_and_combine_multi_gpu(world):
+    """Same over NVLink: tensor-core tiles and peer stores in one kernel, signalled to the owners by its last CTA."""
+    _need(world)
+    run_workers(world, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256", "--fused-layer")
+
+
+def test_moe_layer_fused_with_fp8_dispatch_two_gpus():
+    _need(2)
+    run_workers(2, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256", "--fp8-layer", "--fused-layer")

@@ -154,7 +154,7 @@ def suite_moe_layer(args, rank, world, device):
     fp8 = args.fp8_layer
     config = HostStagedConfig(channels=args.channels, transport=args.transport, timeout_ms=args.timeout_ms,
                               tx_warps=2, rx_warps=3, stage=7 if fp8 else 6, wire_dtype="fp8_e4m3" if fp8 else "bf16",
-                              recv_dtype="fp8_e4m3" if fp8 else "bf16")
+                              recv_dtype="fp8_e4m3" if fp8 else "bf16", fused_expert_combine=args.fused_layer)
     on_gpu = args.transport != "cpu"
     with HostStagedEPBuffer(dist.group.WORLD, tmax, hidden, topk, experts, config) as buffer:
         layer = MoELayer(buffer, inter, seed=5)
@@ -215,6 +215,7 @@ def main():
     parser.add_argument("--timeout-ms", type=int, default=5000)
     parser.add_argument("--numa-mode", default="direct")
     parser.add_argument("--fp8-layer", action="store_true")
+    parser.add_argument("--fused-layer", action="store_true", help="MoE layer with the fused down-projection + combine")
     parser.add_argument("--small", action="store_true")
     parser.add_argument("--fp32", action="store_true")
     args = parser.parse_args()
