@@ -31,10 +31,13 @@ class MoELayer:
             multi-rank run and a single-process dense reference agree on every expert's weights).
         with_router: also create a router matrix ``[num_experts, hidden]``; without it ``forward`` needs
             ``topk_idx`` / ``topk_weights`` from the caller.
+        weights: ``(w_gate_up [local experts, 2*intermediate, hidden], w_down [local experts, hidden, intermediate])``
+            already on the device, used instead of drawing new ones (several layers or buffers sharing one set).
     """
 
     def __init__(self, buffer: Any, intermediate: int, *, seed: int = 0, with_router: bool = True,
-                 dtype: torch.dtype = torch.bfloat16, weight_std: float = 0.02) -> None:
+                 dtype: torch.dtype = torch.bfloat16, weight_std: float = 0.02,
+                 weights: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
         self.buffer = buffer
         self.hidden = buffer.hidden
         self.intermediate = intermediate
@@ -45,13 +48,19 @@ class MoELayer:
         self.device = torch.device("cuda", buffer.device) if buffer.on_gpu else torch.device("cpu")
         self.dtype = dtype if buffer.on_gpu else torch.float32
         first = self.rank * self.local_experts
-        w13, w2 = [], []
-        for e in range(first, first + self.local_experts):
-            g = torch.Generator().manual_seed(seed * 1_000_003 + e)
-            w13.append(torch.randn(2 * intermediate, self.hidden, generator=g) * weight_std)
-            w2.append(torch.randn(self.hidden, intermediate, generator=g) * weight_std)
-        self.w_gate_up = torch.stack(w13).to(self.dtype).to(self.device).contiguous()
-        self.w_down = torch.stack(w2).to(self.dtype).to(self.device).contiguous()
+        if weights is not None:
+            self.w_gate_up, self.w_down = weights
+            if tuple(self.w_gate_up.shape) != (self.local_experts, 2 * intermediate, self.hidden) or \
+                    tuple(self.w_down.shape) != (self.local_experts, self.hidden, intermediate):
+                raise ValueError("weights do not have the layer's shapes")
+        else:
+            w13, w2 = [], []
+            for e in range(first, first + self.local_experts):
+                g = torch.Generator().manual_seed(seed * 1_000_003 + e)
+                w13.append(torch.randn(2 * intermediate, self.hidden, generator=g) * weight_std)
+                w2.append(torch.randn(self.hidden, intermediate, generator=g) * weight_std)
+            self.w_gate_up = torch.stack(w13).to(self.dtype).to(self.device).contiguous()
+            self.w_down = torch.stack(w2).to(self.dtype).to(self.device).contiguous()
         self.router = None
         if with_router:
             g = torch.Generator().manual_seed(seed * 1_000_003 + 999_983)
@@ -61,7 +70,7 @@ class MoELayer:
         self.fp8 = bool(buffer.on_gpu and getattr(buffer.config, "recv_dtype", "bf16") == "fp8_e4m3")
         self.w_gate_up_fp8 = self.w_gate_up_scales = None
         if self.fp8:
-            codes, scales = quantize_weights_fp8(self.w_gate_up.float().cpu())
+            codes, scales = quantize_weights_fp8(self.w_gate_up.float())
             self.w_gate_up_fp8, self.w_gate_up_scales = codes.to(self.device), scales.to(self.device)
         self.fused_combine = bool(buffer.on_gpu and getattr(buffer.config, "fused_expert_combine", False))
         self._hidden_rows: Optional[torch.Tensor] = None

@@ -21,10 +21,15 @@ import torch
 def quantize_weights_fp8(w: torch.Tensor):
     """Per-output-channel E4M3 quantisation of expert weights ``[experts, n, k]``: returns ``(codes float8_e4m3fn,
     scales float32 [experts, n])`` with ``w ~= codes * scales[..., None]`` (scale = amax / 448, 1 for zero rows)."""
-    amax = w.float().abs().amax(dim=2)
-    scales = torch.where(amax == 0, torch.ones_like(amax), amax / 448.0)
-    codes = (w.float() / scales.unsqueeze(2)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
-    return codes.contiguous(), scales.contiguous()
+    codes = torch.empty(w.shape, dtype=torch.float8_e4m3fn, device=w.device)
+    scales = torch.empty(w.shape[:2], dtype=torch.float32, device=w.device)
+    for first in range(0, w.shape[0], 8):  # a few experts at a time: the FP32 temporaries stay small
+        part = w[first:first + 8].float()
+        amax = part.abs().amax(dim=2)
+        scale = torch.where(amax == 0, torch.ones_like(amax), amax / 448.0)
+        scales[first:first + 8] = scale
+        codes[first:first + 8] = (part / scale.unsqueeze(2)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return codes, scales
 
 
 def grouped_gemm_reference(a: torch.Tensor, w: torch.Tensor, expert_offsets: torch.Tensor, expert_counts: torch.Tensor,
