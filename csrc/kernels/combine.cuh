@@ -37,12 +37,40 @@ __device__ __forceinline__ uint4 pack_chunk(const float (&acc)[8]) {
     return out;
 }
 
+// dst[q] = bf16( w * src[q] ): the single-row case of reduce_rows (the common one when a token reaches a rank
+// through one expert only), eight 16-byte chunks per lane in flight instead of four.
+__device__ __noinline__ void scale_row(const std::uint8_t* src, float w, std::uint8_t* dst, int chunks) {
+    const unsigned lane = ptx::lane_id();
+    for (int q0 = 0; q0 < chunks; q0 += 256) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int q = q0 + u * 32 + lane;
+            if (q < chunks) v[u] = ptx::ld_v4(src + static_cast<std::size_t>(q) * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int q = q0 + u * 32 + lane;
+            if (q < chunks) {
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                accumulate_chunk(acc, v[u], w);
+                *reinterpret_cast<uint4*>(dst + static_cast<std::size_t>(q) * 16) = pack_chunk(acc);
+            }
+        }
+    }
+}
+
 // dst[q] = bf16( sum_i w_i * rows_i[q] ) over `n` rows, FP32 accumulation in row order.  Row i lives at
 // base + index(lane i) * stride, its weight in lane i.  `dst` is a generic pointer (shared or global).
 // Rows are taken two at a time, four 16-byte chunks per lane each: 8 loads in flight per lane.
 __device__ __forceinline__ void reduce_rows(const std::uint8_t* base, std::size_t stride, int index_of_lane,
                                             float weight_of_lane, int n, std::uint8_t* dst, int chunks) {
     const unsigned lane = ptx::lane_id();
+    if (n == 1) {
+        scale_row(base + static_cast<std::size_t>(__shfl_sync(0xffffffffu, index_of_lane, 0)) * stride,
+                  __shfl_sync(0xffffffffu, weight_of_lane, 0), dst, chunks);
+        return;
+    }
     for (int q0 = 0; q0 < chunks; q0 += 128) {
         float acc[4][8];
 #pragma unroll

@@ -66,9 +66,6 @@ class HostStagedConfig:
         automatically when ``hidden * 2`` is not a multiple of 16).
     tx_warps / rx_warps: warps per channel CTA in the send and the
         receive/expand role.
-    virtual_ranks: number of EP ranks emulated inside this one process on one
-        GPU (one cooperative launch covers all of them).  Used by tests and by
-        single-GPU development; 1 in production.
     enable_combine: allocate the combine staging area.
     recv_dtype: ``"bf16"`` (rows are decoded at the receiver, local rows bypass the wire format) or
         ``"fp8_e4m3"`` (needs the FP8 wire): every row -- local ones too -- stays E4M3 at the receiver,
@@ -107,7 +104,6 @@ class HostStagedConfig:
     copy_engine: str = "tma"
     tx_warps: int = 2
     rx_warps: int = 10
-    virtual_ranks: int = 1
     enable_combine: bool = True
     recv_dtype: str = "bf16"
     fused_expert_combine: bool = False
@@ -165,8 +161,6 @@ class HostStagedConfig:
             raise ValueError("tx_warps must be an integer in [1, 8]")
         if not isinstance(self.rx_warps, int) or not 1 <= self.rx_warps <= 12:
             raise ValueError("rx_warps must be an integer in [1, 12]")
-        if not isinstance(self.virtual_ranks, int) or not 1 <= self.virtual_ranks <= MAX_RANKS:
-            raise ValueError(f"virtual_ranks must be an integer in [1, {MAX_RANKS}]")
         if self.numa_mode == "relay" and self.transport not in ("host_staged", "auto"):
             raise ValueError("numa_mode='relay' needs transport='host_staged'")
         if self.fused_expert_combine and self.numa_mode == "relay":

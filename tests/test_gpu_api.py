@@ -207,3 +207,35 @@ def test_combine_weighted_and_unique(world1):
         hit = ((cpu[1] >= 0).any(dim=1, keepdim=True)).float()
         assert torch.allclose(combined.cpu().float(), cpu[0].float() * hit, rtol=1e-2, atol=1e-2)
         buffer.check_errors()
+
+
+def test_large_and_small_buffers_alive_together(world1):
+    """Two buffers with very different shared-memory needs share the kernels' opt-in attribute, which is only
+    ever raised (reference: tests/test_f2_buffers.py): dispatches interleave and stay exact on both, whichever
+    was built first, and closing one leaves the other working."""
+    small_cfg = HostStagedConfig(channels=4, timeout_ms=3000, tx_warps=1, rx_warps=1)
+    large_cfg = HostStagedConfig(channels=4, timeout_ms=3000, tx_warps=2, rx_warps=10)
+    small = HostStagedEPBuffer(None, 32, 256, TOPK, EXPERTS, small_cfg)
+    large = HostStagedEPBuffer(None, 32, 8192, TOPK, EXPERTS, large_cfg)
+    assert large.runtime.shared_bytes() > small.runtime.shared_bytes()
+    try:
+        for step in range(6):
+            for buffer, hidden in ((small, 256), (large, 8192)) if step % 2 else ((large, 8192), (small, 256)):
+                cpu = make_inputs(0, 1, 32 - step, hidden, EXPERTS, TOPK, "random", seed=step)
+                out = buffer.dispatch(*(t.cuda() for t in cpu), do_expand=True)
+                out[4].current_stream_wait()
+                torch.cuda.synchronize()
+                expected = reference.dispatch_reference([cpu], 0, EXPERTS, 32, do_expand=True)
+                assert not reference.compare_dispatch(dict(out[3]._result), expected, do_expand=True, do_zero_padding=False)
+                del out
+        large.close()
+        cpu = make_inputs(0, 1, 32, 256, EXPERTS, TOPK, "random", seed=99)
+        out = small.dispatch(*(t.cuda() for t in cpu), do_expand=True)
+        torch.cuda.synchronize()
+        expected = reference.dispatch_reference([cpu], 0, EXPERTS, 32, do_expand=True)
+        assert not reference.compare_dispatch(dict(out[3]._result), expected, do_expand=True, do_zero_padding=False)
+        del out
+        small.check_errors()
+    finally:
+        small.close()
+        large.close()
