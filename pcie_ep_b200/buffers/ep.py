@@ -455,8 +455,6 @@ class HostStagedEPBuffer:
         """
         with self._lock:
             self._check_live()
-            if not self.on_gpu:
-                raise NotImplementedError("fused_expert_combine needs the GPU runtime")
             if not self.config.fused_expert_combine:
                 raise RuntimeError("this buffer was built with fused_expert_combine=False")
             if not isinstance(handle, HostStagedEPHandle):
@@ -465,6 +463,13 @@ class HostStagedEPBuffer:
                 raise ValueError("The handle belongs to another buffer generation")
             if not handle.do_expand:
                 raise ValueError("fused_expert_combine needs a dispatch with do_expand=True")
+            if not self.on_gpu:
+                # CPU transport: the same result in two steps (matmul per expert, then the gloo combine)
+                from ..ops.grouped_ffn import grouped_gemm
+
+                rows = grouped_gemm(hidden_rows, w_down, handle.expert_offsets, handle.expert_counts, swiglu=False)
+                combined = self.runtime.combine(rows, handle._result, True, out)
+                return combined, None, EventOverlap(None, (self, hidden_rows, handle, combined))
             if torch.cuda.is_current_stream_capturing():
                 raise NotImplementedError("fused_expert_combine cannot be issued inside a stream capture")
             compute = self._current_stream()

@@ -72,7 +72,7 @@ class MoELayer:
         if self.fp8:
             codes, scales = quantize_weights_fp8(self.w_gate_up.float())
             self.w_gate_up_fp8, self.w_gate_up_scales = codes.to(self.device), scales.to(self.device)
-        self.fused_combine = bool(buffer.on_gpu and getattr(buffer.config, "fused_expert_combine", False))
+        self.fused_combine = bool(getattr(buffer.config, "fused_expert_combine", False))
         self._hidden_rows: Optional[torch.Tensor] = None
         self._out_rows: Optional[torch.Tensor] = None
         self.gemm_status = torch.zeros(4, dtype=torch.int32, device=self.device) if buffer.on_gpu else None

@@ -33,3 +33,8 @@ def test_cpu_transport_oracle_config_world2():
 
 def test_cpu_moe_layer_world2():
     run_workers(2, "--transport", "cpu", "--suite", "moe_layer", "--hidden", "64")
+
+
+def test_cpu_moe_layer_with_fused_expert_combine_api_world2():
+    """The fused call exists on every transport; on CPU it is the two-step evaluation."""
+    run_workers(2, "--transport", "cpu", "--suite", "moe_layer", "--hidden", "64", "--fused-layer")
