@@ -52,6 +52,7 @@ def parse_args():
     p.add_argument("--engine", default="tma", choices=["tma", "vector"])
     p.add_argument("--transport", default="peer", choices=["peer", "host_staged"])
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-numa-bind", action="store_true", help="leave the process on whatever CPUs it was started on")
     return p.parse_args()
 
 
@@ -196,6 +197,10 @@ def run_ours(args, rank, world, local_rank):
     from pcie_ep_b200 import HostStagedConfig, HostStagedEPBuffer
 
     device = torch.device("cuda", local_rank)
+    # pinned input buffers and the copy-issuing thread on the GPU's own NUMA node (8 ranks share two sockets)
+    from pcie_ep_b200.utils.numa import bind_to_device_numa_node
+
+    numa_node = None if args.no_numa_bind else bind_to_device_numa_node(local_rank)
 
     def time_config(tokens, steps, warmup, want_e2e):
         channels = args.channels or default_channels(world, tokens)
@@ -311,7 +316,8 @@ def run_ours(args, rank, world, local_rank):
             torch.cuda.synchronize()
             result["e2e"] = {"value": max_over_ranks(e0.elapsed_time(e1) * 1000.0 / steps), "unit": "us/step",
                              "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-                             "how": "inputs double-buffered: a copy stream uploads step i+1 from pinned memory while step i runs; every step ends with a blocking 4-byte read of its checksum"}
+                             "how": "inputs double-buffered: a copy stream uploads step i+1 from pinned memory while step i runs; every step ends with a blocking 4-byte read of its checksum",
+                             "host_numa_node": numa_node}
             buffer.check_errors()
         buffer.close()
         return result
