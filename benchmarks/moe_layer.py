@@ -78,14 +78,16 @@ def run_variant(args, fp8, fused, weights, x, idx, w, rank, world, peak) -> None
     everyone_total = gather(total)
     everyone_stage = gather(stage)
     if rank == 0:
-        step = statistics.mean(max(r[i] for r in everyone_total) for i in range(args.iterations))
-        parts = [statistics.mean(max(r[i][k] for r in everyone_stage) for i in range(args.iterations)) for k in range(3)]
+        per_step = [max(r[i] for r in everyone_total) for i in range(args.iterations)]
+        step = statistics.median(per_step)  # median: one straggling iteration must not move the figure
+        parts = [statistics.median(max(r[i][k] for r in everyone_stage) for i in range(args.iterations)) for k in range(3)]
         rows = max(r[0][3] for r in everyone_stage)
         flops = 2.0 * rows * args.hidden * args.intermediate * (2 if fused else 3)
         tflops = flops / (parts[1] * 1e-6) / 1e12
         print(json.dumps({
             "metric": "MoE layer step us (dispatch + grouped SwiGLU FFN + combine), device, max over ranks",
-            "value": round(step, 1), "n_gpus": world, "fp8_path": bool(fp8), "fused_down_combine": bool(fused),
+            "value": round(step, 1), "statistic": "median over iterations of the max over ranks",
+            "slowest_iteration_us": round(max(per_step), 1), "n_gpus": world, "fp8_path": bool(fp8), "fused_down_combine": bool(fused),
             "tokens_per_rank": args.tokens, "dispatch_us": round(parts[0], 1),
             ("gate_up_gemm_us" if fused else "expert_ffn_us"): round(parts[1], 1),
             ("down_projection_plus_combine_us" if fused else "combine_us"): round(parts[2], 1),
