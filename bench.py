@@ -52,6 +52,7 @@ def parse_args():
     p.add_argument("--engine", default="tma", choices=["tma", "vector"])
     p.add_argument("--transport", default="peer", choices=["peer", "host_staged"])
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--combine-reduce", default="auto", choices=["auto", "separate", "inline"])
     p.add_argument("--no-numa-bind", action="store_true", help="leave the process on whatever CPUs it was started on")
     return p.parse_args()
 
@@ -206,8 +207,9 @@ def run_ours(args, rank, world, local_rank):
         channels = args.channels or default_channels(world, tokens)
         config = HostStagedConfig(channels=channels, stage=7 if args.wire != "bf16" else 6, wire_dtype=args.wire,
                                   copy_engine=args.engine, transport=args.transport, timeout_ms=20000,
-                                  output_pool_size=2, tx_warps=2, rx_warps=10)
+                                  output_pool_size=2, tx_warps=2, rx_warps=10, combine_reduce=args.combine_reduce)
         buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
+        launches_per_step = 3 if buffer.runtime.combine_is_split() else 2  # dispatch, combine (+ its owner-side sum)
         g = torch.Generator().manual_seed(1234 + rank)
         host_x = [torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16).pin_memory() for _ in range(INPUT_SETS)]
         idx_cpu, w_cpu = make_routes(tokens, EXPERTS, args.topk, rank)
@@ -264,6 +266,7 @@ def run_ours(args, rank, world, local_rank):
             "dispatch_kernel_us": max_over_ranks(kernel_us),
             "clocks": clocks,
             "channels": channels,
+            "launches_per_step": launches_per_step,
         }
         if want_e2e:
             checksum_host = torch.zeros(1, dtype=torch.float32).pin_memory()
@@ -368,7 +371,9 @@ def run_ours(args, rank, world, local_rank):
             "dispatch_kernel_us": round(headline["dispatch_kernel_us"], 2),
             "combine_us": round(value - headline["dispatch_us"], 2),
             "clocks": headline["clocks"],
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": headline["launches_per_step"] * args.steps,
+            "kernels_per_step": "dispatch_kernel, combine_kernel" + (", fused_reduce_kernel (owner-side sum of combine)"
+                                                                       if headline["launches_per_step"] == 3 else ""),
             "impl": "ours",
         }
         if "e2e" in headline:

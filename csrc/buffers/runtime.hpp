@@ -59,6 +59,7 @@ struct RuntimeOptions {
     bool enable_graph = false;
     bool enable_combine = true;
     bool enable_fused = false;
+    std::string combine_reduce = "auto";  // owner-side sum of combine: "separate" launch, "inline", or "auto" by rank count
     std::uint64_t delay_meta_ns = 0, delay_tx_ns = 0, delay_rx_ns = 0, delay_scatter_ns = 0;
 
     static RuntimeOptions parse(const py::dict& d) {
@@ -80,6 +81,7 @@ struct RuntimeOptions {
         o.enable_graph = get("enable_graph", o.enable_graph);
         o.enable_combine = get("enable_combine", o.enable_combine);
         o.enable_fused = get("fused_expert_combine", o.enable_fused);
+        o.combine_reduce = get("combine_reduce", std::string("auto"));
         o.delay_meta_ns = get("metadata_delay_ns", std::uint64_t{0});
         o.delay_tx_ns = get("tx_delay_ns", std::uint64_t{0});
         o.delay_rx_ns = get("rx_delay_ns", std::uint64_t{0});
@@ -225,9 +227,13 @@ struct PreparedDispatch {
     DispatchArgs args;
     std::shared_ptr<DispatchResult> result;
 };
+constexpr int kSplitCombineMinRanks = 4;
+
 struct PreparedCombine {
     CombineArgs args;
     at::Tensor out;
+    bool split = false;        // the owner-side sum is a second launch
+    FusedReduceArgs reduce{};  // its arguments (split only)
 };
 
 class Runtime {
@@ -303,7 +309,7 @@ class Runtime {
             pools_.push_back(std::make_shared<OutputSet>(make_output_set()));
             plans_.push_back(make_layout());
         }
-        fused_counters_ = at::zeros({2}, i64);
+        fused_counters_ = at::zeros({4}, i64);  // finished CTAs: [0] scatter GEMM, [1] fused reduction, [2] split-combine reduction
         fused_status_ = at::zeros({4}, i32);
         fused_gemm_ctas_ = grouped_gemm_ctas();
         if (options_.enable_combine) {
@@ -437,7 +443,42 @@ class Runtime {
         a.error = set.combine_error.data_ptr<int>();
         a.stats = set.combine_stats.data_ptr<std::int64_t>();
         a.profile = set.combine_profile.data_ptr<std::int64_t>();
+        p.split = combine_is_split();
+        if (p.split) {
+            a.split = 1;
+            FusedReduceArgs& r = p.reduce;
+            r.rc = a.rc;
+            r.expert_ord = nullptr;
+            r.rank_mask = a.plan_mask;
+            r.gemm_status = nullptr;
+            r.num_tokens = T;
+            r.epoch = 0;  // the combine epoch the expert-side launch has just advanced on the device
+            r.cta_done = reinterpret_cast<unsigned long long*>(fused_counters_.data_ptr<std::int64_t>()) + 2;
+            r.stage_off = lay_.cstage_off;
+            r.sig_off = lay_.csig_off;
+            r.done_off = lay_.cdone_off;
+            r.slot_stride = static_cast<std::size_t>(lay_.num_max_tokens) * lay_.crow_stride;
+            r.token_stride = static_cast<std::size_t>(lay_.crow_stride);
+            r.slots = lay_.num_ranks;
+            r.out = a.out;
+            r.error = a.error;
+        }
         return p;
+    }
+
+    // Whether combine runs its owner-side sum as a second launch.  With one or two ranks a token has at most two
+    // partial rows and the in-kernel sum (which overlaps the arrival of the rows) is the faster one.
+    bool combine_is_split() const {
+        if (rc_.vec_ok == 0 || options_.combine_reduce == "inline") return false;
+        if (options_.combine_reduce == "separate") return true;
+        return lay_.num_ranks >= kSplitCombineMinRanks;
+    }
+
+    // second launch of a split combine; `prepared` comes from prepare_combine of this runtime
+    void launch_split_reduce(PreparedCombine& prepared, cudaStream_t stream) {
+        if (!prepared.split) return;
+        prepared.reduce.launch_index = ++split_reduce_launches_;
+        cuda_check(launch_fused_reduce(prepared.reduce, 4 * fused_gemm_ctas_, stream), "combine reduce launch");
     }
 
     at::Tensor combine(const at::Tensor& y, const DispatchResult& dispatch_result, bool weighted,
@@ -450,6 +491,7 @@ class Runtime {
         cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
                                                  : at::cuda::getCurrentCUDAStream(device_).stream();
         cuda_check(launch_combine(launch, options_.channels, static_cast<std::size_t>(lay_.crow_stride), launch_stream), "combine launch");
+        launch_split_reduce(p, launch_stream);
         return p.out;
     }
 
@@ -515,10 +557,18 @@ class Runtime {
         FusedReduceArgs a{};
         a.rc = reinterpret_cast<const RankConst*>(rank_const_.data_ptr<std::uint8_t>());
         a.expert_ord = layout->expert_ord.data_ptr<int>();
+        a.rank_mask = nullptr;
         a.gemm_status = fused_status_.data_ptr<int>();
         a.num_tokens = T;
         a.epoch = fused_reduce_epoch_ + 1;
+        a.launch_index = fused_reduce_epoch_ + 1;
         a.cta_done = reinterpret_cast<unsigned long long*>(fused_counters_.data_ptr<std::int64_t>()) + 1;
+        a.stage_off = lay_.fstage_off;
+        a.sig_off = lay_.fsig_off;
+        a.done_off = lay_.fdone_off;
+        a.slot_stride = static_cast<std::size_t>(lay_.crow_stride);
+        a.token_stride = static_cast<std::size_t>(lay_.num_topk) * lay_.crow_stride;
+        a.slots = lay_.num_topk;
         a.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
         a.error = dispatch_result.set_ref().combine_error.data_ptr<int>();
         cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
@@ -708,7 +758,7 @@ class Runtime {
     std::vector<std::shared_ptr<Layout>> plans_;
     std::vector<at::Tensor> combine_pool_;
     at::Tensor fused_counters_, fused_status_;
-    std::uint64_t fused_gemm_epoch_ = 0, fused_reduce_epoch_ = 0;
+    std::uint64_t fused_gemm_epoch_ = 0, fused_reduce_epoch_ = 0, split_reduce_launches_ = 0;
     int fused_gemm_ctas_ = 0;
     int next_pool_ = 0;
     int next_combine_ = 0;
@@ -737,7 +787,7 @@ inline void launch_dispatch_group(const std::vector<std::shared_ptr<Runtime>>& r
 }
 
 inline void launch_combine_group(const std::vector<std::shared_ptr<Runtime>>& runtimes,
-                                 const std::vector<PreparedCombine>& prepared, int device) {
+                                 std::vector<PreparedCombine>& prepared, int device) {
     if (runtimes.empty() || runtimes.size() != prepared.size() || runtimes.size() > kMaxVirtualRanks)
         throw std::invalid_argument("between 1 and 8 virtual ranks per launch");
     CombineLaunch launch{};
@@ -746,6 +796,9 @@ inline void launch_combine_group(const std::vector<std::shared_ptr<Runtime>>& ru
     cuda_check(launch_combine(launch, runtimes[0]->channels(), static_cast<std::size_t>(runtimes[0]->layout().crow_stride),
                               at::cuda::getCurrentCUDAStream(device)),
                "combine launch");
+    // split combine: every rank's rows are pushed by the launch above; each rank's sum follows in stream order
+    for (std::size_t i = 0; i < runtimes.size(); ++i)
+        runtimes[i]->launch_split_reduce(prepared[i], at::cuda::getCurrentCUDAStream(device));
 }
 
 }  // namespace bep

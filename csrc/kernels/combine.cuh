@@ -131,6 +131,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
     const int num_warps = blockDim.x >> 5;
     const bool vec_ok = rc->vec_ok != 0;
     const int map_stride = 2 + 2 * K;
+    const bool split = a.split != 0;
     __shared__ int cta_flag;
     __shared__ unsigned long long stat[4];
     extern __shared__ __align__(128) unsigned char row_buffers[];  // [warps][crow_stride] (vector-capable hidden only)
@@ -235,12 +236,12 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                 if (pending_flag != nullptr) {
                     if (lane == 0) {
                         ptx::bulk_wait_all();
-                        ptx::st_release_sys(pending_flag, epoch);
+                        if (!split) ptx::st_release_sys(pending_flag, epoch);
                     }
                     pending_flag = nullptr;
                 }
                 if (warp == 0 && lane == 0 && prof[2] == 0) prof[2] = static_cast<std::int64_t>(ptx::globaltimer_ns());
-                if (t >= t1) break;
+                if (t >= t1 || split) break;
                 const unsigned mask = a.plan_mask[t];
                 if (lane < static_cast<unsigned>(P) && (mask >> lane & 1u)) {
                     const std::uint64_t* ready = reinterpret_cast<const std::uint64_t*>(my_seg + lay.cready_off) +
@@ -271,7 +272,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                 if (lane == 0) {
                     ptx::bulk_s2g(dst, my_buffer, static_cast<unsigned>(H) * 2);
                     ptx::bulk_commit();
-                    if (pending_flag != nullptr) {
+                    if (pending_flag != nullptr && !split) {
                         asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
                         ptx::st_release_sys(pending_flag, epoch);
                     }
@@ -301,7 +302,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
         }
         if (lane == 0) {
             ptx::bulk_wait_all();
-            if (pending_flag != nullptr) ptx::st_release_sys(pending_flag, epoch);
+            if (pending_flag != nullptr && !split) ptx::st_release_sys(pending_flag, epoch);
+            if (split) ptx::fence_sys();  // this warp's rows before its CTA is counted as finished
         }
     }
 
@@ -317,7 +319,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
         prof[4] = static_cast<std::int64_t>(ptx::globaltimer_ns());
         std::int64_t* cs = rc->chan_stats + static_cast<std::size_t>(C + c) * 10;  // second half: combine
         for (int i = 0; i < 3; ++i) cs[i] = static_cast<std::int64_t>(stat[i]);
-        __threadfence();
+        if (split) ptx::fence_sys(); else __threadfence();
         const unsigned long long old = atomicAdd(&rc->done_ctas[1], 1ull);
         if ((old + 1) % static_cast<unsigned long long>(C) == 0) {
             __threadfence();
@@ -326,7 +328,13 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                 for (int i = 0; i < 3; ++i) sum[i] += __ldcg(rc->chan_stats + static_cast<std::size_t>(C + c2) * 10 + i);
             for (int i = 0; i < 8; ++i) a.stats[i] = i < 3 ? sum[i] : 0;
             if (!health.failed()) {
-                for (int p = 0; p < P; ++p) ptx::st_release_sys(flag_ptr(rc->seg[p], lay.cdone_off, me), epoch);
+                if (split) {
+                    // every CTA's rows are written: tell the owners; the area is handed back by their reductions
+                    ptx::fence_sys();
+                    for (int p = 0; p < P; ++p) ptx::st_release_sys(flag_ptr(rc->seg[p], lay.csig_off, me), epoch);
+                } else {
+                    for (int p = 0; p < P; ++p) ptx::st_release_sys(flag_ptr(rc->seg[p], lay.cdone_off, me), epoch);
+                }
             }
             rc->epochs[1] = epoch;
         }

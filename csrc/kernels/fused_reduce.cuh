@@ -1,7 +1,13 @@
-// Owner-side half of the fused down-projection + combine.  The expert ranks' GEMM epilogues have written
-// one weighted BF16 row per (token, slot k) into this rank's landing area (csrc/kernels/expert_gemm.cu,
-// scatter variant) and published their epoch; this kernel waits -- bounded -- for every rank's epoch,
-// sums the K slots of every token in slot order (FP32, deterministic) and hands the area back.
+// Owner-side reduction of the combine paths.  Producers on every rank have written weighted BF16 rows into
+// this rank's landing area and published their epoch; this kernel waits -- bounded -- for every rank's
+// epoch, adds the rows of every token in slot order (FP32, deterministic) and hands the area back.
+// Two producers use it:
+//   * the fused down projection (csrc/kernels/expert_gemm.cu, scatter variant): one slot per (token, k),
+//     valid where the routing plan's expert ordinal is >= 0;
+//   * the combine kernel in split mode (csrc/kernels/combine.cuh): one slot per (token, expert rank),
+//     valid where the token's destination mask has that rank's bit.
+// Unlike the in-kernel owner side of the cooperative combine (12 warps per SM, register-bound), this is an
+// ordinary launch with 32 warps per SM and work dealt out in equal ranges, so it runs at HBM speed.
 // The reference has no combine at all (pcie_ep/buffers/ep.py:461-462).
 #pragma once
 
@@ -13,11 +19,16 @@ constexpr int kFusedReduceThreads = 256;
 
 struct FusedReduceArgs {
     const RankConst* rc;
-    const int* expert_ord;         // [Tmax][K] routing plan of this rank's own tokens: -1 = unused slot
-    const int* gemm_status;        // status word of this rank's own scatter GEMM of the same call
+    const int* expert_ord;         // [Tmax][slots] routing plan of this rank's own tokens: -1 = unused slot; or nullptr
+    const std::uint32_t* rank_mask;  // when expert_ord is null: [Tmax] destination mask, bit s = slot s is used
+    const int* gemm_status;        // status word of this rank's own scatter GEMM of the same call (or nullptr)
     int num_tokens;
-    std::uint64_t epoch;           // number of this fused call (1, 2, ...), the same on every rank
+    std::uint64_t epoch;           // epoch every producer publishes (0: read the combine epoch rc->epochs[1])
+    std::uint64_t launch_index;    // 1, 2, ...: how many launches have used `cta_done`, this one included
     unsigned long long* cta_done;  // monotonic count of finished CTAs over all launches
+    std::size_t stage_off, sig_off, done_off;   // landing area, producers' flags, "consumed" flags (segment offsets)
+    std::size_t slot_stride, token_stride;      // bytes between the slots of a token / between tokens
+    int slots;                     // rows per token: top-k or number of ranks
     __nv_bfloat16* out;            // [T, H]
     int* error;                    // [8]
 };
@@ -37,22 +48,23 @@ __device__ __forceinline__ void fused_accumulate(float (&acc)[8], const uint4& v
 __global__ void __launch_bounds__(kFusedReduceThreads, 4) fused_reduce_kernel(const FusedReduceArgs a) {
     const RankConst* rc = a.rc;
     const SegmentLayout& lay = rc->lay;
-    const int P = lay.num_ranks, K = lay.num_topk;
+    const int P = lay.num_ranks, K = a.slots;
+    const std::uint64_t epoch = a.epoch != 0 ? a.epoch : rc->epochs[1];
     __shared__ int failed;
     if (threadIdx.x == 0) failed = 0;
     __syncthreads();
     if (static_cast<int>(threadIdx.x) < P) {
         const int peer = threadIdx.x;
         Health health(rc, a.error);
-        const auto* flag = reinterpret_cast<const std::uint64_t*>(rc->seg[rc->rank] + lay.fsig_off +
+        const auto* flag = reinterpret_cast<const std::uint64_t*>(rc->seg[rc->rank] + a.sig_off +
                                                                   static_cast<std::size_t>(peer) * kFlagStride);
-        while (ptx::ld_acquire_sys(flag) < a.epoch) {
+        while (ptx::ld_acquire_sys(flag) < epoch) {
             if (health.give_up(kErrFusedSignalWait, peer, 0)) {
                 failed = 1;
                 break;
             }
         }
-    } else if (static_cast<int>(threadIdx.x) == P) {
+    } else if (static_cast<int>(threadIdx.x) == P && a.gemm_status != nullptr) {
         const int status = ptx::ld_volatile(a.gemm_status);
         if (status != 0) {
             record_error(rc, a.error, kErrFusedGemm, rc->rank, status);
@@ -73,20 +85,24 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 4) fused_reduce_kernel(co
         const long long total_warps = static_cast<long long>(gridDim.x) * warps;
         const long long me = static_cast<long long>(blockIdx.x) * warps + warp;
         const long long first = units * me / total_warps, last = units * (me + 1) / total_warps;
-        const std::uint8_t* area = rc->seg[rc->rank] + lay.fstage_off;
-        const std::size_t pitch = static_cast<std::size_t>(lay.crow_stride);
+        const std::uint8_t* area = rc->seg[rc->rank] + a.stage_off;
+        const std::size_t pitch = a.slot_stride;
         int cached_token = -1;
         unsigned valid = 0;
         for (long long u = first; u < last; ++u) {
             const int t = static_cast<int>(u / groups);
             const int c = static_cast<int>(u % groups) * 32 + lane;
             if (t != cached_token) {
-                const int ord = lane < K ? a.expert_ord[static_cast<std::size_t>(t) * K + lane] : -1;
-                valid = __ballot_sync(0xffffffffu, ord >= 0);
+                if (a.expert_ord != nullptr) {
+                    const int ord = lane < K ? a.expert_ord[static_cast<std::size_t>(t) * K + lane] : -1;
+                    valid = __ballot_sync(0xffffffffu, ord >= 0);
+                } else {
+                    valid = a.rank_mask[t];
+                }
                 cached_token = t;
             }
             if (c >= chunks) continue;
-            const std::uint8_t* rows = area + static_cast<std::size_t>(t) * K * pitch + static_cast<std::size_t>(c) * 16;
+            const std::uint8_t* rows = area + static_cast<std::size_t>(t) * a.token_stride + static_cast<std::size_t>(c) * 16;
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int k0 = 0; k0 < K; k0 += 8) {
                 uint4 v[8];
@@ -111,12 +127,12 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 4) fused_reduce_kernel(co
     if (threadIdx.x == 0) {
         ptx::fence_sys();
         const unsigned long long finished = atomicAdd(a.cta_done, 1ull) + 1ull;
-        if (finished == a.epoch * gridDim.x) {
+        if (finished == a.launch_index * gridDim.x) {
             ptx::fence_sys();
             for (int r = 0; r < P; ++r)
-                ptx::st_release_sys(reinterpret_cast<std::uint64_t*>(rc->seg[r] + lay.fdone_off +
+                ptx::st_release_sys(reinterpret_cast<std::uint64_t*>(rc->seg[r] + a.done_off +
                                                                      static_cast<std::size_t>(rc->rank) * kFlagStride),
-                                    a.epoch);
+                                    epoch);
         }
     }
 }

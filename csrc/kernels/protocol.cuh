@@ -96,6 +96,7 @@ struct SegmentLayout {
     std::size_t cstage_off;       // bytes [P][Tmax][crow_stride]
     // fused down-projection + combine: the GEMM epilogue of the expert's rank writes weighted output rows
     // straight into the token owner's slots; the owner sums its K slots per token
+    std::size_t csig_off;         // u64 [P] stride kFlagStride : combine with a separate reduction: rank r has pushed all its rows of this epoch
     std::size_t fsig_off;         // u64 [P] stride kFlagStride : written by rank r's GEMM, epoch whose rows are all here
     std::size_t fdone_off;        // u64 [P] stride kFlagStride : written by rank d's reduction, last epoch it has consumed
     std::size_t fstage_off;       // bytes [Tmax][K][crow_stride]
@@ -151,6 +152,7 @@ inline SegmentLayout make_segment_layout(int P, int C, int E, int K, int H, int 
     l.cready_off = take(with_combine ? static_cast<std::size_t>(P) * Tmax * 8 : 0);
     l.stage_off = take(static_cast<std::size_t>(P) * C * l.slots * l.row_stride);
     l.cstage_off = take(with_combine ? static_cast<std::size_t>(P) * Tmax * l.crow_stride : 0);
+    l.csig_off = take(static_cast<std::size_t>(P) * kFlagStride);
     l.fsig_off = take(static_cast<std::size_t>(P) * kFlagStride);
     l.fdone_off = take(static_cast<std::size_t>(P) * kFlagStride);
     l.fstage_off = take(with_fused ? static_cast<std::size_t>(Tmax) * K * l.crow_stride : 0);
@@ -258,6 +260,8 @@ struct CombineArgs {
     const std::uint32_t* plan_mask;  // [Tmax] of this rank's own tokens
     int num_tokens;               // this rank's own token count at dispatch
     int weighted;                 // apply dispatch-time weights (expanded layout)
+    int split;                    // != 0: only the expert side runs here (rows pushed, csig published by the last CTA);
+                                  // the owner-side sum is a separate, fully occupied kernel (fused_reduce.cuh)
     __nv_bfloat16* out;           // [T, H]
     int* error;                   // [8]
     std::int64_t* stats;          // [8]

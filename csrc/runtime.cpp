@@ -146,6 +146,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              py::arg("dispatch_result"), py::arg("stream") = 0)
         .def("fused_reduce", &Runtime::fused_reduce, py::arg("dispatch_result"), py::arg("out"), py::arg("stream") = 0)
         .def("fused_status", &Runtime::fused_status)
+        .def("combine_is_split", &Runtime::combine_is_split)
         .def("pool_debug", &Runtime::pool_debug)
         .def("set_test_delays", &Runtime::set_test_delays)
         .def("set_test_prefix_delay_ns", &Runtime::set_test_prefix_delay_ns)

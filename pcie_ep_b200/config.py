@@ -75,6 +75,11 @@ class HostStagedConfig:
         down-projection GEMM's epilogue then writes each weighted output row straight into the token
         owner's memory and a short reduction sums the K slots (expanded dispatches only, ``hidden`` a
         multiple of 256).
+    combine_reduce: ``"separate"`` runs the owner-side sum of ``combine`` as a second, fully occupied
+        kernel after the cooperative kernel that reduces and pushes the expert-side rows; ``"inline"``
+        does both in the one cooperative kernel, which starts adding rows as they arrive but is
+        register-bound; ``"auto"`` (default) takes ``"separate"`` from four ranks up.  Hidden sizes whose
+        rows are not 16-byte multiples always take ``"inline"``.
     """
 
     payload_slots: int = 0
@@ -107,6 +112,7 @@ class HostStagedConfig:
     enable_combine: bool = True
     recv_dtype: str = "bf16"
     fused_expert_combine: bool = False
+    combine_reduce: str = "auto"
 
     def __post_init__(self) -> None:
         for name in ("timeout_ms", "replica_slots"):
@@ -163,6 +169,8 @@ class HostStagedConfig:
             raise ValueError("rx_warps must be an integer in [1, 12]")
         if self.numa_mode == "relay" and self.transport not in ("host_staged", "auto"):
             raise ValueError("numa_mode='relay' needs transport='host_staged'")
+        if self.combine_reduce not in ("auto", "separate", "inline"):
+            raise ValueError("combine_reduce must be 'auto', 'separate' or 'inline'")
         if self.fused_expert_combine and self.numa_mode == "relay":
             raise ValueError("fused_expert_combine writes peer memory directly; it cannot be combined with numa_mode='relay'")
         if self.descriptor_slots not in (0, 256, self.payload_slots):

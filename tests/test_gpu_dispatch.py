@@ -147,3 +147,41 @@ def test_pool_exhaustion_and_release(ext):
         torch.cuda.synchronize()
         assert all(int(r["error"][0]) == 0 for r in third)
         del second, third
+
+
+@pytest.mark.parametrize("mode", ["separate", "inline"])
+def test_combine_modes_on_emulated_ranks(ext, mode):
+    """Owner-side sum as a second launch ("separate") or inside the cooperative kernel ("inline"): both return
+    x * (sum of the token's weights) for identity experts, over epochs with changing routes, unequal token
+    counts, unused slots and the unique layout."""
+    from pcie_ep_b200.parallel.virtual import VirtualEPGroup
+
+    world, experts, topk, hidden, tmax = 4, 16, 4, 512, 48
+    config = HostStagedConfig(channels=4, timeout_ms=3000, tx_warps=2, rx_warps=3, combine_reduce=mode)
+    with VirtualEPGroup(world, tmax, hidden, topk, experts, config) as group:
+        for epoch in range(5):
+            tokens = [tmax - 5 * r - epoch for r in range(world)]
+            if epoch == 3:
+                tokens[1] = 0
+            expand = epoch != 2
+            pattern = "partial" if epoch == 1 else "random"
+            cpu = [make_inputs(r, world, tokens[r], hidden, experts, topk, pattern, seed=10 + epoch) for r in range(world)]
+            dev = [tuple(t.cuda() for t in inp) for inp in cpu]
+            results = group.dispatch([d[0] for d in dev], [d[1] for d in dev], [d[2] for d in dev], do_expand=expand)
+            outs = group.combine([r["recv_x"] for r in results], results, weighted=expand)
+            torch.cuda.synchronize()
+            local = experts // world
+            for r in range(world):
+                assert results[r]["combine_error"].tolist()[0] == 0, results[r]["combine_error"].tolist()
+                x, idx, w = cpu[r]
+                if expand:
+                    scale = (w * (idx >= 0)).sum(dim=1, keepdim=True)
+                else:  # unique layout, unweighted: one copy per destination rank
+                    ranks = torch.where(idx >= 0, idx // local, torch.full_like(idx, -1))
+                    scale = torch.stack([(ranks == d).any(dim=1) for d in range(world)], dim=1).sum(dim=1, keepdim=True).float()
+                want = x.float() * scale
+                got = outs[r].cpu().float()
+                assert got.shape == want.shape
+                assert torch.allclose(got, want, rtol=2e-2, atol=2e-2), (mode, epoch, r, (got - want).abs().max())
+            del results, outs
+        assert all(int(rt.sticky_error()[0]) == 0 for rt in group.runtimes)
