@@ -427,6 +427,57 @@ def run_reference(args, rank, world, local_rank):
         clocks = sampler.stop()
         buffer.check_errors()
         value = max_over_ranks(start.elapsed_time(end) * 1000.0 / args.steps)
+        e2e = None
+        if not args.no_e2e:
+            # the same serving loop as the other arm around the reference's dispatch: pinned host inputs uploaded
+            # every step by a copy stream (double-buffered), a blocking device->host read of every step's result
+            host_x = [x.cpu().pin_memory() for x in xs]
+            host_idx, host_w = idx_cpu.pin_memory(), w_cpu.pin_memory()
+            checksum_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+            h2d = host_x[0].numel() * 2 + host_idx.numel() * 8 + host_w.numel() * 4
+            copy_stream = torch.cuda.Stream()
+            stages = [(torch.empty_like(xs[0]), torch.empty_like(idx), torch.empty_like(w)) for _ in range(2)]
+            copied = [torch.cuda.Event() for _ in range(2)]
+            consumed = [torch.cuda.Event() for _ in range(2)]
+
+            def upload(i):
+                slot = i % 2
+                with torch.cuda.stream(copy_stream):
+                    copy_stream.wait_event(consumed[slot])
+                    stages[slot][0].copy_(host_x[i % INPUT_SETS], non_blocking=True)
+                    stages[slot][1].copy_(host_idx, non_blocking=True)
+                    stages[slot][2].copy_(host_w, non_blocking=True)
+                    copied[slot].record(copy_stream)
+
+            def e2e_loop(count):
+                compute = torch.cuda.current_stream()
+                for slot in range(2):
+                    consumed[slot].record(compute)
+                upload(0)
+                for i in range(count):
+                    slot = i % 2
+                    if i + 1 < count:
+                        upload(i + 1)
+                    compute.wait_event(copied[slot])
+                    sx, si, sw = stages[slot]
+                    res = buffer.dispatch(sx, si, sw, do_expand=True)
+                    consumed[slot].record(compute)
+                    checksum_host.copy_(res[0][:tokens, :8].float().sum().reshape(1), non_blocking=True)
+                    compute.synchronize()
+                    del res
+
+            e2e_loop(min(3, args.warmup))
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            e2e_loop(args.steps)
+            e1.record()
+            torch.cuda.synchronize()
+            buffer.check_errors()
+            e2e = {"value": max_over_ranks(e0.elapsed_time(e1) * 1000.0 / args.steps), "unit": "us/step",
+                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                   "how": "same double-buffered upload loop as the other arm around the reference's dispatch (it has no combine)"}
         buffer.close()
     except Exception as exc:  # noqa: BLE001 - reported as unavailable
         reason = f"{type(exc).__name__}: {str(exc).splitlines()[0][:200] if str(exc) else ''}"
@@ -451,6 +502,7 @@ def run_reference(args, rank, world, local_rank):
                        "global_batch": args.tokens * world, "seq_len": 1, "parallelism": f"ep{world}",
                        "transport": "host_staged (reference default config)"},
             "clocks": clocks, "gpu_launches": 8 * args.steps,
+            **({"e2e": e2e} if e2e is not None else {}),
         }), flush=True)
 
 

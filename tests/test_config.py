@@ -37,6 +37,7 @@ def test_defaults_are_valid_and_frozen():
     (dict(tx_warps=0), ValueError),
     (dict(rx_warps=13), ValueError),
     (dict(fused_expert_combine=True, stage=8, numa_mode="relay", transport="host_staged"), ValueError),
+    (dict(combine_reduce="sometimes"), ValueError),
     (dict(stage=8, numa_mode="relay", transport="peer"), ValueError),
     (dict(payload_slots=4, descriptor_slots=5), ValueError),
     (dict(recv_dtype="fp8_e4m3"), ValueError),                    # needs the FP8 wire
