@@ -199,9 +199,19 @@ def run_ours(args, rank, world, local_rank):
 
     device = torch.device("cuda", local_rank)
     # pinned input buffers and the copy-issuing thread on the GPU's own NUMA node (8 ranks share two sockets)
-    from pcie_ep_b200.utils.numa import bind_to_device_numa_node
+    from pcie_ep_b200.utils.numa import bind_to_device_numa_node, bind_to_fastest_upload_node
 
     numa_node = None if args.no_numa_bind else bind_to_device_numa_node(local_rank)
+    if numa_node is None and not args.no_numa_bind and not args.no_e2e:
+        # the platform does not name the GPU's node: measure it, one rank at a time
+        torch.cuda.set_device(device)
+        for turn in range(world):
+            if turn == rank:
+                try:
+                    numa_node = bind_to_fastest_upload_node(local_rank)
+                except Exception as exc:  # noqa: BLE001 - placement is an optimisation, never a failure
+                    numa_node = {"node": None, "error": f"{type(exc).__name__}: {exc}"[:160]}
+            dist.barrier()
 
     def time_config(tokens, steps, warmup, want_e2e):
         channels = args.channels or default_channels(world, tokens)

@@ -469,7 +469,7 @@ class Runtime {
     // Whether combine runs its owner-side sum as a second launch.  With one or two ranks a token has at most two
     // partial rows and the in-kernel sum (which overlaps the arrival of the rows) is the faster one.
     bool combine_is_split() const {
-        if (rc_.vec_ok == 0 || options_.combine_reduce == "inline") return false;
+        if (rc_.vec_ok == 0 || lay_.num_ranks == 1 || options_.combine_reduce == "inline") return false;
         if (options_.combine_reduce == "separate") return true;
         return lay_.num_ranks >= kSplitCombineMinRanks;
     }

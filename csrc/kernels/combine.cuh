@@ -132,6 +132,9 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
     const bool vec_ok = rc->vec_ok != 0;
     const int map_stride = 2 + 2 * K;
     const bool split = a.split != 0;
+    // one rank: the reduced row of a token is already the result -- it goes straight to `out`, nothing is
+    // staged and there is no owner-side pass
+    const bool direct = P == 1 && vec_ok;
     __shared__ int cta_flag;
     __shared__ unsigned long long stat[4];
     extern __shared__ __align__(128) unsigned char row_buffers[];  // [warps][crow_stride] (vector-capable hidden only)
@@ -226,6 +229,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                 dst = rc->seg[s] + lay.cstage_off + static_cast<std::size_t>(me) * rank_stride +
                       static_cast<std::size_t>(token) * lay.crow_stride;
                 flag = reinterpret_cast<std::uint64_t*>(rc->seg[s] + lay.cready_off) + static_cast<std::size_t>(me) * Tmax + token;
+                if (direct) dst = reinterpret_cast<std::uint8_t*>(a.out + static_cast<std::size_t>(token) * H);
                 if (lane == 0) {
                     ++st_rows;
                     if (s != me) ++st_remote;
@@ -236,11 +240,20 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                 if (pending_flag != nullptr) {
                     if (lane == 0) {
                         ptx::bulk_wait_all();
-                        if (!split) ptx::st_release_sys(pending_flag, epoch);
+                        if (!split && !direct) ptx::st_release_sys(pending_flag, epoch);
                     }
                     pending_flag = nullptr;
                 }
                 if (warp == 0 && lane == 0 && prof[2] == 0) prof[2] = static_cast<std::int64_t>(ptx::globaltimer_ns());
+                if (direct) {
+                    // tokens that were routed nowhere get no row from the expert side: their result is zero
+                    for (int tz = t0 + w; tz < t1; tz += num_warps) {
+                        if (a.plan_mask[tz] != 0) continue;
+                        uint4* row = reinterpret_cast<uint4*>(a.out + static_cast<std::size_t>(tz) * H);
+                        for (int q = lane; q < H / 8; q += 32) row[q] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    break;
+                }
                 if (t >= t1 || split) break;
                 const unsigned mask = a.plan_mask[t];
                 if (lane < static_cast<unsigned>(P) && (mask >> lane & 1u)) {
@@ -272,7 +285,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                 if (lane == 0) {
                     ptx::bulk_s2g(dst, my_buffer, static_cast<unsigned>(H) * 2);
                     ptx::bulk_commit();
-                    if (pending_flag != nullptr && !split) {
+                    if (pending_flag != nullptr && !split && !direct) {
                         asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
                         ptx::st_release_sys(pending_flag, epoch);
                     }
@@ -302,7 +315,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
         }
         if (lane == 0) {
             ptx::bulk_wait_all();
-            if (pending_flag != nullptr && !split) ptx::st_release_sys(pending_flag, epoch);
+            if (pending_flag != nullptr && !split && !direct) ptx::st_release_sys(pending_flag, epoch);
             if (split) ptx::fence_sys();  // this warp's rows before its CTA is counted as finished
         }
     }

@@ -206,6 +206,17 @@ def test_combine_weighted_and_unique(world1):
         torch.cuda.synchronize()
         hit = ((cpu[1] >= 0).any(dim=1, keepdim=True)).float()
         assert torch.allclose(combined.cpu().float(), cpu[0].float() * hit, rtol=1e-2, atol=1e-2)
+        del recv_x, handle, combined
+        # tokens that are routed nowhere come back as zero rows, also into a caller's dirty output tensor
+        idx2 = idx.clone()
+        idx2[::2] = -1
+        recv_x, _, _, handle, _ = buffer.dispatch(x, idx2, w, do_expand=True)
+        out = torch.full_like(x, 7.0)
+        buffer.combine(recv_x, handle, out=out)
+        torch.cuda.synchronize()
+        want3 = cpu[0].float() * (cpu[2] * (idx2.cpu() >= 0)).sum(dim=1, keepdim=True)
+        assert torch.allclose(out.cpu().float(), want3, rtol=2e-2, atol=2e-2)
+        assert float(out[::2].abs().max()) == 0.0
         buffer.check_errors()
 
 
