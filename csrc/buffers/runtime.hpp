@@ -227,7 +227,7 @@ struct PreparedDispatch {
     DispatchArgs args;
     std::shared_ptr<DispatchResult> result;
 };
-constexpr int kSplitCombineMinRanks = 4;
+constexpr int kSplitCombineMinRanks = 2;
 
 struct PreparedCombine {
     CombineArgs args;
@@ -466,8 +466,8 @@ class Runtime {
         return p;
     }
 
-    // Whether combine runs its owner-side sum as a second launch.  With one or two ranks a token has at most two
-    // partial rows and the in-kernel sum (which overlaps the arrival of the rows) is the faster one.
+    // Whether combine runs its owner-side sum as a second launch: by default whenever there is more than one rank
+    // (a single rank writes its reduced rows straight to the output and has no owner-side pass at all).
     bool combine_is_split() const {
         if (rc_.vec_ok == 0 || lay_.num_ranks == 1 || options_.combine_reduce == "inline") return false;
         if (options_.combine_reduce == "separate") return true;

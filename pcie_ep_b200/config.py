@@ -78,7 +78,7 @@ class HostStagedConfig:
     combine_reduce: ``"separate"`` runs the owner-side sum of ``combine`` as a second, fully occupied
         kernel after the cooperative kernel that reduces and pushes the expert-side rows; ``"inline"``
         does both in the one cooperative kernel, which starts adding rows as they arrive but is
-        register-bound; ``"auto"`` (default) takes ``"separate"`` from four ranks up.  Hidden sizes whose
+        register-bound; ``"auto"`` (default) takes ``"separate"`` whenever there is more than one rank.  Hidden sizes whose
         rows are not 16-byte multiples always take ``"inline"``.
     """
 

@@ -81,3 +81,16 @@ def test_moe_layer_fused_down_projection_and_combine_multi_gpu(world):
 def test_moe_layer_fused_with_fp8_dispatch_two_gpus():
     _need(2)
     run_workers(2, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256", "--fp8-layer", "--fused-layer")
+
+
+@pytest.mark.parametrize("world,mode", [(2, "inline"), (2, "separate"), (4, "inline"), (8, "inline")])
+def test_combine_owner_side_modes_across_processes(world, mode):
+    """Both owner-side modes of combine (auto picks separate with more than one rank, so the other suites cover
+    that one at every size): full correctness suite, one process per GPU, flags crossing NVLink."""
+    _need(world)
+    run_workers(world, "--transport", "peer", "--suite", "correctness", "--hidden", "256", "--combine-reduce", mode)
+
+
+def test_moe_layer_with_separate_combine_reduction_two_gpus():
+    _need(2)
+    run_workers(2, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256", "--combine-reduce", "separate")

@@ -103,7 +103,7 @@ def suite_correctness(args, rank, world, device):
     config = HostStagedConfig(channels=args.channels, timeout_ms=args.timeout_ms, transport=args.transport,
                               tx_warps=2, rx_warps=3, payload_slots=args.payload_slots,
                               descriptor_slots=args.payload_slots, stage=8 if relay else 6, numa_mode=args.numa_mode,
-                              relay_workers_per_numa=2 if relay else 1)
+                              relay_workers_per_numa=2 if relay else 1, combine_reduce=args.combine_reduce)
     with HostStagedEPBuffer(dist.group.WORLD, tmax, hidden, topk, experts, config) as buffer:
         cases = [dict(pattern=p, tokens=17, expand=e, alignment=1)
                  for p in ["random", "local", "multicast", "hotspot", "partial", "none"] for e in (False, True)]
@@ -154,7 +154,8 @@ def suite_moe_layer(args, rank, world, device):
     fp8 = args.fp8_layer
     config = HostStagedConfig(channels=args.channels, transport=args.transport, timeout_ms=args.timeout_ms,
                               tx_warps=2, rx_warps=3, stage=7 if fp8 else 6, wire_dtype="fp8_e4m3" if fp8 else "bf16",
-                              recv_dtype="fp8_e4m3" if fp8 else "bf16", fused_expert_combine=args.fused_layer)
+                              recv_dtype="fp8_e4m3" if fp8 else "bf16", fused_expert_combine=args.fused_layer,
+                              combine_reduce=args.combine_reduce)
     on_gpu = args.transport != "cpu"
     with HostStagedEPBuffer(dist.group.WORLD, tmax, hidden, topk, experts, config) as buffer:
         layer = MoELayer(buffer, inter, seed=5)
@@ -216,6 +217,7 @@ def main():
     parser.add_argument("--numa-mode", default="direct")
     parser.add_argument("--fp8-layer", action="store_true")
     parser.add_argument("--fused-layer", action="store_true", help="MoE layer with the fused down-projection + combine")
+    parser.add_argument("--combine-reduce", default="auto", choices=["auto", "separate", "inline"])
     parser.add_argument("--small", action="store_true")
     parser.add_argument("--fp32", action="store_true")
     args = parser.parse_args()
