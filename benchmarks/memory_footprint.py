@@ -21,10 +21,10 @@ sys.path.insert(0, str(ROOT))
 
 
 def footprint(ranks: int, tokens: int, hidden: int, topk: int, experts: int, channels: int, payload_slots: int,
-              pools: int, graph: bool, combine: bool, relay: bool) -> dict:
+              pools: int, graph: bool, combine: bool, relay: bool, fused: bool = False) -> dict:
     from pcie_ep_b200 import _C
 
-    layout = _C.segment_layout(ranks, channels, experts, topk, hidden, tokens, payload_slots, combine)
+    layout = _C.segment_layout(ranks, channels, experts, topk, hidden, tokens, payload_slots, combine, fused)
     local = experts // ranks
     expanded = ranks * tokens * min(topk, local) + local * 255
     unique = ranks * tokens
@@ -39,6 +39,7 @@ def footprint(ranks: int, tokens: int, hidden: int, topk: int, experts: int, cha
         "segment_bytes": segment,
         "segment_staging_bytes": ranks * channels * int(layout["slots"]) * int(layout["row_stride"]),
         "segment_combine_bytes": ranks * tokens * int(layout["crow_stride"]) if combine else 0,
+        "segment_fused_landing_bytes": tokens * topk * int(layout["crow_stride"]) if fused else 0,
         "outboxes_bytes": segment * (ranks - 1) if relay else 0,
         "result_pools_bytes": per_pool * sets,
         "plan_pool_bytes": plan * sets,
@@ -65,9 +66,10 @@ def main() -> None:
     parser.add_argument("--graph", action="store_true")
     parser.add_argument("--no-combine", dest="combine", action="store_false")
     parser.add_argument("--relay", action="store_true")
+    parser.add_argument("--fused", action="store_true", help="with the landing area of fused_expert_combine")
     args = parser.parse_args()
     result = footprint(args.ranks, args.tokens, args.hidden, args.topk, args.experts, args.channels, args.payload_slots,
-                       args.pools, args.graph, args.combine, args.relay)
+                       args.pools, args.graph, args.combine, args.relay, args.fused)
     result["GiB"] = {k[:-6]: round(v / 2**30, 3) for k, v in result.items() if k.endswith("_bytes")}
     print(json.dumps(result, indent=2))
 
