@@ -87,6 +87,39 @@ def make_routes(tokens, experts, topk, rank, seed=20261024):
     return idx.contiguous(), weights.contiguous()
 
 
+def roofline(idx, world, rank, tokens, topk, experts):
+    """Lower bounds for one rank's dispatch and combine: the slower of its HBM traffic at the measured copy rate and
+    its NVLink egress at the measured peer-copy rate (770 GB/s per direction).  Rows on the wire are the staged row
+    (payload + metadata, 128-byte aligned) for dispatch and one BF16 row for combine."""
+    local = experts // world
+    ranks_hit = (idx // local)
+    sent = 0
+    for d in range(world):
+        if d != rank:
+            sent += int((ranks_hit == d).any(dim=1).sum())
+    received = sent  # uniform routing: ingress equals egress on average
+    expanded = tokens * topk  # rows this rank's experts receive, on average
+    row_wire = ((HIDDEN * 2 + 16 + 12 * topk + 127) // 128) * 128
+    row = HIDDEN * 2
+    hbm = 6548.0e9
+    try:
+        hbm = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["hbm_gbs"]) * 1e9
+    except Exception:  # noqa: BLE001
+        pass
+    nvlink = 770.0e9
+    dispatch_hbm = tokens * row + 2 * received * row_wire + expanded * row
+    combine_hbm = expanded * row + 2 * received * row + tokens * row
+    out = {}
+    for name, hbm_bytes, wire_bytes in (("dispatch", dispatch_hbm, sent * row_wire), ("combine", combine_hbm, sent * row)):
+        t_hbm, t_link = hbm_bytes / hbm * 1e6, wire_bytes / nvlink * 1e6
+        out[name + "_us"] = round(max(t_hbm, t_link), 1)
+        out[name + "_bound"] = "nvlink" if t_link > t_hbm else "hbm"
+    out["model"] = ("per rank: max(HBM bytes / measured copy rate, NVLink egress bytes / 770 GB/s); dispatch HBM = x read + staged "
+                    "rows written and read + expanded rows written, combine HBM = expert rows read + partial rows written and "
+                    "read + output written")
+    return out
+
+
 class ClockSampler:
     """SM clock and throttle reasons sampled every few milliseconds by a thread while the GPU works.
 
@@ -277,6 +310,7 @@ def run_ours(args, rank, world, local_rank):
             "clocks": clocks,
             "channels": channels,
             "launches_per_step": launches_per_step,
+            "roofline": roofline(idx_cpu, world, rank, tokens, args.topk, EXPERTS),
         }
         if want_e2e:
             checksum_host = torch.zeros(1, dtype=torch.float32).pin_memory()
@@ -381,6 +415,9 @@ def run_ours(args, rank, world, local_rank):
             "dispatch_kernel_us": round(headline["dispatch_kernel_us"], 2),
             "combine_us": round(value - headline["dispatch_us"], 2),
             "clocks": headline["clocks"],
+            "roofline": dict(headline["roofline"],
+                             dispatch_fraction=round(headline["roofline"]["dispatch_us"] / headline["dispatch_us"], 3),
+                             combine_fraction=round(headline["roofline"]["combine_us"] / max(value - headline["dispatch_us"], 1e-9), 3)),
             "gpu_launches": headline["launches_per_step"] * args.steps,
             "kernels_per_step": "dispatch_kernel, combine_kernel" + (", fused_reduce_kernel (owner-side sum of combine)"
                                                                        if headline["launches_per_step"] == 3 else ""),
