@@ -234,6 +234,8 @@ struct PreparedCombine {
     at::Tensor out;
     bool split = false;        // the owner-side sum is a second launch
     FusedReduceArgs reduce{};  // its arguments (split only)
+    bool local = false;        // single rank: one ordinary gather-reduce launch replaces the cooperative kernel
+    LocalCombineArgs local_args{};
 };
 
 class Runtime {
@@ -443,6 +445,19 @@ class Runtime {
         a.error = set.combine_error.data_ptr<int>();
         a.stats = set.combine_stats.data_ptr<std::int64_t>();
         a.profile = set.combine_profile.data_ptr<std::int64_t>();
+        p.local = lay_.num_ranks == 1 && rc_.vec_ok != 0 && options_.combine_reduce != "inline";
+        if (p.local) {
+            LocalCombineArgs& l = p.local_args;
+            l.rc = a.rc;
+            l.y = a.y;
+            l.comb_map = a.comb_map;
+            l.recv_chan_counts = a.recv_chan_counts;
+            l.plan_mask = a.plan_mask;
+            l.num_tokens = T;
+            l.weighted = a.weighted;
+            l.out = a.out;
+            l.error = a.error;
+        }
         p.split = combine_is_split();
         if (p.split) {
             a.split = 1;
@@ -485,6 +500,12 @@ class Runtime {
                        const std::optional<at::Tensor>& out_opt, std::int64_t stream) {
         c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
         PreparedCombine p = prepare_combine(y, dispatch_result, weighted, out_opt);
+        if (p.local) {
+            cudaStream_t local_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
+                                                    : at::cuda::getCurrentCUDAStream(device_).stream();
+            cuda_check(launch_local_combine(p.local_args, 3 * fused_gemm_ctas_, local_stream), "local combine launch");
+            return p.out;
+        }
         CombineLaunch launch{};
         launch.num_virtual = 1;
         launch.r[0] = p.args;
@@ -578,6 +599,7 @@ class Runtime {
         return out;
     }
     at::Tensor fused_status() const { return fused_status_; }
+    bool combine_is_local() const { return lay_.num_ranks == 1 && rc_.vec_ok != 0 && options_.combine_reduce != "inline"; }
 
     // ---- diagnostics / test hooks (reference: csrc/buffers/advanced.hpp:158-227) -------------
     py::dict pool_debug() const {

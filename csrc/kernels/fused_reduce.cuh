@@ -33,6 +33,18 @@ struct FusedReduceArgs {
     int* error;                    // [8]
 };
 
+struct LocalCombineArgs {
+    const RankConst* rc;
+    const __nv_bfloat16* y;        // expert outputs in the layout of the dispatch's recv_x
+    const int* comb_map;           // [C][slots_full][2 + 2K]: token, n, then (row, weight bits) pairs
+    const int* recv_chan_counts;   // [1][C] entries per channel
+    const std::uint32_t* plan_mask;  // [Tmax] destination mask of this rank's own tokens (0: routed nowhere)
+    int num_tokens;
+    int weighted;
+    __nv_bfloat16* out;            // [T, H]
+    int* error;                    // [8]
+};
+
 #ifdef __CUDACC__
 
 __device__ __forceinline__ void fused_accumulate(float (&acc)[8], const uint4& v) {
@@ -134,6 +146,85 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 4) fused_reduce_kernel(co
                                                                      static_cast<std::size_t>(rc->rank) * kFlagStride),
                                     epoch);
         }
+    }
+}
+
+// Single-rank combine: nothing travels, so the whole operation is one weighted gather-reduce from the expert
+// outputs into `out` -- an ordinary, fully occupied launch instead of the cooperative kernel.  Work unit =
+// (entry of the dispatch's combine map, group of 32 sixteen-byte chunks), dealt out in equal contiguous ranges.
+__global__ void __launch_bounds__(kFusedReduceThreads, 3) local_combine_kernel(const LocalCombineArgs a) {
+    const RankConst* rc = a.rc;
+    const SegmentLayout& lay = rc->lay;
+    if (ptx::ld_volatile(&rc->sticky[0]) != 0) {
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(&a.error[0], 0, kErrAlreadyAborted);
+        return;
+    }
+    const int C = lay.num_channels, Qf = lay.slots_full, K = lay.num_topk, H = lay.hidden;
+    const int map_stride = 2 + 2 * K;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warps = kFusedReduceThreads / 32;
+    const int chunks = H * 2 / 16;
+    const int groups = (chunks + 31) / 32;
+    const long long total_warps = static_cast<long long>(gridDim.x) * warps;
+    const long long me = static_cast<long long>(blockIdx.x) * warps + warp;
+    const long long units = static_cast<long long>(C) * Qf * groups;
+    const long long first = units * me / total_warps, last = units * (me + 1) / total_warps;
+    const std::uint8_t* y = reinterpret_cast<const std::uint8_t*>(a.y);
+    const std::size_t row_bytes = static_cast<std::size_t>(H) * 2;
+    long long cached_entry = -1;
+    int token = 0, n = 0, row_of_lane = 0;
+    float weight_of_lane = 1.0f;
+    for (long long u = first; u < last; ++u) {
+        const long long entry = u / groups;  // = c * Qf + j
+        const int c = static_cast<int>(entry / Qf), j = static_cast<int>(entry % Qf);
+        if (j >= a.recv_chan_counts[c]) continue;
+        if (entry != cached_entry) {
+            const int* map = a.comb_map + static_cast<std::size_t>(entry) * map_stride;
+            token = map[0];
+            n = map[1];
+            if (lane < n) {
+                row_of_lane = map[2 + 2 * lane];
+                weight_of_lane = a.weighted ? __int_as_float(map[3 + 2 * lane]) : 1.0f;
+            }
+            cached_entry = entry;
+        }
+        const int q = static_cast<int>(u % groups) * 32 + lane;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int k0 = 0; k0 < n; k0 += 8) {
+            uint4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int k = min(k0 + i, n - 1);
+                const int row = __shfl_sync(0xffffffffu, row_of_lane, k);
+                v[i] = (k0 + i < n && q < chunks) ? ptx::ld_nc_v4(y + static_cast<std::size_t>(row) * row_bytes + static_cast<std::size_t>(q) * 16)
+                                                 : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float w = __shfl_sync(0xffffffffu, weight_of_lane, min(k0 + i, n - 1));
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(h[e]);
+                    acc[2 * e] = fmaf(w, f.x, acc[2 * e]);
+                    acc[2 * e + 1] = fmaf(w, f.y, acc[2 * e + 1]);
+                }
+            }
+        }
+        if (q < chunks) {
+            uint4 packed;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+            reinterpret_cast<uint4*>(a.out + static_cast<std::size_t>(token) * H)[q] = packed;
+        }
+    }
+    // tokens that were routed nowhere have no map entry: their result is zero
+    const long long zero_units = static_cast<long long>(a.num_tokens) * groups;
+    for (long long u = zero_units * me / total_warps; u < zero_units * (me + 1) / total_warps; ++u) {
+        const int t = static_cast<int>(u / groups);
+        const int q = static_cast<int>(u % groups) * 32 + lane;
+        if (a.plan_mask[t] == 0 && q < chunks) reinterpret_cast<uint4*>(a.out + static_cast<std::size_t>(t) * H)[q] = make_uint4(0u, 0u, 0u, 0u);
     }
 }
 

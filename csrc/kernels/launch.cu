@@ -92,6 +92,11 @@ cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_
     return cooperative_launch(combine_kernel, launch, dim3(channels, launch.num_virtual, 1), kCombineWarps * 32, smem, stream);
 }
 
+cudaError_t launch_local_combine(const LocalCombineArgs& args, int ctas, cudaStream_t stream) {
+    local_combine_kernel<<<ctas, kFusedReduceThreads, 0, stream>>>(args);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_fused_reduce(const FusedReduceArgs& args, int ctas, cudaStream_t stream) {
     fused_reduce_kernel<<<ctas, kFusedReduceThreads, 0, stream>>>(args);
     return cudaGetLastError();

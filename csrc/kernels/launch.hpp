@@ -28,6 +28,8 @@ cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_
 
 // Owner-side reduction of the fused down-projection + combine; `ctas` must be the same for every launch of one
 // runtime (completion is counted monotonically).
+// Single-rank combine as one ordinary launch (no peers, nothing staged).
+cudaError_t launch_local_combine(const LocalCombineArgs& args, int ctas, cudaStream_t stream);
 cudaError_t launch_fused_reduce(const FusedReduceArgs& args, int ctas, cudaStream_t stream);
 
 }  // namespace bep

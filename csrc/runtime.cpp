@@ -147,6 +147,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("fused_reduce", &Runtime::fused_reduce, py::arg("dispatch_result"), py::arg("out"), py::arg("stream") = 0)
         .def("fused_status", &Runtime::fused_status)
         .def("combine_is_split", &Runtime::combine_is_split)
+        .def("combine_is_local", &Runtime::combine_is_local)
         .def("pool_debug", &Runtime::pool_debug)
         .def("set_test_delays", &Runtime::set_test_delays)
         .def("set_test_prefix_delay_ns", &Runtime::set_test_prefix_delay_ns)

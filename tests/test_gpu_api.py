@@ -186,8 +186,11 @@ def test_cumulative_stats_and_invalid_routes(world1):
                 buffer.dispatch(x, idx, w)
 
 
-def test_combine_weighted_and_unique(world1):
-    with _buffer() as buffer:
+@pytest.mark.parametrize("mode", ["auto", "inline"])
+def test_combine_weighted_and_unique(world1, mode):
+    """Single rank: "auto" is the one-launch gather-reduce, "inline" the cooperative kernel writing straight to out."""
+    with _buffer(combine_reduce=mode) as buffer:
+        assert buffer.runtime.combine_is_local() == (mode == "auto")
         cpu, (x, idx, w) = _dev_inputs(pattern="partial")
         recv_x, _, _, handle, _ = buffer.dispatch(x, idx, w, do_expand=True)
         combined, _, event = buffer.combine(recv_x, handle)
