@@ -52,6 +52,8 @@ def parse_args():
     p.add_argument("--engine", default="tma", choices=["tma", "vector"])
     p.add_argument("--transport", default="peer", choices=["peer", "host_staged"])
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--tx-warps", type=int, default=0, help="send warps per channel CTA (0: by rank count)")
+    p.add_argument("--rx-warps", type=int, default=0, help="receive/expand warps per channel CTA (0: by rank count)")
     p.add_argument("--combine-reduce", default="auto", choices=["auto", "separate", "inline"])
     p.add_argument("--no-numa-bind", action="store_true", help="leave the process on whatever CPUs it was started on")
     return p.parse_args()
@@ -248,9 +250,12 @@ def run_ours(args, rank, world, local_rank):
 
     def time_config(tokens, steps, warmup, want_e2e):
         channels = args.channels or default_channels(world, tokens)
+        # send warps: with one rank every row is staged locally and the send role is latency-bound, four warps measured
+        # best (dispatch 171 -> 161 us at T=4096); across NVLink two send and ten receive warps were best at 4 GPUs
         config = HostStagedConfig(channels=channels, stage=7 if args.wire != "bf16" else 6, wire_dtype=args.wire,
                                   copy_engine=args.engine, transport=args.transport, timeout_ms=20000,
-                                  output_pool_size=2, tx_warps=2, rx_warps=10, combine_reduce=args.combine_reduce)
+                                  output_pool_size=2, tx_warps=args.tx_warps or (4 if world == 1 else 2), rx_warps=args.rx_warps or 10,
+                                  combine_reduce=args.combine_reduce)
         buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
         launches_per_step = 3 if buffer.runtime.combine_is_split() else 2  # dispatch, combine (+ its owner-side sum)
         g = torch.Generator().manual_seed(1234 + rank)
@@ -310,6 +315,7 @@ def run_ours(args, rank, world, local_rank):
             "clocks": clocks,
             "channels": channels,
             "launches_per_step": launches_per_step,
+            "warps": f"1 control + {config.tx_warps} send + {config.rx_warps} receive/expand per channel CTA",
             "roofline": roofline(idx_cpu, world, rank, tokens, args.topk, EXPERTS),
         }
         if want_e2e:
@@ -406,6 +412,7 @@ def run_ours(args, rank, world, local_rank):
                 "parallelism": f"ep{world}",
                 "do_expand": True,
                 "channels": headline["channels"],
+                "warps": headline["warps"],
                 "transport": args.transport,
                 "copy_engine": args.engine,
                 "l2": f"inputs rotate over {INPUT_SETS} token sets ({INPUT_SETS * args.tokens * HIDDEN * 2 >> 20} MiB) and each "
