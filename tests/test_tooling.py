@@ -48,3 +48,25 @@ def test_footprint_arithmetic(ext):
     assert relay["outboxes_bytes"] == 7 * relay["segment_bytes"]
     bounded = footprint(8, 8192, 7168, 8, 256, 32, 16, 3, False, False, False)
     assert bounded["slots"] == 16 and bounded["segment_bytes"] < f["segment_bytes"] // 8
+
+
+def test_bench_routes_and_roofline_model():
+    """The headline benchmark's synthetic routing is deterministic per (rank, tokens) and its roofline is the slower
+    of the HBM and the NVLink bound: HBM-bound at one rank, NVLink-bound at eight."""
+    import torch
+
+    import bench
+
+    idx_a, w_a = bench.make_routes(256, 256, 8, rank=3)
+    idx_b, w_b = bench.make_routes(256, 256, 8, rank=3)
+    assert torch.equal(idx_a, idx_b) and torch.equal(w_a, w_b)
+    assert not torch.equal(idx_a, bench.make_routes(256, 256, 8, rank=4)[0])
+    assert all(len(set(row)) == 8 for row in idx_a.tolist())  # distinct experts per token
+    assert torch.allclose(w_a.sum(dim=1), torch.ones(256))
+    one = bench.roofline(idx_a, 1, 0, 256, 8, 256)
+    eight = bench.roofline(idx_a, 8, 3, 256, 8, 256)
+    assert one["dispatch_bound"] == "hbm" and one["combine_bound"] == "hbm"
+    assert eight["dispatch_bound"] == "nvlink" and eight["combine_bound"] == "nvlink"
+    assert eight["dispatch_us"] > one["dispatch_us"] > 0
+    # one rank, BF16: x read + expanded rows written = (1 + 8) * 256 rows of 14,336 bytes at the copy rate
+    assert abs(one["dispatch_us"] - 9 * 256 * 14336 / 6548e9 * 1e6) / one["dispatch_us"] < 0.05
