@@ -95,11 +95,12 @@ def measure_upload_rate(device: int, num_bytes: int, repeats: int = 3) -> float:
         target.copy_(host, non_blocking=True)
     stop.record()
     stop.synchronize()
-    measure_upload_rate.keep.append(host)  # a freed pinned block would be handed to the next node's probe
+    _PROBE_BUFFERS.append(host)  # a freed pinned block would be handed to the next node's probe
     return repeats * num_bytes / (start.elapsed_time(stop) * 1e-3) / 1e9
 
 
-measure_upload_rate.keep = []  # type: ignore[attr-defined]
+#: pinned probe buffers kept alive until a placement decision is complete
+_PROBE_BUFFERS: List[object] = []
 
 
 def bind_to_fastest_upload_node(device: int, probe_bytes: int = 48 << 20, min_gain: float = 1.05,
@@ -131,5 +132,5 @@ def bind_to_fastest_upload_node(device: int, probe_bytes: int = 48 << 20, min_ga
         os.sched_setaffinity(0, original)
         return None
     finally:
-        measure_upload_rate.keep.clear()  # type: ignore[attr-defined]
+        _PROBE_BUFFERS.clear()
     return {"node": chosen, "rates_gbs": {str(k): round(v, 1) for k, v in rates.items()}}
