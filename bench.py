@@ -217,15 +217,6 @@ def max_over_ranks(value):
     return float(t[0])
 
 
-def default_channels(world, tokens):
-    # one CTA per channel; enough channels to keep NVLink and HBM busy at large T, few at small T
-    if tokens <= 256:
-        return 32
-    if tokens <= 1024:
-        return 64
-    return 128
-
-
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -249,12 +240,13 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
 
     def time_config(tokens, steps, warmup, want_e2e):
-        channels = args.channels or default_channels(world, tokens)
+        tuned = HostStagedConfig.tuned(world, tokens)
+        channels = args.channels or tuned.channels
         # send warps: with one rank every row is staged locally and the send role is latency-bound, four warps measured
         # best (dispatch 171 -> 161 us at T=4096); across NVLink two send and ten receive warps were best at 4 GPUs
         config = HostStagedConfig(channels=channels, stage=7 if args.wire != "bf16" else 6, wire_dtype=args.wire,
                                   copy_engine=args.engine, transport=args.transport, timeout_ms=20000,
-                                  output_pool_size=2, tx_warps=args.tx_warps or (4 if world == 1 else 2), rx_warps=args.rx_warps or 10,
+                                  output_pool_size=2, tx_warps=args.tx_warps or tuned.tx_warps, rx_warps=args.rx_warps or tuned.rx_warps,
                                   combine_reduce=args.combine_reduce)
         buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
         launches_per_step = 3 if buffer.runtime.combine_is_split() else 2  # dispatch, combine (+ its owner-side sum)

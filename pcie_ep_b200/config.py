@@ -176,6 +176,22 @@ class HostStagedConfig:
         if self.descriptor_slots not in (0, 256, self.payload_slots):
             raise ValueError("descriptor_slots must be 0, 256 or equal to payload_slots")
 
+    @classmethod
+    def tuned(cls, num_ranks: int, num_max_tokens_per_rank: int, **overrides) -> "HostStagedConfig":
+        """The settings measured best on 8x B200 for a buffer of this size, with ``overrides`` on top.
+
+        Channels (= CTAs per rank): 32 up to 256 tokens per rank, 64 up to 1024, 128 beyond -- few CTAs keep the
+        grid barrier and the counts exchange short at small T, many keep NVLink and HBM busy at large T.
+        Warps per CTA: ten receive/expand warps; two send warps across NVLink (the link, not the send role, is the
+        limit), four on a single rank, where every row is staged locally and the send role is latency-bound.
+        """
+        if num_ranks < 1 or num_max_tokens_per_rank < 1:
+            raise ValueError("num_ranks and num_max_tokens_per_rank must be positive")
+        channels = 32 if num_max_tokens_per_rank <= 256 else 64 if num_max_tokens_per_rank <= 1024 else 128
+        settings = dict(channels=channels, tx_warps=4 if num_ranks == 1 else 2, rx_warps=10)
+        settings.update(overrides)
+        return cls(**settings)
+
     def native_options(self) -> dict:
         """Options that every rank must agree on before memory is mapped."""
         options = {field.name: getattr(self, field.name) for field in fields(self)}

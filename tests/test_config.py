@@ -63,3 +63,18 @@ def test_native_options_and_transport_resolution():
     assert config.resolved_transport(False) == "cpu"
     assert HostStagedConfig(stage=8, numa_mode="relay").resolved_transport(True) == "host_staged"
     assert HostStagedConfig(transport="host_staged").resolved_transport(True) == "host_staged"
+
+
+def test_tuned_settings_by_size():
+    from pcie_ep_b200 import HostStagedConfig
+
+    one = HostStagedConfig.tuned(1, 4096)
+    assert (one.channels, one.tx_warps, one.rx_warps) == (128, 4, 10)
+    eight = HostStagedConfig.tuned(8, 128, timeout_ms=1234)
+    assert (eight.channels, eight.tx_warps, eight.rx_warps, eight.timeout_ms) == (32, 2, 10, 1234)
+    assert HostStagedConfig.tuned(4, 1024).channels == 64
+    assert HostStagedConfig.tuned(2, 4096, channels=16).channels == 16
+    import pytest
+
+    with pytest.raises(ValueError):
+        HostStagedConfig.tuned(0, 128)
