@@ -35,6 +35,7 @@ HIDDEN, EXPERTS, TOPK = 7168, 256, 8
 # reference dispatch-only latency on 8x H20D, ms (RESULTS_CONTROL_PROGRESS.md:31-40)
 PUBLISHED_MS = {16: 0.260, 32: 0.282, 64: 0.405, 128: 0.647, 256: 1.033, 512: 1.950, 1024: 3.681, 2048: 7.079,
                 4096: 13.558, 8192: 26.546}
+METRIC = "dispatch+combine us (device, max over ranks), H=7168, E=256, top-%d"  # both arms print this string
 INPUT_SETS = 4  # rotated every step: 4 x T x 14 KiB of tokens (> L2 at T >= 2304); see "l2" in config
 
 
@@ -382,7 +383,7 @@ def run_ours(args, rank, world, local_rank):
         published = PUBLISHED_MS.get(args.tokens)
         value = headline["us_per_step"]
         line = {
-            "metric": "dispatch+combine us (device, max over ranks), H=7168, E=256, top-%d" % args.topk,
+            "metric": METRIC % args.topk,
             "value": round(value, 2),
             "unit": "us/step",
             "n_gpus": world,
@@ -539,7 +540,9 @@ def run_reference(args, rank, world, local_rank):
         published = PUBLISHED_MS.get(args.tokens)
         print(json.dumps({
             "impl": "reference",
-            "metric": "dispatch us (device, max over ranks), H=7168, E=256, top-%d; the reference has no combine" % args.topk,
+            "metric": METRIC % args.topk,
+            "reference_note": "dispatch only: the reference has no combine, so its value is a lower bound of what the "
+                              "full exchange would cost it and any ratio against it is an under-estimate",
             "value": round(value, 2), "unit": "us/step", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(value / 1000.0, 5), "higher_is_better": False, "scaling": "weak",
             "vs_baseline": round(value / (published * 1000.0), 5) if published else None,
