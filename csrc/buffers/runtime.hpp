@@ -1,8 +1,8 @@
 // Native runtime of one (virtual) EP rank: owns the device-resident rank constants, the result
-// pools, the routing-plan pool and the launch logic.  Counterpart of the reference's AdvancedRuntime
-// (csrc/buffers/advanced.hpp:43-550) for the peer-memory transport.
+// pools, the routing-plan pool and the launch logic (parity: the reference's AdvancedRuntime,
+// csrc/buffers/advanced.hpp:43-550, for the peer-memory transport).
 //
-// Result pools (reference: csrc/buffers/advanced.hpp:296-336,402-418): `output_pool_size` eager sets
+// Result pools: `output_pool_size` eager sets
 // plus one graph set are allocated up front.  A set is busy while any of its tensors -- or a view of
 // one -- is still referenced from Python; when every set is busy, dispatch fails with "pool exhausted"
 // instead of waiting or allocating.  Routing plans come from a pool of the same size (+1 for graphs).
@@ -31,8 +31,7 @@ namespace py = pybind11;
 // True when nothing outside this runtime can still reach the tensor's memory.  Pool tensors are never
 // handed out themselves: Python only ever receives aliases (distinct tensor objects sharing the
 // storage), so "some result tensor or a view of it is alive" is exactly "the storage has another
-// owner".  This needs nothing of PyTorch's Python-object bookkeeping (the reference's check does:
-// csrc/buffers/advanced.hpp:402-418).
+// owner".  This needs nothing of PyTorch's Python-object bookkeeping.
 inline bool tensor_unowned(const at::Tensor& t) {
     if (!t.defined()) return true;
     return t.use_count() == 1 && t.unsafeGetTensorImpl()->unsafe_storage().use_count() == 1;
@@ -53,8 +52,9 @@ struct RuntimeOptions {
     bool wire_fp8 = false;
     bool recv_fp8 = false;
     bool use_tma = true;
-    int tx_warps = 4;
-    int rx_warps = 6;
+    int tx_warps = 2;
+    int rx_warps = 8;
+    int send_stages = 3;
     int output_pool_size = 3;
     bool enable_graph = false;
     bool enable_combine = true;
@@ -77,6 +77,7 @@ struct RuntimeOptions {
         o.use_tma = get("copy_engine", std::string("tma")) == "tma";
         o.tx_warps = get("tx_warps", o.tx_warps);
         o.rx_warps = get("rx_warps", o.rx_warps);
+        o.send_stages = get("pipeline_stages", o.send_stages);
         o.output_pool_size = get("output_pool_size", o.output_pool_size);
         o.enable_graph = get("enable_graph", o.enable_graph);
         o.enable_combine = get("enable_combine", o.enable_combine);
@@ -89,6 +90,7 @@ struct RuntimeOptions {
         if (o.channels < 1 || o.channels > kMaxChannels) throw std::invalid_argument("channels out of range");
         if (o.tx_warps < 1 || o.rx_warps < 1 || 1 + o.tx_warps + o.rx_warps > kMaxWarps)
             throw std::invalid_argument("1 + tx_warps + rx_warps must not exceed 16");
+        if (o.send_stages < 2 || o.send_stages > kMaxSendStages) throw std::invalid_argument("pipeline_stages must be 2, 3 or 4");
         if (o.output_pool_size < 2 || o.output_pool_size > 8) throw std::invalid_argument("output_pool_size must be in [2,8]");
         if (o.timeout_ms < 1) throw std::invalid_argument("timeout_ms must be positive");
         return o;
@@ -96,7 +98,7 @@ struct RuntimeOptions {
 };
 
 // One routing plan: what the layout phase computed for one topk_idx, reusable while the routing
-// tensor is unchanged (reference: AdvancedLayout, csrc/buffers/advanced.hpp:331-336).
+// tensor is unchanged.
 struct Layout {
     at::Tensor mask, slot, expert_ord, counts;
     int num_tokens = -1;
@@ -109,12 +111,13 @@ struct OutputSet {
     at::Tensor recv_x, recv_idx, recv_w, recv_scale, source_meta, comb_map, recv_chan_counts;
     at::Tensor unique_count, expanded_count, expert_counts, expert_offsets, expert_prefix, source_offsets;
     at::Tensor source_expert_prefix, error, stats, timestamps, prefix_tx_ts;
-    at::Tensor combine_error, combine_stats, profile, combine_profile;
+    at::Tensor combine_error, combine_stats, profile, combine_profile, role_profile;
 
     std::vector<const at::Tensor*> all() const {
         return {&recv_x, &recv_idx, &recv_w, &recv_scale, &source_meta, &comb_map, &recv_chan_counts, &unique_count,
                 &expanded_count, &expert_counts, &expert_offsets, &expert_prefix, &source_offsets,
-                &source_expert_prefix, &error, &stats, &timestamps, &prefix_tx_ts, &combine_error, &combine_stats, &profile, &combine_profile};
+                &source_expert_prefix, &error, &stats, &timestamps, &prefix_tx_ts, &combine_error, &combine_stats, &profile, &combine_profile,
+                &role_profile};
     }
     bool free() const {
         for (const at::Tensor* t : all())
@@ -139,7 +142,7 @@ class DispatchResult {
             "recv_x", "recv_topk_idx", "recv_topk_weights", "source_meta", "comb_map", "recv_chan_counts",
             "unique_count", "expanded_count", "expert_counts", "expert_offsets", "expert_prefix", "source_offsets",
             "source_expert_prefix", "error", "stats", "transport_timestamps_ns", "prefix_tx_timestamps_ns",
-            "combine_error", "combine_stats", "profiling", "combine_profiling", "recv_x_scales"};
+            "combine_error", "combine_stats", "profiling", "combine_profiling", "recv_x_scales", "role_profiling"};
         return keys;
     }
 
@@ -211,6 +214,7 @@ class DispatchResult {
         if (key == "combine_stats") return at::alias(s.combine_stats);
         if (key == "profiling") return at::alias(s.profile);
         if (key == "combine_profiling") return at::alias(s.combine_profile);
+        if (key == "role_profiling") return at::alias(s.role_profile);
         throw py::key_error(key);
     }
 
@@ -227,15 +231,14 @@ struct PreparedDispatch {
     DispatchArgs args;
     std::shared_ptr<DispatchResult> result;
 };
-constexpr int kSplitCombineMinRanks = 2;
 
 struct PreparedCombine {
-    CombineArgs args;
+    CombineArgs args;          // cooperative kernel (combine_reduce="inline")
     at::Tensor out;
-    bool split = false;        // the owner-side sum is a second launch
-    FusedReduceArgs reduce{};  // its arguments (split only)
-    bool local = false;        // single rank: one ordinary gather-reduce launch replaces the cooperative kernel
-    LocalCombineArgs local_args{};
+    bool inline_kernel = false;  // one cooperative launch does both sides
+    CombinePushArgs push{};    // expert side as an ordinary launch (the default)
+    bool reduce_needed = false;  // more than one rank: the owner-side sum follows as a second ordinary launch
+    FusedReduceArgs reduce{};
 };
 
 class Runtime {
@@ -256,14 +259,24 @@ class Runtime {
         const bool vec_ok = (hidden * 2) % 16 == 0;
         use_tma_ = options_.use_tma && vec_ok && !(options_.recv_fp8 && hidden % 16 != 0);
         threads_ = 32 * (1 + options_.tx_warps + options_.rx_warps);
-        smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, use_tma_);
+        if (dispatch_row_buffer_count(options_.tx_warps, options_.rx_warps, options_.send_stages) > kMaxRowBuffers)
+            throw std::invalid_argument("tx_warps * pipeline_stages + rx_warps exceeds the row buffers a channel CTA can manage");
+        smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, use_tma_, options_.send_stages);
         int max_optin = 0;
         cuda_check(cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device), "query shared memory");
-        if (use_tma_ && smem_ > static_cast<std::size_t>(max_optin)) {
-            // too many row buffers for this hidden size: fall back to the register path
-            use_tma_ = false;
-            smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, false);
+        // too many row buffers for this hidden size: give up send stages first, then receive warps, and only
+        // then fall back to the register path
+        while (use_tma_ && smem_ > static_cast<std::size_t>(max_optin)) {
+            if (options_.send_stages > 2) --options_.send_stages;
+            else if (options_.rx_warps > 2) --options_.rx_warps;
+            else break;
+            smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, true, options_.send_stages);
         }
+        if (use_tma_ && smem_ > static_cast<std::size_t>(max_optin)) {
+            use_tma_ = false;
+            smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, false, options_.send_stages);
+        }
+        threads_ = 32 * (1 + options_.tx_warps + options_.rx_warps);
         if (smem_ > static_cast<std::size_t>(max_optin)) throw std::runtime_error("dispatch kernel needs more shared memory than the device offers");
         cuda_check(configure_kernels(smem_), "configure kernels");
 
@@ -290,6 +303,7 @@ class Runtime {
         rc_.vec_ok = vec_ok ? 1 : 0;
         rc_.tx_warps = options_.tx_warps;
         rc_.rx_warps = options_.rx_warps;
+        rc_.send_stages = options_.send_stages;
         rc_.unique_cap = P * num_max_tokens;
         rc_.expanded_cap = P * num_max_tokens * std::min(K, lay_.num_local_experts) + lay_.num_local_experts * 255;
         rc_.timeout_ns = static_cast<std::uint64_t>(options_.timeout_ms) * 1000000ull;
@@ -311,7 +325,9 @@ class Runtime {
             pools_.push_back(std::make_shared<OutputSet>(make_output_set()));
             plans_.push_back(make_layout());
         }
-        fused_counters_ = at::zeros({4}, i64);  // finished CTAs: [0] scatter GEMM, [1] fused reduction, [2] split-combine reduction
+        // finished CTAs of the launch in flight: [0] scatter GEMM, [1] fused reduction, [2] combine owner-side sum,
+        // [3] combine push; [4..5] statistics accumulators of the combine push
+        fused_counters_ = at::zeros({8}, i64);
         fused_status_ = at::zeros({4}, i32);
         fused_gemm_ctas_ = grouped_gemm_ctas();
         if (options_.enable_combine) {
@@ -327,6 +343,7 @@ class Runtime {
     int threads() const { return threads_; }
     std::size_t shared_bytes() const { return smem_; }
     bool uses_tma() const { return use_tma_; }
+    int send_stages() const { return options_.send_stages; }
     const SegmentLayout& layout() const { return lay_; }
     int unique_capacity() const { return rc_.unique_cap; }
     int expanded_capacity() const { return rc_.expanded_cap; }
@@ -387,6 +404,7 @@ class Runtime {
         a.timestamps = out.timestamps.data_ptr<std::int64_t>();
         a.prefix_tx_ts = out.prefix_tx_ts.data_ptr<std::int64_t>();
         a.profile = out.profile.data_ptr<std::int64_t>();
+        a.role_profile = out.role_profile.numel() > 0 ? out.role_profile.data_ptr<std::int64_t>() : nullptr;
         p.result = std::make_shared<DispatchResult>(out_set, plan, expand, T, rc_.unique_cap, rc_.expanded_cap, lay_.num_topk,
                                                     options_.recv_fp8);
         return p;
@@ -445,30 +463,32 @@ class Runtime {
         a.error = set.combine_error.data_ptr<int>();
         a.stats = set.combine_stats.data_ptr<std::int64_t>();
         a.profile = set.combine_profile.data_ptr<std::int64_t>();
-        p.local = lay_.num_ranks == 1 && rc_.vec_ok != 0 && options_.combine_reduce != "inline";
-        if (p.local) {
-            LocalCombineArgs& l = p.local_args;
-            l.rc = a.rc;
-            l.y = a.y;
-            l.comb_map = a.comb_map;
-            l.recv_chan_counts = a.recv_chan_counts;
-            l.plan_mask = a.plan_mask;
-            l.num_tokens = T;
-            l.weighted = a.weighted;
-            l.out = a.out;
-            l.error = a.error;
-        }
-        p.split = combine_is_split();
-        if (p.split) {
-            a.split = 1;
+        p.inline_kernel = combine_is_inline();
+        if (p.inline_kernel) return p;
+        unsigned long long* counters = reinterpret_cast<unsigned long long*>(fused_counters_.data_ptr<std::int64_t>());
+        CombinePushArgs& push = p.push;
+        push.rc = a.rc;
+        push.y = a.y;
+        push.comb_map = a.comb_map;
+        push.recv_chan_counts = a.recv_chan_counts;
+        push.plan_mask = a.plan_mask;
+        push.num_tokens = T;
+        push.weighted = a.weighted;
+        push.out = a.out;
+        push.error = a.error;
+        push.stats = a.stats;
+        push.cta_done = counters + 3;
+        push.stat_scratch = counters + 4;
+        p.reduce_needed = lay_.num_ranks > 1;
+        if (p.reduce_needed) {
             FusedReduceArgs& r = p.reduce;
             r.rc = a.rc;
             r.expert_ord = nullptr;
             r.rank_mask = a.plan_mask;
             r.gemm_status = nullptr;
             r.num_tokens = T;
-            r.epoch = 0;  // the combine epoch the expert-side launch has just advanced on the device
-            r.cta_done = reinterpret_cast<unsigned long long*>(fused_counters_.data_ptr<std::int64_t>()) + 2;
+            r.epoch = 0;  // the combine epoch the push launch has just advanced on the device
+            r.cta_done = counters + 2;
             r.stage_off = lay_.cstage_off;
             r.sig_off = lay_.csig_off;
             r.done_off = lay_.cdone_off;
@@ -481,38 +501,42 @@ class Runtime {
         return p;
     }
 
-    // Whether combine runs its owner-side sum as a second launch: by default whenever there is more than one rank
-    // (a single rank writes its reduced rows straight to the output and has no owner-side pass at all).
-    bool combine_is_split() const {
-        if (rc_.vec_ok == 0 || lay_.num_ranks == 1 || options_.combine_reduce == "inline") return false;
-        if (options_.combine_reduce == "separate") return true;
-        return lay_.num_ranks >= kSplitCombineMinRanks;
+    // combine_reduce="inline" (and every hidden size whose rows are not 16-byte multiples) runs the one cooperative
+    // kernel; otherwise combine is two ordinary launches (one with a single rank: its reduced rows are the result).
+    bool combine_is_inline() const { return rc_.vec_ok == 0 || options_.combine_reduce == "inline"; }
+    bool combine_is_split() const { return !combine_is_inline() && lay_.num_ranks > 1; }
+    bool combine_is_local() const { return !combine_is_inline() && lay_.num_ranks == 1; }
+
+    // CTAs of the ordinary combine launches: `num_sms` > 0 limits them to that many SMs' worth
+    int combine_ctas(int per_sm, int num_sms) const {
+        const int sms = num_sms > 0 ? std::min(num_sms, fused_gemm_ctas_) : fused_gemm_ctas_;
+        return per_sm * std::max(1, sms);
     }
 
-    // second launch of a split combine; `prepared` comes from prepare_combine of this runtime
-    void launch_split_reduce(PreparedCombine& prepared, cudaStream_t stream) {
-        if (!prepared.split) return;
-        prepared.reduce.launch_index = ++split_reduce_launches_;
-        cuda_check(launch_fused_reduce(prepared.reduce, 4 * fused_gemm_ctas_, stream), "combine reduce launch");
+    void launch_combine_push(PreparedCombine& prepared, cudaStream_t stream, int num_sms = 0) {
+        cuda_check(bep::launch_combine_push(prepared.push, combine_ctas(3, num_sms), stream), "combine push launch");
+    }
+    // second launch of the default combine; `prepared` comes from prepare_combine of this runtime
+    void launch_combine_reduce(PreparedCombine& prepared, cudaStream_t stream, int num_sms = 0) {
+        if (!prepared.reduce_needed) return;
+        cuda_check(launch_fused_reduce(prepared.reduce, combine_ctas(4, num_sms), stream), "combine reduce launch");
     }
 
     at::Tensor combine(const at::Tensor& y, const DispatchResult& dispatch_result, bool weighted,
-                       const std::optional<at::Tensor>& out_opt, std::int64_t stream) {
+                       const std::optional<at::Tensor>& out_opt, std::int64_t stream, int num_sms = 0) {
         c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
         PreparedCombine p = prepare_combine(y, dispatch_result, weighted, out_opt);
-        if (p.local) {
-            cudaStream_t local_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
-                                                    : at::cuda::getCurrentCUDAStream(device_).stream();
-            cuda_check(launch_local_combine(p.local_args, 3 * fused_gemm_ctas_, local_stream), "local combine launch");
-            return p.out;
-        }
-        CombineLaunch launch{};
-        launch.num_virtual = 1;
-        launch.r[0] = p.args;
         cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
                                                  : at::cuda::getCurrentCUDAStream(device_).stream();
-        cuda_check(launch_combine(launch, options_.channels, static_cast<std::size_t>(lay_.crow_stride), launch_stream), "combine launch");
-        launch_split_reduce(p, launch_stream);
+        if (p.inline_kernel) {
+            CombineLaunch launch{};
+            launch.num_virtual = 1;
+            launch.r[0] = p.args;
+            cuda_check(launch_combine(launch, options_.channels, static_cast<std::size_t>(lay_.crow_stride), launch_stream), "combine launch");
+            return p.out;
+        }
+        launch_combine_push(p, launch_stream, num_sms);
+        launch_combine_reduce(p, launch_stream, num_sms);
         return p.out;
     }
 
@@ -582,7 +606,6 @@ class Runtime {
         a.gemm_status = fused_status_.data_ptr<int>();
         a.num_tokens = T;
         a.epoch = fused_reduce_epoch_ + 1;
-        a.launch_index = fused_reduce_epoch_ + 1;
         a.cta_done = reinterpret_cast<unsigned long long*>(fused_counters_.data_ptr<std::int64_t>()) + 1;
         a.stage_off = lay_.fstage_off;
         a.sig_off = lay_.fsig_off;
@@ -599,9 +622,8 @@ class Runtime {
         return out;
     }
     at::Tensor fused_status() const { return fused_status_; }
-    bool combine_is_local() const { return lay_.num_ranks == 1 && rc_.vec_ok != 0 && options_.combine_reduce != "inline"; }
 
-    // ---- diagnostics / test hooks (reference: csrc/buffers/advanced.hpp:158-227) -------------
+    // ---- diagnostics / test hooks --------------------------------------------------------------
     py::dict pool_debug() const {
         py::dict d;
         py::list busy;
@@ -631,6 +653,14 @@ class Runtime {
     }
     void set_test_withhold_counts(bool on) {
         rc_.test_withhold_counts = on ? 1 : 0;
+        upload_constants();
+    }
+    void set_test_corrupt_sequence(bool on) {
+        rc_.test_corrupt_sequence = on ? 1 : 0;
+        upload_constants();
+    }
+    void set_test_control_abort_after_ns(std::uint64_t ns) {
+        rc_.test_abort_after_ns = ns;
         upload_constants();
     }
     void set_timeout_ms(int ms) {
@@ -713,6 +743,8 @@ class Runtime {
         s.combine_stats = at::zeros({8}, i64);
         s.profile = at::zeros({C, 16}, i64);
         s.combine_profile = at::zeros({C, 8}, i64);
+        // per-warp role counters exist only in a library built with the role instrumentation
+        s.role_profile = role_profiling_enabled() ? at::zeros({C, kMaxWarps, kRoleFieldCount}, i64) : at::zeros({0, kMaxWarps, kRoleFieldCount}, i64);
         return s;
     }
 
@@ -780,7 +812,7 @@ class Runtime {
     std::vector<std::shared_ptr<Layout>> plans_;
     std::vector<at::Tensor> combine_pool_;
     at::Tensor fused_counters_, fused_status_;
-    std::uint64_t fused_gemm_epoch_ = 0, fused_reduce_epoch_ = 0, split_reduce_launches_ = 0;
+    std::uint64_t fused_gemm_epoch_ = 0, fused_reduce_epoch_ = 0;
     int fused_gemm_ctas_ = 0;
     int next_pool_ = 0;
     int next_combine_ = 0;
@@ -812,15 +844,19 @@ inline void launch_combine_group(const std::vector<std::shared_ptr<Runtime>>& ru
                                  std::vector<PreparedCombine>& prepared, int device) {
     if (runtimes.empty() || runtimes.size() != prepared.size() || runtimes.size() > kMaxVirtualRanks)
         throw std::invalid_argument("between 1 and 8 virtual ranks per launch");
-    CombineLaunch launch{};
-    launch.num_virtual = static_cast<int>(runtimes.size());
-    for (std::size_t i = 0; i < runtimes.size(); ++i) launch.r[i] = prepared[i].args;
-    cuda_check(launch_combine(launch, runtimes[0]->channels(), static_cast<std::size_t>(runtimes[0]->layout().crow_stride),
-                              at::cuda::getCurrentCUDAStream(device)),
-               "combine launch");
-    // split combine: every rank's rows are pushed by the launch above; each rank's sum follows in stream order
-    for (std::size_t i = 0; i < runtimes.size(); ++i)
-        runtimes[i]->launch_split_reduce(prepared[i], at::cuda::getCurrentCUDAStream(device));
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream(device);
+    if (prepared[0].inline_kernel) {
+        CombineLaunch launch{};
+        launch.num_virtual = static_cast<int>(runtimes.size());
+        for (std::size_t i = 0; i < runtimes.size(); ++i) launch.r[i] = prepared[i].args;
+        cuda_check(launch_combine(launch, runtimes[0]->channels(), static_cast<std::size_t>(runtimes[0]->layout().crow_stride), stream),
+                   "combine launch");
+        return;
+    }
+    // Ordinary launches in stream order: every rank's rows are pushed before any rank's sum starts, so no launch
+    // ever waits for one that comes after it on the same GPU.
+    for (std::size_t i = 0; i < runtimes.size(); ++i) runtimes[i]->launch_combine_push(prepared[i], stream);
+    for (std::size_t i = 0; i < runtimes.size(); ++i) runtimes[i]->launch_combine_reduce(prepared[i], stream);
 }
 
 }  // namespace bep

@@ -1,7 +1,7 @@
-// Fused weighted combine: the inverse of a finished dispatch, one cooperative launch per rank.
-// The reference stops at dispatch (pcie_ep/buffers/ep.py:461-462 raises); its design note
-// (docs/pcie-ep/design.md:420-422) sketches this inverse: reduce on the expert rank what belongs to one
-// source token, send one row per (token, expert rank) back, add the partial rows at the source.
+// Weighted combine in one cooperative launch per rank (`combine_reduce="inline"`): the inverse of a finished
+// dispatch with the owner-side sum running in the same kernel, so a token's rows are added as they arrive.
+// The default combine is the two ordinary launches of fused_reduce.cuh; this kernel is the variant that starts
+// the owner-side sum before the last row has been pushed, at the price of a cooperative launch.
 //
 // Expert side (send warps): for every row this rank received in the dispatch (the dispatch left an
 // inverse map: source token, output rows, weights) reduce the expert outputs of that token with the
@@ -131,7 +131,6 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
     const int num_warps = blockDim.x >> 5;
     const bool vec_ok = rc->vec_ok != 0;
     const int map_stride = 2 + 2 * K;
-    const bool split = a.split != 0;
     // one rank: the reduced row of a token is already the result -- it goes straight to `out`, nothing is
     // staged and there is no owner-side pass
     const bool direct = P == 1 && vec_ok;
@@ -240,7 +239,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                 if (pending_flag != nullptr) {
                     if (lane == 0) {
                         ptx::bulk_wait_all();
-                        if (!split && !direct) ptx::st_release_sys(pending_flag, epoch);
+                        if (!direct) ptx::st_release_sys(pending_flag, epoch);
                     }
                     pending_flag = nullptr;
                 }
@@ -254,7 +253,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                     }
                     break;
                 }
-                if (t >= t1 || split) break;
+                if (t >= t1) break;
                 const unsigned mask = a.plan_mask[t];
                 if (lane < static_cast<unsigned>(P) && (mask >> lane & 1u)) {
                     const std::uint64_t* ready = reinterpret_cast<const std::uint64_t*>(my_seg + lay.cready_off) +
@@ -285,7 +284,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                 if (lane == 0) {
                     ptx::bulk_s2g(dst, my_buffer, static_cast<unsigned>(H) * 2);
                     ptx::bulk_commit();
-                    if (pending_flag != nullptr && !split && !direct) {
+                    if (pending_flag != nullptr && !direct) {
                         asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
                         ptx::st_release_sys(pending_flag, epoch);
                     }
@@ -315,8 +314,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
         }
         if (lane == 0) {
             ptx::bulk_wait_all();
-            if (pending_flag != nullptr && !split && !direct) ptx::st_release_sys(pending_flag, epoch);
-            if (split) ptx::fence_sys();  // this warp's rows before its CTA is counted as finished
+            if (pending_flag != nullptr && !direct) ptx::st_release_sys(pending_flag, epoch);
         }
     }
 
@@ -332,7 +330,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
         prof[4] = static_cast<std::int64_t>(ptx::globaltimer_ns());
         std::int64_t* cs = rc->chan_stats + static_cast<std::size_t>(C + c) * 10;  // second half: combine
         for (int i = 0; i < 3; ++i) cs[i] = static_cast<std::int64_t>(stat[i]);
-        if (split) ptx::fence_sys(); else __threadfence();
+        __threadfence();
         const unsigned long long old = atomicAdd(&rc->done_ctas[1], 1ull);
         if ((old + 1) % static_cast<unsigned long long>(C) == 0) {
             __threadfence();
@@ -341,13 +339,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
                 for (int i = 0; i < 3; ++i) sum[i] += __ldcg(rc->chan_stats + static_cast<std::size_t>(C + c2) * 10 + i);
             for (int i = 0; i < 8; ++i) a.stats[i] = i < 3 ? sum[i] : 0;
             if (!health.failed()) {
-                if (split) {
-                    // every CTA's rows are written: tell the owners; the area is handed back by their reductions
-                    ptx::fence_sys();
-                    for (int p = 0; p < P; ++p) ptx::st_release_sys(flag_ptr(rc->seg[p], lay.csig_off, me), epoch);
-                } else {
-                    for (int p = 0; p < P; ++p) ptx::st_release_sys(flag_ptr(rc->seg[p], lay.cdone_off, me), epoch);
-                }
+                for (int p = 0; p < P; ++p) ptx::st_release_sys(flag_ptr(rc->seg[p], lay.cdone_off, me), epoch);
             }
             rc->epochs[1] = epoch;
         }

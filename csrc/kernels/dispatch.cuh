@@ -1,19 +1,24 @@
-// Fused expert-parallel dispatch: one cooperative launch per rank does what the reference spreads
-// over eight launches (csrc/buffers/advanced.hpp:472-523): epoch bookkeeping, route validation,
-// stable ordinals, counts exchange, the all-to-all itself, receive-side expansion into per-expert
-// rows, local-token handling, zero padding and statistics.
+// Fused expert-parallel dispatch: one cooperative launch per rank covers epoch bookkeeping, route
+// validation, stable ordinals, the counts exchange, the all-to-all itself, receive-side expansion into
+// per-expert rows, local-token handling, zero padding and statistics.
 //
 // Grid: (channels, virtual_ranks).  blockIdx.y picks the rank (more than one only when several
 // ranks are emulated on one GPU), blockIdx.x the channel.  Channel c of a rank sends that rank's
 // tokens [c*ceil(T/C), (c+1)*ceil(T/C)) and receives what channel c of every rank sent to it.
 //
-// Warp roles inside a channel CTA (the reference's control / TX / RX / scatter roles,
-// csrc/kernels/host_staged/advanced_dispatch.cuh:287-752, fused_receive.cuh:199-305):
+// Warp roles inside a channel CTA:
 //   warp 0              control: reuse guard, stable ordinals, receive prefix, zero padding
-//   warps 1..tx         send: read a token row once, (quantise,) store it into the staging ring
-//                       of every destination rank, then release that row's READY flag there
+//   warps 1..tx         send: read a token row once, (quantise,) store it into the staging ring of
+//                       every *remote* destination rank, then release that row's READY flag there.
+//                       With the bulk-copy engine each send warp runs a software pipeline over a ring
+//                       of `pipeline_stages` shared-memory row buffers: rows are loaded one or two
+//                       tokens ahead, and a row's READY flags are released two rows late, when its
+//                       own bulk group has completed, so neither the HBM read nor the NVLink round
+//                       trip of one row holds up the next.
 //   warps tx+1..        receive+expand: poll READY flags in local memory, read the staged row once
-//                       and write it to every local expert row (or the unique row)
+//                       and write it to every local expert row (or the unique row).  Rows whose
+//                       destination is this rank itself never touch the staging ring: the receive
+//                       warps take them straight from `x` whenever no remote row is waiting.
 //
 // Transport: a row crosses NVLink once per (token, destination rank) as posted stores into the
 // destination's segment (16-byte stores, or cp.async.bulk from shared memory); every flag is
@@ -23,9 +28,14 @@
 #include "protocol.cuh"
 #include "quant.cuh"
 
+#ifndef BEP_ENABLE_PROFILING
+#define BEP_ENABLE_PROFILING 0
+#endif
+
 namespace bep {
 
 constexpr int kMetaSmemBytes = 16 + 12 * kMaxTopk;
+constexpr int kFlagLag = 2;         // a row's READY flags are released after this many later rows were issued
 
 struct DispatchShared {
     int cnt_r[kMaxRanks];
@@ -39,24 +49,64 @@ struct DispatchShared {
     unsigned long long stat[8];
     unsigned long long first_tx_ns;
     unsigned long long last_tx_ns;
-    unsigned long long mbar[kMaxWarps];
+    unsigned long long mbar[kMaxRowBuffers];
     alignas(16) unsigned char meta[kMaxWarps][kMetaSmemBytes];
 };
 
 // Dynamic shared memory: header | cnt_e[E] | bits_e[E] | total_e[E] | eoff[El+1] | ecount[El] |
-// spre[P*El] | msg[P*counts_stride] | (TMA only) one row buffer per send/receive warp.
-inline std::size_t dispatch_smem_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma) {
+// spre[P*El] | msg[P*counts_stride] | (bulk-copy engine only) `stages` row buffers per send warp and one
+// per receive warp.
+inline std::size_t dispatch_smem_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma, int stages) {
     std::size_t bytes = align_up(sizeof(DispatchShared), 16);
     bytes += static_cast<std::size_t>(lay.num_experts) * 12;
     bytes += static_cast<std::size_t>(lay.num_local_experts) * 8 + 4;
     bytes += static_cast<std::size_t>(lay.num_ranks) * lay.num_local_experts * 4;
     bytes = align_up(bytes, 16) + static_cast<std::size_t>(lay.num_ranks) * lay.counts_stride * 4;
     bytes = align_up(bytes, 128);
-    if (use_tma) bytes += static_cast<std::size_t>(tx_warps + rx_warps) * align_up(lay.meta_off + lay.meta_bytes, 128);
+    if (use_tma)
+        bytes += static_cast<std::size_t>(dispatch_row_buffer_count(tx_warps, rx_warps, stages)) *
+                 align_up(lay.meta_off + lay.meta_bytes, 128);
     return bytes;
 }
 
 #ifdef __CUDACC__
+
+// ---- opt-in role instrumentation ---------------------------------------------------------------
+// Built only with -DBEP_ENABLE_PROFILING=1 (a separate library): every send and receive warp adds up, in
+// registers, how long it spent in each kind of wait and how many rows it handled, and lane 0 writes the
+// sixteen counters of its warp once, when the role ends.  A normal build contains none of this.
+enum RoleField : int {
+    kRoleRows = 0,         // rows sent (send warps) / delivered (receive warps)
+    kRoleTotalNs = 1,      // role start to role end
+    kRoleLoadWaitNs = 2,   // waiting for a row to land in shared memory (mbarrier)
+    kRoleStoreWaitNs = 3,  // send: waiting for a bulk group to complete before its flags / receive: for a buffer to drain
+    kRoleCreditWaitNs = 4, // send, ring mode: waiting for slot credit
+    kRolePrefixWaitNs = 5, // receive: waiting for the receive prefix
+    kRoleIdlePollNs = 6,   // receive: probes that found no row
+    kRoleMetaNs = 7,       // building (send) or decoding and placing (receive) row metadata
+    kRoleLocalRows = 8,    // receive: rows taken straight from x
+    kRoleQuantNs = 9,      // FP8 conversion in shared memory
+    kRoleIssueNs = 10,     // issuing the outgoing copies
+    kRoleFields = kRoleFieldCount,
+};
+#if BEP_ENABLE_PROFILING
+#define BEP_ROLE_DECL() unsigned long long role_prof[kRoleFields] = {0}; const unsigned long long role_t_begin = ptx::globaltimer_ns()
+#define BEP_ROLE_T(var) const unsigned long long var = ptx::globaltimer_ns()
+#define BEP_ROLE_ADD(field, since) role_prof[field] += ptx::globaltimer_ns() - (since)
+#define BEP_ROLE_COUNT(field, n) role_prof[field] += (n)
+#define BEP_ROLE_FLUSH(dst)                                                                        \
+    do {                                                                                           \
+        role_prof[kRoleTotalNs] = ptx::globaltimer_ns() - role_t_begin;                            \
+        if (ptx::lane_id() == 0 && (dst) != nullptr)                                               \
+            for (int f_ = 0; f_ < kRoleFields; ++f_) (dst)[f_] = static_cast<std::int64_t>(role_prof[f_]); \
+    } while (0)
+#else
+#define BEP_ROLE_DECL() do {} while (0)
+#define BEP_ROLE_T(var) do {} while (0)
+#define BEP_ROLE_ADD(field, since) do {} while (0)
+#define BEP_ROLE_COUNT(field, n) do {} while (0)
+#define BEP_ROLE_FLUSH(dst) do {} while (0)
+#endif
 
 namespace detail {
 
@@ -105,7 +155,7 @@ __device__ __forceinline__ void tx_row_bf16(const std::uint8_t* src, std::uint8_
     }
 }
 
-// FP8 wire: remote destinations get E4M3 bytes, this rank itself keeps the BF16 row.
+// FP8: every destination gets E4M3 bytes except lane `self` (pass -1 for none), which keeps BF16.
 // Returns the token scale.
 __device__ __forceinline__ float tx_row_fp8(const std::uint8_t* src, std::uint8_t* dst_of_lane, unsigned mask,
                                             int self, int hidden, bool vec_ok) {
@@ -260,7 +310,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
 
 }  // namespace detail
 
-
 namespace detail {
 
 __device__ __forceinline__ bool warp_failed(const Health& health) {
@@ -270,55 +319,94 @@ __device__ __forceinline__ bool warp_give_up(Health& health, int code, int conte
     return __any_sync(0xffffffffu, health.give_up(code, context, detail_value)) != 0;
 }
 
-// TMA send of one token: the row is in `slot` (BF16 payload, metadata at meta_off).  Lane d holds the
-// destination row of rank d.  Returns false if a copy never completed.
-__device__ __forceinline__ void tx_token_tma(const SegmentLayout& lay, unsigned char* slot, std::uint8_t* dst_of_lane,
-                                             unsigned mask, int self, bool wire_fp8) {
-    // self < 0: no BF16 bypass, this rank's own copy is quantised like everybody else's
+// all but the N most recent bulk groups of this thread are complete (their global writes performed)
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// all but the N most recent bulk groups of this thread have finished reading shared memory
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+// Values every role of one channel CTA needs; filled once by the kernel.
+struct Ctx {
+    const DispatchArgs* a;
+    const RankConst* rc;
+    DispatchShared* sh;
+    int* eoff;                   // [El+1] aligned offsets of the local experts (valid once prefix_ready)
+    int* spre;                   // [P][El] rows of earlier sources inside each expert segment
+    unsigned char* row_buffers;  // bulk-copy engine: first row buffer
+    std::uint8_t* my_seg;
+    std::uint8_t* recv_bytes;
+    std::int64_t* prof;
+    std::int64_t* role_prof;     // [warps][kRoleFields] of this channel (profiling builds), else nullptr
+    std::size_t out_row_bytes;
+    std::uint64_t epoch;
+    int slot_bytes, stages;
+    int P, C, E, El, K, H, Q, Qf, me, c, t0, t1, tx_warps, rx_warps, map_stride;
+    bool vec_ok, use_tma, wire_fp8, recv_fp8, ring;
+};
+
+struct RoleStats {
+    unsigned long long source = 0, remote_rows = 0, deliveries = 0, early = 0, probes = 0, credit = 0, local = 0,
+                       published = 0;
+};
+
+// What a send warp keeps in registers for one token: lane d holds the row index at destination d,
+// lane k the k-th expert id, its ordinal and its weight.
+struct TokenRegs {
+    int t;
+    unsigned mask;  // remote destinations only
+    int j;
+    int e, ord;
+    float w;
+};
+
+// Row metadata behind the payload: {src_token, scale, seq_epoch, seq_index} | expert[K] | ordinal[K] | weight[K].
+// The sequence words let the receiver check that the payload it reads belongs to this epoch and to the token the
+// header names: a READY flag that overtook its payload would expose the previous epoch's row.
+__device__ __forceinline__ void write_row_meta(unsigned char* meta, const SegmentLayout& lay, int token, float scale,
+                                               std::uint32_t seq_epoch, int e, int ord, float w, int K) {
     const unsigned lane = ptx::lane_id();
-    const unsigned self_bit = self >= 0 ? 1u << self : 0u;
-    const unsigned remote = mask & ~self_bit;
-    const unsigned bf16_bytes = static_cast<unsigned>(lay.meta_off + lay.meta_bytes);
-    const int hidden = lay.hidden;
-    if (!wire_fp8 || remote == 0) {
-        ptx::fence_proxy_async_smem();
-        __syncwarp();
-        for (unsigned m = mask; m; m &= m - 1) {
-            std::uint8_t* dst = shfl_ptr(dst_of_lane, __ffs(m) - 1);
-            if (lane == 0) ptx::bulk_s2g(dst, slot, bf16_bytes);
-        }
-        if (lane == 0) {
-            ptx::bulk_commit();
-            ptx::bulk_wait_all();
-        }
-        __syncwarp();
-        return;
+    if (lane == 0) {
+        reinterpret_cast<int*>(meta)[0] = token;
+        reinterpret_cast<float*>(meta)[1] = scale;
+        reinterpret_cast<std::uint32_t*>(meta)[2] = seq_epoch;
+        reinterpret_cast<std::uint32_t*>(meta)[3] = static_cast<std::uint32_t>(token) + 1u;
     }
-    // FP8 wire with at least one remote destination: this rank's own copy leaves first as BF16,
-    // then the row is quantised in place and leaves as E4M3 bytes + metadata.
-    ptx::fence_proxy_async_smem();
-    __syncwarp();
-    {
-        std::uint8_t* dst = shfl_ptr(dst_of_lane, self >= 0 ? self : 0);
-        if ((mask & self_bit) && lane == 0) {
-            ptx::bulk_s2g(dst, slot, bf16_bytes);
-            ptx::bulk_commit();
-            ptx::bulk_wait_read_all();
-        }
+    if (lane < static_cast<unsigned>(K)) {
+        reinterpret_cast<int*>(meta + 16)[lane] = e;
+        reinterpret_cast<int*>(meta + 16)[K + lane] = ord;
+        reinterpret_cast<float*>(meta + 16)[2 * K + lane] = w;
     }
-    __syncwarp();
+    for (int b = 16 + 12 * K + lane; b < lay.meta_bytes; b += 32) meta[b] = 0;
+}
+
+__device__ __forceinline__ void load_token_routes(const DispatchArgs& a, int t, int K, int E, int& e, int& ord, float& w) {
+    const unsigned lane = ptx::lane_id();
+    e = -1;
+    ord = -1;
+    w = 0.0f;
+    if (lane < static_cast<unsigned>(K)) {
+        const std::int64_t e64 = a.topk_idx[static_cast<std::size_t>(t) * K + lane];
+        e = (e64 >= 0 && e64 < E) ? static_cast<int>(e64) : -1;
+        ord = a.plan_expert_ord[static_cast<std::size_t>(t) * K + lane];
+        w = a.topk_w ? a.topk_w[static_cast<std::size_t>(t) * K + lane] : 1.0f;
+    }
+}
+
+// BF16 row in shared memory -> E4M3 codes in its first half; returns the row scale.  Increasing order: chunk q
+// is read by every lane before anything lands on it.
+__device__ __forceinline__ float quantise_row_in_place(unsigned char* slot, int hidden) {
+    const unsigned lane = ptx::lane_id();
     const int chunks = hidden / 8;
     float amax = 0.0f;
     for (int q = lane; q < chunks; q += 32) amax = fmaxf(amax, chunk_amax(*reinterpret_cast<const uint4*>(slot + q * 16)));
     amax = warp_max(amax);
     const float scale = fp8_scale_from_amax(amax);
     const float inv = 1.0f / scale;
-    // metadata out of the way first (the FP8 layout puts it right behind H bytes)
-    uint4 meta_chunk = make_uint4(0, 0, 0, 0);
-    const int meta_chunks = lay.meta_bytes / 16;
-    if (static_cast<int>(lane) < meta_chunks) meta_chunk = *reinterpret_cast<const uint4*>(slot + lay.meta_off + lane * 16);
-    if (lane == 0) meta_chunk.y = __float_as_uint(scale);
-    // in-place narrowing, increasing order: chunk q is read before anything lands on it
     for (int q0 = 0; q0 < chunks; q0 += 32) {
         const int q = q0 + lane;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -327,19 +415,615 @@ __device__ __forceinline__ void tx_token_tma(const SegmentLayout& lay, unsigned 
         if (q < chunks) *reinterpret_cast<uint2*>(slot + q * 8) = chunk_to_fp8(v, inv);
         __syncwarp();
     }
-    if (static_cast<int>(lane) < meta_chunks) *reinterpret_cast<uint4*>(slot + lay.meta_off_fp8 + lane * 16) = meta_chunk;
-    ptx::fence_proxy_async_smem();
-    __syncwarp();
-    const unsigned fp8_bytes = static_cast<unsigned>(lay.meta_off_fp8 + lay.meta_bytes);
-    for (unsigned m = remote; m; m &= m - 1) {
-        std::uint8_t* dst = shfl_ptr(dst_of_lane, __ffs(m) - 1);
-        if (lane == 0) ptx::bulk_s2g(dst, slot, fp8_bytes);
+    return scale;
+}
+
+// scale of a BF16 row in global memory (register path with rows that stay E4M3 at the receiver)
+__device__ __forceinline__ float row_scale_from_global(const std::uint8_t* src, int hidden, bool vec_ok) {
+    const unsigned lane = ptx::lane_id();
+    float amax = 0.0f;
+    if (vec_ok) {
+        for (int q = lane; q < hidden / 8; q += 32) amax = fmaxf(amax, chunk_amax(ptx::ld_nc_v4(src + static_cast<std::size_t>(q) * 16)));
+    } else {
+        const auto* s = reinterpret_cast<const __nv_bfloat16*>(src);
+        for (int i = lane; i < hidden; i += 32) amax = fmaxf(amax, fabsf(__bfloat162float(s[i])));
+    }
+    return fp8_scale_from_amax(warp_max(amax));
+}
+
+// Where one received row goes: computes its output rows, writes the per-row outputs (expert id, weight, source,
+// scale) and the entry of the combine map, and leaves the pointer of output row i in lane i < n_rows.
+// `e`, `ord`, `wgt` are per lane k.  Returns true (warp-uniform) when a row would fall outside its capacity.
+__device__ __forceinline__ bool place_row(const Ctx& k, int s, int j, int token, float scale, int e, int ord, float wgt,
+                                          std::uint8_t*& out_ptr, int& n_rows) {
+    const DispatchArgs& a = *k.a;
+    const unsigned lane = ptx::lane_id();
+    const unsigned full = 0xffffffffu;
+    const unsigned lt_mask = (1u << lane) - 1u;
+    const bool local = e >= 0 && e / k.El == k.me;
+    const int el = local ? e - k.me * k.El : -1;
+    const unsigned lmask = __ballot_sync(full, local);
+    const int n_local = __popc(lmask);
+    const int pos = __popc(lmask & lt_mask);
+    int* map = a.comb_map + ((static_cast<std::size_t>(s) * k.C + k.c) * k.Qf + j) * k.map_stride;
+    out_ptr = nullptr;
+    bool overflow = false;
+    if (a.do_expand) {
+        n_rows = n_local;
+        int row = -1;
+        if (local) {
+            row = k.eoff[el] + k.spre[s * k.El + el] + ord;
+            overflow = row < 0 || row >= k.rc->expanded_cap;
+        }
+        // compact: the i-th local slot's row goes to lane i
+        for (unsigned lm = lmask, i = 0; lm; lm &= lm - 1, ++i) {
+            const int r = __shfl_sync(full, row, __ffs(lm) - 1);
+            if (lane == i) out_ptr = k.recv_bytes + static_cast<std::size_t>(r) * k.out_row_bytes;
+        }
+        if (local && !overflow) {
+            if (k.recv_fp8) a.recv_scale[row] = scale;
+            a.recv_idx[row] = el;
+            a.recv_w[row] = wgt;
+            a.source_meta[static_cast<std::size_t>(row) * 3 + 0] = s;
+            a.source_meta[static_cast<std::size_t>(row) * 3 + 1] = token;
+            a.source_meta[static_cast<std::size_t>(row) * 3 + 2] = lane;
+            map[2 + 2 * pos] = row;
+            map[3 + 2 * pos] = __float_as_int(wgt);
+        }
+    } else {
+        n_rows = 1;
+        const int row = k.sh->source_offsets[s] + k.sh->chan_base[s] + j;
+        overflow = row < 0 || row >= k.rc->unique_cap;
+        if (lane == 0) out_ptr = k.recv_bytes + static_cast<std::size_t>(row) * k.out_row_bytes;
+        if (!overflow) {
+            if (k.recv_fp8 && lane == 0) a.recv_scale[row] = scale;
+            if (lane < static_cast<unsigned>(k.K)) {
+                a.recv_idx[static_cast<std::size_t>(row) * k.K + lane] = el;
+                a.recv_w[static_cast<std::size_t>(row) * k.K + lane] = local ? wgt : 0.0f;
+            }
+            if (lane == 0) {
+                a.source_meta[static_cast<std::size_t>(row) * 3 + 0] = s;
+                a.source_meta[static_cast<std::size_t>(row) * 3 + 1] = token;
+                a.source_meta[static_cast<std::size_t>(row) * 3 + 2] = -1;
+                map[2] = row;
+                map[3] = __float_as_int(1.0f);
+            }
+        }
     }
     if (lane == 0) {
-        ptx::bulk_commit();
-        ptx::bulk_wait_all();
+        map[0] = token;
+        map[1] = a.do_expand ? n_local : 1;
     }
+    return __any_sync(full, overflow) != 0;
+}
+
+// ---- send role, bulk-copy engine ----------------------------------------------------------------
+// One warp, S row buffers.  Row n lives in buffer n % S.  Per loop turn: the row D turns ahead is located and its
+// load issued (the buffer it lands in was used by row n + D - S, whose outgoing copies have finished reading it
+// once all but the R = S - D - 1 most recent bulk groups have); row n's metadata is written, its payload awaited,
+// converted if the wire is FP8, and one bulk store per destination issued as one bulk group; then the READY
+// flags of row n - kFlagLag are released.
+//
+// Ordering of a row and its READY flag.  The payload leaves through the asynchronous proxy
+// (cp.async.bulk shared -> peer global), all copies of one row in one bulk group of lane 0.
+// `cp.async.bulk.wait_group N` returns to lane 0 only when every group but the N most recent is complete, which
+// includes its global writes having been performed and being visible to lane 0.  `__syncwarp()` then orders that
+// observation before the other lanes' later accesses (it is a barrier with memory ordering among the warp's
+// lanes), and each destination's lane publishes with `st.release.sys`, which is cumulative over what the lane has
+// observed.  The receiver reads the flag with `ld.acquire.sys` and issues `fence.proxy.async` before it reads the
+// row through the asynchronous proxy.  The two-GPU litmus test exercises exactly this chain.
+template <int S>
+__device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health, RoleStats& st) {
+    constexpr int D = S >= 4 ? 2 : 1;
+    constexpr int R = S - D - 1;
+    static_assert(S >= 2 && S <= kMaxSendStages && R >= 0, "2..4 send stages");
+    const DispatchArgs& a = *k.a;
+    const RankConst* rc = k.rc;
+    const SegmentLayout& lay = rc->lay;
+    const unsigned lane = ptx::lane_id();
+    const unsigned full = 0xffffffffu;
+    const unsigned self_bit = 1u << k.me;
+    const bool delayed = w == k.tx_warps - 1;
+    const int moff = k.wire_fp8 ? lay.meta_off_fp8 : lay.meta_off;
+    const unsigned row_bytes = static_cast<unsigned>(moff + lay.meta_bytes);
+    const unsigned payload_bytes = static_cast<unsigned>(k.H) * 2u;
+    unsigned char* const base = k.row_buffers + static_cast<std::size_t>(w) * S * k.slot_bytes;
+    unsigned long long* const bars = &k.sh->mbar[w * S];
+    const std::uint32_t seq_epoch = static_cast<std::uint32_t>(k.epoch) + (rc->test_corrupt_sequence ? 1u : 0u);
+    BEP_ROLE_DECL();
+
+    // candidates of this warp: tokens t0+w, t0+w+tx, ...; their masks are fetched 32 at a time
+    int cand = 0, batch = -1;
+    unsigned batch_mask = 0;
+    int issued = 0;  // rows whose load has been issued
+    auto next_token = [&](TokenRegs& r) -> bool {
+        while (true) {
+            const int t = k.t0 + w + cand * k.tx_warps;
+            if (t >= k.t1) return false;
+            if ((cand >> 5) != batch) {
+                batch = cand >> 5;
+                const int tl = k.t0 + w + (batch * 32 + static_cast<int>(lane)) * k.tx_warps;
+                batch_mask = tl < k.t1 ? a.plan_mask[tl] : 0u;
+            }
+            const unsigned m = __shfl_sync(full, batch_mask, cand & 31) & ~self_bit;
+            ++cand;
+            if (m == 0) continue;
+            r.t = t;
+            r.mask = m;
+            r.j = (lane < static_cast<unsigned>(k.P) && (m >> lane & 1u)) ? a.plan_slot[static_cast<std::size_t>(t) * k.P + lane] : -1;
+            load_token_routes(a, t, k.K, k.E, r.e, r.ord, r.w);
+            // payload into the next buffer of the ring
+            if (lane == 0) {
+                const int b = issued % S;
+                bulk_wait_group_read<R>();
+                std::uint64_t* bar = reinterpret_cast<std::uint64_t*>(&bars[b]);
+                ptx::mbar_expect_tx(bar, payload_bytes);
+                ptx::bulk_g2s(base + static_cast<std::size_t>(b) * k.slot_bytes, a.x + static_cast<std::size_t>(t) * k.H, payload_bytes, bar);
+            }
+            ++issued;
+            return true;
+        }
+    };
+
+    TokenRegs ahead[D];
+    bool ahead_ok[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) ahead_ok[i] = next_token(ahead[i]);
+
+    std::uint64_t* flag_ring[kFlagLag];
+    std::uint32_t flag_seq[kFlagLag];
+#pragma unroll
+    for (int i = 0; i < kFlagLag; ++i) {
+        flag_ring[i] = nullptr;
+        flag_seq[i] = 0;
+    }
+    int n = 0;  // rows sent
+    bool broke = false;
+    while (ahead_ok[0]) {
+        const TokenRegs cur = ahead[0];
+#pragma unroll
+        for (int i = 0; i + 1 < D; ++i) {
+            ahead[i] = ahead[i + 1];
+            ahead_ok[i] = ahead_ok[i + 1];
+        }
+        ahead_ok[D - 1] = ahead_ok[D - 1] ? next_token(ahead[D - 1]) : false;
+
+        unsigned char* buf = base + static_cast<std::size_t>(n % S) * k.slot_bytes;
+        const unsigned parity = static_cast<unsigned>(n / S) & 1u;
+        // destination row of lane d; ring mode first waits for the slot's credit
+        std::uint8_t* dst = nullptr;
+        std::uint64_t* ready = nullptr;
+        if (cur.j >= 0) {
+            const std::size_t ring_index = (static_cast<std::size_t>(k.me) * k.C + k.c) * k.Q + (cur.j % k.Q);
+            dst = rc->seg[lane] + lay.stage_off + ring_index * lay.row_stride;
+            ready = reinterpret_cast<std::uint64_t*>(rc->seg[lane] + lay.ready_off) + ring_index;
+        }
+        if (k.ring) {
+            // Bounded rings: slot j % Q is free once the receiver has acknowledged row j - Q.  The receiver only
+            // sees rows whose READY flags are out, so before this warp settles down to wait for credit it
+            // releases every flag it still holds back.
+            BEP_ROLE_T(t_credit);
+            const bool need = cur.j >= k.Q;
+            const std::uint64_t* ack = nullptr;
+            std::uint64_t want = 0;
+            bool have = true;
+            if (need) {
+                ack = reinterpret_cast<const std::uint64_t*>(k.my_seg + lay.ack_off) +
+                      (static_cast<std::size_t>(lane) * k.C + k.c) * k.Q + (cur.j % k.Q);
+                want = make_seq(k.epoch, static_cast<std::uint32_t>(cur.j - k.Q + 1));
+                have = ptx::ld_acquire_sys(ack) == want;
+            }
+            if (!__all_sync(full, have)) {
+                if (lane == 0) bulk_wait_group<0>();
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < kFlagLag; ++i) {
+                    if (flag_ring[i] != nullptr) ptx::st_release_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
+                    flag_ring[i] = nullptr;
+                }
+                if (!have) {
+                    ++st.credit;
+                    while (ptx::ld_acquire_sys(ack) != want) {
+                        if (health.give_up(kErrCreditWait, lane, cur.j)) break;
+                    }
+                }
+            }
+            BEP_ROLE_ADD(kRoleCreditWaitNs, t_credit);
+        }
+        __syncwarp();
+        if (warp_failed(health)) {
+            broke = true;
+            break;
+        }
+        if (delayed) test_delay(rc->delay_meta_ns);
+        BEP_ROLE_T(t_meta);
+        // BF16 wire: the metadata lies behind the payload and can be written while the payload is still landing
+        if (!k.wire_fp8) write_row_meta(buf + moff, lay, cur.t, 1.0f, seq_epoch, cur.e, cur.ord, cur.w, k.K);
+        BEP_ROLE_ADD(kRoleMetaNs, t_meta);
+        BEP_ROLE_T(t_load);
+        const bool arrived = mbar_wait_bounded(&bars[n % S], parity, health);
+        BEP_ROLE_ADD(kRoleLoadWaitNs, t_load);
+        if (!__all_sync(full, arrived)) {
+            broke = true;
+            break;
+        }
+        if (lane == 0 && k.sh->first_tx_ns == 0) atomicCAS(&k.sh->first_tx_ns, 0ull, ptx::globaltimer_ns());
+        if (delayed) test_delay(rc->delay_tx_ns);
+        if (k.wire_fp8) {
+            BEP_ROLE_T(t_quant);
+            const float scale = quantise_row_in_place(buf, k.H);
+            write_row_meta(buf + moff, lay, cur.t, scale, seq_epoch, cur.e, cur.ord, cur.w, k.K);
+            BEP_ROLE_ADD(kRoleQuantNs, t_quant);
+        }
+        BEP_ROLE_T(t_issue);
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        for (unsigned m = cur.mask; m; m &= m - 1) {
+            std::uint8_t* d = shfl_ptr(dst, __ffs(m) - 1);
+            if (lane == 0) ptx::bulk_s2g(d, buf, row_bytes);
+        }
+        if (lane == 0) ptx::bulk_commit();
+        BEP_ROLE_ADD(kRoleIssueNs, t_issue);
+        // READY flags of the row issued kFlagLag turns ago: its bulk group is complete by now (or is awaited here)
+        if (n >= kFlagLag) {
+            BEP_ROLE_T(t_store);
+            if (lane == 0) bulk_wait_group<kFlagLag>();
+            __syncwarp();
+            if (flag_ring[0] != nullptr) ptx::st_release_sys(flag_ring[0], make_seq(k.epoch, flag_seq[0]));
+            BEP_ROLE_ADD(kRoleStoreWaitNs, t_store);
+            if (w == 0 && lane == 0 && n == kFlagLag) k.prof[kProfFirstTxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
+        }
+#pragma unroll
+        for (int i = 0; i + 1 < kFlagLag; ++i) {
+            flag_ring[i] = flag_ring[i + 1];
+            flag_seq[i] = flag_seq[i + 1];
+        }
+        flag_ring[kFlagLag - 1] = ready;
+        flag_seq[kFlagLag - 1] = static_cast<std::uint32_t>(cur.j + 1);
+        if (lane == 0) {
+            ++st.source;
+            st.deliveries += __popc(cur.mask);
+            st.published += __popc(cur.mask);
+            if (*reinterpret_cast<volatile int*>(&k.sh->prefix_ready) == 0) ++st.early;
+        }
+        BEP_ROLE_COUNT(kRoleRows, 1);
+        ++n;
+    }
+    // drain: the last rows' groups, then their flags in row order
+    {
+        BEP_ROLE_T(t_store);
+        if (lane == 0) bulk_wait_group<0>();
+        __syncwarp();
+        if (!broke && !warp_failed(health)) {
+#pragma unroll
+            for (int i = 0; i < kFlagLag; ++i)
+                if (flag_ring[i] != nullptr) ptx::st_release_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
+            if (w == 0 && lane == 0 && n > 0 && n <= kFlagLag) k.prof[kProfFirstTxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
+        }
+        BEP_ROLE_ADD(kRoleStoreWaitNs, t_store);
+    }
+    // a failed warp leaves with loads still on their way into its buffers: give them a bounded time to land
+    for (int r = n; r < issued; ++r) {
+        unsigned polls = 0;
+        while (!ptx::mbar_try_wait(reinterpret_cast<std::uint64_t*>(&bars[r % S]), static_cast<unsigned>(r / S) & 1u) && ++polls < (1u << 20))
+            ptx::nanosleep(64);
+    }
+    BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(1 + w) * kRoleFields : nullptr);
+}
+
+// ---- send role, register path (16-byte or scalar accesses; also the path for odd hidden sizes) ----
+__device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& health, RoleStats& st) {
+    const DispatchArgs& a = *k.a;
+    const RankConst* rc = k.rc;
+    const SegmentLayout& lay = rc->lay;
+    const unsigned lane = ptx::lane_id();
+    const unsigned self_bit = 1u << k.me;
+    const bool delayed = w == k.tx_warps - 1;
+    unsigned char* meta_sm = k.sh->meta[1 + w];
+    const std::uint32_t seq_epoch = static_cast<std::uint32_t>(k.epoch) + (rc->test_corrupt_sequence ? 1u : 0u);
+    const int moff = k.wire_fp8 ? lay.meta_off_fp8 : lay.meta_off;
+    BEP_ROLE_DECL();
+    int sent = 0;
+    for (int t = k.t0 + w; t < k.t1; t += k.tx_warps) {
+        if (warp_failed(health)) break;
+        const unsigned mask = a.plan_mask[t] & ~self_bit;
+        if (mask == 0) continue;
+        int j = -1;
+        std::uint8_t* dst = nullptr;
+        std::uint64_t* ready = nullptr;
+        if (lane < static_cast<unsigned>(k.P) && (mask >> lane & 1u)) {
+            j = a.plan_slot[static_cast<std::size_t>(t) * k.P + lane];
+            const std::size_t ring_index = (static_cast<std::size_t>(k.me) * k.C + k.c) * k.Q + (j % k.Q);
+            dst = rc->seg[lane] + lay.stage_off + ring_index * lay.row_stride;
+            ready = reinterpret_cast<std::uint64_t*>(rc->seg[lane] + lay.ready_off) + ring_index;
+            if (k.ring && j >= k.Q) {
+                const std::uint64_t* ack = reinterpret_cast<const std::uint64_t*>(k.my_seg + lay.ack_off) +
+                                           (static_cast<std::size_t>(lane) * k.C + k.c) * k.Q + (j % k.Q);
+                const std::uint64_t want = make_seq(k.epoch, static_cast<std::uint32_t>(j - k.Q + 1));
+                bool missed = false;
+                while (ptx::ld_acquire_sys(ack) != want) {
+                    missed = true;
+                    if (health.give_up(kErrCreditWait, lane, j)) break;
+                }
+                if (missed) ++st.credit;
+            }
+        }
+        __syncwarp();
+        if (warp_failed(health)) break;
+        const std::uint8_t* src = reinterpret_cast<const std::uint8_t*>(a.x + static_cast<std::size_t>(t) * k.H);
+        if (delayed) test_delay(rc->delay_meta_ns);
+        int e, ord;
+        float wt;
+        load_token_routes(a, t, k.K, k.E, e, ord, wt);
+        if (lane == 0 && k.sh->first_tx_ns == 0) atomicCAS(&k.sh->first_tx_ns, 0ull, ptx::globaltimer_ns());
+        if (delayed) test_delay(rc->delay_tx_ns);
+        float scale = 1.0f;
+        if (k.wire_fp8) scale = tx_row_fp8(src, dst, mask, -1, k.H, k.vec_ok);
+        else tx_row_bf16(src, dst, mask, k.H, k.vec_ok);
+        write_row_meta(meta_sm, lay, t, scale, seq_epoch, e, ord, wt, k.K);
+        __syncwarp();
+        for (unsigned m = mask; m; m &= m - 1) {
+            std::uint8_t* mdst = shfl_ptr(dst, __ffs(m) - 1) + moff;
+            for (int q = lane; q < lay.meta_bytes / 16; q += 32)
+                ptx::st_v4(mdst + q * 16, *reinterpret_cast<const uint4*>(meta_sm + q * 16));
+        }
+        // every lane's stores, then the warp joins, then one lane per destination releases that row's flag
+        __syncwarp();
+        if (j >= 0) ptx::st_release_sys(ready, make_seq(k.epoch, static_cast<std::uint32_t>(j + 1)));
+        if (lane == 0) {
+            ++st.source;
+            st.deliveries += __popc(mask);
+            st.published += __popc(mask);
+            if (*reinterpret_cast<volatile int*>(&k.sh->prefix_ready) == 0) ++st.early;
+            if (w == 0 && sent == 0) k.prof[kProfFirstTxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
+        }
+        BEP_ROLE_COUNT(kRoleRows, 1);
+        ++sent;
+    }
+    BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(1 + w) * kRoleFields : nullptr);
+}
+
+// ---- receive + expand role ------------------------------------------------------------------------
+// Remote rows: poll the READY flags of this channel's rings (local memory), read a staged row once, check its
+// sequence words, write it to its output rows.  Own rows: whenever no remote row is waiting, take the next own
+// token that has a local expert straight from `x`.
+__device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, RoleStats& st) {
+    const DispatchArgs& a = *k.a;
+    const RankConst* rc = k.rc;
+    const SegmentLayout& lay = rc->lay;
+    const unsigned lane = ptx::lane_id();
+    const unsigned full = 0xffffffffu;
+    const bool delayed = w == k.rx_warps - 1;
+    const int P = k.P, C = k.C, Q = k.Q, K = k.K, H = k.H, me = k.me, c = k.c;
+    BEP_ROLE_DECL();
+    // The control warp owns the diagnosis of a missing counts message (it knows which source is late); this
+    // wait only has to end, so its own deadline is a quarter of the timeout later.
+    health.deadline += rc->timeout_ns / 4;
+    {
+        BEP_ROLE_T(t_prefix);
+        while (*reinterpret_cast<volatile int*>(&k.sh->prefix_ready) == 0) {
+            if (warp_give_up(health, kErrCountsWait, -1, 0)) break;
+        }
+        BEP_ROLE_ADD(kRolePrefixWaitNs, t_prefix);
+    }
+    __threadfence_block();
     __syncwarp();
+    if (!warp_failed(health) && *reinterpret_cast<volatile int*>(&k.sh->prefix_ready) != 0) {
+        int next_j = w;
+        // rows of this rank itself do not come through the ring
+        const int expect = (lane < static_cast<unsigned>(P) && static_cast<int>(lane) != me) ? k.sh->chan_expected[lane] : 0;
+        int t_local = k.t0 + w;
+        const std::uint64_t* ready_base = reinterpret_cast<const std::uint64_t*>(k.my_seg + lay.ready_off);
+        const int buffer_index = k.tx_warps * k.stages + w;
+        unsigned char* my_slot = k.row_buffers + static_cast<std::size_t>(buffer_index) * k.slot_bytes;
+        unsigned long long* my_bar = &k.sh->mbar[buffer_index];
+        unsigned parity = 0;
+        bool stop = false;
+        while (!stop) {
+            const bool pending = next_j < expect;
+            const unsigned pend = __ballot_sync(full, pending);
+            if (pend == 0 && t_local >= k.t1) break;
+            bool hit = false;
+            if (pending) {
+                const std::uint64_t v = ptx::ld_acquire_sys(ready_base + (static_cast<std::size_t>(lane) * C + c) * Q + (next_j % Q));
+                hit = v == make_seq(k.epoch, static_cast<std::uint32_t>(next_j + 1));
+            }
+            const unsigned hits = __ballot_sync(full, hit);
+            // the acquiring lane's observation is ordered before every lane's reads of the row
+            __syncwarp();
+            if (hits == 0 && t_local < k.t1) {
+                // ---- one own token, straight from x ----
+                const int t = t_local;
+                t_local += k.rx_warps;
+                const unsigned mask = a.plan_mask[t];
+                if ((mask >> me & 1u) == 0) continue;
+                const int j = a.plan_slot[static_cast<std::size_t>(t) * P + me];
+                int e, ord;
+                float wgt;
+                load_token_routes(a, t, K, k.E, e, ord, wgt);
+                const std::uint8_t* src = reinterpret_cast<const std::uint8_t*>(a.x + static_cast<std::size_t>(t) * H);
+                std::uint8_t* out_ptr = nullptr;
+                int n_rows = 0;
+                if (k.use_tma) {
+                    BEP_ROLE_T(t_drain);
+                    if (lane == 0) {
+                        ptx::bulk_wait_read_all();  // the previous row's stores have left the buffer
+                        ptx::mbar_expect_tx(reinterpret_cast<std::uint64_t*>(my_bar), static_cast<unsigned>(H) * 2u);
+                        ptx::bulk_g2s(my_slot, src, static_cast<unsigned>(H) * 2u, reinterpret_cast<std::uint64_t*>(my_bar));
+                    }
+                    BEP_ROLE_ADD(kRoleStoreWaitNs, t_drain);
+                    BEP_ROLE_T(t_load);
+                    const bool arrived = mbar_wait_bounded(my_bar, parity, health);
+                    parity ^= 1u;
+                    BEP_ROLE_ADD(kRoleLoadWaitNs, t_load);
+                    if (!__all_sync(full, arrived)) break;
+                    float scale = 1.0f;
+                    if (k.recv_fp8) {
+                        scale = quantise_row_in_place(my_slot, H);
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                    }
+                    BEP_ROLE_T(t_meta);
+                    const bool overflow = place_row(k, me, j, t, scale, e, ord, wgt, out_ptr, n_rows);
+                    BEP_ROLE_ADD(kRoleMetaNs, t_meta);
+                    if (overflow) {
+                        if (lane == 0) record_error(rc, a.error, kErrCapacity, me, j);
+                        break;
+                    }
+                    if (delayed) test_delay(rc->delay_scatter_ns);
+                    for (int i = 0; i < n_rows; ++i) {
+                        std::uint8_t* dst = shfl_ptr(out_ptr, i);
+                        if (lane == 0) ptx::bulk_s2g(dst, my_slot, static_cast<unsigned>(k.out_row_bytes));
+                    }
+                    if (lane == 0) ptx::bulk_commit();
+                } else {
+                    const float scale = k.recv_fp8 ? row_scale_from_global(src, H, k.vec_ok) : 1.0f;
+                    const bool overflow = place_row(k, me, j, t, scale, e, ord, wgt, out_ptr, n_rows);
+                    if (overflow) {
+                        if (lane == 0) record_error(rc, a.error, kErrCapacity, me, j);
+                        break;
+                    }
+                    if (delayed) test_delay(rc->delay_scatter_ns);
+                    if (k.recv_fp8) tx_row_fp8(src, out_ptr, n_rows >= 32 ? full : (1u << n_rows) - 1u, -1, H, k.vec_ok);
+                    else rx_row_scatter(src, false, 1.0f, out_ptr, n_rows, H, k.vec_ok);
+                }
+                if (lane == 0) ++st.local;
+                BEP_ROLE_COUNT(kRoleLocalRows, 1);
+                BEP_ROLE_COUNT(kRoleRows, 1);
+                continue;
+            }
+            if (hits == 0) {
+                BEP_ROLE_T(t_idle);
+                ++st.probes;
+                const bool give_up = warp_give_up(health, kErrRowWait, __ffs(pend) - 1, 0);
+                BEP_ROLE_ADD(kRoleIdlePollNs, t_idle);
+                if (give_up) break;
+                continue;
+            }
+            for (unsigned hm = hits; hm && !stop; hm &= hm - 1) {
+                const int s = __ffs(hm) - 1;
+                const int j = __shfl_sync(full, next_j, s);
+                if (lane == static_cast<unsigned>(s)) next_j += k.rx_warps;
+                const bool fp8row = k.wire_fp8;
+                const std::size_t ring_index = (static_cast<std::size_t>(s) * C + c) * Q + (j % Q);
+                const std::uint8_t* row_src = k.my_seg + lay.stage_off + ring_index * lay.row_stride;
+                const int moff = fp8row ? lay.meta_off_fp8 : lay.meta_off;
+                if (delayed) test_delay(rc->delay_rx_ns);
+                const unsigned char* meta;
+                if (k.use_tma) {
+                    ptx::fence_proxy_async();
+                    BEP_ROLE_T(t_drain);
+                    if (lane == 0) {
+                        const unsigned bytes = static_cast<unsigned>(moff + lay.meta_bytes);
+                        ptx::bulk_wait_read_all();  // the previous row's stores have left the buffer
+                        ptx::mbar_expect_tx(reinterpret_cast<std::uint64_t*>(my_bar), bytes);
+                        ptx::bulk_g2s(my_slot, row_src, bytes, reinterpret_cast<std::uint64_t*>(my_bar));
+                    }
+                    BEP_ROLE_ADD(kRoleStoreWaitNs, t_drain);
+                    BEP_ROLE_T(t_load);
+                    const bool arrived = mbar_wait_bounded(my_bar, parity, health);
+                    parity ^= 1u;
+                    BEP_ROLE_ADD(kRoleLoadWaitNs, t_load);
+                    if (!__all_sync(full, arrived)) {
+                        stop = true;
+                        break;
+                    }
+                    meta = my_slot + moff;
+                } else {
+                    meta = row_src + moff;
+                }
+                BEP_ROLE_T(t_meta);
+                // metadata -> registers
+                int token, seq_epoch, seq_index;
+                float scale;
+                if (k.use_tma) {
+                    token = reinterpret_cast<const int*>(meta)[0];
+                    scale = reinterpret_cast<const float*>(meta)[1];
+                    seq_epoch = reinterpret_cast<const int*>(meta)[2];
+                    seq_index = reinterpret_cast<const int*>(meta)[3];
+                } else {
+                    token = ptx::ld_volatile(reinterpret_cast<const int*>(meta));
+                    scale = __int_as_float(ptx::ld_volatile(reinterpret_cast<const int*>(meta) + 1));
+                    seq_epoch = ptx::ld_volatile(reinterpret_cast<const int*>(meta) + 2);
+                    seq_index = ptx::ld_volatile(reinterpret_cast<const int*>(meta) + 3);
+                }
+                int e = -1, ord = 0;
+                float wgt = 0.0f;
+                if (lane < static_cast<unsigned>(K)) {
+                    const int* mi = reinterpret_cast<const int*>(meta + 16);
+                    if (k.use_tma) {
+                        e = mi[lane];
+                        ord = mi[K + lane];
+                        wgt = __int_as_float(mi[2 * K + lane]);
+                    } else {
+                        e = ptx::ld_volatile(mi + lane);
+                        ord = ptx::ld_volatile(mi + K + lane);
+                        wgt = __int_as_float(ptx::ld_volatile(mi + 2 * K + lane));
+                    }
+                }
+                __syncwarp();
+                // the payload behind a READY flag must be the one of this epoch and of the token its header names
+                if (static_cast<std::uint32_t>(seq_epoch) != static_cast<std::uint32_t>(k.epoch) ||
+                    static_cast<std::uint32_t>(seq_index) != static_cast<std::uint32_t>(token) + 1u || token < 0 ||
+                    token >= lay.num_max_tokens) {
+                    if (lane == 0) record_error(rc, a.error, kErrSequence, s, j);
+                    stop = true;
+                    break;
+                }
+                std::uint8_t* out_ptr = nullptr;
+                int n_rows = 0;
+                const bool overflow = place_row(k, s, j, token, scale, e, ord, wgt, out_ptr, n_rows);
+                BEP_ROLE_ADD(kRoleMetaNs, t_meta);
+                if (overflow) {
+                    if (lane == 0) record_error(rc, a.error, kErrCapacity, s, j);
+                    stop = true;
+                    break;
+                }
+                if (delayed) test_delay(rc->delay_scatter_ns);
+                std::uint64_t* ack = reinterpret_cast<std::uint64_t*>(rc->seg[s] + lay.ack_off) +
+                                     (static_cast<std::size_t>(me) * C + c) * Q + (j % Q);
+                if (!k.use_tma) {
+                    if (k.recv_fp8) rx_row_copy_bytes(row_src, out_ptr, n_rows, H);
+                    else rx_row_scatter(row_src, fp8row, scale, out_ptr, n_rows, H, k.vec_ok);
+                    if (k.ring) {
+                        __syncwarp();
+                        if (lane == 0) ptx::st_release_sys(ack, make_seq(k.epoch, static_cast<std::uint32_t>(j + 1)));
+                    }
+                } else {
+                    // the row is in shared memory: its ring slot can be handed back already
+                    if (k.ring && lane == 0) ptx::st_release_sys(ack, make_seq(k.epoch, static_cast<std::uint32_t>(j + 1)));
+                    if (fp8row && !k.recv_fp8) {
+                        BEP_ROLE_T(t_quant);
+                        // widen in place, decreasing order: chunk q is read before anything lands on it
+                        const int chunks = H / 8;
+                        for (int q0 = (chunks - 1) / 32 * 32; q0 >= 0; q0 -= 32) {
+                            const int q = q0 + lane;
+                            uint2 f = make_uint2(0, 0);
+                            if (q < chunks) f = *reinterpret_cast<const uint2*>(my_slot + q * 8);
+                            __syncwarp();
+                            if (q < chunks) *reinterpret_cast<uint4*>(my_slot + q * 16) = chunk_from_fp8(f, scale);
+                            __syncwarp();
+                        }
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        BEP_ROLE_ADD(kRoleQuantNs, t_quant);
+                    }
+                    BEP_ROLE_T(t_issue);
+                    for (int i = 0; i < n_rows; ++i) {
+                        std::uint8_t* dst = shfl_ptr(out_ptr, i);
+                        if (lane == 0) ptx::bulk_s2g(dst, my_slot, static_cast<unsigned>(k.out_row_bytes));
+                    }
+                    if (lane == 0) ptx::bulk_commit();
+                    BEP_ROLE_ADD(kRoleIssueNs, t_issue);
+                }
+                if (lane == 0) ++st.remote_rows;
+                BEP_ROLE_COUNT(kRoleRows, 1);
+                if (w == 0 && lane == 0 && k.prof[kProfFirstRxRow] == 0) k.prof[kProfFirstRxRow] = static_cast<std::int64_t>(ptx::globaltimer_ns());
+            }
+        }
+        if (w == 0 && lane == 0) k.prof[kProfRxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
+    }
+    BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(1 + k.tx_warps + w) * kRoleFields : nullptr);
 }
 
 }  // namespace detail
@@ -351,7 +1035,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     const SegmentLayout& lay = rc->lay;
 
     const int P = lay.num_ranks, C = lay.num_channels, E = lay.num_experts, El = lay.num_local_experts;
-    const int K = lay.num_topk, H = lay.hidden, Q = lay.slots, Qf = lay.slots_full;
+    const int K = lay.num_topk, H = lay.hidden;
     const int me = rc->rank, c = blockIdx.x;
     const int T = a.num_tokens;
     const int Tc = (T + C - 1) / C;
@@ -361,13 +1045,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     const unsigned lt_mask = (1u << lane) - 1u;
     const unsigned full = 0xffffffffu;
     const int tx_warps = rc->tx_warps, rx_warps = rc->rx_warps;
-    const bool vec_ok = rc->vec_ok != 0, use_tma = rc->use_tma != 0, wire_fp8 = rc->wire_fp8 != 0;
-    const bool recv_fp8 = rc->recv_fp8 != 0;  // rows stay E4M3 at the receiver (scales in recv_scale); implies wire_fp8
-    const int bypass_rank = recv_fp8 ? -1 : me;  // the rank whose own copy stays BF16 under an FP8 wire
+    const bool vec_ok = rc->vec_ok != 0, use_tma = rc->use_tma != 0;
+    const bool recv_fp8 = rc->recv_fp8 != 0;  // rows stay E4M3 at the receiver (scales in recv_scale); implies an FP8 wire
     const std::size_t out_row_bytes = static_cast<std::size_t>(H) * (recv_fp8 ? 1 : 2);
     std::uint8_t* const recv_bytes = reinterpret_cast<std::uint8_t*>(a.recv_x);
-    const bool ring = rc->ring_mode != 0;
-    const int map_stride = 2 + 2 * K;
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     auto* sh = reinterpret_cast<DispatchShared*>(smem_raw);
@@ -382,8 +1063,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                                         16);
     int* msg_sm = reinterpret_cast<int*>(smem_raw + msg_at);  // [P][counts_stride]: every source's counts message
     const std::size_t slots_at = align_up(msg_at + static_cast<std::size_t>(P) * lay.counts_stride * 4, 128);
-    const int slot_bytes = static_cast<int>(align_up(lay.meta_off + lay.meta_bytes, 128));
-    unsigned char* my_slot = smem_raw + slots_at + static_cast<std::size_t>(warp > 0 ? warp - 1 : 0) * slot_bytes;
 
     Health health(rc, a.error);
     const std::uint64_t epoch = rc->epochs[0] + 1;
@@ -407,7 +1086,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         sh->first_tx_ns = 0;
         sh->last_tx_ns = 0;
         if (use_tma) {
-            for (int w = 0; w < kMaxWarps; ++w) ptx::mbar_init(reinterpret_cast<std::uint64_t*>(&sh->mbar[w]), 1);
+            for (int b = 0; b < kMaxRowBuffers; ++b) ptx::mbar_init(reinterpret_cast<std::uint64_t*>(&sh->mbar[b]), 1);
             ptx::mbar_fence_init();
         }
     }
@@ -419,8 +1098,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     }
 
     // Reuse guard: nothing of this epoch may reach a peer before that peer has finished reading the
-    // previous epoch out of its segment (reference: the counts_consumed == epoch-1 wait of
-    // advanced_begin_epoch, advanced_layout.cuh:9-89).  The flags are local; the wait is normally free.
+    // previous epoch out of its segment.  The flags are local; the wait is normally free.
     if (warp == 0 && lane < static_cast<unsigned>(P)) {
         const std::uint64_t* done = flag_ptr(my_seg, lay.done_off, lane);
         while (ptx::ld_acquire_sys(done) + 1 < epoch) {
@@ -433,8 +1111,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     }
 
     // ---- phase A: routing layout (skipped with a cached plan) ------------------------------------
-    // (reference: advanced_route_flags + advanced_stable_ordinals + advanced_prepare_channels_parallel,
-    //  advanced_layout.cuh:287-425; here O(T*K) with one barrier instead of O((P+E)*T) block scans)
+    // O(T*K) work with one grid barrier: per-channel histograms, a prefix over channels, then ballots inside
+    // 32-token chunks give every (token, bin) its stable ordinal.
     if (!a.cached) {
         for (int i = threadIdx.x; i < E; i += blockDim.x) {
             cnt_e[i] = 0;
@@ -501,8 +1179,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         __syncthreads();
     }
     // Two things happen side by side before the roles split: warp 1 tells every destination what to
-    // expect (counts message; reference: publish_counts, layout.cuh:7-29 -- channel d, d+C, ... serves
-    // destination d), warp 0 numbers this channel's tokens.
+    // expect (counts message; channel d, d+C, ... serves destination d), warp 0 numbers this channel's tokens.
     if (warp == 1 && !rc->test_withhold_counts) {
         for (int d = c; d < P; d += C) {
             int* msg = reinterpret_cast<int*>(rc->seg[d] + lay.counts_off) + static_cast<std::size_t>(me) * lay.counts_stride;
@@ -572,12 +1249,30 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     if (threadIdx.x == 0) BEP_PROF(kProfRolesSplit);
 
     // ---- role split ------------------------------------------------------------------------------
-    unsigned long long st_source = 0, st_remote_rows = 0, st_deliveries = 0, st_early = 0, st_probes = 0,
-                       st_credit = 0, st_local = 0, st_published = 0;
+    Ctx k;
+    k.a = &a;
+    k.rc = rc;
+    k.sh = sh;
+    k.eoff = eoff;
+    k.spre = spre;
+    k.row_buffers = smem_raw + slots_at;
+    k.my_seg = my_seg;
+    k.recv_bytes = recv_bytes;
+    k.prof = prof;
+    k.role_prof = a.role_profile ? a.role_profile + static_cast<std::size_t>(c) * kMaxWarps * kRoleFields : nullptr;
+    k.out_row_bytes = out_row_bytes;
+    k.epoch = epoch;
+    k.slot_bytes = static_cast<int>(align_up(lay.meta_off + lay.meta_bytes, 128));
+    k.stages = rc->send_stages;
+    k.P = P; k.C = C; k.E = E; k.El = El; k.K = K; k.H = H; k.Q = lay.slots; k.Qf = lay.slots_full;
+    k.me = me; k.c = c; k.t0 = t0; k.t1 = t1; k.tx_warps = tx_warps; k.rx_warps = rx_warps;
+    k.map_stride = 2 + 2 * K;
+    k.vec_ok = vec_ok; k.use_tma = use_tma; k.wire_fp8 = rc->wire_fp8 != 0; k.recv_fp8 = recv_fp8;
+    k.ring = rc->ring_mode != 0;
+    RoleStats st;
 
     if (warp == 0) {
-        // ===== control: receive prefix (reference: advanced_prepare_receive_prefixes,
-        // advanced_layout.cuh:94-195), then zero padding =====
+        // ===== control: receive prefix from every source's counts message, then zero padding =====
         const unsigned long long prefix_t0 = ptx::globaltimer_ns();
         if (lane < static_cast<unsigned>(P)) {
             const std::uint64_t* flag = flag_ptr(my_seg, lay.counts_flag_off, lane);
@@ -673,8 +1368,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                 *reinterpret_cast<volatile int*>(&sh->prefix_ready) = 1;
                 BEP_PROF(kProfPrefixReady);
             }
-            // zero padding between expert segments (reference: advanced_zero_padding,
-            // advanced_layout.cuh:250-265): channel c takes local experts c, c+C, ...
+            // zero padding between expert segments: channel c takes local experts c, c+C, ...
             if (a.do_expand && a.zero_padding && !warp_failed(health)) {
                 for (int el = c; el < El; el += C) {
                     for (int row = eoff[el] + ecount[el]; row < eoff[el + 1]; ++row) {
@@ -693,304 +1387,37 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                 }
             }
         }
+        // test hook: this rank publishes an abort in mid-transfer (a legal owner writing its own abort flag)
+        if (c == 0 && rc->test_abort_after_ns != 0 && !warp_failed(health)) {
+            while (ptx::globaltimer_ns() < t_start + rc->test_abort_after_ns) ptx::nanosleep(200);
+            if (lane == 0) record_error(rc, a.error, kErrInjectedAbort, me, 0);
+        }
     } else if (warp <= tx_warps) {
         // ===== send =====
         const int w = warp - 1;
-        unsigned parity = 0;
-        unsigned char* meta_sm = use_tma ? my_slot + lay.meta_off : sh->meta[warp];
-        const unsigned self_bit = 1u << me;
-        const bool delayed = (w == tx_warps - 1);
-        for (int i = w; t0 + i < t1; i += tx_warps) {
-            if (warp_failed(health)) break;
-            const int t = t0 + i;
-            const unsigned mask = a.plan_mask[t];
-            if (mask == 0) continue;
-            // destination row of lane d; ring mode first waits for the slot's credit
-            int j = -1;
-            std::uint8_t* dst = nullptr;
-            std::uint64_t* ready = nullptr;
-            if (lane < static_cast<unsigned>(P) && (mask >> lane & 1u)) {
-                j = a.plan_slot[static_cast<std::size_t>(t) * P + lane];
-                const std::size_t ring_index = (static_cast<std::size_t>(me) * C + c) * Q + (j % Q);
-                dst = rc->seg[lane] + lay.stage_off + ring_index * lay.row_stride;
-                ready = reinterpret_cast<std::uint64_t*>(rc->seg[lane] + lay.ready_off) + ring_index;
-                if (ring && j >= Q) {
-                    const std::uint64_t* ack = reinterpret_cast<const std::uint64_t*>(my_seg + lay.ack_off) +
-                                               (static_cast<std::size_t>(lane) * C + c) * Q + (j % Q);
-                    const std::uint64_t want = make_seq(epoch, static_cast<std::uint32_t>(j - Q + 1));
-                    bool missed = false;
-                    while (ptx::ld_acquire_sys(ack) != want) {
-                        missed = true;
-                        if (health.give_up(kErrCreditWait, lane, j)) break;
-                    }
-                    if (missed) ++st_credit;
-                }
-            }
-            __syncwarp();
-            if (warp_failed(health)) break;
-            const std::uint8_t* src = reinterpret_cast<const std::uint8_t*>(a.x + static_cast<std::size_t>(t) * H);
-            std::uint64_t* bar = reinterpret_cast<std::uint64_t*>(&sh->mbar[warp]);
-            if (use_tma && lane == 0) {
-                ptx::mbar_expect_tx(bar, static_cast<unsigned>(H) * 2);
-                ptx::bulk_g2s(my_slot, src, static_cast<unsigned>(H) * 2, bar);
-            }
-            // metadata: header | expert[K] | ordinal[K] | weight[K]
-            if (delayed) test_delay(rc->delay_meta_ns);
-            if (lane == 0) {
-                reinterpret_cast<int*>(meta_sm)[0] = t;
-                reinterpret_cast<float*>(meta_sm)[1] = 1.0f;
-                reinterpret_cast<int*>(meta_sm)[2] = 0;
-                reinterpret_cast<int*>(meta_sm)[3] = 0;
-            }
-            for (int k = lane; k < K; k += 32) {
-                const std::int64_t e = a.topk_idx[static_cast<std::size_t>(t) * K + k];
-                reinterpret_cast<int*>(meta_sm + 16)[k] = (e >= 0 && e < E) ? static_cast<int>(e) : -1;
-                reinterpret_cast<int*>(meta_sm + 16)[K + k] = a.plan_expert_ord[static_cast<std::size_t>(t) * K + k];
-                reinterpret_cast<float*>(meta_sm + 16)[2 * K + k] =
-                    a.topk_w ? a.topk_w[static_cast<std::size_t>(t) * K + k] : 1.0f;
-            }
-            for (int b = 16 + 12 * K + lane; b < lay.meta_bytes; b += 32) meta_sm[b] = 0;
-            __syncwarp();
-            if (lane == 0 && sh->first_tx_ns == 0) atomicCAS(&sh->first_tx_ns, 0ull, ptx::globaltimer_ns());
-            if (delayed) test_delay(rc->delay_tx_ns);
-            if (!use_tma) {
-                float scale = 1.0f;
-                if (wire_fp8 && (recv_fp8 || (mask & ~self_bit))) scale = tx_row_fp8(src, dst, mask, bypass_rank, H, vec_ok);
-                else tx_row_bf16(src, dst, mask, H, vec_ok);
-                if (lane == 0) reinterpret_cast<float*>(meta_sm)[1] = scale;
-                __syncwarp();
-                for (unsigned m = mask; m; m &= m - 1) {
-                    const int d = __ffs(m) - 1;
-                    std::uint8_t* row = shfl_ptr(dst, d);
-                    std::uint8_t* mdst = row + ((wire_fp8 && d != bypass_rank) ? lay.meta_off_fp8 : lay.meta_off);
-                    for (int q = lane; q < lay.meta_bytes / 16; q += 32)
-                        ptx::st_v4(mdst + q * 16, *reinterpret_cast<const uint4*>(meta_sm + q * 16));
-                }
-            } else {
-                const bool arrived = mbar_wait_bounded(&sh->mbar[warp], parity, health);
-                parity ^= 1u;
-                if (!__all_sync(full, arrived)) break;
-                tx_token_tma(lay, my_slot, dst, mask, bypass_rank, wire_fp8);
-            }
-            __syncwarp();
-            // publish: READY of this row at every destination (one lane per destination releases)
-            if (j >= 0) ptx::st_release_sys(ready, make_seq(epoch, static_cast<std::uint32_t>(j + 1)));
-            if (lane == 0) {
-                if (mask & ~self_bit) {
-                    ++st_source;
-                    st_deliveries += __popc(mask & ~self_bit);
-                }
-                if (mask & self_bit) ++st_local;
-                st_published += __popc(mask);
-                if (*reinterpret_cast<volatile int*>(&sh->prefix_ready) == 0) ++st_early;
-                if (w == 0 && st_published == static_cast<unsigned long long>(__popc(mask))) BEP_PROF(kProfFirstTxDone);
-            }
-        }
+        if (!use_tma) send_role_vector(k, w, health, st);
+        else if (k.stages >= 4) send_role_bulk<4>(k, w, health, st);
+        else if (k.stages == 3) send_role_bulk<3>(k, w, health, st);
+        else send_role_bulk<2>(k, w, health, st);
         if (lane == 0) atomicMax(&sh->last_tx_ns, ptx::globaltimer_ns());
         if (w == 0 && lane == 0) BEP_PROF(kProfTxDone);
     } else {
         // ===== receive + expand =====
-        const int w = warp - 1 - tx_warps;
-        const bool delayed = (w == rx_warps - 1);
-        // The control warp owns the diagnosis of a missing counts message (it knows which source is
-        // late); this wait only has to end, so its own deadline is a quarter of the timeout later.
-        health.deadline += rc->timeout_ns / 4;
-        while (*reinterpret_cast<volatile int*>(&sh->prefix_ready) == 0) {
-            if (warp_give_up(health, kErrCountsWait, -1, 0)) break;
-        }
-        __threadfence_block();
-        __syncwarp();
-        if (!warp_failed(health) && *reinterpret_cast<volatile int*>(&sh->prefix_ready) != 0) {
-            int next_j = w;
-            const int expect = lane < static_cast<unsigned>(P) ? sh->chan_expected[lane] : 0;
-            const std::uint64_t* ready_base = reinterpret_cast<const std::uint64_t*>(my_seg + lay.ready_off);
-            unsigned parity = 0;
-            std::uint64_t* bar = reinterpret_cast<std::uint64_t*>(&sh->mbar[warp]);
-            while (true) {
-                const bool pending = lane < static_cast<unsigned>(P) && next_j < expect;
-                const unsigned pend = __ballot_sync(full, pending);
-                if (pend == 0) break;
-                bool hit = false;
-                if (pending) {
-                    const std::uint64_t v =
-                        ptx::ld_acquire_sys(ready_base + (static_cast<std::size_t>(lane) * C + c) * Q + (next_j % Q));
-                    hit = v == make_seq(epoch, static_cast<std::uint32_t>(next_j + 1));
-                }
-                const unsigned hits = __ballot_sync(full, hit);
-                if (hits == 0) {
-                    ++st_probes;
-                    if (warp_give_up(health, kErrRowWait, __ffs(pend) - 1, 0)) break;
-                    continue;
-                }
-                bool stop = false;
-                for (unsigned hm = hits; hm && !stop; hm &= hm - 1) {
-                    const int s = __ffs(hm) - 1;
-                    const int j = __shfl_sync(full, next_j, s);
-                    if (lane == static_cast<unsigned>(s)) next_j += rx_warps;
-                    const bool fp8row = wire_fp8 && s != bypass_rank;
-                    const std::size_t ring_index = (static_cast<std::size_t>(s) * C + c) * Q + (j % Q);
-                    const std::uint8_t* row_src = my_seg + lay.stage_off + ring_index * lay.row_stride;
-                    const int moff = fp8row ? lay.meta_off_fp8 : lay.meta_off;
-                    if (delayed) test_delay(rc->delay_rx_ns);
-                    const unsigned char* meta;
-                    if (use_tma) {
-                        ptx::fence_proxy_async();
-                        if (lane == 0) {
-                            const unsigned bytes = static_cast<unsigned>(moff + lay.meta_bytes);
-                            ptx::bulk_wait_read_all();  // the previous row's stores have left the buffer
-                            ptx::mbar_expect_tx(bar, bytes);
-                            ptx::bulk_g2s(my_slot, row_src, bytes, bar);
-                        }
-                        const bool arrived = mbar_wait_bounded(&sh->mbar[warp], parity, health);
-                        parity ^= 1u;
-                        if (!__all_sync(full, arrived)) {
-                            stop = true;
-                            break;
-                        }
-                        meta = my_slot + moff;
-                    } else {
-                        meta = row_src + moff;
-                    }
-                    // metadata -> registers
-                    int token;
-                    float scale;
-                    if (use_tma) {
-                        token = reinterpret_cast<const int*>(meta)[0];
-                        scale = reinterpret_cast<const float*>(meta)[1];
-                    } else {
-                        token = ptx::ld_volatile(reinterpret_cast<const int*>(meta));
-                        scale = __int_as_float(ptx::ld_volatile(reinterpret_cast<const int*>(meta) + 1));
-                    }
-                    int e = -1, ord = 0;
-                    float wgt = 0.0f;
-                    if (lane < static_cast<unsigned>(K)) {
-                        const int* mi = reinterpret_cast<const int*>(meta + 16);
-                        if (use_tma) {
-                            e = mi[lane];
-                            ord = mi[K + lane];
-                            wgt = __int_as_float(mi[2 * K + lane]);
-                        } else {
-                            e = ptx::ld_volatile(mi + lane);
-                            ord = ptx::ld_volatile(mi + K + lane);
-                            wgt = __int_as_float(ptx::ld_volatile(mi + 2 * K + lane));
-                        }
-                    }
-                    __syncwarp();
-                    const bool local = e >= 0 && e / El == me;
-                    const int el = local ? e - me * El : -1;
-                    const unsigned lmask = __ballot_sync(full, local);
-                    const int n_local = __popc(lmask);
-                    const int pos = __popc(lmask & lt_mask);
-                    int* map = a.comb_map + ((static_cast<std::size_t>(s) * C + c) * Qf + j) * map_stride;
-                    // output rows: lane i < n_rows holds row pointer i
-                    std::uint8_t* out_ptr = nullptr;
-                    int n_rows;
-                    bool overflow = false;
-                    if (a.do_expand) {
-                        n_rows = n_local;
-                        int row = -1;
-                        if (local) {
-                            row = eoff[el] + spre[s * El + el] + ord;
-                            overflow = row < 0 || row >= rc->expanded_cap;
-                        }
-                        // compact: the i-th local slot's row goes to lane i
-                        for (unsigned lm = lmask, i = 0; lm; lm &= lm - 1, ++i) {
-                            const int r = __shfl_sync(full, row, __ffs(lm) - 1);
-                            if (lane == i) out_ptr = recv_bytes + static_cast<std::size_t>(r) * out_row_bytes;
-                        }
-                        if (local && !overflow) {
-                            if (recv_fp8) a.recv_scale[row] = scale;
-                            a.recv_idx[row] = el;
-                            a.recv_w[row] = wgt;
-                            a.source_meta[static_cast<std::size_t>(row) * 3 + 0] = s;
-                            a.source_meta[static_cast<std::size_t>(row) * 3 + 1] = token;
-                            a.source_meta[static_cast<std::size_t>(row) * 3 + 2] = lane;
-                            map[2 + 2 * pos] = row;
-                            map[3 + 2 * pos] = __float_as_int(wgt);
-                        }
-                    } else {
-                        n_rows = 1;
-                        const int row = sh->source_offsets[s] + sh->chan_base[s] + j;
-                        overflow = row >= rc->unique_cap;
-                        if (lane == 0) out_ptr = recv_bytes + static_cast<std::size_t>(row) * out_row_bytes;
-                        if (!overflow) {
-                            if (recv_fp8 && lane == 0) a.recv_scale[row] = scale;
-                            if (lane < static_cast<unsigned>(K)) {
-                                a.recv_idx[static_cast<std::size_t>(row) * K + lane] = el;
-                                a.recv_w[static_cast<std::size_t>(row) * K + lane] = local ? wgt : 0.0f;
-                            }
-                            if (lane == 0) {
-                                a.source_meta[static_cast<std::size_t>(row) * 3 + 0] = s;
-                                a.source_meta[static_cast<std::size_t>(row) * 3 + 1] = token;
-                                a.source_meta[static_cast<std::size_t>(row) * 3 + 2] = -1;
-                                map[2] = row;
-                                map[3] = __float_as_int(1.0f);
-                            }
-                        }
-                    }
-                    if (lane == 0) {
-                        map[0] = token;
-                        map[1] = a.do_expand ? n_local : 1;
-                    }
-                    if (__any_sync(full, overflow)) {
-                        if (lane == 0) record_error(rc, a.error, kErrCapacity, s, j);
-                        stop = true;
-                        break;
-                    }
-                    if (delayed) test_delay(rc->delay_scatter_ns);
-                    std::uint64_t* ack = reinterpret_cast<std::uint64_t*>(rc->seg[s] + lay.ack_off) +
-                                         (static_cast<std::size_t>(me) * C + c) * Q + (j % Q);
-                    if (!use_tma) {
-                        if (recv_fp8) rx_row_copy_bytes(row_src, out_ptr, n_rows, H);
-                        else rx_row_scatter(row_src, fp8row, scale, out_ptr, n_rows, H, vec_ok);
-                        if (ring) {
-                            __syncwarp();
-                            if (lane == 0) ptx::st_release_sys(ack, make_seq(epoch, static_cast<std::uint32_t>(j + 1)));
-                        }
-                    } else {
-                        // the row is in shared memory: its ring slot can be handed back already
-                        if (ring && lane == 0) ptx::st_release_sys(ack, make_seq(epoch, static_cast<std::uint32_t>(j + 1)));
-                        if (fp8row && !recv_fp8) {
-                            // widen in place, decreasing order: chunk q is read before anything lands on it
-                            const int chunks = H / 8;
-                            for (int q0 = (chunks - 1) / 32 * 32; q0 >= 0; q0 -= 32) {
-                                const int q = q0 + lane;
-                                uint2 f = make_uint2(0, 0);
-                                if (q < chunks) f = *reinterpret_cast<const uint2*>(my_slot + q * 8);
-                                __syncwarp();
-                                if (q < chunks) *reinterpret_cast<uint4*>(my_slot + q * 16) = chunk_from_fp8(f, scale);
-                                __syncwarp();
-                            }
-                            ptx::fence_proxy_async_smem();
-                            __syncwarp();
-                        }
-                        for (int i = 0; i < n_rows; ++i) {
-                            std::uint8_t* dst = shfl_ptr(out_ptr, i);
-                            if (lane == 0) ptx::bulk_s2g(dst, my_slot, static_cast<unsigned>(out_row_bytes));
-                        }
-                        if (lane == 0) ptx::bulk_commit();
-                    }
-                    if (lane == 0 && s != me) ++st_remote_rows;
-                    if (w == 0 && lane == 0 && prof[kProfFirstRxRow] == 0) BEP_PROF(kProfFirstRxRow);
-                }
-                if (stop) break;
-            }
-            if (w == 0 && lane == 0) BEP_PROF(kProfRxDone);
-        }
+        receive_role(k, warp - 1 - tx_warps, health, st);
     }
 
     // ---- epilogue ----------------------------------------------------------------------------------
     __syncwarp();
     if (lane == 0) {
         if (use_tma) ptx::bulk_wait_all();
-        atomicAdd(&sh->stat[kStatSourceTokens], st_source);
-        atomicAdd(&sh->stat[kStatRemoteRows], st_remote_rows);
-        atomicAdd(&sh->stat[kStatDeliveries], st_deliveries);
-        atomicAdd(&sh->stat[kStatEarlyRows], st_early);
-        atomicAdd(&sh->stat[kStatRxEmptyProbes], st_probes);
-        atomicAdd(&sh->stat[kStatCreditMisses], st_credit);
-        atomicAdd(&sh->stat[kStatLocalRows], st_local);
-        atomicAdd(&sh->stat[kStatRowsPublished], st_published);
+        atomicAdd(&sh->stat[kStatSourceTokens], st.source);
+        atomicAdd(&sh->stat[kStatRemoteRows], st.remote_rows);
+        atomicAdd(&sh->stat[kStatDeliveries], st.deliveries);
+        atomicAdd(&sh->stat[kStatEarlyRows], st.early);
+        atomicAdd(&sh->stat[kStatRxEmptyProbes], st.probes);
+        atomicAdd(&sh->stat[kStatCreditMisses], st.credit);
+        atomicAdd(&sh->stat[kStatLocalRows], st.local);
+        atomicAdd(&sh->stat[kStatRowsPublished], st.published);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -1005,8 +1432,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         __threadfence();
         const unsigned long long old = atomicAdd(&rc->done_ctas[0], 1ull);
         if ((old + 1) % static_cast<unsigned long long>(C) == 0) {
-            // last channel of this rank: statistics (reference: advanced_reduce_statistics,
-            // advanced_layout.cuh:267-283), hand the staging area back to every source, advance the epoch
+            // last channel of this rank: sum the per-channel statistics, hand the staging area back to every
+            // source, advance the epoch
             __threadfence();
             std::int64_t sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             std::int64_t first = INT64_MAX, last = 0;
@@ -1026,6 +1453,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             rc->epochs[0] = epoch;
         }
     }
+#undef BEP_PROF
 }
 
 #endif  // __CUDACC__

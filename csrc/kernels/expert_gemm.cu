@@ -453,8 +453,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const ScatterTarget& sc = p.scatter;
         ptx::fence_sys();
         const unsigned long long finished = atomicAdd(sc.cta_done, 1ull) + 1ull;
-        if (finished == sc.epoch * gridDim.x) {
-            // last CTA of this launch: all rows of all CTAs are written; tell every owner (unless something gave up)
+        if (finished == gridDim.x) {
+            // last CTA of this launch: all rows of all CTAs are written; tell every owner (unless something gave up).
+            // Launches that share the counter are stream-ordered, so the next one finds it at zero again.
+            *sc.cta_done = 0ull;
             ptx::fence_sys();
             if (*reinterpret_cast<volatile int*>(p.status) == 0) {
                 for (int r = 0; r < sc.num_ranks; ++r)

@@ -10,13 +10,14 @@
 
 namespace bep {
 
-std::size_t dispatch_shared_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma) {
-    return dispatch_smem_bytes(lay, tx_warps, rx_warps, use_tma);
+std::size_t dispatch_shared_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma, int stages) {
+    return dispatch_smem_bytes(lay, tx_warps, rx_warps, use_tma, stages);
 }
 
+bool role_profiling_enabled() { return BEP_ENABLE_PROFILING != 0; }
+
 cudaError_t configure_kernels(std::size_t dispatch_smem) {
-    // One attribute per kernel per process: several buffers may be alive, so only ever raise it
-    // (reference: configure_shared_memory, csrc/buffers/advanced.hpp:339-365).
+    // One attribute per kernel per process: several buffers may be alive, so only ever raise it.
     static std::mutex mutex;
     static std::size_t current[64] = {0};
     std::lock_guard<std::mutex> guard(mutex);
@@ -92,8 +93,8 @@ cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_
     return cooperative_launch(combine_kernel, launch, dim3(channels, launch.num_virtual, 1), kCombineWarps * 32, smem, stream);
 }
 
-cudaError_t launch_local_combine(const LocalCombineArgs& args, int ctas, cudaStream_t stream) {
-    local_combine_kernel<<<ctas, kFusedReduceThreads, 0, stream>>>(args);
+cudaError_t launch_combine_push(const CombinePushArgs& args, int ctas, cudaStream_t stream) {
+    combine_push_kernel<<<ctas, kFusedReduceThreads, 0, stream>>>(args);
     return cudaGetLastError();
 }
 

@@ -11,8 +11,8 @@
 
 namespace bep {
 
-// Shared-memory bytes the dispatch kernel needs for this configuration.
-std::size_t dispatch_shared_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma);
+// Shared-memory bytes the dispatch kernel needs for this configuration (`stages` row buffers per send warp).
+std::size_t dispatch_shared_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma, int stages);
 
 // Raise (never lower) the kernels' dynamic shared-memory limit; thread-safe, idempotent.
 cudaError_t configure_kernels(std::size_t dispatch_smem_bytes);
@@ -26,10 +26,10 @@ cudaError_t launch_dispatch(const DispatchLaunch& launch, int channels, int thre
                             cudaStream_t stream);
 cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_t crow_stride, cudaStream_t stream);
 
-// Owner-side reduction of the fused down-projection + combine; `ctas` must be the same for every launch of one
-// runtime (completion is counted monotonically).
-// Single-rank combine as one ordinary launch (no peers, nothing staged).
-cudaError_t launch_local_combine(const LocalCombineArgs& args, int ctas, cudaStream_t stream);
+// Ordinary launches of the combine paths: expert-side gather-reduce-push, owner-side sum.  Any grid size works.
+cudaError_t launch_combine_push(const CombinePushArgs& args, int ctas, cudaStream_t stream);
 cudaError_t launch_fused_reduce(const FusedReduceArgs& args, int ctas, cudaStream_t stream);
+// True when the library was built with the per-role instrumentation (-DBEP_ENABLE_PROFILING=1).
+bool role_profiling_enabled();
 
 }  // namespace bep

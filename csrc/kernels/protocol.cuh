@@ -1,8 +1,9 @@
 // Shared-memory ABI of the peer transport: limits, error codes, the symmetric segment layout,
-// per-rank constants, kernel argument blocks, bounded waits and the intra-rank grid barrier.
+// per-rank constants, kernel argument blocks, bounded waits and the intra-rank grid barrier
+// (parity: the reference's mapped-host-memory ABI, csrc/kernels/host_staged/common.cuh:61-158 and
+// advanced_common.cuh:15-129).
 //
-// What the reference keeps in mapped host memory (csrc/kernels/host_staged/common.cuh:61-158,
-// advanced_common.cuh:15-129) lives here in one *symmetric segment* per rank: the same layout
+// All shared state lives in one *symmetric segment* per rank: the same layout
 // at the same offsets on every rank, reachable from every peer through `RankConst::seg[]`.
 // The segment is HBM mapped over NVLink for transport "peer" and registered host memory for
 // transport "host_staged"; the kernels do not care which.
@@ -37,9 +38,13 @@ constexpr int kMaxVirtualRanks = 8;
 constexpr int kMaxAlignment = 256;
 constexpr int kMaxWarps = 16;  // 1 control + send + receive warps per channel CTA
 constexpr int kFlagStride = 32;  // bytes between small per-rank flags (one sector each)
+constexpr int kMaxSendStages = 4;   // shared-memory row buffers per send warp
+constexpr int kMaxRowBuffers = 40;  // send warps x stages + receive warps of one channel CTA
+constexpr int kRoleFieldCount = 16; // counters per warp in a profiling build
 
-// Error codes; the numbers that also exist in the reference keep its values
-// (csrc/kernels/host_staged/common.cuh:26-38).
+inline int dispatch_row_buffer_count(int tx_warps, int rx_warps, int stages) { return tx_warps * stages + rx_warps; }
+
+// Error codes (2, 11, 12, 15, 16, 18, 19 and 20 keep the numbers DeepEP-style callers already know).
 enum ErrorCode : int {
     kOk = 0,
     kErrInvalidRouting = 2,    // context = token, detail = slot
@@ -56,6 +61,7 @@ enum ErrorCode : int {
     kErrCopyEngine = 24,       // a bulk copy never completed
     kErrFusedSignalWait = 25,  // fused down-projection + combine: a peer's GEMM never signalled (context = peer)
     kErrFusedGemm = 26,        // fused down-projection + combine: this rank's GEMM gave up (detail = its status word)
+    kErrInjectedAbort = 27,    // the abort-after test hook fired on this rank
 };
 
 enum StatField : int {
@@ -76,7 +82,7 @@ __host__ __device__ inline std::uint64_t make_seq(std::uint64_t epoch, std::uint
 }
 
 // Per-row metadata that travels behind the payload.  16 + 12*K bytes, K = top-k.
-//   int32 src_token; float scale; int32 reserved[2];
+//   int32 src_token; float scale; uint32 seq_epoch (low word of the dispatch epoch); uint32 seq_index (src_token + 1);
 //   int32 expert[K] (global id or -1); int32 expert_ordinal[K]; float weight[K];
 __host__ __device__ inline int meta_bytes_for(int topk) { return static_cast<int>(align_up(16 + 12 * topk, 16)); }
 
@@ -173,6 +179,7 @@ struct RankConst {
     int use_tma;       // rows move with cp.async.bulk through shared memory
     int vec_ok;        // hidden*2 is a multiple of 16: 16-byte accesses are legal on rows
     int tx_warps, rx_warps;
+    int send_stages;   // shared-memory row buffers per send warp (bulk-copy engine): 2, 3 or 4
     int unique_cap, expanded_cap;
     int slot_smem_bytes;  // shared-memory bytes of one row buffer (TMA path)
     std::uint64_t timeout_ns;
@@ -187,6 +194,8 @@ struct RankConst {
     std::uint64_t delay_meta_ns, delay_tx_ns, delay_rx_ns, delay_scatter_ns, delay_prefix_ns;
     int test_skip_done_to;      // -1, else: do not publish `done` to this peer (mailbox-timeout test)
     int test_withhold_counts;   // != 0: never publish the counts message (prefix-timeout test)
+    int test_corrupt_sequence;  // != 0: this rank's send warps write a wrong sequence into their rows (sequence-check test)
+    std::uint64_t test_abort_after_ns;  // != 0: the control warp of channel 0 publishes an abort this long after the launch started
 };
 
 // One dispatch of one (virtual) rank.
@@ -225,6 +234,7 @@ struct DispatchArgs {
     std::int64_t* timestamps;      // [2] transport start / end (globaltimer ns)
     std::int64_t* prefix_tx_ts;    // [C+1][2]
     std::int64_t* profile;         // [C][16] per-channel phase timestamps (globaltimer ns), see ProfilePoint
+    std::int64_t* role_profile;    // [C][kMaxWarps][16] per-warp role counters (profiling builds only), or nullptr
 };
 
 // Phase timestamps every channel CTA leaves behind (one store each; always on).
@@ -260,8 +270,6 @@ struct CombineArgs {
     const std::uint32_t* plan_mask;  // [Tmax] of this rank's own tokens
     int num_tokens;               // this rank's own token count at dispatch
     int weighted;                 // apply dispatch-time weights (expanded layout)
-    int split;                    // != 0: only the expert side runs here (rows pushed, csig published by the last CTA);
-                                  // the owner-side sum is a separate, fully occupied kernel (fused_reduce.cuh)
     __nv_bfloat16* out;           // [T, H]
     int* error;                   // [8]
     std::int64_t* stats;          // [8]
@@ -272,6 +280,27 @@ struct CombineLaunch {
     int num_virtual;
     CombineArgs r[kMaxVirtualRanks];
 };
+
+// ---- ABI checks ----------------------------------------------------------------------------
+// The host runtime (plain C++) fills these blocks and the kernels (nvcc) read them; a peer's kernels interpret
+// this rank's segment with their own copy of SegmentLayout.  Pin sizes and key offsets so that a change on one
+// side of either boundary cannot go unnoticed, and keep the by-value launch blocks inside the 4 KB kernel
+// parameter space.
+static_assert(sizeof(SegmentLayout) == 200 && offsetof(SegmentLayout, relay_off) == 120 &&
+                  offsetof(SegmentLayout, num_ranks) == 128 && offsetof(SegmentLayout, has_fused) == 192,
+              "SegmentLayout ABI changed");
+static_assert(sizeof(RankConst) == 496 && offsetof(RankConst, seg) == 200 && offsetof(RankConst, rank) == 328 &&
+                  offsetof(RankConst, timeout_ns) == 376 && offsetof(RankConst, epochs) == 384 &&
+                  offsetof(RankConst, delay_meta_ns) == 432 && offsetof(RankConst, test_abort_after_ns) == 488,
+              "RankConst ABI changed");
+static_assert(sizeof(DispatchArgs) == 248 && offsetof(DispatchArgs, plan_mask) == 56 &&
+                  offsetof(DispatchArgs, recv_x) == 88 && offsetof(DispatchArgs, role_profile) == 240,
+              "DispatchArgs ABI changed");
+static_assert(sizeof(CombineArgs) == 80, "CombineArgs ABI changed");
+static_assert(sizeof(DispatchLaunch) <= 4096 && sizeof(CombineLaunch) <= 4096, "launch blocks must fit the kernel parameter space");
+static_assert(16 + 12 * kMaxTopk <= 400, "row metadata of the largest top-k must fit its shared-memory staging area");
+static_assert(kMaxRanks <= 32, "one lane per rank");
+static_assert(kMaxTopk <= 32, "one lane per top-k slot");
 
 #ifdef __CUDACC__
 

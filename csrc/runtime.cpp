@@ -1,4 +1,4 @@
-// Python bindings of the native runtime (counterpart of the reference's csrc/runtime.cu:8-29).
+// Python bindings of the native runtime (parity: the reference's csrc/runtime.cu:8-29).
 #include <torch/extension.h>
 
 #include "buffers/runtime.hpp"
@@ -141,13 +141,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              py::arg("alignment"), py::arg("expand"), py::arg("zero_padding"), py::arg("cached"), py::arg("graph_pool"),
              py::arg("stream") = 0)
         .def("combine", &Runtime::combine, py::arg("y"), py::arg("dispatch_result"), py::arg("weighted"), py::arg("out"),
-             py::arg("stream") = 0)
+             py::arg("stream") = 0, py::arg("num_sms") = 0)
         .def("fused_scatter_gemm", &Runtime::fused_scatter_gemm, py::arg("hidden_rows"), py::arg("w_down"),
              py::arg("dispatch_result"), py::arg("stream") = 0)
         .def("fused_reduce", &Runtime::fused_reduce, py::arg("dispatch_result"), py::arg("out"), py::arg("stream") = 0)
         .def("fused_status", &Runtime::fused_status)
         .def("combine_is_split", &Runtime::combine_is_split)
         .def("combine_is_local", &Runtime::combine_is_local)
+        .def("combine_is_inline", &Runtime::combine_is_inline)
+        .def("send_stages", &Runtime::send_stages)
+        .def("set_test_corrupt_sequence", &Runtime::set_test_corrupt_sequence)
+        .def("set_test_control_abort_after_ns", &Runtime::set_test_control_abort_after_ns)
         .def("pool_debug", &Runtime::pool_debug)
         .def("set_test_delays", &Runtime::set_test_delays)
         .def("set_test_prefix_delay_ns", &Runtime::set_test_prefix_delay_ns)
@@ -225,6 +229,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         if (error != nullptr) throw std::runtime_error(std::string("litmus: ") + error);
     });
 
+    m.def("role_profiling_enabled", &role_profiling_enabled);
     m.def("dispatch_group", &dispatch_group);
     m.def("combine_group", &combine_group);
 }

@@ -24,8 +24,9 @@ from typing import List
 
 _ROOT = Path(__file__).resolve().parents[1]
 _CSRC = _ROOT / "csrc"
-_EXT_DIR = Path(__file__).resolve().parent / "_ext"
 _PROFILE = os.getenv("PCIE_EP_B200_PROFILE", "0") == "1"
+# the instrumented library is built in a directory of its own so that the two builds never share object files
+_EXT_DIR = Path(__file__).resolve().parent / "_ext" / "prof" if _PROFILE else Path(__file__).resolve().parent / "_ext"
 _NAME = "pcie_ep_b200_cuda_prof" if _PROFILE else "pcie_ep_b200_cuda"
 
 SOURCES: List[Path] = [
@@ -81,7 +82,7 @@ def build(verbose: bool = False) -> Path:
     """Compile the extension for sm_100a into ``pcie_ep_b200/_ext`` (no GPU needed)."""
     from torch.utils.cpp_extension import load
 
-    _EXT_DIR.mkdir(exist_ok=True)
+    _EXT_DIR.mkdir(parents=True, exist_ok=True)
     # torch would otherwise add -gencode flags from its own arch list; an empty list plus the
     # explicit flag above gives exactly one target: sm_100a.
     previous = os.environ.get("TORCH_CUDA_ARCH_LIST")

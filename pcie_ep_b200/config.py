@@ -90,7 +90,7 @@ class HostStagedConfig:
     directory: Optional[str] = None
     numa_mode: str = "direct"
     warp_specialization: bool = True
-    pipeline_stages: int = 2
+    pipeline_stages: int = 3
     fuse_receive_expand: bool = True
     source_fusion: bool = True
     wire_dtype: str = "bf16"
@@ -108,7 +108,7 @@ class HostStagedConfig:
     transport: str = "auto"
     copy_engine: str = "tma"
     tx_warps: int = 2
-    rx_warps: int = 10
+    rx_warps: int = 8
     enable_combine: bool = True
     recv_dtype: str = "bf16"
     fused_expert_combine: bool = False
@@ -125,8 +125,8 @@ class HostStagedConfig:
             raise ValueError("stages 1-5 are retired; stage must be 6, 7 or 8")
         if not isinstance(self.channels, int) or not 1 <= self.channels <= MAX_CHANNELS:
             raise ValueError(f"channels must be an integer in [1, {MAX_CHANNELS}]")
-        if self.pipeline_stages not in (2, 3):
-            raise ValueError("pipeline_stages must be 2 or 3")
+        if self.pipeline_stages not in (2, 3, 4):
+            raise ValueError("pipeline_stages counts the row buffers of a send warp and must be 2, 3 or 4")
         if self.receive_expand_mode not in ("scalar", "vectorized", "pipelined"):
             raise ValueError("receive_expand_mode must be 'scalar', 'vectorized' or 'pipelined'")
         if self.receive_expand_mode != "scalar":
@@ -188,7 +188,7 @@ class HostStagedConfig:
         if num_ranks < 1 or num_max_tokens_per_rank < 1:
             raise ValueError("num_ranks and num_max_tokens_per_rank must be positive")
         channels = 32 if num_max_tokens_per_rank <= 256 else 64 if num_max_tokens_per_rank <= 1024 else 128
-        settings = dict(channels=channels, tx_warps=4 if num_ranks == 1 else 2, rx_warps=10)
+        settings = dict(channels=channels, tx_warps=2, rx_warps=8, pipeline_stages=3)
         settings.update(overrides)
         return cls(**settings)
 

@@ -16,7 +16,7 @@ def test_defaults_are_valid_and_frozen():
     (dict(stage=5), ValueError),
     (dict(channels=0), ValueError),
     (dict(channels=129), ValueError),
-    (dict(pipeline_stages=4), ValueError),
+    (dict(pipeline_stages=5), ValueError),
     (dict(receive_expand_mode="fast"), ValueError),
     (dict(receive_expand_mode="pipelined", fuse_receive_expand=False), ValueError),
     (dict(wire_dtype="fp4"), ValueError),
@@ -69,9 +69,9 @@ def test_tuned_settings_by_size():
     from pcie_ep_b200 import HostStagedConfig
 
     one = HostStagedConfig.tuned(1, 4096)
-    assert (one.channels, one.tx_warps, one.rx_warps) == (128, 4, 10)
+    assert (one.channels, one.tx_warps, one.rx_warps, one.pipeline_stages) == (128, 2, 8, 3)
     eight = HostStagedConfig.tuned(8, 128, timeout_ms=1234)
-    assert (eight.channels, eight.tx_warps, eight.rx_warps, eight.timeout_ms) == (32, 2, 10, 1234)
+    assert (eight.channels, eight.tx_warps, eight.rx_warps, eight.timeout_ms) == (32, 2, 8, 1234)
     assert HostStagedConfig.tuned(4, 1024).channels == 64
     assert HostStagedConfig.tuned(2, 4096, channels=16).channels == 16
     import pytest

@@ -106,6 +106,8 @@ def test_dispatch_and_combine_never_synchronise_the_host(ext):
         inside = [e.name for e in events if e.time_range.start >= lo and e.time_range.end <= hi]
         forbidden = [n for n in inside if "Synchronize" in n or n in ("aten::item", "aten::_local_scalar_dense") or "DtoH" in n]
         assert not forbidden, forbidden
-        kernels = [e.name for e in events if "dispatch_kernel" in e.name or "combine_kernel" in e.name]
-        assert len([k for k in kernels if "dispatch_kernel" in k]) >= 5 and len([k for k in kernels if "combine_kernel" in k]) >= 5
+        kernels = [e.name for e in events if "dispatch_kernel" in e.name or "combine_push_kernel" in e.name]
+        assert len([k for k in kernels if "dispatch_kernel" in k]) >= 5 and len([k for k in kernels if "combine_push_kernel" in k]) >= 5
+        # the payload path is this library's own kernels: no NCCL kernel runs inside the region
+        assert not [e.name for e in events if "nccl" in e.name.lower()]
         buffer.check_errors()
