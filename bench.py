@@ -56,6 +56,8 @@ def parse_args():
     p.add_argument("--tx-warps", type=int, default=0, help="send warps per channel CTA (0: by rank count)")
     p.add_argument("--rx-warps", type=int, default=0, help="receive/expand warps per channel CTA (0: by rank count)")
     p.add_argument("--combine-reduce", default="auto", choices=["auto", "separate", "inline"])
+    p.add_argument("--send-ctas", type=int, default=-1, help="dedicated sender CTAs (-1: by rank count)")
+    p.add_argument("--stages", type=int, default=0, help="row buffers per send warp (0: tuned)")
     p.add_argument("--no-numa-bind", action="store_true", help="leave the process on whatever CPUs it was started on")
     return p.parse_args()
 
@@ -248,7 +250,8 @@ def run_ours(args, rank, world, local_rank):
         config = HostStagedConfig(channels=channels, stage=7 if args.wire != "bf16" else 6, wire_dtype=args.wire,
                                   copy_engine=args.engine, transport=args.transport, timeout_ms=20000,
                                   output_pool_size=2, tx_warps=args.tx_warps or tuned.tx_warps, rx_warps=args.rx_warps or tuned.rx_warps,
-                                  combine_reduce=args.combine_reduce)
+                                  combine_reduce=args.combine_reduce, send_ctas=args.send_ctas,
+                                  pipeline_stages=args.stages or tuned.pipeline_stages)
         buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
         launches_per_step = 3 if buffer.runtime.combine_is_split() else 2  # dispatch, combine (+ its owner-side sum)
         g = torch.Generator().manual_seed(1234 + rank)

@@ -55,6 +55,7 @@ struct RuntimeOptions {
     int tx_warps = 2;
     int rx_warps = 8;
     int send_stages = 3;
+    int send_ctas = -1;  // dedicated sender CTAs; -1: by channel count with more than one rank, none with one
     int output_pool_size = 3;
     bool enable_graph = false;
     bool enable_combine = true;
@@ -78,6 +79,7 @@ struct RuntimeOptions {
         o.tx_warps = get("tx_warps", o.tx_warps);
         o.rx_warps = get("rx_warps", o.rx_warps);
         o.send_stages = get("pipeline_stages", o.send_stages);
+        o.send_ctas = get("send_ctas", o.send_ctas);
         o.output_pool_size = get("output_pool_size", o.output_pool_size);
         o.enable_graph = get("enable_graph", o.enable_graph);
         o.enable_combine = get("enable_combine", o.enable_combine);
@@ -90,6 +92,7 @@ struct RuntimeOptions {
         if (o.channels < 1 || o.channels > kMaxChannels) throw std::invalid_argument("channels out of range");
         if (o.tx_warps < 1 || o.rx_warps < 1 || 1 + o.tx_warps + o.rx_warps > kMaxWarps)
             throw std::invalid_argument("1 + tx_warps + rx_warps must not exceed 16");
+        if (o.send_ctas < -1 || o.send_ctas > 64) throw std::invalid_argument("send_ctas must be -1 (automatic) or in [0,64]");
         if (o.send_stages < 2 || o.send_stages > kMaxSendStages) throw std::invalid_argument("pipeline_stages must be 2, 3 or 4");
         if (o.output_pool_size < 2 || o.output_pool_size > 8) throw std::invalid_argument("output_pool_size must be in [2,8]");
         if (o.timeout_ms < 1) throw std::invalid_argument("timeout_ms must be positive");
@@ -256,27 +259,33 @@ class Runtime {
         c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
         lay_ = make_segment_layout(num_ranks, options_.channels, num_experts, num_topk, hidden, num_max_tokens,
                                    options_.payload_slots, options_.enable_combine, options_.enable_fused);
+        // automatic choice: one sender CTA per eight channels, at most sixteen (sixteen SMs saturate NVLink)
+        if (options_.send_ctas < 0) options_.send_ctas = num_ranks > 1 ? std::min(16, std::max(1, options_.channels / 8)) : 0;
+        if (num_ranks == 1) options_.send_ctas = 0;  // nothing leaves a single rank
         const bool vec_ok = (hidden * 2) % 16 == 0;
         use_tma_ = options_.use_tma && vec_ok && !(options_.recv_fp8 && hidden % 16 != 0);
-        threads_ = 32 * (1 + options_.tx_warps + options_.rx_warps);
-        if (dispatch_row_buffer_count(options_.tx_warps, options_.rx_warps, options_.send_stages) > kMaxRowBuffers)
-            throw std::invalid_argument("tx_warps * pipeline_stages + rx_warps exceeds the row buffers a channel CTA can manage");
-        smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, use_tma_, options_.send_stages);
+        if (dispatch_row_buffer_count(options_.tx_warps, options_.rx_warps, options_.send_stages, options_.send_ctas) > kMaxRowBuffers)
+            throw std::invalid_argument("tx_warps * pipeline_stages + rx_warps exceeds the row buffers a CTA can manage");
+        if (dispatch_cta_warps(options_.tx_warps, options_.rx_warps, options_.send_ctas) > kMaxWarps)
+            throw std::invalid_argument("too many warps per CTA: at most 16");
+        smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, use_tma_, options_.send_stages, options_.send_ctas);
         int max_optin = 0;
         cuda_check(cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device), "query shared memory");
         // too many row buffers for this hidden size: give up send stages first, then receive warps, and only
         // then fall back to the register path
         while (use_tma_ && smem_ > static_cast<std::size_t>(max_optin)) {
             if (options_.send_stages > 2) --options_.send_stages;
+            else if (options_.send_ctas > 0 && options_.tx_warps * options_.send_stages > options_.rx_warps && options_.tx_warps > 1) --options_.tx_warps;
             else if (options_.rx_warps > 2) --options_.rx_warps;
             else break;
-            smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, true, options_.send_stages);
+            smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, true, options_.send_stages, options_.send_ctas);
         }
         if (use_tma_ && smem_ > static_cast<std::size_t>(max_optin)) {
             use_tma_ = false;
-            smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, false, options_.send_stages);
+            smem_ = dispatch_shared_bytes(lay_, options_.tx_warps, options_.rx_warps, false, options_.send_stages, options_.send_ctas);
         }
-        threads_ = 32 * (1 + options_.tx_warps + options_.rx_warps);
+        threads_ = 32 * dispatch_cta_warps(options_.tx_warps, options_.rx_warps, options_.send_ctas);
+        grid_ctas_ = options_.channels + options_.send_ctas;
         if (smem_ > static_cast<std::size_t>(max_optin)) throw std::runtime_error("dispatch kernel needs more shared memory than the device offers");
         cuda_check(configure_kernels(smem_), "configure kernels");
 
@@ -289,7 +298,8 @@ class Runtime {
         done_ctas_ = at::zeros({2}, i64);
         block_hist_ = at::zeros({static_cast<std::int64_t>(C) * (E + P)}, i32);
         sticky_ = at::zeros({8}, i32);
-        chan_stats_ = at::zeros({2, C, 10}, i64);
+        chan_stats_ = at::zeros({2, C + options_.send_ctas, 10}, i64);
+        plan_flags_ = at::zeros({C}, i64);
         rank_const_ = at::zeros({static_cast<std::int64_t>(sizeof(RankConst))}, u8);
 
         rc_ = RankConst{};
@@ -304,6 +314,8 @@ class Runtime {
         rc_.tx_warps = options_.tx_warps;
         rc_.rx_warps = options_.rx_warps;
         rc_.send_stages = options_.send_stages;
+        rc_.send_ctas = options_.send_ctas;
+        rc_.plan_flags = reinterpret_cast<std::uint64_t*>(plan_flags_.data_ptr<std::int64_t>());
         rc_.unique_cap = P * num_max_tokens;
         rc_.expanded_cap = P * num_max_tokens * std::min(K, lay_.num_local_experts) + lay_.num_local_experts * 255;
         rc_.timeout_ns = static_cast<std::uint64_t>(options_.timeout_ms) * 1000000ull;
@@ -340,6 +352,8 @@ class Runtime {
     // ---- geometry -----------------------------------------------------------------------------
     int rank() const { return rank_; }
     int channels() const { return options_.channels; }
+    int send_ctas() const { return options_.send_ctas; }
+    int grid_ctas() const { return grid_ctas_; }
     int threads() const { return threads_; }
     std::size_t shared_bytes() const { return smem_; }
     bool uses_tma() const { return use_tma_; }
@@ -422,7 +436,7 @@ class Runtime {
         launch.r[0] = p.args;
         cudaStream_t launch_stream = stream != 0 ? reinterpret_cast<cudaStream_t>(stream)
                                                  : at::cuda::getCurrentCUDAStream(device_).stream();
-        cuda_check(launch_dispatch(launch, options_.channels, threads_, smem_, launch_stream), "dispatch launch");
+        cuda_check(launch_dispatch(launch, grid_ctas_, threads_, smem_, launch_stream), "dispatch launch");
         return p.result;
     }
 
@@ -738,13 +752,14 @@ class Runtime {
         s.error = at::zeros({8}, i32);
         s.stats = at::zeros({8}, i64);
         s.timestamps = at::zeros({2}, i64);
-        s.prefix_tx_ts = at::zeros({C + 1, 2}, i64);
+        const std::int64_t ctas = grid_ctas_;  // channel CTAs, then the dedicated senders
+        s.prefix_tx_ts = at::zeros({ctas + 1, 2}, i64);
         s.combine_error = at::zeros({8}, i32);
         s.combine_stats = at::zeros({8}, i64);
-        s.profile = at::zeros({C, 16}, i64);
+        s.profile = at::zeros({ctas, 16}, i64);
         s.combine_profile = at::zeros({C, 8}, i64);
         // per-warp role counters exist only in a library built with the role instrumentation
-        s.role_profile = role_profiling_enabled() ? at::zeros({C, kMaxWarps, kRoleFieldCount}, i64) : at::zeros({0, kMaxWarps, kRoleFieldCount}, i64);
+        s.role_profile = role_profiling_enabled() ? at::zeros({ctas, kMaxWarps, kRoleFieldCount}, i64) : at::zeros({0, kMaxWarps, kRoleFieldCount}, i64);
         return s;
     }
 
@@ -807,7 +822,8 @@ class Runtime {
     bool use_tma_ = false;
     int threads_ = 0;
     std::size_t smem_ = 0;
-    at::Tensor epochs_, grid_bar_, done_ctas_, block_hist_, sticky_, chan_stats_, rank_const_;
+    at::Tensor epochs_, grid_bar_, done_ctas_, block_hist_, sticky_, chan_stats_, plan_flags_, rank_const_;
+    int grid_ctas_ = 0;
     std::vector<std::shared_ptr<OutputSet>> pools_;
     std::vector<std::shared_ptr<Layout>> plans_;
     std::vector<at::Tensor> combine_pool_;
@@ -827,15 +843,15 @@ inline void launch_dispatch_group(const std::vector<std::shared_ptr<Runtime>>& r
     DispatchLaunch launch{};
     launch.num_virtual = static_cast<int>(runtimes.size());
     for (std::size_t i = 0; i < runtimes.size(); ++i) {
-        if (runtimes[i]->channels() != runtimes[0]->channels() || runtimes[i]->threads() != runtimes[0]->threads() ||
+        if (runtimes[i]->grid_ctas() != runtimes[0]->grid_ctas() || runtimes[i]->threads() != runtimes[0]->threads() ||
             runtimes[i]->shared_bytes() != runtimes[0]->shared_bytes())
             throw std::invalid_argument("virtual ranks must share one configuration");
         launch.r[i] = prepared[i].args;
     }
     const int resident = dispatch_resident_ctas(runtimes[0]->threads(), runtimes[0]->shared_bytes());
-    if (runtimes[0]->channels() * launch.num_virtual > resident)
-        throw std::runtime_error("channels * virtual_ranks exceeds the number of co-resident CTAs on this GPU");
-    cuda_check(launch_dispatch(launch, runtimes[0]->channels(), runtimes[0]->threads(), runtimes[0]->shared_bytes(),
+    if (runtimes[0]->grid_ctas() * launch.num_virtual > resident)
+        throw std::runtime_error("(channels + send_ctas) * virtual_ranks exceeds the number of co-resident CTAs on this GPU");
+    cuda_check(launch_dispatch(launch, runtimes[0]->grid_ctas(), runtimes[0]->threads(), runtimes[0]->shared_bytes(),
                                at::cuda::getCurrentCUDAStream(device)),
                "dispatch launch");
 }

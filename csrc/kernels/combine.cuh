@@ -328,7 +328,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
     __syncthreads();
     if (threadIdx.x == 0) {
         prof[4] = static_cast<std::int64_t>(ptx::globaltimer_ns());
-        std::int64_t* cs = rc->chan_stats + static_cast<std::size_t>(C + c) * 10;  // second half: combine
+        const int stat_base = C + rc->send_ctas;  // second half of the per-CTA statistics: combine
+        std::int64_t* cs = rc->chan_stats + static_cast<std::size_t>(stat_base + c) * 10;
         for (int i = 0; i < 3; ++i) cs[i] = static_cast<std::int64_t>(stat[i]);
         __threadfence();
         const unsigned long long old = atomicAdd(&rc->done_ctas[1], 1ull);
@@ -336,7 +337,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32, 1) combine_kernel(const __
             __threadfence();
             std::int64_t sum[3] = {0, 0, 0};
             for (int c2 = 0; c2 < C; ++c2)
-                for (int i = 0; i < 3; ++i) sum[i] += __ldcg(rc->chan_stats + static_cast<std::size_t>(C + c2) * 10 + i);
+                for (int i = 0; i < 3; ++i) sum[i] += __ldcg(rc->chan_stats + static_cast<std::size_t>(stat_base + c2) * 10 + i);
             for (int i = 0; i < 8; ++i) a.stats[i] = i < 3 ? sum[i] : 0;
             if (!health.failed()) {
                 for (int p = 0; p < P; ++p) ptx::st_release_sys(flag_ptr(rc->seg[p], lay.cdone_off, me), epoch);

@@ -2,9 +2,11 @@
 // validation, stable ordinals, the counts exchange, the all-to-all itself, receive-side expansion into
 // per-expert rows, local-token handling, zero padding and statistics.
 //
-// Grid: (channels, virtual_ranks).  blockIdx.y picks the rank (more than one only when several
-// ranks are emulated on one GPU), blockIdx.x the channel.  Channel c of a rank sends that rank's
-// tokens [c*ceil(T/C), (c+1)*ceil(T/C)) and receives what channel c of every rank sent to it.
+// Grid: (channels + send_ctas, virtual_ranks).  blockIdx.y picks the rank (more than one only when several
+// ranks are emulated on one GPU).  blockIdx.x < channels is a channel CTA: channel c of a rank owns that rank's
+// tokens [c*ceil(T/C), (c+1)*ceil(T/C)) and receives what channel c of every rank sent to it.  The CTAs beyond
+// are dedicated senders: each pushes the remote rows of the channels c == its index (mod send_ctas).  With
+// send_ctas == 0 the send warps sit inside every channel CTA instead.
 //
 // Warp roles inside a channel CTA:
 //   warp 0              control: reuse guard, stable ordinals, receive prefix, zero padding
@@ -56,16 +58,19 @@ struct DispatchShared {
 // Dynamic shared memory: header | cnt_e[E] | bits_e[E] | total_e[E] | eoff[El+1] | ecount[El] |
 // spre[P*El] | msg[P*counts_stride] | (bulk-copy engine only) `stages` row buffers per send warp and one
 // per receive warp.
-inline std::size_t dispatch_smem_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma, int stages) {
+inline std::size_t dispatch_smem_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma, int stages,
+                                       int send_ctas) {
     std::size_t bytes = align_up(sizeof(DispatchShared), 16);
     bytes += static_cast<std::size_t>(lay.num_experts) * 12;
     bytes += static_cast<std::size_t>(lay.num_local_experts) * 8 + 4;
     bytes += static_cast<std::size_t>(lay.num_ranks) * lay.num_local_experts * 4;
     bytes = align_up(bytes, 16) + static_cast<std::size_t>(lay.num_ranks) * lay.counts_stride * 4;
     bytes = align_up(bytes, 128);
-    if (use_tma)
-        bytes += static_cast<std::size_t>(dispatch_row_buffer_count(tx_warps, rx_warps, stages)) *
+    if (use_tma) {
+        bytes += static_cast<std::size_t>(dispatch_row_buffer_count(tx_warps, rx_warps, stages, send_ctas)) *
                  align_up(lay.meta_off + lay.meta_bytes, 128);
+        bytes += static_cast<std::size_t>(tx_warps) * 32 * (lay.num_ranks + 3 * lay.num_topk) * 4;  // send warps' metadata tiles
+    }
     return bytes;
 }
 
@@ -338,6 +343,7 @@ struct Ctx {
     int* eoff;                   // [El+1] aligned offsets of the local experts (valid once prefix_ready)
     int* spre;                   // [P][El] rows of earlier sources inside each expert segment
     unsigned char* row_buffers;  // bulk-copy engine: first row buffer
+    int* send_tiles;             // bulk-copy engine: one metadata tile [32][P + 3K] per send warp
     std::uint8_t* my_seg;
     std::uint8_t* recv_bytes;
     std::int64_t* prof;
@@ -345,8 +351,13 @@ struct Ctx {
     std::size_t out_row_bytes;
     std::uint64_t epoch;
     int slot_bytes, stages;
-    int P, C, E, El, K, H, Q, Qf, me, c, t0, t1, tx_warps, rx_warps, map_stride;
+    int P, C, E, El, K, H, Q, Qf, me, c, t0, t1, rx_warps, map_stride;
+    int T, Tc;                         // tokens of this rank, tokens per channel
+    int send_warps;                    // send warps in this CTA
+    int send_first, send_stride;       // channels this CTA's send warps serve: send_first, send_first + send_stride, ... < C
+    int rx_buffer_base;                // index of the first receive warp's row buffer
     bool vec_ok, use_tma, wire_fp8, recv_fp8, ring;
+    bool plan_is_foreign;              // the send warps read a plan that other CTAs write during this launch
 };
 
 struct RoleStats {
@@ -358,6 +369,7 @@ struct RoleStats {
 // lane k the k-th expert id, its ordinal and its weight.
 struct TokenRegs {
     int t;
+    int ch;         // the token's channel
     unsigned mask;  // remote destinations only
     int j;
     int e, ord;
@@ -498,77 +510,171 @@ __device__ __forceinline__ bool place_row(const Ctx& k, int s, int j, int token,
 }
 
 // ---- send role, bulk-copy engine ----------------------------------------------------------------
-// One warp, S row buffers.  Row n lives in buffer n % S.  Per loop turn: the row D turns ahead is located and its
-// load issued (the buffer it lands in was used by row n + D - S, whose outgoing copies have finished reading it
-// once all but the R = S - D - 1 most recent bulk groups have); row n's metadata is written, its payload awaited,
-// converted if the wire is FP8, and one bulk store per destination issued as one bulk group; then the READY
-// flags of row n - kFlagLag are released.
+// The send warps of a CTA serve the tokens of the channels send_first, send_first + send_stride, ...: one
+// channel when they sit inside a channel CTA, several when the CTA is a dedicated sender.  Dedicated senders
+// exist because an SM with remote stores in flight loses most of its local store throughput (the stores share
+// one path out of the SM and the slow ones hold up the fast ones): a few SMs saturate NVLink, so all remote
+// stores are confined to those and the channel CTAs' expansion writes run at full HBM speed.  The price is that
+// every load of a sender SM is slow too, so the role is built to need few of them and never to wait for one
+// row at a time:
+//   * routing metadata is fetched for 32 candidate tokens at once (lane = candidate: mask, slot per destination,
+//     expert / ordinal / weight per top-k slot; all loads of a batch are in flight together) and parked in a
+//     shared-memory tile, from which a row's values are picked up when its turn comes;
+//   * payloads run S - 1 rows ahead through a ring of S shared-memory buffers (row n lives in buffer n % S; a
+//     buffer is refilled once the outgoing copies of its previous row have finished reading it);
+//   * a row's READY flags are stored kFlagLag rows late, when its own bulk group has completed.
 //
 // Ordering of a row and its READY flag.  The payload leaves through the asynchronous proxy
-// (cp.async.bulk shared -> peer global), all copies of one row in one bulk group of lane 0.
-// `cp.async.bulk.wait_group N` returns to lane 0 only when every group but the N most recent is complete, which
-// includes its global writes having been performed and being visible to lane 0.  `__syncwarp()` then orders that
-// observation before the other lanes' later accesses (it is a barrier with memory ordering among the warp's
-// lanes), and each destination's lane publishes with `st.release.sys`, which is cumulative over what the lane has
-// observed.  The receiver reads the flag with `ld.acquire.sys` and issues `fence.proxy.async` before it reads the
-// row through the asynchronous proxy.  The two-GPU litmus test exercises exactly this chain.
+// (cp.async.bulk shared -> peer global), all copies of one row in one bulk group of the issuing lane.
+// `cp.async.bulk.wait_group N` returns to that lane only when every group but the N most recent is complete:
+// the writes have been performed at the destination.  `__syncwarp()` orders that observation before the other
+// lanes' later accesses, and only then does each destination's lane store the flag (`st.relaxed.sys`).  No
+// system-scope fence sits in between: on this hardware such a fence (alone or inside `st.release.sys`) waits for
+// every store the SM still has on the wire, which costs a full drain of the pipeline per row (measured: 4.4 us
+// per row against 0.07 us without).  Instead the order rests on the completion of the bulk group, which is
+// stronger than a fence for these writes -- they are not merely ordered but done -- and the receiver verifies it:
+// every row carries the epoch and token it belongs to, and a row that does not match its flag ends the launch
+// with kErrSequence.  The receiver reads the flag with `ld.acquire.sys` and issues `fence.proxy.async` before it
+// reads the row through the asynchronous proxy.  The two-GPU litmus test runs exactly this chain.
 template <int S>
 __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health, RoleStats& st) {
-    constexpr int D = S >= 4 ? 2 : 1;
-    constexpr int R = S - D - 1;
-    static_assert(S >= 2 && S <= kMaxSendStages && R >= 0, "2..4 send stages");
+    constexpr int D = S - 1;  // rows whose payload is loaded ahead of the one being sent
+    static_assert(S >= 2 && S <= kMaxSendStages, "2..4 send stages");
     const DispatchArgs& a = *k.a;
     const RankConst* rc = k.rc;
     const SegmentLayout& lay = rc->lay;
     const unsigned lane = ptx::lane_id();
     const unsigned full = 0xffffffffu;
+    // Every bulk copy of this warp is issued, committed and awaited by lane 31, which never stores a flag
+    // (flags belong to lanes 0..P-1).
+    const bool issuer = lane == 31u;
     const unsigned self_bit = 1u << k.me;
-    const bool delayed = w == k.tx_warps - 1;
+    const bool delayed = w == k.send_warps - 1;
+    const int P = k.P, K = k.K;
     const int moff = k.wire_fp8 ? lay.meta_off_fp8 : lay.meta_off;
     const unsigned row_bytes = static_cast<unsigned>(moff + lay.meta_bytes);
     const unsigned payload_bytes = static_cast<unsigned>(k.H) * 2u;
     unsigned char* const base = k.row_buffers + static_cast<std::size_t>(w) * S * k.slot_bytes;
     unsigned long long* const bars = &k.sh->mbar[w * S];
+    const int tile_stride = P + 3 * K;  // ints per candidate: slot[P] | expert[K] | ordinal[K] | weight[K]
+    int* const tile = k.send_tiles + static_cast<std::size_t>(w) * 32 * tile_stride;
     const std::uint32_t seq_epoch = static_cast<std::uint32_t>(k.epoch) + (rc->test_corrupt_sequence ? 1u : 0u);
     BEP_ROLE_DECL();
 
-    // candidates of this warp: tokens t0+w, t0+w+tx, ...; their masks are fetched 32 at a time
-    int cand = 0, batch = -1;
-    unsigned batch_mask = 0;
-    int issued = 0;  // rows whose load has been issued
-    auto next_token = [&](TokenRegs& r) -> bool {
-        while (true) {
-            const int t = k.t0 + w + cand * k.tx_warps;
-            if (t >= k.t1) return false;
-            if ((cand >> 5) != batch) {
-                batch = cand >> 5;
-                const int tl = k.t0 + w + (batch * 32 + static_cast<int>(lane)) * k.tx_warps;
-                batch_mask = tl < k.t1 ? a.plan_mask[tl] : 0u;
+    // Candidates of this CTA: the tokens of its channels, channel after channel; this warp takes every W-th one.
+    const int W = k.send_warps;
+    const int n_ch = k.send_first < k.C ? (k.C - k.send_first + k.send_stride - 1) / k.send_stride : 0;
+    const int n_cand = n_ch * k.Tc;
+    int batch = -1;            // batch held in the tile
+    unsigned todo = 0;         // candidates of the batch that still have to be sent (bit = lane)
+    int my_t = -1, my_ch = 0;  // this lane's candidate of the batch
+    unsigned my_mask = 0;
+    int issued = 0;            // rows whose payload load has been issued
+
+    // Fetch the routing metadata of candidates w + (32 b + lane) W into the tile.  A dedicated sender reads a plan
+    // that another CTA writes in this very launch: a lane first waits for that channel's plan flag.
+    auto load_batch = [&](int b) {
+        BEP_ROLE_T(t_batch);
+        batch = b;
+        my_t = -1;
+        my_mask = 0u;
+        const int ql = w + (b * 32 + static_cast<int>(lane)) * W;
+        if (ql < n_cand) {
+            const int i = ql / k.Tc;
+            my_ch = k.send_first + i * k.send_stride;
+            const int t = my_ch * k.Tc + (ql - i * k.Tc);
+            if (t < k.T) {
+                if (!a.cached && k.plan_is_foreign) {
+                    const std::uint64_t* plan_flag = rc->plan_flags + my_ch;
+                    while (ptx::ld_acquire_gpu(plan_flag) != k.epoch) {
+                        if (health.give_up(kErrGridBarrier, my_ch, 1)) break;
+                    }
+                }
+                if (!health.failed()) {
+                    my_t = t;
+                    my_mask = a.plan_mask[t] & ~self_bit;
+                }
             }
-            const unsigned m = __shfl_sync(full, batch_mask, cand & 31) & ~self_bit;
-            ++cand;
-            if (m == 0) continue;
-            r.t = t;
-            r.mask = m;
-            r.j = (lane < static_cast<unsigned>(k.P) && (m >> lane & 1u)) ? a.plan_slot[static_cast<std::size_t>(t) * k.P + lane] : -1;
-            load_token_routes(a, t, k.K, k.E, r.e, r.ord, r.w);
-            // payload into the next buffer of the ring
-            if (lane == 0) {
-                const int b = issued % S;
-                bulk_wait_group_read<R>();
-                std::uint64_t* bar = reinterpret_cast<std::uint64_t*>(&bars[b]);
-                ptx::mbar_expect_tx(bar, payload_bytes);
-                ptx::bulk_g2s(base + static_cast<std::size_t>(b) * k.slot_bytes, a.x + static_cast<std::size_t>(t) * k.H, payload_bytes, bar);
-            }
-            ++issued;
-            return true;
         }
+        __syncwarp();  // the tile's previous contents have been picked up by every lane
+        if (my_mask != 0u) {
+            int* row = tile + static_cast<int>(lane) * tile_stride;
+            const int t = my_t;
+            // eight values at a time: all loads of a group are issued before the first is stored
+            for (int d0 = 0; d0 < P; d0 += 8) {
+                int v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    v[u] = (d0 + u < P && (my_mask >> (d0 + u) & 1u)) ? a.plan_slot[static_cast<std::size_t>(t) * P + d0 + u] : -1;
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (d0 + u < P) row[d0 + u] = v[u];
+            }
+            for (int k0 = 0; k0 < K; k0 += 8) {
+                std::int64_t e64[8];
+                int ord[8];
+                float wt[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const bool in = k0 + u < K;
+                    const std::size_t at = static_cast<std::size_t>(t) * K + (in ? k0 + u : 0);
+                    e64[u] = in ? a.topk_idx[at] : -1;
+                    ord[u] = in ? a.plan_expert_ord[at] : -1;
+                    wt[u] = (in && a.topk_w) ? a.topk_w[at] : 1.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (k0 + u < K) {
+                        row[P + k0 + u] = (e64[u] >= 0 && e64[u] < k.E) ? static_cast<int>(e64[u]) : -1;
+                        row[P + K + k0 + u] = ord[u];
+                        row[P + 2 * K + k0 + u] = __float_as_int(wt[u]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        todo = __ballot_sync(full, my_mask != 0u);
+        BEP_ROLE_ADD(kRoleMetaNs, t_batch);
+    };
+
+    // Next row to send: picks its metadata out of the tile and issues its payload load.
+    auto next_token = [&](TokenRegs& r) -> bool {
+        while (todo == 0u) {
+            const int b = batch + 1;
+            if (w + b * 32 * W >= n_cand || warp_failed(health)) return false;
+            load_batch(b);
+        }
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        r.t = __shfl_sync(full, my_t, src);
+        r.ch = __shfl_sync(full, my_ch, src);
+        r.mask = __shfl_sync(full, my_mask, src);
+        const int* row = tile + src * tile_stride;
+        r.j = lane < static_cast<unsigned>(P) ? row[lane] : -1;
+        r.e = -1;
+        r.ord = -1;
+        r.w = 0.0f;
+        if (lane < static_cast<unsigned>(K)) {
+            r.e = row[P + lane];
+            r.ord = row[P + K + lane];
+            r.w = __int_as_float(row[P + 2 * K + lane]);
+        }
+        // payload into the next buffer of the ring, once the row that used it has been read out of it
+        if (issuer) {
+            const int b = issued % S;
+            bulk_wait_group_read<0>();
+            std::uint64_t* bar = reinterpret_cast<std::uint64_t*>(&bars[b]);
+            ptx::mbar_expect_tx(bar, payload_bytes);
+            ptx::bulk_g2s(base + static_cast<std::size_t>(b) * k.slot_bytes, a.x + static_cast<std::size_t>(r.t) * k.H, payload_bytes, bar);
+        }
+        ++issued;
+        return true;
     };
 
     TokenRegs ahead[D];
     bool ahead_ok[D];
 #pragma unroll
-    for (int i = 0; i < D; ++i) ahead_ok[i] = next_token(ahead[i]);
+    for (int i = 0; i < D; ++i) ahead_ok[i] = (i == 0 || ahead_ok[i - 1]) ? next_token(ahead[i]) : false;
 
     std::uint64_t* flag_ring[kFlagLag];
     std::uint32_t flag_seq[kFlagLag];
@@ -590,18 +696,18 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
 
         unsigned char* buf = base + static_cast<std::size_t>(n % S) * k.slot_bytes;
         const unsigned parity = static_cast<unsigned>(n / S) & 1u;
-        // destination row of lane d; ring mode first waits for the slot's credit
+        // destination row of lane d
         std::uint8_t* dst = nullptr;
         std::uint64_t* ready = nullptr;
         if (cur.j >= 0) {
-            const std::size_t ring_index = (static_cast<std::size_t>(k.me) * k.C + k.c) * k.Q + (cur.j % k.Q);
+            const std::size_t ring_index = (static_cast<std::size_t>(k.me) * k.C + cur.ch) * k.Q + (cur.j % k.Q);
             dst = rc->seg[lane] + lay.stage_off + ring_index * lay.row_stride;
             ready = reinterpret_cast<std::uint64_t*>(rc->seg[lane] + lay.ready_off) + ring_index;
         }
         if (k.ring) {
             // Bounded rings: slot j % Q is free once the receiver has acknowledged row j - Q.  The receiver only
             // sees rows whose READY flags are out, so before this warp settles down to wait for credit it
-            // releases every flag it still holds back.
+            // stores every flag it still holds back.
             BEP_ROLE_T(t_credit);
             const bool need = cur.j >= k.Q;
             const std::uint64_t* ack = nullptr;
@@ -609,16 +715,16 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
             bool have = true;
             if (need) {
                 ack = reinterpret_cast<const std::uint64_t*>(k.my_seg + lay.ack_off) +
-                      (static_cast<std::size_t>(lane) * k.C + k.c) * k.Q + (cur.j % k.Q);
+                      (static_cast<std::size_t>(lane) * k.C + cur.ch) * k.Q + (cur.j % k.Q);
                 want = make_seq(k.epoch, static_cast<std::uint32_t>(cur.j - k.Q + 1));
                 have = ptx::ld_acquire_sys(ack) == want;
             }
             if (!__all_sync(full, have)) {
-                if (lane == 0) bulk_wait_group<0>();
+                if (issuer) bulk_wait_group<0>();
                 __syncwarp();
 #pragma unroll
                 for (int i = 0; i < kFlagLag; ++i) {
-                    if (flag_ring[i] != nullptr) ptx::st_release_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
+                    if (flag_ring[i] != nullptr) ptx::st_relaxed_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
                     flag_ring[i] = nullptr;
                 }
                 if (!have) {
@@ -631,15 +737,15 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
             BEP_ROLE_ADD(kRoleCreditWaitNs, t_credit);
         }
         __syncwarp();
-        if (warp_failed(health)) {
+        // The failure latch lives in global memory and a load is slow on an SM that is busy storing to peers: it is
+        // looked at every eighth row here (every bounded wait looks at it as well).
+        if ((n & 7) == 0 && warp_failed(health)) {
             broke = true;
             break;
         }
         if (delayed) test_delay(rc->delay_meta_ns);
-        BEP_ROLE_T(t_meta);
         // BF16 wire: the metadata lies behind the payload and can be written while the payload is still landing
-        if (!k.wire_fp8) write_row_meta(buf + moff, lay, cur.t, 1.0f, seq_epoch, cur.e, cur.ord, cur.w, k.K);
-        BEP_ROLE_ADD(kRoleMetaNs, t_meta);
+        if (!k.wire_fp8) write_row_meta(buf + moff, lay, cur.t, 1.0f, seq_epoch, cur.e, cur.ord, cur.w, K);
         BEP_ROLE_T(t_load);
         const bool arrived = mbar_wait_bounded(&bars[n % S], parity, health);
         BEP_ROLE_ADD(kRoleLoadWaitNs, t_load);
@@ -652,7 +758,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
         if (k.wire_fp8) {
             BEP_ROLE_T(t_quant);
             const float scale = quantise_row_in_place(buf, k.H);
-            write_row_meta(buf + moff, lay, cur.t, scale, seq_epoch, cur.e, cur.ord, cur.w, k.K);
+            write_row_meta(buf + moff, lay, cur.t, scale, seq_epoch, cur.e, cur.ord, cur.w, K);
             BEP_ROLE_ADD(kRoleQuantNs, t_quant);
         }
         BEP_ROLE_T(t_issue);
@@ -660,16 +766,16 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
         __syncwarp();
         for (unsigned m = cur.mask; m; m &= m - 1) {
             std::uint8_t* d = shfl_ptr(dst, __ffs(m) - 1);
-            if (lane == 0) ptx::bulk_s2g(d, buf, row_bytes);
+            if (issuer) ptx::bulk_s2g(d, buf, row_bytes);
         }
-        if (lane == 0) ptx::bulk_commit();
+        if (issuer) ptx::bulk_commit();
         BEP_ROLE_ADD(kRoleIssueNs, t_issue);
         // READY flags of the row issued kFlagLag turns ago: its bulk group is complete by now (or is awaited here)
         if (n >= kFlagLag) {
             BEP_ROLE_T(t_store);
-            if (lane == 0) bulk_wait_group<kFlagLag>();
+            if (issuer) bulk_wait_group<kFlagLag>();
             __syncwarp();
-            if (flag_ring[0] != nullptr) ptx::st_release_sys(flag_ring[0], make_seq(k.epoch, flag_seq[0]));
+            if (flag_ring[0] != nullptr) ptx::st_relaxed_sys(flag_ring[0], make_seq(k.epoch, flag_seq[0]));
             BEP_ROLE_ADD(kRoleStoreWaitNs, t_store);
             if (w == 0 && lane == 0 && n == kFlagLag) k.prof[kProfFirstTxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
         }
@@ -692,12 +798,12 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
     // drain: the last rows' groups, then their flags in row order
     {
         BEP_ROLE_T(t_store);
-        if (lane == 0) bulk_wait_group<0>();
+        if (issuer) bulk_wait_group<0>();
         __syncwarp();
         if (!broke && !warp_failed(health)) {
 #pragma unroll
             for (int i = 0; i < kFlagLag; ++i)
-                if (flag_ring[i] != nullptr) ptx::st_release_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
+                if (flag_ring[i] != nullptr) ptx::st_relaxed_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
             if (w == 0 && lane == 0 && n > 0 && n <= kFlagLag) k.prof[kProfFirstTxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
         }
         BEP_ROLE_ADD(kRoleStoreWaitNs, t_store);
@@ -708,7 +814,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
         while (!ptx::mbar_try_wait(reinterpret_cast<std::uint64_t*>(&bars[r % S]), static_cast<unsigned>(r / S) & 1u) && ++polls < (1u << 20))
             ptx::nanosleep(64);
     }
-    BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(1 + w) * kRoleFields : nullptr);
+    BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(threadIdx.x >> 5) * kRoleFields : nullptr);
 }
 
 // ---- send role, register path (16-byte or scalar accesses; also the path for odd hidden sizes) ----
@@ -718,14 +824,31 @@ __device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& healt
     const SegmentLayout& lay = rc->lay;
     const unsigned lane = ptx::lane_id();
     const unsigned self_bit = 1u << k.me;
-    const bool delayed = w == k.tx_warps - 1;
-    unsigned char* meta_sm = k.sh->meta[1 + w];
+    const bool delayed = w == k.send_warps - 1;
+    unsigned char* meta_sm = k.sh->meta[threadIdx.x >> 5];
     const std::uint32_t seq_epoch = static_cast<std::uint32_t>(k.epoch) + (rc->test_corrupt_sequence ? 1u : 0u);
     const int moff = k.wire_fp8 ? lay.meta_off_fp8 : lay.meta_off;
     BEP_ROLE_DECL();
     int sent = 0;
-    for (int t = k.t0 + w; t < k.t1; t += k.tx_warps) {
+    const int n_ch = k.send_first < k.C ? (k.C - k.send_first + k.send_stride - 1) / k.send_stride : 0;
+    const int n_cand = n_ch * k.Tc;
+    for (int q = w; q < n_cand; q += k.send_warps) {
         if (warp_failed(health)) break;
+        const int ch_i = q / k.Tc;
+        const int ch = k.send_first + ch_i * k.send_stride;
+        const int t = ch * k.Tc + (q - ch_i * k.Tc);
+        if (t >= k.T) continue;
+        if (!a.cached && k.plan_is_foreign) {
+            // a dedicated sender reads a plan that the channel's own CTA writes in this launch
+            if (lane == 0) {
+                const std::uint64_t* plan_flag = rc->plan_flags + ch;
+                while (ptx::ld_acquire_gpu(plan_flag) != k.epoch) {
+                    if (health.give_up(kErrGridBarrier, ch, 1)) break;
+                }
+            }
+            __syncwarp();
+            if (warp_failed(health)) break;
+        }
         const unsigned mask = a.plan_mask[t] & ~self_bit;
         if (mask == 0) continue;
         int j = -1;
@@ -733,12 +856,12 @@ __device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& healt
         std::uint64_t* ready = nullptr;
         if (lane < static_cast<unsigned>(k.P) && (mask >> lane & 1u)) {
             j = a.plan_slot[static_cast<std::size_t>(t) * k.P + lane];
-            const std::size_t ring_index = (static_cast<std::size_t>(k.me) * k.C + k.c) * k.Q + (j % k.Q);
+            const std::size_t ring_index = (static_cast<std::size_t>(k.me) * k.C + ch) * k.Q + (j % k.Q);
             dst = rc->seg[lane] + lay.stage_off + ring_index * lay.row_stride;
             ready = reinterpret_cast<std::uint64_t*>(rc->seg[lane] + lay.ready_off) + ring_index;
             if (k.ring && j >= k.Q) {
                 const std::uint64_t* ack = reinterpret_cast<const std::uint64_t*>(k.my_seg + lay.ack_off) +
-                                           (static_cast<std::size_t>(lane) * k.C + k.c) * k.Q + (j % k.Q);
+                                           (static_cast<std::size_t>(lane) * k.C + ch) * k.Q + (j % k.Q);
                 const std::uint64_t want = make_seq(k.epoch, static_cast<std::uint32_t>(j - k.Q + 1));
                 bool missed = false;
                 while (ptx::ld_acquire_sys(ack) != want) {
@@ -780,7 +903,7 @@ __device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& healt
         BEP_ROLE_COUNT(kRoleRows, 1);
         ++sent;
     }
-    BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(1 + w) * kRoleFields : nullptr);
+    BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(threadIdx.x >> 5) * kRoleFields : nullptr);
 }
 
 // ---- receive + expand role ------------------------------------------------------------------------
@@ -814,7 +937,7 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, R
         const int expect = (lane < static_cast<unsigned>(P) && static_cast<int>(lane) != me) ? k.sh->chan_expected[lane] : 0;
         int t_local = k.t0 + w;
         const std::uint64_t* ready_base = reinterpret_cast<const std::uint64_t*>(k.my_seg + lay.ready_off);
-        const int buffer_index = k.tx_warps * k.stages + w;
+        const int buffer_index = k.rx_buffer_base + w;
         unsigned char* my_slot = k.row_buffers + static_cast<std::size_t>(buffer_index) * k.slot_bytes;
         unsigned long long* my_bar = &k.sh->mbar[buffer_index];
         unsigned parity = 0;
@@ -990,8 +1113,9 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, R
                         if (lane == 0) ptx::st_release_sys(ack, make_seq(k.epoch, static_cast<std::uint32_t>(j + 1)));
                     }
                 } else {
-                    // the row is in shared memory: its ring slot can be handed back already
-                    if (k.ring && lane == 0) ptx::st_release_sys(ack, make_seq(k.epoch, static_cast<std::uint32_t>(j + 1)));
+                    // the row is in shared memory (the load has completed): its ring slot can be handed back already;
+                    // nothing this lane wrote has to become visible first, so the store carries no fence
+                    if (k.ring && lane == 0) ptx::st_relaxed_sys(ack, make_seq(k.epoch, static_cast<std::uint32_t>(j + 1)));
                     if (fp8row && !k.recv_fp8) {
                         BEP_ROLE_T(t_quant);
                         // widen in place, decreasing order: chunk q is read before anything lands on it
@@ -1023,7 +1147,7 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, R
         }
         if (w == 0 && lane == 0) k.prof[kProfRxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
     }
-    BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(1 + k.tx_warps + w) * kRoleFields : nullptr);
+    BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(threadIdx.x >> 5) * kRoleFields : nullptr);
 }
 
 }  // namespace detail
@@ -1037,9 +1161,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     const int P = lay.num_ranks, C = lay.num_channels, E = lay.num_experts, El = lay.num_local_experts;
     const int K = lay.num_topk, H = lay.hidden;
     const int me = rc->rank, c = blockIdx.x;
+    const int S = rc->send_ctas;    // CTAs C .. C+S-1 of the grid only send (see send_role_bulk)
+    const bool is_sender = c >= C;
     const int T = a.num_tokens;
     const int Tc = (T + C - 1) / C;
-    const int t0 = min(T, c * Tc), t1 = min(T, t0 + Tc);
+    const int t0 = is_sender ? 0 : min(T, c * Tc), t1 = is_sender ? 0 : min(T, t0 + Tc);
     const int warp = threadIdx.x >> 5;
     const unsigned lane = ptx::lane_id();
     const unsigned lt_mask = (1u << lane) - 1u;
@@ -1113,7 +1239,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     // ---- phase A: routing layout (skipped with a cached plan) ------------------------------------
     // O(T*K) work with one grid barrier: per-channel histograms, a prefix over channels, then ballots inside
     // 32-token chunks give every (token, bin) its stable ordinal.
-    if (!a.cached) {
+    if (is_sender) {
+        // a sender has no tokens of its own to lay out; it only takes part in the grid barrier
+        if (!a.cached) grid_barrier(&rc->grid_bar[0], health);
+    } else if (!a.cached) {
         for (int i = threadIdx.x; i < E; i += blockDim.x) {
             cnt_e[i] = 0;
             bits_e[i] = 0;
@@ -1180,7 +1309,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     }
     // Two things happen side by side before the roles split: warp 1 tells every destination what to
     // expect (counts message; channel d, d+C, ... serves destination d), warp 0 numbers this channel's tokens.
-    if (warp == 1 && !rc->test_withhold_counts) {
+    if (warp == 1 && !is_sender && !rc->test_withhold_counts) {
         for (int d = c; d < P; d += C) {
             int* msg = reinterpret_cast<int*>(rc->seg[d] + lay.counts_off) + static_cast<std::size_t>(me) * lay.counts_stride;
             for (int i = lane; i < P + El + C; i += 32) {
@@ -1196,7 +1325,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         }
         if (lane == 0) BEP_PROF(kProfCountsSent);
     }
-    if (!a.cached) {
+    if (!a.cached && !is_sender) {
     if (warp == 0) {
         // Stable ordinals, 32 tokens at a time: lane = token.  bits_*[bin] collects which lanes hit a
         // bin; an ordinal is (tokens before this chunk) + (lower lanes in the bin).
@@ -1243,7 +1372,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             __syncwarp();
         }
     }
-        if (warp == 0 && lane == 0) BEP_PROF(kProfOrdinalsDone);
+        if (warp == 0 && lane == 0) {
+            BEP_PROF(kProfOrdinalsDone);
+            if (S > 0) {
+                // this channel's plan is complete (the masks were written before the barrier above): the senders may read it
+                __threadfence();
+                ptx::st_release_gpu(&rc->plan_flags[c], epoch);
+            }
+        }
     }
     if (cta_failed(health, &sh->cta_flag)) return;
     if (threadIdx.x == 0) BEP_PROF(kProfRolesSplit);
@@ -1256,6 +1392,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     k.eoff = eoff;
     k.spre = spre;
     k.row_buffers = smem_raw + slots_at;
+    k.send_tiles = reinterpret_cast<int*>(smem_raw + slots_at + static_cast<std::size_t>(dispatch_row_buffer_count(tx_warps, rx_warps, rc->send_stages, S)) *
+                                                                static_cast<std::size_t>(align_up(lay.meta_off + lay.meta_bytes, 128)));
     k.my_seg = my_seg;
     k.recv_bytes = recv_bytes;
     k.prof = prof;
@@ -1265,13 +1403,33 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     k.slot_bytes = static_cast<int>(align_up(lay.meta_off + lay.meta_bytes, 128));
     k.stages = rc->send_stages;
     k.P = P; k.C = C; k.E = E; k.El = El; k.K = K; k.H = H; k.Q = lay.slots; k.Qf = lay.slots_full;
-    k.me = me; k.c = c; k.t0 = t0; k.t1 = t1; k.tx_warps = tx_warps; k.rx_warps = rx_warps;
+    k.me = me; k.c = c; k.t0 = t0; k.t1 = t1; k.rx_warps = rx_warps;
+    k.T = T; k.Tc = Tc;
+    if (is_sender) {
+        k.send_warps = tx_warps; k.send_first = c - C; k.send_stride = S;
+    } else if (S == 0) {
+        k.send_warps = tx_warps; k.send_first = c; k.send_stride = C;
+    } else {
+        k.send_warps = 0; k.send_first = C; k.send_stride = C;
+    }
+    k.rx_buffer_base = S == 0 ? tx_warps * rc->send_stages : 0;
+    k.plan_is_foreign = is_sender;
     k.map_stride = 2 + 2 * K;
     k.vec_ok = vec_ok; k.use_tma = use_tma; k.wire_fp8 = rc->wire_fp8 != 0; k.recv_fp8 = recv_fp8;
     k.ring = rc->ring_mode != 0;
     RoleStats st;
 
-    if (warp == 0) {
+    if (is_sender) {
+        // ===== dedicated sender: every warp sends =====
+        if (warp < tx_warps) {
+            if (!use_tma) send_role_vector(k, warp, health, st);
+            else if (k.stages >= 4) send_role_bulk<4>(k, warp, health, st);
+            else if (k.stages == 3) send_role_bulk<3>(k, warp, health, st);
+            else send_role_bulk<2>(k, warp, health, st);
+            if (lane == 0) atomicMax(&sh->last_tx_ns, ptx::globaltimer_ns());
+            if (warp == 0 && lane == 0) BEP_PROF(kProfTxDone);
+        }
+    } else if (warp == 0) {
         // ===== control: receive prefix from every source's counts message, then zero padding =====
         const unsigned long long prefix_t0 = ptx::globaltimer_ns();
         if (lane < static_cast<unsigned>(P)) {
@@ -1392,8 +1550,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             while (ptx::globaltimer_ns() < t_start + rc->test_abort_after_ns) ptx::nanosleep(200);
             if (lane == 0) record_error(rc, a.error, kErrInjectedAbort, me, 0);
         }
-    } else if (warp <= tx_warps) {
-        // ===== send =====
+    } else if (S == 0 && warp <= tx_warps) {
+        // ===== send (inside the channel CTA) =====
         const int w = warp - 1;
         if (!use_tma) send_role_vector(k, w, health, st);
         else if (k.stages >= 4) send_role_bulk<4>(k, w, health, st);
@@ -1403,7 +1561,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         if (w == 0 && lane == 0) BEP_PROF(kProfTxDone);
     } else {
         // ===== receive + expand =====
-        receive_role(k, warp - 1 - tx_warps, health, st);
+        const int rw = warp - 1 - (S == 0 ? tx_warps : 0);
+        if (rw < rx_warps) receive_role(k, rw, health, st);
     }
 
     // ---- epilogue ----------------------------------------------------------------------------------
@@ -1431,13 +1590,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         a.prefix_tx_ts[(c + 1) * 2 + 1] = static_cast<std::int64_t>(sh->last_tx_ns);
         __threadfence();
         const unsigned long long old = atomicAdd(&rc->done_ctas[0], 1ull);
-        if ((old + 1) % static_cast<unsigned long long>(C) == 0) {
-            // last channel of this rank: sum the per-channel statistics, hand the staging area back to every
+        if ((old + 1) % static_cast<unsigned long long>(gridDim.x) == 0) {
+            // last CTA of this rank: sum the per-CTA statistics, hand the staging area back to every
             // source, advance the epoch
             __threadfence();
             std::int64_t sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             std::int64_t first = INT64_MAX, last = 0;
-            for (int c2 = 0; c2 < C; ++c2) {
+            for (int c2 = 0; c2 < static_cast<int>(gridDim.x); ++c2) {
                 const std::int64_t* o = rc->chan_stats + static_cast<std::size_t>(c2) * 10;
                 for (int i = 0; i < 8; ++i) sum[i] += __ldcg(o + i);
                 first = min(first, __ldcg(o + 8));

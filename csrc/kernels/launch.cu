@@ -10,8 +10,9 @@
 
 namespace bep {
 
-std::size_t dispatch_shared_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma, int stages) {
-    return dispatch_smem_bytes(lay, tx_warps, rx_warps, use_tma, stages);
+std::size_t dispatch_shared_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma, int stages,
+                                  int send_ctas) {
+    return dispatch_smem_bytes(lay, tx_warps, rx_warps, use_tma, stages, send_ctas);
 }
 
 bool role_profiling_enabled() { return BEP_ENABLE_PROFILING != 0; }
@@ -70,9 +71,9 @@ cudaError_t cooperative_launch(Kernel kernel, const Args& args, dim3 grid, int t
 
 }  // namespace
 
-cudaError_t launch_dispatch(const DispatchLaunch& launch, int channels, int threads, std::size_t smem,
+cudaError_t launch_dispatch(const DispatchLaunch& launch, int ctas, int threads, std::size_t smem,
                             cudaStream_t stream) {
-    return cooperative_launch(dispatch_kernel, launch, dim3(channels, launch.num_virtual, 1), threads, smem, stream);
+    return cooperative_launch(dispatch_kernel, launch, dim3(ctas, launch.num_virtual, 1), threads, smem, stream);
 }
 
 cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_t crow_stride, cudaStream_t stream) {

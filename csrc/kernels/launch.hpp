@@ -12,7 +12,8 @@
 namespace bep {
 
 // Shared-memory bytes the dispatch kernel needs for this configuration (`stages` row buffers per send warp).
-std::size_t dispatch_shared_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma, int stages);
+std::size_t dispatch_shared_bytes(const SegmentLayout& lay, int tx_warps, int rx_warps, bool use_tma, int stages,
+                                  int send_ctas);
 
 // Raise (never lower) the kernels' dynamic shared-memory limit; thread-safe, idempotent.
 cudaError_t configure_kernels(std::size_t dispatch_smem_bytes);
@@ -21,8 +22,8 @@ cudaError_t configure_kernels(std::size_t dispatch_smem_bytes);
 int dispatch_resident_ctas(int threads, std::size_t smem);
 int combine_resident_ctas(int threads);
 
-// Cooperative launches: grid = (channels, virtual ranks).
-cudaError_t launch_dispatch(const DispatchLaunch& launch, int channels, int threads, std::size_t smem,
+// Cooperative launches: grid = (CTAs per rank, virtual ranks); dispatch: channels + dedicated sender CTAs.
+cudaError_t launch_dispatch(const DispatchLaunch& launch, int ctas, int threads, std::size_t smem,
                             cudaStream_t stream);
 cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_t crow_stride, cudaStream_t stream);
 

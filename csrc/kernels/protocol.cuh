@@ -42,7 +42,15 @@ constexpr int kMaxSendStages = 4;   // shared-memory row buffers per send warp
 constexpr int kMaxRowBuffers = 40;  // send warps x stages + receive warps of one channel CTA
 constexpr int kRoleFieldCount = 16; // counters per warp in a profiling build
 
-inline int dispatch_row_buffer_count(int tx_warps, int rx_warps, int stages) { return tx_warps * stages + rx_warps; }
+// Row buffers a dispatch CTA needs: with dedicated sender CTAs a CTA is either all send warps or control + receive
+// warps; without them every channel CTA holds both kinds.
+__host__ __device__ inline int dispatch_row_buffer_count(int tx_warps, int rx_warps, int stages, int send_ctas) {
+    const int send = tx_warps * stages;
+    return send_ctas > 0 ? (send > rx_warps ? send : rx_warps) : send + rx_warps;
+}
+inline int dispatch_cta_warps(int tx_warps, int rx_warps, int send_ctas) {
+    return send_ctas > 0 ? (tx_warps > 1 + rx_warps ? tx_warps : 1 + rx_warps) : 1 + tx_warps + rx_warps;
+}
 
 // Error codes (2, 11, 12, 15, 16, 18, 19 and 20 keep the numbers DeepEP-style callers already know).
 enum ErrorCode : int {
@@ -180,6 +188,7 @@ struct RankConst {
     int vec_ok;        // hidden*2 is a multiple of 16: 16-byte accesses are legal on rows
     int tx_warps, rx_warps;
     int send_stages;   // shared-memory row buffers per send warp (bulk-copy engine): 2, 3 or 4
+    int send_ctas;     // CTAs beyond the channel CTAs that do nothing but send (0: the send warps sit in every channel CTA)
     int unique_cap, expanded_cap;
     int slot_smem_bytes;  // shared-memory bytes of one row buffer (TMA path)
     std::uint64_t timeout_ns;
@@ -188,8 +197,9 @@ struct RankConst {
     unsigned long long* grid_bar;   // [0] dispatch barrier arrivals, [1] combine (monotonic)
     unsigned long long* done_ctas;  // [0] dispatch CTAs finished, [1] combine (monotonic)
     int* block_hist;            // [C][E + P] scratch of the layout phase
+    std::uint64_t* plan_flags;  // [C] epoch whose routing plan channel c has finished writing (read by the sender CTAs)
     int* sticky;                // [0] != 0 once this rank has failed; [1..] first error record
-    std::int64_t* chan_stats;   // [2][C][10]: per-channel counters + start/end time; dispatch, then combine
+    std::int64_t* chan_stats;   // [2][C + send CTAs][10]: per-CTA counters + start/end time; dispatch, then combine
     // test hooks (written by the host between launches; all zero in production)
     std::uint64_t delay_meta_ns, delay_tx_ns, delay_rx_ns, delay_scatter_ns, delay_prefix_ns;
     int test_skip_done_to;      // -1, else: do not publish `done` to this peer (mailbox-timeout test)
@@ -289,9 +299,9 @@ struct CombineLaunch {
 static_assert(sizeof(SegmentLayout) == 200 && offsetof(SegmentLayout, relay_off) == 120 &&
                   offsetof(SegmentLayout, num_ranks) == 128 && offsetof(SegmentLayout, has_fused) == 192,
               "SegmentLayout ABI changed");
-static_assert(sizeof(RankConst) == 496 && offsetof(RankConst, seg) == 200 && offsetof(RankConst, rank) == 328 &&
-                  offsetof(RankConst, timeout_ns) == 376 && offsetof(RankConst, epochs) == 384 &&
-                  offsetof(RankConst, delay_meta_ns) == 432 && offsetof(RankConst, test_abort_after_ns) == 488,
+static_assert(sizeof(RankConst) == 512 && offsetof(RankConst, seg) == 200 && offsetof(RankConst, rank) == 328 &&
+                  offsetof(RankConst, timeout_ns) == 384 && offsetof(RankConst, epochs) == 392 &&
+                  offsetof(RankConst, delay_meta_ns) == 448 && offsetof(RankConst, test_abort_after_ns) == 504,
               "RankConst ABI changed");
 static_assert(sizeof(DispatchArgs) == 248 && offsetof(DispatchArgs, plan_mask) == 56 &&
                   offsetof(DispatchArgs, recv_x) == 88 && offsetof(DispatchArgs, role_profile) == 240,

@@ -1,7 +1,6 @@
 // Thin inline-PTX wrappers used by every kernel of this library (sm_100a).
 //
-// Memory-model rules the protocol relies on (the reference states the same rules for
-// mapped host memory, csrc/kernels/host_staged/common.cuh:59-64,192-198):
+// Memory-model rules the protocol relies on:
 //   * every cross-GPU flag has exactly one writer and is only ever acquire-loaded by others;
 //   * payload bytes are made visible by "every writer fences, the warp joins, one lane
 //     releases the flag" for plain stores, and by "bulk group completes, then release"
@@ -34,6 +33,14 @@ __device__ __forceinline__ std::uint32_t ld_acquire_gpu(const std::uint32_t* p) 
     std::uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+__device__ __forceinline__ std::uint64_t ld_acquire_gpu(const std::uint64_t* p) {
+    std::uint64_t v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(std::uint64_t* p, std::uint64_t v) {
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ int ld_volatile(const int* p) {
     int v;

@@ -150,6 +150,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("combine_is_local", &Runtime::combine_is_local)
         .def("combine_is_inline", &Runtime::combine_is_inline)
         .def("send_stages", &Runtime::send_stages)
+        .def("send_ctas", &Runtime::send_ctas)
+        .def("grid_ctas", &Runtime::grid_ctas)
         .def("set_test_corrupt_sequence", &Runtime::set_test_corrupt_sequence)
         .def("set_test_control_abort_after_ns", &Runtime::set_test_control_abort_after_ns)
         .def("pool_debug", &Runtime::pool_debug)

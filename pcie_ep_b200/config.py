@@ -64,8 +64,12 @@ class HostStagedConfig:
     copy_engine: ``"tma"`` moves rows with ``cp.async.bulk`` through shared
         memory, ``"vector"`` uses 16-byte loads/stores (also the path taken
         automatically when ``hidden * 2`` is not a multiple of 16).
-    tx_warps / rx_warps: warps per channel CTA in the send and the
-        receive/expand role.
+    tx_warps / rx_warps: warps in the send role (per dedicated sender CTA, or per channel CTA when there
+        are none) and in the receive/expand role (per channel CTA).
+    send_ctas: CTAs that do nothing but push rows to peers.  An SM with remote stores in flight loses
+        most of its local store bandwidth, and a few SMs saturate NVLink, so by default (-1) sixteen
+        CTAs send for all channels when there is more than one rank; 0 puts ``tx_warps`` send warps into
+        every channel CTA instead.
     enable_combine: allocate the combine staging area.
     recv_dtype: ``"bf16"`` (rows are decoded at the receiver, local rows bypass the wire format) or
         ``"fp8_e4m3"`` (needs the FP8 wire): every row -- local ones too -- stays E4M3 at the receiver,
@@ -113,6 +117,7 @@ class HostStagedConfig:
     recv_dtype: str = "bf16"
     fused_expert_combine: bool = False
     combine_reduce: str = "auto"
+    send_ctas: int = -1
 
     def __post_init__(self) -> None:
         for name in ("timeout_ms", "replica_slots"):
@@ -169,6 +174,8 @@ class HostStagedConfig:
             raise ValueError("rx_warps must be an integer in [1, 12]")
         if self.numa_mode == "relay" and self.transport not in ("host_staged", "auto"):
             raise ValueError("numa_mode='relay' needs transport='host_staged'")
+        if not isinstance(self.send_ctas, int) or not -1 <= self.send_ctas <= 64:
+            raise ValueError("send_ctas must be -1 (chosen by rank count) or an integer in [0, 64]")
         if self.combine_reduce not in ("auto", "separate", "inline"):
             raise ValueError("combine_reduce must be 'auto', 'separate' or 'inline'")
         if self.fused_expert_combine and self.numa_mode == "relay":
@@ -188,7 +195,7 @@ class HostStagedConfig:
         if num_ranks < 1 or num_max_tokens_per_rank < 1:
             raise ValueError("num_ranks and num_max_tokens_per_rank must be positive")
         channels = 32 if num_max_tokens_per_rank <= 256 else 64 if num_max_tokens_per_rank <= 1024 else 128
-        settings = dict(channels=channels, tx_warps=2, rx_warps=8, pipeline_stages=3)
+        settings = dict(channels=channels, tx_warps=2 if num_ranks == 1 else 4, rx_warps=8, pipeline_stages=3)
         settings.update(overrides)
         return cls(**settings)
 

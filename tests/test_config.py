@@ -71,7 +71,7 @@ def test_tuned_settings_by_size():
     one = HostStagedConfig.tuned(1, 4096)
     assert (one.channels, one.tx_warps, one.rx_warps, one.pipeline_stages) == (128, 2, 8, 3)
     eight = HostStagedConfig.tuned(8, 128, timeout_ms=1234)
-    assert (eight.channels, eight.tx_warps, eight.rx_warps, eight.timeout_ms) == (32, 2, 8, 1234)
+    assert (eight.channels, eight.tx_warps, eight.rx_warps, eight.timeout_ms) == (32, 4, 8, 1234)
     assert HostStagedConfig.tuned(4, 1024).channels == 64
     assert HostStagedConfig.tuned(2, 4096, channels=16).channels == 16
     import pytest
