@@ -220,6 +220,82 @@ def max_over_ranks(value):
     return float(t[0])
 
 
+REPEATS = 5  # the timed region (exactly --steps steps) is measured this many times; the median is reported
+
+
+def timed_repeats(step, steps, repeats=REPEATS):
+    """Time `steps` calls of step(i) `repeats` times, each bracketed by barrier + synchronize on both sides and a
+    CUDA-event pair on the launching stream.  Returns the per-repeat microseconds per step, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    samples = []
+    for _ in range(repeats):
+        dist.barrier()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            step(i)
+        end.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        samples.append(max_over_ranks(start.elapsed_time(end) * 1000.0 / steps))
+    return samples
+
+
+def summarise(samples):
+    return {"median": round(statistics.median(samples), 2), "min": round(min(samples), 2), "max": round(max(samples), 2),
+            "repeats": len(samples)}
+
+
+def hashed_tokens(rank, tokens, hidden, device):
+    """Token rows that any rank can regenerate from (source rank, token, column): small integers, exact in BF16."""
+    import torch
+
+    t = torch.arange(tokens, device=device, dtype=torch.int64).unsqueeze(1)
+    c = torch.arange(hidden, device=device, dtype=torch.int64).unsqueeze(0)
+    return (((rank * 131 + t * 7 + c * 3) % 251) - 125).to(torch.bfloat16)
+
+
+def verify_exchange(buffer, rank, world, tokens, topk, idx_cpu, dev_idx, dev_w, device):
+    """One dispatch + combine with regenerable payload: every received row is compared, on the GPU, with the row
+    its (source rank, source token) metadata says it must be; dedup counters are compared with the route volume;
+    the combined output is compared with the input (identity experts, weights sum to one).  Collective."""
+    import torch
+
+    x = hashed_tokens(rank, tokens, HIDDEN, device)
+    recv_x, recv_idx, _, handle, _ = buffer.dispatch(x, dev_idx, dev_w, do_expand=True)
+    combined, _, _ = buffer.combine(recv_x, handle)
+    torch.cuda.synchronize()
+    buffer.check_errors()
+    rows = int(handle.expanded_count)
+    meta = handle.source_meta[:rows]
+    problems, checked = [], 0
+    cols = torch.arange(HIDDEN, device=device, dtype=torch.int64).unsqueeze(0)
+    for lo in range(0, rows, 4096):
+        part = meta[lo:lo + 4096]
+        want = (((part[:, 0:1] * 131 + part[:, 1:2] * 7 + cols * 3) % 251) - 125).to(torch.bfloat16)
+        if not torch.equal(recv_x[lo:lo + part.shape[0]], want):
+            problems.append(f"rows {lo}..{lo + part.shape[0]} differ from their source")
+            break
+        checked += part.shape[0]
+    local = EXPERTS // world
+    ranks_hit = idx_cpu // local
+    remote = ranks_hit != rank
+    expect_sources = int(remote.any(dim=1).sum())
+    expect_deliveries = sum(int((ranks_hit == d).any(dim=1).sum()) for d in range(world) if d != rank)
+    stats = handle.stats.cpu().tolist()
+    if stats[0] != expect_sources or stats[2] != expect_deliveries:
+        problems.append(f"dedup counters {stats[:3]} != route volume ({expect_sources}, {expect_deliveries})")
+    if rows != tokens * topk and world == 1:
+        problems.append(f"expanded rows {rows} != {tokens * topk}")
+    if not torch.allclose(combined.float(), x.float(), rtol=3e-2, atol=1.0):
+        problems.append("combined output differs from the input beyond BF16 rounding")
+    del recv_x, recv_idx, handle, combined
+    return {"ok": not problems, "rows_checked": checked, "elements_checked": checked * HIDDEN, "problems": problems[:3]}
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -253,7 +329,6 @@ def run_ours(args, rank, world, local_rank):
                                   combine_reduce=args.combine_reduce, send_ctas=args.send_ctas,
                                   pipeline_stages=args.stages or tuned.pipeline_stages)
         buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
-        launches_per_step = 3 if buffer.runtime.combine_is_split() else 2  # dispatch, combine (+ its owner-side sum)
         g = torch.Generator().manual_seed(1234 + rank)
         host_x = [torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16).pin_memory() for _ in range(INPUT_SETS)]
         idx_cpu, w_cpu = make_routes(tokens, EXPERTS, args.topk, rank)
@@ -266,37 +341,51 @@ def run_ours(args, rank, world, local_rank):
             combined, _, _ = buffer.combine(recv_x, handle)
             return combined, handle
 
+        # correctness evidence inside this very run: payload, dedup counters and the round trip (not timed)
+        payload_check = verify_exchange(buffer, rank, world, tokens, args.topk, idx_cpu, dev_idx, dev_w, device)
+        verdicts = [None] * world
+        dist.all_gather_object(verdicts, payload_check)
+        if not all(v["ok"] for v in verdicts):
+            raise RuntimeError(f"payload check failed: {[v['problems'] for v in verdicts if not v['ok']]}")
+        payload_check["elements_checked_all_ranks"] = sum(v["elements_checked"] for v in verdicts)
         for i in range(warmup):
             out, handle = step(i)
         torch.cuda.synchronize()
         buffer.check_errors()
         del out, handle
-        sampler = ClockSampler(local_rank)
-        dist.barrier()
-        torch.cuda.synchronize()
-        sampler.start()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for i in range(steps):
+
+        def full_step(i):
             out, handle = step(i)
             del out, handle
-        end.record()
-        torch.cuda.synchronize()
-        dist.barrier()
-        clocks = sampler.stop()
-        total_ms = start.elapsed_time(end)
-        # split: dispatch alone
-        dist.barrier()
-        torch.cuda.synchronize()
-        d0.record()
-        for i in range(steps):
+
+        def dispatch_only(i):
             res = buffer.dispatch(dev_x[i % INPUT_SETS], dev_idx, dev_w, do_expand=True)
             del res
-        d1.record()
-        torch.cuda.synchronize()
-        dispatch_ms = d0.elapsed_time(d1)
+
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        total_samples = timed_repeats(full_step, steps)
+        clocks = sampler.stop()
+        dispatch_samples = timed_repeats(dispatch_only, steps, 3)
         buffer.check_errors()
+        # dispatch and combine each with an event pair of their own, inside the full step (one extra pass)
+        def split_pass():
+            # in a function of its own: no name of this scope keeps a result pool referenced afterwards
+            dist.barrier()
+            torch.cuda.synchronize()
+            marks = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+            for i in range(steps):
+                marks[i][0].record()
+                recv_x, _, _, handle, event = buffer.dispatch(dev_x[i % INPUT_SETS], dev_idx, dev_w, do_expand=True)
+                marks[i][1].record()
+                combined, _, cevent = buffer.combine(recv_x, handle)
+                marks[i][2].record()
+                del recv_x, handle, combined, event, cevent
+            torch.cuda.synchronize()
+            return (max_over_ranks(sum(m[0].elapsed_time(m[1]) for m in marks) * 1000.0 / steps),
+                    max_over_ranks(sum(m[1].elapsed_time(m[2]) for m in marks) * 1000.0 / steps))
+
+        dispatch_in_step, combine_in_step = split_pass()
         # the dispatch kernel's own span (first CTA start to last CTA end, %globaltimer): separates
         # device time from host launch overhead at small T
         res = buffer.dispatch(dev_x[0], dev_idx, dev_w, do_expand=True)
@@ -304,15 +393,29 @@ def run_ours(args, rank, world, local_rank):
         stamps = res[3].transport_timestamps_ns.cpu().tolist()
         kernel_us = (stamps[1] - stamps[0]) / 1000.0
         del res
+        kernels = ["dispatch_kernel"]
+        if buffer.runtime.combine_is_inline():
+            kernels.append("combine_kernel")
+        else:
+            kernels.append("combine_push_kernel")
+            if buffer.runtime.combine_is_split():
+                kernels.append("fused_reduce_kernel")
         result = {
-            "us_per_step": max_over_ranks(total_ms * 1000.0 / steps),
-            "dispatch_us": max_over_ranks(dispatch_ms * 1000.0 / steps),
+            "us_per_step": statistics.median(total_samples),
+            "spread": summarise(total_samples),
+            "dispatch_us": statistics.median(dispatch_samples),
+            "dispatch_in_step_us": dispatch_in_step,
+            "combine_us": combine_in_step,
             "dispatch_kernel_us": max_over_ranks(kernel_us),
             "clocks": clocks,
             "channels": channels,
-            "launches_per_step": launches_per_step,
-            "warps": f"1 control + {config.tx_warps} send + {config.rx_warps} receive/expand per channel CTA",
+            "kernels": kernels,
+            "launches_per_step": len(kernels),
+            "warps": (f"{buffer.runtime.send_ctas()} sender CTAs x {config.tx_warps} send warps, {channels} channel CTAs x "
+                      f"(1 control + {config.rx_warps} receive/expand warps)" if buffer.runtime.send_ctas() else
+                      f"1 control + {config.tx_warps} send + {config.rx_warps} receive/expand warps per channel CTA"),
             "roofline": roofline(idx_cpu, world, rank, tokens, args.topk, EXPERTS),
+            "payload_check": payload_check,
         }
         if want_e2e:
             checksum_host = torch.zeros(1, dtype=torch.float32).pin_memory()
@@ -356,14 +459,17 @@ def run_ours(args, rank, world, local_rank):
                 return total
 
             e2e_loop(min(3, warmup))
-            dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            e2e_loop(steps)
-            e1.record()
-            torch.cuda.synchronize()
-            result["e2e"] = {"value": max_over_ranks(e0.elapsed_time(e1) * 1000.0 / steps), "unit": "us/step",
+            e2e_samples = []
+            for _ in range(3):
+                dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                e2e_loop(steps)
+                e1.record()
+                torch.cuda.synchronize()
+                e2e_samples.append(max_over_ranks(e0.elapsed_time(e1) * 1000.0 / steps))
+            result["e2e"] = {"value": statistics.median(e2e_samples), "unit": "us/step", "spread": summarise(e2e_samples),
                              "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                              "how": "inputs double-buffered: a copy stream uploads step i+1 from pinned memory while step i runs; every step ends with a blocking 4-byte read of its checksum",
                              "host_numa_node": numa_node}
@@ -414,16 +520,21 @@ def run_ours(args, rank, world, local_rank):
                 "l2": f"inputs rotate over {INPUT_SETS} token sets ({INPUT_SETS * args.tokens * HIDDEN * 2 >> 20} MiB) and each "
                       "step writes staging + expanded rows well beyond the 126 MB L2",
             },
+            "timing": dict(headline["spread"], how=f"{REPEATS} timed regions of exactly --steps steps each, every one between "
+                                                   "barrier + synchronize and a CUDA-event pair, max over ranks; value = median"),
             "dispatch_us": round(headline["dispatch_us"], 2),
+            "dispatch_in_step_us": round(headline["dispatch_in_step_us"], 2),
             "dispatch_kernel_us": round(headline["dispatch_kernel_us"], 2),
-            "combine_us": round(value - headline["dispatch_us"], 2),
+            "combine_us": round(headline["combine_us"], 2),
+            "split_how": "dispatch_us: dispatch-only loops (median of 3); dispatch_in_step_us and combine_us: an event pair "
+                         "around each call inside full steps (one extra pass)",
             "clocks": headline["clocks"],
             "roofline": dict(headline["roofline"],
                              dispatch_fraction=round(headline["roofline"]["dispatch_us"] / headline["dispatch_us"], 3),
-                             combine_fraction=round(headline["roofline"]["combine_us"] / max(value - headline["dispatch_us"], 1e-9), 3)),
+                             combine_fraction=round(headline["roofline"]["combine_us"] / max(headline["combine_us"], 1e-9), 3)),
             "gpu_launches": headline["launches_per_step"] * args.steps,
-            "kernels_per_step": "dispatch_kernel, combine_kernel" + (", fused_reduce_kernel (owner-side sum of combine)"
-                                                                       if headline["launches_per_step"] == 3 else ""),
+            "kernels_per_step": ", ".join(headline["kernels"]),
+            "payload_check": headline["payload_check"],
             "impl": "ours",
         }
         if "e2e" in headline:
@@ -462,21 +573,16 @@ def run_reference(args, rank, world, local_rank):
             del res
         torch.cuda.synchronize()
         buffer.check_errors()
-        sampler = ClockSampler(local_rank)
-        dist.barrier()
-        torch.cuda.synchronize()
-        sampler.start()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for i in range(args.steps):
+        def reference_step(i):
             res = buffer.dispatch(xs[i % INPUT_SETS], idx, w, do_expand=True)
             del res
-        end.record()
-        torch.cuda.synchronize()
-        dist.barrier()
+
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        samples = timed_repeats(reference_step, args.steps)
         clocks = sampler.stop()
         buffer.check_errors()
-        value = max_over_ranks(start.elapsed_time(end) * 1000.0 / args.steps)
+        value = statistics.median(samples)
         e2e = None
         if not args.no_e2e:
             # the same serving loop as the other arm around the reference's dispatch: pinned host inputs uploaded
@@ -517,15 +623,18 @@ def run_reference(args, rank, world, local_rank):
                     del res
 
             e2e_loop(min(3, args.warmup))
-            dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            e2e_loop(args.steps)
-            e1.record()
-            torch.cuda.synchronize()
+            e2e_samples = []
+            for _ in range(3):
+                dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                e2e_loop(args.steps)
+                e1.record()
+                torch.cuda.synchronize()
+                e2e_samples.append(max_over_ranks(e0.elapsed_time(e1) * 1000.0 / args.steps))
             buffer.check_errors()
-            e2e = {"value": max_over_ranks(e0.elapsed_time(e1) * 1000.0 / args.steps), "unit": "us/step",
+            e2e = {"value": round(statistics.median(e2e_samples), 2), "unit": "us/step", "spread": summarise(e2e_samples),
                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                    "how": "same double-buffered upload loop as the other arm around the reference's dispatch (it has no combine)"}
         buffer.close()
@@ -553,6 +662,8 @@ def run_reference(args, rank, world, local_rank):
             "config": {"model": "DeepSeek-V3-shaped MoE dispatch", "tokens_per_rank": args.tokens,
                        "global_batch": args.tokens * world, "seq_len": 1, "parallelism": f"ep{world}",
                        "transport": "host_staged (reference default config)"},
+            "timing": dict(summarise(samples), how=f"{REPEATS} timed regions of exactly --steps steps, median"),
+            "dispatch_us": round(value, 2),
             "clocks": clocks, "gpu_launches": 8 * args.steps,
             **({"e2e": e2e} if e2e is not None else {}),
         }), flush=True)

@@ -52,6 +52,8 @@ struct RuntimeOptions {
     bool wire_fp8 = false;
     bool recv_fp8 = false;
     bool use_tma = true;
+    bool host_segments = false;  // the segments are registered host memory (transport "host_staged")
+    bool force_scalar = false;  // ablation: 2-byte register copies even where 16-byte accesses would be legal
     int tx_warps = 2;
     int rx_warps = 8;
     int send_stages = 3;
@@ -76,6 +78,8 @@ struct RuntimeOptions {
         o.recv_fp8 = get("recv_dtype", std::string("bf16")) == "fp8_e4m3";
         if (o.recv_fp8 && !o.wire_fp8) throw std::invalid_argument("recv_dtype fp8_e4m3 needs wire_dtype fp8_e4m3");
         o.use_tma = get("copy_engine", std::string("tma")) == "tma";
+        o.force_scalar = get("force_scalar", false);
+        o.host_segments = get("segment_kind", std::string("peer")) == "host_staged";
         o.tx_warps = get("tx_warps", o.tx_warps);
         o.rx_warps = get("rx_warps", o.rx_warps);
         o.send_stages = get("pipeline_stages", o.send_stages);
@@ -262,7 +266,7 @@ class Runtime {
         // automatic choice: one sender CTA per eight channels, at most sixteen (sixteen SMs saturate NVLink)
         if (options_.send_ctas < 0) options_.send_ctas = num_ranks > 1 ? std::min(16, std::max(1, options_.channels / 8)) : 0;
         if (num_ranks == 1) options_.send_ctas = 0;  // nothing leaves a single rank
-        const bool vec_ok = (hidden * 2) % 16 == 0;
+        const bool vec_ok = (hidden * 2) % 16 == 0 && !options_.force_scalar;
         use_tma_ = options_.use_tma && vec_ok && !(options_.recv_fp8 && hidden % 16 != 0);
         if (dispatch_row_buffer_count(options_.tx_warps, options_.rx_warps, options_.send_stages, options_.send_ctas) > kMaxRowBuffers)
             throw std::invalid_argument("tx_warps * pipeline_stages + rx_warps exceeds the row buffers a CTA can manage");
@@ -315,6 +319,7 @@ class Runtime {
         rc_.rx_warps = options_.rx_warps;
         rc_.send_stages = options_.send_stages;
         rc_.send_ctas = options_.send_ctas;
+        rc_.fence_flags = options_.host_segments ? 1 : 0;
         rc_.plan_flags = reinterpret_cast<std::uint64_t*>(plan_flags_.data_ptr<std::int64_t>());
         rc_.unique_cap = P * num_max_tokens;
         rc_.expanded_cap = P * num_max_tokens * std::min(K, lay_.num_local_experts) + lay_.num_local_experts * 255;
@@ -338,10 +343,13 @@ class Runtime {
             plans_.push_back(make_layout());
         }
         // finished CTAs of the launch in flight: [0] scatter GEMM, [1] fused reduction, [2] combine owner-side sum,
-        // [3] combine push; [4..5] statistics accumulators of the combine push
-        fused_counters_ = at::zeros({8}, i64);
+        // [3] combine push; [4..8] statistics accumulators of the combine push
+        fused_counters_ = at::zeros({12}, i64);
+        fused_counters_[6] = -1;  // "first start" accumulator of the combine push: all ones = unset
         fused_status_ = at::zeros({4}, i32);
         fused_gemm_ctas_ = grouped_gemm_ctas();
+        combine_forward_ctas_ = std::min(16, std::max(1, fused_gemm_ctas_ / 8));
+        if (options_.enable_combine && num_ranks > 1 && !combine_is_inline()) ensure_outbox();
         if (options_.enable_combine) {
             const auto bf16 = at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device);
             for (int i = 0; i < options_.output_pool_size; ++i)
@@ -493,6 +501,12 @@ class Runtime {
         push.stats = a.stats;
         push.cta_done = counters + 3;
         push.stat_scratch = counters + 4;
+        push.forward_ctas = lay_.num_ranks > 1 ? combine_forward_ctas_ : 0;
+        if (push.forward_ctas > 0) {
+            ensure_outbox();
+            push.outbox = outbox_.data_ptr<std::uint8_t>();
+            push.outbox_units = reinterpret_cast<unsigned long long*>(outbox_units_.data_ptr<std::int64_t>());
+        }
         p.reduce_needed = lay_.num_ranks > 1;
         if (p.reduce_needed) {
             FusedReduceArgs& r = p.reduce;
@@ -528,7 +542,12 @@ class Runtime {
     }
 
     void launch_combine_push(PreparedCombine& prepared, cudaStream_t stream, int num_sms = 0) {
-        cuda_check(bep::launch_combine_push(prepared.push, combine_ctas(3, num_sms), stream), "combine push launch");
+        const int forward = prepared.push.forward_ctas;
+        // two reducer CTAs per SM; with `num_sms` the whole launch (forwarders included) stays inside that many SMs
+        // forwarders + reducers together never exceed what is resident at once (a reducer CTA that had to wait for a
+        // slot would hold back the forwarders, which take rows in order)
+        const int reducers = std::max(2, combine_ctas(2, num_sms) - forward);
+        cuda_check(bep::launch_combine_push(prepared.push, reducers, combine_push_smem_bytes(lay_, forward), stream), "combine push launch");
     }
     // second launch of the default combine; `prepared` comes from prepare_combine of this runtime
     void launch_combine_reduce(PreparedCombine& prepared, cudaStream_t stream, int num_sms = 0) {
@@ -685,6 +704,8 @@ class Runtime {
     at::Tensor epochs() const { return epochs_; }
 
     void close() {
+        outbox_ = at::Tensor();
+        outbox_units_ = at::Tensor();
         pools_.clear();
         plans_.clear();
         combine_pool_.clear();
@@ -775,6 +796,13 @@ class Runtime {
         return plan;
     }
 
+    void ensure_outbox() {
+        if (outbox_.defined()) return;
+        const std::int64_t rows = static_cast<std::int64_t>(lay_.num_ranks) * lay_.num_channels * lay_.slots_full;
+        outbox_ = at::empty({rows * lay_.crow_stride}, at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device_));
+        outbox_units_ = at::zeros({rows}, at::TensorOptions().dtype(at::kLong).device(at::kCUDA, device_));
+    }
+
     std::shared_ptr<OutputSet> select_output(bool graph_pool) {
         if (graph_pool) {
             if (!options_.enable_graph) throw std::runtime_error("graph pool requires enable_graph=True");
@@ -828,6 +856,8 @@ class Runtime {
     std::vector<std::shared_ptr<Layout>> plans_;
     std::vector<at::Tensor> combine_pool_;
     at::Tensor fused_counters_, fused_status_;
+    at::Tensor outbox_, outbox_units_;  // combine: local staging of rows owned by other ranks + per-row unit counters
+    int combine_forward_ctas_ = 16;
     std::uint64_t fused_gemm_epoch_ = 0, fused_reduce_epoch_ = 0;
     int fused_gemm_ctas_ = 0;
     int next_pool_ = 0;

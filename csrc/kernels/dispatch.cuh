@@ -548,6 +548,9 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
     // Every bulk copy of this warp is issued, committed and awaited by lane 31, which never stores a flag
     // (flags belong to lanes 0..P-1).
     const bool issuer = lane == 31u;
+    // Segments in registered host memory: completion of a bulk group does not mean its writes have reached host
+    // memory (they are posted over PCIe), so there the issuing lane does execute the system-scope fence.
+    const bool fence_flags = rc->fence_flags != 0;
     const unsigned self_bit = 1u << k.me;
     const bool delayed = w == k.send_warps - 1;
     const int P = k.P, K = k.K;
@@ -561,7 +564,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
     const std::uint32_t seq_epoch = static_cast<std::uint32_t>(k.epoch) + (rc->test_corrupt_sequence ? 1u : 0u);
     BEP_ROLE_DECL();
 
-    // Candidates of this CTA: the tokens of its channels, channel after channel; this warp takes every W-th one.
+    // Candidates of this CTA: the tokens of its channels, interleaved; this warp takes every W-th one.
     const int W = k.send_warps;
     const int n_ch = k.send_first < k.C ? (k.C - k.send_first + k.send_stride - 1) / k.send_stride : 0;
     const int n_cand = n_ch * k.Tc;
@@ -580,9 +583,11 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
         my_mask = 0u;
         const int ql = w + (b * 32 + static_cast<int>(lane)) * W;
         if (ql < n_cand) {
-            const int i = ql / k.Tc;
+            // candidates go round the CTA's channels (candidate q = token q / n_ch of channel q % n_ch), so that every
+            // channel's receiver sees rows from the start instead of one channel after the other
+            const int i = ql % n_ch;
             my_ch = k.send_first + i * k.send_stride;
-            const int t = my_ch * k.Tc + (ql - i * k.Tc);
+            const int t = my_ch * k.Tc + ql / n_ch;
             if (t < k.T) {
                 if (!a.cached && k.plan_is_foreign) {
                     const std::uint64_t* plan_flag = rc->plan_flags + my_ch;
@@ -720,7 +725,10 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
                 have = ptx::ld_acquire_sys(ack) == want;
             }
             if (!__all_sync(full, have)) {
-                if (issuer) bulk_wait_group<0>();
+                if (issuer) {
+                    bulk_wait_group<0>();
+                    if (fence_flags) ptx::fence_sys();
+                }
                 __syncwarp();
 #pragma unroll
                 for (int i = 0; i < kFlagLag; ++i) {
@@ -773,7 +781,10 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
         // READY flags of the row issued kFlagLag turns ago: its bulk group is complete by now (or is awaited here)
         if (n >= kFlagLag) {
             BEP_ROLE_T(t_store);
-            if (issuer) bulk_wait_group<kFlagLag>();
+            if (issuer) {
+                bulk_wait_group<kFlagLag>();
+                if (fence_flags) ptx::fence_sys();
+            }
             __syncwarp();
             if (flag_ring[0] != nullptr) ptx::st_relaxed_sys(flag_ring[0], make_seq(k.epoch, flag_seq[0]));
             BEP_ROLE_ADD(kRoleStoreWaitNs, t_store);
@@ -798,7 +809,10 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
     // drain: the last rows' groups, then their flags in row order
     {
         BEP_ROLE_T(t_store);
-        if (issuer) bulk_wait_group<0>();
+        if (issuer) {
+            bulk_wait_group<0>();
+            if (fence_flags) ptx::fence_sys();
+        }
         __syncwarp();
         if (!broke && !warp_failed(health)) {
 #pragma unroll
@@ -834,9 +848,8 @@ __device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& healt
     const int n_cand = n_ch * k.Tc;
     for (int q = w; q < n_cand; q += k.send_warps) {
         if (warp_failed(health)) break;
-        const int ch_i = q / k.Tc;
-        const int ch = k.send_first + ch_i * k.send_stride;
-        const int t = ch * k.Tc + (q - ch_i * k.Tc);
+        const int ch = k.send_first + (q % n_ch) * k.send_stride;  // round the CTA's channels
+        const int t = ch * k.Tc + q / n_ch;
         if (t >= k.T) continue;
         if (!a.cached && k.plan_is_foreign) {
             // a dedicated sender reads a plan that the channel's own CTA writes in this launch
@@ -1432,6 +1445,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     } else if (warp == 0) {
         // ===== control: receive prefix from every source's counts message, then zero padding =====
         const unsigned long long prefix_t0 = ptx::globaltimer_ns();
+        // test hook: this rank publishes an abort in mid-transfer (a legal owner writing its own abort flag) while
+        // its send warps and its peers are busy
+        if (c == 0 && rc->test_abort_after_ns != 0) {
+            while (ptx::globaltimer_ns() < t_start + rc->test_abort_after_ns) ptx::nanosleep(200);
+            if (lane == 0) record_error(rc, a.error, kErrInjectedAbort, me, 0);
+            __syncwarp();
+        }
         if (lane < static_cast<unsigned>(P)) {
             const std::uint64_t* flag = flag_ptr(my_seg, lay.counts_flag_off, lane);
             while (ptx::ld_acquire_sys(flag) != epoch) {
@@ -1544,11 +1564,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                     }
                 }
             }
-        }
-        // test hook: this rank publishes an abort in mid-transfer (a legal owner writing its own abort flag)
-        if (c == 0 && rc->test_abort_after_ns != 0 && !warp_failed(health)) {
-            while (ptx::globaltimer_ns() < t_start + rc->test_abort_after_ns) ptx::nanosleep(200);
-            if (lane == 0) record_error(rc, a.error, kErrInjectedAbort, me, 0);
         }
     } else if (S == 0 && warp <= tx_warps) {
         // ===== send (inside the channel CTA) =====

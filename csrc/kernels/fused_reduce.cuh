@@ -1,11 +1,10 @@
 // The ordinary (non-cooperative, fully occupied) launches of the combine paths.
 //
 // combine_push_kernel -- expert side of `combine`: for every row this rank received in the dispatch, reduce the
-//   expert outputs of that token with the dispatch-time weights in FP32, round to BF16 and store the partial row
-//   straight into the token owner's landing area over NVLink (16-byte stores, 512 contiguous bytes per warp
-//   instruction).  The launch's last CTA publishes the epoch to every owner.  Nothing in it waits on another
-//   kernel of the same launch wave, so it needs no co-residency and any grid size works.  With one rank the
-//   reduced rows are the result and go straight to `out`.
+//   expert outputs of that token with the dispatch-time weights in FP32, round to BF16 and deliver the partial
+//   row to the token owner's landing area: reducer CTAs write it to a local outbox, a few forwarder CTAs of the
+//   same launch copy completed rows over NVLink with bulk copies.  The launch's last CTA publishes the epoch to
+//   every owner.  With one rank the reduced rows are the result and go straight to `out`.
 // fused_reduce_kernel -- owner side: producers on every rank have written weighted BF16 rows into this rank's
 //   landing area and published their epoch; this kernel waits -- bounded -- for every rank's epoch, adds the rows
 //   of every token in slot order (FP32, deterministic) and hands the area back.  Two producers use it:
@@ -46,10 +45,24 @@ struct CombinePushArgs {
     int weighted;
     __nv_bfloat16* out;            // [T, H]; written here only with a single rank
     int* error;                    // [8]
-    std::int64_t* stats;           // [8]: rows pushed, of which to other ranks
+    std::int64_t* stats;           // [8]: rows pushed, of which to other ranks, ns until the last reducer CTA / the last
+                                   // forwarder CTA had finished (from the first CTA's start)
     unsigned long long* cta_done;  // CTAs of this launch that have finished; the last one puts it back to zero
-    unsigned long long* stat_scratch;  // [2] accumulators, zero between launches
+    unsigned long long* stat_scratch;  // [5] accumulators (rows, remote rows, first start, last reducer end, last forwarder
+                                       // end); zero between launches, the first start all ones
+    // rows whose owner is another rank are reduced into a local outbox and forwarded by dedicated CTAs
+    std::uint8_t* outbox;              // [P*C*slots_full][crow_stride], local memory
+    unsigned long long* outbox_units;  // [P*C*slots_full] finished units of the row in the outbox; zero between launches
+    int forward_ctas;                  // the first CTAs of the grid only forward; 0 with a single rank
 };
+
+constexpr int kPushGroupsPerUnit = 4;
+constexpr int kForwardWarps = 2;   // per forwarder CTA
+constexpr int kForwardStages = 2;  // row buffers per forwarder warp
+
+inline std::size_t combine_push_smem_bytes(const SegmentLayout& lay, int forward_ctas) {
+    return forward_ctas > 0 ? 128 + static_cast<std::size_t>(kForwardWarps) * kForwardStages * lay.crow_stride : 0;
+}
 
 #ifdef __CUDACC__
 
@@ -157,15 +170,55 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 4) fused_reduce_kernel(co
     }
 }
 
-// Work unit = (entry of the dispatch's combine map, group of 32 sixteen-byte chunks): one warp iteration with up to
-// eight row loads per lane in flight.  Entries are numbered (channel, row index, source step) with the source
-// fastest and rotated by this rank's index, so that at any moment a rank writes to all its peers at once and no
-// owner is the target of every rank at the same time.  Units are dealt out in equal contiguous ranges.
-__global__ void __launch_bounds__(kFusedReduceThreads, 3) combine_push_kernel(const CombinePushArgs a) {
+// Expert side of combine.  Work unit = (entry of the dispatch's combine map, four groups of 32 sixteen-byte
+// chunks): one warp iteration keeps eight row loads per lane in flight, whether the entry reduces one expert row
+// or eight.  Entries are numbered (channel, row index, source step) with the source fastest and rotated by this
+// rank's index; units are dealt out round-robin over the warps of the grid, so the entries complete roughly in
+// their numbering order.
+//
+// Where the reduced row goes:
+//   * one rank: straight to `out`;
+//   * owner = this rank: straight into this rank's own landing area (a local store);
+//   * owner = another rank: into a local outbox row.  The first `forward_ctas` CTAs of the grid do nothing but
+//     copy completed outbox rows to their owners (bulk load into shared memory, bulk store to the peer).  A few SMs
+//     saturate NVLink, and an SM with remote stores in flight loses most of its load and store throughput, so
+//     confining the remote stores to those CTAs lets every other SM reduce at full HBM speed.
+// A forwarder learns that an outbox row is complete from a per-entry counter of finished units (bounded wait).
+// Forwarders never hold up a reducer, and reducers never wait for anything but the reuse guard, so the launch
+// needs no co-residency guarantee: it is an ordinary launch and any grid size works.
+namespace push_detail {
+
+struct Entry {
+    bool present;
+    int s, token, n, slot;  // owner rank, its token, expert rows to reduce, index of the entry in the combine map
+};
+
+// entry number -> (channel, row index, owner); `slot` addresses the combine map and the outbox
+__device__ __forceinline__ Entry locate_entry(const CombinePushArgs& a, const SegmentLayout& lay, long long entry, int J, int me) {
+    const int P = lay.num_ranks, C = lay.num_channels, Qf = lay.slots_full;
+    Entry e;
+    const int step = static_cast<int>(entry % P);
+    const long long cj = entry / P;
+    const int c = static_cast<int>(cj / J), j = static_cast<int>(cj % J);
+    e.s = (me + 1 + step) % P;
+    e.present = j < a.recv_chan_counts[e.s * C + c];
+    e.slot = (e.s * C + c) * Qf + j;
+    e.token = 0;
+    e.n = 0;
+    return e;
+}
+
+}  // namespace push_detail
+
+__global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(const CombinePushArgs a) {
+    using namespace push_detail;
     const RankConst* rc = a.rc;
     const SegmentLayout& lay = rc->lay;
     const int P = lay.num_ranks, C = lay.num_channels, Qf = lay.slots_full, K = lay.num_topk, H = lay.hidden;
     const int me = rc->rank;
+    const int F = a.forward_ctas;
+    const bool forwarder = static_cast<int>(blockIdx.x) < F;
+    extern __shared__ __align__(128) unsigned char push_smem[];
     __shared__ int s_failed;
     __shared__ int s_max_rows;
     if (threadIdx.x == 0) {
@@ -175,6 +228,7 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 3) combine_push_kernel(co
     __syncthreads();
     const bool aborted = ptx::ld_volatile(&rc->sticky[0]) != 0;
     const std::uint64_t epoch = rc->epochs[1] + 1;
+    if (threadIdx.x == 0) atomicMin(&a.stat_scratch[2], ptx::globaltimer_ns());  // all ones between launches
     if (aborted) {
         if (threadIdx.x == 0) {
             if (blockIdx.x == 0) atomicCAS(&a.error[0], 0, kErrAlreadyAborted);
@@ -191,7 +245,7 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 3) combine_push_kernel(co
             }
         }
     }
-    // the longest (source, channel) list bounds the row index of the unit space
+    // the longest (source, channel) list bounds the row index of the entry space
     {
         int local_max = 0;
         for (int i = threadIdx.x; i < P * C; i += blockDim.x) local_max = max(local_max, a.recv_chan_counts[i]);
@@ -199,89 +253,238 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 3) combine_push_kernel(co
     }
     __syncthreads();
 
+    const int map_stride = 2 + 2 * K;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warps = kFusedReduceThreads / 32;
+    const int chunks = H * 2 / 16;
+    const int groups = (chunks + 31) / 32;
+    const int units_per_entry = (groups + kPushGroupsPerUnit - 1) / kPushGroupsPerUnit;
+    const int J = min(s_max_rows, Qf);
+    const long long entries = static_cast<long long>(C) * J * P;
+    const std::size_t rank_stride = static_cast<std::size_t>(lay.num_max_tokens) * lay.crow_stride;
     unsigned long long pushed = 0, pushed_remote = 0;
-    if (!s_failed) {
-        const int map_stride = 2 + 2 * K;
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        const int warps = kFusedReduceThreads / 32;
-        const int chunks = H * 2 / 16;
-        const int groups = (chunks + 31) / 32;
-        const int J = min(s_max_rows, Qf);
-        const long long total_warps = static_cast<long long>(gridDim.x) * warps;
-        const long long wid = static_cast<long long>(blockIdx.x) * warps + warp;
-        const long long units = static_cast<long long>(C) * J * P * groups;
-        const long long first = units * wid / total_warps, last = units * (wid + 1) / total_warps;
+
+    if (!s_failed && forwarder) {
+        // ---- forward completed outbox rows to their owners --------------------------------------------
+        if (warp < kForwardWarps) {
+            Health health(rc, a.error);
+            const int fw = blockIdx.x * kForwardWarps + warp, fws = F * kForwardWarps;
+            unsigned char* buffers = push_smem + 128 + static_cast<std::size_t>(warp) * kForwardStages * lay.crow_stride;
+            unsigned long long* bars = reinterpret_cast<unsigned long long*>(push_smem) + warp * kForwardStages;
+            const bool issuer = lane == 31;
+            const unsigned row_bytes = static_cast<unsigned>(H) * 2u;
+            if (lane == 0)
+                for (int i = 0; i < kForwardStages; ++i) ptx::mbar_init(reinterpret_cast<std::uint64_t*>(&bars[i]), 1);
+            ptx::mbar_fence_init();
+            __syncwarp();
+            // Rows owned by other ranks, numbered like the entries but without the local owner's step; this warp
+            // takes every fws-th of them, in increasing order (the order in which the reducers finish them).
+            // Everything a row needs from global memory -- is the entry present, whose token is it, is the row
+            // complete -- is fetched for 32 candidates at a time, one per lane: on an SM that is busy storing to
+            // peers a dependent load per row would cost more than the row's copy.
+            const long long remote_entries = static_cast<long long>(C) * J * (P - 1);
+            long long batch_base = fw;   // remote-entry number of lane 0's candidate in the next batch
+            unsigned todo = 0;           // lanes of the current batch whose rows still have to be forwarded
+            int my_slot = 0, my_owner = 0, my_token = 0;
+            bool my_ready = false;
+            int issued = 0, sent = 0;
+            std::uint8_t* dst_of[kForwardStages];
+            bool ok = true;
+            auto load_batch = [&]() {
+                const long long q = batch_base + static_cast<long long>(lane) * fws;
+                batch_base += 32ll * fws;
+                bool present = false;
+                my_ready = false;
+                if (q < remote_entries) {
+                    const int step = static_cast<int>(q % (P - 1));
+                    const Entry e = locate_entry(a, lay, (q / (P - 1)) * P + step, J, me);  // steps 0..P-2 are the other ranks
+                    present = e.present;
+                    if (present) {
+                        my_slot = e.slot;
+                        my_owner = e.s;
+                        my_token = a.comb_map[static_cast<std::size_t>(e.slot) * map_stride];
+                        my_ready = ptx::ld_acquire_gpu(reinterpret_cast<const std::uint64_t*>(a.outbox_units + e.slot)) >=
+                                   static_cast<std::uint64_t>(units_per_entry);
+                    }
+                }
+                todo = __ballot_sync(0xffffffffu, present);
+            };
+            // Start loading this warp's next row if there is one and it is complete.  `may_block`: wait (bounded) for
+            // it to become complete; otherwise return at once when it is not, so that a loaded row is never held back.
+            auto issue_next = [&](bool may_block) -> bool {
+                while (todo == 0u) {
+                    if (batch_base >= remote_entries) return false;
+                    load_batch();
+                }
+                const int src = __ffs(todo) - 1;
+                const int slot = __shfl_sync(0xffffffffu, my_slot, src);
+                const int owner = __shfl_sync(0xffffffffu, my_owner, src);
+                const int token = __shfl_sync(0xffffffffu, my_token, src);
+                int state = __shfl_sync(0xffffffffu, my_ready ? 1 : 0, src);  // 1 complete, 0 not yet, -1 gave up
+                if (state == 0) {
+                    if (lane == 0) {
+                        const auto* done_units = reinterpret_cast<const std::uint64_t*>(a.outbox_units + slot);
+                        state = 1;
+                        while (ptx::ld_acquire_gpu(done_units) < static_cast<std::uint64_t>(units_per_entry)) {
+                            if (!may_block) {
+                                state = 0;
+                                break;
+                            }
+                            if (health.give_up(kErrRowWait, owner, slot)) {
+                                state = -1;
+                                break;
+                            }
+                        }
+                    }
+                    state = __shfl_sync(0xffffffffu, state, 0);
+                    if (state == 1 && static_cast<int>(lane) == src) my_ready = true;
+                }
+                if (state < 0) ok = false;
+                if (state != 1) return false;
+                todo &= todo - 1;
+                // every producer of this row has finished: its counter starts the next combine at zero
+                if (lane == 0) a.outbox_units[slot] = 0ull;
+                const int b = issued % kForwardStages;
+                dst_of[b] = rc->seg[owner] + lay.cstage_off + static_cast<std::size_t>(me) * rank_stride +
+                            static_cast<std::size_t>(token) * lay.crow_stride;
+                __syncwarp();  // the lane that saw the row complete, before the lane that copies it
+                if (issuer) {
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the buffer's previous row has left it
+                    ptx::mbar_expect_tx(reinterpret_cast<std::uint64_t*>(&bars[b]), row_bytes);
+                    ptx::bulk_g2s(buffers + static_cast<std::size_t>(b) * lay.crow_stride,
+                                  a.outbox + static_cast<std::size_t>(slot) * lay.crow_stride, row_bytes,
+                                  reinterpret_cast<std::uint64_t*>(&bars[b]));
+                }
+                ++issued;
+                return true;
+            };
+            while (ok) {
+                // keep up to kForwardStages rows between "load issued" and "store issued"; only block for a row
+                // when nothing is loaded
+                while (ok && issued - sent < kForwardStages && issue_next(issued == sent)) {}
+                if (!ok || issued == sent) break;
+                const int b = sent % kForwardStages;
+                while (!ptx::mbar_try_wait(reinterpret_cast<std::uint64_t*>(&bars[b]), static_cast<unsigned>(sent / kForwardStages) & 1u)) {
+                    if (health.give_up(kErrCopyEngine, static_cast<int>(blockIdx.x), 1)) {
+                        ok = false;
+                        break;
+                    }
+                }
+                ok = __all_sync(0xffffffffu, ok) != 0;
+                if (!ok) break;
+                if (issuer) {
+                    ptx::bulk_s2g(dst_of[b], buffers + static_cast<std::size_t>(b) * lay.crow_stride, row_bytes);
+                    ptx::bulk_commit();
+                }
+                ++sent;
+            }
+            if (issuer) ptx::bulk_wait_all();  // every forwarded row has been performed at its owner
+            // loads still in flight after a failure: give them a bounded time to land
+            for (int r = sent; r < issued; ++r) {
+                unsigned polls = 0;
+                while (!ptx::mbar_try_wait(reinterpret_cast<std::uint64_t*>(&bars[r % kForwardStages]), static_cast<unsigned>(r / kForwardStages) & 1u) &&
+                       ++polls < (1u << 20))
+                    ptx::nanosleep(64);
+            }
+            if (!ok && lane == 0) s_failed = 1;
+        }
+    } else if (!s_failed) {
+        // ---- reduce ----------------------------------------------------------------------------------------
+        const long long total_warps = static_cast<long long>(gridDim.x - F) * warps;
+        const long long wid = static_cast<long long>(blockIdx.x - F) * warps + warp;
+        const long long units = entries * units_per_entry;
         const std::uint8_t* y = reinterpret_cast<const std::uint8_t*>(a.y);
         const std::size_t row_bytes = static_cast<std::size_t>(H) * 2;
-        const std::size_t rank_stride = static_cast<std::size_t>(lay.num_max_tokens) * lay.crow_stride;
-        long long cached_entry = -1;
-        bool present = false;
-        int n = 0, row_of_lane = 0;
-        float weight_of_lane = 1.0f;
-        std::uint8_t* dst_row = nullptr;
-        for (long long u = first; u < last; ++u) {
-            const long long entry = u / groups;  // = (c * J + j) * P + step
-            if (entry != cached_entry) {
-                cached_entry = entry;
-                const int step = static_cast<int>(entry % P);
-                const long long cj = entry / P;
-                const int c = static_cast<int>(cj / J), j = static_cast<int>(cj % J);
-                const int s = (me + 1 + step) % P;
-                present = j < a.recv_chan_counts[s * C + c];
-                if (present) {
-                    const int* map = a.comb_map + ((static_cast<std::size_t>(s) * C + c) * Qf + j) * map_stride;
-                    const int token = map[0];
-                    n = map[1];
-                    if (lane < n) {
-                        row_of_lane = map[2 + 2 * lane];
-                        weight_of_lane = a.weighted ? __int_as_float(map[3 + 2 * lane]) : 1.0f;
+        for (long long u = wid; u < units; u += total_warps) {
+            const long long entry_no = u / units_per_entry;
+            const int unit = static_cast<int>(u % units_per_entry);
+            Entry e = locate_entry(a, lay, entry_no, J, me);
+            if (!e.present) continue;
+            const int* map = a.comb_map + static_cast<std::size_t>(e.slot) * map_stride;
+            e.token = map[0];
+            e.n = map[1];
+            int row_of_lane = 0;
+            float weight_of_lane = 1.0f;
+            if (lane < e.n) {
+                row_of_lane = map[2 + 2 * lane];
+                weight_of_lane = a.weighted ? __int_as_float(map[3 + 2 * lane]) : 1.0f;
+            }
+            const bool remote = P > 1 && e.s != me;
+            std::uint8_t* dst_row =
+                P == 1 ? reinterpret_cast<std::uint8_t*>(a.out + static_cast<std::size_t>(e.token) * H)
+                : remote ? a.outbox + static_cast<std::size_t>(e.slot) * lay.crow_stride
+                         : rc->seg[me] + lay.cstage_off + static_cast<std::size_t>(me) * rank_stride + static_cast<std::size_t>(e.token) * lay.crow_stride;
+            if (lane == 0 && unit == 0) {
+                ++pushed;
+                if (remote) ++pushed_remote;
+            }
+            const int q0 = unit * kPushGroupsPerUnit * 32 + lane;  // this lane's chunk in the unit's first group
+            float acc[kPushGroupsPerUnit][8];
+#pragma unroll
+            for (int g = 0; g < kPushGroupsPerUnit; ++g)
+#pragma unroll
+                for (int x = 0; x < 8; ++x) acc[g][x] = 0.0f;
+            // rows two at a time, four chunk groups each: eight 16-byte loads per lane in flight
+            for (int i0 = 0; i0 < e.n; i0 += 2) {
+                const int r0 = __shfl_sync(0xffffffffu, row_of_lane, i0);
+                const int r1 = __shfl_sync(0xffffffffu, row_of_lane, min(i0 + 1, e.n - 1));
+                const float w0 = __shfl_sync(0xffffffffu, weight_of_lane, i0);
+                const float w1 = i0 + 1 < e.n ? __shfl_sync(0xffffffffu, weight_of_lane, min(i0 + 1, e.n - 1)) : 0.0f;
+                const bool two = i0 + 1 < e.n;
+                uint4 v0[kPushGroupsPerUnit], v1[kPushGroupsPerUnit];
+#pragma unroll
+                for (int g = 0; g < kPushGroupsPerUnit; ++g) {
+                    const int q = q0 + g * 32;
+                    v0[g] = q < chunks ? ptx::ld_nc_v4(y + static_cast<std::size_t>(r0) * row_bytes + static_cast<std::size_t>(q) * 16) : make_uint4(0u, 0u, 0u, 0u);
+                    v1[g] = (two && q < chunks) ? ptx::ld_nc_v4(y + static_cast<std::size_t>(r1) * row_bytes + static_cast<std::size_t>(q) * 16) : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int g = 0; g < kPushGroupsPerUnit; ++g) {
+                    const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0[g]);
+                    const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1[g]);
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        const float2 f0 = __bfloat1622float2(h0[x]);
+                        acc[g][2 * x] = fmaf(w0, f0.x, acc[g][2 * x]);
+                        acc[g][2 * x + 1] = fmaf(w0, f0.y, acc[g][2 * x + 1]);
                     }
-                    dst_row = P == 1 ? reinterpret_cast<std::uint8_t*>(a.out + static_cast<std::size_t>(token) * H)
-                                     : rc->seg[s] + lay.cstage_off + static_cast<std::size_t>(me) * rank_stride +
-                                           static_cast<std::size_t>(token) * lay.crow_stride;
-                    // an entry spans `groups` units, possibly of two warps: it is counted with its first unit
-                    if (lane == 0 && u % groups == 0) {
-                        ++pushed;
-                        if (s != me) ++pushed_remote;
+                    if (two) {
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            const float2 f1 = __bfloat1622float2(h1[x]);
+                            acc[g][2 * x] = fmaf(w1, f1.x, acc[g][2 * x]);
+                            acc[g][2 * x + 1] = fmaf(w1, f1.y, acc[g][2 * x + 1]);
+                        }
                     }
                 }
             }
-            if (!present) continue;
-            const int q = static_cast<int>(u % groups) * 32 + lane;
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int k0 = 0; k0 < n; k0 += 8) {
-                uint4 v[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int k = min(k0 + i, n - 1);
-                    const int row = __shfl_sync(0xffffffffu, row_of_lane, k);
-                    v[i] = (k0 + i < n && q < chunks) ? ptx::ld_nc_v4(y + static_cast<std::size_t>(row) * row_bytes + static_cast<std::size_t>(q) * 16)
-                                                     : make_uint4(0u, 0u, 0u, 0u);
-                }
+            for (int g = 0; g < kPushGroupsPerUnit; ++g) {
+                const int q = q0 + g * 32;
+                if (q < chunks) {
+                    uint4 packed;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float w = __shfl_sync(0xffffffffu, weight_of_lane, min(k0 + i, n - 1));
-                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = __bfloat1622float2(h[e]);
-                        acc[2 * e] = fmaf(w, f.x, acc[2 * e]);
-                        acc[2 * e + 1] = fmaf(w, f.y, acc[2 * e + 1]);
-                    }
+                    for (int x = 0; x < 4; ++x) h[x] = __floats2bfloat162_rn(acc[g][2 * x], acc[g][2 * x + 1]);
+                    ptx::st_v4(dst_row + static_cast<std::size_t>(q) * 16, packed);
                 }
             }
-            if (q < chunks) {
-                uint4 packed;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-                ptx::st_v4(dst_row + static_cast<std::size_t>(q) * 16, packed);
+            if (remote) {
+                // The row will be read by a bulk copy (asynchronous proxy) of a forwarder: every lane orders its ordinary
+                // stores against that proxy here, on the writing side -- a proxy fence on a forwarder's SM would wait
+                // behind that SM's stores to peers.  Then the warp joins and one lane counts the unit as finished.
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    __threadfence();
+                    atomicAdd(a.outbox_units + e.slot, 1ull);
+                }
             }
         }
         if (P == 1) {
             // tokens that were routed nowhere have no map entry: their result is zero
             const long long zero_units = static_cast<long long>(a.num_tokens) * groups;
-            for (long long u = zero_units * wid / total_warps; u < zero_units * (wid + 1) / total_warps; ++u) {
+            for (long long u = wid; u < zero_units; u += total_warps) {
                 const int t = static_cast<int>(u / groups);
                 const int q = static_cast<int>(u % groups) * 32 + lane;
                 if (a.plan_mask[t] == 0 && q < chunks)
@@ -297,16 +500,19 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 3) combine_push_kernel(co
     // every thread's stores, then the CTA joins, then one thread fences at system scope and counts the CTA
     __syncthreads();
     if (threadIdx.x == 0) {
+        atomicMax(&a.stat_scratch[forwarder ? 4 : 3], ptx::globaltimer_ns());
         ptx::fence_sys();
         const unsigned long long finished = atomicAdd(a.cta_done, 1ull) + 1ull;
         if (finished == gridDim.x) {
             *a.cta_done = 0ull;  // launches that share this counter are stream-ordered
             ptx::fence_sys();
+            const unsigned long long first_start = a.stat_scratch[2];
             a.stats[0] = static_cast<std::int64_t>(a.stat_scratch[0]);
             a.stats[1] = static_cast<std::int64_t>(a.stat_scratch[1]);
-            for (int i = 2; i < 8; ++i) a.stats[i] = 0;
-            a.stat_scratch[0] = 0ull;
-            a.stat_scratch[1] = 0ull;
+            a.stats[2] = static_cast<std::int64_t>(a.stat_scratch[3] - first_start);
+            a.stats[3] = a.stat_scratch[4] ? static_cast<std::int64_t>(a.stat_scratch[4] - first_start) : 0;
+            for (int i = 4; i < 8; ++i) a.stats[i] = 0;
+            for (int i = 0; i < 5; ++i) a.stat_scratch[i] = i == 2 ? ~0ull : 0ull;
             if (ptx::ld_volatile(&rc->sticky[0]) == 0) {
                 if (P > 1)
                     for (int p = 0; p < P; ++p) ptx::st_release_sys(flag_ptr(rc->seg[p], lay.csig_off, me), epoch);

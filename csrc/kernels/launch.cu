@@ -94,8 +94,21 @@ cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_
     return cooperative_launch(combine_kernel, launch, dim3(channels, launch.num_virtual, 1), kCombineWarps * 32, smem, stream);
 }
 
-cudaError_t launch_combine_push(const CombinePushArgs& args, int ctas, cudaStream_t stream) {
-    combine_push_kernel<<<ctas, kFusedReduceThreads, 0, stream>>>(args);
+cudaError_t launch_combine_push(const CombinePushArgs& args, int reduce_ctas, std::size_t smem, cudaStream_t stream) {
+    static std::mutex mutex;
+    static std::size_t configured[64] = {0};
+    {
+        std::lock_guard<std::mutex> guard(mutex);
+        int device = 0;
+        cudaError_t status = cudaGetDevice(&device);
+        if (status != cudaSuccess) return status;
+        if (device >= 0 && device < 64 && smem > configured[device]) {
+            status = cudaFuncSetAttribute(combine_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (status != cudaSuccess) return status;
+            configured[device] = smem;
+        }
+    }
+    combine_push_kernel<<<args.forward_ctas + reduce_ctas, kFusedReduceThreads, smem, stream>>>(args);
     return cudaGetLastError();
 }
 

@@ -28,7 +28,8 @@ cudaError_t launch_dispatch(const DispatchLaunch& launch, int ctas, int threads,
 cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_t crow_stride, cudaStream_t stream);
 
 // Ordinary launches of the combine paths: expert-side gather-reduce-push, owner-side sum.  Any grid size works.
-cudaError_t launch_combine_push(const CombinePushArgs& args, int ctas, cudaStream_t stream);
+// `reduce_ctas` reducer CTAs follow the args.forward_ctas forwarder CTAs in one grid.
+cudaError_t launch_combine_push(const CombinePushArgs& args, int reduce_ctas, std::size_t smem, cudaStream_t stream);
 cudaError_t launch_fused_reduce(const FusedReduceArgs& args, int ctas, cudaStream_t stream);
 // True when the library was built with the per-role instrumentation (-DBEP_ENABLE_PROFILING=1).
 bool role_profiling_enabled();

@@ -220,16 +220,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
        py::arg("swiglu"), py::arg("a_scales") = py::none(), py::arg("w_scales") = py::none(), py::arg("stream") = 0);
 
     m.def("litmus", [](std::int64_t mine, std::int64_t theirs, int role, int rounds, int words, at::Tensor& status,
-                       int timeout_ms, int device) {
+                       int timeout_ms, int device, int method) {
         if (!status.is_cuda() || status.scalar_type() != at::kLong || status.numel() < (role < 0 ? 8 : 4))
             throw std::invalid_argument("status must be a CUDA int64 tensor with 4 (8 for both roles) elements");
         c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
         const char* error = litmus_pingpong(reinterpret_cast<void*>(mine), reinterpret_cast<void*>(theirs), role, rounds, words,
                                             reinterpret_cast<long long*>(status.data_ptr<std::int64_t>()),
                                             static_cast<unsigned long long>(timeout_ms) * 1000000ull,
-                                            at::cuda::getCurrentCUDAStream(device).stream());
+                                            at::cuda::getCurrentCUDAStream(device).stream(), method);
         if (error != nullptr) throw std::runtime_error(std::string("litmus: ") + error);
-    });
+    }, py::arg("mine"), py::arg("theirs"), py::arg("role"), py::arg("rounds"), py::arg("words"), py::arg("status"),
+       py::arg("timeout_ms"), py::arg("device"), py::arg("method") = 0);
 
     m.def("role_profiling_enabled", &role_profiling_enabled);
     m.def("dispatch_group", &dispatch_group);

@@ -1,42 +1,36 @@
 """DeepEP-shaped expert-parallel buffer: ``dispatch`` and ``combine`` over peer HBM, host-staged
 memory or a CPU (gloo) group.
 
-The public surface -- constructor arguments, ``dispatch`` keywords, rejections, stream handling,
-result pools, ``cache_layout``, ``capture_dispatch``, ``check_errors``, collective ``close`` -- is that
-of the reference's ``HostStagedEPBuffer`` (``pcie_ep/buffers/ep.py:19-500``).  Differences:
+Parity: the reference's ``HostStagedEPBuffer`` (``pcie_ep/buffers/ep.py:19-500``) -- constructor
+arguments, ``dispatch`` keywords and rejections, stream handling, result pools, ``cache_layout``,
+``capture_dispatch``, ``check_errors``, collective ``close``.  Beyond it:
 
-* ``transport`` selects the substrate (``"peer"`` over NVLink by default on a GPU; ``"host_staged"``
-  is the reference's substrate; ``"cpu"`` runs without a GPU);
-* ``combine`` exists (the reference raises ``NotImplementedError``, ``ep.py:461-462``);
-* one fused kernel launch per dispatch instead of eight.
+* ``transport`` selects the substrate (``"peer"`` over NVLink by default on a GPU, ``"host_staged"``
+  over registered host memory, ``"cpu"`` without a GPU);
+* ``combine`` and ``fused_expert_combine`` exist;
+* a dispatch is one fused kernel launch.
 
 Nothing on the dispatch/combine path waits on the CPU or issues a collective.
 """
 
 from __future__ import annotations
 
+import itertools
 import threading
-from typing import Any, Dict, Optional
+from typing import Any, Optional
 
 import torch
 import torch.distributed as dist
 
 from ..config import HostStagedConfig
 from ..parallel import control
-from ..utils.event import EventOverlap, _record_tensors
+from ..utils.event import EventOverlap, hold_for_stream
+from . import arguments
 from .handle import HostStagedEPHandle
+from .streams import StreamPolicy
 
-_next_buffer_id = [0]
-
-
-class _NullStream:
-    """Stands in for a CUDA stream on the CPU transport: every operation is already ordered."""
-
-    def wait_stream(self, other: Any) -> None:
-        pass
-
-    def wait_event(self, event: Any) -> None:
-        pass
+_TRANSPORT_NAMES = ("peer", "host_staged", "cpu", "auto")
+_buffer_serial = itertools.count(1)
 
 
 class HostStagedEPBuffer:
@@ -44,7 +38,7 @@ class HostStagedEPBuffer:
 
     Construction and ``close`` are collective over ``group`` and may block the CPU; ``dispatch`` and
     ``combine`` only enqueue device work.  CPU-side calls on one buffer must be serialised by the
-    caller (a lock protects the internal bookkeeping, not the ordering of your launches).
+    caller (the internal lock protects bookkeeping, not the order of your launches).
     """
 
     def __init__(
@@ -64,196 +58,132 @@ class HostStagedEPBuffer:
         explicitly_destroy: bool = False,
     ) -> None:
         if not dist.is_initialized():
-            raise RuntimeError("Initialize torch.distributed before constructing a buffer")
+            raise RuntimeError("Initialize torch.distributed (init_process_group) before building an EP buffer")
         if config is not None and host_staged_config is not None:
-            raise ValueError("Supply config or host_staged_config, not both")
+            raise ValueError("config and host_staged_config name the same thing: pass one of them, not both")
         self.config = config or host_staged_config or HostStagedConfig()
-        if transport is not None and transport not in ("peer", "host_staged", "cpu", "auto"):
-            raise ValueError("transport must be 'peer', 'host_staged', 'cpu' or 'auto'")
-        chosen = transport if transport not in (None, "auto") else self.config.resolved_transport(torch.cuda.is_available())
-        if chosen != "cpu" and not torch.cuda.is_available():
-            raise RuntimeError(f"transport {chosen!r} requires NVIDIA CUDA")
+        if transport is not None and transport not in _TRANSPORT_NAMES:
+            raise ValueError(f"unknown transport {transport!r}; choose from {_TRANSPORT_NAMES}")
+        have_cuda = torch.cuda.is_available()
+        chosen = self.config.resolved_transport(have_cuda) if transport in (None, "auto") else transport
+        if chosen != "cpu" and not have_cuda:
+            raise RuntimeError(f"transport {chosen!r} requires NVIDIA CUDA, which this process does not have")
+        dims = dict(num_max_tokens_per_rank=num_max_tokens_per_rank, hidden=hidden, num_topk=num_topk, num_experts=num_experts)
+        for name, value in dims.items():
+            if isinstance(value, bool) or not isinstance(value, int) or value < 1:
+                raise ValueError(f"{name} must be a positive integer, got {value!r}")
         self.transport = chosen
-        for name, value in (
-            ("num_max_tokens_per_rank", num_max_tokens_per_rank),
-            ("hidden", hidden),
-            ("num_topk", num_topk),
-            ("num_experts", num_experts),
-        ):
-            if not isinstance(value, int) or value < 1:
-                raise ValueError(f"{name} must be a positive integer")
-        self.group = group if group is not None else dist.group.WORLD
-        self.rank_idx = dist.get_rank(self.group)
-        self.num_ranks = dist.get_world_size(self.group)
-        if self.rank_idx < 0:
-            raise ValueError("This process is not a member of the supplied EP group")
-        self.global_ranks = tuple(dist.get_process_group_ranks(self.group))
-        if num_experts % self.num_ranks:
-            raise ValueError("Experts must be uniformly divisible among EP ranks")
-        self.num_max_tokens_per_rank = num_max_tokens_per_rank
-        self.hidden, self.num_topk, self.num_experts = hidden, num_topk, num_experts
-        self.deterministic = deterministic
-        self.explicitly_destroy = explicitly_destroy
         self.on_gpu = chosen != "cpu"
+        self.group = dist.group.WORLD if group is None else group
+        self.rank_idx = dist.get_rank(self.group)
+        if self.rank_idx < 0:
+            raise ValueError("the calling process is not part of the EP group it passed")
+        self.num_ranks = dist.get_world_size(self.group)
+        self.global_ranks = tuple(dist.get_process_group_ranks(self.group))
+        if num_experts % self.num_ranks != 0:
+            raise ValueError(f"{num_experts} experts cannot be split evenly over {self.num_ranks} ranks")
+        self.num_max_tokens_per_rank, self.hidden = num_max_tokens_per_rank, hidden
+        self.num_topk, self.num_experts = num_topk, num_experts
+        self.deterministic, self.explicitly_destroy = deterministic, explicitly_destroy
         self.device = torch.cuda.current_device() if self.on_gpu else "cpu"
-        self._comm_stream = torch.cuda.Stream(device=self.device) if self.on_gpu else _NullStream()
-        self._last_event = None
-        self._last_handle: Optional[HostStagedEPHandle] = None
-        self._generation = 0
-        self._failed = False
-        self._closed = False
+        self.buffer_id = f"{self.rank_idx}-{next(_buffer_serial)}"
+
+        self._streams = StreamPolicy(self.device, self.on_gpu)
         self._lock = threading.RLock()
-        self._consumer_streams: Dict[tuple, Any] = {}
-        self._graph_capture = None
-        self._comm_busy = False  # work was queued on the communication stream that the compute stream has not waited for
-        self._owns_control_group = False
-        self.runtime = None
-        self.segments = None
-        self.relay = None
-        self.directory = None
-        self.nccl_comm = None
-        self.comm_reused = False
-        self.comm_reuse_status = "not_an_nccl_group"
-        _next_buffer_id[0] += 1
-        self.buffer_id = f"{self.rank_idx}-{_next_buffer_id[0]}"
+        self._generation = 0
+        self._failed = self._closed = False
+        self._last_event: Any = None
+        self._last_handle: Optional[HostStagedEPHandle] = None
+        self._graph_capture: Any = None
+        self._extension: Any = None
+        self.runtime = self.segments = self.relay = self.directory = None
 
         borrowed = control.borrow_nccl_comm(self.group, self.device, require_reuse=require_reuse_nccl_comm)
         self.nccl_comm, self.comm_reused, self.comm_reuse_status = borrowed.nccl_comm, borrowed.reused, borrowed.status
-
-        self.control_group, self._owns_control_group = control.get_control_group(
-            self.group, self.global_ranks, control_group
-        )
-        control.validate_group_configuration(
-            self.control_group, self.num_ranks, num_max_tokens_per_rank, hidden, num_topk, num_experts,
-            self.config, chosen,
-        )
-        options = self.config.native_options()
-        if chosen == "cpu":
+        self.control_group, self._owns_control_group = control.get_control_group(self.group, self.global_ranks, control_group)
+        control.validate_group_configuration(self.control_group, self.num_ranks, num_max_tokens_per_rank, hidden, num_topk,
+                                             num_experts, self.config, chosen)
+        if self.on_gpu:
+            self._build_gpu_runtime()
+        else:
             from ..parallel.cpu_backend import CpuRuntime
 
-            self.runtime = CpuRuntime(
-                self.rank_idx, self.num_ranks, num_max_tokens_per_rank, hidden, num_topk, num_experts, options,
-                self.control_group,
-            )
-            return
+            self.runtime = CpuRuntime(self.rank_idx, self.num_ranks, num_max_tokens_per_rank, hidden, num_topk, num_experts,
+                                      self.config.native_options(), self.control_group)
 
-        # The extension is loaded (and built, if need be) only when a GPU buffer is constructed.
-        from .. import _C
+    def _build_gpu_runtime(self) -> None:
+        """Segments, native runtime and (optionally) relay threads; every step ends in a collective agreement."""
+        from .. import _C  # loaded (and built, if need be) only when a GPU buffer is constructed
         from ..parallel.peer_memory import open_segments
 
         self._extension = _C
-        layout = _C.segment_layout(
-            self.num_ranks, self.config.channels, num_experts, num_topk, hidden, num_max_tokens_per_rank,
-            self.config.payload_slots, self.config.enable_combine, self.config.fused_expert_combine,
-        )
-        self.segments = open_segments(
-            _C, chosen, self.rank_idx, self.num_ranks, int(layout["size_bytes"]), self.device, self.control_group,
-            self.config.directory, relay=self.config.numa_mode == "relay",
-        )
+        cfg = self.config
+        layout = _C.segment_layout(self.num_ranks, cfg.channels, self.num_experts, self.num_topk, self.hidden,
+                                   self.num_max_tokens_per_rank, cfg.payload_slots, cfg.enable_combine, cfg.fused_expert_combine)
+        self.segments = open_segments(_C, self.transport, self.rank_idx, self.num_ranks, int(layout["size_bytes"]), self.device,
+                                      self.control_group, cfg.directory, relay=cfg.numa_mode == "relay")
         self.directory = self.segments.directory
 
+        options = cfg.native_options()
+        options["segment_kind"] = self.transport  # where the segments live decides how flags are ordered after bulk copies
+
         def make_runtime() -> Any:
-            runtime = _C.Runtime(
-                self.rank_idx, self.num_ranks, num_max_tokens_per_rank, hidden, num_topk, num_experts, options,
-                self.segments.pointers, self.device,
-            )
-            # the dispatch stream must see fully initialised state without a CPU wait later on
-            self._comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+            runtime = _C.Runtime(self.rank_idx, self.num_ranks, self.num_max_tokens_per_rank, self.hidden, self.num_topk,
+                                 self.num_experts, options, self.segments.pointers, self.device)
+            # later launches on the communication stream must see fully initialised state without a CPU wait
+            self._streams.comm.wait_stream(torch.cuda.current_stream(self.device))
             return runtime
 
         self.runtime = control.run_agreed(make_runtime, self.control_group, "runtime construction", self.rank_idx)
+        if cfg.numa_mode != "relay":
+            return
 
-        if self.config.numa_mode == "relay":
-            def make_relay() -> Any:
-                relay_options = {
-                    "num_ranks": self.num_ranks, "channels": self.config.channels, "num_experts": num_experts,
-                    "num_topk": num_topk, "hidden": hidden, "num_max_tokens": num_max_tokens_per_rank,
-                    "payload_slots": self.config.payload_slots, "enable_combine": self.config.enable_combine,
-                    "workers": self.config.relay_workers_per_numa, "cpu_affinity": list(self.config.relay_cpu_affinity),
-                }
-                relay = _C.NumaRelay(relay_options, self.segments.outbox_host_pointers, self.segments.host_pointers,
-                                     self.rank_idx)
-                relay.start()
-                return relay
+        def make_relay() -> Any:
+            options = dict(num_ranks=self.num_ranks, channels=cfg.channels, num_experts=self.num_experts,
+                           num_topk=self.num_topk, hidden=self.hidden, num_max_tokens=self.num_max_tokens_per_rank,
+                           payload_slots=cfg.payload_slots, enable_combine=cfg.enable_combine,
+                           workers=cfg.relay_workers_per_numa, cpu_affinity=list(cfg.relay_cpu_affinity))
+            relay = _C.NumaRelay(options, self.segments.outbox_host_pointers, self.segments.host_pointers, self.rank_idx)
+            relay.start()
+            return relay
 
-            self.relay = control.run_agreed(make_relay, self.control_group, "relay start", self.rank_idx)
+        self.relay = control.run_agreed(make_relay, self.control_group, "relay start", self.rank_idx)
 
     # ------------------------------------------------------------------ streams
     def get_comm_stream(self) -> Any:
-        return self._comm_stream
+        return self._streams.comm
 
-    @staticmethod
-    def _stream_key(stream: Any) -> tuple:
-        return (stream.device.index, int(stream.cuda_stream))
+    @property
+    def _comm_stream(self) -> Any:
+        return self._streams.comm
+
+    @property
+    def _consumer_streams(self) -> dict:
+        return self._streams.consumers
 
     def _register_consumer_stream(self, stream: Any) -> None:
-        """Remember a stream that reads results, even after the Python tensors are gone."""
-        if not self.on_gpu:
-            return
         with self._lock:
-            key = self._stream_key(stream)
-            if key != self._stream_key(self._comm_stream):
-                self._consumer_streams[key] = stream
-
-    def _wait_consumer_streams(self, compute: Any, compute_already_waited: bool) -> None:
-        """Result pools are overwritten in place: order that after every registered reader's tail.
-
-        Device-side waits only (reference: ``ep.py:204-220``).
-        """
-        if not self.on_gpu:
-            return
-        skip = {self._stream_key(self._comm_stream)}
-        if compute_already_waited:
-            skip.add(self._stream_key(compute))
-        for key, stream in self._consumer_streams.items():
-            if key not in skip:
-                self._comm_stream.wait_stream(stream)
-                skip.add(key)
+            self._streams.add_consumer(stream)
 
     @staticmethod
     def capture() -> EventOverlap:
-        """Record a producer dependency on the current CUDA stream."""
+        """Record a producer dependency on the current CUDA stream (pass it as ``previous_event``)."""
+        marker = torch.cuda.Event()
+        marker.record(torch.cuda.current_stream())
+        return EventOverlap(marker)
+
+    def _enqueue(self, launch: Any, inputs: Any, previous_event: Any, run_async: bool) -> Any:
+        """Run ``launch(stream_handle)`` on the stream the policy picks; returns (value, event, stream)."""
+        compute = self._streams.current()
+        stream = self._streams.begin(compute, previous_event, run_async)
+        if stream is not compute:
+            hold_for_stream(inputs, stream)
+        value = launch(stream)
         event = torch.cuda.Event()
-        event.record(torch.cuda.current_stream())
-        return EventOverlap(event)
-
-    def _current_stream(self) -> Any:
-        return torch.cuda.current_stream(self.device) if self.on_gpu else _NullStream()
-
-    def _launch_stream(self, compute: Any, previous_event: Any, async_with_compute_stream: bool) -> Any:
-        """Pick the stream a launch goes to and set up its dependencies (device-side waits only).
-
-        A synchronous call without a producer event is "communication stream waits for the compute
-        stream, compute stream waits for the result": that is ordinary in-order execution, so the kernel
-        is put on the compute stream itself and both cross-stream hand-offs (tens of microseconds of
-        device latency per call) disappear.  Everything else goes to the communication stream.
-        """
-        if async_with_compute_stream or previous_event is not None:
-            self._wait_for_inputs(compute, previous_event)
-            self._comm_busy = True
-            return self._comm_stream
-        if self._comm_busy:
-            compute.wait_stream(self._comm_stream)
-            self._comm_busy = False
-        skip = {self._stream_key(self._comm_stream), self._stream_key(compute)}
-        for key, stream in self._consumer_streams.items():
-            if key not in skip:
-                compute.wait_stream(stream)
-        return compute
-
-    def _wait_for_inputs(self, compute: Any, previous_event: Any) -> None:
-        if previous_event is None:
-            self._comm_stream.wait_stream(compute)
-        elif hasattr(previous_event, "current_stream_wait"):
-            # an EventOverlap (or look-alike): the *communication* stream is the one that must wait
-            if getattr(previous_event, "event", None) is not None:
-                self._comm_stream.wait_event(previous_event.event)
-            else:
-                with torch.cuda.stream(self._comm_stream):
-                    previous_event.current_stream_wait()
-        else:
-            self._comm_stream.wait_event(previous_event)
-        self._wait_consumer_streams(compute, compute_already_waited=previous_event is None)
+        event.record(stream)
+        self._last_event = event
+        self._streams.finish(compute, stream, event, run_async)
+        return value, event
 
     # ------------------------------------------------------------------ dispatch
     def dispatch(
@@ -284,103 +214,63 @@ class HostStagedEPBuffer:
         (-1 = unused slot), ``topk_weights`` optional FP32 ``[T, K]``.  Returns
         ``(recv_x, recv_topk_idx, recv_topk_weights, handle, event)`` or, with ``defer_epilogue``, only
         the event whose first ``wait()`` returns the first four.  Shapes are capacities; the valid
-        ranges are the device-side counts/offsets on the handle.  See the reference for the argument
-        contract this follows (``pcie_ep/buffers/ep.py:229-360``).
+        ranges are the device-side counts and offsets on the handle.
         """
         with self._lock:
             self._check_live()
-            if do_cpu_sync:
-                raise NotImplementedError("The main path supports do_cpu_sync=False only")
-            cached_layout = None
-            if handle is not None:
-                if topk_idx is not None:
-                    raise ValueError("topk_idx must be None when a cached handle is supplied")
-                topk_idx = handle.topk_idx
-            if do_handle_copy or num_qps or num_sms or use_tma_aligned_col_major_sf:
-                raise NotImplementedError("Handle copy, QPs, SM overrides and FP8 scale layouts are unsupported")
-            if previous_event is not None and not allocate_on_comm_stream:
-                raise ValueError("previous_event requires allocate_on_comm_stream=True")
+            arguments.reject_unsupported(dict(do_cpu_sync=do_cpu_sync, do_handle_copy=do_handle_copy, num_qps=num_qps,
+                                              num_sms=num_sms, use_tma_aligned_col_major_sf=use_tma_aligned_col_major_sf))
+            self._check_stream_options(previous_event, allocate_on_comm_stream)
             if defer_epilogue and not async_with_compute_stream:
-                raise ValueError("defer_epilogue requires async_with_compute_stream=True")
-            if do_zero_padding and not do_expand:
-                raise ValueError("do_zero_padding is valid only with do_expand=True")
-            alignment = (
-                (handle.expert_alignment if handle is not None else 1) if expert_alignment is None else expert_alignment
-            )
-            if not isinstance(alignment, int) or isinstance(alignment, bool) or alignment < 1:
-                raise ValueError("expert_alignment must be a positive integer")
-            if num_experts not in (None, self.num_experts):
-                raise ValueError("num_experts differs from the prepared buffer")
-            if num_max_tokens_per_rank not in (None, self.num_max_tokens_per_rank):
-                raise ValueError("num_max_tokens_per_rank differs from the prepared buffer")
-            payload_dtype = torch.bfloat16 if self.on_gpu else None
-            self._validate_input(x, "x", payload_dtype, (None, self.hidden))
-            self._validate_input(topk_idx, "topk_idx", torch.int64, (x.shape[0], self.num_topk))
-            if x.shape[0] > self.num_max_tokens_per_rank:
-                raise ValueError("Input token count exceeds the prepared capacity")
-            if topk_weights is not None:
-                self._validate_input(topk_weights, "topk_weights", torch.float32, topk_idx.shape)
-            if cumulative_local_expert_recv_stats is not None:
-                self._validate_input(
-                    cumulative_local_expert_recv_stats, "cumulative_local_expert_recv_stats", torch.int32,
-                    (self.num_experts // self.num_ranks,),
-                )
-            if handle is not None:
-                cached_layout = handle.validate_cached(self, x, alignment, do_expand)
+                raise ValueError("defer_epilogue hands the outputs over at the first wait(), which needs async_with_compute_stream=True")
+            request = arguments.build_dispatch_request(
+                self, x, topk_idx, topk_weights, handle=handle, expert_alignment=expert_alignment, do_expand=do_expand,
+                do_zero_padding=do_zero_padding, cumulative=cumulative_local_expert_recv_stats, num_experts=num_experts,
+                num_max_tokens_per_rank=num_max_tokens_per_rank)
             if self.on_gpu and torch.cuda.is_current_stream_capturing():
-                raise NotImplementedError("Use capture_dispatch for explicit CUDA Graph preparation")
-            compute = self._current_stream()
-            result, event = self._dispatch_on_comm_stream(
-                x, topk_idx, topk_weights, cumulative_local_expert_recv_stats, alignment, do_expand,
-                do_zero_padding, compute, previous_event, cached_layout, async_with_compute_stream,
-            )
-            refs = (self, x, topk_idx, topk_weights, result, cumulative_local_expert_recv_stats)
-            if handle is not None:
-                refs = (*refs, handle)
-            overlap = EventOverlap(event, refs, self._register_consumer_stream)
-            output_handle = HostStagedEPHandle(self, topk_idx, result, do_expand, alignment, overlap)
-            self._last_event, self._last_handle = event, output_handle
-            outputs = (
-                result["recv_x"],
-                result.get("recv_topk_idx"),
-                result.get("recv_topk_weights") if topk_weights is not None else None,
-                output_handle,
-            )
-            if not async_with_compute_stream and self.on_gpu:
-                # result tensors live in pools owned by the runtime, not by the caching allocator:
-                # nothing to record, but the reader stream must be known before the pool is reused
-                if previous_event is not None:
-                    compute.wait_event(event)
-                    self._comm_busy = False
-                self._register_consumer_stream(compute)
+                raise NotImplementedError("dispatch cannot run inside a stream capture; capture_dispatch prepares a CUDA graph")
+            result, event = self._launch_dispatch(request, previous_event, async_with_compute_stream)
+            overlap = EventOverlap(event, request.keepalive(self, result), self._register_consumer_stream)
+            out_handle = HostStagedEPHandle(self, request.topk_idx, result, request.expand, request.alignment, overlap)
+            self._last_handle = out_handle
+            outputs = (result["recv_x"], result.get("recv_topk_idx"),
+                       result.get("recv_topk_weights") if request.topk_weights is not None else None, out_handle)
             if defer_epilogue:
                 overlap.register_hook_after_wait(lambda: outputs)
                 return overlap
             return (*outputs, overlap)
 
-    def _dispatch_on_comm_stream(
-        self, x, topk_idx, topk_weights, cumulative, alignment, do_expand, do_zero_padding, compute,
-        previous_event, cached_layout=None, async_with_compute_stream=True,
-    ):
+    def _launch_dispatch(self, request: arguments.DispatchRequest, previous_event: Any, run_async: bool) -> Any:
         """Order dependencies, launch, record completion; never waits on the CPU."""
+        r = request
         if not self.on_gpu:
-            result = self.runtime.dispatch(x, topk_idx, topk_weights, alignment, do_expand, do_zero_padding,
-                                           cached_layout, False)
-            if cumulative is not None:
-                cumulative.add_(result["expert_counts"])
+            result = self.runtime.dispatch(r.x, r.topk_idx, r.topk_weights, r.alignment, r.expand, r.zero_padding,
+                                           r.cached_layout, False)
+            if r.cumulative is not None:
+                r.cumulative.add_(result["expert_counts"])
             return result, None
-        comm = self._launch_stream(compute, previous_event, async_with_compute_stream)
-        if comm is not compute:
-            _record_tensors((x, topk_idx, topk_weights), comm)
-        result = self.runtime.dispatch(x, topk_idx, topk_weights, alignment, do_expand, do_zero_padding,
-                                       cached_layout, False, comm.cuda_stream)
-        if cumulative is not None:
-            with torch.cuda.stream(comm):
-                cumulative.add_(result["expert_counts"])
-                cumulative.record_stream(comm)
-        event = torch.cuda.Event()
-        event.record(comm)
-        return result, event
+
+        def launch(stream: Any) -> Any:
+            result = self.runtime.dispatch(r.x, r.topk_idx, r.topk_weights, r.alignment, r.expand, r.zero_padding,
+                                           r.cached_layout, False, stream.cuda_stream)
+            if r.cumulative is not None:
+                with torch.cuda.stream(stream):
+                    r.cumulative.add_(result["expert_counts"])
+                    r.cumulative.record_stream(stream)
+            return result
+
+        return self._enqueue(launch, (r.x, r.topk_idx, r.topk_weights), previous_event, run_async)
+
+    @staticmethod
+    def _check_stream_options(previous_event: Any, allocate_on_comm_stream: bool) -> None:
+        if previous_event is not None and not allocate_on_comm_stream:
+            raise ValueError("previous_event moves the launch to the communication stream: pass allocate_on_comm_stream=True with it")
+
+    def _check_handle(self, handle: Any, purpose: str) -> None:
+        if not isinstance(handle, HostStagedEPHandle):
+            raise TypeError(f"{purpose} takes the handle that dispatch returned, not {type(handle).__name__}")
+        if (handle.buffer_id, handle.generation) != (self.buffer_id, self._generation):
+            raise ValueError(f"{purpose}: the handle comes from another buffer, or from before this buffer was rebuilt")
 
     # ------------------------------------------------------------------ combine
     def combine(
@@ -394,6 +284,7 @@ class HostStagedEPBuffer:
         previous_event: Any = None,
         async_with_compute_stream: bool = False,
         allocate_on_comm_stream: bool = False,
+        num_sms: int = 0,
     ) -> Any:
         """Return the expert outputs to their source tokens: the inverse of ``dispatch``.
 
@@ -402,45 +293,33 @@ class HostStagedEPBuffer:
         expanded layout each rank first reduces the rows of one source token with the weights that
         travelled with the dispatch (``weighted=False`` sums them unweighted), sends one BF16 row per
         (token, rank) back and the source adds the rows of all ranks in rank order in FP32.
-        Returns ``(combined_x [T, hidden], None, event)``.
+        ``num_sms`` > 0 limits the two combine launches to that many SMs' worth of CTAs, so that an
+        expert GEMM on another stream keeps the rest.  Returns ``(combined_x [T, hidden], None, event)``.
         """
         with self._lock:
             self._check_live()
             if topk_weights is not None:
-                raise NotImplementedError("combine applies the weights given to dispatch; pass weighted=False to skip them")
-            if not isinstance(handle, HostStagedEPHandle):
-                raise TypeError("combine needs the handle returned by dispatch")
-            if handle.buffer_id != self.buffer_id or handle.generation != self._generation:
-                raise ValueError("The handle belongs to another buffer generation")
-            if previous_event is not None and not allocate_on_comm_stream:
-                raise ValueError("previous_event requires allocate_on_comm_stream=True")
-            if weighted is None:
-                weighted = handle.do_expand
+                raise NotImplementedError("combine applies the weights that travelled with the dispatch; use weighted=False for a plain sum")
+            self._check_handle(handle, "combine")
+            self._check_stream_options(previous_event, allocate_on_comm_stream)
+            if isinstance(num_sms, bool) or not isinstance(num_sms, int) or num_sms < 0:
+                raise ValueError("num_sms must be a non-negative integer")
+            use_weights = handle.do_expand if weighted is None else bool(weighted)
+            arguments.TensorRule("x", torch.bfloat16 if self.on_gpu else None, (None, self.hidden)).check(
+                x, device=self.device, on_gpu=self.on_gpu)
             capacity = handle._result["recv_x"].shape[0]
-            self._validate_input(x, "x", torch.bfloat16 if self.on_gpu else None, (None, self.hidden))
             if x.shape[0] > capacity:
-                raise ValueError("combine input has more rows than the dispatch capacity")
+                raise ValueError(f"x has {x.shape[0]} rows, the dispatch result holds at most {capacity}")
             if not self.on_gpu:
-                combined = self.runtime.combine(x, handle._result, weighted, out)
+                combined = self.runtime.combine(x, handle._result, use_weights, out)
                 return combined, None, EventOverlap(None, (self, x, handle, combined))
             if torch.cuda.is_current_stream_capturing():
-                raise NotImplementedError("combine cannot be issued inside a stream capture")
-            compute = self._current_stream()
-            comm = self._launch_stream(compute, previous_event, async_with_compute_stream)
-            if comm is not compute:
-                _record_tensors((x, out), comm)
+                raise NotImplementedError("combine cannot run inside a stream capture")
             # without `out` the result is a preallocated pool tensor (busy while referenced)
-            combined = self.runtime.combine(x, handle._result, weighted, out, comm.cuda_stream)
-            event = torch.cuda.Event()
-            event.record(comm)
-            self._last_event = event
-            overlap = EventOverlap(event, (self, x, handle, combined), self._register_consumer_stream)
-            if not async_with_compute_stream:
-                if previous_event is not None:
-                    compute.wait_event(event)
-                    self._comm_busy = False
-                self._register_consumer_stream(compute)
-            return combined, None, overlap
+            combined, event = self._enqueue(
+                lambda stream: self.runtime.combine(x, handle._result, use_weights, out, stream.cuda_stream, num_sms),
+                (x, out), previous_event, async_with_compute_stream)
+            return combined, None, EventOverlap(event, (self, x, handle, combined), self._register_consumer_stream)
 
     def fused_expert_combine(self, hidden_rows: torch.Tensor, w_down: torch.Tensor, handle: HostStagedEPHandle,
                              *, out: Optional[torch.Tensor] = None) -> Any:
@@ -457,12 +336,9 @@ class HostStagedEPBuffer:
             self._check_live()
             if not self.config.fused_expert_combine:
                 raise RuntimeError("this buffer was built with fused_expert_combine=False")
-            if not isinstance(handle, HostStagedEPHandle):
-                raise TypeError("fused_expert_combine needs the handle returned by dispatch")
-            if handle.buffer_id != self.buffer_id or handle.generation != self._generation:
-                raise ValueError("The handle belongs to another buffer generation")
+            self._check_handle(handle, "fused_expert_combine")
             if not handle.do_expand:
-                raise ValueError("fused_expert_combine needs a dispatch with do_expand=True")
+                raise ValueError("fused_expert_combine works on the expanded layout: dispatch with do_expand=True")
             if not self.on_gpu:
                 # CPU transport: the same result in two steps (matmul per expert, then the gloo combine)
                 from ..ops.grouped_ffn import grouped_gemm
@@ -471,17 +347,13 @@ class HostStagedEPBuffer:
                 combined = self.runtime.combine(rows, handle._result, True, out)
                 return combined, None, EventOverlap(None, (self, hidden_rows, handle, combined))
             if torch.cuda.is_current_stream_capturing():
-                raise NotImplementedError("fused_expert_combine cannot be issued inside a stream capture")
-            compute = self._current_stream()
-            comm = self._launch_stream(compute, None, False)
-            if comm is not compute:
-                _record_tensors((hidden_rows, w_down, out), comm)
-            self.runtime.fused_scatter_gemm(hidden_rows, w_down, handle._result, comm.cuda_stream)
-            combined = self.runtime.fused_reduce(handle._result, out, comm.cuda_stream)
-            event = torch.cuda.Event()
-            event.record(comm)
-            self._last_event = event
-            self._register_consumer_stream(compute)
+                raise NotImplementedError("fused_expert_combine cannot run inside a stream capture")
+
+            def launch(stream: Any) -> Any:
+                self.runtime.fused_scatter_gemm(hidden_rows, w_down, handle._result, stream.cuda_stream)
+                return self.runtime.fused_reduce(handle._result, out, stream.cuda_stream)
+
+            combined, event = self._enqueue(launch, (hidden_rows, w_down, out), None, False)
             return combined, None, EventOverlap(event, (self, hidden_rows, w_down, handle, combined), self._register_consumer_stream)
 
     # ------------------------------------------------------------------ cache / graph
@@ -494,75 +366,49 @@ class HostStagedEPBuffer:
     def cache_layout(self, handle: HostStagedEPHandle) -> Any:
         """Detach the routing plan of ``handle`` without keeping its result pool busy."""
         self._check_live()
-        if handle.buffer_id != self.buffer_id or handle.generation != self._generation:
-            raise ValueError("The handle belongs to another buffer generation")
+        self._check_handle(handle, "cache_layout")
         return handle.cache_layout()
 
-    # ------------------------------------------------------------------ validation / errors
-    def _validate_input(self, tensor: Any, name: str, dtype: Any, shape: Any) -> None:
-        if not isinstance(tensor, torch.Tensor):
-            raise TypeError(f"{name} must be a torch Tensor")
-        if self.on_gpu:
-            if not tensor.is_cuda or tensor.device.index != self.device:
-                raise ValueError(f"{name} must be on this buffer's CUDA device")
-        elif tensor.is_cuda:
-            raise ValueError(f"{name} must be a CPU tensor for the cpu transport")
-        if dtype is None:
-            if not tensor.is_floating_point():
-                raise ValueError(f"{name} must be a floating-point tensor")
-        elif tensor.dtype != dtype:
-            raise ValueError(f"{name} must be contiguous with dtype {dtype}")
-        if not tensor.is_contiguous():
-            raise ValueError(f"{name} must be contiguous with dtype {dtype}")
-        if tensor.ndim != len(shape) or any(
-            expected is not None and actual != expected for actual, expected in zip(tensor.shape, shape)
-        ):
-            raise ValueError(f"{name} has shape {tuple(tensor.shape)}, expected {tuple(shape)}")
-
+    # ------------------------------------------------------------------ state / errors
     def _check_live(self) -> None:
         if self._closed or self.runtime is None:
-            raise RuntimeError("This buffer is closed")
+            raise RuntimeError("this EP buffer is closed")
         if self._failed:
-            raise RuntimeError("This buffer has failed; do not dispatch again")
+            raise RuntimeError("this EP buffer has failed (see check_errors); close it and build a new one")
         if self.on_gpu and torch.cuda.current_device() != self.device:
-            raise RuntimeError("The current CUDA device differs from the buffer's device")
+            raise RuntimeError(f"the buffer lives on cuda:{self.device}, the current device is cuda:{torch.cuda.current_device()}")
 
     def check_errors(self, handle: Optional[HostStagedEPHandle] = None) -> None:
-        """Explicit diagnostic: waits for the dispatch and reads its error words back."""
-        selected = handle or self._last_handle
-        if selected is None:
+        """Explicit diagnostic: waits for the dispatch (and a combine issued after it) and raises on a device error."""
+        target = handle if handle is not None else self._last_handle
+        if target is None:
             return
-        if selected.buffer_id != self.buffer_id or selected.generation != self._generation:
-            raise ValueError("The handle belongs to a different buffer generation")
-        if selected._completion_event is not None:
-            selected._completion_event.synchronize()
-        codes = selected.error.detach().cpu().reshape(-1).tolist()
-        combine_error = selected._result.get("combine_error")
-        if combine_error is not None:
+        if (target.buffer_id, target.generation) != (self.buffer_id, self._generation):
+            raise ValueError("check_errors: the handle comes from another buffer, or from before this buffer was rebuilt")
+        if target._completion_event is not None:
+            target._completion_event.synchronize()
+        words = target.error.detach().cpu().reshape(-1).tolist()
+        combine_words = target._result.get("combine_error")
+        if combine_words is not None and not any(words):
             if self.on_gpu:
                 torch.cuda.current_stream(self.device).synchronize()
-                self._comm_stream.synchronize()
-            codes_combine = combine_error.detach().cpu().reshape(-1).tolist()
-            if any(codes_combine) and not any(codes):
-                codes = codes_combine
-        if any(codes):
+                self._streams.comm.synchronize()
+            words = combine_words.detach().cpu().reshape(-1).tolist()
+        if any(words):
             self._failed = True
-            raise RuntimeError(f"EP dispatch GPU error on rank {self.rank_idx}: {codes}")
+            raise RuntimeError(f"EP dispatch GPU error on rank {self.rank_idx}: {words}")
 
     # ------------------------------------------------------------------ close
     def close(self) -> None:
-        """Collectively drain, release peer mappings, then free the segments."""
+        """Collective: drain the streams, stop the relay, release peer mappings, free the segments."""
         with self._lock:
             if self._closed:
                 return
             if self._graph_capture is not None:
                 self._graph_capture.close()
                 self._graph_capture = None
-            if self.on_gpu:
-                if self._last_event is not None:
-                    self._last_event.synchronize()
-                self._comm_stream.synchronize()
-            dist.barrier(group=self.control_group)
+            self._streams.drain(self._last_event)
+            dist.barrier(group=self.control_group)  # no rank unmaps while a peer's kernel may still write here
             if self.relay is not None:
                 self.relay.stop()
                 self.relay = None
@@ -576,7 +422,7 @@ class HostStagedEPBuffer:
             self._closed = True
             self._generation += 1
             self._last_handle = None
-            self._consumer_streams.clear()
+            self._streams.consumers.clear()
             if self._owns_control_group:
                 dist.destroy_process_group(self.control_group)
 

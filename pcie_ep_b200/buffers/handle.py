@@ -1,8 +1,8 @@
-"""Result handle of one dispatch and the detachable routing cache.
+"""What a dispatch leaves behind: the handle of one result and the detachable routing cache.
 
-Field names (including the DeepEP aliases) follow the reference's handle
-(``pcie_ep/buffers/handle.py:55-111``).  All counts live on the device and are never read back by
-the library; ``check_errors`` is the one explicit synchronising call.
+Parity: the reference's ``pcie_ep/buffers/handle.py:15-174`` (same attribute names, including the
+DeepEP aliases, and the same set of cached-layout rejections).  Every count lives on the device and is
+never read back by the library; ``check_errors`` is the one explicit synchronising call.
 """
 
 from __future__ import annotations
@@ -17,113 +17,137 @@ if TYPE_CHECKING:  # pragma: no cover
     from .ep import HostStagedEPBuffer
 
 
-def _tensor_signature(tensor: torch.Tensor) -> tuple:
+def _fingerprint(tensor: torch.Tensor) -> tuple:
+    """Everything that makes a tensor 'the same memory seen the same way' (not its contents)."""
     return (id(tensor), tensor.data_ptr(), tuple(tensor.shape), tuple(tensor.stride()), tensor.dtype, tensor.device)
 
 
-class _RouteGuard:
-    """Shared by the handle and the cached layout: the routing tensor must not change under them."""
+class RouteBinding:
+    """The routing tensor a plan was computed from, with the means to notice that it changed.
 
-    _topk_idx: torch.Tensor
-    _topk_version: Optional[int]
-    _route_signature: tuple
+    PyTorch bumps a tensor's version counter on every in-place write; inference tensors have none,
+    which is why they can be dispatched but not cached.
+    """
+
+    __slots__ = ("tensor", "version", "fingerprint")
+
+    def __init__(self, tensor: torch.Tensor) -> None:
+        self.tensor = tensor
+        self.version: Optional[int] = None if tensor.is_inference() else tensor._version
+        self.fingerprint = _fingerprint(tensor)
+
+    @property
+    def cacheable(self) -> bool:
+        return self.version is not None
+
+    def current(self) -> torch.Tensor:
+        if self.version is not None and self.tensor._version != self.version:
+            raise RuntimeError("topk_idx changed after the dispatch that this handle describes; dispatch again instead of reusing it")
+        return self.tensor
+
+    def same_memory(self) -> bool:
+        return _fingerprint(self.tensor) == self.fingerprint
+
+
+class _Routed:
+    """What the handle and the cached layout have in common: a routing tensor and the buffer state it is valid for."""
+
+    _route: RouteBinding
+    _layout: Any
+    _owner: Any
 
     @property
     def topk_idx(self) -> torch.Tensor:
-        if self._topk_version is not None and self._topk_idx._version != self._topk_version:
-            raise RuntimeError("topk_idx changed while its dispatch handle was in use")
-        return self._topk_idx
+        return self._route.current()
+
+    # kept for callers that looked at these directly
+    @property
+    def _topk_version(self) -> Optional[int]:
+        return self._route.version
 
     def validate_cached(self, owner: "HostStagedEPBuffer", x: torch.Tensor, alignment: int, do_expand: bool) -> Any:
-        """Host-side checks only; no device value is read (reference: ``handle.py:117-136``)."""
-        if self.buffer_id != owner.buffer_id or self.generation != owner._generation:
-            raise ValueError("Cached handle belongs to another buffer generation")
+        """May this routing be reused for ``x`` on ``owner``?  Returns the native plan.  Host-side checks only."""
+        if (self.buffer_id, self.generation) != (owner.buffer_id, owner._generation):
+            raise ValueError("cached routing was produced by another buffer, or the buffer has been rebuilt since")
         if self._owner is not owner or self.group is not owner.group or self.global_ranks != owner.global_ranks:
-            raise ValueError("Cached handle belongs to another EP group or owner map")
-        if self.num_experts != owner.num_experts or self.num_max_tokens_per_rank != owner.num_max_tokens_per_rank:
-            raise ValueError("Cached handle dimensions or expert ownership changed")
-        route = self.topk_idx
-        if self._topk_version is None:
-            raise ValueError("Cached routing requires a tensor with a PyTorch version counter")
-        if _tensor_signature(route) != self._route_signature:
-            raise ValueError("Cached routing tensor address, shape or strides changed")
-        if x.shape[0] != route.shape[0] or x.shape[1] != owner.hidden:
-            raise ValueError("Cached dispatch input dimensions changed")
-        if (alignment, do_expand) != (self.expert_alignment, self.do_expand):
-            raise ValueError("Cached dispatch alignment or expansion mode changed")
+            raise ValueError("cached routing belongs to a different EP group or rank-to-expert ownership")
+        if (self.num_experts, self.num_max_tokens_per_rank) != (owner.num_experts, owner.num_max_tokens_per_rank):
+            raise ValueError("cached routing was made for other buffer dimensions")
+        route = self.topk_idx  # raises if the routing tensor was written to
+        if not self._route.cacheable:
+            raise ValueError("a routing tensor without a PyTorch version counter (inference tensor) cannot be cached")
+        if not self._route.same_memory():
+            raise ValueError("the cached routing tensor now has another address, shape or stride")
+        if tuple(x.shape) != (route.shape[0], owner.hidden):
+            raise ValueError(f"x has shape {tuple(x.shape)}, the cached routing covers {route.shape[0]} tokens of hidden {owner.hidden}")
+        if (alignment, bool(do_expand)) != (self.expert_alignment, bool(self.do_expand)):
+            raise ValueError("a cached routing fixes expert alignment and layout: alignment or expansion differs from the cached dispatch")
         if self._layout is None:
-            raise RuntimeError("The native runtime did not provide an immutable cached layout")
+            raise RuntimeError("this dispatch produced no reusable native routing plan")
         return self._layout
 
 
-class HostStagedEPHandle(_RouteGuard):
-    """Device-side description of one capacity-shaped dispatch result."""
+# attribute on the handle -> key of the native result (DeepEP-compatible aliases included)
+_RESULT_FIELDS = {
+    "unique_count": "unique_count",
+    "num_recv_tokens": "unique_count",
+    "expanded_count": "expanded_count",
+    "num_expanded_tokens": "expanded_count",
+    "expert_counts": "expert_counts",
+    "num_unaligned_recv_tokens_per_expert": "expert_counts",
+    "expert_offsets": "expert_offsets",
+    "psum_num_recv_tokens_per_expert": "expert_prefix",
+    "source_meta": "source_meta",
+    "recv_src_metadata": "source_meta",
+    "source_offsets": "source_offsets",
+    "source_expert_prefix": "source_expert_prefix",
+    "error": "error",
+    "stats": "stats",
+    "transport_timestamps_ns": "transport_timestamps_ns",
+    "prefix_tx_timestamps_ns": "prefix_tx_timestamps_ns",
+    "receive_expand_overlap": "receive_expand_overlap",
+    "profiling": "profiling",
+    "role_profiling": "role_profiling",
+    "dst_buffer_slot_idx": "dst_buffer_slot_idx",
+}
 
-    def __init__(
-        self,
-        owner: "HostStagedEPBuffer",
-        topk_idx: torch.Tensor,
-        result: Dict[str, Any],
-        do_expand: bool,
-        expert_alignment: int,
-        event: EventOverlap,
-    ) -> None:
-        self.buffer_id = owner.buffer_id
-        self.generation = owner._generation
-        self.group = owner.group
-        self.global_ranks = owner.global_ranks
-        self.do_expand = do_expand
-        self.expert_alignment = expert_alignment
-        self.num_experts = owner.num_experts
-        self.num_max_tokens_per_rank = owner.num_max_tokens_per_rank
-        self.num_sms = 0
-        self._topk_idx = topk_idx
-        self._topk_version = None if topk_idx.is_inference() else topk_idx._version
-        self._route_signature = _tensor_signature(topk_idx)
-        self._layout = result.get("_layout")
+
+class HostStagedEPHandle(_Routed):
+    """Device-side description of one capacity-shaped dispatch result.
+
+    Result tensors are looked up in the native result when first asked for, so a dispatch spends no CPU
+    time on fields nobody reads.
+    """
+
+    def __init__(self, owner: "HostStagedEPBuffer", topk_idx: torch.Tensor, result: Dict[str, Any], do_expand: bool,
+                 expert_alignment: int, event: EventOverlap) -> None:
+        self._owner = owner
+        self._route = RouteBinding(topk_idx)
         self._result = result
+        self._layout = result.get("_layout")
+        self.buffer_id, self.generation = owner.buffer_id, owner._generation
+        self.group, self.global_ranks = owner.group, owner.global_ranks
+        self.num_experts, self.num_max_tokens_per_rank = owner.num_experts, owner.num_max_tokens_per_rank
+        self.do_expand, self.expert_alignment = do_expand, expert_alignment
+        self.num_sms = 0
         self.num_recv_tokens_per_expert_list = None
         self.completion = event
         self._completion_event = event.event
-        self._owner = owner
-
-    # Result fields are looked up when first asked for (a dispatch touches none of them on the CPU).
-    # name on the handle -> key in the native result; DeepEP-compatible aliases included.
-    _FIELDS = {
-        "unique_count": "unique_count",
-        "num_recv_tokens": "unique_count",
-        "expanded_count": "expanded_count",
-        "num_expanded_tokens": "expanded_count",
-        "expert_counts": "expert_counts",
-        "num_unaligned_recv_tokens_per_expert": "expert_counts",
-        "expert_offsets": "expert_offsets",
-        "source_meta": "source_meta",
-        "recv_src_metadata": "source_meta",
-        "source_offsets": "source_offsets",
-        "source_expert_prefix": "source_expert_prefix",
-        "psum_num_recv_tokens_per_expert": "expert_prefix",
-        "error": "error",
-        "stats": "stats",
-        "transport_timestamps_ns": "transport_timestamps_ns",
-        "receive_expand_overlap": "receive_expand_overlap",
-        "prefix_tx_timestamps_ns": "prefix_tx_timestamps_ns",
-        "profiling": "profiling",
-        "dst_buffer_slot_idx": "dst_buffer_slot_idx",
-    }
 
     def __getattr__(self, name: str) -> Any:
-        # only called for attributes not set in __init__
+        # reached only for names that __init__ did not set: resolve against the native result and remember
         if name == "psum_num_recv_tokens_per_scaleup_rank":
             value = self._result["source_offsets"][1:]
-        elif name in HostStagedEPHandle._FIELDS:
-            value = self._result.get(HostStagedEPHandle._FIELDS[name])
         else:
-            raise AttributeError(name)
+            key = _RESULT_FIELDS.get(name)
+            if key is None:
+                raise AttributeError(name)
+            value = self._result.get(key)
         self.__dict__[name] = value
         return value
 
     def check_errors(self) -> None:
-        """Explicit diagnostic synchronisation; never called by dispatch itself."""
+        """Explicit diagnostic: waits for this dispatch and raises if the device recorded an error."""
         self._owner.check_errors(self)
 
     def cache_layout(self) -> "CachedLayout":
@@ -131,27 +155,25 @@ class HostStagedEPHandle(_RouteGuard):
 
     @property
     def cached_layout(self) -> "CachedLayout":
-        return self.cache_layout()
-
-    _tensor_signature = staticmethod(_tensor_signature)
+        return CachedLayout(self)
 
 
-class CachedLayout(_RouteGuard):
-    """Routing plan + route identity, without any result-pool tensor (reference: ``handle.py:139-171``)."""
+class CachedLayout(_Routed):
+    """A routing plan detached from its result: holds the routing tensor's identity and the native plan, and
+    no output tensor, so keeping it alive does not keep a result pool busy."""
+
+    _COPIED = ("_owner", "_layout", "buffer_id", "generation", "group", "global_ranks", "num_experts",
+               "num_max_tokens_per_rank", "expert_alignment", "do_expand")
 
     def __init__(self, handle: HostStagedEPHandle) -> None:
         if handle._layout is None:
-            raise RuntimeError("This dispatch has no immutable native layout to cache")
-        if handle._topk_version is None:
-            raise ValueError("Cached routing requires a PyTorch version counter")
-        self._topk_idx = handle.topk_idx
-        for name in (
-            "_topk_version", "_route_signature", "_layout", "_owner", "buffer_id", "generation", "group",
-            "global_ranks", "num_experts", "num_max_tokens_per_rank", "expert_alignment", "do_expand",
-        ):
+            raise RuntimeError("this dispatch produced no reusable native routing plan")
+        if not handle._route.cacheable:
+            raise ValueError("a routing tensor without a PyTorch version counter (inference tensor) cannot be cached")
+        handle.topk_idx  # refuses a routing tensor that has been written to since
+        self._route = handle._route
+        for name in self._COPIED:
             setattr(self, name, getattr(handle, name))
-
-    _tensor_signature = staticmethod(_tensor_signature)
 
 
 EPHandle = HostStagedEPHandle

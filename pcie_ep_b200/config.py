@@ -1,7 +1,7 @@
 """Configuration of the expert-parallel dispatch/combine transport.
 
 ``HostStagedConfig`` keeps the field names of the reference's flag system
-(reference: ``pcie_ep/config.py:42-63``) so that existing call sites keep
+(parity: ``pcie_ep/config.py:9-129``) so that existing call sites keep
 working, and adds the fields that select the Blackwell transport.  The
 class is frozen: one instance is agreed on collectively when a buffer is
 built and never changes afterwards.
@@ -42,13 +42,18 @@ class HostStagedConfig:
     payload_slots: per (source, channel) receive-ring capacity in rows.  ``0``
         (the default here) sizes the ring for ``num_max_tokens_per_rank`` so a
         sender never waits for credit; a positive value bounds peer memory and
-        turns on the ACK/credit path (reference: bounded rings,
-        ``docs/pcie-ep/design.md:176-200``).
+        turns on the ACK/credit path.
     descriptor_slots: kept for source compatibility; rows and their READY
         flags share one ring here, so it must equal ``payload_slots`` or 0/256.
     channels: number of independently owned channels = CTAs per rank.
-    stage: capability gate 6 (BF16), 7 (FP8 wire), 8 (relay); the gates are
-        checked exactly like the reference's (``pcie_ep/config.py:65-102``).
+    stage: capability gate 6 (BF16), 7 (FP8 wire), 8 (relay).
+    pipeline_stages: shared-memory row buffers per send warp (2, 3 or 4): a send warp loads
+        ``pipeline_stages - 1`` rows ahead of the one it is pushing.
+    receive_expand_mode: row-copy path of the kernel: ``"pipelined"`` (bulk copies through shared
+        memory), ``"vectorized"`` (16-byte register copies) or ``"scalar"`` (2-byte register copies).
+    warp_specialization / fuse_receive_expand / source_fusion / replica_slots: accepted at their
+        defaults only; the other values name code paths of the host-staged design that this
+        library does not contain and are refused with ``NotImplementedError``.
     timeout_ms: device-side bound of every protocol wait.
     wire_dtype: ``"bf16"`` or ``"fp8_e4m3"`` (one FP32 scale per token).
     enable_graph: allocate the extra fixed-address result pool for
@@ -120,68 +125,73 @@ class HostStagedConfig:
     send_ctas: int = -1
 
     def __post_init__(self) -> None:
-        for name in ("timeout_ms", "replica_slots"):
-            if not isinstance(getattr(self, name), int) or getattr(self, name) < 1:
-                raise ValueError(f"{name} must be a positive integer")
-        for name in ("payload_slots", "descriptor_slots"):
-            if not isinstance(getattr(self, name), int) or getattr(self, name) < 0:
-                raise ValueError(f"{name} must be a nonnegative integer")
-        if self.stage not in (6, 7, 8):
-            raise ValueError("stages 1-5 are retired; stage must be 6, 7 or 8")
-        if not isinstance(self.channels, int) or not 1 <= self.channels <= MAX_CHANNELS:
-            raise ValueError(f"channels must be an integer in [1, {MAX_CHANNELS}]")
-        if self.pipeline_stages not in (2, 3, 4):
-            raise ValueError("pipeline_stages counts the row buffers of a send warp and must be 2, 3 or 4")
-        if self.receive_expand_mode not in ("scalar", "vectorized", "pipelined"):
-            raise ValueError("receive_expand_mode must be 'scalar', 'vectorized' or 'pipelined'")
-        if self.receive_expand_mode != "scalar":
-            if not self.fuse_receive_expand or not self.warp_specialization:
-                raise ValueError("Non-scalar receive expansion requires fuse_receive_expand and warp_specialization")
-        if self.wire_dtype not in _WIRE_DTYPES:
-            raise ValueError("wire_dtype must be 'bf16' or 'fp8_e4m3'")
-        if self.stage < 7 and self.wire_dtype != "bf16":
-            raise NotImplementedError("FP8 wire transport requires S7")
-        if self.numa_mode not in ("direct", "relay"):
-            raise ValueError("numa_mode must be 'direct' or 'relay'")
-        if self.numa_mode == "relay" and self.stage < 8:
-            raise NotImplementedError("NUMA relay is an S8 optimization")
-        if not isinstance(self.relay_workers_per_numa, int) or not 1 <= self.relay_workers_per_numa <= self.channels:
-            raise ValueError("relay_workers_per_numa must be an integer in [1, channels]")
-        if not isinstance(self.relay_cpu_affinity, tuple) or any(
-            not isinstance(cpu, int) or cpu < 0 for cpu in self.relay_cpu_affinity
-        ):
-            raise ValueError("relay_cpu_affinity must be a tuple of nonnegative CPU indices")
-        if len(set(self.relay_cpu_affinity)) != len(self.relay_cpu_affinity):
-            raise ValueError("relay_cpu_affinity must contain distinct CPU indices")
-        if self.stage < 8 and (self.relay_workers_per_numa != 1 or self.relay_cpu_affinity):
-            raise NotImplementedError("Relay worker configuration requires S8")
-        if not isinstance(self.output_pool_size, int) or not 2 <= self.output_pool_size <= 8:
-            raise ValueError("output_pool_size must be at least two and at most eight")
+        def whole(name: str, low: int, high: Optional[int] = None) -> None:
+            value = getattr(self, name)
+            if isinstance(value, bool) or not isinstance(value, int) or value < low or (high is not None and value > high):
+                span = f"at least {low}" if high is None else f"in [{low}, {high}]"
+                raise ValueError(f"{name}={value!r}: expected an integer {span}")
+
+        def one_of(name: str, allowed: Tuple[str, ...]) -> None:
+            if getattr(self, name) not in allowed:
+                raise ValueError(f"{name}={getattr(self, name)!r}: expected one of {allowed}")
+
+        # capacities and sizes
+        whole("timeout_ms", 1)
+        whole("replica_slots", 1)
+        whole("payload_slots", 0)
+        whole("descriptor_slots", 0)
+        whole("channels", 1, MAX_CHANNELS)
+        whole("output_pool_size", 2, 8)
+        whole("pipeline_stages", 2, 4)
+        whole("tx_warps", 1, 8)
+        whole("rx_warps", 1, 12)
+        whole("send_ctas", -1, 64)
         for name in ("metadata_delay_ns", "tx_delay_ns", "rx_delay_ns", "scatter_delay_ns"):
-            if not isinstance(getattr(self, name), int) or getattr(self, name) < 0:
-                raise ValueError(f"{name} must be a nonnegative integer")
-        if self.transport not in _TRANSPORTS:
-            raise ValueError(f"transport must be one of {_TRANSPORTS}")
-        if self.recv_dtype not in _WIRE_DTYPES:
-            raise ValueError("recv_dtype must be 'bf16' or 'fp8_e4m3'")
-        if self.recv_dtype == "fp8_e4m3" and self.wire_dtype != "fp8_e4m3":
-            raise ValueError("recv_dtype='fp8_e4m3' needs wire_dtype='fp8_e4m3'")
-        if self.copy_engine not in _COPY_ENGINES:
-            raise ValueError(f"copy_engine must be one of {_COPY_ENGINES}")
-        if not isinstance(self.tx_warps, int) or not 1 <= self.tx_warps <= 8:
-            raise ValueError("tx_warps must be an integer in [1, 8]")
-        if not isinstance(self.rx_warps, int) or not 1 <= self.rx_warps <= 12:
-            raise ValueError("rx_warps must be an integer in [1, 12]")
-        if self.numa_mode == "relay" and self.transport not in ("host_staged", "auto"):
-            raise ValueError("numa_mode='relay' needs transport='host_staged'")
-        if not isinstance(self.send_ctas, int) or not -1 <= self.send_ctas <= 64:
-            raise ValueError("send_ctas must be -1 (chosen by rank count) or an integer in [0, 64]")
-        if self.combine_reduce not in ("auto", "separate", "inline"):
-            raise ValueError("combine_reduce must be 'auto', 'separate' or 'inline'")
-        if self.fused_expert_combine and self.numa_mode == "relay":
-            raise ValueError("fused_expert_combine writes peer memory directly; it cannot be combined with numa_mode='relay'")
+            whole(name, 0)
         if self.descriptor_slots not in (0, 256, self.payload_slots):
-            raise ValueError("descriptor_slots must be 0, 256 or equal to payload_slots")
+            raise ValueError("rows and their READY flags share one ring here: descriptor_slots must be 0, 256 or payload_slots")
+        # choices
+        one_of("wire_dtype", _WIRE_DTYPES)
+        one_of("recv_dtype", _WIRE_DTYPES)
+        one_of("numa_mode", ("direct", "relay"))
+        one_of("receive_expand_mode", ("scalar", "vectorized", "pipelined"))
+        one_of("transport", _TRANSPORTS)
+        one_of("copy_engine", _COPY_ENGINES)
+        one_of("combine_reduce", ("auto", "separate", "inline"))
+        # capability gates (stage 6: BF16 wire, 7: + FP8 wire, 8: + CPU relay)
+        if self.stage not in (6, 7, 8):
+            raise ValueError(f"stage={self.stage!r}: the capability gates are 6 (BF16), 7 (FP8 wire) and 8 (relay)")
+        if self.wire_dtype != "bf16" and self.stage < 7:
+            raise NotImplementedError("an FP8 wire is gated behind stage >= 7")
+        if self.recv_dtype == "fp8_e4m3" and self.wire_dtype != "fp8_e4m3":
+            raise ValueError("rows can only stay FP8 at the receiver if they travel as FP8: recv_dtype='fp8_e4m3' needs wire_dtype='fp8_e4m3'")
+        if self.numa_mode == "relay" and self.stage < 8:
+            raise NotImplementedError("the CPU relay is gated behind stage 8")
+        if self.numa_mode == "relay" and self.transport not in ("host_staged", "auto"):
+            raise ValueError("the CPU relay forwards host-staged segments: numa_mode='relay' needs transport='host_staged'")
+        if self.fused_expert_combine and self.numa_mode == "relay":
+            raise ValueError("fused_expert_combine stores into peer memory from a GEMM epilogue; CPU relay threads cannot forward that")
+        # relay workers
+        whole("relay_workers_per_numa", 1, self.channels)
+        affinity = self.relay_cpu_affinity
+        if not isinstance(affinity, tuple) or any(isinstance(c, bool) or not isinstance(c, int) or c < 0 for c in affinity):
+            raise ValueError("relay_cpu_affinity must be a tuple of CPU numbers")
+        if len(set(affinity)) != len(affinity):
+            raise ValueError("relay_cpu_affinity names a CPU twice")
+        if self.stage < 8 and (self.relay_workers_per_numa != 1 or affinity):
+            raise NotImplementedError("relay worker settings are gated behind stage 8")
+        # Flags of the host-staged design that select code paths of *this* kernel.  A value that would select a
+        # path this library does not contain is refused rather than silently ignored.
+        if self.receive_expand_mode != "scalar" and not (self.fuse_receive_expand and self.warp_specialization):
+            raise ValueError("receive_expand_mode 'vectorized' and 'pipelined' are modes of the fused, warp-specialised kernel")
+        if not self.warp_specialization:
+            raise NotImplementedError("warp_specialization=False (one homogeneous role per CTA) is not built; the kernel is warp-specialised")
+        if not self.fuse_receive_expand:
+            raise NotImplementedError("fuse_receive_expand=False (unique rows first, a separate scatter launch afterwards) is not built")
+        if not self.source_fusion:
+            raise NotImplementedError("source_fusion=False is not built: send warps always read routes and weights from the live inputs")
+        if self.replica_slots != 256:
+            raise NotImplementedError("replica_slots is not configurable: the relay forwards through full-size outboxes, not replica rings")
 
     @classmethod
     def tuned(cls, num_ranks: int, num_max_tokens_per_rank: int, **overrides) -> "HostStagedConfig":
@@ -204,8 +214,21 @@ class HostStagedConfig:
         options = {field.name: getattr(self, field.name) for field in fields(self)}
         options["relay_cpu_affinity"] = list(self.relay_cpu_affinity)
         options["payload_dtype"] = "fp8" if self.wire_dtype == "fp8_e4m3" else "bf16"
+        options["copy_engine"] = self.effective_copy_engine()
+        options["force_scalar"] = self.receive_expand_mode == "scalar"
+        if self.numa_mode == "relay":
+            # the relay threads forward combine rows by their per-row flags, which only the one-kernel combine writes
+            options["combine_reduce"] = "inline"
         options.pop("directory")
         return options
+
+    def effective_copy_engine(self) -> str:
+        """``receive_expand_mode`` picks the row-copy path of the kernel: ``"pipelined"`` = bulk copies through
+        shared memory (what ``copy_engine="tma"`` means), ``"vectorized"`` = 16-byte register copies
+        (``copy_engine="vector"``), ``"scalar"`` = 2-byte register copies.  The slower of the two settings wins."""
+        if self.receive_expand_mode != "pipelined":
+            return "vector"
+        return self.copy_engine
 
     def resolved_transport(self, cuda_available: bool) -> str:
         if self.transport != "auto":

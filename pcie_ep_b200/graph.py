@@ -1,90 +1,107 @@
-"""Fixed-address CUDA-graph dispatch: capture once (collectively), then replay with no host work.
+"""Dispatch as a CUDA graph: captured once, collectively; replayed with no host work beyond the launch.
 
-Same contract as the reference's ``GraphDispatch`` (``pcie_ep/graph.py:14-202``): one graph per buffer,
-results in a dedicated pool that the next replay overwrites, inputs bound by address, the epoch lives
-on the device so a replay needs nothing from the host, and both preparation steps end in an agreement
-round so no rank is left alone inside a capture.
+Parity: the reference's ``pcie_ep/graph.py:14-202`` (one graph per buffer, inputs bound by address, a
+result pool of its own that the next replay overwrites, two agreement rounds around the capture).
+The dispatch epoch lives on the device, so a replay carries no per-launch host state; every rank has
+to replay in the same order, exactly as it has to call ``dispatch`` in the same order.
 """
 
 from __future__ import annotations
 
-from typing import Any, Optional
+from typing import Any, Callable, Optional, Tuple
 
 import torch
 
+from .buffers import arguments
 from .buffers.handle import HostStagedEPHandle
 from .parallel import control
-from .utils.event import EventOverlap, _record_tensors
+from .utils.event import EventOverlap, hold_for_stream
 
 
-def _signature(tensor: Any) -> Any:
+def _address_binding(tensor: Optional[torch.Tensor]) -> Optional[tuple]:
+    """What a captured kernel argument depends on: where the tensor lives and how it is laid out."""
     if tensor is None:
         return None
     return (tensor.data_ptr(), tuple(tensor.shape), tuple(tensor.stride()), tensor.dtype, tensor.device)
 
 
 class GraphDispatch:
-    """One captured dispatch bound to a buffer and to fixed input addresses."""
+    """One captured dispatch of one buffer.  Write new values *into* ``x`` / ``topk_idx`` /
+    ``topk_weights`` (same tensors, same addresses), then ``replay()``.
 
-    def __init__(self, owner, x, topk_idx, weights, graph, result, alignment, expand, cached_handle) -> None:
+    A graph captured with routing (``topk_idx`` given) recomputes the routing plan on every replay, so
+    the routing tensor may change between replays.  A graph captured from a cached handle replays a
+    fixed plan and refuses to run once that routing tensor has been written to.
+    """
+
+    def __init__(self, owner: Any, request: arguments.DispatchRequest, graph: Any, result: Any) -> None:
         self._owner = owner
-        self.x, self.topk_idx, self.topk_weights = x, topk_idx, weights
-        self._graph, self._result = graph, result
-        self.expert_alignment, self.do_expand = alignment, expand
-        self._cached_handle = cached_handle
-        self._bindings = tuple(_signature(value) for value in (x, topk_idx, weights))
-        self._generation = owner._generation
-        self._closed = False
-        self._last_event = None
+        self._graph = graph
+        self._result = result
+        self._cache = request.source_handle
+        self._born_in = owner._generation
+        self._last_replay: Any = None
+        self._open = True
+        self.x, self.topk_idx, self.topk_weights = request.x, request.topk_idx, request.topk_weights
+        self.do_expand, self.expert_alignment = request.expand, request.alignment
+        self._captured_at = self._inputs_now()
 
-    def _validate_bindings(self) -> None:
-        if self._closed or self._owner._generation != self._generation:
-            raise RuntimeError("GraphDispatch is closed or its buffer generation changed")
-        actual = tuple(_signature(value) for value in (self.x, self.topk_idx, self.topk_weights))
-        if actual != self._bindings:
-            raise ValueError("GraphDispatch input address, shape, dtype or strides changed")
-        if self._cached_handle is not None:
-            self._cached_handle.validate_cached(self._owner, self.x, self.expert_alignment, self.do_expand)
+    def _inputs_now(self) -> Tuple[Optional[tuple], ...]:
+        return tuple(_address_binding(t) for t in (self.x, self.topk_idx, self.topk_weights))
+
+    def _check_replayable(self) -> None:
+        if not self._open or self._owner._generation != self._born_in:
+            raise RuntimeError("this GraphDispatch was closed, or its buffer has been rebuilt since the capture")
+        if self._inputs_now() != self._captured_at:
+            raise ValueError("a captured dispatch reads fixed addresses: an input tensor's address, shape, dtype or stride changed")
+        if self._cache is not None:
+            self._cache.validate_cached(self._owner, self.x, self.expert_alignment, self.do_expand)
 
     def replay(self, *, previous_event: Any = None, async_with_compute_stream: bool = False) -> Any:
-        """Enqueue the captured dispatch; returns the usual five items.  No CPU wait, no read-back."""
+        """Enqueue the captured dispatch and return the usual five items.  No CPU wait, no read-back."""
         owner = self._owner
         with owner._lock:
             owner._check_live()
-            self._validate_bindings()
+            self._check_replayable()
             if torch.cuda.is_current_stream_capturing():
-                raise RuntimeError("GraphDispatch.replay cannot be nested in another capture")
-            compute = torch.cuda.current_stream(owner.device)
-            stream = owner._launch_stream(compute, previous_event, async_with_compute_stream)
-            with torch.cuda.stream(stream):
-                self._graph.replay()
-                event = torch.cuda.Event()
-                event.record(stream)
-            refs = (owner, self, self.x, self.topk_idx, self.topk_weights, self._result)
-            overlap = EventOverlap(event, refs, owner._register_consumer_stream)
+                raise RuntimeError("replay() launches a graph and cannot itself be captured")
+
+            def launch(stream: Any) -> None:
+                with torch.cuda.stream(stream):
+                    self._graph.replay()
+
+            _, event = owner._enqueue(launch, (), previous_event, async_with_compute_stream)
+            self._last_replay = event
+            keep = (owner, self, self.x, self.topk_idx, self.topk_weights, self._result)
+            overlap = EventOverlap(event, keep, owner._register_consumer_stream)
             handle = HostStagedEPHandle(owner, self.topk_idx, self._result, self.do_expand, self.expert_alignment, overlap)
-            owner._last_event, owner._last_handle = event, handle
-            self._last_event = event
-            if not async_with_compute_stream:
-                if previous_event is not None:
-                    compute.wait_event(event)
-                    owner._comm_busy = False
-                owner._register_consumer_stream(compute)
-            return (
-                self._result["recv_x"],
-                self._result.get("recv_topk_idx"),
-                self._result.get("recv_topk_weights") if self.topk_weights is not None else None,
-                handle,
-                overlap,
-            )
+            owner._last_handle = handle
+            weights = self._result.get("recv_topk_weights") if self.topk_weights is not None else None
+            return self._result["recv_x"], self._result.get("recv_topk_idx"), weights, handle, overlap
 
     def close(self) -> None:
-        if self._closed:
+        """Wait for the last replay and free the graph.  The buffer's ``close`` does this as well."""
+        if not self._open:
             return
-        if self._last_event is not None:
-            self._last_event.synchronize()
+        if self._last_replay is not None:
+            self._last_replay.synchronize()
         self._graph.reset()
-        self._closed = True
+        self._open = False
+
+
+def _agreed(step: Callable[[], Any], owner: Any, what: str, undo: Callable[[], None]) -> Any:
+    """Run ``step`` on this rank, then let all ranks agree on whether it worked; ``undo`` runs if any rank failed."""
+    value, problem = None, None
+    try:
+        value = step()
+    except Exception as exc:  # noqa: BLE001 - reported to every rank below
+        problem = f"rank {owner.rank_idx}: {type(exc).__name__}: {exc}"
+    try:
+        control.agree(problem, owner.control_group, what)
+    except RuntimeError:
+        undo()
+        raise
+    return value
 
 
 def capture_dispatch(
@@ -98,60 +115,47 @@ def capture_dispatch(
     expert_alignment: Optional[int] = None,
     do_zero_padding: bool = False,
 ) -> GraphDispatch:
-    """Collective.  May synchronise; the returned object's ``replay`` never does."""
+    """Collective.  Validates, synchronises the device, captures one dispatch into the buffer's graph pool.
+
+    Both phases end in an agreement round over the control group: a rank whose arguments are wrong, or
+    whose capture fails, makes every rank raise instead of leaving the others inside a capture.
+    """
     with owner._lock:
         owner._check_live()
         if not owner.on_gpu:
             raise NotImplementedError("capture_dispatch needs a GPU transport")
         if not owner.config.enable_graph:
-            raise NotImplementedError("capture_dispatch requires enable_graph=True")
+            raise NotImplementedError("capture_dispatch needs a buffer built with enable_graph=True (it reserves the graph's result pool)")
         if owner._graph_capture is not None:
-            raise RuntimeError("A buffer supports one fixed-address GraphDispatch; rebuild it to recapture")
-        graph, cached, alignment, error = None, None, None, None
-        try:
-            if handle is not None:
-                if topk_idx is not None:
-                    raise ValueError("topk_idx must be None when a cached handle is supplied")
-                topk_idx = handle.topk_idx
-            alignment = (handle.expert_alignment if handle is not None else 1) if expert_alignment is None else expert_alignment
-            if not isinstance(alignment, int) or not 1 <= alignment <= 256:
-                raise ValueError("expert_alignment must be in [1,256]")
-            if do_zero_padding and not do_expand:
-                raise ValueError("do_zero_padding requires do_expand=True")
-            owner._validate_input(x, "x", torch.bfloat16, (None, owner.hidden))
-            owner._validate_input(topk_idx, "topk_idx", torch.int64, (x.shape[0], owner.num_topk))
-            if x.shape[0] > owner.num_max_tokens_per_rank:
-                raise ValueError("Graph input exceeds the prepared capacity")
-            if topk_weights is not None:
-                owner._validate_input(topk_weights, "topk_weights", torch.float32, topk_idx.shape)
-            if handle is not None:
-                cached = handle.validate_cached(owner, x, alignment, do_expand)
-            torch.cuda.synchronize(owner.device)
-            graph = torch.cuda.CUDAGraph()
-        except Exception as exc:  # noqa: BLE001 - agreed on below
-            error = f"rank {owner.rank_idx}: {type(exc).__name__}: {exc}"
-        try:
-            control.agree(error, owner.control_group, "Collective graph preparation")
-        except RuntimeError:
-            if graph is not None:
-                graph.reset()
-            raise
+            raise RuntimeError("this buffer already holds its one fixed-address GraphDispatch; build a new buffer to capture again")
 
-        result, error = None, None
-        try:
-            with torch.cuda.stream(owner._comm_stream):
-                _record_tensors((x, topk_idx, topk_weights), owner._comm_stream)
-            with torch.cuda.graph(graph, stream=owner._comm_stream):
-                result = owner.runtime.dispatch(x, topk_idx, topk_weights, alignment, do_expand, do_zero_padding, cached, True)
-        except Exception as exc:  # noqa: BLE001
-            error = f"rank {owner.rank_idx}: {type(exc).__name__}: {exc}"
-        try:
-            control.agree(error, owner.control_group, "Collective graph capture")
-        except RuntimeError:
-            graph.reset()
-            raise
-        # a dynamic graph recomputes its routing on every replay: its plan is not a cacheable layout
-        result["_layout"] = cached
-        captured = GraphDispatch(owner, x, topk_idx, topk_weights, graph, result, alignment, do_expand, handle)
+        holder = {}
+
+        def prepare() -> arguments.DispatchRequest:
+            request = arguments.build_dispatch_request(
+                owner, x, topk_idx, topk_weights, handle=handle, expert_alignment=expert_alignment, do_expand=do_expand,
+                do_zero_padding=do_zero_padding, alignment_limit=arguments.MAX_ALIGNMENT)
+            torch.cuda.synchronize(owner.device)
+            holder["graph"] = torch.cuda.CUDAGraph()
+            return request
+
+        def drop_graph() -> None:
+            if "graph" in holder:
+                holder["graph"].reset()
+
+        request = _agreed(prepare, owner, "Collective graph preparation", drop_graph)
+        graph = holder["graph"]
+        comm = owner._streams.comm
+
+        def capture() -> Any:
+            hold_for_stream((request.x, request.topk_idx, request.topk_weights), comm)
+            with torch.cuda.graph(graph, stream=comm):
+                return owner.runtime.dispatch(request.x, request.topk_idx, request.topk_weights, request.alignment,
+                                              request.expand, request.zero_padding, request.cached_layout, True)
+
+        result = _agreed(capture, owner, "Collective graph capture", graph.reset)
+        # a graph that recomputes its routing on every replay has no plan worth caching
+        result["_layout"] = request.cached_layout
+        captured = GraphDispatch(owner, request, graph, result)
         owner._graph_capture = captured
         return captured

@@ -1,12 +1,11 @@
-"""Stream-dependency wrapper handed out with every dispatch/combine result.
+"""``EventOverlap``: the completion token that comes back with every dispatch and combine.
 
-Same contract as the reference's ``EventOverlap`` (``pcie_ep/utils/event.py:10-100``):
-waiting only enqueues a device-side dependency, the calling CPU thread never
-blocks; a wait also tells the owning buffer which stream consumes the result so
-that the result pool is not overwritten under a queued reader.
-
-The class works with CUDA events and, for the CPU transport, with ``None``
-events (a CPU result is complete when the call returns).
+Parity: the reference's ``pcie_ep/utils/event.py:10-100`` (same public methods and the same one-shot
+epilogue rule).  A token stands for device work that may still be running.  Waiting on it never blocks
+the calling CPU thread: it lines the *current CUDA stream* up behind the work, pins the objects that
+work still reads to that stream, and reports the stream to the owning buffer so that the buffer knows
+who may still be reading a result pool.  Tokens of the CPU transport carry no event: their work was
+complete when the call returned.
 """
 
 from __future__ import annotations
@@ -16,71 +15,87 @@ from typing import Any, Callable, Optional
 import torch
 
 
-class EventOverlap:
-    """One completion dependency plus the objects queued GPU work still needs."""
+def hold_for_stream(payload: Any, stream: Any) -> None:
+    """Tell the caching allocator that ``stream`` uses every CUDA tensor inside ``payload``.
 
-    def __init__(
-        self, event: Any = None, extra_tensors: Any = None, on_wait: Optional[Callable[[Any], None]] = None
-    ) -> None:
+    ``payload`` may be a tensor or any nesting of lists, tuples and dicts; other objects are skipped.
+    """
+    pending = [payload]
+    while pending:
+        item = pending.pop()
+        if isinstance(item, torch.Tensor):
+            if item.is_cuda:
+                item.record_stream(stream)
+        elif isinstance(item, dict):
+            pending.extend(item.values())
+        elif isinstance(item, (list, tuple)):
+            pending.extend(item)
+
+
+class EventOverlap:
+    """Completion of one piece of device work, plus what has to stay alive until it is consumed.
+
+    ``event``          CUDA event recorded behind the work, or ``None`` (CPU transport).
+    ``extra_tensors``  anything the queued work still references; kept alive by this object and pinned
+                       to every stream that waits on it.
+    ``on_wait``        callback ``f(stream)`` invoked with each waiting stream.
+    """
+
+    def __init__(self, event: Any = None, extra_tensors: Any = None,
+                 on_wait: Optional[Callable[[Any], None]] = None) -> None:
         self.event = event
         self.extra_tensors = extra_tensors
-        self._on_wait = on_wait
-        self.hook_after_wait: Optional[Callable[[], Any]] = None
-        self._release_handle_by_call = False
-        self._released = False
+        self._notify = on_wait
+        self._epilogue: Optional[Callable[[], Any]] = None
+        self._release_on_exit = False
+        self._spent = False
 
+    # -- waiting ---------------------------------------------------------------------------------
     def current_stream_wait(self, release_handle: bool = False) -> Any:
-        """Make the current stream wait for the event; return the hook's result once."""
-        if self._released:
-            raise RuntimeError("The event has already been released")
+        """Order the current stream after the work.  The first wait returns the deferred epilogue's
+        result (if one was registered), later waits return ``None``.  ``release_handle=True`` also drops
+        the event and the pinned objects; the token cannot be waited on again afterwards."""
+        if self._spent:
+            raise RuntimeError("this EventOverlap has been released and can no longer be waited on")
         if self.event is not None:
-            stream = torch.cuda.current_stream()
-            stream.wait_event(self.event)
-            _record_tensors(self.extra_tensors, stream)
-            if self._on_wait is not None:
-                self._on_wait(stream)
-        result = None
-        if self.hook_after_wait is not None:
-            hook, self.hook_after_wait = self.hook_after_wait, None
-            result = hook()
+            waiter = torch.cuda.current_stream()
+            waiter.wait_event(self.event)
+            hold_for_stream(self.extra_tensors, waiter)
+            if self._notify is not None:
+                self._notify(waiter)
+        epilogue, self._epilogue = self._epilogue, None
+        outcome = epilogue() if epilogue is not None else None
         if release_handle:
-            self.event = None
-            self.extra_tensors = None
-            self._on_wait = None
-            self._released = True
-        return result
+            self.event = self.extra_tensors = self._notify = None
+            self._spent = True
+        return outcome
 
     def wait(self) -> Any:
         return self.current_stream_wait()
 
     def register_hook_after_wait(self, hook_after_wait: Callable[[], Any]) -> None:
-        if self.hook_after_wait is not None:
-            raise RuntimeError("An epilogue hook is already registered")
-        self.hook_after_wait = hook_after_wait
+        """Attach the deferred epilogue; at most one may be pending."""
+        if self._epilogue is not None:
+            raise RuntimeError("an epilogue is already waiting on this EventOverlap")
+        self._epilogue = hook_after_wait
 
+    @property
+    def hook_after_wait(self) -> Optional[Callable[[], Any]]:
+        return self._epilogue
+
+    # -- ``with event:`` / ``with event(release_handle=True):`` -----------------------------------
     def __call__(self, release_handle: bool = False) -> "EventOverlap":
-        self._release_handle_by_call = release_handle
+        self._release_on_exit = bool(release_handle)
         return self
 
     def __enter__(self) -> "EventOverlap":
         return self
 
     def __exit__(self, exc_type: Any, exc_value: Any, traceback: Any) -> None:
-        try:
-            if not self._released:
-                self.current_stream_wait(self._release_handle_by_call)
-        finally:
-            self._release_handle_by_call = False
+        release, self._release_on_exit = self._release_on_exit, False
+        if not self._spent:
+            self.current_stream_wait(release)
 
 
-def _record_tensors(value: Any, stream: Any) -> None:
-    """``record_stream`` every CUDA tensor found in a nested container."""
-    if isinstance(value, torch.Tensor):
-        if value.is_cuda:
-            value.record_stream(stream)
-    elif isinstance(value, dict):
-        for child in value.values():
-            _record_tensors(child, stream)
-    elif isinstance(value, (list, tuple)):
-        for child in value:
-            _record_tensors(child, stream)
+# earlier name of the helper, still imported by user code
+_record_tensors = hold_for_stream

@@ -42,6 +42,12 @@ def test_defaults_are_valid_and_frozen():
     (dict(payload_slots=4, descriptor_slots=5), ValueError),
     (dict(recv_dtype="fp8_e4m3"), ValueError),                    # needs the FP8 wire
     (dict(recv_dtype="int8"), ValueError),
+    # flags of the host-staged design whose other value names a code path that does not exist here
+    (dict(warp_specialization=False, receive_expand_mode="scalar"), NotImplementedError),
+    (dict(fuse_receive_expand=False, receive_expand_mode="scalar"), NotImplementedError),
+    (dict(source_fusion=False), NotImplementedError),
+    (dict(replica_slots=128), NotImplementedError),
+    (dict(send_ctas=65), ValueError),
 ])
 def test_rejections(kwargs, error):
     with pytest.raises(error):
@@ -78,3 +84,17 @@ def test_tuned_settings_by_size():
 
     with pytest.raises(ValueError):
         HostStagedConfig.tuned(0, 128)
+
+
+def test_every_accepted_flag_value_reaches_the_native_options():
+    """No flag is validated and then dropped: a value that passes changes what the runtime is told."""
+    from pcie_ep_b200 import HostStagedConfig
+
+    base = HostStagedConfig().native_options()
+    assert base["copy_engine"] == "tma" and base["force_scalar"] is False and base["pipeline_stages"] == 3
+    vectorized = HostStagedConfig(receive_expand_mode="vectorized").native_options()
+    assert vectorized["copy_engine"] == "vector" and vectorized["force_scalar"] is False
+    scalar = HostStagedConfig(receive_expand_mode="scalar").native_options()
+    assert scalar["copy_engine"] == "vector" and scalar["force_scalar"] is True
+    assert HostStagedConfig(pipeline_stages=2).native_options()["pipeline_stages"] == 2
+    assert HostStagedConfig(send_ctas=0).native_options()["send_ctas"] == 0

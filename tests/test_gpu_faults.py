@@ -123,3 +123,47 @@ def test_profiling_timestamps_are_monotonic(ext):
         prof = results[0]["profiling"].cpu()
         start, split, end = prof[:, 0], prof[:, 7], prof[:, 14]
         assert (start > 0).all() and (split >= start).all() and (end >= split).all()
+
+
+def test_row_with_wrong_sequence_is_refused(ext):
+    """A row whose sequence words do not match the epoch of its READY flag ends the launch with error 18.
+
+    The wrong sequence is written by the legal owner of the row (the sending rank's own send warps, through a
+    test hook of the runtime): nothing faults, every rank leaves its kernel normally."""
+    with _group(timeout_ms=300) as group:
+        cpu, args = _inputs()
+        ok = group.dispatch(*args, do_expand=True)
+        assert all(code[0] == 0 for code in _codes(ok))
+        del ok
+        group.runtimes[1].set_test_corrupt_sequence(True)
+        failed = group.dispatch(*args, do_expand=True)
+        codes = _codes(failed)
+        # whoever received a row of rank 1 refuses it (18, context = source rank 1); the others learn of the abort
+        assert any(code[0] == 18 and code[1] == 1 for code in codes), codes
+        assert all(code[0] in (0, 15, 18, 22) for code in codes), codes
+        assert codes[1][0] in (0, 15, 22), codes  # the sender itself never reads its own rows from a ring
+        del failed
+        group.runtimes[1].set_test_corrupt_sequence(False)
+        again = group.dispatch(*args, do_expand=True)
+        assert any(code[0] == 19 for code in _codes(again))  # the failure is terminal for the ranks that saw it
+
+
+def test_abort_published_in_mid_transfer_reaches_waiting_ranks(ext):
+    """Rank 2 withholds its counts, so everybody waits; rank 1 publishes an abort 2 ms into the launch.  The
+    waiting ranks leave with "peer abort" from rank 1 long before their own 5 s timeout would have fired."""
+    import time
+
+    with _group(timeout_ms=5000) as group:
+        cpu, args = _inputs()
+        ok = group.dispatch(*args, do_expand=True)
+        assert all(code[0] == 0 for code in _codes(ok))
+        del ok
+        group.runtimes[2].set_test_withhold_counts(True)
+        group.runtimes[1].set_test_control_abort_after_ns(2_000_000)
+        started = time.perf_counter()
+        failed = group.dispatch(*args, do_expand=True)
+        codes = _codes(failed)
+        elapsed = time.perf_counter() - started
+        assert elapsed < 2.5, f"ranks waited {elapsed:.2f} s: the abort did not cut their waits short"
+        assert any(code[0] == 22 and code[1] == 1 for code in codes), codes
+        assert all(code[0] in (12, 22, 27) for code in codes), codes

@@ -1,5 +1,6 @@
-"""READY/ACK publication litmus (reference: tests/mapped_litmus.cu + MAPPED_LITMUS.md): payload stores,
-st.release.sys of a single-writer flag, ld.acquire.sys + payload check on the other side, ACK back.
+"""READY/ACK publication litmus (parity: the reference's tests/mapped_litmus.cu + MAPPED_LITMUS.md): payload stores,
+st.release.sys of a single-writer flag, ld.acquire.sys + payload check on the other side, ACK back; and the same
+round trip with the payload pushed by cp.async.bulk and the flag stored after the bulk group's completion.
 One GPU: both sides as two CTAs of one cooperative launch.  Two GPUs: one process per side over IPC."""
 
 import pytest
@@ -10,12 +11,14 @@ from tests.test_cpu_transport import run_workers
 pytestmark = pytest.mark.gpu
 
 
-def test_litmus_two_ctas_one_gpu(ext):
-    size, rounds, words = 1 << 16, 50000, 512
+@pytest.mark.parametrize("method", [0, 1])
+def test_litmus_two_ctas_one_gpu(ext, method):
+    """method 0: ordinary stores + st.release.sys; method 1: bulk copy, completion wait, flag without a fence."""
+    size, rounds, words = 1 << 16, 50000 if method == 0 else 20000, 512
     a = ext.allocate_device_segment(size, 0)
     b = ext.allocate_device_segment(size, 0)
     status = torch.zeros(8, dtype=torch.int64, device="cuda")
-    ext.litmus(a, b, -1, rounds, words, status, 5000, 0)
+    ext.litmus(a, b, -1, rounds, words, status, 5000, 0, method)
     torch.cuda.synchronize()
     producer, consumer = status[:4].tolist(), status[4:].tolist()
     assert producer[0] == 0 and consumer[0] == 0, "a bounded wait expired"

@@ -94,3 +94,14 @@ def test_combine_owner_side_modes_across_processes(world, mode):
 def test_moe_layer_with_separate_combine_reduction_two_gpus():
     _need(2)
     run_workers(2, "--transport", "peer", "--suite", "moe_layer", "--hidden", "256", "--combine-reduce", "separate")
+
+
+def test_large_payload_headline_shape():
+    """T=4096 tokens per rank at hidden 7168 / 256 experts / top-8 on every GPU of the box (2, 4 or 8): every received
+    row is compared with its regenerated source, BF16 and FP8 wire, plus dedup counters and the combine round trip."""
+    gpus = torch.cuda.device_count()
+    world = 8 if gpus >= 8 else 4 if gpus >= 4 else 2 if gpus >= 2 else 0
+    if world == 0:
+        pytest.skip("needs at least 2 GPUs")
+    out = run_workers(world, "--transport", "peer", "--suite", "large", "--tokens", "4096", "--timeout-ms", "20000")
+    assert "large:" in out

@@ -185,17 +185,20 @@ def suite_litmus(args, rank, world, device):
     own = _C.allocate_device_segment(size, device.index)
     handles = gather(_C.export_device_segment(own))
     peer = _C.import_device_segment(handles[1 - rank], device.index)
-    status = torch.zeros(4, dtype=torch.int64, device=device)
-    dist.barrier()
-    _C.litmus(own, peer, rank, rounds, words, status, 5000, device.index)
-    torch.cuda.synchronize()
-    timed_out, mismatches, done, elapsed = status.cpu().tolist()
-    failure = None
-    if timed_out or mismatches or done != rounds:
-        failure = f"rank {rank}: timed_out={timed_out} mismatches={mismatches} rounds={done}/{rounds}"
-    agree(failure, "litmus")
-    if rank == 0:
-        print(f"litmus: {rounds} rounds, {elapsed / rounds / 1000:.2f} us per READY/ACK round trip with {words * 8} payload bytes", flush=True)
+    # method 0: ordinary stores + st.release.sys; method 1: the send warps' chain (bulk copy, completion wait,
+    # flag stored by another lane without a system-scope fence; bulk load behind fence.proxy.async on the other side)
+    for method, name in ((0, "stores+release"), (1, "bulk copy, flag after completion")):
+        status = torch.zeros(4, dtype=torch.int64, device=device)
+        dist.barrier()
+        _C.litmus(own, peer, rank, rounds, words, status, 5000, device.index, method)
+        torch.cuda.synchronize()
+        timed_out, mismatches, done, elapsed = status.cpu().tolist()
+        failure = None
+        if timed_out or mismatches or done != rounds:
+            failure = f"rank {rank} method {method}: timed_out={timed_out} mismatches={mismatches} rounds={done}/{rounds}"
+        agree(failure, "litmus")
+        if rank == 0:
+            print(f"litmus: [{name}] {rounds} rounds, {elapsed / rounds / 1000:.2f} us per READY/ACK round trip with {words * 8} payload bytes", flush=True)
     dist.barrier()
     _C.release_imported_segment(peer)
     dist.barrier()
@@ -203,7 +206,76 @@ def suite_litmus(args, rank, world, device):
     return 1
 
 
-SUITES = {"litmus": suite_litmus, "correctness": suite_correctness, "oracle_config": suite_oracle_config, "moe_layer": suite_moe_layer}
+def suite_large(args, rank, world, device):
+    """Payload validation at the headline shape (parity: the reference's tests/test_large.py:54-170): hidden 7168,
+    256 experts, top-8, T = 4096 / 8192 tokens per rank, BF16 and FP8 wire, dispatch (expanded) + combine.
+
+    Every token row is a hash of (source rank, token, column), so each rank regenerates on its GPU what every row
+    it received must contain, from the row's own (source, token) metadata, and compares chunk by chunk; the dedup
+    counters are compared with the route volume computed from all ranks' routing tables."""
+    import bench
+    from pcie_ep_b200.quantization import fp8_roundtrip_reference
+
+    hidden, experts, topk = 7168, 256, 8
+    local = experts // world
+    elements, cases = 0, 0
+    for tokens in [int(t) for t in args.tokens.split(",")]:
+        for wire in ("bf16", "fp8_e4m3"):
+            config = HostStagedConfig.tuned(world, tokens, transport=args.transport, timeout_ms=args.timeout_ms, output_pool_size=2,
+                                            stage=7 if wire != "bf16" else 6, wire_dtype=wire)
+            idx_cpu, w_cpu = bench.make_routes(tokens, experts, topk, rank)
+            all_idx = gather(idx_cpu)
+            x = bench.hashed_tokens(rank, tokens, hidden, device)
+            idx, w = idx_cpu.to(device), w_cpu.to(device)
+            failure = None
+            with HostStagedEPBuffer(dist.group.WORLD, tokens, hidden, topk, experts, config) as buffer:
+                try:
+                    recv_x, recv_idx, recv_w, handle, _ = buffer.dispatch(x, idx, w, do_expand=True)
+                    combined, _, _ = buffer.combine(recv_x, handle)
+                    torch.cuda.synchronize()
+                    buffer.check_errors()
+                    rows = int(handle.expanded_count)
+                    # rows this rank's experts must receive, and the dedup counters, from everybody's routing table
+                    want_rows = sum(int(((table // local) == rank).sum()) for table in all_idx)
+                    hits = idx_cpu // local
+                    want_sources = int((hits != rank).any(dim=1).sum())
+                    want_deliveries = sum(int((hits == d).any(dim=1).sum()) for d in range(world) if d != rank)
+                    want_received = sum(int(((table // local) == rank).any(dim=1).sum()) for s, table in enumerate(all_idx) if s != rank)
+                    stats = handle.stats.cpu().tolist()
+                    problems = []
+                    if rows != want_rows:
+                        problems.append(f"expanded rows {rows} != {want_rows}")
+                    if stats[:3] != [want_sources, want_received, want_deliveries]:
+                        problems.append(f"dedup counters {stats[:3]} != {[want_sources, want_received, want_deliveries]}")
+                    meta = handle.source_meta[:rows]
+                    cols = torch.arange(hidden, device=device, dtype=torch.int64).unsqueeze(0)
+                    for lo in range(0, rows, 2048):
+                        part = meta[lo:lo + 2048]
+                        want = (((part[:, 0:1] * 131 + part[:, 1:2] * 7 + cols * 3) % 251) - 125).to(torch.bfloat16)
+                        if wire != "bf16":
+                            remote = part[:, 0] != rank
+                            want = torch.where(remote.unsqueeze(1), fp8_roundtrip_reference(want), want)
+                        if not torch.equal(recv_x[lo:lo + part.shape[0]], want):
+                            problems.append(f"payload of rows {lo}..{lo + part.shape[0]} differs from its source")
+                            break
+                        elements += part.shape[0] * hidden
+                    tolerance = dict(rtol=3e-2, atol=1.0) if wire == "bf16" else dict(rtol=8e-2, atol=3.0)
+                    if not torch.allclose(combined.float(), x.float(), **tolerance):
+                        problems.append(f"combined output off by up to {float((combined.float() - x.float()).abs().max())}")
+                    if problems:
+                        failure = f"rank {rank} T={tokens} wire={wire}: {problems}"
+                    del recv_x, recv_idx, recv_w, handle, combined
+                except Exception as exc:  # noqa: BLE001 - reported collectively
+                    failure = f"rank {rank} T={tokens} wire={wire}: {type(exc).__name__}: {exc}"
+                agree(failure, "large payload")
+            cases += 1
+    total = sum(gather(elements))
+    if rank == 0:
+        print(f"large: {total} BF16 elements compared with their regenerated source on {world} ranks", flush=True)
+    return cases
+
+
+SUITES = {"large": suite_large, "litmus": suite_litmus, "correctness": suite_correctness, "oracle_config": suite_oracle_config, "moe_layer": suite_moe_layer}
 
 
 def main():
@@ -220,6 +292,7 @@ def main():
     parser.add_argument("--combine-reduce", default="auto", choices=["auto", "separate", "inline"])
     parser.add_argument("--small", action="store_true")
     parser.add_argument("--fp32", action="store_true")
+    parser.add_argument("--tokens", default="4096", help="suite large: tokens per rank, comma-separated")
     args = parser.parse_args()
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("gloo")
