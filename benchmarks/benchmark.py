@@ -3,7 +3,7 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         benchmarks/benchmark.py --tokens 128 256 1024 4096 8192 --mode eager --profile uniform
 
-Same measurement rules as the reference benchmark (``benchmarks/benchmark.py:150-233`` there): every
+Parity: the reference's ``benchmarks/benchmark.py`` (same measurement rules): every
 latency is a CUDA-event interval on the submitting stream around one whole call, the per-iteration
 maximum over ranks is taken and averaged; validation and reductions happen outside timed intervals;
 the deduplication counters of every iteration-free check dispatch must equal the route volume.  Modes:
@@ -27,7 +27,7 @@ sys.path.insert(0, str(ROOT))
 import torch
 import torch.distributed as dist
 
-from benchmarks.routing_fixture import DEFAULT_SEED, FixtureSpec, make_routes
+from benchmarks.routing_fixture import DEFAULT_SEED, FROZEN_SPECS, FixtureSpec, frozen_manifest, load_fixture, make_routes
 from pcie_ep_b200 import HostStagedConfig, HostStagedEPBuffer
 from pcie_ep_b200.ops.reference import route_volume
 
@@ -40,23 +40,37 @@ def gather(value):
     return values
 
 
-def channels_for(tokens: int) -> int:
-    return 32 if tokens <= 256 else 64 if tokens <= 1024 else 128
+def routes_for(args, tokens: int, rank: int, world: int):
+    """Skewed top-4 profiles at 8 ranks / 256 experts come from the committed frozen files (first T rows of every
+    rank's table, verified against the manifest's hashes); everything else from the seeded generator."""
+    spec = FixtureSpec(args.profile, tokens, args.experts, args.topk, world, args.seed)
+    for frozen in FROZEN_SPECS:
+        if (frozen.profile, frozen.experts, frozen.topk, frozen.world, frozen.seed) == (args.profile, args.experts, args.topk, world, args.seed) \
+                and tokens <= frozen.tokens:
+            _, routes = load_fixture(frozen_manifest(args.profile), tokens=tokens)
+            return routes[rank], "frozen file " + frozen_manifest(args.profile).name
+    return make_routes(spec, rank), "seeded generator"
 
 
 def bench_one(args, tokens: int, rank: int, world: int, device: torch.device):
     wire_fp8 = args.wire == "fp8_e4m3"
-    config = HostStagedConfig(channels=args.channels or channels_for(tokens), stage=7 if wire_fp8 else 6,
-                              wire_dtype=args.wire, enable_graph=args.mode.startswith("graph"), timeout_ms=20000,
-                              output_pool_size=2, tx_warps=2, rx_warps=10, copy_engine=args.engine)
-    spec = FixtureSpec(args.profile, tokens, args.experts, args.topk, world, args.seed)
-    idx_cpu, w_cpu = make_routes(spec, rank)
+    overrides = dict(channels=args.channels) if args.channels else {}
+    config = HostStagedConfig.tuned(world, tokens, stage=7 if wire_fp8 else 6, wire_dtype=args.wire,
+                                    enable_graph=args.mode.startswith("graph"), timeout_ms=20000, output_pool_size=2,
+                                    copy_engine=args.engine, **overrides)
+    (idx_cpu, w_cpu), route_source = routes_for(args, tokens, rank, world)
     volume = route_volume(idx_cpu, rank, world, args.experts)
     g = torch.Generator().manual_seed(4321 + rank)
-    xs = [torch.randn(tokens, args.hidden, generator=g).to(torch.bfloat16).to(device) for _ in range(4)]
+    xs = [torch.randn(tokens, args.hidden, generator=g).to(torch.bfloat16) for _ in range(4)]
+    if args.outliers:
+        # one element in a hundred fifty times larger: the FP8 wire's per-token scale has to absorb it
+        for x in xs:
+            spikes = torch.rand(x.shape, generator=g) < 0.01
+            x[spikes] *= 50
+    xs = [x.to(device) for x in xs]
     idx, w = idx_cpu.to(device), w_cpu.to(device)
     record = {"tokens": tokens, "mode": args.mode, "profile": args.profile, "wire": args.wire, "topk": args.topk,
-              "channels": config.channels, "world": world, "route_volume": gather(volume) if rank == 0 or True else None}
+              "channels": config.channels, "world": world, "routes": route_source, "route_volume": gather(volume)}
     with HostStagedEPBuffer(dist.group.WORLD, tokens, args.hidden, args.topk, args.experts, config) as buffer:
         # one checked dispatch: counters must equal the route volume (sender / receiver dedup)
         first = buffer.dispatch(xs[0], idx, w, do_expand=True)
@@ -129,7 +143,8 @@ def main() -> None:
     parser.add_argument("--experts", type=int, default=256)
     parser.add_argument("--topk", type=int, default=8)
     parser.add_argument("--mode", default="eager", choices=["eager", "cached", "graph", "graph_cached"])
-    parser.add_argument("--profile", default="uniform", choices=["uniform", "hotspot_20_80", "zipf"])
+    parser.add_argument("--profile", default="uniform", choices=["uniform", "hotspot_20_80", "zipf", "nvidia_calibrated"])
+    parser.add_argument("--outliers", action="store_true", help="x ~ N(0,1) with 1%% of the elements multiplied by 50")
     parser.add_argument("--wire", default="bf16", choices=["bf16", "fp8_e4m3"])
     parser.add_argument("--engine", default="tma", choices=["tma", "vector"])
     parser.add_argument("--channels", type=int, default=0)

@@ -8,14 +8,18 @@
 // between GPU and CPU uses the very flags of the protocol: the GPU's st.release.sys is the CPU's
 // acquire load, the CPU's release store is the destination GPU's ld.acquire.sys.
 //
-// This is the counterpart of the reference's NumaRelay (csrc/comm/numa_relay.hpp:59-366 there:
-// pinned worker threads that copy payload + metadata into NUMA-local replica rings and republish
-// descriptors), re-expressed for the push protocol: a worker follows one or more flows (r->d) and
-// per flow forwards, in this order, the abort flag, the counts message, staged rows channel by
-// channel as their READY flags appear, the done/cdone hand-backs and the combine rows.
+// Parity: the reference's NumaRelay (csrc/comm/numa_relay.hpp:59-366: pinned worker threads per target NUMA
+// domain that copy payload + metadata and republish descriptors, credit recycling, a drained epoch, page-placement
+// query), re-expressed for the push protocol: a worker follows one or more flows (r->d) and per flow forwards, in
+// this order, the abort flag, the counts message, staged rows channel by channel as their READY flags appear (in
+// bounded-ring mode only into slots the destination has acknowledged), the acknowledgements this rank's GPU wrote
+// for rows it received, the done/cdone hand-backs and the combine rows.
+//
+// Workers are grouped by the NUMA node of the destination GPU: `workers` threads per node, each pinned to that
+// node's CPUs (or to `cpu_affinity` when given), so that a copy runs next to the memory it writes.
 //
 // Failure codes (reported through diagnostics() and, where possible, as the rank's abort flag):
-//   101 a flow's READY sequence went backwards, 102 counts announce more rows than a ring holds,
+//   101 a flow's READY sequence went backwards, 102 counts announce more rows than a channel can ever hold,
 //   199 the relay was stopped while rows were still pending.
 #pragma once
 
@@ -31,6 +35,11 @@
 
 #include <pthread.h>
 #include <sched.h>
+#include <sys/syscall.h>
+#include <unistd.h>
+
+#include <cstdio>
+#include <map>
 
 #include <pybind11/pybind11.h>
 
@@ -53,9 +62,16 @@ class NumaRelay {
                                    options["num_topk"].cast<int>(), options["hidden"].cast<int>(),
                                    options["num_max_tokens"].cast<int>(), options["payload_slots"].cast<int>(),
                                    options["enable_combine"].cast<bool>());
-        if (lay_.slots != lay_.slots_full) throw std::invalid_argument("relay mode needs full-size rings (payload_slots = 0)");
+        ring_mode_ = lay_.slots < lay_.slots_full;
         if (static_cast<int>(outboxes.size()) != P || static_cast<int>(targets.size()) != P)
             throw std::invalid_argument("one outbox and one target per rank");
+        own_segment_ = reinterpret_cast<std::uint8_t*>(targets[rank]);
+        if (ring_mode_ && own_segment_ == nullptr) throw std::invalid_argument("bounded rings need this rank's own segment (credit checks)");
+        std::vector<int> nodes(P, 0);
+        if (options.contains("target_numa_nodes")) {
+            nodes = options["target_numa_nodes"].cast<std::vector<int>>();
+            if (static_cast<int>(nodes.size()) != P) throw std::invalid_argument("one NUMA node per rank");
+        }
         workers_ = std::max(1, options.contains("workers") ? options["workers"].cast<int>() : 1);
         if (options.contains("cpu_affinity"))
             for (auto cpu : options["cpu_affinity"].cast<std::vector<int>>()) affinity_.push_back(cpu);
@@ -65,6 +81,8 @@ class NumaRelay {
             flow->dest = d;
             flow->outbox = reinterpret_cast<std::uint8_t*>(outboxes[d]);
             flow->target = reinterpret_cast<std::uint8_t*>(targets[d]);
+            flow->numa_node = nodes[d] < 0 ? 0 : nodes[d];
+            flow->acks_seen.assign(ring_mode_ ? static_cast<std::size_t>(lay_.num_channels) * lay_.slots : 0, 0);
             flow->forwarded.assign(lay_.num_channels, 0);
             flow->expected.assign(lay_.num_channels, 0);
             flow->combine_epoch.assign(lay_.has_combine ? lay_.num_max_tokens : 0, 0);
@@ -78,8 +96,19 @@ class NumaRelay {
         if (running_) return;
         stopping_.store(false);
         running_ = true;
-        const int count = std::min<int>(workers_, std::max<std::size_t>(1, flows_.size()));
-        for (int w = 0; w < count; ++w) threads_.emplace_back([this, w, count] { run(w, count); });
+        // `workers_` threads per NUMA node that has destinations; a thread serves every workers_-th flow of its node
+        std::map<int, std::vector<std::size_t>> by_node;
+        for (std::size_t i = 0; i < flows_.size(); ++i) by_node[flows_[i]->numa_node].push_back(i);
+        int ordinal = 0;
+        for (const auto& [node, members] : by_node) {
+            const int count = std::min<int>(workers_, static_cast<int>(members.size()));
+            for (int w = 0; w < count; ++w) {
+                std::vector<std::size_t> mine;
+                for (std::size_t k = w; k < members.size(); k += count) mine.push_back(members[k]);
+                threads_.emplace_back([this, node, ordinal, mine] { run(node, ordinal, mine); });
+                ++ordinal;
+            }
+        }
     }
 
     void stop() {
@@ -106,11 +135,16 @@ class NumaRelay {
             f["combine_rows_copied"] = flow->combine_rows.load();
             f["failure"] = flow->failure.load();
             f["worker_cpu"] = flow->worker_cpu.load();
+            f["numa_node"] = flow->numa_node;
+            f["acks_forwarded"] = flow->acks_forwarded.load();
+            f["credit_waits"] = flow->credit_waits.load();
+            f["drained_epoch"] = flow->drained_epoch.load();
             flows.append(f);
         }
         d["flows"] = flows;
         d["workers"] = static_cast<int>(threads_.size());
         d["running"] = running_;
+        d["ring_mode"] = ring_mode_;
         return d;
     }
 
@@ -119,6 +153,9 @@ class NumaRelay {
         int dest = 0;
         std::uint8_t* outbox = nullptr;
         std::uint8_t* target = nullptr;
+        int numa_node = 0;                         // of the destination GPU
+        std::vector<std::uint64_t> acks_seen;      // ring mode: last acknowledgement forwarded per (channel, slot)
+        std::atomic<std::uint64_t> acks_forwarded{0}, credit_waits{0}, drained_epoch{0};
         std::vector<int> forwarded, expected;      // per channel, for the current counts epoch
         std::vector<std::uint64_t> combine_epoch;  // per token: last combine epoch forwarded
         std::uint64_t last_done = 0, last_cdone = 0, last_abort = 0;
@@ -138,21 +175,56 @@ class NumaRelay {
         __atomic_store_n(reinterpret_cast<std::uint64_t*>(p), v, __ATOMIC_RELEASE);
     }
 
-    void pin(int worker) {
-        if (affinity_.empty()) return;
-        cpu_set_t set;
-        CPU_ZERO(&set);
-        CPU_SET(affinity_[worker % affinity_.size()], &set);
-        pthread_setaffinity_np(pthread_self(), sizeof(set), &set);  // best effort
+    // CPUs of one NUMA node, from sysfs ("0-15,32-47"); empty when the platform does not say
+    static std::vector<int> node_cpus(int node) {
+        std::vector<int> cpus;
+        char path[96];
+        std::snprintf(path, sizeof(path), "/sys/devices/system/node/node%d/cpulist", node);
+        std::FILE* f = std::fopen(path, "r");
+        if (f == nullptr) return cpus;
+        char text[4096] = {0};
+        const std::size_t got = std::fread(text, 1, sizeof(text) - 1, f);
+        std::fclose(f);
+        text[got] = 0;
+        const char* p = text;
+        while (*p) {
+            char* end = nullptr;
+            const long lo = std::strtol(p, &end, 10);
+            if (end == p) break;
+            long hi = lo;
+            p = end;
+            if (*p == '-') {
+                hi = std::strtol(p + 1, &end, 10);
+                p = end;
+            }
+            for (long c = lo; c <= hi && c < CPU_SETSIZE; ++c) cpus.push_back(static_cast<int>(c));
+            while (*p == ',' || *p == '\n' || *p == ' ') ++p;
+        }
+        return cpus;
     }
 
-    void run(int worker, int count) {
-        pin(worker);
+    // Pin the calling worker: to one of the explicitly allowed CPUs if any were given, else to the CPUs of the
+    // destination's NUMA node.  Best effort: a refused affinity call leaves the thread where it is.
+    void pin(int node, int ordinal) {
+        cpu_set_t set;
+        CPU_ZERO(&set);
+        if (!affinity_.empty()) {
+            CPU_SET(affinity_[ordinal % affinity_.size()], &set);
+        } else {
+            const std::vector<int> cpus = node_cpus(node);
+            if (cpus.empty()) return;
+            for (int c : cpus) CPU_SET(c, &set);
+        }
+        pthread_setaffinity_np(pthread_self(), sizeof(set), &set);
+    }
+
+    void run(int node, int ordinal, const std::vector<std::size_t>& mine) {
+        pin(node, ordinal);
         const int cpu = sched_getcpu();
         unsigned idle = 0;
         while (!stopping_.load(std::memory_order_relaxed)) {
             bool progressed = false;
-            for (std::size_t i = worker; i < flows_.size(); i += count) {
+            for (std::size_t i : mine) {
                 flows_[i]->worker_cpu.store(cpu);
                 progressed |= progress(*flows_[i]);
             }
@@ -186,7 +258,7 @@ class NumaRelay {
             const int* message = reinterpret_cast<const int*>(f.outbox + at);
             const int* chan = message + lay_.num_ranks + lay_.num_local_experts;
             for (int c = 0; c < lay_.num_channels; ++c) {
-                if (chan[c] > lay_.slots) {
+                if (chan[c] > lay_.slots_full) {
                     f.failure.store(102);
                     return true;
                 }
@@ -204,12 +276,21 @@ class NumaRelay {
             for (int c = 0; c < lay_.num_channels; ++c) {
                 while (f.forwarded[c] < f.expected[c]) {
                     const int j = f.forwarded[c];
-                    const std::size_t ring = (static_cast<std::size_t>(me) * lay_.num_channels + c) * lay_.slots + j;
+                    const std::size_t ring = (static_cast<std::size_t>(me) * lay_.num_channels + c) * lay_.slots + j % lay_.slots;
                     const std::uint64_t want = make_seq(current, static_cast<std::uint32_t>(j + 1));
                     const std::uint64_t seen = load_acquire(f.outbox + lay_.ready_off + ring * 8);
                     if (seen != want) {
                         if ((seen >> 32) > current) f.failure.store(101);
                         break;
+                    }
+                    if (ring_mode_ && j >= lay_.slots) {
+                        // the destination's slot is free once its GPU has acknowledged row j - slots; that
+                        // acknowledgement arrives in this rank's own segment (forwarded by the destination's relay)
+                        const std::size_t credit = (static_cast<std::size_t>(f.dest) * lay_.num_channels + c) * lay_.slots + j % lay_.slots;
+                        if (load_acquire(own_segment_ + lay_.ack_off + credit * 8) != make_seq(current, static_cast<std::uint32_t>(j - lay_.slots + 1))) {
+                            f.credit_waits.fetch_add(1, std::memory_order_relaxed);
+                            break;
+                        }
                     }
                     if (delay) std::this_thread::sleep_for(std::chrono::nanoseconds(delay));
                     const std::size_t row = lay_.stage_off + ring * lay_.row_stride;
@@ -222,8 +303,24 @@ class NumaRelay {
                     moved = true;
                 }
             }
+            // everything the counts message of this epoch announced has been forwarded
+            if (!f.rows_pending() && f.drained_epoch.load() != current) f.drained_epoch.store(current);
         }
-        // 4. hand-backs
+        // 4. ring mode: acknowledgements this rank's GPU wrote (as a destination) for rows that came from f.dest
+        if (ring_mode_) {
+            const std::size_t base = static_cast<std::size_t>(me) * lay_.num_channels * lay_.slots;
+            for (std::size_t i = 0; i < f.acks_seen.size(); ++i) {
+                const std::uint64_t value = load_acquire(f.outbox + lay_.ack_off + (base + i) * 8);
+                if (value != f.acks_seen[i]) {
+                    store_release(f.target + lay_.ack_off + (base + i) * 8, value);
+                    f.acks_seen[i] = value;
+                    f.acks_forwarded.fetch_add(1, std::memory_order_relaxed);
+                    moved = true;
+                }
+            }
+        }
+        {
+        // 5. hand-backs
         const std::uint64_t done = load_acquire(f.outbox + lay_.done_off + flag);
         if (done != f.last_done) {
             store_release(f.target + lay_.done_off + flag, done);
@@ -237,7 +334,7 @@ class NumaRelay {
                 f.last_cdone = cdone;
                 moved = true;
             }
-            // 5. combine rows: one flag per (this rank, token)
+            // 6. combine rows: one flag per (this rank, token)
             const std::size_t flags = lay_.cready_off + static_cast<std::size_t>(me) * lay_.num_max_tokens * 8;
             const std::size_t rows = lay_.cstage_off + static_cast<std::size_t>(me) * lay_.num_max_tokens * lay_.crow_stride;
             for (int t = 0; t < lay_.num_max_tokens; ++t) {
@@ -252,10 +349,13 @@ class NumaRelay {
                 }
             }
         }
+        }
         return moved;
     }
 
     int rank_;
+    bool ring_mode_ = false;
+    std::uint8_t* own_segment_ = nullptr;
     SegmentLayout lay_{};
     int workers_ = 1;
     std::vector<int> affinity_;
@@ -265,5 +365,26 @@ class NumaRelay {
     std::atomic<std::uint64_t> delay_ns_{0};
     bool running_ = false;
 };
+
+// Which NUMA node holds each page of [address, address + bytes)?  node -> page count; -1 collects pages the kernel
+// could not place (not yet touched, or the call is not permitted here).  Uses move_pages(2) in its query form
+// (no node list): nothing is moved.
+inline std::map<int, long> query_numa_pages(std::uintptr_t address, std::size_t bytes) {
+    std::map<int, long> per_node;
+    const long page = sysconf(_SC_PAGESIZE);
+    if (bytes == 0 || page <= 0) return per_node;
+    const std::uintptr_t first = address & ~static_cast<std::uintptr_t>(page - 1);
+    const std::size_t count = (address + bytes - first + page - 1) / page;
+    constexpr std::size_t kBatch = 4096;
+    std::vector<void*> pages(kBatch);
+    std::vector<int> status(kBatch);
+    for (std::size_t done = 0; done < count; done += kBatch) {
+        const std::size_t n = std::min(kBatch, count - done);
+        for (std::size_t i = 0; i < n; ++i) pages[i] = reinterpret_cast<void*>(first + (done + i) * page);
+        const long rc = syscall(SYS_move_pages, 0, static_cast<unsigned long>(n), pages.data(), nullptr, status.data(), 0);
+        for (std::size_t i = 0; i < n; ++i) per_node[rc == 0 && status[i] >= 0 ? status[i] : -1] += 1;
+    }
+    return per_node;
+}
 
 }  // namespace bep

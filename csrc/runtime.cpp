@@ -96,6 +96,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("release_imported_segment", [](std::int64_t ptr) { release_imported_segment(reinterpret_cast<void*>(ptr)); });
     m.def("free_device_segment", [](std::int64_t ptr) { free_device_segment(reinterpret_cast<void*>(ptr)); });
     m.def("get_device_numa_node", &device_numa_node);
+    m.def("query_numa_pages", [](std::int64_t address, std::size_t bytes) {
+        py::dict out;
+        for (const auto& [node, pages] : query_numa_pages(static_cast<std::uintptr_t>(address), bytes)) out[py::int_(node)] = pages;
+        return out;
+    }, py::arg("address"), py::arg("bytes"));
     m.def("create_host_segment", &create_host_segment);
     m.def("first_touch_host_segment", &first_touch_host_segment);
     m.def("tensor_refs", [](const at::Tensor& t) {

@@ -136,6 +136,7 @@ import_device_segment = _module.import_device_segment
 release_imported_segment = _module.release_imported_segment
 free_device_segment = _module.free_device_segment
 get_device_numa_node = _module.get_device_numa_node
+query_numa_pages = _module.query_numa_pages
 create_host_segment = _module.create_host_segment
 first_touch_host_segment = _module.first_touch_host_segment
 dispatch_group = _module.dispatch_group

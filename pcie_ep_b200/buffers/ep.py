@@ -138,8 +138,13 @@ class HostStagedEPBuffer:
         if cfg.numa_mode != "relay":
             return
 
+        # relay workers are grouped by the NUMA node of the destination GPU: every rank reports its own
+        nodes = [None] * self.num_ranks
+        dist.all_gather_object(nodes, int(_C.get_device_numa_node(self.device)), group=self.control_group)
+
         def make_relay() -> Any:
             options = dict(num_ranks=self.num_ranks, channels=cfg.channels, num_experts=self.num_experts,
+                           target_numa_nodes=[max(0, n) for n in nodes],
                            num_topk=self.num_topk, hidden=self.hidden, num_max_tokens=self.num_max_tokens_per_rank,
                            payload_slots=cfg.payload_slots, enable_combine=cfg.enable_combine,
                            workers=cfg.relay_workers_per_numa, cpu_affinity=list(cfg.relay_cpu_affinity))

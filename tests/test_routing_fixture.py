@@ -53,3 +53,31 @@ def test_save_load_and_tamper_rejection(tmp_path):
     manifest.write_text(json.dumps(info))
     with pytest.raises(ValueError):
         load_fixture(manifest)
+
+
+def test_calibrated_profile_matches_the_published_moments():
+    from benchmarks.routing_fixture import CALIBRATED_CV, CALIBRATED_MAX_OVER_MEAN, calibrated_spectrum
+
+    spectrum = calibrated_spectrum(256, 4)
+    loads = spectrum * 256 / 4
+    assert abs(float(spectrum.sum()) - 4.0) < 1e-9 and float(spectrum.max()) <= 1.0
+    assert abs(float(loads.std(unbiased=False) / loads.mean()) - CALIBRATED_CV) < 1e-6
+    assert abs(float(loads.max() / loads.mean()) - CALIBRATED_MAX_OVER_MEAN) < 1e-9
+    stats = route_statistics(FixtureSpec("nvidia_calibrated", 4096, 256, 4, 8))
+    assert abs(stats["expert_cv"] - CALIBRATED_CV) < 0.05 and abs(stats["expert_max_over_mean"] - CALIBRATED_MAX_OVER_MEAN) < 0.6
+    idx, _ = make_routes(FixtureSpec("nvidia_calibrated", 512, 256, 4, 8), 3)
+    ordered = idx.sort(dim=1).values
+    assert not (ordered[:, 1:] == ordered[:, :-1]).any() and idx.min() >= 0 and idx.max() < 256
+    with pytest.raises(ValueError):
+        calibrated_spectrum(16, 4)  # the heaviest expert would need an inclusion probability above one
+
+
+def test_committed_frozen_fixtures_load_and_match_their_generators():
+    from benchmarks.routing_fixture import FROZEN_SPECS, frozen_manifest
+
+    for spec in FROZEN_SPECS:
+        loaded, routes = load_fixture(frozen_manifest(spec.profile), tokens=128)
+        assert loaded == spec and len(routes) == 8 and routes[0][0].shape == (128, 4)
+        assert torch.equal(routes[5][0], make_routes(spec, 5)[0][:128])  # frozen file == its generator
+    with pytest.raises(ValueError):
+        load_fixture(frozen_manifest("zipf"), tokens=9000)

@@ -70,3 +70,76 @@ def test_bench_routes_and_roofline_model():
     assert eight["dispatch_us"] > one["dispatch_us"] > 0
     # one rank, BF16: x read + expanded rows written = (1 + 8) * 256 rows of 14,336 bytes at the copy rate
     assert abs(one["dispatch_us"] - 9 * 256 * 14336 / 6548e9 * 1e6) / one["dispatch_us"] < 0.05
+
+
+def _trace(extra=()):
+    """A hand-made Chrome trace: two markers, launches inside and outside them, kernels linked by correlation id."""
+    events = [
+        {"ph": "X", "cat": "user_annotation", "name": "ep.dispatch", "ts": 100, "dur": 50, "tid": 1},
+        {"ph": "X", "cat": "user_annotation", "name": "ep.combine", "ts": 200, "dur": 60, "tid": 1},
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaLaunchKernelExC", "ts": 110, "dur": 5, "tid": 1, "args": {"correlation": 1}},
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaLaunchKernel", "ts": 210, "dur": 5, "tid": 1, "args": {"correlation": 2}},
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaLaunchKernel", "ts": 230, "dur": 5, "tid": 1, "args": {"correlation": 3}},
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaLaunchKernel", "ts": 400, "dur": 5, "tid": 1, "args": {"correlation": 4}},
+        # kernels run later than their launches, possibly after the marker has ended on the host
+        {"ph": "X", "cat": "kernel", "name": "bep::dispatch_kernel(bep::DispatchLaunch)", "ts": 160, "dur": 140, "args": {"correlation": 1}},
+        {"ph": "X", "cat": "kernel", "name": "bep::combine_push_kernel(bep::CombinePushArgs)", "ts": 310, "dur": 90, "args": {"correlation": 2}},
+        {"ph": "X", "cat": "kernel", "name": "bep::fused_reduce_kernel(bep::FusedReduceArgs)", "ts": 405, "dur": 30, "args": {"correlation": 3}},
+        {"ph": "X", "cat": "kernel", "name": "elementwise_kernel", "ts": 500, "dur": 3, "args": {"correlation": 4}},
+    ]
+    return {"traceEvents": events + list(extra)}
+
+
+def test_trace_attribution_by_correlation_id():
+    from benchmarks.analysis_dispatch_profile import attribute, audit, format_report
+
+    report = attribute(_trace())
+    assert [k for k, _ in report["ep.dispatch"]["kernels"]] == ["bep::dispatch_kernel(bep::DispatchLaunch)"]
+    assert len(report["ep.combine"]["kernels"]) == 2 and report["ep.combine"]["device_us"] == 120
+    assert [k for k, _ in report["(outside)"]["kernels"]] == ["elementwise_kernel"]
+    assert audit(report) == []
+    assert "dispatch_kernel" in format_report(report)
+
+
+def test_trace_audit_flags_nccl_sync_and_readback():
+    from benchmarks.analysis_dispatch_profile import attribute, audit
+
+    bad = _trace([
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaLaunchKernel", "ts": 120, "dur": 2, "tid": 1, "args": {"correlation": 9}},
+        {"ph": "X", "cat": "kernel", "name": "ncclDevKernel_AllGather_RING_LL", "ts": 300, "dur": 50, "args": {"correlation": 9}},
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaStreamSynchronize", "ts": 130, "dur": 20, "tid": 1, "args": {"correlation": 10}},
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaMemcpyAsync", "ts": 240, "dur": 2, "tid": 1, "args": {"correlation": 11}},
+        {"ph": "X", "cat": "gpu_memcpy", "name": "Memcpy DtoH (Device -> Pinned)", "ts": 420, "dur": 2, "args": {"correlation": 11}},
+    ])
+    problems = audit(attribute(bad))
+    assert any("NCCL" in p for p in problems) and any("cudaStreamSynchronize" in p for p in problems)
+    assert any("device-to-host" in p for p in problems) and len(problems) == 3
+
+
+def test_role_summary_layouts():
+    import torch
+
+    from benchmarks.analysis_dispatch_profile import summarise_roles
+
+    assert summarise_roles(torch.zeros(0, 16, 16), 4, 2, 2, 3) == {}
+    role = torch.zeros(6, 16, 16)
+    role[4:6, 0:2, 0] = 10     # two sender CTAs, two send warps each: 10 rows per warp
+    role[0:4, 1:4, 0] = 5      # four channel CTAs, three receive warps each
+    role[0:4, 1:4, 8] = 2
+    summary = summarise_roles(role, channels=4, send_ctas=2, tx_warps=2, rx_warps=3)
+    assert summary["send"]["rows"] == 10 and summary["send"]["warps"] == 4
+    assert summary["receive"]["rows"] == 5 and summary["receive"]["local_rows"] == 2 and summary["receive"]["warps"] == 12
+    inside = torch.zeros(4, 16, 16)
+    inside[:, 1:3, 0] = 7
+    inside[:, 3:6, 0] = 3
+    summary = summarise_roles(inside, channels=4, send_ctas=0, tx_warps=2, rx_warps=3)
+    assert summary["send"]["rows"] == 7 and summary["receive"]["rows"] == 3
+
+
+def test_smaps_rollup_parser():
+    from benchmarks.memory_footprint import parse_smaps_rollup
+
+    text = ("55d0c0a00000-7ffd1c5f2000 ---p 00000000 00:00 0                          [rollup]\n"
+            "Rss:              123456 kB\nPss:               65432 kB\nPss_Shmem:         2048 kB\nSwap:                  0 kB\n")
+    counters = parse_smaps_rollup(text)
+    assert counters == {"Rss": 123456 * 1024, "Pss": 65432 * 1024, "Pss_Shmem": 2048 * 1024, "Swap": 0}
