@@ -3,12 +3,15 @@
 ``nccl_payload``   one ``all_gather_into_tensor`` of the BF16 tokens (every rank receives everything).
 ``nccl_dispatch``  expert-ready dispatch: pack (tokens | ids | weights) per row, one uint8 all-gather,
                    then a stable per-expert expansion of the rows this rank owns (PyTorch kernels).
+``nccl_dispatch_kernels``  the same with the reference's own pack / count / prefix / scatter CUDA kernels
+                   (``benchmarks/csrc/nccl_expand.cu`` of the reference, used unmodified from ``baseline/_ref`` when
+                   that copy and its build exist; at most 32 experts per rank).
 ``fused``          this framework's fused dispatch kernel.
 
-Mirrors the reference's three-way comparison (``benchmarks/benchmark_nccl_shm.py:6-9,86-117`` there,
-which forces NCCL onto shared memory because its target has no NVLink); here NCCL runs over
-NVLink/NVSwitch as it would in production.  The expansion result is validated against the fused
-kernel's output outside the timed region.
+Parity: the reference's three-way comparison (``benchmarks/benchmark_nccl_shm.py``), which forces NCCL onto
+shared memory because its target has no NVLink (``benchmarks/reference_nccl_shm.py`` runs that script as it
+is); here NCCL runs over NVLink/NVSwitch as it would in production.  The expansion result is validated against
+the fused kernel's output outside the timed region.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         benchmarks/benchmark_nccl.py --tokens 128 1024 4096
@@ -55,6 +58,24 @@ def expand(rows, hidden, topk, rank, local):
     row, slot, expert = row[order], slot[order], expert[order]
     counts = torch.bincount(expert, minlength=local)
     return x[row], expert, w[row, slot], counts
+
+
+def reference_expand(world, tokens, hidden, topk, experts, rank, device):
+    """The reference's NCCLExpand helper (its pack and expansion kernels), or None when baseline/_ref has no build."""
+    ref = ROOT / "baseline" / "_ref" / "benchmarks"
+    if not (ref / "nccl_expand.py").exists() or experts // world > 32:
+        return None
+    os.environ["TORCH_CUDA_ARCH_LIST"] = "10.0"
+    os.environ.setdefault("TORCH_EXTENSIONS_DIR", str(ROOT / "baseline" / "_ref_build"))
+    sys.path.insert(0, str(ref))
+    try:
+        from nccl_expand import NCCLExpand
+
+        return NCCLExpand(world, tokens, hidden, topk, experts, rank, device)
+    except Exception as exc:  # noqa: BLE001 - the column is simply left out
+        if rank == 0:
+            print(f"reference expansion kernels unavailable: {type(exc).__name__}: {exc}", flush=True)
+        return None
 
 
 def timed(fn, iterations, warmup):
@@ -112,8 +133,13 @@ def main() -> None:
             dist.all_gather_into_tensor(gathered_rows, pack(x, idx, w))
             return expand(gathered_rows, args.hidden, args.topk, rank, local)
 
-        config = HostStagedConfig(channels=32 if tokens <= 256 else 64 if tokens <= 1024 else 128, timeout_ms=20000,
-                                  output_pool_size=2, tx_warps=2, rx_warps=10, enable_combine=False)
+        helper = reference_expand(world, tokens, args.hidden, args.topk, args.experts, rank, device)
+
+        def nccl_dispatch_kernels():
+            dist.all_gather_into_tensor(helper.packed_recv, helper.pack(x, idx, w))
+            return helper.expand()
+
+        config = HostStagedConfig.tuned(world, tokens, timeout_ms=20000, output_pool_size=2, enable_combine=False)
         buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, args.hidden, args.topk, args.experts, config,
                                     control_group=control)
 
@@ -142,6 +168,8 @@ def main() -> None:
             "nccl_dispatch_us": timed(nccl_dispatch, args.iterations, args.warmup),
             "fused_dispatch_us": timed(lambda: fused(), args.iterations, args.warmup),
         }
+        if helper is not None:
+            record["nccl_dispatch_kernels_us"] = timed(nccl_dispatch_kernels, args.iterations, args.warmup)
         buffer.close()
         records.append(record)
         if rank == 0:

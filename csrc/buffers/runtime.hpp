@@ -344,11 +344,14 @@ class Runtime {
         }
         // finished CTAs of the launch in flight: [0] scatter GEMM, [1] fused reduction, [2] combine owner-side sum,
         // [3] combine push; [4..8] statistics accumulators of the combine push
-        fused_counters_ = at::zeros({12}, i64);
+        fused_counters_ = at::zeros({16 + kMaxSmTable}, i64);
         fused_counters_[6] = -1;  // "first start" accumulator of the combine push: all ones = unset
         fused_status_ = at::zeros({4}, i32);
         fused_gemm_ctas_ = grouped_gemm_ctas();
-        combine_forward_ctas_ = std::min(16, std::max(1, fused_gemm_ctas_ / 8));
+        // Forwarder CTAs of the combine push.  What keeps NVLink full is the number of bytes in flight: six row buffers per
+        // forwarder CTA (more would cost the reducer CTAs their second CTA per SM), so thirty-two CTAs where the push is
+        // bound by the link (four ranks and more) and sixteen where it is bound by the reducers' HBM traffic.
+        combine_forward_ctas_ = std::min(num_ranks > 2 ? 32 : 16, std::max(1, fused_gemm_ctas_ / 4));
         if (options_.enable_combine && num_ranks > 1 && !combine_is_inline()) ensure_outbox();
         if (options_.enable_combine) {
             const auto bf16 = at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, device);
@@ -501,6 +504,8 @@ class Runtime {
         push.stats = a.stats;
         push.cta_done = counters + 3;
         push.stat_scratch = counters + 4;
+        push.next_unit = counters + 9;
+        push.forwarder_sms = counters + 16;
         push.forward_ctas = lay_.num_ranks > 1 ? combine_forward_ctas_ : 0;
         if (push.forward_ctas > 0) {
             ensure_outbox();

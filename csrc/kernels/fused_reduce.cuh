@@ -54,14 +54,21 @@ struct CombinePushArgs {
     std::uint8_t* outbox;              // [P*C*slots_full][crow_stride], local memory
     unsigned long long* outbox_units;  // [P*C*slots_full] finished units of the row in the outbox; zero between launches
     int forward_ctas;                  // the first CTAs of the grid only forward; 0 with a single rank
+    unsigned long long* next_unit;     // next entry to hand out to a reducer warp; zero between launches
+    unsigned long long* forwarder_sms; // [kMaxSmTable] combine epoch in which SM i hosts a forwarder CTA
 };
 
 constexpr int kPushGroupsPerUnit = 4;
+constexpr int kMaxSmTable = 256;
 constexpr int kForwardWarps = 2;   // per forwarder CTA
-constexpr int kForwardStages = 2;  // row buffers per forwarder warp
+constexpr int kForwardStages = 3;  // row buffers per forwarder warp: loads run two rows ahead of the row being sent
 
-inline std::size_t combine_push_smem_bytes(const SegmentLayout& lay, int forward_ctas) {
+// dynamic shared memory of the push kernel: the forwarder warps' row buffers behind 128 bytes of mbarriers
+__host__ __device__ inline std::size_t combine_push_tile_offset(const SegmentLayout& lay, int forward_ctas) {
     return forward_ctas > 0 ? 128 + static_cast<std::size_t>(kForwardWarps) * kForwardStages * lay.crow_stride : 0;
+}
+inline std::size_t combine_push_smem_bytes(const SegmentLayout& lay, int forward_ctas) {
+    return combine_push_tile_offset(lay, forward_ctas);
 }
 
 #ifdef __CUDACC__
@@ -173,8 +180,8 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 4) fused_reduce_kernel(co
 // Expert side of combine.  Work unit = (entry of the dispatch's combine map, four groups of 32 sixteen-byte
 // chunks): one warp iteration keeps eight row loads per lane in flight, whether the entry reduces one expert row
 // or eight.  Entries are numbered (channel, row index, source step) with the source fastest and rotated by this
-// rank's index; units are dealt out round-robin over the warps of the grid, so the entries complete roughly in
-// their numbering order.
+// rank's index; reducer warps take entries one at a time from one counter, so the rows complete roughly in their
+// numbering order.
 //
 // Where the reduced row goes:
 //   * one rank: straight to `out`;
@@ -266,6 +273,11 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
 
     if (!s_failed && forwarder) {
         // ---- forward completed outbox rows to their owners --------------------------------------------
+        if (threadIdx.x == 0) {
+            unsigned sm;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+            if (sm < static_cast<unsigned>(kMaxSmTable)) ptx::st_relaxed_sys(reinterpret_cast<std::uint64_t*>(a.forwarder_sms + sm), epoch);
+        }
         if (warp < kForwardWarps) {
             Health health(rc, a.error);
             const int fw = blockIdx.x * kForwardWarps + warp, fws = F * kForwardWarps;
@@ -395,10 +407,30 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
         const long long units = entries * units_per_entry;
         const std::uint8_t* y = reinterpret_cast<const std::uint8_t*>(a.y);
         const std::size_t row_bytes = static_cast<std::size_t>(H) * 2;
-        for (long long u = wid; u < units; u += total_warps) {
-            const long long entry_no = u / units_per_entry;
-            const int unit = static_cast<int>(u % units_per_entry);
-            Entry e = locate_entry(a, lay, entry_no, J, me);
+        // Entries are handed out one at a time through a counter (a warp reduces all units of its entry), so that rows
+        // complete in roughly their numbering order -- the order in which the forwarders take them -- and so that
+        // a slow reducer CTA is not left with a fixed share.  A reducer CTA that finds a forwarder on its own SM stops
+        // taking entries: the two would hold each other up on the SM's one path to memory.
+        unsigned long long* completed = nullptr;  // counter of the unit whose stores may still be in flight
+        unsigned my_sm;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(my_sm));
+        int taken = 0, yields = 0;
+        bool shares_sm = false;
+        while (true) {
+            if (F > 0 && !shares_sm && (taken++ & 3) == 0 && my_sm < static_cast<unsigned>(kMaxSmTable))
+                shares_sm = ptx::ld_relaxed_sys(reinterpret_cast<const std::uint64_t*>(a.forwarder_sms + my_sm)) == epoch;
+            if (shares_sm && yields < 128) {
+                // stand aside (a few hundred microseconds at most, then help after all) and leave once every entry is taken
+                ptx::nanosleep(2000);
+                ++yields;
+                if (ptx::ld_relaxed_sys(reinterpret_cast<const std::uint64_t*>(a.next_unit)) >= static_cast<std::uint64_t>(entries)) break;
+                continue;
+            }
+            unsigned long long grabbed = 0;
+            if (lane == 0) grabbed = atomicAdd(a.next_unit, 1ull);
+            grabbed = __shfl_sync(0xffffffffu, grabbed, 0);
+            if (grabbed >= static_cast<unsigned long long>(entries)) break;
+            Entry e = locate_entry(a, lay, static_cast<long long>(grabbed), J, me);
             if (!e.present) continue;
             const int* map = a.comb_map + static_cast<std::size_t>(e.slot) * map_stride;
             e.token = map[0];
@@ -414,10 +446,11 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
                 P == 1 ? reinterpret_cast<std::uint8_t*>(a.out + static_cast<std::size_t>(e.token) * H)
                 : remote ? a.outbox + static_cast<std::size_t>(e.slot) * lay.crow_stride
                          : rc->seg[me] + lay.cstage_off + static_cast<std::size_t>(me) * rank_stride + static_cast<std::size_t>(e.token) * lay.crow_stride;
-            if (lane == 0 && unit == 0) {
+            if (lane == 0) {
                 ++pushed;
                 if (remote) ++pushed_remote;
             }
+            for (int unit = 0; unit < units_per_entry; ++unit) {
             const int q0 = unit * kPushGroupsPerUnit * 32 + lane;  // this lane's chunk in the unit's first group
             float acc[kPushGroupsPerUnit][8];
 #pragma unroll
@@ -437,6 +470,15 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
                     const int q = q0 + g * 32;
                     v0[g] = q < chunks ? ptx::ld_nc_v4(y + static_cast<std::size_t>(r0) * row_bytes + static_cast<std::size_t>(q) * 16) : make_uint4(0u, 0u, 0u, 0u);
                     v1[g] = (two && q < chunks) ? ptx::ld_nc_v4(y + static_cast<std::size_t>(r1) * row_bytes + static_cast<std::size_t>(q) * 16) : make_uint4(0u, 0u, 0u, 0u);
+                }
+                if (completed != nullptr) {
+                    // The previous unit's row went to the outbox: count it as finished now, while this unit's loads
+                    // are on their way (its stores have had a whole unit's time to drain, so the fence is cheap).
+                    if (lane == 0) {
+                        __threadfence();
+                        atomicAdd(completed, 1ull);
+                    }
+                    completed = nullptr;
                 }
 #pragma unroll
                 for (int g = 0; g < kPushGroupsPerUnit; ++g) {
@@ -472,14 +514,16 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
             if (remote) {
                 // The row will be read by a bulk copy (asynchronous proxy) of a forwarder: every lane orders its ordinary
                 // stores against that proxy here, on the writing side -- a proxy fence on a forwarder's SM would wait
-                // behind that SM's stores to peers.  Then the warp joins and one lane counts the unit as finished.
+                // behind that SM's stores to peers.  The warp joins; the unit is counted as finished one unit later.
                 asm volatile("fence.proxy.async.global;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) {
-                    __threadfence();
-                    atomicAdd(a.outbox_units + e.slot, 1ull);
-                }
+                completed = a.outbox_units + e.slot;
             }
+            }  // units of the entry
+        }
+        if (completed != nullptr && lane == 0) {
+            __threadfence();
+            atomicAdd(completed, 1ull);
         }
         if (P == 1) {
             // tokens that were routed nowhere have no map entry: their result is zero
@@ -513,6 +557,7 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
             a.stats[3] = a.stat_scratch[4] ? static_cast<std::int64_t>(a.stat_scratch[4] - first_start) : 0;
             for (int i = 4; i < 8; ++i) a.stats[i] = 0;
             for (int i = 0; i < 5; ++i) a.stat_scratch[i] = i == 2 ? ~0ull : 0ull;
+            *a.next_unit = 0ull;
             if (ptx::ld_volatile(&rc->sticky[0]) == 0) {
                 if (P > 1)
                     for (int p = 0; p < P; ++p) ptx::st_release_sys(flag_ptr(rc->seg[p], lay.csig_off, me), epoch);

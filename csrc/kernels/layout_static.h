@@ -30,6 +30,10 @@
  *   - `status` is an output: 4 ints in device memory, zero on success; status[0] = 2 reports an
  *     invalid route (expert id out of range or repeated within a token; status[1] = token,
  *     status[2] = slot), status[0] = 21 a barrier that did not complete within 2 s.
+ *   - When status[0] != 0 the four plan arrays hold unspecified values (the dispatch kernel never
+ *     uses a plan either once it has seen an invalid route): read `status` before the plan.
+ *   - num_tokens = 0 is a valid request (the counts come out zero; the per-token arrays may then be
+ *     null), and so is num_channels > num_tokens (the surplus channels own no token).
  *   - All pointers are device pointers on the current device; topk_idx is int64 [T][K], contiguous.
  *
  * Return value: 0 on success (the work is enqueued on `stream`), a positive cudaError_t value if a

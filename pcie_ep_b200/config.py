@@ -197,15 +197,25 @@ class HostStagedConfig:
     def tuned(cls, num_ranks: int, num_max_tokens_per_rank: int, **overrides) -> "HostStagedConfig":
         """The settings measured best on 8x B200 for a buffer of this size, with ``overrides`` on top.
 
-        Channels (= CTAs per rank): 32 up to 256 tokens per rank, 64 up to 1024, 128 beyond -- few CTAs keep the
-        grid barrier and the counts exchange short at small T, many keep NVLink and HBM busy at large T.
-        Warps per CTA: ten receive/expand warps; two send warps across NVLink (the link, not the send role, is the
-        limit), four on a single rank, where every row is staged locally and the send role is latency-bound.
+        Channels (= channel CTAs per rank): 32 up to 256 tokens per rank, 64 up to 1024, 128 beyond -- few CTAs keep
+        the grid barrier and the counts exchange short at small T, many keep HBM busy at large T.  Eight
+        receive/expand warps per channel CTA.  Sending: sixteen dedicated sender CTAs of four send warps with three
+        row buffers each once the exchange is bandwidth-bound (more than 512 tokens per rank); below that two send
+        warps inside every channel CTA, which start more rows at once.
         """
         if num_ranks < 1 or num_max_tokens_per_rank < 1:
             raise ValueError("num_ranks and num_max_tokens_per_rank must be positive")
         channels = 32 if num_max_tokens_per_rank <= 256 else 64 if num_max_tokens_per_rank <= 1024 else 128
-        settings = dict(channels=channels, tx_warps=2 if num_ranks == 1 else 4, rx_warps=8, pipeline_stages=3)
+        settings = dict(channels=channels, rx_warps=8, pipeline_stages=3)
+        if num_ranks == 1:
+            settings.update(tx_warps=2, send_ctas=0)      # nothing leaves a single rank
+        elif num_max_tokens_per_rank <= 512:
+            # latency-bound: a few hundred rows per rank never load the link; two send warps inside every channel CTA
+            # start more rows at once than a handful of sender CTAs could
+            settings.update(tx_warps=2, send_ctas=0)
+        else:
+            # bandwidth-bound: all remote stores confined to sixteen sender CTAs of four deeply pipelined warps
+            settings.update(tx_warps=4, send_ctas=16)
         settings.update(overrides)
         return cls(**settings)
 

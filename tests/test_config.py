@@ -77,7 +77,9 @@ def test_tuned_settings_by_size():
     one = HostStagedConfig.tuned(1, 4096)
     assert (one.channels, one.tx_warps, one.rx_warps, one.pipeline_stages) == (128, 2, 8, 3)
     eight = HostStagedConfig.tuned(8, 128, timeout_ms=1234)
-    assert (eight.channels, eight.tx_warps, eight.rx_warps, eight.timeout_ms) == (32, 4, 8, 1234)
+    assert (eight.channels, eight.tx_warps, eight.rx_warps, eight.send_ctas, eight.timeout_ms) == (32, 2, 8, 0, 1234)
+    big = HostStagedConfig.tuned(8, 4096)
+    assert (big.channels, big.tx_warps, big.send_ctas) == (128, 4, 16)
     assert HostStagedConfig.tuned(4, 1024).channels == 64
     assert HostStagedConfig.tuned(2, 4096, channels=16).channels == 16
     import pytest

@@ -86,3 +86,41 @@ def test_static_layout_rejects_oversize_and_bad_arguments(ext):
     null_status[10] = None
     assert fn(*null_status) == -2
     torch.cuda.synchronize()
+
+
+def test_static_layout_reports_invalid_routes_and_handles_edge_sizes(ext):
+    """A repeated or out-of-range expert id is reported through `status` ([2, token, slot, 0]); zero tokens and more
+    channels than tokens are ordinary requests."""
+    _, fn = _entry(ext)
+    experts, ranks, topk, channels, tokens = 16, 2, 4, 4, 9
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def run(idx, tokens, channels):
+        mask = torch.full((max(tokens, 1),), -7, dtype=torch.int32, device="cuda")
+        slot = torch.full((max(tokens, 1), ranks), -7, dtype=torch.int32, device="cuda")
+        order = torch.full((max(tokens, 1), topk), -7, dtype=torch.int32, device="cuda")
+        counts = torch.full((ranks + experts + channels * ranks,), -7, dtype=torch.int32, device="cuda")
+        status = torch.full((4,), -7, dtype=torch.int32, device="cuda")
+        rc = fn(idx.data_ptr() if tokens else None, tokens, topk, experts, ranks, channels,
+                mask.data_ptr() if tokens else None, slot.data_ptr() if tokens else None,
+                order.data_ptr() if tokens else None, counts.data_ptr(), status.data_ptr(), stream)
+        torch.cuda.synchronize()
+        return rc, status.tolist(), counts, mask
+
+    base = torch.stack([torch.randperm(experts)[:topk] for _ in range(tokens)]).to(torch.int64)
+    duplicate = base.clone()
+    duplicate[5, 2] = duplicate[5, 0]
+    rc, status, _, _ = run(duplicate.cuda(), tokens, channels)
+    assert rc == 0 and status == [2, 5, 2, 0]
+    out_of_range = base.clone()
+    out_of_range[7, 1] = experts
+    rc, status, _, _ = run(out_of_range.cuda(), tokens, channels)
+    assert rc == 0 and status == [2, 7, 1, 0]
+    # no tokens at all: per-token arrays may be null, every count is zero
+    rc, status, counts, _ = run(base.cuda(), 0, channels)
+    assert rc == 0 and status == [0, 0, 0, 0] and int(counts.abs().sum()) == 0
+    # more channels than tokens: same totals as with one channel
+    rc_many, status_many, counts_many, mask_many = run(base.cuda(), tokens, 16)
+    rc_one, status_one, counts_one, mask_one = run(base.cuda(), tokens, 1)
+    assert rc_many == 0 and rc_one == 0 and status_many == [0, 0, 0, 0] and status_one == [0, 0, 0, 0]
+    assert torch.equal(counts_many[:ranks + experts], counts_one[:ranks + experts]) and torch.equal(mask_many, mask_one)
