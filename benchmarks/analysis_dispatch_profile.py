@@ -32,7 +32,7 @@ sys.path.insert(0, str(ROOT))
 SYNCHRONISING_CALLS = ("cudaDeviceSynchronize", "cudaStreamSynchronize", "cudaEventSynchronize", "cuStreamSynchronize",
                        "cuCtxSynchronize", "cuEventSynchronize")
 ROLE_FIELDS = ("rows", "total_ns", "load_wait_ns", "store_wait_ns", "credit_wait_ns", "prefix_wait_ns", "idle_poll_ns",
-               "meta_ns", "local_rows", "quant_ns", "issue_ns")
+               "meta_ns", "local_rows", "quant_ns", "issue_ns", "buffer_wait_ns", "first_batch_ns", "first_issue_ns", "drain_ns")
 
 
 def _events(trace: Dict[str, Any], category: str) -> List[Dict[str, Any]]:

@@ -35,10 +35,9 @@ def gather(value):
 
 
 def run_variant(args, fp8, fused, weights, x, idx, w, rank, world, peak) -> None:
-    config = HostStagedConfig(channels=128 if args.tokens > 1024 else 64, timeout_ms=20000, output_pool_size=2,
-                              tx_warps=2, rx_warps=10, stage=7 if fp8 else 6,
-                              wire_dtype="fp8_e4m3" if fp8 else "bf16", recv_dtype="fp8_e4m3" if fp8 else "bf16",
-                              fused_expert_combine=fused)
+    config = HostStagedConfig.tuned(world, args.tokens, timeout_ms=20000, output_pool_size=2, stage=7 if fp8 else 6,
+                                    wire_dtype="fp8_e4m3" if fp8 else "bf16", recv_dtype="fp8_e4m3" if fp8 else "bf16",
+                                    fused_expert_combine=fused)
     with HostStagedEPBuffer(dist.group.WORLD, args.tokens, args.hidden, args.topk, args.experts, config) as buffer:
         layer = MoELayer(buffer, args.intermediate, seed=1, with_router=False, weights=weights)
         for _ in range(args.warmup):

@@ -5,8 +5,8 @@
 
 One rank (world size 1): the kernels never wait for another process, so a profiler may replay them.
 Each iteration is dispatch -> grouped SwiGLU FFN -> combine at the headline shape (hidden 7168,
-256 experts, top-8); NVTX ranges mark the three stages (the reference's profiling driver does the
-same with NVTX + record_function markers, benchmarks/profile_dispatch.py:65-103 there).
+256 experts, top-8); NVTX ranges mark the three stages (parity: the reference's profiling driver,
+benchmarks/profile_dispatch.py, NVTX + record_function markers).
 """
 
 from __future__ import annotations
@@ -42,8 +42,8 @@ def main() -> None:
     args = parser.parse_args()
     torch.cuda.set_device(0)
     dist.init_process_group("gloo", store=dist.FileStore(tempfile.mktemp(prefix="profile-store-"), 1), rank=0, world_size=1)
-    config = HostStagedConfig(channels=args.channels, timeout_ms=20000, output_pool_size=2, tx_warps=2, rx_warps=10,
-                              stage=7, wire_dtype=args.wire)
+    config = HostStagedConfig.tuned(1, args.tokens, channels=args.channels, timeout_ms=20000, output_pool_size=2,
+                                    stage=7, wire_dtype=args.wire)
     idx, w = make_routes(FixtureSpec("uniform", args.tokens, args.experts, args.topk, 1, DEFAULT_SEED), 0)
     idx, w = idx.cuda(), w.cuda()
     x = torch.randn(args.tokens, args.hidden, device="cuda").to(torch.bfloat16)

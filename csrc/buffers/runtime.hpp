@@ -300,7 +300,7 @@ class Runtime {
         epochs_ = at::zeros({4}, i64);
         grid_bar_ = at::zeros({2}, i64);
         done_ctas_ = at::zeros({2}, i64);
-        block_hist_ = at::zeros({static_cast<std::int64_t>(C) * (E + P)}, i32);
+        block_hist_ = at::zeros({static_cast<std::int64_t>(hist_scratch_ints(C, E + P))}, i32);
         sticky_ = at::zeros({8}, i32);
         chan_stats_ = at::zeros({2, C + options_.send_ctas, 10}, i64);
         plan_flags_ = at::zeros({C}, i64);

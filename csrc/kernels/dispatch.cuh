@@ -39,6 +39,41 @@ namespace bep {
 constexpr int kMetaSmemBytes = 16 + 12 * kMaxTopk;
 constexpr int kFlagLag = 2;         // a row's READY flags are released after this many later rows were issued
 
+struct DispatchShared;
+
+// What the roles of one CTA work from.  It lives in shared memory (DispatchShared::ctx), written once before the roles
+// split: as a local variable of the kernel it sat in local memory, and the roles' loads of its fields missed L1 four
+// times out of ten (measured), each a round trip to L2 in the middle of a row.
+struct Ctx {
+    const DispatchArgs* a;
+    const RankConst* rc;
+    DispatchShared* sh;
+    int* eoff;                   // [El+1] aligned offsets of the local experts (valid once prefix_ready)
+    int* spre;                   // [P][El] rows of earlier sources inside each expert segment
+    unsigned char* row_buffers;  // bulk-copy engine: first row buffer
+    int* send_tiles;             // bulk-copy engine: one metadata tile [32][P + 3K] per send warp
+    std::uint8_t* my_seg;
+    std::uint8_t* recv_bytes;
+    std::int64_t* prof;
+    std::int64_t* role_prof;     // [warps][kRoleFields] of this channel (profiling builds), else nullptr
+    std::size_t out_row_bytes;
+    std::uint64_t epoch;
+    int slot_bytes, stages;
+    int P, C, E, El, K, H, Q, Qf, me, c, t0, t1, rx_warps, map_stride;
+    int T, Tc;                         // tokens of this rank, tokens per channel
+    int send_warps;                    // send warps in this CTA
+    int send_first, send_stride;       // channels this CTA's send warps serve: send_first, send_first + send_stride, ... < C
+    int rx_buffer_base;                // index of the first receive warp's row buffer
+    bool vec_ok, use_tma, wire_fp8, recv_fp8, ring;
+    bool plan_is_foreign;              // the send warps read a plan that other CTAs write during this launch
+    bool fence_flags, corrupt_sequence;
+    // copies of what the roles read per row from the rank's constants (those live in global memory)
+    int expanded_cap, unique_cap;
+    std::uint64_t delay_meta_ns, delay_tx_ns, delay_rx_ns, delay_scatter_ns, timeout_ns;
+    std::uint8_t* seg[kMaxRanks];
+    SegmentLayout lay;
+};
+
 struct DispatchShared {
     int cnt_r[kMaxRanks];
     unsigned bits_r[kMaxRanks];
@@ -52,6 +87,8 @@ struct DispatchShared {
     unsigned long long first_tx_ns;
     unsigned long long last_tx_ns;
     unsigned long long mbar[kMaxRowBuffers];
+    unsigned long long prefix_bar;  // the control warp arrives once the receive prefix is settled (prefix_ready says how)
+    Ctx ctx;
     alignas(16) unsigned char meta[kMaxWarps][kMetaSmemBytes];
 };
 
@@ -92,6 +129,10 @@ enum RoleField : int {
     kRoleLocalRows = 8,    // receive: rows taken straight from x
     kRoleQuantNs = 9,      // FP8 conversion in shared memory
     kRoleIssueNs = 10,     // issuing the outgoing copies
+    kRoleBufferWaitNs = 11, // send: waiting for a row buffer's previous row to have left it before it is refilled
+    kRoleFirstBatchNs = 12, // send: role start until the first batch of routing metadata is in shared memory
+    kRoleFirstIssueNs = 13, // send: role start until the first row's copies have been issued
+    kRoleDrainNs = 14,      // send: the final wait for the last rows' copies, up to their flags
     kRoleFields = kRoleFieldCount,
 };
 #if BEP_ENABLE_PROFILING
@@ -99,6 +140,7 @@ enum RoleField : int {
 #define BEP_ROLE_T(var) const unsigned long long var = ptx::globaltimer_ns()
 #define BEP_ROLE_ADD(field, since) role_prof[field] += ptx::globaltimer_ns() - (since)
 #define BEP_ROLE_COUNT(field, n) role_prof[field] += (n)
+#define BEP_ROLE_MARK(field) do { if (role_prof[field] == 0) role_prof[field] = ptx::globaltimer_ns() - role_t_begin; } while (0)
 #define BEP_ROLE_FLUSH(dst)                                                                        \
     do {                                                                                           \
         role_prof[kRoleTotalNs] = ptx::globaltimer_ns() - role_t_begin;                            \
@@ -110,6 +152,7 @@ enum RoleField : int {
 #define BEP_ROLE_T(var) do {} while (0)
 #define BEP_ROLE_ADD(field, since) do {} while (0)
 #define BEP_ROLE_COUNT(field, n) do {} while (0)
+#define BEP_ROLE_MARK(field) do {} while (0)
 #define BEP_ROLE_FLUSH(dst) do {} while (0)
 #endif
 
@@ -336,29 +379,6 @@ __device__ __forceinline__ void bulk_wait_group_read() {
 }
 
 // Values every role of one channel CTA needs; filled once by the kernel.
-struct Ctx {
-    const DispatchArgs* a;
-    const RankConst* rc;
-    DispatchShared* sh;
-    int* eoff;                   // [El+1] aligned offsets of the local experts (valid once prefix_ready)
-    int* spre;                   // [P][El] rows of earlier sources inside each expert segment
-    unsigned char* row_buffers;  // bulk-copy engine: first row buffer
-    int* send_tiles;             // bulk-copy engine: one metadata tile [32][P + 3K] per send warp
-    std::uint8_t* my_seg;
-    std::uint8_t* recv_bytes;
-    std::int64_t* prof;
-    std::int64_t* role_prof;     // [warps][kRoleFields] of this channel (profiling builds), else nullptr
-    std::size_t out_row_bytes;
-    std::uint64_t epoch;
-    int slot_bytes, stages;
-    int P, C, E, El, K, H, Q, Qf, me, c, t0, t1, rx_warps, map_stride;
-    int T, Tc;                         // tokens of this rank, tokens per channel
-    int send_warps;                    // send warps in this CTA
-    int send_first, send_stride;       // channels this CTA's send warps serve: send_first, send_first + send_stride, ... < C
-    int rx_buffer_base;                // index of the first receive warp's row buffer
-    bool vec_ok, use_tma, wire_fp8, recv_fp8, ring;
-    bool plan_is_foreign;              // the send warps read a plan that other CTAs write during this launch
-};
 
 struct RoleStats {
     unsigned long long source = 0, remote_rows = 0, deliveries = 0, early = 0, probes = 0, credit = 0, local = 0,
@@ -394,6 +414,25 @@ __device__ __forceinline__ void write_row_meta(unsigned char* meta, const Segmen
         reinterpret_cast<float*>(meta + 16)[2 * K + lane] = w;
     }
     for (int b = 16 + 12 * K + lane; b < lay.meta_bytes; b += 32) meta[b] = 0;
+}
+
+// Up to eight expert ids of one token into registers: 16-byte read-only loads when the row allows them (the ids are
+// an input of the launch, nothing writes them).  Entries past `left` read as -1.
+__device__ __forceinline__ void load_experts8(const std::int64_t* p, int left, std::int64_t (&e)[8]) {
+    if (left >= 8 && (reinterpret_cast<std::uintptr_t>(p) & 15u) == 0) {
+        const longlong2* p2 = reinterpret_cast<const longlong2*>(p);
+        longlong2 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = __ldg(p2 + u);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            e[2 * u] = v[u].x;
+            e[2 * u + 1] = v[u].y;
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) e[u] = u < left ? __ldg(p + u) : -1;
+    }
 }
 
 __device__ __forceinline__ void load_token_routes(const DispatchArgs& a, int t, int K, int E, int& e, int& ord, float& w) {
@@ -465,7 +504,7 @@ __device__ __forceinline__ bool place_row(const Ctx& k, int s, int j, int token,
         int row = -1;
         if (local) {
             row = k.eoff[el] + k.spre[s * k.El + el] + ord;
-            overflow = row < 0 || row >= k.rc->expanded_cap;
+            overflow = row < 0 || row >= k.expanded_cap;
         }
         // compact: the i-th local slot's row goes to lane i
         for (unsigned lm = lmask, i = 0; lm; lm &= lm - 1, ++i) {
@@ -485,7 +524,7 @@ __device__ __forceinline__ bool place_row(const Ctx& k, int s, int j, int token,
     } else {
         n_rows = 1;
         const int row = k.sh->source_offsets[s] + k.sh->chan_base[s] + j;
-        overflow = row < 0 || row >= k.rc->unique_cap;
+        overflow = row < 0 || row >= k.unique_cap;
         if (lane == 0) out_ptr = k.recv_bytes + static_cast<std::size_t>(row) * k.out_row_bytes;
         if (!overflow) {
             if (k.recv_fp8 && lane == 0) a.recv_scale[row] = scale;
@@ -537,12 +576,16 @@ __device__ __forceinline__ bool place_row(const Ctx& k, int s, int j, int token,
 // with kErrSequence.  The receiver reads the flag with `ld.acquire.sys` and issues `fence.proxy.async` before it
 // reads the row through the asynchronous proxy.  The two-GPU litmus test runs exactly this chain.
 template <int S>
-__device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health, RoleStats& st) {
+__device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& cta_health, RoleStats& cta_stats) {
+    // own copies: the kernel's objects live in local memory, and every access through a reference is a load or store there
+    Health health = cta_health;
+    RoleStats st;
     constexpr int D = S - 1;  // rows whose payload is loaded ahead of the one being sent
     static_assert(S >= 2 && S <= kMaxSendStages, "2..4 send stages");
     const DispatchArgs& a = *k.a;
     const RankConst* rc = k.rc;
-    const SegmentLayout& lay = rc->lay;
+    const SegmentLayout& lay = k.lay;  // the CTA's copy in shared memory
+    const std::uint64_t* const plan_flags = rc->plan_flags;
     const unsigned lane = ptx::lane_id();
     const unsigned full = 0xffffffffu;
     // Every bulk copy of this warp is issued, committed and awaited by lane 31, which never stores a flag
@@ -550,7 +593,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
     const bool issuer = lane == 31u;
     // Segments in registered host memory: completion of a bulk group does not mean its writes have reached host
     // memory (they are posted over PCIe), so there the issuing lane does execute the system-scope fence.
-    const bool fence_flags = rc->fence_flags != 0;
+    const bool fence_flags = k.fence_flags;
     const unsigned self_bit = 1u << k.me;
     const bool delayed = w == k.send_warps - 1;
     const int P = k.P, K = k.K;
@@ -561,7 +604,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
     unsigned long long* const bars = &k.sh->mbar[w * S];
     const int tile_stride = P + 3 * K;  // ints per candidate: slot[P] | expert[K] | ordinal[K] | weight[K]
     int* const tile = k.send_tiles + static_cast<std::size_t>(w) * 32 * tile_stride;
-    const std::uint32_t seq_epoch = static_cast<std::uint32_t>(k.epoch) + (rc->test_corrupt_sequence ? 1u : 0u);
+    const std::uint32_t seq_epoch = static_cast<std::uint32_t>(k.epoch) + (k.corrupt_sequence ? 1u : 0u);
     BEP_ROLE_DECL();
 
     // Candidates of this CTA: the tokens of its channels, interleaved; this warp takes every W-th one.
@@ -589,57 +632,67 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
             my_ch = k.send_first + i * k.send_stride;
             const int t = my_ch * k.Tc + ql / n_ch;
             if (t < k.T) {
+                bool plan_there = true;
                 if (!a.cached && k.plan_is_foreign) {
-                    const std::uint64_t* plan_flag = rc->plan_flags + my_ch;
+                    const std::uint64_t* plan_flag = plan_flags + my_ch;
                     while (ptx::ld_acquire_gpu(plan_flag) != k.epoch) {
-                        if (health.give_up(kErrGridBarrier, my_ch, 1)) break;
+                        if (health.give_up(kErrGridBarrier, my_ch, 1)) {
+                            plan_there = false;
+                            break;
+                        }
                     }
                 }
-                if (!health.failed()) {
-                    my_t = t;
-                    my_mask = a.plan_mask[t] & ~self_bit;
-                }
+                if (plan_there) my_t = t;  // (the caller has looked at the failure latch before asking for a batch)
             }
         }
         __syncwarp();  // the tile's previous contents have been picked up by every lane
-        if (my_mask != 0u) {
+        if (my_t >= 0) {
             int* row = tile + static_cast<int>(lane) * tile_stride;
             const int t = my_t;
-            // eight values at a time: all loads of a group are issued before the first is stored
-            for (int d0 = 0; d0 < P; d0 += 8) {
-                int v[8];
+            // Everything the first eight ranks and the first eight choices need is requested before anything is
+            // used: one round trip to memory per batch, also for the destination mask (slots of ranks the token
+            // does not go to are stored as -1 in the plan, so they need no mask to be read).
+            const unsigned raw_mask = a.plan_mask[t];
+            int slot8[8], ord8[8];
+            std::int64_t e8[8];
+            float w8[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    v[u] = (d0 + u < P && (my_mask >> (d0 + u) & 1u)) ? a.plan_slot[static_cast<std::size_t>(t) * P + d0 + u] : -1;
+            for (int u = 0; u < 8; ++u) slot8[u] = u < P ? a.plan_slot[static_cast<std::size_t>(t) * P + u] : -1;
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    if (d0 + u < P) row[d0 + u] = v[u];
+            for (int u = 0; u < 8; ++u) {
+                const bool in = u < K;
+                const std::size_t at = static_cast<std::size_t>(t) * K + (in ? u : 0);
+                e8[u] = in ? a.topk_idx[at] : -1;
+                ord8[u] = in ? a.plan_expert_ord[at] : -1;
+                w8[u] = (in && a.topk_w) ? a.topk_w[at] : 1.0f;
             }
-            for (int k0 = 0; k0 < K; k0 += 8) {
-                std::int64_t e64[8];
-                int ord[8];
-                float wt[8];
+            my_mask = raw_mask & ~self_bit;
+            if (my_mask != 0u) {
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (u < P) row[u] = (my_mask >> u & 1u) ? slot8[u] : -1;
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    const bool in = k0 + u < K;
-                    const std::size_t at = static_cast<std::size_t>(t) * K + (in ? k0 + u : 0);
-                    e64[u] = in ? a.topk_idx[at] : -1;
-                    ord[u] = in ? a.plan_expert_ord[at] : -1;
-                    wt[u] = (in && a.topk_w) ? a.topk_w[at] : 1.0f;
-                }
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    if (k0 + u < K) {
-                        row[P + k0 + u] = (e64[u] >= 0 && e64[u] < k.E) ? static_cast<int>(e64[u]) : -1;
-                        row[P + K + k0 + u] = ord[u];
-                        row[P + 2 * K + k0 + u] = __float_as_int(wt[u]);
+                    if (u < K) {
+                        row[P + u] = (e8[u] >= 0 && e8[u] < k.E) ? static_cast<int>(e8[u]) : -1;
+                        row[P + K + u] = ord8[u];
+                        row[P + 2 * K + u] = __float_as_int(w8[u]);
                     }
+                }
+                for (int d = 8; d < P; ++d) row[d] = (my_mask >> d & 1u) ? a.plan_slot[static_cast<std::size_t>(t) * P + d] : -1;
+                for (int kk = 8; kk < K; ++kk) {
+                    const std::size_t at = static_cast<std::size_t>(t) * K + kk;
+                    const std::int64_t e = a.topk_idx[at];
+                    row[P + kk] = (e >= 0 && e < k.E) ? static_cast<int>(e) : -1;
+                    row[P + K + kk] = a.plan_expert_ord[at];
+                    row[P + 2 * K + kk] = __float_as_int(a.topk_w ? a.topk_w[at] : 1.0f);
                 }
             }
         }
         __syncwarp();
         todo = __ballot_sync(full, my_mask != 0u);
         BEP_ROLE_ADD(kRoleMetaNs, t_batch);
+        BEP_ROLE_MARK(kRoleFirstBatchNs);
     };
 
     // Next row to send: picks its metadata out of the tile and issues its payload load.
@@ -698,6 +751,13 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
             ahead_ok[i] = ahead_ok[i + 1];
         }
         ahead_ok[D - 1] = ahead_ok[D - 1] ? next_token(ahead[D - 1]) : false;
+#if BEP_ENABLE_PROFILING
+        {   // the issuing lane may sit in next_token's buffer wait: make the warp's wait show up under a name of its own
+            BEP_ROLE_T(t_buffer);
+            __syncwarp();
+            BEP_ROLE_ADD(kRoleBufferWaitNs, t_buffer);
+        }
+#endif
 
         unsigned char* buf = base + static_cast<std::size_t>(n % S) * k.slot_bytes;
         const unsigned parity = static_cast<unsigned>(n / S) & 1u;
@@ -706,8 +766,8 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
         std::uint64_t* ready = nullptr;
         if (cur.j >= 0) {
             const std::size_t ring_index = (static_cast<std::size_t>(k.me) * k.C + cur.ch) * k.Q + (cur.j % k.Q);
-            dst = rc->seg[lane] + lay.stage_off + ring_index * lay.row_stride;
-            ready = reinterpret_cast<std::uint64_t*>(rc->seg[lane] + lay.ready_off) + ring_index;
+            dst = k.seg[lane] + lay.stage_off + ring_index * lay.row_stride;
+            ready = reinterpret_cast<std::uint64_t*>(k.seg[lane] + lay.ready_off) + ring_index;
         }
         if (k.ring) {
             // Bounded rings: slot j % Q is free once the receiver has acknowledged row j - Q.  The receiver only
@@ -751,7 +811,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
             broke = true;
             break;
         }
-        if (delayed) test_delay(rc->delay_meta_ns);
+        if (delayed) test_delay(k.delay_meta_ns);
         // BF16 wire: the metadata lies behind the payload and can be written while the payload is still landing
         if (!k.wire_fp8) write_row_meta(buf + moff, lay, cur.t, 1.0f, seq_epoch, cur.e, cur.ord, cur.w, K);
         BEP_ROLE_T(t_load);
@@ -762,7 +822,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
             break;
         }
         if (lane == 0 && k.sh->first_tx_ns == 0) atomicCAS(&k.sh->first_tx_ns, 0ull, ptx::globaltimer_ns());
-        if (delayed) test_delay(rc->delay_tx_ns);
+        if (delayed) test_delay(k.delay_tx_ns);
         if (k.wire_fp8) {
             BEP_ROLE_T(t_quant);
             const float scale = quantise_row_in_place(buf, k.H);
@@ -778,6 +838,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
         }
         if (issuer) ptx::bulk_commit();
         BEP_ROLE_ADD(kRoleIssueNs, t_issue);
+        BEP_ROLE_MARK(kRoleFirstIssueNs);
         // READY flags of the row issued kFlagLag turns ago: its bulk group is complete by now (or is awaited here)
         if (n >= kFlagLag) {
             BEP_ROLE_T(t_store);
@@ -821,6 +882,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
             if (w == 0 && lane == 0 && n > 0 && n <= kFlagLag) k.prof[kProfFirstTxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
         }
         BEP_ROLE_ADD(kRoleStoreWaitNs, t_store);
+        BEP_ROLE_ADD(kRoleDrainNs, t_store);
     }
     // a failed warp leaves with loads still on their way into its buffers: give them a bounded time to land
     for (int r = n; r < issued; ++r) {
@@ -828,19 +890,24 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, Health& health,
         while (!ptx::mbar_try_wait(reinterpret_cast<std::uint64_t*>(&bars[r % S]), static_cast<unsigned>(r / S) & 1u) && ++polls < (1u << 20))
             ptx::nanosleep(64);
     }
+    cta_stats = st;
     BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(threadIdx.x >> 5) * kRoleFields : nullptr);
 }
 
 // ---- send role, register path (16-byte or scalar accesses; also the path for odd hidden sizes) ----
-__device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& health, RoleStats& st) {
+__device__ __noinline__ void send_role_vector(const Ctx& k, int w, const Health& cta_health, RoleStats& cta_stats) {
+    // own copies: the kernel's objects live in local memory, and every access through a reference is a load or store there
+    Health health = cta_health;
+    RoleStats st;
     const DispatchArgs& a = *k.a;
     const RankConst* rc = k.rc;
-    const SegmentLayout& lay = rc->lay;
+    const SegmentLayout& lay = k.lay;  // the CTA's copy in shared memory
+    const std::uint64_t* const plan_flags = rc->plan_flags;
     const unsigned lane = ptx::lane_id();
     const unsigned self_bit = 1u << k.me;
     const bool delayed = w == k.send_warps - 1;
     unsigned char* meta_sm = k.sh->meta[threadIdx.x >> 5];
-    const std::uint32_t seq_epoch = static_cast<std::uint32_t>(k.epoch) + (rc->test_corrupt_sequence ? 1u : 0u);
+    const std::uint32_t seq_epoch = static_cast<std::uint32_t>(k.epoch) + (k.corrupt_sequence ? 1u : 0u);
     const int moff = k.wire_fp8 ? lay.meta_off_fp8 : lay.meta_off;
     BEP_ROLE_DECL();
     int sent = 0;
@@ -854,7 +921,7 @@ __device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& healt
         if (!a.cached && k.plan_is_foreign) {
             // a dedicated sender reads a plan that the channel's own CTA writes in this launch
             if (lane == 0) {
-                const std::uint64_t* plan_flag = rc->plan_flags + ch;
+                const std::uint64_t* plan_flag = plan_flags + ch;
                 while (ptx::ld_acquire_gpu(plan_flag) != k.epoch) {
                     if (health.give_up(kErrGridBarrier, ch, 1)) break;
                 }
@@ -870,8 +937,8 @@ __device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& healt
         if (lane < static_cast<unsigned>(k.P) && (mask >> lane & 1u)) {
             j = a.plan_slot[static_cast<std::size_t>(t) * k.P + lane];
             const std::size_t ring_index = (static_cast<std::size_t>(k.me) * k.C + ch) * k.Q + (j % k.Q);
-            dst = rc->seg[lane] + lay.stage_off + ring_index * lay.row_stride;
-            ready = reinterpret_cast<std::uint64_t*>(rc->seg[lane] + lay.ready_off) + ring_index;
+            dst = k.seg[lane] + lay.stage_off + ring_index * lay.row_stride;
+            ready = reinterpret_cast<std::uint64_t*>(k.seg[lane] + lay.ready_off) + ring_index;
             if (k.ring && j >= k.Q) {
                 const std::uint64_t* ack = reinterpret_cast<const std::uint64_t*>(k.my_seg + lay.ack_off) +
                                            (static_cast<std::size_t>(lane) * k.C + ch) * k.Q + (j % k.Q);
@@ -887,12 +954,12 @@ __device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& healt
         __syncwarp();
         if (warp_failed(health)) break;
         const std::uint8_t* src = reinterpret_cast<const std::uint8_t*>(a.x + static_cast<std::size_t>(t) * k.H);
-        if (delayed) test_delay(rc->delay_meta_ns);
+        if (delayed) test_delay(k.delay_meta_ns);
         int e, ord;
         float wt;
         load_token_routes(a, t, k.K, k.E, e, ord, wt);
         if (lane == 0 && k.sh->first_tx_ns == 0) atomicCAS(&k.sh->first_tx_ns, 0ull, ptx::globaltimer_ns());
-        if (delayed) test_delay(rc->delay_tx_ns);
+        if (delayed) test_delay(k.delay_tx_ns);
         float scale = 1.0f;
         if (k.wire_fp8) scale = tx_row_fp8(src, dst, mask, -1, k.H, k.vec_ok);
         else tx_row_bf16(src, dst, mask, k.H, k.vec_ok);
@@ -916,6 +983,7 @@ __device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& healt
         BEP_ROLE_COUNT(kRoleRows, 1);
         ++sent;
     }
+    cta_stats = st;
     BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(threadIdx.x >> 5) * kRoleFields : nullptr);
 }
 
@@ -923,10 +991,14 @@ __device__ __noinline__ void send_role_vector(const Ctx& k, int w, Health& healt
 // Remote rows: poll the READY flags of this channel's rings (local memory), read a staged row once, check its
 // sequence words, write it to its output rows.  Own rows: whenever no remote row is waiting, take the next own
 // token that has a local expert straight from `x`.
-__device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, RoleStats& st) {
+__device__ __noinline__ void receive_role(const Ctx& k, int w, const Health& cta_health, RoleStats& cta_stats) {
+    // own copies: the kernel's objects live in local memory, and every access through a reference is a load or store there
+    Health health = cta_health;
+    RoleStats st;
     const DispatchArgs& a = *k.a;
     const RankConst* rc = k.rc;
-    const SegmentLayout& lay = rc->lay;
+    const SegmentLayout& lay = k.lay;  // the CTA's copy in shared memory
+    const std::uint64_t* const plan_flags = rc->plan_flags;
     const unsigned lane = ptx::lane_id();
     const unsigned full = 0xffffffffu;
     const bool delayed = w == k.rx_warps - 1;
@@ -934,10 +1006,12 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, R
     BEP_ROLE_DECL();
     // The control warp owns the diagnosis of a missing counts message (it knows which source is late); this
     // wait only has to end, so its own deadline is a quarter of the timeout later.
-    health.deadline += rc->timeout_ns / 4;
+    health.deadline += k.timeout_ns / 4;
     {
+        // The wait sits on an mbarrier: a waiting warp is suspended by the hardware instead of taking issue slots from
+        // the control warp that it is waiting for.
         BEP_ROLE_T(t_prefix);
-        while (*reinterpret_cast<volatile int*>(&k.sh->prefix_ready) == 0) {
+        while (!ptx::mbar_try_wait(reinterpret_cast<std::uint64_t*>(&k.sh->prefix_bar), 0u)) {
             if (warp_give_up(health, kErrCountsWait, -1, 0)) break;
         }
         BEP_ROLE_ADD(kRolePrefixWaitNs, t_prefix);
@@ -1006,7 +1080,7 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, R
                         if (lane == 0) record_error(rc, a.error, kErrCapacity, me, j);
                         break;
                     }
-                    if (delayed) test_delay(rc->delay_scatter_ns);
+                    if (delayed) test_delay(k.delay_scatter_ns);
                     for (int i = 0; i < n_rows; ++i) {
                         std::uint8_t* dst = shfl_ptr(out_ptr, i);
                         if (lane == 0) ptx::bulk_s2g(dst, my_slot, static_cast<unsigned>(k.out_row_bytes));
@@ -1019,7 +1093,7 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, R
                         if (lane == 0) record_error(rc, a.error, kErrCapacity, me, j);
                         break;
                     }
-                    if (delayed) test_delay(rc->delay_scatter_ns);
+                    if (delayed) test_delay(k.delay_scatter_ns);
                     if (k.recv_fp8) tx_row_fp8(src, out_ptr, n_rows >= 32 ? full : (1u << n_rows) - 1u, -1, H, k.vec_ok);
                     else rx_row_scatter(src, false, 1.0f, out_ptr, n_rows, H, k.vec_ok);
                 }
@@ -1044,7 +1118,7 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, R
                 const std::size_t ring_index = (static_cast<std::size_t>(s) * C + c) * Q + (j % Q);
                 const std::uint8_t* row_src = k.my_seg + lay.stage_off + ring_index * lay.row_stride;
                 const int moff = fp8row ? lay.meta_off_fp8 : lay.meta_off;
-                if (delayed) test_delay(rc->delay_rx_ns);
+                if (delayed) test_delay(k.delay_rx_ns);
                 const unsigned char* meta;
                 if (k.use_tma) {
                     ptx::fence_proxy_async();
@@ -1115,8 +1189,8 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, R
                     stop = true;
                     break;
                 }
-                if (delayed) test_delay(rc->delay_scatter_ns);
-                std::uint64_t* ack = reinterpret_cast<std::uint64_t*>(rc->seg[s] + lay.ack_off) +
+                if (delayed) test_delay(k.delay_scatter_ns);
+                std::uint64_t* ack = reinterpret_cast<std::uint64_t*>(k.seg[s] + lay.ack_off) +
                                      (static_cast<std::size_t>(me) * C + c) * Q + (j % Q);
                 if (!k.use_tma) {
                     if (k.recv_fp8) rx_row_copy_bytes(row_src, out_ptr, n_rows, H);
@@ -1160,6 +1234,7 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, Health& health, R
         }
         if (w == 0 && lane == 0) k.prof[kProfRxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
     }
+    cta_stats = st;
     BEP_ROLE_FLUSH(k.role_prof ? k.role_prof + static_cast<std::size_t>(threadIdx.x >> 5) * kRoleFields : nullptr);
 }
 
@@ -1208,6 +1283,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     std::uint8_t* my_seg = rc->seg[me];
     std::int64_t* prof = a.profile + static_cast<std::size_t>(c) * 16;
 #define BEP_PROF(point) prof[point] = static_cast<std::int64_t>(ptx::globaltimer_ns())
+#if BEP_ENABLE_PROFILING
+    // instrumented build: finer marks of the layout and prefix phases, in the (otherwise unused) counters of the control warp
+    std::int64_t* const layout_marks = a.role_profile ? a.role_profile + static_cast<std::size_t>(c) * kMaxWarps * kRoleFields : nullptr;
+#define BEP_LAYOUT_MARK(i) do { if (layout_marks) layout_marks[i] = static_cast<std::int64_t>(ptx::globaltimer_ns() - t_start); } while (0)
+#else
+#define BEP_LAYOUT_MARK(i) do {} while (0)
+#endif
 
     // ---- launch-wide preconditions ---------------------------------------------------------------
     if (ptx::ld_volatile(&rc->sticky[0]) != 0) {
@@ -1224,10 +1306,59 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         sh->prefix_ready = 0;
         sh->first_tx_ns = 0;
         sh->last_tx_ns = 0;
-        if (use_tma) {
-            for (int b = 0; b < kMaxRowBuffers; ++b) ptx::mbar_init(reinterpret_cast<std::uint64_t*>(&sh->mbar[b]), 1);
-            ptx::mbar_fence_init();
+        ptx::mbar_init(reinterpret_cast<std::uint64_t*>(&sh->prefix_bar), 1);
+        ptx::mbar_fence_init();
+    }
+    // one mbarrier per row buffer, each set up by a thread of its own (every path below joins the CTA before the roles split)
+    if (use_tma && static_cast<int>(threadIdx.x) < dispatch_row_buffer_count(tx_warps, rx_warps, rc->send_stages, S)) {
+        ptx::mbar_init(reinterpret_cast<std::uint64_t*>(&sh->mbar[threadIdx.x]), 1);
+        ptx::mbar_fence_init();
+    }
+    // ---- the roles' context, in shared memory (the last thread writes it while the others start on the layout; every path joins the CTA before the roles split) ----------------
+    Ctx& k = sh->ctx;
+    if (threadIdx.x == blockDim.x - 1) {
+        k.a = &a;
+        k.rc = rc;
+        k.sh = sh;
+        k.eoff = eoff;
+        k.spre = spre;
+        k.row_buffers = smem_raw + slots_at;
+        k.send_tiles = reinterpret_cast<int*>(smem_raw + slots_at + static_cast<std::size_t>(dispatch_row_buffer_count(tx_warps, rx_warps, rc->send_stages, S)) *
+                                                                    static_cast<std::size_t>(align_up(lay.meta_off + lay.meta_bytes, 128)));
+        k.my_seg = my_seg;
+        k.recv_bytes = recv_bytes;
+        k.prof = prof;
+        k.role_prof = a.role_profile ? a.role_profile + static_cast<std::size_t>(c) * kMaxWarps * kRoleFields : nullptr;
+        k.out_row_bytes = out_row_bytes;
+        k.epoch = epoch;
+        k.slot_bytes = static_cast<int>(align_up(lay.meta_off + lay.meta_bytes, 128));
+        k.stages = rc->send_stages;
+        k.P = P; k.C = C; k.E = E; k.El = El; k.K = K; k.H = H; k.Q = lay.slots; k.Qf = lay.slots_full;
+        k.me = me; k.c = c; k.t0 = t0; k.t1 = t1; k.rx_warps = rx_warps;
+        k.T = T; k.Tc = Tc;
+        if (is_sender) {
+            k.send_warps = tx_warps; k.send_first = c - C; k.send_stride = S;
+        } else if (S == 0) {
+            k.send_warps = tx_warps; k.send_first = c; k.send_stride = C;
+        } else {
+            k.send_warps = 0; k.send_first = C; k.send_stride = C;
         }
+        k.rx_buffer_base = S == 0 ? tx_warps * rc->send_stages : 0;
+        k.plan_is_foreign = is_sender;
+        k.map_stride = 2 + 2 * K;
+        k.vec_ok = vec_ok; k.use_tma = use_tma; k.wire_fp8 = rc->wire_fp8 != 0; k.recv_fp8 = recv_fp8;
+        k.ring = rc->ring_mode != 0;
+        k.fence_flags = rc->fence_flags != 0;
+        k.corrupt_sequence = rc->test_corrupt_sequence != 0;
+        k.expanded_cap = rc->expanded_cap;
+        k.unique_cap = rc->unique_cap;
+        k.delay_meta_ns = rc->delay_meta_ns;
+        k.delay_tx_ns = rc->delay_tx_ns;
+        k.delay_rx_ns = rc->delay_rx_ns;
+        k.delay_scatter_ns = rc->delay_scatter_ns;
+        k.timeout_ns = rc->timeout_ns;
+        for (int p = 0; p < kMaxRanks; ++p) k.seg[p] = p < P ? rc->seg[p] : nullptr;
+        k.lay = lay;
     }
     const unsigned long long t_start = ptx::globaltimer_ns();
     if (threadIdx.x == 0) {
@@ -1256,6 +1387,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         // a sender has no tokens of its own to lay out; it only takes part in the grid barrier
         if (!a.cached) grid_barrier(&rc->grid_bar[0], health);
     } else if (!a.cached) {
+        // which copy of the running sums this layout uses (asked for now, needed after the histogram)
+        const int generation = __ldcg(rc->block_hist + static_cast<std::size_t>(C) * (E + P) +
+                                      static_cast<std::size_t>(2) * ((C + kHistGroup - 1) / kHistGroup + 1) * (E + P));
         for (int i = threadIdx.x; i < E; i += blockDim.x) {
             cnt_e[i] = 0;
             bits_e[i] = 0;
@@ -1265,37 +1399,81 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             sh->bits_r[threadIdx.x] = 0;
         }
         __syncthreads();
+        if (threadIdx.x == 0) BEP_LAYOUT_MARK(0);
         for (int t = t0 + threadIdx.x; t < t1; t += blockDim.x) {
             unsigned mask = 0;
             const std::int64_t* row = a.topk_idx + static_cast<std::size_t>(t) * K;
-            for (int k = 0; k < K; ++k) {
-                const std::int64_t e = row[k];
-                if (e == -1) continue;
-                bool bad = e < -1 || e >= E;
-                for (int k2 = 0; k2 < k && !bad; ++k2) bad = row[k2] == e;
-                if (bad) {
-                    record_error(rc, a.error, kErrInvalidRouting, t, k);
-                    continue;
+            for (int k0 = 0; k0 < K; k0 += 8) {
+                std::int64_t e8[8];
+                load_experts8(row + k0, K - k0, e8);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int k = k0 + u;
+                    const std::int64_t e = e8[u];
+                    if (k >= K || e == -1) continue;
+                    bool bad = e < -1 || e >= E;
+#pragma unroll
+                    for (int u2 = 0; u2 < u; ++u2) bad = bad || e8[u2] == e;
+                    for (int k2 = 0; k2 < k0 && !bad; ++k2) bad = row[k2] == e;
+                    if (bad) {
+                        record_error(rc, a.error, kErrInvalidRouting, t, k);
+                        continue;
+                    }
+                    mask |= 1u << (static_cast<int>(e) / El);
+                    atomicAdd(&cnt_e[e], 1);
                 }
-                mask |= 1u << static_cast<int>(e / El);
-                atomicAdd(&cnt_e[e], 1);
             }
             a.plan_mask[t] = mask;
             for (unsigned m = mask; m; m &= m - 1) atomicAdd(&sh->cnt_r[__ffs(m) - 1], 1);
         }
+        if (threadIdx.x == 0) BEP_LAYOUT_MARK(1);
         __syncthreads();
-        int* hist = rc->block_hist + static_cast<std::size_t>(c) * (E + P);
-        for (int i = threadIdx.x; i < E + P; i += blockDim.x) hist[i] = i < E ? cnt_e[i] : sh->cnt_r[i - E];
+        if (threadIdx.x == 0) BEP_LAYOUT_MARK(2);
+        // Every CTA needs, per bin, the sum over the channels before it and the sum over all channels.  Reading all C
+        // rows in every CTA makes the whole grid read the same lines at the same time, and those few L2 slices set
+        // the pace.  So the counts are also added (fire-and-forget reductions) to a sum per group of kHistGroup channels
+        // and to a grand total before the barrier; after it a CTA reads the grand total, the sums of the groups before
+        // its own and the rows of the channels before it inside its group: 1 + C / kHistGroup + kHistGroup rows at most.
+        const int W = E + P;
+        const int groups = (C + kHistGroup - 1) / kHistGroup;
+        int* const hist_rows = rc->block_hist;  // [C][W]
+        int* const sums_base = rc->block_hist + static_cast<std::size_t>(C) * W;  // [2][groups + 1][W], then the generation
+        // the sums are used alternately: this launch adds to one copy and clears the other for the next layout
+        int* const sums = sums_base + static_cast<std::size_t>(generation & 1) * (groups + 1) * W;
+        int* const sums_next = sums_base + static_cast<std::size_t>((generation + 1) & 1) * (groups + 1) * W;
+        for (int i = threadIdx.x; i < W; i += blockDim.x) {
+            const int v = i < E ? cnt_e[i] : sh->cnt_r[i - E];
+            hist_rows[static_cast<std::size_t>(c) * W + i] = v;
+            if (v != 0) {
+                atomicAdd(sums + static_cast<std::size_t>(c / kHistGroup) * W + i, v);
+                atomicAdd(sums + static_cast<std::size_t>(groups) * W + i, v);
+            }
+        }
+        for (int i = c * static_cast<int>(blockDim.x) + threadIdx.x; i < (groups + 1) * W; i += C * static_cast<int>(blockDim.x)) sums_next[i] = 0;
         if (threadIdx.x == 0) BEP_PROF(kProfHistDone);
         grid_barrier(&rc->grid_bar[0], health);
         if (threadIdx.x == 0) BEP_PROF(kProfBarrierDone);
         // exclusive prefix over earlier channels (stable order = channel order = token order)
-        for (int i = threadIdx.x; i < E + P; i += blockDim.x) {
-            int base = 0, total = 0;
-            for (int c2 = 0; c2 < C; ++c2) {
-                const int v = __ldcg(rc->block_hist + static_cast<std::size_t>(c2) * (E + P) + i);
-                total += v;
-                if (c2 < c) base += v;
+        for (int i = threadIdx.x; i < W; i += blockDim.x) {
+            const int my_group = c / kHistGroup;
+            int base = 0;
+            const int total = __ldcg(sums + static_cast<std::size_t>(groups) * W + i);
+            for (int g0 = 0; g0 < my_group; g0 += 8) {
+                int v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = g0 + u < my_group ? __ldcg(sums + static_cast<std::size_t>(g0 + u) * W + i) : 0;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) base += v[u];
+            }
+            {
+                int v[kHistGroup];
+#pragma unroll
+                for (int u = 0; u < kHistGroup; ++u) {
+                    const int c2 = my_group * kHistGroup + u;
+                    v[u] = c2 < c ? __ldcg(hist_rows + static_cast<std::size_t>(c2) * W + i) : 0;
+                }
+#pragma unroll
+                for (int u = 0; u < kHistGroup; ++u) base += v[u];
             }
             if (i < E) {
                 cnt_e[i] = base;
@@ -1305,6 +1483,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                 sh->total_r[i - E] = total;
             }
         }
+        if (threadIdx.x == 0) BEP_LAYOUT_MARK(3);
         __syncthreads();
         if (threadIdx.x == 0) BEP_PROF(kProfPrefixScan);
         if (c == 0) {  // keep the totals with the plan so a cached dispatch can skip all of the above
@@ -1345,30 +1524,76 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         for (int base_t = t0; base_t < t1; base_t += 32) {
             const int t = base_t + lane;
             const bool active = t < t1;
-            const unsigned mask = active ? a.plan_mask[t] : 0u;
             const std::int64_t* row = a.topk_idx + static_cast<std::size_t>(active ? t : 0) * K;
-            for (int k = 0; k < K; ++k) {
-                const std::int64_t e = active ? row[k] : -1;
-                if (e >= 0 && e < E) atomicOr(&bits_e[e], 1u << lane);
+            // The ids of the first eight choices are loaded once and stay in registers for all four passes; further
+            // choices (top-k above 8) are read again in every pass.  The destination mask is rebuilt from the ids
+            // (entries the histogram refused are refused here as well: a launch with such an entry has failed
+            // already and its plan is never used).
+            if (lane == 0) BEP_LAYOUT_MARK(4);
+            std::int64_t first8[8];
+            load_experts8(row, active ? K : 0, first8);
+            auto ids_of_group = [&](int k0, std::int64_t (&e8)[8]) {
+                if (k0 == 0) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) e8[u] = first8[u];
+                } else {
+                    load_experts8(row + k0, active ? K - k0 : 0, e8);
+                }
+            };
+            unsigned mask = 0;
+            for (int k0 = 0; k0 < K; k0 += 8) {
+                std::int64_t e8[8];
+                ids_of_group(k0, e8);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const std::int64_t e = e8[u];
+                    if (e >= 0 && e < E) {
+                        atomicOr(&bits_e[e], 1u << lane);
+                        mask |= 1u << (static_cast<int>(e) / El);
+                    }
+                }
             }
             for (unsigned m = mask; m; m &= m - 1) atomicOr(&sh->bits_r[__ffs(m) - 1], 1u << lane);
             __syncwarp();
-            if (active) {
-                for (int k = 0; k < K; ++k) {
-                    const std::int64_t e = row[k];
-                    a.plan_expert_ord[static_cast<std::size_t>(t) * K + k] =
-                        (e >= 0 && e < E) ? cnt_e[e] + __popc(bits_e[e] & lt_mask) : -1;
+            if (lane == 0) BEP_LAYOUT_MARK(5);
+            for (int k0 = 0; k0 < K; k0 += 8) {
+                std::int64_t e8[8];
+                ids_of_group(k0, e8);
+                int ord8[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const std::int64_t e = e8[u];
+                    ord8[u] = (e >= 0 && e < E) ? cnt_e[e] + __popc(bits_e[e] & lt_mask) : -1;
                 }
+                if (active) {
+                    int* out = a.plan_expert_ord + static_cast<std::size_t>(t) * K + k0;
+                    if (K - k0 >= 8 && (reinterpret_cast<std::uintptr_t>(out) & 15u) == 0) {
+                        reinterpret_cast<int4*>(out)[0] = make_int4(ord8[0], ord8[1], ord8[2], ord8[3]);
+                        reinterpret_cast<int4*>(out)[1] = make_int4(ord8[4], ord8[5], ord8[6], ord8[7]);
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            if (k0 + u < K) out[u] = ord8[u];
+                    }
+                }
+            }
+            if (active) {
                 for (int d = 0; d < P; ++d)
                     a.plan_slot[static_cast<std::size_t>(t) * P + d] =
                         (mask >> d & 1u) ? sh->cnt_r[d] + __popc(sh->bits_r[d] & lt_mask) : -1;
             }
             __syncwarp();
-            for (int k = 0; k < K; ++k) {
-                const std::int64_t e = active ? row[k] : -1;
-                if (e >= 0 && e < E) {
-                    const unsigned b = bits_e[e];
-                    if (lane == 31u - __clz(b)) cnt_e[e] += __popc(b);
+            if (lane == 0) BEP_LAYOUT_MARK(6);
+            for (int k0 = 0; k0 < K; k0 += 8) {
+                std::int64_t e8[8];
+                ids_of_group(k0, e8);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const std::int64_t e = e8[u];
+                    if (e >= 0 && e < E) {
+                        const unsigned b = bits_e[e];
+                        if (lane == 31u - __clz(b)) cnt_e[e] += __popc(b);
+                    }
                 }
             }
             for (unsigned m = mask; m; m &= m - 1) {
@@ -1377,9 +1602,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                 if (lane == 31u - __clz(b)) sh->cnt_r[d] += __popc(b);
             }
             __syncwarp();
-            for (int k = 0; k < K; ++k) {
-                const std::int64_t e = active ? row[k] : -1;
-                if (e >= 0 && e < E) bits_e[e] = 0;
+            if (lane == 0) BEP_LAYOUT_MARK(7);
+            for (int k0 = 0; k0 < K; k0 += 8) {
+                std::int64_t e8[8];
+                ids_of_group(k0, e8);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const std::int64_t e = e8[u];
+                    if (e >= 0 && e < E) bits_e[e] = 0;
+                }
             }
             for (unsigned m = mask; m; m &= m - 1) sh->bits_r[__ffs(m) - 1] = 0;
             __syncwarp();
@@ -1398,38 +1629,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     if (threadIdx.x == 0) BEP_PROF(kProfRolesSplit);
 
     // ---- role split ------------------------------------------------------------------------------
-    Ctx k;
-    k.a = &a;
-    k.rc = rc;
-    k.sh = sh;
-    k.eoff = eoff;
-    k.spre = spre;
-    k.row_buffers = smem_raw + slots_at;
-    k.send_tiles = reinterpret_cast<int*>(smem_raw + slots_at + static_cast<std::size_t>(dispatch_row_buffer_count(tx_warps, rx_warps, rc->send_stages, S)) *
-                                                                static_cast<std::size_t>(align_up(lay.meta_off + lay.meta_bytes, 128)));
-    k.my_seg = my_seg;
-    k.recv_bytes = recv_bytes;
-    k.prof = prof;
-    k.role_prof = a.role_profile ? a.role_profile + static_cast<std::size_t>(c) * kMaxWarps * kRoleFields : nullptr;
-    k.out_row_bytes = out_row_bytes;
-    k.epoch = epoch;
-    k.slot_bytes = static_cast<int>(align_up(lay.meta_off + lay.meta_bytes, 128));
-    k.stages = rc->send_stages;
-    k.P = P; k.C = C; k.E = E; k.El = El; k.K = K; k.H = H; k.Q = lay.slots; k.Qf = lay.slots_full;
-    k.me = me; k.c = c; k.t0 = t0; k.t1 = t1; k.rx_warps = rx_warps;
-    k.T = T; k.Tc = Tc;
-    if (is_sender) {
-        k.send_warps = tx_warps; k.send_first = c - C; k.send_stride = S;
-    } else if (S == 0) {
-        k.send_warps = tx_warps; k.send_first = c; k.send_stride = C;
-    } else {
-        k.send_warps = 0; k.send_first = C; k.send_stride = C;
-    }
-    k.rx_buffer_base = S == 0 ? tx_warps * rc->send_stages : 0;
-    k.plan_is_foreign = is_sender;
-    k.map_stride = 2 + 2 * K;
-    k.vec_ok = vec_ok; k.use_tma = use_tma; k.wire_fp8 = rc->wire_fp8 != 0; k.recv_fp8 = recv_fp8;
-    k.ring = rc->ring_mode != 0;
     RoleStats st;
 
     if (is_sender) {
@@ -1452,24 +1651,47 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             if (lane == 0) record_error(rc, a.error, kErrInjectedAbort, me, 0);
             __syncwarp();
         }
+        // what the prefix needs from the rank's constants is read while the counts are still on their way
+        const int expanded_cap = rc->expanded_cap, unique_cap = rc->unique_cap;
+        const std::uint64_t delay_prefix_ns = rc->delay_prefix_ns;
+        bool gave_up = false;
         if (lane < static_cast<unsigned>(P)) {
             const std::uint64_t* flag = flag_ptr(my_seg, lay.counts_flag_off, lane);
             while (ptx::ld_acquire_sys(flag) != epoch) {
-                if (health.give_up(kErrCountsWait, lane, 0)) break;
+                if (health.give_up(kErrCountsWait, lane, 0)) {
+                    gave_up = true;
+                    break;
+                }
             }
         }
         __syncwarp();
         if (lane == 0) BEP_PROF(kProfCountsArrived);
-        test_delay(rc->delay_prefix_ns);
-        const bool bad = warp_failed(health);
+        test_delay(delay_prefix_ns);
+        // (a wait that ended without its flag has latched the failure; the latch itself is looked at again below)
+        const bool bad = __any_sync(full, gave_up) != 0;
         if (!bad) {
             const int stride = lay.counts_stride;
             {   // bring all P messages into shared memory with wide, independent loads
                 const uint4* g = reinterpret_cast<const uint4*>(my_seg + lay.counts_off);
                 uint4* d4 = reinterpret_cast<uint4*>(msg_sm);
-                for (int i = lane; i < P * stride / 4; i += 32) d4[i] = ptx::ld_v4(g + i);
+                const int n4 = P * stride / 4;
+                // eight loads per lane on their way before the first is stored: one round trip per 4 KB, not per 512 bytes
+                for (int i0 = 0; i0 < n4; i0 += 256) {
+                    uint4 v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int i = i0 + u * 32 + static_cast<int>(lane);
+                        v[u] = i < n4 ? ptx::ld_v4(g + i) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int i = i0 + u * 32 + static_cast<int>(lane);
+                        if (i < n4) d4[i] = v[u];
+                    }
+                }
             }
             __syncwarp();
+            if (lane == 0) BEP_LAYOUT_MARK(8);
             const int* msg = msg_sm;
             for (int el = lane; el < El; el += 32) {
                 int run = 0;
@@ -1501,6 +1723,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                 true_total += __shfl_sync(full, tsum, 31);
             }
             if (lane == 0) eoff[El] = carry;
+            if (lane == 0) BEP_LAYOUT_MARK(9);
             // unique layout: rows grouped by source rank
             const int from = lane < static_cast<unsigned>(P) ? msg[lane * stride + me] : 0;
             int incl = from;
@@ -1520,7 +1743,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                 sh->chan_expected[lane] = chan[c];
                 a.recv_chan_counts[lane * C + c] = sh->chan_expected[lane];
             }
-            if (carry > rc->expanded_cap || unique_total > rc->unique_cap) {
+            if (lane == 0) BEP_LAYOUT_MARK(10);
+            if (carry > expanded_cap || unique_total > unique_cap) {
                 if (lane == 0) record_error(rc, a.error, kErrCapacity, carry, unique_total);
             }
             __syncwarp();
@@ -1544,6 +1768,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
             __syncwarp();
             if (lane == 0) {
                 *reinterpret_cast<volatile int*>(&sh->prefix_ready) = 1;
+                ptx::mbar_arrive(reinterpret_cast<std::uint64_t*>(&sh->prefix_bar));
                 BEP_PROF(kProfPrefixReady);
             }
             // zero padding between expert segments: channel c takes local experts c, c+C, ...
@@ -1564,6 +1789,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
                     }
                 }
             }
+        } else if (lane == 0) {
+            // no prefix: release the receive warps all the same (prefix_ready stays 0 and tells them to leave)
+            ptx::mbar_arrive(reinterpret_cast<std::uint64_t*>(&sh->prefix_bar));
         }
     } else if (S == 0 && warp <= tx_warps) {
         // ===== send (inside the channel CTA) =====
@@ -1594,40 +1822,72 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
         atomicAdd(&sh->stat[kStatRowsPublished], st.published);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned long long t_end = ptx::globaltimer_ns();
-        prof[kProfEnd] = static_cast<std::int64_t>(t_end);
-        std::int64_t* cs = rc->chan_stats + static_cast<std::size_t>(c) * 10;
-        for (int i = 0; i < 8; ++i) cs[i] = static_cast<std::int64_t>(sh->stat[i]);
-        cs[8] = static_cast<std::int64_t>(t_start);
-        cs[9] = static_cast<std::int64_t>(t_end);
-        a.prefix_tx_ts[(c + 1) * 2 + 0] = static_cast<std::int64_t>(sh->first_tx_ns);
-        a.prefix_tx_ts[(c + 1) * 2 + 1] = static_cast<std::int64_t>(sh->last_tx_ns);
-        __threadfence();
-        const unsigned long long old = atomicAdd(&rc->done_ctas[0], 1ull);
+    if (warp == 0) {
+        unsigned long long old = 0;
+        if (lane == 0) {
+            const unsigned long long t_end = ptx::globaltimer_ns();
+            prof[kProfEnd] = static_cast<std::int64_t>(t_end);
+            std::int64_t* cs = rc->chan_stats + static_cast<std::size_t>(c) * 10;
+            for (int i = 0; i < 8; ++i) cs[i] = static_cast<std::int64_t>(sh->stat[i]);
+            cs[8] = static_cast<std::int64_t>(t_start);
+            cs[9] = static_cast<std::int64_t>(t_end);
+            a.prefix_tx_ts[(c + 1) * 2 + 0] = static_cast<std::int64_t>(sh->first_tx_ns);
+            a.prefix_tx_ts[(c + 1) * 2 + 1] = static_cast<std::int64_t>(sh->last_tx_ns);
+            __threadfence();
+            old = atomicAdd(&rc->done_ctas[0], 1ull);
+        }
+        old = __shfl_sync(full, old, 0);
         if ((old + 1) % static_cast<unsigned long long>(gridDim.x) == 0) {
-            // last CTA of this rank: sum the per-CTA statistics, hand the staging area back to every
-            // source, advance the epoch
+            // last CTA of this rank: sum the per-CTA statistics (a lane per CTA, then across the warp), hand the
+            // staging area back to every source, advance the epoch
             __threadfence();
             std::int64_t sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             std::int64_t first = INT64_MAX, last = 0;
-            for (int c2 = 0; c2 < static_cast<int>(gridDim.x); ++c2) {
+            for (int c2 = lane; c2 < static_cast<int>(gridDim.x); c2 += 32) {
                 const std::int64_t* o = rc->chan_stats + static_cast<std::size_t>(c2) * 10;
-                for (int i = 0; i < 8; ++i) sum[i] += __ldcg(o + i);
-                first = min(first, __ldcg(o + 8));
-                last = max(last, __ldcg(o + 9));
+                std::int64_t v[10];
+#pragma unroll
+                for (int i = 0; i < 10; ++i) v[i] = __ldcg(o + i);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum[i] += v[i];
+                first = min(first, v[8]);
+                last = max(last, v[9]);
             }
-            for (int i = 0; i < 8; ++i) a.stats[i] = sum[i];
-            a.timestamps[0] = first;
-            a.timestamps[1] = last;
-            if (!health.failed()) {
-                for (int p = 0; p < P; ++p)
-                    if (p != rc->test_skip_done_to) ptx::st_release_sys(flag_ptr(rc->seg[p], lay.done_off, me), epoch);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum[i] += __shfl_xor_sync(full, sum[i], o);
+                first = min(first, __shfl_xor_sync(full, first, o));
+                last = max(last, __shfl_xor_sync(full, last, o));
             }
-            rc->epochs[0] = epoch;
+            if (lane < 8) {
+                std::int64_t mine = sum[0];
+#pragma unroll
+                for (int i = 1; i < 8; ++i)
+                    if (static_cast<int>(lane) == i) mine = sum[i];
+                a.stats[lane] = mine;
+            }
+            if (lane == 0) {
+                a.timestamps[0] = first;
+                a.timestamps[1] = last;
+            }
+            if (!warp_failed(health)) {
+                // one system fence orders every store of this CTA's epilogue; the P flags then go out side by side
+                if (lane < static_cast<unsigned>(P) && static_cast<int>(lane) != rc->test_skip_done_to)
+                    ptx::st_release_sys(flag_ptr(rc->seg[lane], lay.done_off, me), epoch);
+            }
+            __syncwarp();
+            if (lane == 0) {
+                rc->epochs[0] = epoch;
+                if (!a.cached) {  // the layout's running sums change sides (see the layout phase)
+                    const int groups = (C + kHistGroup - 1) / kHistGroup;
+                    rc->block_hist[static_cast<std::size_t>(C) * (E + P) + static_cast<std::size_t>(2) * (groups + 1) * (E + P)] += 1;
+                }
+            }
         }
     }
 #undef BEP_PROF
+#undef BEP_LAYOUT_MARK
 }
 
 #endif  // __CUDACC__

@@ -404,13 +404,18 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
         // ---- reduce ----------------------------------------------------------------------------------------
         const long long total_warps = static_cast<long long>(gridDim.x - F) * warps;
         const long long wid = static_cast<long long>(blockIdx.x - F) * warps + warp;
-        const long long units = entries * units_per_entry;
         const std::uint8_t* y = reinterpret_cast<const std::uint8_t*>(a.y);
         const std::size_t row_bytes = static_cast<std::size_t>(H) * 2;
         // Entries are handed out one at a time through a counter (a warp reduces all units of its entry), so that rows
         // complete in roughly their numbering order -- the order in which the forwarders take them -- and so that
         // a slow reducer CTA is not left with a fixed share.  A reducer CTA that finds a forwarder on its own SM stops
         // taking entries: the two would hold each other up on the SM's one path to memory.
+        // With fewer entries than warps (few tokens) an entry's units are shared out between several warps instead: a
+        // row is then a handful of dependent round trips to memory for each of them, not one long chain for one warp.
+        const int share = entries >= total_warps ? 1 : static_cast<int>(min(static_cast<long long>(units_per_entry), total_warps / max(entries, 1ll)));
+        const int units_per_grab = (units_per_entry + share - 1) / share;
+        const int parts = (units_per_entry + units_per_grab - 1) / units_per_grab;
+        const unsigned long long grabs = static_cast<unsigned long long>(entries) * parts;
         unsigned long long* completed = nullptr;  // counter of the unit whose stores may still be in flight
         unsigned my_sm;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(my_sm));
@@ -423,14 +428,15 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
                 // stand aside (a few hundred microseconds at most, then help after all) and leave once every entry is taken
                 ptx::nanosleep(2000);
                 ++yields;
-                if (ptx::ld_relaxed_sys(reinterpret_cast<const std::uint64_t*>(a.next_unit)) >= static_cast<std::uint64_t>(entries)) break;
+                if (ptx::ld_relaxed_sys(reinterpret_cast<const std::uint64_t*>(a.next_unit)) >= grabs) break;
                 continue;
             }
             unsigned long long grabbed = 0;
             if (lane == 0) grabbed = atomicAdd(a.next_unit, 1ull);
             grabbed = __shfl_sync(0xffffffffu, grabbed, 0);
-            if (grabbed >= static_cast<unsigned long long>(entries)) break;
-            Entry e = locate_entry(a, lay, static_cast<long long>(grabbed), J, me);
+            if (grabbed >= grabs) break;
+            const int part = static_cast<int>(grabbed % parts);
+            Entry e = locate_entry(a, lay, static_cast<long long>(grabbed / parts), J, me);
             if (!e.present) continue;
             const int* map = a.comb_map + static_cast<std::size_t>(e.slot) * map_stride;
             e.token = map[0];
@@ -446,11 +452,12 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
                 P == 1 ? reinterpret_cast<std::uint8_t*>(a.out + static_cast<std::size_t>(e.token) * H)
                 : remote ? a.outbox + static_cast<std::size_t>(e.slot) * lay.crow_stride
                          : rc->seg[me] + lay.cstage_off + static_cast<std::size_t>(me) * rank_stride + static_cast<std::size_t>(e.token) * lay.crow_stride;
-            if (lane == 0) {
+            if (lane == 0 && part == 0) {
                 ++pushed;
                 if (remote) ++pushed_remote;
             }
-            for (int unit = 0; unit < units_per_entry; ++unit) {
+            const int unit_end = min(units_per_entry, (part + 1) * units_per_grab);
+            for (int unit = part * units_per_grab; unit < unit_end; ++unit) {
             const int q0 = unit * kPushGroupsPerUnit * 32 + lane;  // this lane's chunk in the unit's first group
             float acc[kPushGroupsPerUnit][8];
 #pragma unroll

@@ -42,6 +42,13 @@ constexpr int kMaxSendStages = 4;   // shared-memory row buffers per send warp
 constexpr int kMaxRowBuffers = 40;  // send warps x stages + receive warps of one channel CTA
 constexpr int kRoleFieldCount = 16; // counters per warp in a profiling build
 
+// Channels per group of the layout phase's two-level prefix, and the size of its scratch.
+constexpr int kHistGroup = 16;
+__host__ __device__ inline std::size_t hist_scratch_ints(int channels, int bins) {
+    const std::size_t groups = static_cast<std::size_t>((channels + kHistGroup - 1) / kHistGroup);
+    return static_cast<std::size_t>(channels) * bins + 2 * (groups + 1) * bins + 1;
+}
+
 // Row buffers a dispatch CTA needs: with dedicated sender CTAs a CTA is either all send warps or control + receive
 // warps; without them every channel CTA holds both kinds.
 __host__ __device__ inline int dispatch_row_buffer_count(int tx_warps, int rx_warps, int stages, int send_ctas) {
@@ -197,7 +204,8 @@ struct RankConst {
     std::uint64_t* epochs;      // [0] dispatch epoch, [1] combine epoch, [2] first-error latch time
     unsigned long long* grid_bar;   // [0] dispatch barrier arrivals, [1] combine (monotonic)
     unsigned long long* done_ctas;  // [0] dispatch CTAs finished, [1] combine (monotonic)
-    int* block_hist;            // [C][E + P] scratch of the layout phase
+    int* block_hist;            // scratch of the layout phase: per-channel counts [C][E + P], then two copies of the
+                                // per-group and grand sums [2][groups + 1][E + P] and their generation (see hist_scratch_ints)
     std::uint64_t* plan_flags;  // [C] epoch whose routing plan channel c has finished writing (read by the sender CTAs)
     int* sticky;                // [0] != 0 once this rank has failed; [1..] first error record
     std::int64_t* chan_stats;   // [2][C + send CTAs][10]: per-CTA counters + start/end time; dispatch, then combine

@@ -95,6 +95,9 @@ __device__ __forceinline__ void mbar_expect_tx(std::uint64_t* bar, unsigned byte
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(std::uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(std::uint64_t* bar, unsigned parity) {
     std::uint32_t ok;
     asm volatile(

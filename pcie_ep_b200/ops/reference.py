@@ -39,7 +39,7 @@ def unique_capacity(num_ranks: int, num_max_tokens_per_rank: int) -> int:
 
 
 def expanded_capacity(num_ranks: int, num_max_tokens_per_rank: int, num_topk: int, num_experts: int) -> int:
-    """Rows reserved for the expanded layout (reference: ``csrc/buffers/advanced.hpp:298``)."""
+    """Rows reserved for the expanded layout."""
     local = num_experts // num_ranks
     return num_ranks * num_max_tokens_per_rank * min(num_topk, local) + local * 255
 
@@ -57,7 +57,7 @@ def validate_routes(topk_idx: torch.Tensor, num_experts: int) -> bool:
 
 
 def route_volume(topk_idx: torch.Tensor, rank: int, num_ranks: int, num_experts: int) -> Dict[str, int]:
-    """Deduplicated traffic counters of one source rank (reference: ``benchmarks/benchmark.py:44-63``)."""
+    """Deduplicated traffic counters of one source rank."""
     local = num_experts // num_ranks
     tokens = topk_idx.shape[0]
     destinations = torch.zeros(tokens, num_ranks + 1, dtype=torch.bool, device=topk_idx.device)

@@ -33,7 +33,7 @@ class BorrowedNCCLComm:
 
 
 def borrow_nccl_comm(group: Any, device: Any, require_reuse: bool = False) -> BorrowedNCCLComm:
-    """Read the raw communicator of an NCCL group if PyTorch exposes it (reference: ``pcie_ep/comm.py:32-57``).
+    """Read the raw communicator of an NCCL group if PyTorch exposes it.
 
     The transport issues no NCCL call; the pointer is only recorded so an application can check
     that no second communicator was made.
@@ -105,7 +105,7 @@ def validate_group_configuration(
     transport: str,
     require_same_host: bool = True,
 ) -> None:
-    """All ranks must run on one host with identical dimensions and options (reference: ``pcie_ep/comm.py:80-99``)."""
+    """All ranks must run on one host with identical dimensions and options."""
     mine = (
         socket.gethostname() if require_same_host else "",
         (num_ranks, num_max_tokens_per_rank, hidden, num_topk, num_experts),
@@ -118,7 +118,7 @@ def validate_group_configuration(
 
 
 def create_shared_directory(rank: int, control_group: Any, parent: Optional[str]) -> Tuple[str, str]:
-    """Rank 0 makes a private directory (``/dev/shm`` by default) and tells the others (reference: ``pcie_ep/comm.py:102-142``)."""
+    """Rank 0 makes a private directory (``/dev/shm`` by default) and tells the others."""
     payload = [None]
     error = None
     if rank == 0:

@@ -140,7 +140,6 @@ def open_segments(
                         extension.first_touch_host_segment(path, size_bytes, node)
 
         # every owner places and touches its pages before anybody registers them
-        # (reference: pcie_ep/comm.py:145-182)
         control.run_agreed(first_touch, control_group, "first touch", rank)
 
         def register() -> None:
