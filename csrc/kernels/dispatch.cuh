@@ -575,7 +575,7 @@ __device__ __forceinline__ bool place_row(const Ctx& k, int s, int j, int token,
 // every row carries the epoch and token it belongs to, and a row that does not match its flag ends the launch
 // with kErrSequence.  The receiver reads the flag with `ld.acquire.sys` and issues `fence.proxy.async` before it
 // reads the row through the asynchronous proxy.  The two-GPU litmus test runs exactly this chain.
-template <int S>
+template <int S, int kCtaThreads>
 __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& cta_health, RoleStats& cta_stats) {
     // own copies: the kernel's objects live in local memory, and every access through a reference is a load or store there
     Health health = cta_health;
@@ -895,6 +895,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
 }
 
 // ---- send role, register path (16-byte or scalar accesses; also the path for odd hidden sizes) ----
+template <int kCtaThreads>
 __device__ __noinline__ void send_role_vector(const Ctx& k, int w, const Health& cta_health, RoleStats& cta_stats) {
     // own copies: the kernel's objects live in local memory, and every access through a reference is a load or store there
     Health health = cta_health;
@@ -991,6 +992,7 @@ __device__ __noinline__ void send_role_vector(const Ctx& k, int w, const Health&
 // Remote rows: poll the READY flags of this channel's rings (local memory), read a staged row once, check its
 // sequence words, write it to its output rows.  Own rows: whenever no remote row is waiting, take the next own
 // token that has a local expert straight from `x`.
+template <int kCtaThreads>
 __device__ __noinline__ void receive_role(const Ctx& k, int w, const Health& cta_health, RoleStats& cta_stats) {
     // own copies: the kernel's objects live in local memory, and every access through a reference is a load or store there
     Health health = cta_health;
@@ -1240,7 +1242,12 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, const Health& cta
 
 }  // namespace detail
 
-__global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __grid_constant__ DispatchLaunch launch) {
+// Two builds of the same kernel: CTAs of up to kSmallCtaThreads threads (every tuned configuration) get the larger
+// register budget that one CTA per SM allows them, which keeps the receive role free of spills; wider CTAs take the
+// other one.  The roles are instantiated per build so that each is compiled against its own kernel's budget.
+constexpr int kSmallCtaThreads = 384;
+template <int kCtaThreads>
+__global__ void __launch_bounds__(kCtaThreads, 1) dispatch_kernel(const __grid_constant__ DispatchLaunch launch) {
     using namespace detail;
     const DispatchArgs& a = launch.r[blockIdx.y];
     const RankConst* __restrict__ rc = a.rc;
@@ -1634,10 +1641,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     if (is_sender) {
         // ===== dedicated sender: every warp sends =====
         if (warp < tx_warps) {
-            if (!use_tma) send_role_vector(k, warp, health, st);
-            else if (k.stages >= 4) send_role_bulk<4>(k, warp, health, st);
-            else if (k.stages == 3) send_role_bulk<3>(k, warp, health, st);
-            else send_role_bulk<2>(k, warp, health, st);
+            if (!use_tma) send_role_vector<kCtaThreads>(k, warp, health, st);
+            else if (k.stages >= 4) send_role_bulk<4, kCtaThreads>(k, warp, health, st);
+            else if (k.stages == 3) send_role_bulk<3, kCtaThreads>(k, warp, health, st);
+            else send_role_bulk<2, kCtaThreads>(k, warp, health, st);
             if (lane == 0) atomicMax(&sh->last_tx_ns, ptx::globaltimer_ns());
             if (warp == 0 && lane == 0) BEP_PROF(kProfTxDone);
         }
@@ -1796,16 +1803,16 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) dispatch_kernel(const __gri
     } else if (S == 0 && warp <= tx_warps) {
         // ===== send (inside the channel CTA) =====
         const int w = warp - 1;
-        if (!use_tma) send_role_vector(k, w, health, st);
-        else if (k.stages >= 4) send_role_bulk<4>(k, w, health, st);
-        else if (k.stages == 3) send_role_bulk<3>(k, w, health, st);
-        else send_role_bulk<2>(k, w, health, st);
+        if (!use_tma) send_role_vector<kCtaThreads>(k, w, health, st);
+        else if (k.stages >= 4) send_role_bulk<4, kCtaThreads>(k, w, health, st);
+        else if (k.stages == 3) send_role_bulk<3, kCtaThreads>(k, w, health, st);
+        else send_role_bulk<2, kCtaThreads>(k, w, health, st);
         if (lane == 0) atomicMax(&sh->last_tx_ns, ptx::globaltimer_ns());
         if (w == 0 && lane == 0) BEP_PROF(kProfTxDone);
     } else {
         // ===== receive + expand =====
         const int rw = warp - 1 - (S == 0 ? tx_warps : 0);
-        if (rw < rx_warps) receive_role(k, rw, health, st);
+        if (rw < rx_warps) receive_role<kCtaThreads>(k, rw, health, st);
     }
 
     // ---- epilogue ----------------------------------------------------------------------------------

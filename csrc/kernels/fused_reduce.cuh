@@ -201,8 +201,7 @@ struct Entry {
 };
 
 // entry number -> (channel, row index, owner); `slot` addresses the combine map and the outbox
-__device__ __forceinline__ Entry locate_entry(const CombinePushArgs& a, const SegmentLayout& lay, long long entry, int J, int me) {
-    const int P = lay.num_ranks, C = lay.num_channels, Qf = lay.slots_full;
+__device__ __forceinline__ Entry locate_entry(const CombinePushArgs& a, int P, int C, int Qf, long long entry, int J, int me) {
     Entry e;
     const int step = static_cast<int>(entry % P);
     const long long cj = entry / P;
@@ -228,10 +227,16 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
     extern __shared__ __align__(128) unsigned char push_smem[];
     __shared__ int s_failed;
     __shared__ int s_max_rows;
+    // The segment table and the two layout values a row needs are copied out of global memory once: a load per row is
+    // slow on a forwarder's SM (it queues behind that SM's stores to peers), and the compiler cannot keep values
+    // read through `rc` in registers across the inline assembly of the copy loop.
+    __shared__ std::uint8_t* s_seg[kMaxRanks];
     if (threadIdx.x == 0) {
         s_failed = 0;
         s_max_rows = 0;
     }
+    if (threadIdx.x < kMaxRanks) s_seg[threadIdx.x] = static_cast<int>(threadIdx.x) < P ? rc->seg[threadIdx.x] : nullptr;
+    const std::size_t crow_stride = lay.crow_stride, cstage_off = lay.cstage_off;
     __syncthreads();
     const bool aborted = ptx::ld_volatile(&rc->sticky[0]) != 0;
     const std::uint64_t epoch = rc->epochs[1] + 1;
@@ -268,7 +273,7 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
     const int units_per_entry = (groups + kPushGroupsPerUnit - 1) / kPushGroupsPerUnit;
     const int J = min(s_max_rows, Qf);
     const long long entries = static_cast<long long>(C) * J * P;
-    const std::size_t rank_stride = static_cast<std::size_t>(lay.num_max_tokens) * lay.crow_stride;
+    const std::size_t rank_stride = static_cast<std::size_t>(lay.num_max_tokens) * crow_stride;
     unsigned long long pushed = 0, pushed_remote = 0;
 
     if (!s_failed && forwarder) {
@@ -281,7 +286,7 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
         if (warp < kForwardWarps) {
             Health health(rc, a.error);
             const int fw = blockIdx.x * kForwardWarps + warp, fws = F * kForwardWarps;
-            unsigned char* buffers = push_smem + 128 + static_cast<std::size_t>(warp) * kForwardStages * lay.crow_stride;
+            unsigned char* buffers = push_smem + 128 + static_cast<std::size_t>(warp) * kForwardStages * crow_stride;
             unsigned long long* bars = reinterpret_cast<unsigned long long*>(push_smem) + warp * kForwardStages;
             const bool issuer = lane == 31;
             const unsigned row_bytes = static_cast<unsigned>(H) * 2u;
@@ -309,7 +314,7 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
                 my_ready = false;
                 if (q < remote_entries) {
                     const int step = static_cast<int>(q % (P - 1));
-                    const Entry e = locate_entry(a, lay, (q / (P - 1)) * P + step, J, me);  // steps 0..P-2 are the other ranks
+                    const Entry e = locate_entry(a, P, C, Qf, (q / (P - 1)) * P + step, J, me);  // steps 0..P-2 are the other ranks
                     present = e.present;
                     if (present) {
                         my_slot = e.slot;
@@ -357,14 +362,14 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
                 // every producer of this row has finished: its counter starts the next combine at zero
                 if (lane == 0) a.outbox_units[slot] = 0ull;
                 const int b = issued % kForwardStages;
-                dst_of[b] = rc->seg[owner] + lay.cstage_off + static_cast<std::size_t>(me) * rank_stride +
-                            static_cast<std::size_t>(token) * lay.crow_stride;
+                dst_of[b] = s_seg[owner] + cstage_off + static_cast<std::size_t>(me) * rank_stride +
+                            static_cast<std::size_t>(token) * crow_stride;
                 __syncwarp();  // the lane that saw the row complete, before the lane that copies it
                 if (issuer) {
                     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the buffer's previous row has left it
                     ptx::mbar_expect_tx(reinterpret_cast<std::uint64_t*>(&bars[b]), row_bytes);
-                    ptx::bulk_g2s(buffers + static_cast<std::size_t>(b) * lay.crow_stride,
-                                  a.outbox + static_cast<std::size_t>(slot) * lay.crow_stride, row_bytes,
+                    ptx::bulk_g2s(buffers + static_cast<std::size_t>(b) * crow_stride,
+                                  a.outbox + static_cast<std::size_t>(slot) * crow_stride, row_bytes,
                                   reinterpret_cast<std::uint64_t*>(&bars[b]));
                 }
                 ++issued;
@@ -385,7 +390,7 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
                 ok = __all_sync(0xffffffffu, ok) != 0;
                 if (!ok) break;
                 if (issuer) {
-                    ptx::bulk_s2g(dst_of[b], buffers + static_cast<std::size_t>(b) * lay.crow_stride, row_bytes);
+                    ptx::bulk_s2g(dst_of[b], buffers + static_cast<std::size_t>(b) * crow_stride, row_bytes);
                     ptx::bulk_commit();
                 }
                 ++sent;
@@ -436,7 +441,7 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
             grabbed = __shfl_sync(0xffffffffu, grabbed, 0);
             if (grabbed >= grabs) break;
             const int part = static_cast<int>(grabbed % parts);
-            Entry e = locate_entry(a, lay, static_cast<long long>(grabbed / parts), J, me);
+            Entry e = locate_entry(a, P, C, Qf, static_cast<long long>(grabbed / parts), J, me);
             if (!e.present) continue;
             const int* map = a.comb_map + static_cast<std::size_t>(e.slot) * map_stride;
             e.token = map[0];
@@ -450,8 +455,8 @@ __global__ void __launch_bounds__(kFusedReduceThreads, 2) combine_push_kernel(co
             const bool remote = P > 1 && e.s != me;
             std::uint8_t* dst_row =
                 P == 1 ? reinterpret_cast<std::uint8_t*>(a.out + static_cast<std::size_t>(e.token) * H)
-                : remote ? a.outbox + static_cast<std::size_t>(e.slot) * lay.crow_stride
-                         : rc->seg[me] + lay.cstage_off + static_cast<std::size_t>(me) * rank_stride + static_cast<std::size_t>(e.token) * lay.crow_stride;
+                : remote ? a.outbox + static_cast<std::size_t>(e.slot) * crow_stride
+                         : s_seg[me] + cstage_off + static_cast<std::size_t>(me) * rank_stride + static_cast<std::size_t>(e.token) * crow_stride;
             if (lane == 0 && part == 0) {
                 ++pushed;
                 if (remote) ++pushed_remote;

@@ -27,7 +27,10 @@ cudaError_t configure_kernels(std::size_t dispatch_smem) {
     if (status != cudaSuccess) return status;
     if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
     if (dispatch_smem > current[device]) {
-        status = cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        status = cudaFuncSetAttribute(dispatch_kernel<kSmallCtaThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(dispatch_smem));
+        if (status != cudaSuccess) return status;
+        status = cudaFuncSetAttribute(dispatch_kernel<kMaxWarps * 32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(dispatch_smem));
         if (status != cudaSuccess) return status;
         current[device] = dispatch_smem;
@@ -39,7 +42,10 @@ int dispatch_resident_ctas(int threads, std::size_t smem) {
     int per_sm = 0, device = 0, sms = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dispatch_kernel, threads, smem) != cudaSuccess) return 0;
+    const cudaError_t status = threads <= kSmallCtaThreads
+                                   ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dispatch_kernel<kSmallCtaThreads>, threads, smem)
+                                   : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dispatch_kernel<kMaxWarps * 32>, threads, smem);
+    if (status != cudaSuccess) return 0;
     return per_sm * sms;
 }
 
@@ -73,7 +79,9 @@ cudaError_t cooperative_launch(Kernel kernel, const Args& args, dim3 grid, int t
 
 cudaError_t launch_dispatch(const DispatchLaunch& launch, int ctas, int threads, std::size_t smem,
                             cudaStream_t stream) {
-    return cooperative_launch(dispatch_kernel, launch, dim3(ctas, launch.num_virtual, 1), threads, smem, stream);
+    const dim3 grid(ctas, launch.num_virtual, 1);
+    if (threads <= kSmallCtaThreads) return cooperative_launch(dispatch_kernel<kSmallCtaThreads>, launch, grid, threads, smem, stream);
+    return cooperative_launch(dispatch_kernel<kMaxWarps * 32>, launch, grid, threads, smem, stream);
 }
 
 cudaError_t launch_combine(const CombineLaunch& launch, int channels, std::size_t crow_stride, cudaStream_t stream) {
