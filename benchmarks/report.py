@@ -1,6 +1,7 @@
 """Recompute comparison tables from saved benchmark records (CPU only).
 
     python benchmarks/report.py results/eager.json results/graph.json --baseline published
+    python benchmarks/report.py --bench benchmarks/data/results/bench_*gpu*.json      # scaling + sweep tables from bench.py lines
 
 Inputs are the JSON files written by ``benchmarks/benchmark.py --output``.  Records are only compared
 when their shape arguments agree (hidden, experts, top-k, world, profile, wire); anything else is
@@ -63,11 +64,89 @@ def table(files: List[Dict], labels: List[str], baseline: str = "") -> str:
     return "\n".join(lines)
 
 
+def load_bench_line(path: Path) -> Dict:
+    """The JSON line that ``bench.py`` prints (the last line of a saved log that parses as JSON with a ``metric``)."""
+    for line in reversed(Path(path).read_text().splitlines()):
+        line = line.strip()
+        if line.startswith("{"):
+            try:
+                record = json.loads(line)
+            except json.JSONDecodeError:
+                continue
+            if "metric" in record or "unavailable" in record:
+                return record
+    raise ValueError(f"{path}: no bench.py result line")
+
+
+def scaling_table(records: List[Dict]) -> str:
+    """Weak-scaling table from ``bench.py`` lines of one implementation at several GPU counts.
+
+    Lines are only put side by side when metric, unit, dtype and the model part of ``config`` agree.  Efficiency is
+    time(1 GPU) / time(N GPUs) for this time-like metric (per-GPU work is fixed); the reference arm's lines, when
+    given as well, add the ratio reference / ours per GPU count.
+    """
+    ours = sorted((r for r in records if r.get("impl", "ours") != "reference" and "value" in r), key=lambda r: r["n_gpus"])
+    reference = {r["n_gpus"]: r for r in records if r.get("impl") == "reference" and "value" in r}
+    if not ours:
+        raise ValueError("no result line of this framework among the inputs")
+    first = ours[0]
+    for other in ours[1:] + list(reference.values()):
+        for key in ("metric", "unit", "dtype", "higher_is_better"):
+            if other.get(key) != first.get(key):
+                raise ValueError(f"lines disagree on {key!r}: {first.get(key)!r} vs {other.get(key)!r}")
+        for key in ("model", "seq_len"):
+            if other.get("config", {}).get(key) != first.get("config", {}).get(key):
+                raise ValueError(f"lines disagree on config.{key}")
+    base = next((r["value"] for r in ours if r["n_gpus"] == 1), None)
+    header = ["GPUs", "dispatch+combine us", "dispatch us", "combine us", "end to end us", "fraction of bound (dispatch / combine)",
+              "efficiency vs 1 GPU", "reference us", "reference / ours"]
+    lines = ["| " + " | ".join(header) + " |", "|" + "---|" * len(header)]
+    for r in ours:
+        roof = r.get("roofline", {})
+        ref = reference.get(r["n_gpus"])
+        lines.append("| " + " | ".join([
+            str(r["n_gpus"]), f"{r['value']:.1f}",
+            f"{r['dispatch_us']:.1f}" if r.get("dispatch_us") is not None else "-",
+            f"{r['combine_us']:.1f}" if r.get("combine_us") is not None else "-",
+            f"{r['e2e']['value']:.1f}" if isinstance(r.get("e2e"), dict) and r["e2e"].get("value") is not None else "-",
+            f"{roof.get('dispatch_fraction', float('nan')):.2f} / {roof.get('combine_fraction', float('nan')):.2f}" if roof else "-",
+            f"{base / r['value']:.2f}" if base else "-",
+            f"{ref['value']:.1f}" if ref else "-",
+            f"{ref['value'] / r['value']:.1f}x" if ref else "-",
+        ]) + " |")
+    return "\n".join(lines)
+
+
+def sweep_table(record: Dict) -> str:
+    """Token sweep of one ``bench.py --sweep`` line next to the reference's published dispatch latencies."""
+    sweep = record.get("sweep") or {}
+    if not sweep:
+        raise ValueError("the line has no sweep (run bench.py with --sweep)")
+    header = ["T per rank", "dispatch us", "dispatch + combine us", "published reference dispatch us (8x H20D)", "published / ours (dispatch)"]
+    lines = ["| " + " | ".join(header) + " |", "|" + "---|" * len(header)]
+    for tokens in sorted(sweep, key=int):
+        entry = sweep[tokens]
+        ref = PUBLISHED_US.get(int(tokens))
+        lines.append(f"| {tokens} | {entry['dispatch_us']:.1f} | {entry['us_per_step']:.1f} | {ref if ref else '-'} | "
+                     f"{ref / entry['dispatch_us']:.0f}x |" if ref else f"| {tokens} | {entry['dispatch_us']:.1f} | {entry['us_per_step']:.1f} | - | - |")
+    return "\n".join(lines)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__)
     parser.add_argument("files", type=Path, nargs="+")
     parser.add_argument("--baseline", default="", choices=["", "published"])
+    parser.add_argument("--bench", action="store_true",
+                        help="the files are saved outputs of bench.py (either arm, any GPU count): print the scaling table and, "
+                             "for lines that carry one, the token sweep")
     args = parser.parse_args()
+    if args.bench:
+        records = [load_bench_line(p) for p in args.files]
+        print(scaling_table(records))
+        for record in records:
+            if record.get("sweep"):
+                print(f"\nsweep at {record['n_gpus']} GPUs\n" + sweep_table(record))
+        return
     files = [load(p) for p in args.files]
     print(table(files, [p.stem for p in args.files], args.baseline))
 

@@ -40,7 +40,7 @@ ATOMIC_CALL = re.compile(r"\b(atomic(?:Add|Sub|Exch|CAS|Min|Max|Or|And|Xor|Inc|D
 ATOMIC_PTX = re.compile(r"\b(atom|red)\.(?:[a-z_0-9:.]+)")
 PEER_ADDRESS = re.compile(r"seg\s*\[|peer_|remote_|dst_of|->seg\b")
 POLL_LOOP = re.compile(r"\bwhile\s*\(.*(ld_acquire_|ld_relaxed_|ld_volatile|try_wait|mbar_test)")
-BOUND_WORDS = ("give_up(", "deadline", "expired", "timed_out", "spins", "budget")
+BOUND_WORDS = ("give_up(", "deadline", "expired", "timed_out", "spins", "polls", "budget")
 LOOP_WINDOW = 10
 # assembled from pieces so that this file does not itself contain the names it looks for
 FORBIDDEN = {

@@ -143,3 +143,76 @@ def test_smaps_rollup_parser():
             "Rss:              123456 kB\nPss:               65432 kB\nPss_Shmem:         2048 kB\nSwap:                  0 kB\n")
     counters = parse_smaps_rollup(text)
     assert counters == {"Rss": 123456 * 1024, "Pss": 65432 * 1024, "Pss_Shmem": 2048 * 1024, "Swap": 0}
+
+
+def _bench_line(n_gpus, value, impl="ours", **extra):
+    line = {"metric": "dispatch+combine us", "value": value, "unit": "us/step", "n_gpus": n_gpus, "dtype": "bf16",
+            "higher_is_better": False, "impl": impl, "config": {"model": "moe-dispatch", "seq_len": 4096},
+            "dispatch_us": value * 0.45, "combine_us": value * 0.55, "e2e": {"value": value + 800.0},
+            "roofline": {"dispatch_fraction": 0.6, "combine_fraction": 0.5}}
+    line.update(extra)
+    return line
+
+
+def test_scaling_table_from_bench_lines(tmp_path):
+    paths = []
+    for n, v, impl in ((1, 200.0, "ours"), (2, 400.0, "ours"), (2, 4000.0, "reference")):
+        path = tmp_path / f"{impl}{n}.log"
+        path.write_text("some log line\n" + json.dumps(_bench_line(n, v, impl)) + "\n")
+        paths.append(path)
+    text = report.scaling_table([report.load_bench_line(p) for p in paths])
+    rows = [r for r in text.splitlines() if r.startswith("| 2 ")]
+    assert len(rows) == 1 and "0.50" in rows[0] and "10.0x" in rows[0] and "4000.0" in rows[0]
+    assert "| 1 | 200.0" in text and "1.00" in text
+
+
+def test_scaling_table_refuses_lines_of_different_metrics():
+    other = _bench_line(2, 300.0)
+    other["metric"] = "dispatch us"
+    with pytest.raises(ValueError, match="metric"):
+        report.scaling_table([_bench_line(1, 200.0), other])
+    with pytest.raises(ValueError, match="no result line"):
+        report.scaling_table([_bench_line(1, 1.0, impl="reference")])
+
+
+def test_sweep_table_uses_published_numbers():
+    line = _bench_line(8, 900.0, sweep={"128": {"dispatch_us": 64.7, "us_per_step": 120.0}, "4096": {"dispatch_us": 400.0, "us_per_step": 900.0}})
+    text = report.sweep_table(line)
+    assert "| 128 | 64.7 | 120.0 | 647 | 10x |" in text and "| 4096 | 400.0 | 900.0 | 13558 | 34x |" in text
+
+
+def test_committed_bench_samples_recompute():
+    from pathlib import Path
+
+    samples = sorted((Path(report.__file__).parent / "data" / "results").glob("bench_*gpu*.json"))
+    assert samples, "sample results are part of the repository"
+    text = report.scaling_table([report.load_bench_line(p) for p in samples])
+    assert text.count("\n") >= 2
+
+
+def test_source_audit_is_clean_and_sees_violations():
+    from benchmarks import source_manifest
+
+    result = source_manifest.audit()
+    assert result["violations"] == []
+    assert len(result["atomics"]) > 20
+    bad = source_manifest.audit_text("x.cu", "void f() {\n  atomicAdd(rc->seg[p] + 4, 1);\n  while (ptx::ld_acquire_sys(flag) != v) {\n    ++n;\n  }\n}\n")
+    assert len(bad["violations"]) == 2
+    assert "peer memory" in bad["violations"][0] and "polling loop" in bad["violations"][1]
+    commented = source_manifest.audit_text("x.cu", "// atomicAdd(rc->seg[p], 1);\n/* while (ptx::ld_acquire_sys(f)) {} */\n")
+    assert commented["violations"] == [] and commented["atomics"] == []
+
+
+def test_source_manifest_compare(ext):
+    from benchmarks import source_manifest
+
+    current = source_manifest.manifest()
+    assert current["fingerprint"] and "csrc/kernels/dispatch.cuh" in current["files"]
+    assert source_manifest.compare(current, current) == []
+    changed = json.loads(json.dumps(current))
+    changed["files"]["csrc/kernels/dispatch.cuh"] = "0" * 64
+    changed["files"].pop("csrc/kernels/ptx.cuh")
+    changed["cuda_flags"] = ["-O0"]
+    differences = source_manifest.compare(changed, current)
+    assert any(d.startswith("modified: csrc/kernels/dispatch.cuh") for d in differences)
+    assert any(d.startswith("added: csrc/kernels/ptx.cuh") for d in differences) and any("cuda_flags" in d for d in differences)
