@@ -32,6 +32,13 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 HIDDEN, EXPERTS, TOPK = 7168, 256, 8
+def source_fingerprint() -> str:
+    """Hash of the native sources and flags the loaded library was built from (see benchmarks/source_manifest.py)."""
+    from pcie_ep_b200 import _C
+
+    return _C.source_fingerprint()[:16]
+
+
 # reference dispatch-only latency on 8x H20D, ms (RESULTS_CONTROL_PROGRESS.md:31-40)
 PUBLISHED_MS = {16: 0.260, 32: 0.282, 64: 0.405, 128: 0.647, 256: 1.033, 512: 1.950, 1024: 3.681, 2048: 7.079,
                 4096: 13.558, 8192: 26.546}
@@ -536,6 +543,7 @@ def run_ours(args, rank, world, local_rank):
             "kernels_per_step": ", ".join(headline["kernels"]),
             "payload_check": headline["payload_check"],
             "impl": "ours",
+            "source_fingerprint": source_fingerprint(),
         }
         if "e2e" in headline:
             line["e2e"] = {k: (round(v, 2) if isinstance(v, float) else v) for k, v in headline["e2e"].items()}

@@ -171,7 +171,10 @@ def main() -> None:
             print(f"{r['tokens']:>6} {r['dispatch_us_mean']:>12.1f} {comb:>11} {r['logical_GBps']:>13.1f} {frac:>12}")
         if args.output:
             args.output.parent.mkdir(parents=True, exist_ok=True)
-            args.output.write_text(json.dumps({"arguments": {k: str(v) for k, v in vars(args).items()}, "records": records}, indent=2))
+            from pcie_ep_b200 import _C
+
+            args.output.write_text(json.dumps({"arguments": {k: str(v) for k, v in vars(args).items()},
+                                               "source_fingerprint": _C.source_fingerprint()[:16], "records": records}, indent=2))
     dist.destroy_process_group()
 
 

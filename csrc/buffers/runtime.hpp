@@ -557,7 +557,9 @@ class Runtime {
     // second launch of the default combine; `prepared` comes from prepare_combine of this runtime
     void launch_combine_reduce(PreparedCombine& prepared, cudaStream_t stream, int num_sms = 0) {
         if (!prepared.reduce_needed) return;
-        cuda_check(launch_fused_reduce(prepared.reduce, combine_ctas(4, num_sms), stream), "combine reduce launch");
+        // as many CTAs as are resident at once (the wider steps of the few-rank builds take more registers)
+        cuda_check(launch_fused_reduce(prepared.reduce, combine_ctas(fused_reduce_groups(prepared.reduce.slots) == 1 ? 4 : 3, num_sms), stream),
+                   "combine reduce launch");
     }
 
     at::Tensor combine(const at::Tensor& y, const DispatchResult& dispatch_result, bool weighted,

@@ -121,7 +121,11 @@ cudaError_t launch_combine_push(const CombinePushArgs& args, int reduce_ctas, st
 }
 
 cudaError_t launch_fused_reduce(const FusedReduceArgs& args, int ctas, cudaStream_t stream) {
-    fused_reduce_kernel<<<ctas, kFusedReduceThreads, 0, stream>>>(args);
+    switch (fused_reduce_groups(args.slots)) {
+        case 4: fused_reduce_kernel<4><<<ctas, kFusedReduceThreads, 0, stream>>>(args); break;
+        case 2: fused_reduce_kernel<2><<<ctas, kFusedReduceThreads, 0, stream>>>(args); break;
+        default: fused_reduce_kernel<1><<<ctas, kFusedReduceThreads, 0, stream>>>(args); break;
+    }
     return cudaGetLastError();
 }
 

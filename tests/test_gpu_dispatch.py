@@ -109,6 +109,47 @@ def test_dispatch_fp8_rows_stay_fp8_at_the_receiver(ext, engine):
             del results
 
 
+@pytest.mark.parametrize("engine", ["vector", "tma"])
+@pytest.mark.parametrize("recv", ["bf16", "fp8_e4m3"])
+def test_dispatch_fp8_corner_rows(ext, engine, recv):
+    """Rows that sit on the edges of the E4M3 wire format go through the kernel's own quantisation (send warps and
+    the local path) and come out exactly as the PyTorch reference of the format says: an all-zero row (scale 1), a
+    row whose largest magnitude is exactly 448 (scale 1), a negative extreme, a row with one element 50 times the
+    rest, a row of tiny values whose scaled codes are subnormal, and a row that mixes all of these."""
+    from pcie_ep_b200.parallel.virtual import VirtualEPGroup
+
+    world, experts, topk, hidden, tmax = 4, 16, 4, 512, 32
+    tokens = [32, 9, 20, 32]
+    config = HostStagedConfig(channels=4, stage=7, wire_dtype="fp8_e4m3", recv_dtype=recv, copy_engine=engine, timeout_ms=2000,
+                              tx_warps=2, rx_warps=3)
+    with VirtualEPGroup(world, tmax, hidden, topk, experts, config) as group:
+        for expand in (True, False):
+            cpu_inputs = [list(make_inputs(r, world, tokens[r], hidden, experts, topk, "random", seed=11)) for r in range(world)]
+            for r, inp in enumerate(cpu_inputs):
+                x = inp[0].float()
+                x[0] = 0.0
+                x[1] = torch.linspace(-1.0, 1.0, hidden) * 448.0
+                x[2] = -x[2].abs() - 1.0
+                x[2, 7] = -30000.0
+                x[3, r] = x[3].abs().max() * 50.0
+                x[4] = torch.randn(hidden) * 1e-30
+                x[5, ::2] = 0.0
+                x[5, 1] = 448.0
+                x[5, 3] = -1e-3
+                inp[0] = x.to(torch.bfloat16)
+            cpu_inputs = [tuple(inp) for inp in cpu_inputs]
+            dev = [tuple(None if t is None else t.cuda() for t in inp) for inp in cpu_inputs]
+            results = group.dispatch([d[0] for d in dev], [d[1] for d in dev], [d[2] for d in dev], do_expand=expand,
+                                     expert_alignment=1, do_zero_padding=expand)
+            torch.cuda.synchronize()
+            for rank in range(world):
+                expected = reference.dispatch_reference(cpu_inputs, rank, experts, tmax, do_expand=expand, expert_alignment=1,
+                                                        do_zero_padding=expand, wire_dtype="fp8_e4m3", recv_dtype=recv)
+                problems = reference.compare_dispatch(results[rank], expected, do_expand=expand, do_zero_padding=expand,
+                                                      have_weights=True)
+                assert not problems, f"rank {rank} expand={expand}: {problems}"
+
+
 def test_dispatch_headline_shape_small_t(ext):
     """DeepSeek-V3 shape (hidden 7168, 256 experts, top-8) at small T on 8 emulated ranks."""
     from pcie_ep_b200.parallel.virtual import VirtualEPGroup
