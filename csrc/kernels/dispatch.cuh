@@ -448,24 +448,45 @@ __device__ __forceinline__ void load_token_routes(const DispatchArgs& a, int t, 
     }
 }
 
-// BF16 row in shared memory -> E4M3 codes in its first half; returns the row scale.  Increasing order: chunk q
-// is read by every lane before anything lands on it.
+// BF16 row in shared memory -> E4M3 codes in its first half; returns the row scale.  Four 16-byte chunks per lane and
+// step (128 chunks per step): the codes of a step land on bytes [8 q0, 8 q0 + 1024), that is on input chunks
+// [q0 / 2, q0 / 2 + 64).  Only in the first step do these overlap the chunks the step itself reads, and there every
+// lane has read before any lane writes (the barrier); from the second step on they lie wholly below q0, in chunks
+// consumed by earlier steps, and the chunks of later steps start above every byte written so far.  So one barrier per
+// step is enough.  With dedicated sender CTAs a few warps quantise every row of the rank, and this loop is their
+// critical path: at hidden 7168 it went from 56 barrier-separated steps of one chunk per lane to 7 + 7 steps.
 __device__ __forceinline__ float quantise_row_in_place(unsigned char* slot, int hidden) {
     const unsigned lane = ptx::lane_id();
     const int chunks = hidden / 8;
     float amax = 0.0f;
-    for (int q = lane; q < chunks; q += 32) amax = fmaxf(amax, chunk_amax(*reinterpret_cast<const uint4*>(slot + q * 16)));
+    for (int q0 = 0; q0 < chunks; q0 += 128) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int q = q0 + u * 32 + static_cast<int>(lane);
+            v[u] = q < chunks ? *reinterpret_cast<const uint4*>(slot + q * 16) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) amax = fmaxf(amax, chunk_amax(v[u]));
+    }
     amax = warp_max(amax);
     const float scale = fp8_scale_from_amax(amax);
     const float inv = 1.0f / scale;
-    for (int q0 = 0; q0 < chunks; q0 += 32) {
-        const int q = q0 + lane;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (q < chunks) v = *reinterpret_cast<const uint4*>(slot + q * 16);
+    for (int q0 = 0; q0 < chunks; q0 += 128) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int q = q0 + u * 32 + static_cast<int>(lane);
+            v[u] = q < chunks ? *reinterpret_cast<const uint4*>(slot + q * 16) : make_uint4(0, 0, 0, 0);
+        }
         __syncwarp();
-        if (q < chunks) *reinterpret_cast<uint2*>(slot + q * 8) = chunk_to_fp8(v, inv);
-        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int q = q0 + u * 32 + static_cast<int>(lane);
+            if (q < chunks) *reinterpret_cast<uint2*>(slot + q * 8) = chunk_to_fp8(v[u], inv);
+        }
     }
+    __syncwarp();
     return scale;
 }
 
