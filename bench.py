@@ -32,6 +32,10 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 HIDDEN, EXPERTS, TOPK = 7168, 256, 8
+# both arms name the same model and shape in their result line
+MODEL_NAME = "DeepSeek-V3-shaped MoE exchange (hidden 7168, 256 experts, top-%d)"
+
+
 def source_fingerprint() -> str:
     """Hash of the native sources and flags the loaded library was built from (see benchmarks/source_manifest.py)."""
     from pcie_ep_b200 import _C
@@ -523,7 +527,7 @@ def run_ours(args, rank, world, local_rank):
             "dtype": "bf16" if args.wire == "bf16" else "bf16 in/out, fp8_e4m3 wire",
             "data": "synthetic: x~N(0,1) bf16, distinct uniform top-k expert ids, softmax weights, random-init",
             "config": {
-                "model": "DeepSeek-V3-shaped MoE exchange (hidden 7168, 256 experts, top-%d)" % args.topk,
+                "model": MODEL_NAME % args.topk,
                 "tokens_per_rank": args.tokens,
                 "global_batch": args.tokens * world,
                 "seq_len": 1,
@@ -676,7 +680,7 @@ def run_reference(args, rank, world, local_rank):
             "ms_per_step": round(value / 1000.0, 5), "higher_is_better": False, "scaling": "weak",
             "vs_baseline": round(value / (published * 1000.0), 5) if published else None,
             "dtype": "bf16", "data": "synthetic, same generator as the other arm",
-            "config": {"model": "DeepSeek-V3-shaped MoE dispatch", "tokens_per_rank": args.tokens,
+            "config": {"model": MODEL_NAME % args.topk, "tokens_per_rank": args.tokens,
                        "global_batch": args.tokens * world, "seq_len": 1, "parallelism": f"ep{world}",
                        "transport": "host_staged (reference default config)"},
             "timing": dict(summarise(samples), how=f"{REPEATS} timed regions of exactly --steps steps, median"),

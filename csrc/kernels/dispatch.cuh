@@ -37,7 +37,8 @@
 namespace bep {
 
 constexpr int kMetaSmemBytes = 16 + 12 * kMaxTopk;
-constexpr int kFlagLag = 2;         // a row's READY flags are released after this many later rows were issued
+constexpr int kFlagLag = 2;         // a row's READY flags are released after at least this many later rows were issued
+constexpr int kFlagBatch = 8;       // READY flags of up to this many rows share one system-scope fence
 
 struct DispatchShared;
 
@@ -586,16 +587,17 @@ __device__ __forceinline__ bool place_row(const Ctx& k, int s, int j, int token,
 //
 // Ordering of a row and its READY flag.  The payload leaves through the asynchronous proxy
 // (cp.async.bulk shared -> peer global), all copies of one row in one bulk group of the issuing lane.
-// `cp.async.bulk.wait_group N` returns to that lane only when every group but the N most recent is complete:
-// the writes have been performed at the destination.  `__syncwarp()` orders that observation before the other
-// lanes' later accesses, and only then does each destination's lane store the flag (`st.relaxed.sys`).  No
-// system-scope fence sits in between: on this hardware such a fence (alone or inside `st.release.sys`) waits for
-// every store the SM still has on the wire, which costs a full drain of the pipeline per row (measured: 4.4 us
-// per row against 0.07 us without).  Instead the order rests on the completion of the bulk group, which is
-// stronger than a fence for these writes -- they are not merely ordered but done -- and the receiver verifies it:
-// every row carries the epoch and token it belongs to, and a row that does not match its flag ends the launch
-// with kErrSequence.  The receiver reads the flag with `ld.acquire.sys` and issues `fence.proxy.async` before it
-// reads the row through the asynchronous proxy.  The two-GPU litmus test runs exactly this chain.
+// `cp.async.bulk.wait_group N` returns to that lane when every group but the N most recent is complete.  That is a
+// statement about what the issuing thread can see; it is not a system-scope release.  So before any READY flag goes out
+// the issuing lane executes `fence.acq_rel.sys`, then `__syncwarp()` hands the order to the destinations' lanes,
+// which store the flags (`st.relaxed.sys`).  On this hardware such a fence waits for every store the SM still has
+// on the wire (measured: 4.4 us when it is paid for every row, against 0.07 us for a flag without it), which is why it
+// is not paid per row: the flags of up to kFlagBatch rows wait in registers and go out behind one fence.  A version
+// that relied on the completion of the bulk group alone passed the two-GPU litmus and every two-GPU run, and then
+// delivered rows whose payload was partly stale on four GPUs with BF16 rows (the flag and the last packets of its row
+// took different ways through the switch); the per-row sequence words did not catch it because they sit in the
+// row's last bytes.  The receiver reads the flag with `ld.acquire.sys` and issues `fence.proxy.async` before it
+// reads the row through the asynchronous proxy.
 template <int S, int kCtaThreads>
 __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& cta_health, RoleStats& cta_stats) {
     // own copies: the kernel's objects live in local memory, and every access through a reference is a load or store there
@@ -755,13 +757,22 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
 #pragma unroll
     for (int i = 0; i < D; ++i) ahead_ok[i] = (i == 0 || ahead_ok[i - 1]) ? next_token(ahead[i]) : false;
 
-    std::uint64_t* flag_ring[kFlagLag];
-    std::uint32_t flag_seq[kFlagLag];
+    // READY flags not yet stored: the newest row's at the end, one step towards the front per row.  A flag may go out
+    // once its row's bulk group is complete (all but the kFlagLag most recent groups are, after the wait below) and a
+    // system-scope fence has followed; one such fence serves the flags of up to `flag_batch` rows.
+    constexpr int kRing = kFlagBatch + kFlagLag;
+    std::uint64_t* flag_ring[kRing];
+    std::uint32_t flag_seq[kRing];
 #pragma unroll
-    for (int i = 0; i < kFlagLag; ++i) {
+    for (int i = 0; i < kRing; ++i) {
         flag_ring[i] = nullptr;
         flag_seq[i] = 0;
     }
+    // rows per fence: every row on host segments (as before); on peer segments a quarter of what this warp has to
+    // send, at most kFlagBatch, so that a warp with a handful of rows does not sit on their flags
+    const int flag_batch = fence_flags ? 1 : max(1, min(kFlagBatch, n_cand / (4 * max(W, 1))));
+    int since_flags = 0;  // rows issued since flags last went out
+    bool first_flags_stamped = false;
     int n = 0;  // rows sent
     bool broke = false;
     while (ahead_ok[0]) {
@@ -808,14 +819,15 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
             if (!__all_sync(full, have)) {
                 if (issuer) {
                     bulk_wait_group<0>();
-                    if (fence_flags) ptx::fence_sys();
+                    ptx::fence_sys();
                 }
                 __syncwarp();
 #pragma unroll
-                for (int i = 0; i < kFlagLag; ++i) {
+                for (int i = 0; i < kRing; ++i) {
                     if (flag_ring[i] != nullptr) ptx::st_relaxed_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
                     flag_ring[i] = nullptr;
                 }
+                since_flags = 0;
                 if (!have) {
                     ++st.credit;
                     while (ptx::ld_acquire_sys(ack) != want) {
@@ -860,25 +872,37 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
         if (issuer) ptx::bulk_commit();
         BEP_ROLE_ADD(kRoleIssueNs, t_issue);
         BEP_ROLE_MARK(kRoleFirstIssueNs);
-        // READY flags of the row issued kFlagLag turns ago: its bulk group is complete by now (or is awaited here)
-        if (n >= kFlagLag) {
-            BEP_ROLE_T(t_store);
-            if (issuer) {
-                bulk_wait_group<kFlagLag>();
-                if (fence_flags) ptx::fence_sys();
-            }
-            __syncwarp();
-            if (flag_ring[0] != nullptr) ptx::st_relaxed_sys(flag_ring[0], make_seq(k.epoch, flag_seq[0]));
-            BEP_ROLE_ADD(kRoleStoreWaitNs, t_store);
-            if (w == 0 && lane == 0 && n == kFlagLag) k.prof[kProfFirstTxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
-        }
+        // this row's flags join the ring (an entry that reaches the front has long been stored: flags go out at
+        // least every kFlagBatch rows and the ring holds kFlagBatch + kFlagLag)
 #pragma unroll
-        for (int i = 0; i + 1 < kFlagLag; ++i) {
+        for (int i = 0; i + 1 < kRing; ++i) {
             flag_ring[i] = flag_ring[i + 1];
             flag_seq[i] = flag_seq[i + 1];
         }
-        flag_ring[kFlagLag - 1] = ready;
-        flag_seq[kFlagLag - 1] = static_cast<std::uint32_t>(cur.j + 1);
+        flag_ring[kRing - 1] = ready;
+        flag_seq[kRing - 1] = static_cast<std::uint32_t>(cur.j + 1);
+        ++since_flags;
+        // READY flags of every row but the kFlagLag most recent: their bulk groups are complete after the wait, and
+        // the fence that follows orders those writes before the flags at system scope.  (Completion of a bulk group
+        // alone is not enough: it tells this thread that the writes are done as far as it can see, and with four
+        // ranks and BF16 rows a relaxed flag was seen to overtake part of its row on its way through the switch.)
+        if (since_flags >= flag_batch && n >= kFlagLag) {
+            BEP_ROLE_T(t_store);
+            if (issuer) {
+                bulk_wait_group<kFlagLag>();
+                ptx::fence_sys();
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < kRing - kFlagLag; ++i) {
+                if (flag_ring[i] != nullptr) ptx::st_relaxed_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
+                flag_ring[i] = nullptr;
+            }
+            since_flags = 0;
+            BEP_ROLE_ADD(kRoleStoreWaitNs, t_store);
+            if (w == 0 && lane == 0 && !first_flags_stamped) k.prof[kProfFirstTxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
+            first_flags_stamped = true;
+        }
         if (lane == 0) {
             ++st.source;
             st.deliveries += __popc(cur.mask);
@@ -893,14 +917,14 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
         BEP_ROLE_T(t_store);
         if (issuer) {
             bulk_wait_group<0>();
-            if (fence_flags) ptx::fence_sys();
+            ptx::fence_sys();
         }
         __syncwarp();
         if (!broke && !warp_failed(health)) {
 #pragma unroll
-            for (int i = 0; i < kFlagLag; ++i)
+            for (int i = 0; i < kRing; ++i)
                 if (flag_ring[i] != nullptr) ptx::st_relaxed_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
-            if (w == 0 && lane == 0 && n > 0 && n <= kFlagLag) k.prof[kProfFirstTxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
+            if (w == 0 && lane == 0 && n > 0 && !first_flags_stamped) k.prof[kProfFirstTxDone] = static_cast<std::int64_t>(ptx::globaltimer_ns());
         }
         BEP_ROLE_ADD(kRoleStoreWaitNs, t_store);
         BEP_ROLE_ADD(kRoleDrainNs, t_store);
@@ -1478,6 +1502,11 @@ __global__ void __launch_bounds__(kCtaThreads, 1) dispatch_kernel(const __grid_c
             }
         }
         for (int i = c * static_cast<int>(blockDim.x) + threadIdx.x; i < (groups + 1) * W; i += C * static_cast<int>(blockDim.x)) sums_next[i] = 0;
+        // Every thread makes its own reductions and stores visible to the GPU before it joins the barrier.  The
+        // barrier's one fence (by thread 0, behind the CTA barrier) was enough while the scratch was written with plain
+        // stores; with reductions in flight from the CTA's last warps it was not on every machine: on one four-GPU box
+        // the bins of the highest experts -- the last warps' -- came out short and rows collided at the receiver.
+        __threadfence();
         if (threadIdx.x == 0) BEP_PROF(kProfHistDone);
         grid_barrier(&rc->grid_bar[0], health);
         if (threadIdx.x == 0) BEP_PROF(kProfBarrierDone);
@@ -1900,9 +1929,13 @@ __global__ void __launch_bounds__(kCtaThreads, 1) dispatch_kernel(const __grid_c
                 a.timestamps[1] = last;
             }
             if (!warp_failed(health)) {
-                // one system fence orders every store of this CTA's epilogue; the P flags then go out side by side
-                if (lane < static_cast<unsigned>(P) && static_cast<int>(lane) != rc->test_skip_done_to)
+                // The P flags go out side by side, one lane each.  A publishing lane first reads the CTA counter itself
+                // (acquire): that orders every CTA's reads of the staging area before this lane's release, which the
+                // shuffle that told it the count does not.
+                if (lane < static_cast<unsigned>(P) && static_cast<int>(lane) != rc->test_skip_done_to) {
+                    (void)ptx::ld_acquire_gpu(reinterpret_cast<const std::uint64_t*>(&rc->done_ctas[0]));
                     ptx::st_release_sys(flag_ptr(rc->seg[lane], lay.done_off, me), epoch);
+                }
             }
             __syncwarp();
             if (lane == 0) {

@@ -167,6 +167,28 @@ def test_dispatch_headline_shape_small_t(ext):
             assert stats[2] == volume["remote_deliveries"]
 
 
+@pytest.mark.parametrize("send_ctas", [0, 4])
+def test_dispatch_headline_shape_four_ranks_many_channels(ext, send_ctas):
+    """Four emulated ranks with 32 channels each (two groups of the layout's two-level prefix, several sources per
+    receive warp, rows with up to three remote destinations), with the send warps inside the channel CTAs and with
+    dedicated sender CTAs; repeated, so that the layout's alternating scratch is used on both sides."""
+    from pcie_ep_b200.parallel.virtual import VirtualEPGroup
+
+    world, experts, topk, hidden, tmax = 4, 256, 8, 7168, 128
+    config = HostStagedConfig(channels=32, timeout_ms=5000, tx_warps=2 if send_ctas == 0 else 4, rx_warps=8, send_ctas=send_ctas,
+                              output_pool_size=2)
+    with VirtualEPGroup(world, tmax, hidden, topk, experts, config) as group:
+        for repeat in range(4):
+            results, inputs = _run_case(group, world, experts, topk, hidden, tmax, [128, 128, 97, 128], "random", True, 1,
+                                        seed=7 + repeat)
+            for rank in range(world):
+                volume = reference.route_volume(inputs[rank][1], rank, world, experts)
+                stats = results[rank]["stats"].cpu().tolist()
+                assert stats[0] == volume["remote_source_tokens"]
+                assert stats[2] == volume["remote_deliveries"]
+            del results
+
+
 def test_pool_exhaustion_and_release(ext):
     from pcie_ep_b200.parallel.virtual import VirtualEPGroup
 
