@@ -4,9 +4,11 @@
 //   method 0  payload by ordinary stores, then `st.release.sys` of a flag written by exactly one side;
 //             `ld.acquire.sys` on the other side, then plain loads of the payload;
 //   method 1  the chain of the dispatch send warps: payload staged in shared memory and pushed with
-//             `cp.async.bulk` by lane 31, `cp.async.bulk.wait_group 0` on that lane, `__syncwarp()`, then
-//             `st.relaxed.sys` of the flag by lane 0 (no system-scope fence); the other side reads the flag
+//             `cp.async.bulk` by lane 31, `cp.async.bulk.wait_group 0` and `fence.acq_rel.sys` on that lane,
+//             `__syncwarp()`, then `st.relaxed.sys` of the flag by lane 0; the other side reads the flag
 //             with `ld.acquire.sys`, issues `fence.proxy.async` and fetches the payload with a bulk load.
+//             (Without the fence the same chain passed here on two GPUs a million times and still let a flag
+//             overtake part of a 14 KB row on four: a passing litmus is no proof of the rule.)
 // An ACK flag goes the other way in both.
 //
 // role 0 = producer, role 1 = consumer, role -1 = both roles as two CTAs of one cooperative launch on
@@ -78,6 +80,7 @@ __global__ void litmus_kernel(std::uint8_t* mine, std::uint8_t* theirs, int role
                 ptx::bulk_s2g(peer + 256, stage, static_cast<unsigned>(words) * 8u);
                 ptx::bulk_commit();
                 ptx::bulk_wait_all();
+                ptx::fence_sys();
             }
             __syncwarp();
             if (lane == 0) {
