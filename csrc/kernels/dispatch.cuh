@@ -14,9 +14,9 @@
 //                       every *remote* destination rank, then release that row's READY flag there.
 //                       With the bulk-copy engine each send warp runs a software pipeline over a ring
 //                       of `pipeline_stages` shared-memory row buffers: rows are loaded one or two
-//                       tokens ahead, and a row's READY flags are released two rows late, when its
-//                       own bulk group has completed, so neither the HBM read nor the NVLink round
-//                       trip of one row holds up the next.
+//                       tokens ahead, and READY flags are released at least two rows late, several rows
+//                       at a time behind one system-scope fence, so neither the HBM read nor the NVLink
+//                       round trip of one row holds up the next.
 //   warps tx+1..        receive+expand: poll READY flags in local memory, read the staged row once
 //                       and write it to every local expert row (or the unique row).  Rows whose
 //                       destination is this rank itself never touch the staging ring: the receive
@@ -583,7 +583,8 @@ __device__ __forceinline__ bool place_row(const Ctx& k, int s, int j, int token,
 //     shared-memory tile, from which a row's values are picked up when its turn comes;
 //   * payloads run S - 1 rows ahead through a ring of S shared-memory buffers (row n lives in buffer n % S; a
 //     buffer is refilled once the outgoing copies of its previous row have finished reading it);
-//   * a row's READY flags are stored kFlagLag rows late, when its own bulk group has completed.
+//   * a row's READY flags are stored at least kFlagLag rows late, when its own bulk group has completed, together
+//     with those of up to kFlagBatch rows behind one system-scope fence.
 //
 // Ordering of a row and its READY flag.  The payload leaves through the asynchronous proxy
 // (cp.async.bulk shared -> peer global), all copies of one row in one bulk group of the issuing lane.

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("method", [0, 1])
 def test_litmus_two_ctas_one_gpu(ext, method):
-    """method 0: ordinary stores + st.release.sys; method 1: bulk copy, completion wait, flag without a fence."""
+    """method 0: ordinary stores + st.release.sys; method 1: bulk copy, completion wait, system fence, relaxed flag (the send warps' chain)."""
     size, rounds, words = 1 << 16, 50000 if method == 0 else 20000, 512
     a = ext.allocate_device_segment(size, 0)
     b = ext.allocate_device_segment(size, 0)
