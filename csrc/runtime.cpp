@@ -84,6 +84,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         return layout_to_dict(make_segment_layout(P, C, E, K, H, Tmax, payload_slots, combine, fused));
     }, py::arg("P"), py::arg("C"), py::arg("E"), py::arg("K"), py::arg("H"), py::arg("Tmax"), py::arg("payload_slots"),
        py::arg("combine"), py::arg("fused") = false);
+    // dynamic shared memory one dispatch CTA needs with the given roles (no GPU needed: configuration checks and tests)
+    m.def("dispatch_shared_bytes", [](int P, int C, int E, int K, int H, int Tmax, int payload_slots, int tx_warps, int rx_warps,
+                                      bool bulk_engine, int stages, int send_ctas) {
+        return dispatch_shared_bytes(make_segment_layout(P, C, E, K, H, Tmax, payload_slots, true, false), tx_warps, rx_warps, bulk_engine,
+                                     stages, send_ctas);
+    }, py::arg("P"), py::arg("C"), py::arg("E"), py::arg("K"), py::arg("H"), py::arg("Tmax"), py::arg("payload_slots"),
+       py::arg("tx_warps"), py::arg("rx_warps"), py::arg("bulk_engine"), py::arg("stages"), py::arg("send_ctas"));
     m.def("allocate_device_segment", [](std::size_t bytes, int device) {
         c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
         return reinterpret_cast<std::int64_t>(allocate_device_segment(bytes).ptr);

@@ -100,3 +100,20 @@ def test_every_accepted_flag_value_reaches_the_native_options():
     assert scalar["copy_engine"] == "vector" and scalar["force_scalar"] is True
     assert HostStagedConfig(pipeline_stages=2).native_options()["pipeline_stages"] == 2
     assert HostStagedConfig(send_ctas=0).native_options()["send_ctas"] == 0
+
+
+def test_tuned_configurations_fit_the_shared_memory_of_one_cta(ext):
+    """Every tuned configuration of the headline shape keeps its dispatch CTA inside the 227 KB a Blackwell CTA can
+    get, so that the runtime never has to fall back to fewer row buffers or warps than the configuration names."""
+    from pcie_ep_b200 import _C
+
+    limit = 227 * 1024
+    for ranks in (1, 2, 4, 8, 16):
+        for tokens in (128, 512, 1024, 4096, 8192):
+            cfg = HostStagedConfig.tuned(ranks, tokens)
+            send_ctas = cfg.send_ctas if cfg.send_ctas >= 0 else (0 if ranks == 1 else min(16, max(1, cfg.channels // 8)))
+            needed = _C.dispatch_shared_bytes(ranks, cfg.channels, 256, 8, 7168, tokens, 0, cfg.tx_warps, cfg.rx_warps, True,
+                                              cfg.pipeline_stages, send_ctas)
+            assert needed <= limit, (ranks, tokens, needed)
+    # more row buffers than fit are reported as such (the runtime then reduces stages, send warps, receive warps)
+    assert _C.dispatch_shared_bytes(8, 128, 256, 8, 7168, 4096, 0, 4, 8, True, 4, 0) > limit
