@@ -1046,7 +1046,6 @@ __device__ __noinline__ void receive_role(const Ctx& k, int w, const Health& cta
     const DispatchArgs& a = *k.a;
     const RankConst* rc = k.rc;
     const SegmentLayout& lay = k.lay;  // the CTA's copy in shared memory
-    const std::uint64_t* const plan_flags = rc->plan_flags;
     const unsigned lane = ptx::lane_id();
     const unsigned full = 0xffffffffu;
     const bool delayed = w == k.rx_warps - 1;
