@@ -1,0 +1,77 @@
+"""Builds and runs the host model of the dispatch protocol (``csrc/model/protocol_model.cpp``).
+
+    python -m pcie_ep_b200.utils.protocol_model --ranks 4 --slots 2 --epochs 6 --delay-us 20
+    python -m pcie_ep_b200.utils.protocol_model --sanitize --publish relaxed        # ThreadSanitizer names the race
+    python -m pcie_ep_b200.utils.protocol_model --withhold-counts 1 --timeout-ms 300 --expect 12
+
+Ranks are threads, segments are host memory with the kernels' own layout, flags are ``std::atomic_ref``: the
+protocol's rules run under ThreadSanitizer, and the failure scenarios that must not be staged on a shared GPU
+(a rank that never sends counts, never returns credit, never hands its staging area back, writes a wrong sequence)
+run on the CPU.  The program prints one JSON object per rank.
+"""
+
+from __future__ import annotations
+
+import json
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+from typing import Dict, List, Sequence, Tuple
+
+_ROOT = Path(__file__).resolve().parents[2]
+_SOURCE = _ROOT / "csrc" / "model" / "protocol_model.cpp"
+_OUT = Path(__file__).resolve().parents[1] / "_ext" / "model"
+
+
+def _cuda_include() -> List[str]:
+    for candidate in ("/usr/local/cuda/include",):
+        if Path(candidate, "cuda_runtime.h").exists():
+            return ["-I" + candidate]
+    nvcc = shutil.which("nvcc")
+    if nvcc:
+        return ["-I" + str(Path(nvcc).resolve().parents[1] / "include")]
+    return []
+
+
+def build(sanitize: bool = False) -> Path:
+    """Compile the model with the host compiler (``-fsanitize=thread`` on request); returns the executable."""
+    compiler = shutil.which("g++")
+    if compiler is None:
+        raise RuntimeError("no g++ on PATH")
+    _OUT.mkdir(parents=True, exist_ok=True)
+    target = _OUT / ("protocol_model_tsan" if sanitize else "protocol_model")
+    headers = list((_ROOT / "csrc" / "kernels").glob("protocol.cuh")) + [_SOURCE]
+    if target.exists() and all(target.stat().st_mtime >= h.stat().st_mtime for h in headers):
+        return target
+    command = [compiler, "-std=c++20", "-O1", "-g", "-pthread", "-Wno-tsan", "-I" + str(_ROOT / "csrc"), *_cuda_include()]
+    if sanitize:
+        command.append("-fsanitize=thread")
+    command += [str(_SOURCE), "-o", str(target)]
+    done = subprocess.run(command, capture_output=True, text=True)
+    if done.returncode != 0:
+        raise RuntimeError("building the protocol model failed:\n" + done.stderr[-2000:])
+    return target
+
+
+def run(arguments: Sequence[str], sanitize: bool = False, timeout: float = 120.0) -> Tuple[int, List[Dict], str]:
+    """(exit status, one dict per rank, stderr).  Under the sanitizer a reported race makes the status non-zero."""
+    done = subprocess.run([str(build(sanitize)), *map(str, arguments)], capture_output=True, text=True, timeout=timeout)
+    ranks = [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+    return done.returncode, ranks, done.stderr
+
+
+def main() -> None:
+    arguments = sys.argv[1:]
+    sanitize = "--sanitize" in arguments
+    arguments = [a for a in arguments if a != "--sanitize"]
+    status, ranks, stderr = run(arguments, sanitize)
+    for rank in ranks:
+        print(json.dumps(rank))
+    if stderr:
+        print(stderr[-3000:], file=sys.stderr)
+    raise SystemExit(status)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,64 @@
+"""The host model of the dispatch protocol: rules under ThreadSanitizer, failure scenarios on the CPU.
+
+Ranks are threads over host memory with the kernels' own segment layout.  What the GPU suites may only do with
+withheld flags and short timeouts -- and what they may not do at all, such as a rank that stops handing its
+staging area back -- runs here with real concurrency and a race detector."""
+
+import shutil
+
+import pytest
+
+from pcie_ep_b200.utils import protocol_model
+
+pytestmark = pytest.mark.skipif(shutil.which("g++") is None, reason="needs a host C++ compiler")
+
+BASE = ["--ranks", 4, "--channels", 2, "--tokens", 48, "--slots", 2, "--hidden", 64]
+
+
+def _tsan_works() -> bool:
+    try:
+        status, ranks, _ = protocol_model.run(["--ranks", 2, "--tokens", 8, "--epochs", 1], sanitize=True)
+    except RuntimeError:
+        return False
+    return status == 0 and len(ranks) == 2
+
+
+def test_epochs_with_bounded_rings_and_random_delays():
+    status, ranks, _ = protocol_model.run(BASE + ["--epochs", 8, "--delay-us", 20])
+    assert status == 0 and len(ranks) == 4
+    assert all(r["error"] == 0 for r in ranks)
+    # every row that was sent was received by someone, and the credit path was needed (more rows per ring than slots)
+    assert sum(r["rows_sent"] for r in ranks) == sum(r["rows_received"] for r in ranks) > 4 * 8 * 48 / 2
+
+
+@pytest.mark.parametrize("publish", ["release", "fenced"])
+def test_both_correct_publication_chains_deliver_every_row(publish):
+    status, ranks, _ = protocol_model.run(BASE + ["--epochs", 4, "--delay-us", 5, "--publish", publish, "--slots", 0])
+    assert status == 0 and all(r["error"] == 0 for r in ranks)
+
+
+def test_release_publication_is_race_free_under_thread_sanitizer():
+    if not _tsan_works():
+        pytest.skip("ThreadSanitizer is not usable with this compiler")
+    status, ranks, stderr = protocol_model.run(BASE + ["--epochs", 4, "--delay-us", 10, "--publish", "release"], sanitize=True)
+    assert "ThreadSanitizer" not in stderr, stderr[-1500:]
+    assert status == 0 and all(r["error"] == 0 for r in ranks)
+
+
+def test_a_relaxed_flag_without_a_fence_is_reported_as_a_race():
+    """The chain that passed every two-GPU run and failed on four: the detector names it at once."""
+    if not _tsan_works():
+        pytest.skip("ThreadSanitizer is not usable with this compiler")
+    status, _, stderr = protocol_model.run(BASE + ["--epochs", 2, "--delay-us", 10, "--publish", "relaxed"], sanitize=True)
+    assert status != 0 and "data race" in stderr
+
+
+@pytest.mark.parametrize("fault,code", [("--withhold-counts", 12), ("--skip-done", 11), ("--withhold-credit", 23), ("--corrupt-sequence", 18)])
+def test_failure_scenarios_end_in_their_error_code_and_reach_every_rank(fault, code):
+    status, ranks, _ = protocol_model.run(BASE + ["--epochs", 4, fault, 1, "--timeout-ms", 300, "--expect", code])
+    assert status == 0, ranks
+    codes = [r["error"] for r in ranks]
+    assert code in codes                              # someone diagnosed the fault itself ...
+    assert all(c in (code, 22) for c in codes if c)   # ... and everyone else who failed learned of it as a peer's abort
+    if fault != "--corrupt-sequence":
+        assert all(c != 0 for c in codes)             # a rank that goes silent stops every rank, within the timeout
