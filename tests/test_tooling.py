@@ -216,3 +216,38 @@ def test_source_manifest_compare(ext):
     differences = source_manifest.compare(changed, current)
     assert any(d.startswith("modified: csrc/kernels/dispatch.cuh") for d in differences)
     assert any(d.startswith("added: csrc/kernels/ptx.cuh") for d in differences) and any("cuda_flags" in d for d in differences)
+
+
+def test_run_matrix_plans_sequential_jobs_and_records_them(tmp_path):
+    from benchmarks import run_matrix
+
+    parser = run_matrix.build_parser()
+    args = parser.parse_args(["bench", "--gpus", "4", "--rounds", "2", "--modes", "eager", "graph_cached", "--wires", "bf16", "fp8_e4m3",
+                              "--profiles", "uniform", "zipf", "--results", str(tmp_path), "--run-id", "unit_1"])
+    jobs = run_matrix.bench_jobs(args, tmp_path / "unit_1")
+    assert len(jobs) == 2 * (1 + 2 * 2 * 2 + 1)                       # headline + matrix + NCCL comparison, per round
+    ports = [j["command"][j["command"].index("--master-port") + 1] for j in jobs]
+    assert len(set(ports)) == len(ports)                               # no two jobs share a rendezvous port
+    assert all("--master-addr" in j["command"] and "127.0.0.1" in j["command"] for j in jobs)
+    zipf = [j for j in jobs if j["name"].endswith("eager_bf16_zipf")][0]
+    assert zipf["command"][-2:] == ["--topk", "4"] and str(zipf["record"]).endswith("eager_bf16_zipf.json")
+
+    ran = []
+
+    def fake(job):
+        ran.append(job["name"])
+        job["log"].parent.mkdir(parents=True, exist_ok=True)
+        job["log"].write_text("")
+        return 3 if job["name"].endswith("nccl") else 0
+
+    assert run_matrix.run(args, runner=fake) == 1                      # a failed job fails the run, but every job still ran
+    assert ran == [j["name"] for j in jobs]
+    manifest = json.loads((tmp_path / "unit_1" / "manifest.json").read_text())
+    assert [j["exit"] for j in manifest["jobs"]].count(3) == 2 and manifest["sources"]["fingerprint"]
+
+    with pytest.raises(SystemExit):
+        run_matrix.run(parser.parse_args(["bench", "--run-id", "bad id", "--results", str(tmp_path)]), runner=fake)
+    single = run_matrix.validate_jobs(parser.parse_args(["validate", "--group", "all", "--gpus", "1"]), tmp_path / "v")
+    assert [j["name"] for j in single] == [g for g in run_matrix.GROUPS if g != "all"]
+    assert single[3]["command"][0].endswith("python") or "python" in single[3]["command"][0]   # one GPU: no torchrun
+    assert "torch.distributed.run" not in single[3]["command"]
