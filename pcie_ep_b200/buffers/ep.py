@@ -93,6 +93,8 @@ class HostStagedEPBuffer:
         self._generation = 0
         self._failed = self._closed = False
         self._last_event: Any = None
+        self._watchdog: Any = None
+        self._launches_watched = 0
         self._last_handle: Optional[HostStagedEPHandle] = None
         self._graph_capture: Any = None
         self._extension: Any = None
@@ -188,7 +190,15 @@ class HostStagedEPBuffer:
         event.record(stream)
         self._last_event = event
         self._streams.finish(compute, stream, event, run_async)
+        if self._watchdog is not None:
+            self._launches_watched += 1
+            self._watchdog.watch(f"rank {self.rank_idx} launch {self._launches_watched}", event.query)
         return value, event
+
+    def attach_watchdog(self, watchdog: Any) -> None:
+        """Have ``watchdog`` (``pcie_ep_b200.utils.watchdog.ProgressWatchdog``, or None to detach) told about every
+        launch of this buffer; it only queries the launch's event and reports, it never touches the GPU."""
+        self._watchdog = watchdog
 
     # ------------------------------------------------------------------ dispatch
     def dispatch(
