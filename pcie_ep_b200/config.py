@@ -84,11 +84,12 @@ class HostStagedConfig:
         down-projection GEMM's epilogue then writes each weighted output row straight into the token
         owner's memory and a short reduction sums the K slots (expanded dispatches only, ``hidden`` a
         multiple of 256).
-    combine_reduce: ``"separate"`` runs the owner-side sum of ``combine`` as a second, fully occupied
-        kernel after the cooperative kernel that reduces and pushes the expert-side rows; ``"inline"``
-        does both in the one cooperative kernel, which starts adding rows as they arrive but is
-        register-bound; ``"auto"`` (default) takes ``"separate"`` whenever there is more than one rank.  Hidden sizes whose
-        rows are not 16-byte multiples always take ``"inline"``.
+    combine_reduce: ``"separate"`` runs ``combine`` as two ordinary launches: reducer CTAs sum a token's
+        local expert rows and forwarder CTAs push the rows owned by other ranks, then a fully occupied
+        owner-side launch adds the ranks' rows; ``"inline"`` does both in one cooperative kernel, which
+        starts adding rows as they arrive but is register-bound; ``"auto"`` (default) takes ``"separate"``
+        whenever there is more than one rank.  Hidden sizes whose rows are not 16-byte multiples and the CPU
+        relay always take ``"inline"``.
     """
 
     payload_slots: int = 0
