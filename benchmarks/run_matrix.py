@@ -10,6 +10,7 @@ log and, where the tool writes one, its own JSON record under ``results/<run id>
 ``manifest.json``: the source manifest of the tree (``benchmarks/source_manifest.py``), the arguments, every job's
 command, exit status and duration.  Jobs never overlap: two of these programs on the same GPUs would wait for each
 other's kernels.  A failing job does not stop the run; the exit status of the whole run is non-zero if any job failed.
+Before a ``bench`` run NVML is asked (read-only) whether the GPUs are there and idle; busy GPUs end the run with status 3.
 After a ``bench`` run the tables of ``benchmarks/report.py`` are printed from the records just written.
 
 Parity: the reference's ``scripts/benchmark_f2.sh`` (sequential rounds with run ids, result directories, dry run)
@@ -101,6 +102,36 @@ def validate_jobs(args: argparse.Namespace, run_dir: Path) -> List[Dict]:
     return jobs
 
 
+def preflight(gpus: int, nvml: object = None) -> List[str]:
+    """Reasons not to benchmark now: GPUs that are missing or already busy.  Only reads (NVML queries); never changes a
+    clock, a power limit or any other setting of a GPU."""
+    try:
+        if nvml is None:
+            import pynvml as nvml  # type: ignore[no-redef]
+        nvml.nvmlInit()
+    except Exception as exc:  # noqa: BLE001 - no NVML: nothing to check against
+        return [f"NVML is not available ({type(exc).__name__}): the GPUs' state is unknown"]
+    problems = []
+    try:
+        count = nvml.nvmlDeviceGetCount()
+        if count < gpus:
+            problems.append(f"{gpus} GPUs wanted, {count} present")
+        for index in range(min(gpus, count)):
+            handle = nvml.nvmlDeviceGetHandleByIndex(index)
+            processes = nvml.nvmlDeviceGetComputeRunningProcesses(handle)
+            busy = nvml.nvmlDeviceGetUtilizationRates(handle).gpu
+            if processes:
+                problems.append(f"GPU {index}: {len(processes)} compute process(es) already running")
+            elif busy > 10:
+                problems.append(f"GPU {index}: {busy} % busy")
+    finally:
+        try:
+            nvml.nvmlShutdown()
+        except Exception:  # noqa: BLE001
+            pass
+    return problems
+
+
 def execute(job: Dict) -> int:
     job["log"].parent.mkdir(parents=True, exist_ok=True)
     with open(job["log"], "w") as log:
@@ -117,6 +148,11 @@ def run(args: argparse.Namespace, runner: Callable[[Dict], int] = execute) -> in
         for job in jobs:
             print(job["name"] + ": " + " ".join(job["command"]))
         return 0
+    if args.what == "bench" and args.preflight:
+        problems = preflight(args.gpus)
+        if problems:
+            print("not benchmarking: " + "; ".join(problems) + "  (--no-preflight runs anyway)", file=sys.stderr)
+            return 3
     run_dir.mkdir(parents=True, exist_ok=True)
     from benchmarks import source_manifest
 
@@ -177,6 +213,8 @@ def build_parser() -> argparse.ArgumentParser:
             p.add_argument("--wires", nargs="+", default=["bf16"], choices=["bf16", "fp8_e4m3"])
             p.add_argument("--profiles", nargs="+", default=["uniform"], choices=["uniform", "hotspot_20_80", "zipf", "nvidia_calibrated"])
             p.add_argument("--no-nccl", dest="nccl", action="store_false")
+            p.add_argument("--no-preflight", dest="preflight", action="store_false",
+                           help="benchmark even if NVML shows other compute processes or load on the GPUs")
         else:
             p.add_argument("--group", default="smoke", choices=GROUPS)
     return parser

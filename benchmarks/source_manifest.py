@@ -16,7 +16,9 @@ The audit reads the kernels as text and checks the rules the protocol relies on:
   the segment of a peer is only written with plain stores and only polled locally, so no atomic may take an
   address formed from the peer table;
 * every loop that polls a flag or an mbarrier carries a deadline (a bounded wait that records an error code);
-* no load with cluster multicast and none of the batched copy calls that this library never uses.
+* no load with cluster multicast and none of the batched copy calls that this library never uses;
+* the Python launch path (dispatch, combine, the fused launch, graph replay, the stream policy) calls nothing that
+  makes the host wait for the device or reads device memory back (`.item()`, `.cpu()`, `.tolist()`, `synchronize`, ...).
 
 Parity: the reference's ``scripts/source_manifest.py`` and the read-modify-write provenance part of its
 ``scripts/collect_advanced_path_audit.py`` (its machine-code dump is not reproduced).
@@ -124,12 +126,41 @@ def audit_text(name: str, text: str) -> Dict[str, List[str]]:
     return {"atomics": atomics, "violations": violations}
 
 
+# Calls that make the host wait for the device or read device memory back.  The launch path (dispatch, combine, the
+# fused launch, a graph replay and what they go through) must contain none: sizes stay on the device, errors are only
+# read by check_errors().
+HOST_WAITING_CALLS = ("item", "cpu", "tolist", "numpy", "synchronize")
+HOT_PATH = {
+    "pcie_ep_b200/buffers/ep.py": ("dispatch", "combine", "fused_expert_combine", "_enqueue", "capture_dispatch"),
+    "pcie_ep_b200/graph.py": ("replay",),
+    "pcie_ep_b200/buffers/streams.py": ("begin", "finish", "current"),
+}
+
+
+def audit_python(name: str, text: str, functions: tuple) -> List[str]:
+    """Host-waiting calls inside the named functions of one Python source (nested helpers included)."""
+    import ast
+
+    found = []
+    tree = ast.parse(text)
+    for node in ast.walk(tree):
+        if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef)) and node.name in functions:
+            for inner in ast.walk(node):
+                if isinstance(inner, ast.Call) and isinstance(inner.func, ast.Attribute) and inner.func.attr in HOST_WAITING_CALLS:
+                    found.append(f"{name}:{inner.lineno}: {node.name}() calls .{inner.func.attr}()")
+    return found
+
+
 def audit(root: Path = ROOT) -> Dict[str, List[str]]:
     result: Dict[str, List[str]] = {"atomics": [], "violations": []}
     for path in native_files(root):
         part = audit_text(str(path.relative_to(root)), path.read_text())
         result["atomics"] += part["atomics"]
         result["violations"] += part["violations"]
+    for name, functions in HOT_PATH.items():
+        path = root / name
+        if path.exists():
+            result["violations"] += audit_python(name, path.read_text(), functions)
     return result
 
 

@@ -240,6 +240,7 @@ def test_run_matrix_plans_sequential_jobs_and_records_them(tmp_path):
         job["log"].write_text("")
         return 3 if job["name"].endswith("nccl") else 0
 
+    args.preflight = False
     assert run_matrix.run(args, runner=fake) == 1                      # a failed job fails the run, but every job still ran
     assert ran == [j["name"] for j in jobs]
     manifest = json.loads((tmp_path / "unit_1" / "manifest.json").read_text())
@@ -251,3 +252,39 @@ def test_run_matrix_plans_sequential_jobs_and_records_them(tmp_path):
     assert [j["name"] for j in single] == [g for g in run_matrix.GROUPS if g != "all"]
     assert single[3]["command"][0].endswith("python") or "python" in single[3]["command"][0]   # one GPU: no torchrun
     assert "torch.distributed.run" not in single[3]["command"]
+
+
+def test_preflight_only_reads_and_names_busy_gpus():
+    from types import SimpleNamespace
+
+    from benchmarks import run_matrix
+
+    calls = []
+
+    class FakeNvml:
+        def __init__(self, processes, busy):
+            self.processes, self.busy = processes, busy
+
+        def __getattr__(self, name):
+            calls.append(name)
+            table = {
+                "nvmlInit": lambda: None, "nvmlShutdown": lambda: None, "nvmlDeviceGetCount": lambda: 2,
+                "nvmlDeviceGetHandleByIndex": lambda i: i,
+                "nvmlDeviceGetComputeRunningProcesses": lambda h: self.processes[h],
+                "nvmlDeviceGetUtilizationRates": lambda h: SimpleNamespace(gpu=self.busy[h]),
+            }
+            return table[name]
+
+    assert run_matrix.preflight(2, FakeNvml([[], []], [0, 3])) == []
+    problems = run_matrix.preflight(4, FakeNvml([[1], []], [0, 55]))
+    assert problems == ["4 GPUs wanted, 2 present", "GPU 0: 1 compute process(es) already running", "GPU 1: 55 % busy"]
+    assert all(name.startswith(("nvmlInit", "nvmlShutdown", "nvmlDeviceGet")) for name in calls)   # queries only, no setters
+
+
+def test_python_launch_path_audit_sees_host_waits():
+    from benchmarks import source_manifest
+
+    bad = "class B:\n    def dispatch(self, x):\n        n = x.sum().item()\n        def inner():\n            torch.cuda.synchronize()\n        return n\n    def other(self, x):\n        return x.cpu()\n"
+    found = source_manifest.audit_python("b.py", bad, ("dispatch",))
+    assert len(found) == 2 and ".item()" in found[0] and ".synchronize()" in found[1]
+    assert source_manifest.audit()["violations"] == []
