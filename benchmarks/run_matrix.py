@@ -34,7 +34,7 @@ sys.path.insert(0, str(ROOT))
 
 RUN_ID = re.compile(r"^[A-Za-z0-9_-]+$")
 TOKENS = (128, 256, 1024, 4096, 8192)
-GROUPS = ("smoke", "correctness", "faults", "large", "litmus", "layer", "profiler", "model", "all")
+GROUPS = ("smoke", "correctness", "faults", "large", "stress", "litmus", "layer", "profiler", "model", "all")
 
 
 def launcher(gpus: int, port: int) -> List[str]:
@@ -89,6 +89,8 @@ def validate_jobs(args: argparse.Namespace, run_dir: Path) -> List[Dict]:
         elif group == "large":
             command = launcher(args.gpus, port) + ["tests/workers/ep_worker.py", "--transport", "peer", "--suite", "large", "--tokens",
                                                    "4096,8192", "--timeout-ms", "20000"]
+        elif group == "stress":
+            command = pytest + ["-m", "gpu", "tests/test_gpu_scale.py", "-k", "epochs"]
         elif group == "litmus":
             command = pytest + ["-m", "gpu", "tests/test_gpu_litmus.py"]
         elif group == "layer":
@@ -97,7 +99,10 @@ def validate_jobs(args: argparse.Namespace, run_dir: Path) -> List[Dict]:
             command = [sys.executable, "benchmarks/analysis_dispatch_profile.py", "--collect", str(run_dir / group / "trace.json"), "--tokens", "1024"]
         else:  # model: the host model of the protocol, also under ThreadSanitizer (no GPU)
             command = pytest + ["tests/test_protocol_model.py"]
-        jobs.append({"name": group, "log": run_dir / group / "log.txt", "record": None, "command": command})
+        job = {"name": group, "log": run_dir / group / "log.txt", "record": None, "command": command}
+        if group == "stress":
+            job["env"] = {"PCIE_EP_B200_STRESS_EPOCHS": str(args.stress_epochs)}
+        jobs.append(job)
         port += 1
     return jobs
 
@@ -135,7 +140,8 @@ def preflight(gpus: int, nvml: object = None) -> List[str]:
 def execute(job: Dict) -> int:
     job["log"].parent.mkdir(parents=True, exist_ok=True)
     with open(job["log"], "w") as log:
-        return subprocess.run(job["command"], cwd=str(ROOT), stdout=log, stderr=subprocess.STDOUT).returncode
+        return subprocess.run(job["command"], cwd=str(ROOT), stdout=log, stderr=subprocess.STDOUT,
+                              env=dict(os.environ, **job.get("env", {}))).returncode
 
 
 def run(args: argparse.Namespace, runner: Callable[[Dict], int] = execute) -> int:
@@ -217,6 +223,7 @@ def build_parser() -> argparse.ArgumentParser:
                            help="benchmark even if NVML shows other compute processes or load on the GPUs")
         else:
             p.add_argument("--group", default="smoke", choices=GROUPS)
+            p.add_argument("--stress-epochs", type=int, default=100000, help="back-to-back epochs of the stress group")
     return parser
 
 
