@@ -32,6 +32,8 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 HIDDEN, EXPERTS, TOPK = 7168, 256, 8
+VERIFY_ROUNDS = 3  # verified exchanges before (and after) the timed loops of every configuration
+
 # both arms name the same model and shape in their result line
 MODEL_NAME = "DeepSeek-V3-shaped MoE exchange (hidden 7168, 256 experts, top-%d)"
 
@@ -269,6 +271,24 @@ def hashed_tokens(rank, tokens, hidden, device):
     return (((rank * 131 + t * 7 + c * 3) % 251) - 125).to(torch.bfloat16)
 
 
+def repeated_check(verify, all_gather, world, rounds=None):
+    """``rounds`` verified exchanges (not timed), every rank in step: (this rank's last verdict, the verdicts of all
+    ranks from the last round, whether every verdict of every round was fine).  Stops at the first round that any rank
+    found wrong; an error raised by a check counts as that rank's verdict, so that all ranks keep making the same
+    collective calls."""
+    verdict, gathered = None, []
+    for _ in range(VERIFY_ROUNDS if rounds is None else rounds):
+        try:
+            verdict = verify()
+        except RuntimeError as exc:  # an error word from the device: this buffer is finished
+            verdict = {"ok": False, "rows_checked": 0, "elements_checked": 0, "problems": [str(exc)[:200]]}
+        gathered = [None] * world
+        all_gather(gathered, verdict)
+        if not all(v["ok"] for v in gathered):
+            return verdict, gathered, False
+    return verdict, gathered, True
+
+
 def verify_exchange(buffer, rank, world, tokens, topk, idx_cpu, dev_idx, dev_w, device, wire="bf16"):
     """One dispatch + combine with regenerable payload: every received row is compared, on the GPU, with the row
     its (source rank, source token) metadata says it must be; dedup counters are compared with the route volume;
@@ -348,26 +368,44 @@ def run_ours(args, rank, world, local_rank):
                                   output_pool_size=2, tx_warps=args.tx_warps or tuned.tx_warps, rx_warps=args.rx_warps or tuned.rx_warps,
                                   combine_reduce=args.combine_reduce, send_ctas=args.send_ctas,
                                   pipeline_stages=args.stages or tuned.pipeline_stages)
+        idx_cpu, w_cpu = make_routes(tokens, EXPERTS, args.topk, rank)
+        dev_idx, dev_w = idx_cpu.to(device), w_cpu.to(device)
+
+        def checked_exchanges(buf):
+            return repeated_check(lambda: verify_exchange(buf, rank, world, tokens, args.topk, idx_cpu, dev_idx, dev_w, device, args.wire),
+                                  dist.all_gather_object, world)
+
+        # correctness evidence inside this very run: payload, dedup counters and the round trip (not timed).  Should
+        # the exchange deliver a wrong row, the run is repeated once with one system-scope fence per row (the
+        # conservative way to publish a row) and says so in its result line; a second failure ends it.
         buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
+        payload_check, verdicts, fine = checked_exchanges(buffer)
+        conservative = None
+        if not fine and world > 1 and os.environ.get("PCIE_EP_B200_FENCE_EVERY_ROW") != "1":
+            conservative = {"mode": "one system-scope fence per row", "after": [v["problems"] for v in verdicts if not v["ok"]][:2]}
+            try:
+                buffer.close()
+            except Exception:  # noqa: BLE001 - a buffer that failed on the device may refuse an orderly close
+                pass
+            os.environ["PCIE_EP_B200_FENCE_EVERY_ROW"] = "1"
+            buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
+            payload_check, verdicts, fine = checked_exchanges(buffer)
+        if not fine:
+            raise RuntimeError(f"payload check failed: {[v['problems'] for v in verdicts if not v['ok']]}")
+        payload_check["elements_checked_all_ranks"] = sum(v["elements_checked"] for v in verdicts)
+        payload_check["rounds"] = VERIFY_ROUNDS
+        if conservative is not None:
+            payload_check["conservative_flags"] = conservative
         g = torch.Generator().manual_seed(1234 + rank)
         host_x = [torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16).pin_memory() for _ in range(INPUT_SETS)]
-        idx_cpu, w_cpu = make_routes(tokens, EXPERTS, args.topk, rank)
         host_idx, host_w = idx_cpu.pin_memory(), w_cpu.pin_memory()
         dev_x = [h.to(device) for h in host_x]
-        dev_idx, dev_w = host_idx.to(device), host_w.to(device)
 
         def step(i):
             recv_x, _, _, handle, _ = buffer.dispatch(dev_x[i % INPUT_SETS], dev_idx, dev_w, do_expand=True)
             combined, _, _ = buffer.combine(recv_x, handle)
             return combined, handle
 
-        # correctness evidence inside this very run: payload, dedup counters and the round trip (not timed)
-        payload_check = verify_exchange(buffer, rank, world, tokens, args.topk, idx_cpu, dev_idx, dev_w, device, args.wire)
-        verdicts = [None] * world
-        dist.all_gather_object(verdicts, payload_check)
-        if not all(v["ok"] for v in verdicts):
-            raise RuntimeError(f"payload check failed: {[v['problems'] for v in verdicts if not v['ok']]}")
-        payload_check["elements_checked_all_ranks"] = sum(v["elements_checked"] for v in verdicts)
         for i in range(warmup):
             out, handle = step(i)
         torch.cuda.synchronize()
@@ -494,6 +532,9 @@ def run_ours(args, rank, world, local_rank):
                              "how": "inputs double-buffered: a copy stream uploads step i+1 from pinned memory while step i runs; every step ends with a blocking 4-byte read of its checksum",
                              "host_numa_node": numa_node}
             buffer.check_errors()
+        # and once more after everything that was timed: the exchange still delivers what it should
+        after, after_all, after_fine = checked_exchanges(buffer)
+        result["payload_check_after"] = {"ok": after_fine, "problems": [v["problems"] for v in after_all if not v["ok"]][:2]}
         buffer.close()
         return result
 
@@ -555,6 +596,9 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": headline["launches_per_step"] * args.steps,
             "kernels_per_step": ", ".join(headline["kernels"]),
             "payload_check": headline["payload_check"],
+            "payload_check_after": headline.get("payload_check_after"),
+            "flag_publication": ("one system-scope fence per row" if os.environ.get("PCIE_EP_B200_FENCE_EVERY_ROW") == "1"
+                                 else "READY flags of up to eight rows behind one system-scope fence"),
             "impl": "ours",
             "source_fingerprint": source_fingerprint(),
         }

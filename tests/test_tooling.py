@@ -288,3 +288,38 @@ def test_python_launch_path_audit_sees_host_waits():
     found = source_manifest.audit_python("b.py", bad, ("dispatch",))
     assert len(found) == 2 and ".item()" in found[0] and ".synchronize()" in found[1]
     assert source_manifest.audit()["violations"] == []
+
+
+def test_bench_repeated_check_keeps_ranks_in_step_and_stops_at_the_first_bad_round():
+    import bench
+
+    calls = {"verify": 0, "gather": 0}
+
+    def gather_two(out, mine):               # the other rank always agrees with this one
+        calls["gather"] += 1
+        out[0], out[1] = mine, dict(mine)
+
+    def fine():
+        calls["verify"] += 1
+        return {"ok": True, "rows_checked": 4, "elements_checked": 8, "problems": []}
+
+    verdict, everyone, ok = bench.repeated_check(fine, gather_two, 2, rounds=3)
+    assert ok and calls == {"verify": 3, "gather": 3} and len(everyone) == 2 and verdict["rows_checked"] == 4
+
+    sequence = iter([True, False, True])
+
+    def second_round_bad():
+        if next(sequence):
+            return {"ok": True, "rows_checked": 1, "elements_checked": 1, "problems": []}
+        raise RuntimeError("EP dispatch GPU error on rank 1: [18, 0, 3]")
+
+    calls["gather"] = 0
+    verdict, everyone, ok = bench.repeated_check(second_round_bad, gather_two, 2, rounds=3)
+    assert not ok and calls["gather"] == 2                       # the failing round is still gathered, the third never runs
+    assert verdict["ok"] is False and "GPU error" in verdict["problems"][0]
+
+    def peer_bad(out, mine):                 # this rank is fine, the other one is not
+        out[0], out[1] = mine, {"ok": False, "rows_checked": 0, "elements_checked": 0, "problems": ["rows 0..4096 differ"]}
+
+    verdict, everyone, ok = bench.repeated_check(fine, peer_bad, 2, rounds=3)
+    assert not ok and verdict["ok"] is True and everyone[1]["problems"] == ["rows 0..4096 differ"]
