@@ -111,7 +111,7 @@ bool give_up(World& w, int me, Clock::time_point deadline, int code, int context
         fail(w, me, code, context);
         return true;
     }
-    std::this_thread::yield();
+    std::this_thread::sleep_for(std::chrono::microseconds(20));  // (a probe of a bounded wait backs off, like the kernels' waits)
     return false;
 }
 

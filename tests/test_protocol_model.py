@@ -55,7 +55,7 @@ def test_a_relaxed_flag_without_a_fence_is_reported_as_a_race():
 
 @pytest.mark.parametrize("fault,code", [("--withhold-counts", 12), ("--skip-done", 11), ("--withhold-credit", 23), ("--corrupt-sequence", 18)])
 def test_failure_scenarios_end_in_their_error_code_and_reach_every_rank(fault, code):
-    status, ranks, _ = protocol_model.run(BASE + ["--epochs", 4, fault, 1, "--timeout-ms", 300, "--expect", code])
+    status, ranks, _ = protocol_model.run(BASE + ["--epochs", 4, fault, 1, "--timeout-ms", 800, "--expect", code])
     assert status == 0, ranks
     codes = [r["error"] for r in ranks]
     assert code in codes                              # someone diagnosed the fault itself ...
