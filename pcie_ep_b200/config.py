@@ -188,7 +188,7 @@ class HostStagedConfig:
         if not self.warp_specialization:
             raise NotImplementedError("warp_specialization=False (one homogeneous role per CTA) is not built; the kernel is warp-specialised")
         if not self.fuse_receive_expand:
-            raise NotImplementedError("fuse_receive_expand=False (unique rows first, a separate scatter launch afterwards) is not built")
+            raise NotImplementedError("fuse_receive_expand=False is not a mode of the dispatch kernel; for the two-step form call dispatch(do_expand=False) and ops.unfused_expand.scatter_expert_inputs")
         if not self.source_fusion:
             raise NotImplementedError("source_fusion=False is not built: send warps always read routes and weights from the live inputs")
         if self.replica_slots != 256:
