@@ -196,7 +196,7 @@ class HostStagedConfig:
 
     @classmethod
     def tuned(cls, num_ranks: int, num_max_tokens_per_rank: int, **overrides) -> "HostStagedConfig":
-        """The settings measured best on 8x B200 for a buffer of this size, with ``overrides`` on top.
+        """The settings measured best on B200 (one to four ranks) for a buffer of this size, with ``overrides`` on top.
 
         Channels (= channel CTAs per rank): 32 up to 256 tokens per rank, 64 up to 1024, 128 beyond -- few CTAs keep
         the grid barrier and the counts exchange short at small T, many keep HBM busy at large T.  Eight
