@@ -1,11 +1,17 @@
-// Host model of the dispatch data plane: ranks are threads, segments are plain memory, every flag is a
+// Host model of the dispatch data plane (and, with --combine 1, of the combine that follows it): ranks are threads, segments are plain memory, every flag is a
 // std::atomic_ref on the same offsets the kernels use (SegmentLayout and make_seq come from the kernels' own
 // header).  It exists for two reasons.  It is an executable statement of the protocol's rules -- single-writer
 // epoch-valued flags, local polling, counts before rows, credit before a ring slot is reused, `done` before the next
 // epoch's first remote write, bounded waits that end in an error code and an abort every peer sees -- that runs
 // under ThreadSanitizer, which no GPU tool on hand can do for the kernels.  And failure scenarios that must not be
 // staged on a shared GPU (a rank that never sends its counts, never returns credit, never hands its staging area
-// back, writes a wrong sequence) run here instead.
+// back, writes a wrong sequence, never signals that its combine rows are out, never hands the landing area back) run
+// here instead.
+//
+// Combine (--combine 1), the form with a separate owner-side sum: the rank that received a token's row for epoch e
+// writes one result row into the owner's landing area [rank][token], behind the reuse guard `cdone >= e - 1` of every
+// owner; when all its rows are out it releases `csig = e` to every owner.  An owner acquires every peer's `csig`,
+// reads the landing rows of the ranks each token went to, and releases `cdone = e` to every peer.
 //
 // Publication of a row, selectable so that the rule can be seen to matter:
 //   release   payload by ordinary stores, flag by a release store (what `st.release.sys` is on the GPU);
@@ -24,6 +30,7 @@
 #include <cstring>
 #include <string>
 #include <thread>
+#include <utility>
 #include <vector>
 
 #include "kernels/protocol.cuh"
@@ -41,6 +48,9 @@ struct Options {
     int withhold_credit = -1;    // this rank never acknowledges rows (ring mode)
     int skip_done = -1;          // this rank never hands its staging area back
     int corrupt_sequence = -1;   // this rank writes a wrong sequence into its rows
+    int combine = 0;             // 1: every epoch's dispatch is followed by its combine
+    int withhold_signal = -1;    // this rank never signals that its combine rows are out
+    int skip_combine_done = -1;  // this rank never hands the combine landing area back
     int expect = 0;              // error code every failing rank is expected to end with (0: nobody fails)
     std::string publish = "release";
     unsigned seed = 1;
@@ -52,6 +62,7 @@ struct Rank {
     std::atomic<int> context{0};
     long long rows_received = 0;
     long long rows_sent = 0;
+    long long rows_combined = 0;  // landing rows this rank read as an owner
 };
 
 struct World {
@@ -135,6 +146,40 @@ Plan make_plan(const Options& o, int s, int e) {
     return p;
 }
 
+// Owner side of the combine of one epoch: every peer's rows have landed (its signal says so), then every token's rows
+// are read from the ranks the token went to.  False when the rank has failed.
+bool combine_owner(World& w, int me, int epoch) {
+    const Options& o = w.opt;
+    const SegmentLayout& lay = w.lay;
+    // between the expert side's reuse guard (which a missing signal may be the consequence of) and the next epoch's
+    // counts wait (which is the consequence of an owner stuck here)
+    const auto deadline = Clock::now() + std::chrono::milliseconds(o.timeout_ms + o.timeout_ms / 16);
+    for (int r = 0; r < o.ranks; ++r) {
+        auto sig = flag_at(w.rank[me].segment, lay.csig_off + static_cast<std::size_t>(r) * bep::kFlagStride);
+        while (sig.load(std::memory_order_acquire) < static_cast<std::uint64_t>(epoch))
+            if (give_up(w, me, deadline, bep::kErrFusedSignalWait, r)) return false;
+    }
+    for (int t = 0; t < o.tokens; ++t) {
+        const unsigned mask = route_mask(o, me, t, epoch);
+        for (int r = 0; r < o.ranks; ++r) {
+            if (!(mask >> r & 1u)) continue;
+            const auto* row = reinterpret_cast<const std::uint16_t*>(w.rank[me].segment.data() + lay.cstage_off +
+                                                                     (static_cast<std::size_t>(r) * o.tokens + t) * lay.crow_stride);
+            for (int col = 0; col < o.hidden; ++col) {
+                if (row[col] != static_cast<std::uint16_t>(payload_word(me, t, epoch, col) + r)) {
+                    fail(w, me, 98, r);  // a landing row that is not what the expert's rank made of this token: never expected
+                    return false;
+                }
+            }
+            ++w.rank[me].rows_combined;
+        }
+    }
+    if (me != o.skip_combine_done)
+        for (int p = 0; p < o.ranks; ++p)
+            flag_at(w.rank[p].segment, lay.cdone_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
+    return true;
+}
+
 void sender(World& w, int me) {
     const Options& o = w.opt;
     const SegmentLayout& lay = w.lay;
@@ -197,6 +242,7 @@ void sender(World& w, int me) {
                 ++w.rank[me].rows_sent;
             }
         }
+        if (o.combine && !combine_owner(w, me, epoch)) return;
     }
 }
 
@@ -217,6 +263,7 @@ void receiver(World& w, int me) {
         }
         // rows of every (source, channel) in row order; sources are visited round-robin like the receive warps do
         std::vector<int> next(static_cast<std::size_t>(o.ranks) * o.channels, 0);
+        std::vector<std::pair<int, int>> received;  // (source, token) of every row, for the combine
         bool pending = true;
         while (pending) {
             pending = false;
@@ -247,6 +294,7 @@ void receiver(World& w, int me) {
                         }
                     }
                     ++w.rank[me].rows_received;
+                    if (o.combine) received.emplace_back(s, token);
                     if (lay.slots < lay.slots_full && me != o.withhold_credit) {
                         // credit back to the source (in the source's segment, written by this rank only)
                         auto ack = flag_at(w.rank[s].segment, lay.ack_off + ((static_cast<std::size_t>(me) * o.channels + c) * lay.slots + static_cast<std::size_t>(j % lay.slots)) * 8);
@@ -260,6 +308,23 @@ void receiver(World& w, int me) {
         if (me != o.skip_done)
             for (int s = 0; s < o.ranks; ++s)
                 flag_at(w.rank[s].segment, lay.done_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
+        if (!o.combine) continue;
+        // expert side of the combine.  Reuse guard: every owner has read the previous epoch out of its landing area
+        const auto guard_deadline = Clock::now() + std::chrono::milliseconds(o.timeout_ms);
+        for (int p = 0; p < o.ranks; ++p) {
+            auto done = flag_at(w.rank[me].segment, lay.cdone_off + static_cast<std::size_t>(p) * bep::kFlagStride);
+            while (done.load(std::memory_order_acquire) + 1 < static_cast<std::uint64_t>(epoch))
+                if (give_up(w, me, guard_deadline, bep::kErrReuseGuardWait, p)) return;
+        }
+        for (const auto& [s, token] : received) {
+            auto* row = reinterpret_cast<std::uint16_t*>(w.rank[s].segment.data() + lay.cstage_off +
+                                                         (static_cast<std::size_t>(me) * o.tokens + token) * lay.crow_stride);
+            for (int col = 0; col < o.hidden; ++col) row[col] = static_cast<std::uint16_t>(payload_word(s, token, epoch, col) + me);
+            random_delay(o, rng);
+        }
+        if (me != o.withhold_signal)
+            for (int p = 0; p < o.ranks; ++p)
+                flag_at(w.rank[p].segment, lay.csig_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
     }
 }
 
@@ -285,6 +350,9 @@ int main(int argc, char** argv) {
         else if (key == "--withhold-credit") o.withhold_credit = to_int(v);
         else if (key == "--skip-done") o.skip_done = to_int(v);
         else if (key == "--corrupt-sequence") o.corrupt_sequence = to_int(v);
+        else if (key == "--combine") o.combine = to_int(v);
+        else if (key == "--withhold-signal") o.withhold_signal = to_int(v);
+        else if (key == "--skip-combine-done") o.skip_combine_done = to_int(v);
         else if (key == "--expect") o.expect = to_int(v);
         else if (key == "--publish") o.publish = v;
         else if (key == "--seed") o.seed = static_cast<unsigned>(to_int(v));
@@ -299,7 +367,7 @@ int main(int argc, char** argv) {
         return 2;
     }
     // experts only size the counts message here: one local expert per rank
-    w.lay = bep::make_segment_layout(o.ranks, o.channels, o.ranks, 1, o.hidden, o.tokens, o.slots, false);
+    w.lay = bep::make_segment_layout(o.ranks, o.channels, o.ranks, 1, o.hidden, o.tokens, o.slots, o.combine != 0);
     w.rank = std::vector<Rank>(static_cast<std::size_t>(o.ranks));
     for (auto& r : w.rank) r.segment.assign(w.lay.size_bytes + 64, 0);
     std::vector<std::thread> threads;
@@ -312,8 +380,8 @@ int main(int argc, char** argv) {
     int failed = 0;
     for (int r = 0; r < o.ranks; ++r) {
         const int code = w.rank[r].error.load();
-        std::printf("{\"rank\": %d, \"error\": %d, \"context\": %d, \"rows_sent\": %lld, \"rows_received\": %lld}\n", r, code,
-                    w.rank[r].context.load(), w.rank[r].rows_sent, w.rank[r].rows_received);
+        std::printf("{\"rank\": %d, \"error\": %d, \"context\": %d, \"rows_sent\": %lld, \"rows_received\": %lld, \"rows_combined\": %lld}\n", r, code,
+                    w.rank[r].context.load(), w.rank[r].rows_sent, w.rank[r].rows_received, w.rank[r].rows_combined);
         if (code != 0) ++failed;
         // a scenario names the code of the rank that found the fault; the others may end with it, with "a peer
         // aborted", or -- if they were done before the fault mattered to them -- without an error

@@ -1,12 +1,14 @@
-"""Builds and runs the host model of the dispatch protocol (``csrc/model/protocol_model.cpp``).
+"""Builds and runs the host model of the dispatch and combine protocol (``csrc/model/protocol_model.cpp``).
 
     python -m pcie_ep_b200.utils.protocol_model --ranks 4 --slots 2 --epochs 6 --delay-us 20
     python -m pcie_ep_b200.utils.protocol_model --sanitize --publish relaxed        # ThreadSanitizer names the race
     python -m pcie_ep_b200.utils.protocol_model --withhold-counts 1 --timeout-ms 300 --expect 12
+    python -m pcie_ep_b200.utils.protocol_model --combine 1 --withhold-signal 2 --timeout-ms 800 --expect 25
 
 Ranks are threads, segments are host memory with the kernels' own layout, flags are ``std::atomic_ref``: the
 protocol's rules run under ThreadSanitizer, and the failure scenarios that must not be staged on a shared GPU
-(a rank that never sends counts, never returns credit, never hands its staging area back, writes a wrong sequence)
+(a rank that never sends counts, never returns credit, never hands its staging or landing area back, writes a wrong
+sequence, never signals its combine rows)
 run on the CPU.  The program prints one JSON object per rank.
 """
 

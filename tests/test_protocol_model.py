@@ -1,4 +1,4 @@
-"""The host model of the dispatch protocol: rules under ThreadSanitizer, failure scenarios on the CPU.
+"""The host model of the dispatch and combine protocol: rules under ThreadSanitizer, failure scenarios on the CPU.
 
 Ranks are threads over host memory with the kernels' own segment layout.  What the GPU suites may only do with
 withheld flags and short timeouts -- and what they may not do at all, such as a rank that stops handing its
@@ -62,3 +62,29 @@ def test_failure_scenarios_end_in_their_error_code_and_reach_every_rank(fault, c
     assert all(c in (code, 22) for c in codes if c)   # ... and everyone else who failed learned of it as a peer's abort
     if fault != "--corrupt-sequence":
         assert all(c != 0 for c in codes)             # a rank that goes silent stops every rank, within the timeout
+
+
+def test_dispatch_followed_by_its_combine_every_epoch():
+    status, ranks, _ = protocol_model.run(BASE + ["--combine", 1, "--epochs", 8, "--delay-us", 20])
+    assert status == 0 and all(r["error"] == 0 for r in ranks)
+    # an owner reads one landing row per (token, destination rank): exactly the rows it sent
+    assert all(r["rows_combined"] == r["rows_sent"] > 0 for r in ranks)
+
+
+def test_combine_is_race_free_under_thread_sanitizer():
+    """Landing rows are plain stores and loads: the signal and the reuse guard are all that order them."""
+    if not _tsan_works():
+        pytest.skip("ThreadSanitizer is not usable with this compiler")
+    status, ranks, stderr = protocol_model.run(BASE + ["--combine", 1, "--epochs", 4, "--delay-us", 10], sanitize=True)
+    assert "ThreadSanitizer" not in stderr, stderr[-1500:]
+    assert status == 0 and all(r["error"] == 0 and r["rows_combined"] == r["rows_sent"] for r in ranks)
+
+
+@pytest.mark.parametrize("fault,code", [("--withhold-signal", 25), ("--skip-combine-done", 11)])
+def test_combine_failure_scenarios(fault, code):
+    """A rank that never says its combine rows are out stops the owners (signal wait); an owner that never hands its
+    landing area back stops the next epoch's combine at the reuse guard."""
+    status, ranks, _ = protocol_model.run(BASE + ["--combine", 1, "--epochs", 4, fault, 1, "--timeout-ms", 800, "--expect", code])
+    assert status == 0, ranks
+    codes = [r["error"] for r in ranks]
+    assert code in codes and all(c in (code, 22) for c in codes) and all(codes)
