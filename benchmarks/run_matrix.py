@@ -2,6 +2,7 @@
 
     python benchmarks/run_matrix.py bench --gpus 8 --rounds 2                       # the published-style sweep
     python benchmarks/run_matrix.py bench --gpus 8 --modes eager graph_cached --wires bf16 fp8_e4m3 --profiles uniform zipf
+    python benchmarks/run_matrix.py bench --gpus 8 --ablation                       # plus fused against two-step dispatch
     python benchmarks/run_matrix.py validate --gpus 8 --group all
     python benchmarks/run_matrix.py bench --gpus 2 --dry-run                        # print the commands only
 
@@ -66,6 +67,11 @@ def bench_jobs(args: argparse.Namespace, run_dir: Path) -> List[Dict]:
                         command += ["--topk", "4"]  # the frozen non-uniform fixtures are top-4
                     jobs.append({"name": f"round{round_index}/{name}", "log": directory / f"{name}.log", "record": record, "command": command})
                     port += 1
+        if args.ablation:
+            jobs.append({"name": f"round{round_index}/ablation_unfused", "log": directory / "ablation_unfused.log", "record": None,
+                         "command": launcher(args.gpus, port) + ["benchmarks/ablation_unfused.py", "--tokens", *map(str, args.tokens),
+                                                                "--iterations", str(args.iterations)]})
+            port += 1
         if args.nccl and args.gpus > 1:
             jobs.append({"name": f"round{round_index}/nccl", "log": directory / "nccl.log", "record": None,
                          "command": launcher(args.gpus, port) + ["benchmarks/benchmark_nccl.py", "--tokens", *map(str, args.tokens)]})
@@ -219,6 +225,7 @@ def build_parser() -> argparse.ArgumentParser:
             p.add_argument("--wires", nargs="+", default=["bf16"], choices=["bf16", "fp8_e4m3"])
             p.add_argument("--profiles", nargs="+", default=["uniform"], choices=["uniform", "hotspot_20_80", "zipf", "nvidia_calibrated"])
             p.add_argument("--no-nccl", dest="nccl", action="store_false")
+            p.add_argument("--ablation", action="store_true", help="also time the two-step form (unique rows, then a separate scatter pass)")
             p.add_argument("--no-preflight", dest="preflight", action="store_false",
                            help="benchmark even if NVML shows other compute processes or load on the GPUs")
         else:

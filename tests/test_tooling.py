@@ -229,6 +229,9 @@ def test_run_matrix_plans_sequential_jobs_and_records_them(tmp_path):
     ports = [j["command"][j["command"].index("--master-port") + 1] for j in jobs]
     assert len(set(ports)) == len(ports)                               # no two jobs share a rendezvous port
     assert all("--master-addr" in j["command"] and "127.0.0.1" in j["command"] for j in jobs)
+    with_ablation = run_matrix.bench_jobs(parser.parse_args(["bench", "--gpus", "4", "--rounds", "1", "--ablation"]), tmp_path / "unit_2")
+    assert sum("benchmarks/ablation_unfused.py" in j["command"] for j in with_ablation) == 1   # once per round, only on request
+    assert not any("benchmarks/ablation_unfused.py" in j["command"] for j in jobs)
     zipf = [j for j in jobs if j["name"].endswith("eager_bf16_zipf")][0]
     assert zipf["command"][-2:] == ["--topk", "4"] and str(zipf["record"]).endswith("eager_bf16_zipf.json")
 
