@@ -820,9 +820,10 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
             if (!__all_sync(full, have)) {
                 if (issuer) {
                     bulk_wait_group<0>();
-                    ptx::fence_sys();
+                    if (!fence_flags) ptx::fence_sys();
                 }
                 __syncwarp();
+                if (fence_flags) ptx::fence_sys();  // (see the note on the two chains below)
 #pragma unroll
                 for (int i = 0; i < kRing; ++i) {
                     if (flag_ring[i] != nullptr) ptx::st_relaxed_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
@@ -887,13 +888,19 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
         // the fence that follows orders those writes before the flags at system scope.  (Completion of a bulk group
         // alone is not enough: it tells this thread that the writes are done as far as it can see, and with four
         // ranks and BF16 rows a relaxed flag was seen to overtake part of its row on its way through the switch.)
+        // Two chains.  By default the issuing lane fences and the warp barrier carries the order to the lanes that
+        // store the flags (one fence instruction with one active lane; what the litmus and the payload checks ran).
+        // With one fence per row (`fence_flags`: host segments, or the conservative setting for peer segments) every
+        // lane fences after the barrier, so that the fence and the flag store it orders are in the same thread: the
+        // release pattern as the memory model spells it.
         if (since_flags >= flag_batch && n >= kFlagLag) {
             BEP_ROLE_T(t_store);
             if (issuer) {
                 bulk_wait_group<kFlagLag>();
-                ptx::fence_sys();
+                if (!fence_flags) ptx::fence_sys();
             }
             __syncwarp();
+            if (fence_flags) ptx::fence_sys();
 #pragma unroll
             for (int i = 0; i < kRing - kFlagLag; ++i) {
                 if (flag_ring[i] != nullptr) ptx::st_relaxed_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
@@ -918,9 +925,10 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
         BEP_ROLE_T(t_store);
         if (issuer) {
             bulk_wait_group<0>();
-            ptx::fence_sys();
+            if (!fence_flags) ptx::fence_sys();
         }
         __syncwarp();
+        if (fence_flags) ptx::fence_sys();
         if (!broke && !warp_failed(health)) {
 #pragma unroll
             for (int i = 0; i < kRing; ++i)
