@@ -289,6 +289,38 @@ def repeated_check(verify, all_gather, world, rounds=None):
     return verdict, gathered, True
 
 
+FENCE_ENV = "PCIE_EP_B200_FENCE_EVERY_ROW"
+
+
+def verified_buffer(make_buffer, check, world, environ=None):
+    """A buffer whose exchange passed ``check`` (``repeated_check`` bound to the buffer), and the check's record.
+
+    Should the exchange deliver a wrong row, the buffer is rebuilt once with one system-scope fence per row (the
+    conservative way to publish a row; the runtime reads the setting from the environment when it is built) and the
+    record says so under ``conservative_flags``; a second failure, or a failure where nothing is left to fall back
+    to (one rank, or the conservative setting already in force), raises.  Every rank takes the same branch: ``check``
+    returns the same verdict on all of them."""
+    environ = os.environ if environ is None else environ
+    buffer = make_buffer()
+    payload_check, verdicts, fine = check(buffer)
+    conservative = None
+    if not fine and world > 1 and environ.get(FENCE_ENV) != "1":
+        conservative = {"mode": "one system-scope fence per row", "after": [v["problems"] for v in verdicts if not v["ok"]][:2]}
+        try:
+            buffer.close()
+        except Exception:  # noqa: BLE001 - a buffer that failed on the device may refuse an orderly close
+            pass
+        environ[FENCE_ENV] = "1"
+        buffer = make_buffer()
+        payload_check, verdicts, fine = check(buffer)
+    if not fine:
+        raise RuntimeError(f"payload check failed: {[v['problems'] for v in verdicts if not v['ok']]}")
+    payload_check = dict(payload_check, elements_checked_all_ranks=sum(v["elements_checked"] for v in verdicts), rounds=VERIFY_ROUNDS)
+    if conservative is not None:
+        payload_check["conservative_flags"] = conservative
+    return buffer, payload_check
+
+
 def verify_exchange(buffer, rank, world, tokens, topk, idx_cpu, dev_idx, dev_w, device, wire="bf16"):
     """One dispatch + combine with regenerable payload: every received row is compared, on the GPU, with the row
     its (source rank, source token) metadata says it must be; dedup counters are compared with the route volume;
@@ -375,27 +407,9 @@ def run_ours(args, rank, world, local_rank):
             return repeated_check(lambda: verify_exchange(buf, rank, world, tokens, args.topk, idx_cpu, dev_idx, dev_w, device, args.wire),
                                   dist.all_gather_object, world)
 
-        # correctness evidence inside this very run: payload, dedup counters and the round trip (not timed).  Should
-        # the exchange deliver a wrong row, the run is repeated once with one system-scope fence per row (the
-        # conservative way to publish a row) and says so in its result line; a second failure ends it.
-        buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
-        payload_check, verdicts, fine = checked_exchanges(buffer)
-        conservative = None
-        if not fine and world > 1 and os.environ.get("PCIE_EP_B200_FENCE_EVERY_ROW") != "1":
-            conservative = {"mode": "one system-scope fence per row", "after": [v["problems"] for v in verdicts if not v["ok"]][:2]}
-            try:
-                buffer.close()
-            except Exception:  # noqa: BLE001 - a buffer that failed on the device may refuse an orderly close
-                pass
-            os.environ["PCIE_EP_B200_FENCE_EVERY_ROW"] = "1"
-            buffer = HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config)
-            payload_check, verdicts, fine = checked_exchanges(buffer)
-        if not fine:
-            raise RuntimeError(f"payload check failed: {[v['problems'] for v in verdicts if not v['ok']]}")
-        payload_check["elements_checked_all_ranks"] = sum(v["elements_checked"] for v in verdicts)
-        payload_check["rounds"] = VERIFY_ROUNDS
-        if conservative is not None:
-            payload_check["conservative_flags"] = conservative
+        # correctness evidence inside this very run: payload, dedup counters and the round trip (not timed)
+        buffer, payload_check = verified_buffer(lambda: HostStagedEPBuffer(dist.group.WORLD, tokens, HIDDEN, args.topk, EXPERTS, config),
+                                                checked_exchanges, world)
         g = torch.Generator().manual_seed(1234 + rank)
         host_x = [torch.randn(tokens, HIDDEN, generator=g).to(torch.bfloat16).pin_memory() for _ in range(INPUT_SETS)]
         host_idx, host_w = idx_cpu.pin_memory(), w_cpu.pin_memory()
@@ -597,7 +611,7 @@ def run_ours(args, rank, world, local_rank):
             "kernels_per_step": ", ".join(headline["kernels"]),
             "payload_check": headline["payload_check"],
             "payload_check_after": headline.get("payload_check_after"),
-            "flag_publication": ("one system-scope fence per row" if os.environ.get("PCIE_EP_B200_FENCE_EVERY_ROW") == "1"
+            "flag_publication": ("one system-scope fence per row" if os.environ.get(FENCE_ENV) == "1"
                                  else "READY flags of up to eight rows behind one system-scope fence"),
             "impl": "ours",
             "source_fingerprint": source_fingerprint(),

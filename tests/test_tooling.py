@@ -326,3 +326,49 @@ def test_bench_repeated_check_keeps_ranks_in_step_and_stops_at_the_first_bad_rou
 
     verdict, everyone, ok = bench.repeated_check(fine, peer_bad, 2, rounds=3)
     assert not ok and verdict["ok"] is True and everyone[1]["problems"] == ["rows 0..4096 differ"]
+
+
+def test_bench_falls_back_to_the_conservative_publication_once_and_says_so():
+    import bench
+
+    class FakeBuffer:
+        built = 0
+
+        def __init__(self, env):
+            FakeBuffer.built += 1
+            self.conservative = env.get(bench.FENCE_ENV) == "1"   # the runtime reads the setting when it is built
+            self.closed = False
+
+        def close(self):
+            self.closed = True
+            raise RuntimeError("a failed buffer may refuse an orderly close")
+
+    def check(buffer):
+        good = {"ok": True, "rows_checked": 5, "elements_checked": 50, "problems": []}
+        bad = {"ok": False, "rows_checked": 0, "elements_checked": 0, "problems": ["rows 0..4096 differ from their source"]}
+        return (good, [good, good], True) if buffer.conservative else (good, [good, bad], False)
+
+    env = {}
+    made = []
+
+    def make():
+        made.append(FakeBuffer(env))
+        return made[-1]
+
+    buffer, record = bench.verified_buffer(make, check, 2, env)
+    assert len(made) == 2 and made[0].closed and buffer is made[1] and env[bench.FENCE_ENV] == "1"
+    assert record["conservative_flags"]["after"] == [["rows 0..4096 differ from their source"]]
+    assert record["elements_checked_all_ranks"] == 100 and record["rounds"] == bench.VERIFY_ROUNDS and record["ok"]
+
+    # nothing left to fall back to: the conservative setting is already in force, or there is one rank only
+    with pytest.raises(RuntimeError, match="payload check failed"):
+        bench.verified_buffer(make, lambda b: check(made[0]), 2, {bench.FENCE_ENV: "1"})
+    with pytest.raises(RuntimeError, match="payload check failed"):
+        bench.verified_buffer(make, lambda b: check(made[0]), 1, {})
+
+    # the usual case: one buffer, no mention of a fallback
+    env2 = {}
+    made.clear()
+    buffer, record = bench.verified_buffer(make, lambda b: ({"ok": True, "rows_checked": 1, "elements_checked": 7, "problems": []},
+                                                            [{"ok": True, "elements_checked": 7, "problems": []}], True), 1, env2)
+    assert len(made) == 1 and "conservative_flags" not in record and env2 == {} and record["elements_checked_all_ranks"] == 7
