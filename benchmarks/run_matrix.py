@@ -35,7 +35,7 @@ sys.path.insert(0, str(ROOT))
 
 RUN_ID = re.compile(r"^[A-Za-z0-9_-]+$")
 TOKENS = (128, 256, 1024, 4096, 8192)
-GROUPS = ("smoke", "correctness", "faults", "large", "stress", "litmus", "layer", "profiler", "model", "all")
+GROUPS = ("smoke", "correctness", "faults", "large", "stress", "litmus", "layer", "profiler", "path", "model", "all")
 
 
 def launcher(gpus: int, port: int) -> List[str]:
@@ -103,6 +103,8 @@ def validate_jobs(args: argparse.Namespace, run_dir: Path) -> List[Dict]:
             command = pytest + ["-m", "gpu", "tests/test_gpu_gemm.py", "tests/test_gpu_fused_combine.py"]
         elif group == "profiler":
             command = [sys.executable, "benchmarks/analysis_dispatch_profile.py", "--collect", str(run_dir / group / "trace.json"), "--tokens", "1024"]
+        elif group == "path":  # NVLink counters against the deduplicated route volume (needs two GPUs or more)
+            command = launcher(args.gpus, port) + ["benchmarks/nvlink_audit.py", "--tokens", "4096"]
         else:  # model: the host model of the protocol, also under ThreadSanitizer (no GPU)
             command = pytest + ["tests/test_protocol_model.py"]
         job = {"name": group, "log": run_dir / group / "log.txt", "record": None, "command": command}

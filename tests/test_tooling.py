@@ -372,3 +372,46 @@ def test_bench_falls_back_to_the_conservative_publication_once_and_says_so():
     buffer, record = bench.verified_buffer(make, lambda b: ({"ok": True, "rows_checked": 1, "elements_checked": 7, "problems": []},
                                                             [{"ok": True, "elements_checked": 7, "problems": []}], True), 1, env2)
     assert len(made) == 1 and "conservative_flags" not in record and env2 == {} and record["elements_checked_all_ranks"] == 7
+
+
+def test_nvlink_audit_reads_counters_and_judges_the_volume():
+    import types
+
+    import torch
+
+    from benchmarks import nvlink_audit
+    from pcie_ep_b200.ops.reference import route_volume
+
+    class Value:
+        def __init__(self, kib, status=0):
+            self.nvmlReturn = status
+            self.value = types.SimpleNamespace(ullVal=kib)
+
+    class FakeNvml:
+        NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX, NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX = 138, 139
+        asked = None
+
+        def __init__(self, tx, rx, status=0):
+            self.tx, self.rx, self.status = tx, rx, status
+
+        def nvmlDeviceGetFieldValues(self, handle, fields):
+            FakeNvml.asked = fields
+            return [Value(self.tx, self.status), Value(self.rx)]
+
+    assert nvlink_audit.read_counters(FakeNvml(10, 20), object()) == (10240, 20480)
+    assert FakeNvml.asked == [(138, 0xFFFFFFFF), (139, 0xFFFFFFFF)]            # summed over the links, not link 0 alone
+    assert nvlink_audit.read_counters(FakeNvml(10, 20, status=3), object()) is None   # a field the driver does not support
+
+    assert nvlink_audit.judge(1000, 1100, 0.9, 1.3)["ok"] and not nvlink_audit.judge(1000, 1600, 0.9, 1.3)["ok"]
+    assert not nvlink_audit.judge(1000, 500, 0.9, 1.3)["ok"]
+    assert nvlink_audit.judge(0, 4096, 0.9, 1.3)["ok"] and not nvlink_audit.judge(0, 1 << 24, 0.9, 1.3)["ok"]
+    assert nvlink_audit.staged_row_bytes(7168, 8, "bf16") == 14336 + 112 and nvlink_audit.staged_row_bytes(7168, 8, "fp8_e4m3") == 7168 + 112
+
+    # two ranks, four experts: token 0 goes to both ranks, token 1 stays on rank 0, token 2 goes to rank 1 twice (one row)
+    idx0 = torch.tensor([[0, 2], [1, -1], [2, 3]])
+    idx1 = torch.tensor([[0, 1], [3, -1]])
+    per_destination = [nvlink_audit.deliveries_per_destination(i, 2, 4) for i in (idx0, idx1)]
+    assert per_destination == [[2, 2], [1, 1]]
+    volumes = [route_volume(idx0, 0, 2, 4), route_volume(idx1, 1, 2, 4)]
+    assert nvlink_audit.expected_traffic(volumes, 0, per_destination, 100, 10) == (2 * 100 * 10, 1 * 100 * 10)
+    assert nvlink_audit.expected_traffic(volumes, 1, per_destination, 100, 10) == (1 * 100 * 10, 2 * 100 * 10)
