@@ -591,7 +591,9 @@ __device__ __forceinline__ bool place_row(const Ctx& k, int s, int j, int token,
 // `cp.async.bulk.wait_group N` returns to that lane when every group but the N most recent is complete.  That is a
 // statement about what the issuing thread can see; it is not a system-scope release.  So before any READY flag goes out
 // the issuing lane executes `fence.acq_rel.sys`, then `__syncwarp()` hands the order to the destinations' lanes,
-// which store the flags (`st.relaxed.sys`).  On this hardware such a fence waits for every store the SM still has
+// which store the flags (`st.relaxed.sys`).  (With one fence per row -- host segments, or the conservative setting
+// for peer segments -- every lane executes the fence after the `__syncwarp()` instead, so that the fence and the flag
+// store it orders are in one thread.)  On this hardware such a fence waits for every store the SM still has
 // on the wire (measured: 4.4 us when it is paid for every row, against 0.07 us for a flag without it), which is why it
 // is not paid per row: the flags of up to kFlagBatch rows wait in registers and go out behind one fence.  A version
 // that relied on the completion of the bulk group alone passed the two-GPU litmus and every two-GPU run, and then
