@@ -41,40 +41,47 @@
 #include <cstdio>
 #include <map>
 
-#include <pybind11/pybind11.h>
-
 #include "../kernels/protocol.cuh"
 
 namespace bep {
 
-namespace py = pybind11;
+// What a relay is built from.  Plain data: the Python binding fills it from the options dictionary, the host model
+// of the protocol (csrc/model/protocol_model.cpp) fills it directly and runs the relay under ThreadSanitizer.
+struct RelayOptions {
+    int num_ranks = 0, channels = 0, num_experts = 0, num_topk = 0, hidden = 0, num_max_tokens = 0, payload_slots = 0;
+    bool enable_combine = false;
+    int workers = 1;                    // threads per NUMA node that has destinations
+    std::vector<int> cpu_affinity;      // allowed CPUs (empty: the CPUs of the destination's NUMA node)
+    std::vector<int> target_numa_nodes; // NUMA node of every rank's GPU (empty: node 0 for all)
+};
+
+// Progress of one flow (this rank -> dest), as diagnostics() reports it.
+struct RelayFlowState {
+    int dest = 0, numa_node = 0, failure = 0, worker_cpu = -1;
+    std::uint64_t rows_copied = 0, bytes_copied = 0, counts_epoch = 0, combine_rows_copied = 0, acks_forwarded = 0, credit_waits = 0,
+                  drained_epoch = 0;
+};
 
 class NumaRelay {
    public:
-    // options: num_ranks, channels, num_experts, num_topk, hidden, num_max_tokens, payload_slots,
-    //          enable_combine, workers, cpu_affinity (list of allowed CPUs, may be empty)
     // outboxes[d] / targets[d]: host addresses of O(rank->d) and S(d); entries for d == rank are ignored.
-    NumaRelay(const py::dict& options, const std::vector<std::int64_t>& outboxes, const std::vector<std::int64_t>& targets,
-              int rank)
+    NumaRelay(const RelayOptions& options, const std::vector<std::int64_t>& outboxes, const std::vector<std::int64_t>& targets, int rank)
         : rank_(rank) {
-        const int P = options["num_ranks"].cast<int>();
-        lay_ = make_segment_layout(P, options["channels"].cast<int>(), options["num_experts"].cast<int>(),
-                                   options["num_topk"].cast<int>(), options["hidden"].cast<int>(),
-                                   options["num_max_tokens"].cast<int>(), options["payload_slots"].cast<int>(),
-                                   options["enable_combine"].cast<bool>());
+        const int P = options.num_ranks;
+        lay_ = make_segment_layout(P, options.channels, options.num_experts, options.num_topk, options.hidden, options.num_max_tokens,
+                                   options.payload_slots, options.enable_combine);
         ring_mode_ = lay_.slots < lay_.slots_full;
         if (static_cast<int>(outboxes.size()) != P || static_cast<int>(targets.size()) != P)
             throw std::invalid_argument("one outbox and one target per rank");
         own_segment_ = reinterpret_cast<std::uint8_t*>(targets[rank]);
         if (ring_mode_ && own_segment_ == nullptr) throw std::invalid_argument("bounded rings need this rank's own segment (credit checks)");
         std::vector<int> nodes(P, 0);
-        if (options.contains("target_numa_nodes")) {
-            nodes = options["target_numa_nodes"].cast<std::vector<int>>();
+        if (!options.target_numa_nodes.empty()) {
+            nodes = options.target_numa_nodes;
             if (static_cast<int>(nodes.size()) != P) throw std::invalid_argument("one NUMA node per rank");
         }
-        workers_ = std::max(1, options.contains("workers") ? options["workers"].cast<int>() : 1);
-        if (options.contains("cpu_affinity"))
-            for (auto cpu : options["cpu_affinity"].cast<std::vector<int>>()) affinity_.push_back(cpu);
+        workers_ = std::max(1, options.workers);
+        affinity_ = options.cpu_affinity;
         for (int d = 0; d < P; ++d) {
             if (d == rank) continue;
             auto flow = std::make_unique<Flow>();
@@ -123,30 +130,28 @@ class NumaRelay {
 
     void set_delay_ns(std::uint64_t ns) { delay_ns_.store(ns); }
 
-    py::dict diagnostics() const {
-        py::dict d;
-        py::list flows;
+    std::vector<RelayFlowState> flow_states() const {
+        std::vector<RelayFlowState> states;
         for (const auto& flow : flows_) {
-            py::dict f;
-            f["dest"] = flow->dest;
-            f["rows_copied"] = flow->rows_copied.load();
-            f["bytes_copied"] = flow->bytes_copied.load();
-            f["counts_epoch"] = flow->counts_epoch.load();
-            f["combine_rows_copied"] = flow->combine_rows.load();
-            f["failure"] = flow->failure.load();
-            f["worker_cpu"] = flow->worker_cpu.load();
-            f["numa_node"] = flow->numa_node;
-            f["acks_forwarded"] = flow->acks_forwarded.load();
-            f["credit_waits"] = flow->credit_waits.load();
-            f["drained_epoch"] = flow->drained_epoch.load();
-            flows.append(f);
+            RelayFlowState f;
+            f.dest = flow->dest;
+            f.numa_node = flow->numa_node;
+            f.failure = flow->failure.load();
+            f.worker_cpu = flow->worker_cpu.load();
+            f.rows_copied = flow->rows_copied.load();
+            f.bytes_copied = flow->bytes_copied.load();
+            f.counts_epoch = flow->counts_epoch.load();
+            f.combine_rows_copied = flow->combine_rows.load();
+            f.acks_forwarded = flow->acks_forwarded.load();
+            f.credit_waits = flow->credit_waits.load();
+            f.drained_epoch = flow->drained_epoch.load();
+            states.push_back(f);
         }
-        d["flows"] = flows;
-        d["workers"] = static_cast<int>(threads_.size());
-        d["running"] = running_;
-        d["ring_mode"] = ring_mode_;
-        return d;
+        return states;
     }
+    int worker_count() const { return static_cast<int>(threads_.size()); }
+    bool running() const { return running_; }
+    bool ring_mode() const { return ring_mode_; }
 
    private:
     struct Flow {

@@ -19,6 +19,11 @@
 //             wait, `fence.acq_rel.sys`, `st.relaxed.sys`);
 //   relaxed   payload, then a relaxed flag with nothing in between -- wrong, and ThreadSanitizer says so.
 //
+// With --relay 1 the ranks do not write into each other's segments: rank r writes what it would send to rank d into an
+// outbox O(r->d) of its own, and the product's CPU relay (csrc/comm/numa_relay.hpp, the very class the host-staged
+// transport runs) forwards it into d's segment.  The relay's threads then run under ThreadSanitizer together with the
+// scripted ranks: counts, rows, bounded rings with credit, acknowledgements and hand-backs all pass through it.
+//
 // Build: g++ -std=c++20 -O1 -g -pthread [-fsanitize=thread] -I<csrc> -I<cuda include> protocol_model.cpp
 // Output: one JSON object per rank on stdout; exit status 0 when every rank ended as the scenario expects
 // (--expect CODE, default 0).
@@ -28,11 +33,13 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 #include <string>
 #include <thread>
 #include <utility>
 #include <vector>
 
+#include "comm/numa_relay.hpp"
 #include "kernels/protocol.cuh"
 
 namespace {
@@ -51,6 +58,7 @@ struct Options {
     int combine = 0;             // 1: every epoch's dispatch is followed by its combine
     int withhold_signal = -1;    // this rank never signals that its combine rows are out
     int skip_combine_done = -1;  // this rank never hands the combine landing area back
+    int relay = 0;               // 1: remote writes go into outboxes that the product's CPU relay forwards
     int expect = 0;              // error code every failing rank is expected to end with (0: nobody fails)
     std::string publish = "release";
     unsigned seed = 1;
@@ -69,7 +77,14 @@ struct World {
     Options opt;
     SegmentLayout lay;
     std::vector<Rank> rank;
+    std::vector<std::vector<std::uint8_t>> outbox;  // relay mode: [source * ranks + destination], laid out like a segment
+    std::vector<std::unique_ptr<bep::NumaRelay>> relays;
 };
+
+// Where rank `me` writes what is meant for rank `d`: d's segment, or (relay mode) me's outbox for d.
+std::vector<std::uint8_t>& remote(World& w, int me, int d) {
+    return (w.opt.relay && d != me) ? w.outbox[static_cast<std::size_t>(me) * w.opt.ranks + d] : w.rank[d].segment;
+}
 
 std::atomic_ref<std::uint64_t> flag_at(std::vector<std::uint8_t>& seg, std::size_t off) {
     return std::atomic_ref<std::uint64_t>(*reinterpret_cast<std::uint64_t*>(seg.data() + off));
@@ -103,7 +118,7 @@ void fail(World& w, int me, int code, int context) {
     if (w.rank[me].error.compare_exchange_strong(expected, code)) {
         w.rank[me].context.store(context);
         for (int p = 0; p < w.opt.ranks; ++p)
-            flag_at(w.rank[p].segment, w.lay.abort_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(code), std::memory_order_release);
+            flag_at(remote(w, me, p), w.lay.abort_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(code), std::memory_order_release);
     }
 }
 
@@ -201,10 +216,10 @@ void sender(World& w, int me) {
         // counts first: a destination learns how many rows to expect per channel before (or while) they arrive
         if (me != o.withhold_counts) {
             for (int d = 0; d < o.ranks; ++d) {
-                int* msg = reinterpret_cast<int*>(w.rank[d].segment.data() + lay.counts_off) + static_cast<std::size_t>(me) * lay.counts_stride;
+                int* msg = reinterpret_cast<int*>(remote(w, me, d).data() + lay.counts_off) + static_cast<std::size_t>(me) * lay.counts_stride;
                 for (int c = 0; c < o.channels; ++c) msg[o.ranks + lay.num_local_experts + c] = plan.chan_count[static_cast<std::size_t>(c) * o.ranks + d];
                 random_delay(o, rng);
-                flag_at(w.rank[d].segment, lay.counts_flag_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
+                flag_at(remote(w, me, d), lay.counts_flag_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
             }
         }
         for (int t = 0; t < o.tokens; ++t) {
@@ -221,7 +236,7 @@ void sender(World& w, int me) {
                     while (ack.load(std::memory_order_acquire) != want)
                         if (give_up(w, me, deadline, bep::kErrCreditWait, d)) return;
                 }
-                std::uint8_t* row = w.rank[d].segment.data() + lay.stage_off + ring * lay.row_stride;
+                std::uint8_t* row = remote(w, me, d).data() + lay.stage_off + ring * lay.row_stride;
                 auto* payload = reinterpret_cast<std::uint16_t*>(row);
                 for (int col = 0; col < o.hidden; ++col) payload[col] = payload_word(me, t, epoch, col);
                 auto* meta = reinterpret_cast<std::uint32_t*>(row + lay.meta_off);
@@ -229,7 +244,7 @@ void sender(World& w, int me) {
                 meta[2] = static_cast<std::uint32_t>(epoch) + (me == o.corrupt_sequence ? 1u : 0u);
                 meta[3] = static_cast<std::uint32_t>(t) + 1u;
                 random_delay(o, rng);
-                auto ready = flag_at(w.rank[d].segment, lay.ready_off + ring * 8);
+                auto ready = flag_at(remote(w, me, d), lay.ready_off + ring * 8);
                 const std::uint64_t value = bep::make_seq(static_cast<std::uint64_t>(epoch), static_cast<std::uint32_t>(j + 1));
                 if (o.publish == "release") {
                     ready.store(value, std::memory_order_release);
@@ -297,7 +312,7 @@ void receiver(World& w, int me) {
                     if (o.combine) received.emplace_back(s, token);
                     if (lay.slots < lay.slots_full && me != o.withhold_credit) {
                         // credit back to the source (in the source's segment, written by this rank only)
-                        auto ack = flag_at(w.rank[s].segment, lay.ack_off + ((static_cast<std::size_t>(me) * o.channels + c) * lay.slots + static_cast<std::size_t>(j % lay.slots)) * 8);
+                        auto ack = flag_at(remote(w, me, s), lay.ack_off + ((static_cast<std::size_t>(me) * o.channels + c) * lay.slots + static_cast<std::size_t>(j % lay.slots)) * 8);
                         ack.store(bep::make_seq(static_cast<std::uint64_t>(epoch), static_cast<std::uint32_t>(j + 1)), std::memory_order_release);
                     }
                     ++j;
@@ -307,7 +322,7 @@ void receiver(World& w, int me) {
         // the staging area of this epoch has been read: hand it back to every source
         if (me != o.skip_done)
             for (int s = 0; s < o.ranks; ++s)
-                flag_at(w.rank[s].segment, lay.done_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
+                flag_at(remote(w, me, s), lay.done_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
         if (!o.combine) continue;
         // expert side of the combine.  Reuse guard: every owner has read the previous epoch out of its landing area
         const auto guard_deadline = Clock::now() + std::chrono::milliseconds(o.timeout_ms);
@@ -353,6 +368,7 @@ int main(int argc, char** argv) {
         else if (key == "--combine") o.combine = to_int(v);
         else if (key == "--withhold-signal") o.withhold_signal = to_int(v);
         else if (key == "--skip-combine-done") o.skip_combine_done = to_int(v);
+        else if (key == "--relay") o.relay = to_int(v);
         else if (key == "--expect") o.expect = to_int(v);
         else if (key == "--publish") o.publish = v;
         else if (key == "--seed") o.seed = static_cast<unsigned>(to_int(v));
@@ -362,7 +378,8 @@ int main(int argc, char** argv) {
         }
     }
     if (o.ranks < 1 || o.ranks > bep::kMaxRanks || o.channels < 1 || o.tokens < 1 || o.hidden < 8 || o.hidden % 8 != 0 ||
-        (o.publish != "release" && o.publish != "fenced" && o.publish != "relaxed")) {
+        (o.publish != "release" && o.publish != "fenced" && o.publish != "relaxed") ||
+        (o.relay && o.combine)) {  // (the relay forwards the one-kernel combine's per-row flags, which this model does not script)
         std::fprintf(stderr, "bad arguments\n");
         return 2;
     }
@@ -370,13 +387,47 @@ int main(int argc, char** argv) {
     w.lay = bep::make_segment_layout(o.ranks, o.channels, o.ranks, 1, o.hidden, o.tokens, o.slots, o.combine != 0);
     w.rank = std::vector<Rank>(static_cast<std::size_t>(o.ranks));
     for (auto& r : w.rank) r.segment.assign(w.lay.size_bytes + 64, 0);
+    if (o.relay) {
+        w.outbox.assign(static_cast<std::size_t>(o.ranks) * o.ranks, std::vector<std::uint8_t>());
+        for (int s = 0; s < o.ranks; ++s)
+            for (int d = 0; d < o.ranks; ++d)
+                if (s != d) w.outbox[static_cast<std::size_t>(s) * o.ranks + d].assign(w.lay.size_bytes + 64, 0);
+        bep::RelayOptions ro;
+        ro.num_ranks = o.ranks;
+        ro.channels = o.channels;
+        ro.num_experts = o.ranks;
+        ro.num_topk = 1;
+        ro.hidden = o.hidden;
+        ro.num_max_tokens = o.tokens;
+        ro.payload_slots = o.slots;
+        for (int r = 0; r < o.ranks; ++r) {
+            std::vector<std::int64_t> outboxes, targets;
+            for (int d = 0; d < o.ranks; ++d) {
+                outboxes.push_back(d == r ? 0 : reinterpret_cast<std::int64_t>(w.outbox[static_cast<std::size_t>(r) * o.ranks + d].data()));
+                targets.push_back(reinterpret_cast<std::int64_t>(w.rank[d].segment.data()));
+            }
+            w.relays.push_back(std::make_unique<bep::NumaRelay>(ro, outboxes, targets, r));
+            w.relays.back()->start();
+        }
+    }
     std::vector<std::thread> threads;
     for (int r = 0; r < o.ranks; ++r) {
         threads.emplace_back(sender, std::ref(w), r);
         threads.emplace_back(receiver, std::ref(w), r);
     }
     for (auto& t : threads) t.join();
-    bool as_expected = true;
+    long long relayed = 0;
+    int relay_failures = 0;
+    for (auto& relay : w.relays) {
+        relay->stop();
+        for (const bep::RelayFlowState& flow : relay->flow_states()) {
+            relayed += static_cast<long long>(flow.rows_copied);
+            // (199 = stopped with rows pending: what a relay reports when its ranks gave up in a failure scenario)
+            if (flow.failure != 0 && flow.failure != 199) ++relay_failures;
+        }
+    }
+    if (o.relay) std::printf("{\"relay_rows\": %lld, \"relay_failures\": %d}\n", relayed, relay_failures);
+    bool as_expected = relay_failures == 0;
     int failed = 0;
     for (int r = 0; r < o.ranks; ++r) {
         const int code = w.rank[r].error.load();

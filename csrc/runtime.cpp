@@ -122,10 +122,49 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("close", &HostSegment::close);
 
     py::class_<NumaRelay, std::shared_ptr<NumaRelay>>(m, "NumaRelay")
-        .def(py::init<const py::dict&, const std::vector<std::int64_t>&, const std::vector<std::int64_t>&, int>())
+        // options: num_ranks, channels, num_experts, num_topk, hidden, num_max_tokens, payload_slots, enable_combine, and
+        // optionally workers, cpu_affinity (list of allowed CPUs), target_numa_nodes (one per rank)
+        .def(py::init([](const py::dict& options, const std::vector<std::int64_t>& outboxes, const std::vector<std::int64_t>& targets, int rank) {
+            RelayOptions o;
+            o.num_ranks = options["num_ranks"].cast<int>();
+            o.channels = options["channels"].cast<int>();
+            o.num_experts = options["num_experts"].cast<int>();
+            o.num_topk = options["num_topk"].cast<int>();
+            o.hidden = options["hidden"].cast<int>();
+            o.num_max_tokens = options["num_max_tokens"].cast<int>();
+            o.payload_slots = options["payload_slots"].cast<int>();
+            o.enable_combine = options["enable_combine"].cast<bool>();
+            if (options.contains("workers")) o.workers = options["workers"].cast<int>();
+            if (options.contains("cpu_affinity")) o.cpu_affinity = options["cpu_affinity"].cast<std::vector<int>>();
+            if (options.contains("target_numa_nodes")) o.target_numa_nodes = options["target_numa_nodes"].cast<std::vector<int>>();
+            return std::make_shared<NumaRelay>(o, outboxes, targets, rank);
+        }))
         .def("start", &NumaRelay::start)
         .def("stop", &NumaRelay::stop, py::call_guard<py::gil_scoped_release>())
-        .def("diagnostics", &NumaRelay::diagnostics)
+        .def("diagnostics", [](const NumaRelay& relay) {
+            py::dict d;
+            py::list flows;
+            for (const RelayFlowState& flow : relay.flow_states()) {
+                py::dict f;
+                f["dest"] = flow.dest;
+                f["rows_copied"] = flow.rows_copied;
+                f["bytes_copied"] = flow.bytes_copied;
+                f["counts_epoch"] = flow.counts_epoch;
+                f["combine_rows_copied"] = flow.combine_rows_copied;
+                f["failure"] = flow.failure;
+                f["worker_cpu"] = flow.worker_cpu;
+                f["numa_node"] = flow.numa_node;
+                f["acks_forwarded"] = flow.acks_forwarded;
+                f["credit_waits"] = flow.credit_waits;
+                f["drained_epoch"] = flow.drained_epoch;
+                flows.append(f);
+            }
+            d["flows"] = flows;
+            d["workers"] = relay.worker_count();
+            d["running"] = relay.running();
+            d["ring_mode"] = relay.ring_mode();
+            return d;
+        })
         .def("set_delay_ns", &NumaRelay::set_delay_ns);
 
     py::class_<Layout, std::shared_ptr<Layout>>(m, "_Layout")

@@ -4,6 +4,7 @@
     python -m pcie_ep_b200.utils.protocol_model --sanitize --publish relaxed        # ThreadSanitizer names the race
     python -m pcie_ep_b200.utils.protocol_model --withhold-counts 1 --timeout-ms 300 --expect 12
     python -m pcie_ep_b200.utils.protocol_model --combine 1 --withhold-signal 2 --timeout-ms 800 --expect 25
+    python -m pcie_ep_b200.utils.protocol_model --sanitize --relay 1 --slots 2      # the product's CPU relay in the middle
 
 Ranks are threads, segments are host memory with the kernels' own layout, flags are ``std::atomic_ref``: the
 protocol's rules run under ThreadSanitizer, and the failure scenarios that must not be staged on a shared GPU
@@ -43,7 +44,7 @@ def build(sanitize: bool = False) -> Path:
         raise RuntimeError("no g++ on PATH")
     _OUT.mkdir(parents=True, exist_ok=True)
     target = _OUT / ("protocol_model_tsan" if sanitize else "protocol_model")
-    headers = list((_ROOT / "csrc" / "kernels").glob("protocol.cuh")) + [_SOURCE]
+    headers = [_ROOT / "csrc" / "kernels" / "protocol.cuh", _ROOT / "csrc" / "comm" / "numa_relay.hpp", _SOURCE]
     if target.exists() and all(target.stat().st_mtime >= h.stat().st_mtime for h in headers):
         return target
     command = [compiler, "-std=c++20", "-O1", "-g", "-pthread", "-Wno-tsan", "-I" + str(_ROOT / "csrc"), *_cuda_include()]
@@ -56,20 +57,31 @@ def build(sanitize: bool = False) -> Path:
     return target
 
 
-def run(arguments: Sequence[str], sanitize: bool = False, timeout: float = 120.0) -> Tuple[int, List[Dict], str]:
-    """(exit status, one dict per rank, stderr).  Under the sanitizer a reported race makes the status non-zero."""
+def run_with_summary(arguments: Sequence[str], sanitize: bool = False, timeout: float = 120.0) -> Tuple[int, List[Dict], Dict, str]:
+    """(exit status, one dict per rank, the relay's summary line or {}, stderr).  Under the sanitizer a reported race
+    makes the status non-zero."""
     done = subprocess.run([str(build(sanitize)), *map(str, arguments)], capture_output=True, text=True, timeout=timeout)
-    ranks = [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
-    return done.returncode, ranks, done.stderr
+    records = [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+    ranks = [r for r in records if "rank" in r]
+    summary = next((r for r in records if "relay_rows" in r), {})
+    return done.returncode, ranks, summary, done.stderr
+
+
+def run(arguments: Sequence[str], sanitize: bool = False, timeout: float = 120.0) -> Tuple[int, List[Dict], str]:
+    """(exit status, one dict per rank, stderr)."""
+    status, ranks, _, stderr = run_with_summary(arguments, sanitize, timeout)
+    return status, ranks, stderr
 
 
 def main() -> None:
     arguments = sys.argv[1:]
     sanitize = "--sanitize" in arguments
     arguments = [a for a in arguments if a != "--sanitize"]
-    status, ranks, stderr = run(arguments, sanitize)
+    status, ranks, summary, stderr = run_with_summary(arguments, sanitize)
     for rank in ranks:
         print(json.dumps(rank))
+    if summary:
+        print(json.dumps(summary))
     if stderr:
         print(stderr[-3000:], file=sys.stderr)
     raise SystemExit(status)

@@ -88,3 +88,33 @@ def test_combine_failure_scenarios(fault, code):
     assert status == 0, ranks
     codes = [r["error"] for r in ranks]
     assert code in codes and all(c in (code, 22) for c in codes) and all(codes)
+
+
+@pytest.mark.parametrize("slots", [0, 2])
+def test_the_cpu_relay_in_the_middle_forwards_every_remote_row(slots):
+    """``--relay 1``: ranks write into outboxes, the product's ``NumaRelay`` (csrc/comm/numa_relay.hpp) forwards counts,
+    rows, acknowledgements and hand-backs into the destinations' segments."""
+    status, ranks, summary, _ = protocol_model.run_with_summary(BASE[:-4] + ["--slots", slots, "--hidden", 64, "--relay", 1, "--epochs", 6,
+                                                                            "--delay-us", 20])
+    assert status == 0 and all(r["error"] == 0 for r in ranks)
+    assert sum(r["rows_sent"] for r in ranks) == sum(r["rows_received"] for r in ranks)
+    assert summary["relay_failures"] == 0 and 0 < summary["relay_rows"] < sum(r["rows_sent"] for r in ranks)   # local rows bypass it
+
+
+def test_the_cpu_relay_is_race_free_under_thread_sanitizer():
+    """Product code under a race detector: the relay's worker threads against scripted senders and receivers."""
+    if not _tsan_works():
+        pytest.skip("ThreadSanitizer is not usable with this compiler")
+    status, ranks, summary, stderr = protocol_model.run_with_summary(BASE + ["--relay", 1, "--epochs", 4, "--delay-us", 10], sanitize=True)
+    assert "ThreadSanitizer" not in stderr, stderr[-1500:]
+    assert status == 0 and all(r["error"] == 0 for r in ranks) and summary["relay_failures"] == 0
+
+
+@pytest.mark.parametrize("fault,code", [("--withhold-counts", 12), ("--skip-done", 11), ("--withhold-credit", 23)])
+def test_failures_reach_every_rank_through_the_relay(fault, code):
+    """The abort flag is one of the things the relay forwards: a rank that goes silent still stops every rank."""
+    status, ranks, summary, _ = protocol_model.run_with_summary(BASE + ["--relay", 1, "--epochs", 4, fault, 1, "--timeout-ms", 800,
+                                                                        "--expect", code])
+    assert status == 0, ranks
+    codes = [r["error"] for r in ranks]
+    assert code in codes and all(c in (code, 22) for c in codes) and all(codes) and summary["relay_failures"] == 0
