@@ -37,19 +37,25 @@ def _cuda_include() -> List[str]:
     return []
 
 
-def build(sanitize: bool = False) -> Path:
-    """Compile the model with the host compiler (``-fsanitize=thread`` on request); returns the executable."""
+def build(sanitize=False) -> Path:
+    """Compile the model with the host compiler; returns the executable.  ``sanitize``: False, True or ``"thread"``
+    (ThreadSanitizer), ``"address"`` (AddressSanitizer + UndefinedBehaviorSanitizer)."""
     compiler = shutil.which("g++")
     if compiler is None:
         raise RuntimeError("no g++ on PATH")
+    kind = "thread" if sanitize is True else (sanitize or "")
+    if kind not in ("", "thread", "address"):
+        raise ValueError("sanitize is False, True, 'thread' or 'address'")
     _OUT.mkdir(parents=True, exist_ok=True)
-    target = _OUT / ("protocol_model_tsan" if sanitize else "protocol_model")
+    target = _OUT / {"": "protocol_model", "thread": "protocol_model_tsan", "address": "protocol_model_asan"}[kind]
     headers = [_ROOT / "csrc" / "kernels" / "protocol.cuh", _ROOT / "csrc" / "comm" / "numa_relay.hpp", _SOURCE]
     if target.exists() and all(target.stat().st_mtime >= h.stat().st_mtime for h in headers):
         return target
     command = [compiler, "-std=c++20", "-O1", "-g", "-pthread", "-Wno-tsan", "-I" + str(_ROOT / "csrc"), *_cuda_include()]
-    if sanitize:
+    if kind == "thread":
         command.append("-fsanitize=thread")
+    elif kind == "address":
+        command += ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]
     command += [str(_SOURCE), "-o", str(target)]
     done = subprocess.run(command, capture_output=True, text=True)
     if done.returncode != 0:
@@ -57,7 +63,7 @@ def build(sanitize: bool = False) -> Path:
     return target
 
 
-def run_with_summary(arguments: Sequence[str], sanitize: bool = False, timeout: float = 120.0) -> Tuple[int, List[Dict], Dict, str]:
+def run_with_summary(arguments: Sequence[str], sanitize=False, timeout: float = 120.0) -> Tuple[int, List[Dict], Dict, str]:
     """(exit status, one dict per rank, the relay's summary line or {}, stderr).  Under the sanitizer a reported race
     makes the status non-zero."""
     done = subprocess.run([str(build(sanitize)), *map(str, arguments)], capture_output=True, text=True, timeout=timeout)
@@ -67,7 +73,7 @@ def run_with_summary(arguments: Sequence[str], sanitize: bool = False, timeout: 
     return done.returncode, ranks, summary, done.stderr
 
 
-def run(arguments: Sequence[str], sanitize: bool = False, timeout: float = 120.0) -> Tuple[int, List[Dict], str]:
+def run(arguments: Sequence[str], sanitize=False, timeout: float = 120.0) -> Tuple[int, List[Dict], str]:
     """(exit status, one dict per rank, stderr)."""
     status, ranks, _, stderr = run_with_summary(arguments, sanitize, timeout)
     return status, ranks, stderr
@@ -75,8 +81,8 @@ def run(arguments: Sequence[str], sanitize: bool = False, timeout: float = 120.0
 
 def main() -> None:
     arguments = sys.argv[1:]
-    sanitize = "--sanitize" in arguments
-    arguments = [a for a in arguments if a != "--sanitize"]
+    sanitize = "address" if "--sanitize-address" in arguments else "--sanitize" in arguments
+    arguments = [a for a in arguments if a not in ("--sanitize", "--sanitize-address")]
     status, ranks, summary, stderr = run_with_summary(arguments, sanitize)
     for rank in ranks:
         print(json.dumps(rank))

@@ -118,3 +118,14 @@ def test_failures_reach_every_rank_through_the_relay(fault, code):
     assert status == 0, ranks
     codes = [r["error"] for r in ranks]
     assert code in codes and all(c in (code, 22) for c in codes) and all(codes) and summary["relay_failures"] == 0
+
+
+def test_relay_and_combine_under_address_and_undefined_behaviour_sanitizers():
+    try:
+        protocol_model.build("address")
+    except RuntimeError:
+        pytest.skip("AddressSanitizer is not usable with this compiler")
+    for extra in (["--relay", 1], ["--combine", 1]):
+        status, ranks, stderr = protocol_model.run(BASE + extra + ["--epochs", 4, "--delay-us", 5], sanitize="address")
+        assert "Sanitizer" not in stderr and "runtime error" not in stderr, stderr[-1500:]
+        assert status == 0 and all(r["error"] == 0 for r in ranks)
