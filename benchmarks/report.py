@@ -99,7 +99,7 @@ def scaling_table(records: List[Dict]) -> str:
                 raise ValueError(f"lines disagree on config.{key}")
     base = next((r["value"] for r in ours if r["n_gpus"] == 1), None)
     header = ["GPUs", "dispatch+combine us", "dispatch us", "combine us", "end to end us", "fraction of bound (dispatch / combine)",
-              "efficiency vs 1 GPU", "reference us", "reference / ours"]
+              "efficiency vs 1 GPU", "reference us", "reference / ours", "payload check"]
     lines = ["| " + " | ".join(header) + " |", "|" + "---|" * len(header)]
     for r in ours:
         roof = r.get("roofline", {})
@@ -113,8 +113,23 @@ def scaling_table(records: List[Dict]) -> str:
             f"{base / r['value']:.2f}" if base else "-",
             f"{ref['value']:.1f}" if ref else "-",
             f"{ref['value'] / r['value']:.1f}x" if ref else "-",
+            payload_verdict(r),
         ]) + " |")
     return "\n".join(lines)
+
+
+def payload_verdict(record: Dict) -> str:
+    """What a ``bench.py`` line says about its own correctness checks: the verified exchanges before the timed loops, the
+    one after them, and whether the run had to fall back to one fence per row."""
+    before, after = record.get("payload_check"), record.get("payload_check_after")
+    if not isinstance(before, dict):
+        return "-"
+    parts = ["ok" if before.get("ok") else "FAILED"]
+    if isinstance(after, dict):
+        parts.append("after: ok" if after.get("ok") else "after: FAILED")
+    if before.get("conservative_flags"):
+        parts.append("one fence per row (fallback)")
+    return ", ".join(parts)
 
 
 def sweep_table(record: Dict) -> str:

@@ -415,3 +415,13 @@ def test_nvlink_audit_reads_counters_and_judges_the_volume():
     volumes = [route_volume(idx0, 0, 2, 4), route_volume(idx1, 1, 2, 4)]
     assert nvlink_audit.expected_traffic(volumes, 0, per_destination, 100, 10) == (2 * 100 * 10, 1 * 100 * 10)
     assert nvlink_audit.expected_traffic(volumes, 1, per_destination, 100, 10) == (1 * 100 * 10, 2 * 100 * 10)
+
+
+def test_report_shows_what_a_bench_line_says_about_its_payload_checks():
+    from benchmarks import report
+
+    assert report.payload_verdict({}) == "-"
+    assert report.payload_verdict({"payload_check": {"ok": True}}) == "ok"
+    line = {"payload_check": {"ok": True, "conservative_flags": {"mode": "one system-scope fence per row"}},
+            "payload_check_after": {"ok": False, "problems": [["rows 0..4096 differ from their source"]]}}
+    assert report.payload_verdict(line) == "ok, after: FAILED, one fence per row (fallback)"
