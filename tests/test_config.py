@@ -115,5 +115,7 @@ def test_tuned_configurations_fit_the_shared_memory_of_one_cta(ext):
             needed = _C.dispatch_shared_bytes(ranks, cfg.channels, 256, 8, 7168, tokens, 0, cfg.tx_warps, cfg.rx_warps, True,
                                               cfg.pipeline_stages, send_ctas)
             assert needed <= limit, (ranks, tokens, needed)
+            # one CTA per SM and all of them resident at once (the launch is cooperative): a B200 has 148 SMs
+            assert cfg.channels + send_ctas <= 148, (ranks, tokens)
     # more row buffers than fit are reported as such (the runtime then reduces stages, send warps, receive warps)
     assert _C.dispatch_shared_bytes(8, 128, 256, 8, 7168, 4096, 0, 4, 8, True, 4, 0) > limit
