@@ -13,7 +13,8 @@ from pathlib import Path
 
 import pytest
 
-HEADER = (Path(__file__).resolve().parents[1] / "csrc" / "kernels" / "dispatch.cuh").read_text()
+KERNELS = Path(__file__).resolve().parents[1] / "csrc" / "kernels"
+HEADER = (KERNELS / "dispatch_common.cuh").read_text() + (KERNELS / "dispatch_send.cuh").read_text()
 
 
 def constant(name: str) -> int:
