@@ -1,6 +1,6 @@
 // Weighted combine in one cooperative launch per rank (`combine_reduce="inline"`): the inverse of a finished
 // dispatch with the owner-side sum running in the same kernel, so a token's rows are added as they arrive.
-// The default combine is the two ordinary launches of fused_reduce.cuh; this kernel is the variant that starts
+// The default combine is the two ordinary launches of combine_push.cuh and fused_reduce.cuh; this kernel is the variant that starts
 // the owner-side sum before the last row has been pushed, at the price of a cooperative launch.
 //
 // Expert side (send warps): for every row this rank received in the dispatch (the dispatch left an

@@ -6,6 +6,7 @@
 
 #include "combine.cuh"
 #include "dispatch.cuh"
+#include "combine_push.cuh"
 #include "fused_reduce.cuh"
 
 namespace bep {

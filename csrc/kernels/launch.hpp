@@ -6,6 +6,7 @@
 
 #include <cuda_runtime.h>
 
+#include "combine_push.cuh"
 #include "fused_reduce.cuh"
 #include "protocol.cuh"
 
