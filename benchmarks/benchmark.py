@@ -129,11 +129,28 @@ def bench_one(args, tokens: int, rank: int, world: int, device: torch.device):
     record.update(
         dispatch_us_mean=mean_d, dispatch_us_p50=statistics.median(max_d), dispatch_us_min=min(max_d),
         combine_us_mean=statistics.mean(max_c) if args.combine else None,
-        logical_GBps=tokens * args.topk * args.hidden * 2 / mean_d / 1e3,
+        **bandwidth_metrics(record["route_volume"], tokens, args.topk, args.hidden, wire_fp8, mean_d),
         nvlink_roofline_us=remote * row_bytes / NVLINK_GBPS / 1e3,
         nvlink_fraction=(remote * row_bytes / NVLINK_GBPS / 1e3) / mean_d if world > 1 else None,
     )
     return record
+
+
+def bandwidth_metrics(route_volumes, tokens: int, topk: int, hidden: int, wire_fp8: bool, mean_us: float) -> dict:
+    """The reference's bandwidth definitions for one measured dispatch latency (decimal GB/s).
+
+    ``logical_GBps``: ``T*K*H*2 / t`` per GPU -- every top-k branch, before deduplication, no world-size factor (the
+    published comparison metric).  ``remote_delivery_GBps_total`` / ``_per_gpu``: ``F*B / t`` with F the deduplicated
+    (token, destination rank) pairs that leave their rank, summed over the ranks, and B the payload bytes of a row
+    (``2H`` for BF16, ``H + 4`` for the FP8 wire with its scale): what actually crossed the links, metadata and local
+    rows excluded."""
+    payload = hidden + 4 if wire_fp8 else hidden * 2
+    deliveries = sum(v["remote_deliveries"] for v in route_volumes)
+    seconds = mean_us * 1e-6
+    total = deliveries * payload / seconds / 1e9
+    return {"logical_GBps": tokens * topk * hidden * 2 / seconds / 1e9,
+            "remote_delivery_GBps_total": total,
+            "remote_delivery_GBps_per_gpu": total / max(1, len(route_volumes))}
 
 
 def main() -> None:

@@ -425,3 +425,16 @@ def test_report_shows_what_a_bench_line_says_about_its_payload_checks():
     line = {"payload_check": {"ok": True, "conservative_flags": {"mode": "one system-scope fence per row"}},
             "payload_check_after": {"ok": False, "problems": [["rows 0..4096 differ from their source"]]}}
     assert report.payload_verdict(line) == "ok, after: FAILED, one fence per row (fallback)"
+
+
+def test_benchmark_bandwidth_definitions():
+    from benchmarks import benchmark
+
+    volumes = [{"remote_deliveries": 1000}, {"remote_deliveries": 3000}]
+    m = benchmark.bandwidth_metrics(volumes, tokens=4096, topk=8, hidden=7168, wire_fp8=False, mean_us=200.0)
+    assert m["logical_GBps"] == pytest.approx(4096 * 8 * 7168 * 2 / 200e-6 / 1e9)
+    assert m["remote_delivery_GBps_total"] == pytest.approx(4000 * 14336 / 200e-6 / 1e9)
+    assert m["remote_delivery_GBps_per_gpu"] == pytest.approx(m["remote_delivery_GBps_total"] / 2)
+    fp8 = benchmark.bandwidth_metrics(volumes, 4096, 8, 7168, True, 200.0)
+    assert fp8["remote_delivery_GBps_total"] == pytest.approx(4000 * (7168 + 4) / 200e-6 / 1e9)   # codes plus one scale per row
+    assert fp8["logical_GBps"] == m["logical_GBps"]                                                # defined on the BF16 input
