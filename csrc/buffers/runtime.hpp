@@ -323,7 +323,7 @@ class Runtime {
         // one system-scope fence per row: always on host segments; on peer segments only on request (the conservative
         // way to publish a row, PCIE_EP_B200_FENCE_EVERY_ROW=1 -- by default the flags of several rows share a fence)
         const char* every_row = std::getenv("PCIE_EP_B200_FENCE_EVERY_ROW");
-        rc_.fence_flags = (options_.host_segments || (every_row != nullptr && every_row[0] == '1')) ? 1 : 0;
+        rc_.fence_flags = (every_row != nullptr && every_row[0] == '1') ? 2 : (options_.host_segments ? 1 : 0);
         rc_.plan_flags = reinterpret_cast<std::uint64_t*>(plan_flags_.data_ptr<std::int64_t>());
         rc_.unique_cap = P * num_max_tokens;
         rc_.expanded_cap = P * num_max_tokens * std::min(K, lay_.num_local_experts) + lay_.num_local_experts * 255;

@@ -152,6 +152,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) dispatch_kernel(const __grid_c
         k.vec_ok = vec_ok; k.use_tma = use_tma; k.wire_fp8 = rc->wire_fp8 != 0; k.recv_fp8 = recv_fp8;
         k.ring = rc->ring_mode != 0;
         k.fence_flags = rc->fence_flags != 0;
+        k.fence_every_lane = rc->fence_flags == 2;
         k.corrupt_sequence = rc->test_corrupt_sequence != 0;
         k.expanded_cap = rc->expanded_cap;
         k.unique_cap = rc->unique_cap;

@@ -43,7 +43,7 @@ struct Ctx {
     int rx_buffer_base;                // index of the first receive warp's row buffer
     bool vec_ok, use_tma, wire_fp8, recv_fp8, ring;
     bool plan_is_foreign;              // the send warps read a plan that other CTAs write during this launch
-    bool fence_flags, corrupt_sequence;
+    bool fence_flags, fence_every_lane, corrupt_sequence;
     // copies of what the roles read per row from the rank's constants (those live in global memory)
     int expanded_cap, unique_cap;
     std::uint64_t delay_meta_ns, delay_tx_ns, delay_rx_ns, delay_scatter_ns, timeout_ns;

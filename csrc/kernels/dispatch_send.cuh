@@ -31,9 +31,9 @@ namespace detail {
 // `cp.async.bulk.wait_group N` returns to that lane when every group but the N most recent is complete.  That is a
 // statement about what the issuing thread can see; it is not a system-scope release.  So before any READY flag goes out
 // the issuing lane executes `fence.acq_rel.sys`, then `__syncwarp()` hands the order to the destinations' lanes,
-// which store the flags (`st.relaxed.sys`).  (With one fence per row -- host segments, or the conservative setting
-// for peer segments -- every lane executes the fence after the `__syncwarp()` instead, so that the fence and the flag
-// store it orders are in one thread.)  On this hardware such a fence waits for every store the SM still has
+// which store the flags (`st.relaxed.sys`).  (In the conservative setting every lane executes the fence after the
+// `__syncwarp()` instead, so that the fence and the flag store it orders are in one thread.)  On this hardware such a
+// fence waits for every store the SM still has
 // on the wire (measured: 4.4 us when it is paid for every row, against 0.07 us for a flag without it), which is why it
 // is not paid per row: the flags of up to kFlagBatch rows wait in registers and go out behind one fence.  A version
 // that relied on the completion of the bulk group alone passed the two-GPU litmus and every two-GPU run, and then
@@ -60,6 +60,7 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
     // Segments in registered host memory: completion of a bulk group does not mean its writes have reached host
     // memory (they are posted over PCIe), so there the issuing lane does execute the system-scope fence.
     const bool fence_flags = k.fence_flags;
+    const bool fence_every_lane = k.fence_every_lane;
     const unsigned self_bit = 1u << k.me;
     const bool delayed = w == k.send_warps - 1;
     const int P = k.P, K = k.K;
@@ -262,10 +263,10 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
             if (!__all_sync(full, have)) {
                 if (issuer) {
                     bulk_wait_group<0>();
-                    if (!fence_flags) ptx::fence_sys();
+                    if (!fence_every_lane) ptx::fence_sys();
                 }
                 __syncwarp();
-                if (fence_flags) ptx::fence_sys();  // (see the note on the two chains below)
+                if (fence_every_lane) ptx::fence_sys();  // (see the note on the two chains below)
 #pragma unroll
                 for (int i = 0; i < kRing; ++i) {
                     if (flag_ring[i] != nullptr) ptx::st_relaxed_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
@@ -332,17 +333,17 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
         // ranks and BF16 rows a relaxed flag was seen to overtake part of its row on its way through the switch.)
         // Two chains.  By default the issuing lane fences and the warp barrier carries the order to the lanes that
         // store the flags (one fence instruction with one active lane; what the litmus and the payload checks ran).
-        // With one fence per row (`fence_flags`: host segments, or the conservative setting for peer segments) every
-        // lane fences after the barrier, so that the fence and the flag store it orders are in the same thread: the
-        // release pattern as the memory model spells it.
+        // In the conservative setting (`fence_every_lane`, one fence per row as well) every lane fences after the
+        // barrier, so that the fence and the flag store it orders are in the same thread: the release pattern as the
+        // memory model spells it.
         if (since_flags >= flag_batch && n >= kFlagLag) {
             BEP_ROLE_T(t_store);
             if (issuer) {
                 bulk_wait_group<kFlagLag>();
-                if (!fence_flags) ptx::fence_sys();
+                if (!fence_every_lane) ptx::fence_sys();
             }
             __syncwarp();
-            if (fence_flags) ptx::fence_sys();
+            if (fence_every_lane) ptx::fence_sys();
 #pragma unroll
             for (int i = 0; i < kRing - kFlagLag; ++i) {
                 if (flag_ring[i] != nullptr) ptx::st_relaxed_sys(flag_ring[i], make_seq(k.epoch, flag_seq[i]));
@@ -367,10 +368,10 @@ __device__ __noinline__ void send_role_bulk(const Ctx& k, int w, const Health& c
         BEP_ROLE_T(t_store);
         if (issuer) {
             bulk_wait_group<0>();
-            if (!fence_flags) ptx::fence_sys();
+            if (!fence_every_lane) ptx::fence_sys();
         }
         __syncwarp();
-        if (fence_flags) ptx::fence_sys();
+        if (fence_every_lane) ptx::fence_sys();
         if (!broke && !warp_failed(health)) {
 #pragma unroll
             for (int i = 0; i < kRing; ++i)

@@ -195,7 +195,9 @@ struct RankConst {
     int vec_ok;        // hidden*2 is a multiple of 16: 16-byte accesses are legal on rows
     int tx_warps, rx_warps;
     int send_stages;   // shared-memory row buffers per send warp (bulk-copy engine): 2, 3 or 4
-    int fence_flags;   // != 0: a system-scope fence separates a completed bulk group from its READY flags (host segments)
+    int fence_flags;   // READY flags of the send warps: 0 batches of rows behind one system-scope fence; 1 one fence per row, executed
+                       // by the lane that waited for the copies (host segments); 2 one fence per row in every lane that stores a flag
+                       // (the conservative setting)
     int send_ctas;     // CTAs beyond the channel CTAs that do nothing but send (0: the send warps sit in every channel CTA)
     int unique_cap, expanded_cap;
     int slot_smem_bytes;  // shared-memory bytes of one row buffer (TMA path)
