@@ -438,3 +438,46 @@ def test_benchmark_bandwidth_definitions():
     fp8 = benchmark.bandwidth_metrics(volumes, 4096, 8, 7168, True, 200.0)
     assert fp8["remote_delivery_GBps_total"] == pytest.approx(4000 * (7168 + 4) / 200e-6 / 1e9)   # codes plus one scale per row
     assert fp8["logical_GBps"] == m["logical_GBps"]                                                # defined on the BF16 input
+
+
+def test_nccl_log_audit_tells_nvlink_from_shared_memory():
+    from benchmarks import nccl_log_audit as audit
+
+    def log(transport, ranks=2, extra=""):
+        lines = ["NCCL version 2.28.9+cuda12.9"]
+        for r in range(ranks):
+            peer = (r + 1) % ranks
+            lines.append(f"node7:41{r}:500 [{r}] NCCL INFO ncclCommInitRankConfig comm 0x7f00 rank {r} nranks {ranks} cudaDev {r} nvmlDev {r} "
+                         f"busId 1b000 commId 0xdeadbeef - Init COMPLETE")
+            lines.append(f"node7:41{r}:501 [{r}] NCCL INFO Channel 00/0 : {r}[{r}] -> {peer}[{peer}] via {transport}")
+            lines.append(f"node7:41{r}:501 [{r}] NCCL INFO Channel 01/0 : {r}[{r}] -> {peer}[{peer}] via {transport}")
+        return "\n".join(lines) + "\n" + extra
+
+    nvlink = audit.summarise([log("P2P/CUMEM/read", extra="node7:410:502 [0] NCCL INFO Connected NVLS tree\n")])
+    assert nvlink["nccl_versions"] == ["2.28.9"] and nvlink["ranks_initialised"] == 2 and nvlink["communicator_sizes"] == [2]
+    assert nvlink["connection_lines"] == {"P2P": 4} and nvlink["connected_pairs"] == {"P2P": 2} and nvlink["nvls_active"]
+    assert audit.verdict(nvlink, "nvlink", 2) == []
+    assert any("via P2P" in p for p in audit.verdict(nvlink, "shm", 2)) and any("NVLS" in p for p in audit.verdict(nvlink, "shm", 2))
+
+    shm = audit.summarise([log("SHM/direct/direct")])
+    assert audit.verdict(shm, "shm", 2) == [] and any("via SHM" in p for p in audit.verdict(shm, "nvlink", 2))
+    mixed = audit.summarise([log("P2P/IPC"), "node7:9:9 [0] NCCL INFO Channel 00/0 : 0[0] -> 1[1] [send] via NET/Socket/0\n"])
+    assert any("via NET" in p for p in audit.verdict(mixed, "nvlink", 2))
+    assert any("2 of 8 ranks" in p for p in audit.verdict(nvlink, "nvlink", 8))
+    empty = audit.summarise(["nothing of interest\n"])
+    assert any("NCCL_DEBUG=INFO" in p for p in audit.verdict(empty, "nvlink", 2))
+    # nothing that identifies a machine or a process survives
+    assert "node7" not in json.dumps(nvlink) and "deadbeef" not in json.dumps(nvlink)
+
+
+def test_nccl_log_audit_command_line(tmp_path):
+    from benchmarks import nccl_log_audit as audit
+
+    good = tmp_path / "a.log"
+    good.write_text("h:1:2 [0] NCCL INFO comm 0x1 rank 0 nranks 1 cudaDev 0 busId 0 commId 0x2 - Init COMPLETE\n"
+                    "h:1:2 [0] NCCL INFO Channel 00/0 : 0[0] -> 0[0] via P2P/CUMEM\n")
+    assert audit.main(["--expect", "nvlink", "--world", "1", str(good)]) == 0
+    assert audit.main(["--expect", "shm", "--world", "1", str(good)]) == 1
+    bare = tmp_path / "b.log"
+    bare.write_text("no NCCL lines\n")
+    assert audit.main(["--expect", "nvlink", "--world", "1", str(bare)]) == 2
