@@ -23,6 +23,7 @@
 //   199 the relay was stopped while rows were still pending.
 #pragma once
 
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <cstdint>
@@ -82,6 +83,16 @@ class NumaRelay {
         }
         workers_ = std::max(1, options.workers);
         affinity_ = options.cpu_affinity;
+        // Explicit CPUs are a restriction, not a wish: for every NUMA node that has destinations, the CPUs named, the
+        // CPUs of that node (where the platform tells) and the CPUs this process may run on must have one in common.
+        if (!affinity_.empty()) {
+            for (int d = 0; d < P; ++d) {
+                if (d == rank) continue;
+                const int node = nodes[d] < 0 ? 0 : nodes[d];
+                if (worker_cpus(node).empty())
+                    throw std::invalid_argument("relay_cpu_affinity leaves no usable CPU for the workers of NUMA node " + std::to_string(node));
+            }
+        }
         for (int d = 0; d < P; ++d) {
             if (d == rank) continue;
             auto flow = std::make_unique<Flow>();
@@ -208,16 +219,43 @@ class NumaRelay {
         return cpus;
     }
 
-    // Pin the calling worker: to one of the explicitly allowed CPUs if any were given, else to the CPUs of the
-    // destination's NUMA node.  Best effort: a refused affinity call leaves the thread where it is.
+    // Can a thread of this process be pinned to this CPU?  Tried on a short-lived thread of its own, so that nobody's
+    // affinity changes (the calling thread may itself be bound to a few CPUs, which says nothing about what is permitted).
+    static bool cpu_permitted(int cpu) {
+        if (cpu < 0 || cpu >= CPU_SETSIZE) return false;
+        bool ok = false;
+        std::thread([&ok, cpu] {
+            cpu_set_t set;
+            CPU_ZERO(&set);
+            CPU_SET(cpu, &set);
+            ok = pthread_setaffinity_np(pthread_self(), sizeof(set), &set) == 0;
+        }).join();
+        return ok;
+    }
+
+    // Where the workers of one NUMA node run.  With explicit CPUs (`cpu_affinity`): those of them that lie on the node
+    // (where the platform names the node's CPUs) and that this process may use.  Without: the node's CPUs.
+    std::vector<int> worker_cpus(int node) const {
+        const std::vector<int> of_node = node_cpus(node);
+        if (affinity_.empty()) return of_node;
+        std::vector<int> cpus;
+        for (int c : affinity_) {
+            if (!of_node.empty() && std::find(of_node.begin(), of_node.end(), c) == of_node.end()) continue;
+            if (cpu_permitted(c)) cpus.push_back(c);
+        }
+        return cpus;
+    }
+
+    // Pin the calling worker.  With explicit CPUs: to one of them, the workers taking turns.  Without: to the CPUs of
+    // the destination's NUMA node as a set.  Best effort: a refused call leaves the thread where it is.
     void pin(int node, int ordinal) {
+        const std::vector<int> cpus = worker_cpus(node);
+        if (cpus.empty()) return;
         cpu_set_t set;
         CPU_ZERO(&set);
         if (!affinity_.empty()) {
-            CPU_SET(affinity_[ordinal % affinity_.size()], &set);
+            CPU_SET(cpus[static_cast<std::size_t>(ordinal) % cpus.size()], &set);
         } else {
-            const std::vector<int> cpus = node_cpus(node);
-            if (cpus.empty()) return;
             for (int c : cpus) CPU_SET(c, &set);
         }
         pthread_setaffinity_np(pthread_self(), sizeof(set), &set);

@@ -185,3 +185,27 @@ def test_query_numa_pages_counts_every_page(ext):
     placement = ext.query_numa_pages(buf.ctypes.data, buf.nbytes)
     assert sum(placement.values()) in (pages, pages + 1)  # +1 when the array is not page-aligned
     assert all(isinstance(node, int) and node >= -1 for node in placement)
+
+
+def test_explicit_relay_cpus_are_a_restriction_not_a_wish(ext):
+    """``cpu_affinity``: workers run on the named CPUs that lie on the destination's NUMA node and that the process may
+    use; if none is left, construction fails (on every rank alike, through the buffer's agreement round)."""
+    import os
+
+    P, C, E, K, H, TMAX = 2, 2, 8, 2, 64, 8
+    lay = ext.segment_layout(P, C, E, K, H, TMAX, 0, False)
+    size = int(lay["size_bytes"])
+    outbox, target, unused = (np.zeros(size, dtype=np.uint8), np.zeros(size, dtype=np.uint8), np.zeros(8, dtype=np.uint8))
+    options = {"num_ranks": P, "channels": C, "num_experts": E, "num_topk": K, "hidden": H, "num_max_tokens": TMAX,
+               "payload_slots": 0, "enable_combine": False, "workers": 1}
+    pointers = ([unused.ctypes.data, outbox.ctypes.data], [unused.ctypes.data, target.ctypes.data], 0)
+    usable = sorted(os.sched_getaffinity(0))
+    chosen = usable[-1]
+    relay = ext.NumaRelay(dict(options, cpu_affinity=[chosen, 100000]), *pointers)     # an impossible CPU beside a usable one
+    relay.start()
+    try:
+        assert _wait(lambda: relay.diagnostics()["flows"][0]["worker_cpu"] == chosen)
+    finally:
+        relay.stop()
+    with pytest.raises(ValueError, match="no usable CPU"):
+        ext.NumaRelay(dict(options, cpu_affinity=[100000]), *pointers)
