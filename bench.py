@@ -154,6 +154,7 @@ class ClockSampler:
 
         self.device_index = device_index
         self.samples, self.max_clock, self.reasons = [], None, set()
+        self.direct = 0  # samples taken by sample_now()
         self._stop = threading.Event()
         self._thread = None
         self._nvml = None
@@ -198,6 +199,20 @@ class ClockSampler:
                 if value.lower().startswith("active"):
                     self.reasons.add(name)
 
+    def sample_now(self):
+        """One sample on the calling thread.  The timed loops call it right after their last launch, while the GPU
+        still works through the queue: the sampling thread has to win the interpreter lock from a main thread that is
+        busy launching, and with several ranks querying NVML at once a query can take tens of milliseconds, so on its
+        own it may see a short region only once.  Never inside an event pair."""
+        try:
+            if self._nvml is not None:
+                self._sample_nvml()
+            else:
+                self._sample_smi()
+            self.direct += 1
+        except Exception:  # noqa: BLE001 - a failed sample is skipped
+            pass
+
     def _run(self):
         while not self._stop.is_set():
             try:
@@ -220,8 +235,9 @@ class ClockSampler:
         if self._thread is not None:
             self._thread.join(timeout=15)
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_clock,
-                "samples": len(self.samples), "reasons": sorted(self.reasons),
-                "how": "NVML, about 1 ms period, during the timed loop" if self._nvml is not None else "nvidia-smi per sample"}
+                "samples": len(self.samples), "samples_after_last_launch": self.direct, "reasons": sorted(self.reasons),
+                "how": ("NVML, a thread with about 1 ms period during the timed loop plus one query after the last launch of every "
+                        "timed region, while the GPU works through the queue") if self._nvml is not None else "nvidia-smi per sample"}
 
 
 def max_over_ranks(value):
@@ -236,9 +252,10 @@ def max_over_ranks(value):
 REPEATS = 5  # the timed region (exactly --steps steps) is measured this many times; the median is reported
 
 
-def timed_repeats(step, steps, repeats=REPEATS):
+def timed_repeats(step, steps, repeats=REPEATS, sampler=None):
     """Time `steps` calls of step(i) `repeats` times, each bracketed by barrier + synchronize on both sides and a
-    CUDA-event pair on the launching stream.  Returns the per-repeat microseconds per step, max over ranks."""
+    CUDA-event pair on the launching stream.  Returns the per-repeat microseconds per step, max over ranks.  A clock
+    sampler, if given, is asked for one sample after the closing event has been recorded and before the host waits."""
     import torch
     import torch.distributed as dist
 
@@ -251,6 +268,8 @@ def timed_repeats(step, steps, repeats=REPEATS):
         for i in range(steps):
             step(i)
         end.record()
+        if sampler is not None:
+            sampler.sample_now()
         torch.cuda.synchronize()
         dist.barrier()
         samples.append(max_over_ranks(start.elapsed_time(end) * 1000.0 / steps))
@@ -436,7 +455,7 @@ def run_ours(args, rank, world, local_rank):
 
         sampler = ClockSampler(local_rank)
         sampler.start()
-        total_samples = timed_repeats(full_step, steps)
+        total_samples = timed_repeats(full_step, steps, sampler=sampler)
         clocks = sampler.stop()
         dispatch_samples = timed_repeats(dispatch_only, steps, 3)
         buffer.check_errors()
@@ -658,7 +677,7 @@ def run_reference(args, rank, world, local_rank):
 
         sampler = ClockSampler(local_rank)
         sampler.start()
-        samples = timed_repeats(reference_step, args.steps)
+        samples = timed_repeats(reference_step, args.steps, sampler=sampler)
         clocks = sampler.stop()
         buffer.check_errors()
         value = statistics.median(samples)

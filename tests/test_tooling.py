@@ -481,3 +481,29 @@ def test_nccl_log_audit_command_line(tmp_path):
     bare = tmp_path / "b.log"
     bare.write_text("no NCCL lines\n")
     assert audit.main(["--expect", "nvlink", "--world", "1", str(bare)]) == 2
+
+
+def test_bench_clock_sampler_takes_direct_samples_and_reports_them():
+    import bench
+
+    class FakeNvml:
+        NVML_CLOCK_SM = 1
+        calls = 0
+
+        def nvmlDeviceGetClockInfo(self, handle, kind):
+            FakeNvml.calls += 1
+            return 1965 if FakeNvml.calls != 2 else 1410
+
+        def nvmlDeviceGetCurrentClocksEventReasons(self, handle):
+            return 0x4 if FakeNvml.calls == 2 else 0          # the second sample saw the power cap
+
+    sampler = bench.ClockSampler(0)
+    sampler._nvml, sampler._handle, sampler.max_clock = FakeNvml(), object(), 1965.0
+    for _ in range(3):
+        sampler.sample_now()
+    record = sampler.stop()                                    # (the thread was never started)
+    assert record["samples"] == 3 and record["samples_after_last_launch"] == 3
+    assert record["sm_mhz"] == 1965.0 and record["sm_max_mhz"] == 1965.0 and record["reasons"] == ["sw_power_cap"]
+    sampler._nvml = type("Broken", (), {"NVML_CLOCK_SM": 1, "nvmlDeviceGetClockInfo": lambda *a: 1 / 0})()
+    sampler.sample_now()                                       # a failing query is skipped, never raised
+    assert len(sampler.samples) == 3
