@@ -1,6 +1,8 @@
 """Attribute GPU kernels to the API calls that launched them, and audit what runs inside a dispatch / combine.
 
     python benchmarks/analysis_dispatch_profile.py --collect trace.json --tokens 1024     # 1 GPU: record, then analyse
+    python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 \
+        benchmarks/analysis_dispatch_profile.py --collect trace.json --tokens 4096          # every rank runs, rank 0 records
     python benchmarks/analysis_dispatch_profile.py --trace trace.json                     # analyse a saved trace
     python benchmarks/analysis_dispatch_profile.py --roles roles.pt                       # per-role counters (instrumented build)
 
@@ -143,8 +145,12 @@ def summarise_roles(role_profiling: Any, channels: int, send_ctas: int, tx_warps
     return out
 
 
-def collect(path: Path, tokens: int, iterations: int) -> Dict[str, Any]:
-    """Record dispatch + combine of one rank under the torch profiler with ``ep.*`` markers and save the trace."""
+def collect(path: Path, tokens: int, iterations: int) -> Optional[Dict[str, Any]]:
+    """Record dispatch + combine under the torch profiler with ``ep.*`` markers and save rank 0's trace.
+
+    One process: one rank on GPU 0.  Under ``torch.distributed.run`` (RANK / WORLD_SIZE / LOCAL_RANK in the environment):
+    every rank runs the exchange, rank 0 records and returns the trace, the other ranks return None."""
+    import os
     import tempfile
 
     import torch
@@ -153,14 +159,18 @@ def collect(path: Path, tokens: int, iterations: int) -> Dict[str, Any]:
     import bench
     from pcie_ep_b200 import HostStagedConfig, HostStagedEPBuffer
 
-    torch.cuda.set_device(0)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     if not dist.is_initialized():
-        dist.init_process_group("gloo", store=dist.FileStore(tempfile.mktemp(prefix="analysis-store-"), 1), rank=0, world_size=1)
-    config = HostStagedConfig.tuned(1, tokens, timeout_ms=20000, output_pool_size=2)
-    idx, w = bench.make_routes(tokens, 256, 8, 0)
+        if world == 1:
+            dist.init_process_group("gloo", store=dist.FileStore(tempfile.mktemp(prefix="analysis-store-"), 1), rank=0, world_size=1)
+        else:
+            dist.init_process_group("gloo")
+    config = HostStagedConfig.tuned(world, tokens, timeout_ms=20000, output_pool_size=2)
+    idx, w = bench.make_routes(tokens, 256, 8, rank)
     idx, w = idx.cuda(), w.cuda()
     x = torch.randn(tokens, 7168, device="cuda").to(torch.bfloat16)
-    with HostStagedEPBuffer(None, tokens, 7168, 8, 256, config) as buffer:
+    with HostStagedEPBuffer(None if world == 1 else dist.group.WORLD, tokens, 7168, 8, 256, config) as buffer:
         def step() -> None:
             with torch.profiler.record_function("ep.dispatch"):
                 recv_x, _, _, handle, _ = buffer.dispatch(x, idx, w, do_expand=True)
@@ -171,11 +181,15 @@ def collect(path: Path, tokens: int, iterations: int) -> Dict[str, Any]:
         for _ in range(3):
             step()
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA]) as prof:
             for _ in range(iterations):
                 step()
             torch.cuda.synchronize()
         buffer.check_errors()
+    if rank != 0:
+        return None
     prof.export_chrome_trace(str(path))
     return json.loads(Path(path).read_text())
 
@@ -183,7 +197,8 @@ def collect(path: Path, tokens: int, iterations: int) -> Dict[str, Any]:
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     parser.add_argument("--trace", type=Path, help="Chrome trace written by torch.profiler")
-    parser.add_argument("--collect", type=Path, help="record a 1-GPU dispatch + combine trace to this file, then analyse it")
+    parser.add_argument("--collect", type=Path, help="record a dispatch + combine trace to this file (rank 0's, when started with "
+                        "torch.distributed.run on several GPUs), then analyse it")
     parser.add_argument("--tokens", type=int, default=1024)
     parser.add_argument("--iterations", type=int, default=5)
     parser.add_argument("--roles", type=Path, help="torch.save'd dict with role_profiling, channels, send_ctas, tx_warps, rx_warps")
