@@ -1,5 +1,6 @@
 """A complete expert-parallel exchange in forty lines: route, dispatch, run the local experts, combine.
 
+    python examples/moe_exchange.py                                                                       # one rank
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 examples/moe_exchange.py
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 examples/moe_exchange.py --tokens 4096 --hidden 7168
 
@@ -13,6 +14,7 @@ from __future__ import annotations
 import argparse
 import os
 import sys
+import tempfile
 from pathlib import Path
 
 import torch
@@ -31,7 +33,10 @@ def main() -> int:
     parser.add_argument("--topk", type=int, default=4)
     args = parser.parse_args()
 
-    dist.init_process_group("gloo")                         # control plane only: the data plane never uses it on GPUs
+    if "RANK" in os.environ:
+        dist.init_process_group("gloo")                     # control plane only: the data plane never uses it on GPUs
+    else:                                                   # started without a launcher: one rank
+        dist.init_process_group("gloo", store=dist.FileStore(tempfile.mktemp(prefix="moe-exchange-"), 1), rank=0, world_size=1)
     rank, world = dist.get_rank(), dist.get_world_size()
     on_gpu = torch.cuda.is_available()
     if on_gpu:
