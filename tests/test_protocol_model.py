@@ -129,3 +129,13 @@ def test_relay_and_combine_under_address_and_undefined_behaviour_sanitizers():
         status, ranks, stderr = protocol_model.run(BASE + extra + ["--epochs", 4, "--delay-us", 5], sanitize="address")
         assert "Sanitizer" not in stderr and "runtime error" not in stderr, stderr[-1500:]
         assert status == 0 and all(r["error"] == 0 for r in ranks)
+
+
+@pytest.mark.parametrize("ranks,extra", [(8, ["--combine", 1, "--slots", 2]), (16, ["--relay", 1, "--slots", 0])])
+def test_the_rank_counts_of_a_full_node_and_of_the_limit(ranks, extra):
+    """Eight ranks (a node) with the combine, sixteen (the protocol's limit) through the relay: the segment layout's strides
+    and the per-rank flag slots at the sizes the single-digit cases never reach."""
+    status, ranks_out, _ = protocol_model.run(["--ranks", ranks, "--channels", 2, "--tokens", 32, "--hidden", 64, "--epochs", 3] + extra,
+                                              timeout=300)
+    assert status == 0 and len(ranks_out) == ranks and all(r["error"] == 0 for r in ranks_out)
+    assert sum(r["rows_sent"] for r in ranks_out) == sum(r["rows_received"] for r in ranks_out) > 0
