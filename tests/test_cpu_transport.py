@@ -22,7 +22,7 @@ def run_workers(world, *extra, timeout=300):
     return proc.stdout
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_cpu_transport_correctness(world):
     run_workers(world, "--transport", "cpu", "--suite", "correctness", "--hidden", "64", "--small")
 
