@@ -299,8 +299,9 @@ def repeated_check(verify, all_gather, world, rounds=None):
     for _ in range(VERIFY_ROUNDS if rounds is None else rounds):
         try:
             verdict = verify()
-        except RuntimeError as exc:  # an error word from the device: this buffer is finished
-            verdict = {"ok": False, "rows_checked": 0, "elements_checked": 0, "problems": [str(exc)[:200]]}
+        except Exception as exc:  # noqa: BLE001 - an error word from the device (this buffer is finished) or anything else
+            # that went wrong on this rank alone: it becomes this rank's verdict, so that every rank still reaches the gather
+            verdict = {"ok": False, "rows_checked": 0, "elements_checked": 0, "problems": [f"{type(exc).__name__}: {exc}"[:200]]}
         gathered = [None] * world
         all_gather(gathered, verdict)
         if not all(v["ok"] for v in gathered):
