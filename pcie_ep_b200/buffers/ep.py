@@ -41,22 +41,10 @@ class HostStagedEPBuffer:
     caller (the internal lock protects bookkeeping, not the order of your launches).
     """
 
-    def __init__(
-        self,
-        group: Any = None,
-        num_max_tokens_per_rank: int = 0,
-        hidden: int = 0,
-        num_topk: int = 0,
-        num_experts: int = 0,
-        config: Optional[HostStagedConfig] = None,
-        *,
-        control_group: Any = None,
-        host_staged_config: Optional[HostStagedConfig] = None,
-        transport: Optional[str] = None,
-        deterministic: bool = True,
-        require_reuse_nccl_comm: bool = False,
-        explicitly_destroy: bool = False,
-    ) -> None:
+    def __init__(self, group: Any = None, num_max_tokens_per_rank: int = 0, hidden: int = 0, num_topk: int = 0, num_experts: int = 0,
+                 config: Optional[HostStagedConfig] = None, *, control_group: Any = None,
+                 host_staged_config: Optional[HostStagedConfig] = None, transport: Optional[str] = None, deterministic: bool = True,
+                 require_reuse_nccl_comm: bool = False, explicitly_destroy: bool = False) -> None:
         if not dist.is_initialized():
             raise RuntimeError("Initialize torch.distributed (init_process_group) before building an EP buffer")
         if config is not None and host_staged_config is not None:
@@ -201,28 +189,12 @@ class HostStagedEPBuffer:
         self._watchdog = watchdog
 
     # ------------------------------------------------------------------ dispatch
-    def dispatch(
-        self,
-        x: torch.Tensor,
-        topk_idx: Optional[torch.Tensor] = None,
-        topk_weights: Optional[torch.Tensor] = None,
-        cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
-        num_experts: Optional[int] = None,
-        num_max_tokens_per_rank: Optional[int] = None,
-        expert_alignment: Optional[int] = None,
-        num_sms: int = 0,
-        num_qps: int = 0,
-        previous_event: Any = None,
-        async_with_compute_stream: bool = False,
-        allocate_on_comm_stream: bool = False,
-        handle: Any = None,
-        do_handle_copy: bool = False,
-        do_cpu_sync: Optional[bool] = False,
-        do_expand: bool = False,
-        do_zero_padding: bool = False,
-        use_tma_aligned_col_major_sf: bool = False,
-        defer_epilogue: bool = False,
-    ) -> Any:
+    def dispatch(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None,
+                 cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None, num_experts: Optional[int] = None,
+                 num_max_tokens_per_rank: Optional[int] = None, expert_alignment: Optional[int] = None, num_sms: int = 0, num_qps: int = 0,
+                 previous_event: Any = None, async_with_compute_stream: bool = False, allocate_on_comm_stream: bool = False,
+                 handle: Any = None, do_handle_copy: bool = False, do_cpu_sync: Optional[bool] = False, do_expand: bool = False,
+                 do_zero_padding: bool = False, use_tma_aligned_col_major_sf: bool = False, defer_epilogue: bool = False) -> Any:
         """Send every token to the ranks that own its experts; sender and receiver deduplicated.
 
         ``x`` is contiguous BF16 ``[T, hidden]``, ``topk_idx`` int64 ``[T, K]`` of global expert ids
@@ -288,19 +260,9 @@ class HostStagedEPBuffer:
             raise ValueError(f"{purpose}: the handle comes from another buffer, or from before this buffer was rebuilt")
 
     # ------------------------------------------------------------------ combine
-    def combine(
-        self,
-        x: torch.Tensor,
-        handle: HostStagedEPHandle,
-        topk_weights: Optional[torch.Tensor] = None,
-        *,
-        out: Optional[torch.Tensor] = None,
-        weighted: Optional[bool] = None,
-        previous_event: Any = None,
-        async_with_compute_stream: bool = False,
-        allocate_on_comm_stream: bool = False,
-        num_sms: int = 0,
-    ) -> Any:
+    def combine(self, x: torch.Tensor, handle: HostStagedEPHandle, topk_weights: Optional[torch.Tensor] = None, *,
+                out: Optional[torch.Tensor] = None, weighted: Optional[bool] = None, previous_event: Any = None,
+                async_with_compute_stream: bool = False, allocate_on_comm_stream: bool = False, num_sms: int = 0) -> Any:
         """Return the expert outputs to their source tokens: the inverse of ``dispatch``.
 
         ``x`` holds this rank's expert outputs in the layout of the dispatch's ``recv_x``

@@ -104,17 +104,9 @@ def _agreed(step: Callable[[], Any], owner: Any, what: str, undo: Callable[[], N
     return value
 
 
-def capture_dispatch(
-    owner: Any,
-    x: torch.Tensor,
-    topk_idx: Optional[torch.Tensor] = None,
-    topk_weights: Optional[torch.Tensor] = None,
-    *,
-    handle: Any = None,
-    do_expand: bool = False,
-    expert_alignment: Optional[int] = None,
-    do_zero_padding: bool = False,
-) -> GraphDispatch:
+def capture_dispatch(owner: Any, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None, topk_weights: Optional[torch.Tensor] = None, *,
+                     handle: Any = None, do_expand: bool = False, expert_alignment: Optional[int] = None,
+                     do_zero_padding: bool = False) -> GraphDispatch:
     """Collective.  Validates, synchronises the device, captures one dispatch into the buffer's graph pool.
 
     Both phases end in an agreement round over the control group: a rank whose arguments are wrong, or
