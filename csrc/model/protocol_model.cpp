@@ -8,7 +8,9 @@
 // back, writes a wrong sequence, never signals that its combine rows are out, never hands the landing area back) run
 // here instead.
 //
-// Combine (--combine 1), the form with a separate owner-side sum: the rank that received a token's row for epoch e
+// Combine (--combine 1; with --relay 1 the one-kernel form instead, whose per-row flags the relay forwards: a flag per
+// (expert rank, token) follows each landing row and the owner waits for the flags of the rows it reads), by default
+// the form with a separate owner-side sum: the rank that received a token's row for epoch e
 // writes one result row into the owner's landing area [rank][token], behind the reuse guard `cdone >= e - 1` of every
 // owner; when all its rows are out it releases `csig = e` to every owner.  An owner acquires every peer's `csig`,
 // reads the landing rows of the ranks each token went to, and releases `cdone = e` to every peer.
@@ -169,15 +171,23 @@ bool combine_owner(World& w, int me, int epoch) {
     // between the expert side's reuse guard (which a missing signal may be the consequence of) and the next epoch's
     // counts wait (which is the consequence of an owner stuck here)
     const auto deadline = Clock::now() + std::chrono::milliseconds(o.timeout_ms + o.timeout_ms / 16);
-    for (int r = 0; r < o.ranks; ++r) {
-        auto sig = flag_at(w.rank[me].segment, lay.csig_off + static_cast<std::size_t>(r) * bep::kFlagStride);
-        while (sig.load(std::memory_order_acquire) < static_cast<std::uint64_t>(epoch))
-            if (give_up(w, me, deadline, bep::kErrFusedSignalWait, r)) return false;
+    if (!o.relay) {
+        for (int r = 0; r < o.ranks; ++r) {
+            auto sig = flag_at(w.rank[me].segment, lay.csig_off + static_cast<std::size_t>(r) * bep::kFlagStride);
+            while (sig.load(std::memory_order_acquire) < static_cast<std::uint64_t>(epoch))
+                if (give_up(w, me, deadline, bep::kErrFusedSignalWait, r)) return false;
+        }
     }
     for (int t = 0; t < o.tokens; ++t) {
         const unsigned mask = route_mask(o, me, t, epoch);
         for (int r = 0; r < o.ranks; ++r) {
             if (!(mask >> r & 1u)) continue;
+            if (o.relay) {
+                // the one-kernel form of the combine, the one the relay forwards: a flag per (expert rank, token)
+                auto ready = flag_at(w.rank[me].segment, lay.cready_off + (static_cast<std::size_t>(r) * o.tokens + t) * 8);
+                while (ready.load(std::memory_order_acquire) < static_cast<std::uint64_t>(epoch))
+                    if (give_up(w, me, deadline, bep::kErrRowWait, r)) return false;
+            }
             const auto* row = reinterpret_cast<const std::uint16_t*>(w.rank[me].segment.data() + lay.cstage_off +
                                                                      (static_cast<std::size_t>(r) * o.tokens + t) * lay.crow_stride);
             for (int col = 0; col < o.hidden; ++col) {
@@ -191,7 +201,7 @@ bool combine_owner(World& w, int me, int epoch) {
     }
     if (me != o.skip_combine_done)
         for (int p = 0; p < o.ranks; ++p)
-            flag_at(w.rank[p].segment, lay.cdone_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
+            flag_at(remote(w, me, p), lay.cdone_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
     return true;
 }
 
@@ -332,12 +342,14 @@ void receiver(World& w, int me) {
                 if (give_up(w, me, guard_deadline, bep::kErrReuseGuardWait, p)) return;
         }
         for (const auto& [s, token] : received) {
-            auto* row = reinterpret_cast<std::uint16_t*>(w.rank[s].segment.data() + lay.cstage_off +
+            auto* row = reinterpret_cast<std::uint16_t*>(remote(w, me, s).data() + lay.cstage_off +
                                                          (static_cast<std::size_t>(me) * o.tokens + token) * lay.crow_stride);
             for (int col = 0; col < o.hidden; ++col) row[col] = static_cast<std::uint16_t>(payload_word(s, token, epoch, col) + me);
             random_delay(o, rng);
+            if (o.relay && me != o.withhold_signal)  // per-row flag: the relay forwards the row, then the flag
+                flag_at(remote(w, me, s), lay.cready_off + (static_cast<std::size_t>(me) * o.tokens + token) * 8).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
         }
-        if (me != o.withhold_signal)
+        if (!o.relay && me != o.withhold_signal)
             for (int p = 0; p < o.ranks; ++p)
                 flag_at(w.rank[p].segment, lay.csig_off + static_cast<std::size_t>(me) * bep::kFlagStride).store(static_cast<std::uint64_t>(epoch), std::memory_order_release);
     }
@@ -378,8 +390,7 @@ int main(int argc, char** argv) {
         }
     }
     if (o.ranks < 1 || o.ranks > bep::kMaxRanks || o.channels < 1 || o.tokens < 1 || o.hidden < 8 || o.hidden % 8 != 0 ||
-        (o.publish != "release" && o.publish != "fenced" && o.publish != "relaxed") ||
-        (o.relay && o.combine)) {  // (the relay forwards the one-kernel combine's per-row flags, which this model does not script)
+        (o.publish != "release" && o.publish != "fenced" && o.publish != "relaxed")) {
         std::fprintf(stderr, "bad arguments\n");
         return 2;
     }
@@ -400,6 +411,7 @@ int main(int argc, char** argv) {
         ro.hidden = o.hidden;
         ro.num_max_tokens = o.tokens;
         ro.payload_slots = o.slots;
+        ro.enable_combine = o.combine != 0;
         for (int r = 0; r < o.ranks; ++r) {
             std::vector<std::int64_t> outboxes, targets;
             for (int d = 0; d < o.ranks; ++d) {

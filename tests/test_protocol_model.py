@@ -139,3 +139,25 @@ def test_the_rank_counts_of_a_full_node_and_of_the_limit(ranks, extra):
                                               timeout=300)
     assert status == 0 and len(ranks_out) == ranks and all(r["error"] == 0 for r in ranks_out)
     assert sum(r["rows_sent"] for r in ranks_out) == sum(r["rows_received"] for r in ranks_out) > 0
+
+
+def test_the_relay_forwards_the_combine_rows_and_their_flags():
+    """``--relay 1 --combine 1``: landing rows and their per-row flags (the one-kernel form of the combine, the one the relay
+    serves) and the hand-back of the landing area all pass through the relay's threads -- also under ThreadSanitizer."""
+    status, ranks, summary, _ = protocol_model.run_with_summary(BASE + ["--relay", 1, "--combine", 1, "--epochs", 5, "--delay-us", 10])
+    assert status == 0 and all(r["error"] == 0 and r["rows_combined"] == r["rows_sent"] > 0 for r in ranks) and summary["relay_failures"] == 0
+    if _tsan_works():
+        status, ranks, _, stderr = protocol_model.run_with_summary(BASE + ["--relay", 1, "--combine", 1, "--epochs", 3, "--delay-us", 10],
+                                                                   sanitize=True)
+        assert "ThreadSanitizer" not in stderr, stderr[-1500:]
+        assert status == 0 and all(r["error"] == 0 for r in ranks)
+
+
+@pytest.mark.parametrize("fault,code", [("--withhold-signal", 15), ("--skip-combine-done", 11)])
+def test_combine_failures_through_the_relay(fault, code):
+    """Per-row flags that never come end the owners' row wait; a landing area never handed back ends the next reuse guard."""
+    status, ranks, _, _ = protocol_model.run_with_summary(BASE + ["--relay", 1, "--combine", 1, "--epochs", 4, fault, 1, "--timeout-ms", 800,
+                                                                  "--expect", code])
+    assert status == 0, ranks
+    codes = [r["error"] for r in ranks]
+    assert code in codes and all(c in (code, 22) for c in codes) and all(codes)
